@@ -1,0 +1,899 @@
+// C ABI of the decode path: builds stage programs on the host and launches the persistent
+// interpreter (fsvd_kernel.cuh).  No torch types; see include/flashsvd_b200.h.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "../../include/flashsvd_b200.h"
+#include "fsvd_stage.h"
+
+using namespace fsvd;
+
+static constexpr int kRowsPerTile = 4;
+static constexpr int kRowBytes = 1024;
+static constexpr int kSlotBytes = kRowsPerTile * kRowBytes;
+
+// ------------------------------------------------------------------------------- errors
+static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+static unsigned long long* g_trace = nullptr;
+static size_t g_trace_bytes = 0;
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+#define CUDA_TRY(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (expr);                                                             \
+    if (e_ != cudaSuccess)                                                               \
+      return fail(FSVD_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));        \
+  } while (0)
+
+// ------------------------------------------------------------------------------- geometry
+struct LaunchCfg {
+  int nw, nd, direct, grid, inflight;
+};
+static LaunchCfg g_cfg = {0, 0, 0, 0, 0};
+static std::once_flag g_cfg_once;
+
+static int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+static void cfg_from_env() {
+  g_cfg.nw = env_int("FSVD_NW", 16);
+  g_cfg.nd = env_int("FSVD_ND", 3);
+  g_cfg.direct = env_int("FSVD_DIRECT", 0);
+  g_cfg.grid = env_int("FSVD_GRID", 0);
+  g_cfg.inflight = env_int("FSVD_INFLIGHT", 1);
+}
+static LaunchCfg current_cfg() {
+  std::call_once(g_cfg_once, cfg_from_env);
+  return g_cfg;
+}
+
+struct DevProps {
+  int device = -1, sms = 0, smem_optin = 0;
+};
+static int get_props(DevProps& p) {
+  static DevProps cache[16];
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 16 && cache[dev].device == dev) {
+    p = cache[dev];
+    return 0;
+  }
+  p.device = dev;
+  CUDA_TRY(cudaDeviceGetAttribute(&p.sms, cudaDevAttrMultiProcessorCount, dev));
+  CUDA_TRY(cudaDeviceGetAttribute(&p.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+  if (dev >= 0 && dev < 16) cache[dev] = p;
+  return 0;
+}
+
+static constexpr int hdr_bytes(int nw, int nd) { return smem_header_bytes(nw, nd); }
+
+// ------------------------------------------------------------------------------- kernel table
+// The kernel instantiations live in fsvd_inst_*.cu (one translation unit per element type and
+// batch width, so they compile in parallel); each exports a table of launchers.
+#include "fsvd_launch.h"
+extern const KernelEntry g_kernels_bf16_b1[];
+extern const KernelEntry g_kernels_bf16_b4[];
+extern const KernelEntry g_kernels_f32_b1[];
+extern const KernelEntry g_kernels_f32_b4[];
+static const KernelEntry* const g_kernel_tables[] = {g_kernels_bf16_b1, g_kernels_bf16_b4,
+                                                     g_kernels_f32_b1, g_kernels_f32_b4};
+
+// Resolved launch: kernel + sizes for a given dtype / batch / vector length.
+struct Resolved {
+  LaunchFn fn = nullptr;
+  int nw = 0, nd = 0, bulk = 0, grid = 0, nb = 0, inflight = 0;
+  size_t smem = 0;
+  int total_warps() const { return grid * nw; }
+};
+
+static int resolve(int dtype, int B, int max_vec_len, Resolved& r) {
+  const LaunchCfg c = current_cfg();
+  DevProps p;
+  if (int e = get_props(p)) return e;
+  if (B < 1 || B > 4) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..4)", B);
+  const int nb = B == 1 ? 1 : 4;
+  const int esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
+  const size_t vec = (size_t)B * ((max_vec_len + 7) / 8 * 8) * esize;
+  r.grid = c.grid > 0 ? (c.grid < p.sms ? c.grid : p.sms) : p.sms;
+  r.nb = nb;
+  r.inflight = c.inflight;
+  // Prefer the requested warp count with the most slots (not above the request) that fit in
+  // shared memory next to the staged vector; otherwise any variant that fits.
+  const KernelEntry* best = nullptr;
+  for (int pass = 0; pass < 2 && !best; ++pass) {
+    for (const KernelEntry* tab : g_kernel_tables)
+    for (const KernelEntry* kp = tab; kp->fn; ++kp) {
+      const KernelEntry& k = *kp;
+      if (k.dtype != dtype || k.nb != nb || k.bulk != (c.direct ? 0 : 1)) continue;
+      if (pass == 0 && (k.nw != c.nw || (k.bulk && k.nd > c.nd))) continue;
+      const size_t need = hdr_bytes(k.nw, k.nd) + (k.bulk ? (size_t)k.nw * k.nd * kSlotBytes : 0) + vec;
+      if (need > (size_t)p.smem_optin) continue;
+      if (!best || k.nd > best->nd) best = &k;
+    }
+  }
+  if (!best)
+    return fail(FSVD_ERR_UNSUPPORTED, "no kernel variant fits: vector of %zu bytes, %d bytes of shared memory",
+                vec, p.smem_optin);
+  r.fn = best->fn;
+  r.nw = best->nw;
+  r.nd = best->nd;
+  r.bulk = best->bulk;
+  r.smem = hdr_bytes(best->nw, best->nd) + (best->bulk ? (size_t)best->nw * best->nd * kSlotBytes : 0) + vec;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------- workspace
+static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
+constexpr int kMaxSegs = 8;
+constexpr int kMaxSplit = 32;
+constexpr size_t kCounterBytes = 4096;  // B * Hk ints, B <= 4
+
+struct WsLayout {
+  size_t sync, pa, pb, hact, qbuf, attn, hidden, part_acc, part_ml, counters, total;
+};
+static int imax(int a, int b) { return a > b ? a : b; }
+
+static WsLayout ws_layout(const fsvd_dims& D) {
+  WsLayout L;
+  size_t o = 0;
+  const int B = D.B;
+  const int maxrank = imax(imax(D.Rq + D.Rk + D.Rv, D.Ru + D.Rg), imax(D.Ro, D.Rd));
+  // The barrier words and the attention arrival counters sit at fixed offsets, whatever the
+  // shapes: every entry point that shares one workspace finds them where the others left them
+  // (zero between launches).
+  L.sync = o;      o += al256(sizeof(SyncState));
+  L.counters = o;  o += kCounterBytes;
+  // pa, pb, hact, attn and hidden hold (fp32, tag) pairs: 8 bytes per element
+  L.pa = o;        o += al256((size_t)kMaxSegs * B * maxrank * 8);
+  L.pb = o;        o += al256((size_t)kMaxSegs * B * maxrank * 8);
+  L.hact = o;      o += al256((size_t)B * imax(D.I, 8) * 8);
+  L.qbuf = o;      o += al256((size_t)B * D.H * D.Dh * 4);
+  L.attn = o;      o += al256((size_t)B * D.H * D.Dh * 8);
+  L.hidden = o;    o += al256((size_t)B * D.d * 8);
+  L.part_acc = o;  o += al256((size_t)B * D.H * kMaxSplit * D.Dh * 4);
+  L.part_ml = o;   o += al256((size_t)B * D.H * kMaxSplit * 2 * 4);
+  L.total = o;
+  return L;
+}
+
+// ------------------------------------------------------------------------------- builder
+struct Builder {
+  std::vector<Stage> st;
+  int TW, KC, B, esize;
+  long long cum = 0;
+  int max_vec = 8;
+
+  Builder(const Resolved& r, int dtype, int B_) {
+    TW = r.total_warps();
+    esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
+    KC = kRowBytes / esize;
+    B = B_;
+  }
+  Stage blank() {
+    Stage s;
+    memset(&s, 0, sizeof(s));
+    s.B = B;
+    s.segs = 1;
+    return s;
+  }
+  void finish_items(Stage& s, long long items) {
+    s.rot = (int)(cum % TW);
+    cum += items;
+  }
+  // generic GEMV stage; segs chosen when split_k
+  Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k) {
+    Stage s = blank();
+    s.type = ST_GEMV;
+    s.WA = WA;
+    s.WB = WB;
+    s.P = P;
+    s.K = K;
+    s.ldw = ldw;
+    const int groups = (P + kRowsPerTile - 1) / kRowsPerTile;
+    int segs = 1;
+    if (split_k) {
+      const int maxsegs = imax(1, (K + KC - 1) / KC) < kMaxSegs ? imax(1, (K + KC - 1) / KC) : kMaxSegs;
+      while (segs < maxsegs && (long long)groups * segs * 10 < (long long)TW * 9) ++segs;
+    }
+    int kseg = (K + segs - 1) / segs;
+    kseg = (kseg + KC - 1) / KC * KC;
+    segs = (K + kseg - 1) / kseg;
+    s.segs = segs;
+    s.kseg = kseg;
+    finish_items(s, (long long)groups * segs);
+    st.push_back(s);
+    return st.back();
+  }
+  // Input vector from a caller tensor or a buffer that is complete when the stage starts.
+  void vec(Stage& s, int mode, const void* src, int len, int nseg, bool barrier) {
+    s.vl_mode = mode;
+    s.vl_src = src;
+    s.vl_len = len;
+    s.vl_nseg = nseg;
+    if (barrier) s.flags |= SF_BARRIER;
+    if (len > max_vec) max_vec = len;
+  }
+  // Input vector of (fp32, tag) pairs produced by stage `producer` of this program: the
+  // consumer polls the tags, no barrier.
+  void vec_tagged(Stage& s, int mode, const void* src, int len, int nseg, int producer) {
+    vec(s, mode, src, len, nseg, false);
+    s.flags |= SF_IN_TAG;
+    s.vl_tag = producer;
+  }
+  int last() const { return (int)st.size() - 1; }
+};
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_dims(const fsvd_dims& D) {
+  if (D.dtype != FSVD_DTYPE_BF16 && D.dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype %d", D.dtype);
+  if (D.B < 1 || D.B > 4) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..4)", D.B);
+  if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim %d unsupported (64, 128)", D.Dh);
+  if (D.Hk < 1 || D.H % D.Hk) return fail(FSVD_ERR_ARG, "H=%d not a multiple of Hk=%d", D.H, D.Hk);
+  const int G = D.H / D.Hk;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return fail(FSVD_ERR_UNSUPPORTED, "H/Hk=%d unsupported (1,2,4,8)", G);
+  const int m8[] = {D.d, D.I, D.Rq, D.Rk, D.Rv, D.Ro, D.Rg, D.Ru, D.Rd};
+  for (int v : m8)
+    if (v <= 0 || v % 8) return fail(FSVD_ERR_ALIGN, "sizes and ranks must be positive multiples of 8 (got %d)", v);
+  if (D.S_max < 1) return fail(FSVD_ERR_ARG, "S_max=%d", D.S_max);
+  if ((size_t)D.B * D.Hk * 4 > kCounterBytes) return fail(FSVD_ERR_UNSUPPORTED, "B*Hk=%d too large", D.B * D.Hk);
+  return 0;
+}
+
+struct LayerIO {
+  const void* x_in;    // hidden state read by the first RMSNorm and the first residual
+  int x_in_producer;   // >= 0: x_in holds (fp32, tag) pairs written by that stage; -1: tensor of T
+  void* x_out;         // destination of the last residual
+  int x_out_tagged;    // 1: (fp32, tag) pairs, 0: tensor of T
+  const int* seqlens;
+  const void* cos_tab;
+  const void* sin_tab;
+};
+
+// Appends the stages of one decoder layer and returns the index of the stage that writes
+// x_out.  `mid` (in the workspace) holds the hidden state between the attention and MLP halves.
+// Every vector handed from one stage to the next is tagged, so the only grid barrier of a layer
+// is the one in front of the attention stage (q and the new cache row are plain stores).
+static int build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, const LayerIO& io,
+                       char* ws, const WsLayout& L) {
+  void* pa = ws + L.pa;
+  void* pb = ws + L.pb;
+  void* hact = ws + L.hact;
+  float* qbuf = reinterpret_cast<float*>(ws + L.qbuf);
+  void* attn = ws + L.attn;
+  void* mid = ws + L.hidden;
+  const int Rqkv = D.Rq + D.Rk + D.Rv, HD = D.H * D.Dh, half = D.Dh / 2;
+
+  {  // 1. rank projection of q/k/v on the normalised hidden state
+    Stage& s = b.gemv(Lw.qkv_v, nullptr, Rqkv, D.d, D.d, true);
+    if (io.x_in_producer >= 0) {
+      b.vec_tagged(s, VL_RMSNORM, io.x_in, D.d, 1, io.x_in_producer);
+    } else {
+      b.vec(s, VL_RMSNORM, io.x_in, D.d, 1, false);
+      s.flags |= SF_IN_T;
+    }
+    s.vl_w = Lw.ln1_w;
+    s.eps = D.eps;
+    s.epi = EPI_PARTIAL;
+    s.flags |= SF_OUT_TAG;
+    s.out = pa;
+  }
+  const int i1 = b.last(), segs1 = b.st.back().segs;
+  {  // 2. lift q with rotary
+    Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
+                      D.H * half, D.Rq, D.Rq, false);
+    b.vec_tagged(s, VL_SUM, pa, Rqkv, segs1, i1);
+    s.rope_half = half;
+    s.xA_off = s.xB_off = 0;
+    s.epi = EPI_ROPE_Q;
+    s.out = qbuf;
+    s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+  }
+  {  // 3. lift k with rotary into the cache
+    Stage& s = b.gemv(Lw.k_u, reinterpret_cast<const char*>(Lw.k_u) + (size_t)half * D.Rk * b.esize,
+                      D.Hk * half, D.Rk, D.Rk, false);
+    s.rope_half = half;
+    s.xA_off = s.xB_off = D.Rq;
+    s.epi = EPI_ROPE_K;
+    s.cache = Lw.k_cache;
+    s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+  }
+  {  // 4. lift v into the cache
+    Stage& s = b.gemv(Lw.v_u, nullptr, D.Hk * D.Dh, D.Rv, D.Rv, false);
+    s.xA_off = D.Rq + D.Rk;
+    s.epi = EPI_V;
+    s.cache = Lw.v_cache;
+    s.seqlens = io.seqlens;
+    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+  }
+  {  // 5. attention over the cache including the token just appended
+    Stage s = b.blank();
+    s.type = ST_ATTN;
+    s.flags = SF_BARRIER | SF_OUT_TAG;
+    s.q = qbuf;
+    s.kcache = Lw.k_cache;
+    s.vcache = Lw.v_cache;
+    s.seqlens = io.seqlens;
+    s.seqlen_add = 1;
+    s.out = attn;
+    s.part_acc = reinterpret_cast<float*>(ws + L.part_acc);
+    s.part_ml = reinterpret_cast<float*>(ws + L.part_ml);
+    s.counters = reinterpret_cast<int*>(ws + L.counters);
+    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+    s.scale = 1.0f / sqrtf((float)D.Dh);
+    int ns = b.TW / imax(1, D.B * D.Hk);
+    if (ns < 1) ns = 1;
+    if (ns > kMaxSplit) ns = kMaxSplit;
+    s.nsplit = ns;
+    b.finish_items(s, (long long)D.B * D.Hk * ns);
+    b.st.push_back(s);
+  }
+  const int i5 = b.last();
+  {  // 6. o rank projection
+    Stage& s = b.gemv(Lw.o_v, nullptr, D.Ro, HD, HD, true);
+    b.vec_tagged(s, VL_SUM, attn, HD, 1, i5);
+    s.epi = EPI_PARTIAL;
+    s.flags |= SF_OUT_TAG;
+    s.out = pb;
+  }
+  const int i6 = b.last(), segs6 = b.st.back().segs;
+  {  // 7. o lift + residual
+    Stage& s = b.gemv(Lw.o_u, nullptr, D.d, D.Ro, D.Ro, false);
+    b.vec_tagged(s, VL_SUM, pb, D.Ro, segs6, i6);
+    s.epi = EPI_RESID;
+    s.resid = io.x_in;
+    s.flags |= (io.x_in_producer >= 0 ? SF_RESID_TAG : SF_RESID_T) | SF_OUT_TAG;
+    s.out = mid;
+  }
+  const int i7 = b.last();
+  {  // 8. MLP rank projection on the normalised hidden state: [p_up | p_gate]
+    Stage& s = b.gemv(Lw.upgate_v, nullptr, D.Ru + D.Rg, D.d, D.d, true);
+    b.vec_tagged(s, VL_RMSNORM, mid, D.d, 1, i7);
+    s.vl_w = Lw.ln2_w;
+    s.eps = D.eps;
+    s.epi = EPI_PARTIAL;
+    s.flags |= SF_OUT_TAG;
+    s.out = pa;
+  }
+  const int i8 = b.last(), segs8 = b.st.back().segs;
+  {  // 9. gate/up lift + SiLU·mul
+    Stage& s = b.gemv(Lw.gate_u, Lw.up_u, D.I, D.Rg, D.Rg, false);
+    b.vec_tagged(s, VL_SUM, pa, D.Ru + D.Rg, segs8, i8);
+    s.xA_off = D.Ru;  // gate input follows the up input
+    s.xB_off = 0;
+    s.epi = EPI_SWIGLU;
+    s.flags |= SF_OUT_TAG;
+    s.out = hact;
+  }
+  const int i9 = b.last();
+  {  // 10. down rank projection
+    Stage& s = b.gemv(Lw.down_v, nullptr, D.Rd, D.I, D.I, true);
+    b.vec_tagged(s, VL_SUM, hact, D.I, 1, i9);
+    s.epi = EPI_PARTIAL;
+    s.flags |= SF_OUT_TAG;
+    s.out = pb;
+  }
+  const int i10 = b.last(), segs10 = b.st.back().segs;
+  {  // 11. down lift + residual
+    Stage& s = b.gemv(Lw.down_u, nullptr, D.d, D.Rd, D.Rd, false);
+    b.vec_tagged(s, VL_SUM, pb, D.Rd, segs10, i10);
+    s.epi = EPI_RESID;
+    s.resid = mid;
+    s.flags |= SF_RESID_TAG | (io.x_out_tagged ? SF_OUT_TAG : SF_OUT_T);
+    s.out = io.x_out;
+  }
+  return b.last();
+}
+
+static int check_layer_ptrs(const fsvd_layer& Lw) {
+  const void* ps[] = {Lw.ln1_w, Lw.qkv_v, Lw.q_u, Lw.k_u, Lw.v_u, Lw.o_v, Lw.o_u, Lw.ln2_w,
+                      Lw.upgate_v, Lw.gate_u, Lw.up_u, Lw.down_v, Lw.down_u, Lw.k_cache, Lw.v_cache};
+  for (const void* p : ps) {
+    if (!p) return fail(FSVD_ERR_ARG, "null layer pointer");
+    if (!aligned16(p)) return fail(FSVD_ERR_ALIGN, "layer pointer %p is not 16-byte aligned", p);
+  }
+  return 0;
+}
+
+static int launch_small(const Resolved& r, const Builder& b, SyncState* sync, cudaStream_t stream) {
+  if ((int)b.st.size() > kMaxSmallStages) return fail(FSVD_ERR_UNSUPPORTED, "program too long");
+  SmallProgram sp;
+  memset(&sp, 0, sizeof(sp));
+  for (size_t i = 0; i < b.st.size(); ++i) sp.st[i] = b.st[i];
+  const int xstride = (b.max_vec + 7) / 8 * 8;
+  unsigned long long* tr = g_trace_bytes >= b.st.size() * (size_t)r.grid * 64 ? g_trace : nullptr;
+  cudaError_t e = r.fn(nullptr, &sp, 1, (int)b.st.size(), sync, xstride, tr, r.inflight, r.grid, r.smem, stream);
+  if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------- C ABI
+extern "C" {
+
+int fsvd_version(void) { return 100; }
+const char* fsvd_last_error_string(void) { return g_err; }
+long long fsvd_launch_count(void) { return g_launches.load(); }
+
+int fsvd_device_props(int* sm_count, int* smem_optin_bytes) {
+  DevProps p;
+  if (int e = get_props(p)) return e;
+  if (sm_count) *sm_count = p.sms;
+  if (smem_optin_bytes) *smem_optin_bytes = p.smem_optin;
+  return 0;
+}
+
+int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes) {
+  g_trace = reinterpret_cast<unsigned long long*>(dev_ptr);
+  g_trace_bytes = dev_ptr ? bytes : 0;
+  return 0;
+}
+
+int fsvd_model_num_stages(fsvd_model* m);
+
+int fsvd_set_launch_config(int warps, int slots, int direct, int grid, int inflight) {
+  current_cfg();
+  if (warps != 8 && warps != 16) return fail(FSVD_ERR_ARG, "warps must be 8 or 16");
+  if (slots < 1) return fail(FSVD_ERR_ARG, "slots must be >= 1");
+  g_cfg.nw = warps;
+  g_cfg.nd = slots;
+  g_cfg.direct = direct ? 1 : 0;
+  g_cfg.grid = grid < 0 ? 0 : grid;
+  g_cfg.inflight = inflight < 0 ? 0 : inflight;
+  return 0;
+}
+
+size_t fsvd_workspace_bytes(const fsvd_dims* dims) {
+  if (!dims) return 0;
+  return ws_layout(*dims).total;
+}
+
+int fsvd_workspace_init(void* ws, size_t ws_bytes, void* stream) {
+  if (!ws || ws_bytes < sizeof(SyncState)) return fail(FSVD_ERR_WORKSPACE, "workspace too small");
+  CUDA_TRY(cudaMemsetAsync(ws, 0, ws_bytes, (cudaStream_t)stream));
+  return 0;
+}
+
+int fsvd_workspace_status(void* ws, int* device_status) {
+  if (!ws || !device_status) return fail(FSVD_ERR_ARG, "null argument");
+  SyncState s;
+  CUDA_TRY(cudaMemcpy(&s, ws, sizeof(s), cudaMemcpyDeviceToHost));
+  *device_status = s.status;
+  if (s.status) return fail(FSVD_ERR_DEVICE_WAIT, "device wait ran out: code %d at stage %d", s.status, s.status_detail);
+  return 0;
+}
+
+static fsvd_dims op_dims(int dtype, int B) {
+  fsvd_dims D;
+  memset(&D, 0, sizeof(D));
+  D.dtype = dtype;
+  D.B = B;
+  D.d = D.I = D.Rq = D.Rk = D.Rv = D.Ro = D.Rg = D.Ru = D.Rd = 8;
+  D.H = D.Hk = 1;
+  D.Dh = 64;
+  D.S_max = 1;
+  return D;
+}
+
+static int check_ws(const fsvd_dims& D, void* ws, size_t ws_bytes, WsLayout& L) {
+  L = ws_layout(D);
+  if (!ws) return fail(FSVD_ERR_WORKSPACE, "null workspace");
+  if (!aligned16(ws)) return fail(FSVD_ERR_ALIGN, "workspace is not 16-byte aligned");
+  if (ws_bytes < L.total) return fail(FSVD_ERR_WORKSPACE, "workspace of %zu bytes, %zu needed", ws_bytes, L.total);
+  return 0;
+}
+
+int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* residual, void* y,
+                      int B, int d_in, int R, int d_out, int dtype, void* ws, size_t ws_bytes,
+                      void* stream) {
+  if (!x || !v || !u || !y) return fail(FSVD_ERR_ARG, "null argument");
+  if (d_in <= 0 || R <= 0 || d_out <= 0 || d_in % 8 || R % 8)
+    return fail(FSVD_ERR_ALIGN, "d_in=%d and R=%d must be positive multiples of 8", d_in, R);
+  if (!aligned16(x) || !aligned16(v) || !aligned16(u) || !aligned16(y))
+    return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  fsvd_dims D = op_dims(dtype, B);
+  D.Ro = R;
+  WsLayout L;
+  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
+  Resolved r;
+  if (int e = resolve(dtype, B, imax(d_in, R), r)) return e;
+  Builder b(r, dtype, B);
+  char* w = reinterpret_cast<char*>(ws);
+  {
+    Stage& s = b.gemv(v, nullptr, R, d_in, d_in, true);
+    b.vec(s, VL_SUM, x, d_in, 1, false);
+    s.flags |= SF_IN_T | SF_OUT_TAG;
+    s.epi = EPI_PARTIAL;
+    s.out = w + L.pb;
+  }
+  const int segs = b.st.back().segs;
+  {
+    Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
+    b.vec_tagged(s, VL_SUM, w + L.pb, R, segs, 0);
+    s.epi = residual ? EPI_RESID : EPI_STORE;
+    s.resid = residual;
+    s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
+    s.out = y;
+  }
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
+}
+
+int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const void* upgate_v,
+                           const void* gate_u, const void* up_u, const void* down_v,
+                           const void* down_u, const void* residual, void* y, int B, int d, int I,
+                           int Ru, int Rg, int Rd, int dtype, void* ws, size_t ws_bytes,
+                           void* stream) {
+  if (!x || !gate_u || !up_u || !down_v || !down_u || !y) return fail(FSVD_ERR_ARG, "null argument");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  if (d <= 0 || I <= 0 || Ru <= 0 || Rg <= 0 || Rd <= 0 || d % 8 || I % 8 || Ru % 8 || Rg % 8 || Rd % 8)
+    return fail(FSVD_ERR_ALIGN, "d, I and the ranks must be positive multiples of 8");
+  if (Ru != Rg) return fail(FSVD_ERR_UNSUPPORTED, "gate and up ranks must match (Rg=%d, Ru=%d)", Rg, Ru);
+  const void* ps[] = {x, gate_u, up_u, down_v, down_u, y};
+  for (const void* p : ps)
+    if (!aligned16(p)) return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
+  fsvd_dims D = op_dims(dtype, B);
+  D.d = d; D.I = I; D.Ru = Ru; D.Rg = Rg; D.Rd = Rd;
+  WsLayout L;
+  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
+  Resolved r;
+  if (int e = resolve(dtype, B, imax(imax(d, I), Ru + Rg), r)) return e;
+  Builder b(r, dtype, B);
+  char* w = reinterpret_cast<char*>(ws);
+  int segs_rank = 1;
+  const void* pcat = x;
+  bool pcat_T = true;
+  if (upgate_v) {
+    Stage& s = b.gemv(upgate_v, nullptr, Ru + Rg, d, d, true);
+    b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, false);
+    s.flags |= SF_IN_T | SF_OUT_TAG;
+    s.vl_w = norm_w;
+    s.eps = eps;
+    s.epi = EPI_PARTIAL;
+    s.out = w + L.pa;
+    segs_rank = s.segs;
+    pcat = w + L.pa;
+    pcat_T = false;
+  }
+  {
+    Stage& s = b.gemv(gate_u, up_u, I, Rg, Rg, false);
+    if (pcat_T) {
+      b.vec(s, VL_SUM, pcat, Ru + Rg, 1, false);
+      s.flags |= SF_IN_T;
+    } else {
+      b.vec_tagged(s, VL_SUM, pcat, Ru + Rg, segs_rank, 0);
+    }
+    s.xA_off = Ru;
+    s.xB_off = 0;
+    s.epi = EPI_SWIGLU;
+    s.flags |= SF_OUT_TAG;
+    s.out = w + L.hact;
+  }
+  const int i_act = b.last();
+  {
+    Stage& s = b.gemv(down_v, nullptr, Rd, I, I, true);
+    b.vec_tagged(s, VL_SUM, w + L.hact, I, 1, i_act);
+    s.epi = EPI_PARTIAL;
+    s.flags |= SF_OUT_TAG;
+    s.out = w + L.pb;
+  }
+  const int i_down = b.last();
+  const int segs = b.st.back().segs;
+  {
+    Stage& s = b.gemv(down_u, nullptr, d, Rd, Rd, false);
+    b.vec_tagged(s, VL_SUM, w + L.pb, Rd, segs, i_down);
+    s.epi = residual ? EPI_RESID : EPI_STORE;
+    s.resid = residual;
+    s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
+    s.out = y;
+  }
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
+}
+
+int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const void* qkv_v,
+                         const void* q_u, const void* k_u, const void* v_u, const void* cos_tab,
+                         const void* sin_tab, void* k_cache, void* v_cache,
+                         const int* cache_seqlens, void* q_out, int B, int d, int H, int Hk, int Dh,
+                         int Rq, int Rk, int Rv, int S_max, int dtype, void* ws, size_t ws_bytes,
+                         void* stream) {
+  if (!x || !qkv_v || !q_u || !k_u || !v_u || !cos_tab || !sin_tab || !k_cache || !v_cache ||
+      !cache_seqlens || !q_out)
+    return fail(FSVD_ERR_ARG, "null argument");
+  fsvd_dims D = op_dims(dtype, B);
+  D.d = d; D.H = H; D.Hk = Hk; D.Dh = Dh; D.Rq = Rq; D.Rk = Rk; D.Rv = Rv; D.S_max = S_max;
+  if (int e = check_dims(D)) return e;
+  const void* ps[] = {x, qkv_v, q_u, k_u, v_u, k_cache, v_cache, q_out};
+  for (const void* p : ps)
+    if (!aligned16(p)) return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
+  WsLayout L;
+  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
+  Resolved r;
+  if (int e = resolve(dtype, B, imax(d, Rq + Rk + Rv), r)) return e;
+  Builder b(r, dtype, B);
+  char* w = reinterpret_cast<char*>(ws);
+  const int half = Dh / 2, Rqkv = Rq + Rk + Rv;
+  {
+    Stage& s = b.gemv(qkv_v, nullptr, Rqkv, d, d, true);
+    b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, false);
+    s.flags |= SF_IN_T | SF_OUT_TAG;
+    s.vl_w = norm_w;
+    s.eps = eps;
+    s.epi = EPI_PARTIAL;
+    s.out = w + L.pa;
+  }
+  const int segs = b.st.back().segs;
+  {
+    Stage& s = b.gemv(q_u, reinterpret_cast<const char*>(q_u) + (size_t)half * Rq * b.esize, H * half, Rq, Rq, false);
+    b.vec_tagged(s, VL_SUM, w + L.pa, Rqkv, segs, 0);
+    s.rope_half = half;
+    s.epi = EPI_ROPE_Q;
+    s.flags |= SF_OUT_T;
+    s.out = q_out;
+    s.cos_tab = cos_tab; s.sin_tab = sin_tab; s.seqlens = cache_seqlens;
+    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  }
+  {
+    Stage& s = b.gemv(k_u, reinterpret_cast<const char*>(k_u) + (size_t)half * Rk * b.esize, Hk * half, Rk, Rk, false);
+    s.rope_half = half;
+    s.xA_off = s.xB_off = Rq;
+    s.epi = EPI_ROPE_K;
+    s.cache = k_cache;
+    s.cos_tab = cos_tab; s.sin_tab = sin_tab; s.seqlens = cache_seqlens;
+    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  }
+  {
+    Stage& s = b.gemv(v_u, nullptr, Hk * Dh, Rv, Rv, false);
+    s.xA_off = Rq + Rk;
+    s.epi = EPI_V;
+    s.cache = v_cache;
+    s.seqlens = cache_seqlens;
+    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  }
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
+}
+
+int fsvd_flash_decode(const void* q, const void* k_cache, const void* v_cache,
+                      const int* cache_seqlens, int seqlen_add, void* out, int B, int H, int Hk,
+                      int Dh, int S_max, float scale, int dtype, void* ws, size_t ws_bytes,
+                      void* stream) {
+  if (!q || !k_cache || !v_cache || !cache_seqlens || !out) return fail(FSVD_ERR_ARG, "null argument");
+  fsvd_dims D = op_dims(dtype, B);
+  D.H = H; D.Hk = Hk; D.Dh = Dh; D.S_max = S_max;
+  if (int e = check_dims(D)) return e;
+  WsLayout L;
+  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
+  Resolved r;
+  if (int e = resolve(dtype, B, 8, r)) return e;
+  Builder b(r, dtype, B);
+  char* w = reinterpret_cast<char*>(ws);
+  Stage s = b.blank();
+  s.type = ST_ATTN;
+  s.flags = SF_IN_T | SF_OUT_T;
+  s.q = q;
+  s.kcache = k_cache;
+  s.vcache = v_cache;
+  s.seqlens = cache_seqlens;
+  s.seqlen_add = seqlen_add;
+  s.out = out;
+  s.part_acc = reinterpret_cast<float*>(w + L.part_acc);
+  s.part_ml = reinterpret_cast<float*>(w + L.part_ml);
+  s.counters = reinterpret_cast<int*>(w + L.counters);
+  s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  s.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)Dh);
+  int ns = b.TW / imax(1, B * Hk);
+  if (ns < 1) ns = 1;
+  if (ns > kMaxSplit) ns = kMaxSplit;
+  s.nsplit = ns;
+  b.finish_items(s, (long long)B * Hk * ns);
+  b.st.push_back(s);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
+}
+
+int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab,
+                      const void* sin_tab, const int* cache_seqlens, const void* x_in, void* x_out,
+                      void* ws, size_t ws_bytes, void* stream) {
+  if (!dims || !layer || !cos_tab || !sin_tab || !cache_seqlens || !x_in || !x_out)
+    return fail(FSVD_ERR_ARG, "null argument");
+  const fsvd_dims& D = *dims;
+  if (int e = check_dims(D)) return e;
+  if (int e = check_layer_ptrs(*layer)) return e;
+  WsLayout L;
+  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
+  Resolved r;
+  const int maxvec = imax(imax(D.d, D.I), imax(D.Rq + D.Rk + D.Rv, imax(D.Ru + D.Rg, D.H * D.Dh)));
+  if (int e = resolve(D.dtype, D.B, maxvec, r)) return e;
+  Builder b(r, D.dtype, D.B);
+  LayerIO io = {x_in, -1, x_out, 0, cache_seqlens, cos_tab, sin_tab};
+  build_layer(b, D, *layer, io, reinterpret_cast<char*>(ws), L);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(reinterpret_cast<char*>(ws) + L.sync),
+                      (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------------------- model
+struct fsvd_model {
+  fsvd_dims D;
+  Resolved r;
+  WsLayout L;
+  char* ws = nullptr;
+  Stage* prog = nullptr;
+  int nstages = 0, xstride = 0, max_steps = 0;
+  int* tokens = nullptr;
+  int* seqlens = nullptr;
+  int* token_log = nullptr;
+  int* step_counter = nullptr;
+  float* logits = nullptr;
+  float* xbuf = nullptr;  // hidden state between layers, (fp32, tag) pairs
+  char* extra = nullptr;
+};
+
+int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const void* embed,
+                      const void* final_norm_w, const void* lm_head, const void* cos_tab,
+                      const void* sin_tab, int max_steps, fsvd_model** out) {
+  if (!dims || !layers || !embed || !final_norm_w || !lm_head || !cos_tab || !sin_tab || !out)
+    return fail(FSVD_ERR_ARG, "null argument");
+  const fsvd_dims& D = *dims;
+  if (int e = check_dims(D)) return e;
+  if (D.n_layers < 1 || D.vocab < 1) return fail(FSVD_ERR_ARG, "n_layers=%d vocab=%d", D.n_layers, D.vocab);
+  for (int l = 0; l < D.n_layers; ++l)
+    if (int e = check_layer_ptrs(layers[l])) return e;
+  if (!aligned16(embed) || !aligned16(lm_head) || !aligned16(final_norm_w))
+    return fail(FSVD_ERR_ALIGN, "embed / lm_head / norm pointers must be 16-byte aligned");
+  if (max_steps < 1) max_steps = 1;
+
+  fsvd_model* m = new fsvd_model();
+  m->D = D;
+  m->max_steps = max_steps;
+  m->L = ws_layout(D);
+  const int maxvec = imax(imax(D.d, D.I), imax(D.Rq + D.Rk + D.Rv, imax(D.Ru + D.Rg, D.H * D.Dh)));
+  if (int e = resolve(D.dtype, D.B, maxvec, m->r)) { delete m; return e; }
+
+  const size_t extra_bytes = al256((size_t)D.B * 4) * 2 + al256(4) + al256((size_t)max_steps * D.B * 4) +
+                             al256((size_t)D.B * D.vocab * 4);
+  cudaError_t ce = cudaMalloc(&m->ws, m->L.total);
+  if (ce == cudaSuccess) ce = cudaMalloc(&m->extra, extra_bytes);
+  if (ce == cudaSuccess) ce = cudaMemset(m->ws, 0, m->L.total);
+  if (ce == cudaSuccess) ce = cudaMemset(m->extra, 0, extra_bytes);
+  if (ce != cudaSuccess) {
+    cudaFree(m->ws); cudaFree(m->extra); delete m;
+    return fail(FSVD_ERR_CUDA, "allocating model scratch failed: %s", cudaGetErrorString(ce));
+  }
+  size_t o = 0;
+  m->tokens = reinterpret_cast<int*>(m->extra + o);        o += al256((size_t)D.B * 4);
+  m->seqlens = reinterpret_cast<int*>(m->extra + o);       o += al256((size_t)D.B * 4);
+  m->step_counter = reinterpret_cast<int*>(m->extra + o);  o += al256(4);
+  m->token_log = reinterpret_cast<int*>(m->extra + o);     o += al256((size_t)max_steps * D.B * 4);
+  m->logits = reinterpret_cast<float*>(m->extra + o);
+
+  Builder b(m->r, D.dtype, D.B);
+  float* hidden = reinterpret_cast<float*>(m->ws + m->L.hidden);
+  // The hidden state ping-pongs between two fp32 buffers: `hidden` (between the halves of a
+  // layer) and `xbuf` (between layers), so a residual never reads what its stage overwrites.
+  float* xbuf = nullptr;
+  ce = cudaMalloc(&xbuf, al256((size_t)D.B * D.d * 8));
+  if (ce == cudaSuccess) ce = cudaMemset(xbuf, 0, al256((size_t)D.B * D.d * 8));
+  if (ce != cudaSuccess) {
+    cudaFree(m->ws); cudaFree(m->extra); delete m;
+    return fail(FSVD_ERR_CUDA, "allocating model scratch failed: %s", cudaGetErrorString(ce));
+  }
+  {
+    Stage s = b.blank();
+    s.type = ST_EMBED;
+    s.WA = embed;
+    s.P = D.d;
+    s.out = xbuf;
+    s.flags = SF_OUT_TAG;
+    s.tokens = m->tokens;
+    s.vocab = D.vocab;
+    b.st.push_back(s);
+  }
+  int producer = b.last();
+  for (int l = 0; l < D.n_layers; ++l) {
+    LayerIO io = {xbuf, producer, xbuf, 1, m->seqlens, cos_tab, sin_tab};
+    producer = build_layer(b, D, layers[l], io, m->ws, m->L);
+  }
+  if ((unsigned)b.st.size() + 2 >= kTagStride) {
+    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); delete m;
+    return fail(FSVD_ERR_UNSUPPORTED, "program of %zu stages is too long", b.st.size());
+  }
+  {
+    Stage& s = b.gemv(lm_head, nullptr, D.vocab, D.d, D.d, false);
+    b.vec_tagged(s, VL_RMSNORM, xbuf, D.d, 1, producer);
+    s.vl_w = final_norm_w;
+    s.eps = D.eps;
+    s.epi = EPI_STORE;
+    s.out = m->logits;
+  }
+  {
+    Stage s = b.blank();
+    s.type = ST_ARGMAX;
+    s.flags = SF_BARRIER;
+    s.vl_src = m->logits;
+    s.vocab = D.vocab;
+    s.tokens = m->tokens;
+    s.token_log = m->token_log;
+    s.step_counter = m->step_counter;
+    s.seqlens_rw = m->seqlens;
+    s.max_steps = max_steps;
+    b.st.push_back(s);
+  }
+  m->nstages = (int)b.st.size();
+  m->xstride = (b.max_vec + 7) / 8 * 8;
+  ce = cudaMalloc(&m->prog, sizeof(Stage) * b.st.size());
+  if (ce == cudaSuccess)
+    ce = cudaMemcpy(m->prog, b.st.data(), sizeof(Stage) * b.st.size(), cudaMemcpyHostToDevice);
+  if (ce != cudaSuccess) {
+    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); cudaFree(m->prog); delete m;
+    return fail(FSVD_ERR_CUDA, "uploading the stage program failed: %s", cudaGetErrorString(ce));
+  }
+  m->xbuf = xbuf;
+  *out = m;
+  return 0;
+}
+
+int fsvd_model_destroy(fsvd_model* m) {
+  if (!m) return 0;
+  cudaFree(m->ws);
+  cudaFree(m->extra);
+  cudaFree(m->prog);
+  cudaFree(m->xbuf);
+  delete m;
+  return 0;
+}
+
+int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
+  if (!m) return fail(FSVD_ERR_ARG, "null model");
+  SyncState* sync = reinterpret_cast<SyncState*>(m->ws + m->L.sync);
+  for (int i = 0; i < n_steps; ++i) {
+    unsigned long long* tr = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 64 ? g_trace : nullptr;
+    cudaError_t e = m->r.fn(m->prog, nullptr, 0, m->nstages, sync, m->xstride, tr, m->r.inflight,
+                            m->r.grid, m->r.smem, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    g_launches.fetch_add(1);
+  }
+  return 0;
+}
+
+int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
+                       int** step_counter, float** logits, float** hidden) {
+  if (!m) return fail(FSVD_ERR_ARG, "null model");
+  if (tokens) *tokens = m->tokens;
+  if (seqlens) *seqlens = m->seqlens;
+  if (token_log) *token_log = m->token_log;
+  if (step_counter) *step_counter = m->step_counter;
+  if (logits) *logits = m->logits;
+  if (hidden) *hidden = m->xbuf;
+  return 0;
+}
+
+int fsvd_model_num_stages(fsvd_model* m) { return m ? m->nstages : 0; }
+
+int fsvd_model_status(fsvd_model* m, int* device_status) {
+  if (!m) return fail(FSVD_ERR_ARG, "null model");
+  return fsvd_workspace_status(m->ws, device_status);
+}
+
+int fsvd_model_reset_sync(fsvd_model* m, void* stream) {
+  if (!m) return fail(FSVD_ERR_ARG, "null model");
+  CUDA_TRY(cudaMemsetAsync(m->ws + m->L.sync, 0, sizeof(SyncState), (cudaStream_t)stream));
+  CUDA_TRY(cudaMemsetAsync(m->ws + m->L.counters, 0, kCounterBytes, (cudaStream_t)stream));
+  return 0;
+}
+
+}  // extern "C"

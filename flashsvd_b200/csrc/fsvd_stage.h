@@ -1,0 +1,135 @@
+// Stage program shared by the host-side program builder and the device interpreter.
+//
+// One decode step is a short program of dependent stages (rank projection, lift with a
+// fused epilogue, split-KV attention, ...).  A single persistent kernel, one CTA per SM,
+// walks the program.  Every stage streams its slice of the factor matrices through
+// per-warp shared-memory rings filled by bulk async copies; because the addresses of the
+// factors do not depend on the activations, a warp keeps prefetching the factors of the
+// following stages while it waits at the grid barrier that separates two stages.
+#pragma once
+#include <stdint.h>
+
+#ifdef __CUDACC__
+#define FSVD_HD __host__ __device__
+#else
+#define FSVD_HD
+#endif
+
+namespace fsvd {
+
+enum StageType : int {
+  ST_END = 0,
+  ST_GEMV = 1,    // y = W x, rows split over warps, optional K split into partial sums
+  ST_ATTN = 2,    // split-KV single-query attention over the dense cache + ordered combine
+  ST_EMBED = 3,   // hidden[b,:] = embed[token[b],:]
+  ST_ARGMAX = 4,  // token[b] = argmax_v logits[b,v]; advances seqlens / step counter
+};
+
+enum Epilogue : int {
+  EPI_PARTIAL = 0,  // out[(seg*B+b)*P + p] = acc            (fp32, summed by the consumer)
+  EPI_STORE = 1,    // out[b*P + p] = rnd(acc)               (fp32 container or T, see OUT_T)
+  EPI_RESID = 2,    // out[b*P + p] = rnd(resid[b*P+p] + rnd(acc))
+  EPI_SWIGLU = 3,   // out[b*P + p] = rnd(rnd(silu(rnd(accA))) * rnd(accB))   A=gate, B=up
+  EPI_ROPE_Q = 4,   // rotate (accA, accB) = dims (j, j+half) of a head, store to q buffer
+  EPI_ROPE_K = 5,   // same rotation, store into the key cache at position seqlens[b]
+  EPI_V = 6,        // store rnd(acc) into the value cache at position seqlens[b]
+};
+
+enum VecLoad : int {
+  VL_NONE = 0,     // keep the vector already staged in shared memory
+  VL_SUM = 1,      // x[b,k] = rnd(sum_s src[(s*B+b)*len + k])
+  VL_RMSNORM = 2,  // x[b,:] = rnd(w * rnd(src[b,:] * rsqrt(mean(src[b,:]^2) + eps)))
+};
+
+enum StageFlags : int {
+  SF_BARRIER = 1,    // grid-wide barrier before this stage
+  SF_IN_T = 2,       // vl_src (or q for ST_ATTN) holds T instead of fp32
+  SF_OUT_T = 4,      // out holds T instead of fp32
+  SF_RESID_T = 8,    // resid holds T instead of fp32
+  SF_IN_TAG = 16,    // vl_src holds (fp32, tag) pairs written by stage vl_tag of this launch
+  SF_OUT_TAG = 32,   // out receives (fp32, tag) pairs
+  SF_RESID_TAG = 64, // resid holds (fp32, tag) pairs (the tag is not checked)
+};
+
+// Tagged vectors: a value that another CTA consumes in the same launch is stored as one aligned
+// 8-byte word {fp32 bits, tag}, tag = launch epoch * kTagStride + producing stage + 1.  The
+// consumer polls the words themselves until every tag matches, so a dependent stage starts one
+// store and one load after its last producer, without a separate grid barrier; 8-byte accesses
+// are single-copy atomic, so a matching tag implies the value beside it.
+constexpr unsigned kTagStride = 2048;  // > number of stages of any program
+
+// `rnd` above rounds to the storage type T (bf16) and is the identity when T is fp32: these
+// are the points at which the PyTorch low-rank path materialises a tensor in the model dtype.
+struct alignas(16) Stage {
+  int type, flags, epi, vl_mode;
+  const void* WA;        // [rows, ldw] row-major factor (nn.Linear weight layout), type T
+  const void* WB;        // second operand group (up factor / second rotary half) or null
+  int P;                 // logical rows (a logical row owns one A row and, if WB, one B row)
+  int K;                 // reduction length
+  int ldw;               // row stride of WA/WB in elements
+  int segs;              // number of K segments (partial sums) per row group
+  int kseg;              // elements per K segment
+  int xA_off, xB_off;    // offset of the operand-group input inside the staged vector
+  int rope_half;         // >0: physical row of logical row p is (p/half)*2*half + p%half
+  int vl_len;            // staged vector length per batch row
+  int vl_nseg;           // partial sums to add when staging
+  int vl_tag;            // SF_IN_TAG: index of the stage that produces vl_src
+  int rot;               // rotation of the item -> warp assignment
+  int B;                 // batch rows
+  const void* vl_src;    // fp32 (or T with SF_IN_T) [vl_nseg, B, vl_len]
+  const void* vl_w;      // RMSNorm weight, type T
+  void* out;             // epilogue destination
+  const void* resid;     // EPI_RESID addend
+  void* cache;           // EPI_ROPE_K / EPI_V: cache base [B, S_max, Hk, Dh] of type T
+  const void* cos_tab;   // [S_max, Dh/2] type T
+  const void* sin_tab;
+  const int* seqlens;    // [B] number of tokens already in the cache (= write position)
+  float eps, scale;
+  int H, Hk, Dh, S_max;
+  // ST_ATTN
+  const void* q;         // [B, H*Dh] fp32 (or T with SF_IN_T), already rotated
+  const void* kcache;
+  const void* vcache;
+  float* part_acc;       // [B, H, nsplit, Dh]
+  float* part_ml;        // [B, H, nsplit, 2]
+  int* counters;         // [B, Hk] zero between uses
+  int nsplit, seqlen_add;  // keys attended = seqlens[b] + seqlen_add
+  // ST_EMBED / ST_ARGMAX
+  int* tokens;           // [B] token ids: input of ST_EMBED, output of ST_ARGMAX
+  int* token_log;        // [max_steps, B] or null
+  int* step_counter;     // incremented once per ST_ARGMAX
+  int* seqlens_rw;       // [B] incremented by ST_ARGMAX
+  int vocab, max_steps;
+};
+
+// Persistent words shared by all launches that use one workspace.
+struct SyncState {
+  unsigned long long arrivals;   // monotonically increasing barrier arrival count
+  unsigned long long bar_base;   // barriers completed by earlier launches
+  int status;                    // 0 = ok, else first error code raised on the device
+  int status_detail;
+  unsigned epoch;                // launches completed on this workspace (tag generation)
+  unsigned done_ctas;            // CTAs that have finished the running launch
+};
+
+enum DeviceStatus : int {
+  DS_OK = 0,
+  DS_BARRIER_TIMEOUT = 1,
+  DS_COPY_TIMEOUT = 2,
+  DS_TAG_TIMEOUT = 3,
+};
+
+constexpr int kMaxSmallStages = 14;
+struct SmallProgram {
+  Stage st[kMaxSmallStages];
+};
+
+// Shared-memory header of the interpreter (mbarriers, two stage descriptors, reduction scratch,
+// the copy of a by-value program), rounded so that the rings that follow are 1 KB aligned.
+constexpr int kStageBytesAl = ((int)sizeof(Stage) + 15) / 16 * 16;
+constexpr int kSmallProgBytes = kMaxSmallStages * kStageBytesAl;
+FSVD_HD constexpr int smem_header_bytes(int nw, int nd) {
+  return ((((nw * nd * 8 + 15) / 16) * 16 + 2 * kStageBytesAl + 512 + kSmallProgBytes + 1023) / 1024) * 1024;
+}
+
+}  // namespace fsvd

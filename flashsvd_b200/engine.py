@@ -1,0 +1,166 @@
+"""Whole-model greedy decode on the device-resident stage program (fsvd_model_* of the C ABI).
+
+One ``step`` is one kernel launch: embed -> all decoder layers -> final norm -> lm_head -> argmax.
+Token ids and sequence lengths stay on the device between steps, which removes the per-token
+``torch.tensor([pos])`` / ``.item()`` host round trips of the reference loop
+(scripts/demo_support/api.py:285-312, utils/evaluator.py:499-512).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib, ops
+from ._lib import FsvdLayer, LAYER_FIELDS, check
+
+
+def rope_tables(seqlen: int, head_dim: int, theta: float, dtype, device):
+    """cos/sin [seqlen, head_dim/2] exactly as FlashSVDV15DenseKVCache.get_rope_tables builds
+    them (runtime/cache/attn_dense_kv.py:331-357): fp32 angles, cast to the model dtype."""
+    half = head_dim // 2
+    pos = torch.arange(seqlen, device=device, dtype=torch.float32)
+    inv_freq = 1.0 / (float(theta) ** (torch.arange(0, half, device=device, dtype=torch.float32) / half))
+    ang = torch.einsum("m,d->md", pos, inv_freq)
+    return torch.cos(ang).to(dtype).contiguous(), torch.sin(ang).to(dtype).contiguous()
+
+
+class DecodeEngine:
+    """Owns the caches, the rope tables and the device program of one model replica.
+
+    ``layers`` is a list of dicts with the tensors of ``packing.pack_layer`` (already on the
+    device, model dtype).  ``k_cache`` / ``v_cache`` [B, S_max, Hk, Dh] are allocated here, one
+    pair per layer, zero-initialised like the reference cache
+    (runtime/cache/attn_dense_kv.py:110-130).
+    """
+
+    def __init__(self, *, layers, embed, final_norm, lm_head, num_heads, num_kv_heads, head_dim,
+                 batch_size, max_cache_len, rope_theta=10000.0, eps=1e-6, max_steps=4096,
+                 share_cache_alloc=True):
+        self.lib = _lib.load()
+        dev = embed.device
+        if dev.type != "cuda":
+            raise ValueError("flashsvd_b200 runs on CUDA devices only (there is no CPU path)")
+        dtype = embed.dtype
+        self.device, self.dtype = dev, dtype
+        L0 = layers[0]
+        d = embed.shape[1]
+        H, Hk, Dh = int(num_heads), int(num_kv_heads), int(head_dim)
+        Rq = L0["q_u"].shape[1]
+        Rk = L0["k_u"].shape[1]
+        Rv = L0["v_u"].shape[1]
+        if L0["qkv_v"].shape[0] != Rq + Rk + Rv:
+            raise ValueError("qkv_v rows must equal Rq + Rk + Rv")
+        self.dims = ops.make_dims(
+            dtype=dtype, B=int(batch_size), d=d, H=H, Hk=Hk, Dh=Dh, I=L0["gate_u"].shape[0],
+            Rq=Rq, Rk=Rk, Rv=Rv, Ro=L0["o_v"].shape[0], Rg=L0["gate_u"].shape[1],
+            Ru=L0["up_u"].shape[1], Rd=L0["down_v"].shape[0], S_max=int(max_cache_len),
+            vocab=embed.shape[0], n_layers=len(layers), eps=float(eps))
+        self.B, self.S_max, self.vocab, self.d = int(batch_size), int(max_cache_len), embed.shape[0], d
+        self.cos, self.sin = rope_tables(self.S_max, Dh, rope_theta, dtype, dev)
+        self.key_cache, self.value_cache = [], []
+        self._keep = [embed, final_norm, lm_head, layers]
+        arr = (FsvdLayer * len(layers))()
+        for i, lw in enumerate(layers):
+            kc = torch.zeros(self.B, self.S_max, Hk, Dh, dtype=dtype, device=dev)
+            vc = torch.zeros_like(kc)
+            self.key_cache.append(kc)
+            self.value_cache.append(vc)
+            t = dict(lw)
+            t["k_cache"], t["v_cache"] = kc, vc
+            for name in LAYER_FIELDS:
+                x = t[name]
+                if not (x.is_cuda and x.is_contiguous() and x.dtype == dtype):
+                    raise ValueError(f"layer {i} tensor {name}: need a contiguous {dtype} CUDA tensor")
+                setattr(arr[i], name, x.data_ptr())
+        for name, x in (("embed", embed), ("final_norm", final_norm), ("lm_head", lm_head)):
+            if not (x.is_cuda and x.is_contiguous() and x.dtype == dtype):
+                raise ValueError(f"{name}: need a contiguous {dtype} CUDA tensor")
+        handle = C.c_void_p()
+        with torch.cuda.device(dev):
+            check(self.lib.fsvd_model_create(
+                C.byref(self.dims), arr, embed.data_ptr(), final_norm.data_ptr(), lm_head.data_ptr(),
+                self.cos.data_ptr(), self.sin.data_ptr(), int(max_steps), C.byref(handle)))
+        self.handle = handle
+        self.max_steps = int(max_steps)
+        ptrs = [C.c_void_p() for _ in range(6)]
+        check(self.lib.fsvd_model_buffers(self.handle, *[C.byref(p) for p in ptrs]))
+        self._ptrs = dict(zip(("tokens", "seqlens", "token_log", "step_counter", "logits", "hidden"),
+                              (p.value for p in ptrs)))
+        self.num_stages = int(self.lib.fsvd_model_num_stages(self.handle))
+
+    # ---- device buffers as tensors (views over library-owned memory) -----------------------
+    def _view(self, name, shape, dtype):
+        return _from_ptr(self._ptrs[name], shape, dtype, self.device)
+
+    @property
+    def tokens(self):
+        return self._view("tokens", (self.B,), torch.int32)
+
+    @property
+    def seqlens(self):
+        return self._view("seqlens", (self.B,), torch.int32)
+
+    @property
+    def token_log(self):
+        return self._view("token_log", (self.max_steps, self.B), torch.int32)
+
+    @property
+    def step_counter(self):
+        return self._view("step_counter", (1,), torch.int32)
+
+    @property
+    def logits(self):
+        return self._view("logits", (self.B, self.vocab), torch.float32)
+
+    # ---- stepping ---------------------------------------------------------------------------
+    def step(self, n_steps: int = 1) -> None:
+        """Enqueue n greedy decode steps on the current stream (no synchronisation)."""
+        check(self.lib.fsvd_model_step(self.handle, int(n_steps), torch.cuda.current_stream().cuda_stream))
+
+    def reset(self) -> None:
+        self.seqlens.zero_()
+        self.step_counter.zero_()
+
+    def prefill(self, prompt: torch.Tensor) -> None:
+        """Feed prompt[B, L] token by token through the decode kernel (fills the caches and leaves
+        the first generated token in ``tokens``)."""
+        prompt = prompt.to(device=self.device, dtype=torch.int32).contiguous()
+        if prompt.shape[0] != self.B:
+            raise ValueError(f"prompt batch {prompt.shape[0]} != engine batch {self.B}")
+        tok = self.tokens
+        for t in range(prompt.shape[1]):
+            tok.copy_(prompt[:, t])
+            self.step(1)
+
+    def status(self) -> int:
+        st = C.c_int(0)
+        check(self.lib.fsvd_model_status(self.handle, C.byref(st)))
+        return int(st.value)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            self.lib.fsvd_model_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _from_ptr(ptr: int, shape, dtype, device) -> torch.Tensor:
+    """Wrap library-owned device memory as a tensor without copying (CUDA array interface)."""
+    typestr = {torch.int32: "<i4", torch.float32: "<f4", torch.int64: "<i8", torch.uint8: "|u1"}[dtype]
+
+    class _Holder:
+        pass
+
+    h = _Holder()
+    h.__cuda_array_interface__ = {
+        "shape": tuple(int(s) for s in shape), "typestr": typestr, "data": (int(ptr), False),
+        "version": 2, "strides": None,
+    }
+    with torch.cuda.device(device):
+        return torch.as_tensor(h, device=device)

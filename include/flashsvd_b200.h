@@ -1,0 +1,182 @@
+/* flashsvd_b200 — C ABI of the B200 decode path for SVD-factored (W = U·V) Llama-shaped models.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*), enqueues
+ * work on that stream without synchronising, and returns an int status:
+ *     0  ok
+ *    <0  argument / shape / alignment / launch error (text via fsvd_last_error_string())
+ * Device-side waits are bounded; if one runs out, a non-zero word is left in the workspace and
+ * is returned by fsvd_workspace_status() / fsvd_model_status().
+ *
+ * Factor naming follows the reference: for a projection d_in -> r -> d_out the input-side
+ * factor is `*_v` with nn.Linear weight layout [r, d_in] and the output-side factor is `*_u`
+ * with layout [d_out, r]; y = u(v(x)).  All matrices are row-major and contiguous, element type
+ * given by `dtype`.  "Reference" paths below are relative to the FlashSVD repository root.
+ */
+#ifndef FLASHSVD_B200_H_
+#define FLASHSVD_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FSVD_DTYPE_BF16 0 /* bf16 storage, fp32 accumulation, outputs rounded to bf16 */
+#define FSVD_DTYPE_F32 1  /* fp32 storage and arithmetic (greedy-parity mode) */
+
+#define FSVD_OK 0
+#define FSVD_ERR_ARG (-1)
+#define FSVD_ERR_UNSUPPORTED (-2)
+#define FSVD_ERR_ALIGN (-3)
+#define FSVD_ERR_WORKSPACE (-4)
+#define FSVD_ERR_CUDA (-5)
+#define FSVD_ERR_DEVICE_WAIT (-6)
+
+/* Shapes of one model / layer.  Ranks must be multiples of 8, d and I multiples of 8,
+ * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}, B <= 4. */
+typedef struct fsvd_dims {
+  int dtype;
+  int B;       /* independent sequences */
+  int d;       /* hidden size */
+  int H, Hk;   /* query heads, key/value heads */
+  int Dh;      /* head dim */
+  int I;       /* SwiGLU intermediate size */
+  int Rq, Rk, Rv, Ro; /* attention ranks */
+  int Rg, Ru, Rd;     /* gate / up / down ranks */
+  int S_max;   /* cache capacity in tokens */
+  int vocab;
+  int n_layers;
+  float eps;   /* RMSNorm epsilon */
+} fsvd_dims;
+
+/* Device pointers of one decoder layer. */
+typedef struct fsvd_layer {
+  const void* ln1_w;    /* [d]            input_layernorm.weight */
+  const void* qkv_v;    /* [Rq+Rk+Rv, d]  cat(q_v_proj, k_v_proj, v_v_proj).weight */
+  const void* q_u;      /* [H*Dh, Rq] */
+  const void* k_u;      /* [Hk*Dh, Rk] */
+  const void* v_u;      /* [Hk*Dh, Rv] */
+  const void* o_v;      /* [Ro, H*Dh] */
+  const void* o_u;      /* [d, Ro] */
+  const void* ln2_w;    /* [d]            post_attention_layernorm.weight */
+  const void* upgate_v; /* [Ru+Rg, d]     cat(up_v_proj, gate_v_proj).weight — up rows first,
+                           the PCat order of kernels/mlp/decode/dual_split_triton_pcat_s.py:81-90 */
+  const void* gate_u;   /* [I, Rg] */
+  const void* up_u;     /* [I, Ru] */
+  const void* down_v;   /* [Rd, I] */
+  const void* down_u;   /* [d, Rd] */
+  void* k_cache;        /* [B, S_max, Hk, Dh] keys after RoPE (runtime/cache/attn_dense_kv.py:7-15) */
+  void* v_cache;        /* [B, S_max, Hk, Dh] */
+} fsvd_layer;
+
+typedef struct fsvd_model fsvd_model;
+
+/* ---- library ---------------------------------------------------------------------------- */
+int fsvd_version(void);
+const char* fsvd_last_error_string(void);
+/* SM count and opt-in shared memory per block of the current device. */
+int fsvd_device_props(int* sm_count, int* smem_optin_bytes);
+/* Launch geometry: warps per CTA (8 or 16), ring slots per warp, direct != 0 reads the factors
+ * with plain global loads instead of the bulk-copy rings, grid = number of CTAs (0 = one per
+ * SM), inflight = tiles a warp may have outstanding in the memory system at once (0 = as many
+ * as it has slots).  Defaults come from FSVD_NW / FSVD_ND / FSVD_DIRECT / FSVD_GRID /
+ * FSVD_INFLIGHT or (16, 3, 0, 0, 1). */
+int fsvd_set_launch_config(int warps, int slots, int direct, int grid, int inflight);
+
+/* Stage timeline for profiling (the analogue of the reference's per-module CUDA-event hooks,
+ * utils/evaluator.py:553-689).  While a device buffer of at least nstages * grid * 64 bytes is
+ * set, every launch records for each (stage, CTA) eight %globaltimer slots: 0 stage entry,
+ * 1 grid barrier passed, 2 input vector staged, 3 body done, 4-7 finer marks inside the vector
+ * stage-in and the tile loop.  NULL switches it off. */
+int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes);
+
+/* ---- workspace -------------------------------------------------------------------------- */
+/* Scratch (global memory beyond inputs and outputs) for the per-op entry points and
+ * fsvd_decode_layer; zero it once with fsvd_workspace_init before first use. */
+size_t fsvd_workspace_bytes(const fsvd_dims* dims);
+int fsvd_workspace_init(void* ws, size_t ws_bytes, void* stream);
+/* Blocking: copies the device status word back. 0 = no device-side wait ran out. */
+int fsvd_workspace_status(void* ws, int* device_status);
+
+/* ---- per-op entry points ------------------------------------------------------------------
+ * y[B,d_out] = (residual +) u(v(x)).  Replaces the two F.linear GEMVs of the low-rank output
+ * projection o_u_proj(o_v_proj(a)) (reference: utils/model_utils.py:640 for the shapes,
+ * benchmark/attn/bench_real_checkpoint_decode_reconstruct.py:116-123 for y = u(v(x))). */
+int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* residual, void* y,
+                      int B, int d_in, int R, int d_out, int dtype,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/* y[B,d] = (residual +) down_u(down_v(silu(gate_u(p_gate)) * up_u(p_up))).
+ * With upgate_v != NULL: x is the hidden state [B,d], optionally RMS-normalised by norm_w, and
+ * [p_up | p_gate] = upgate_v(x).  With upgate_v == NULL: x is PCat [B, Ru+Rg] = [p_up | p_gate],
+ * the input of flashsvd_mlp_dual_split_triton_pcat_s
+ * (kernels/mlp/decode/dual_split_triton_pcat_s.py:123-218, kernel :39-120); gate_u/up_u/down_v/
+ * down_u here are the nn.Linear weights, i.e. the transposes of that function's GateU/UpU/DownV/
+ * DownU arguments. */
+int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const void* upgate_v,
+                           const void* gate_u, const void* up_u, const void* down_v,
+                           const void* down_u, const void* residual, void* y,
+                           int B, int d, int I, int Ru, int Rg, int Rd, int dtype,
+                           void* ws, size_t ws_bytes, void* stream);
+
+/* Current-token q/k/v from rank space with RoPE and cache append, one launch.  Replaces the
+ * packed rank projection hidden @ packed_qkv_rank
+ * (benchmark/attn/bench_real_checkpoint_decode_reconstruct.py:125-127), the lift
+ * reconstruct_qkv_token_shared{,_hetero,_prepacked}
+ * (kernels/attn/decode/densekv_reconstruct_triton.py:464-760) and the rotary + cache-append half
+ * of flash_attn_with_kvcache (runtime/attn/decode_registry.py:177-211).  q_out[B,H,Dh] is the
+ * rotated query; k (rotated) and v are written at position cache_seqlens[b] of the caches.
+ * cos/sin are [S_max, Dh/2] tables of type dtype (runtime/cache/attn_dense_kv.py:331-357). */
+int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const void* qkv_v,
+                         const void* q_u, const void* k_u, const void* v_u,
+                         const void* cos_tab, const void* sin_tab, void* k_cache, void* v_cache,
+                         const int* cache_seqlens, void* q_out,
+                         int B, int d, int H, int Hk, int Dh, int Rq, int Rk, int Rv, int S_max,
+                         int dtype, void* ws, size_t ws_bytes, void* stream);
+
+/* out[B,H,Dh] = softmax(q·K^T * scale)·V over the first cache_seqlens[b] + seqlen_add cached
+ * positions (GQA by head grouping), split over the keys and combined in split order.  Replaces
+ * the attention half of flash_attn_with_kvcache (runtime/attn/decode_registry.py:177-211);
+ * scale <= 0 selects 1/sqrt(Dh). */
+int fsvd_flash_decode(const void* q, const void* k_cache, const void* v_cache,
+                      const int* cache_seqlens, int seqlen_add, void* out,
+                      int B, int H, int Hk, int Dh, int S_max, float scale, int dtype,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/* One whole decoder layer for one new token per sequence, one launch:
+ * x_out = h + mlp(rms(h)), h = x_in + attn(rms(x_in)); the layer's caches receive the new
+ * token at position cache_seqlens[b].  Replaces transformers' LlamaDecoderLayer.forward as the
+ * reference drives it from utils/evaluator.py:69-78 in mode="flashsvd". */
+int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab,
+                      const void* sin_tab, const int* cache_seqlens, const void* x_in, void* x_out,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/* ---- whole-model decode -------------------------------------------------------------------
+ * A model owns a device-resident stage program and its scratch (allocated here, once).  One
+ * step = embed -> n_layers decoder layers -> final RMSNorm -> lm_head -> argmax in ONE launch;
+ * token ids and sequence lengths live on the device, so consecutive steps need no host
+ * round-trip (the reference builds torch.tensor([pos]) and calls .item() every token,
+ * scripts/demo_support/api.py:285-312, utils/evaluator.py:39-82,505-512). */
+int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const void* embed,
+                      const void* final_norm_w, const void* lm_head, const void* cos_tab,
+                      const void* sin_tab, int max_steps, fsvd_model** out);
+int fsvd_model_destroy(fsvd_model* m);
+/* Enqueue n_steps greedy decode steps. */
+int fsvd_model_step(fsvd_model* m, int n_steps, void* stream);
+/* Device buffers: tokens[B] (in: token to feed, out: sampled token), seqlens[B],
+ * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32, hidden[B,d] fp32. */
+int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
+                       int** step_counter, float** logits, float** hidden);
+/* Number of stages of the model's program (sizes the trace buffer). */
+int fsvd_model_num_stages(fsvd_model* m);
+/* Blocking: 0 when no device-side wait ran out since the last reset. */
+int fsvd_model_status(fsvd_model* m, int* device_status);
+/* Clears the barrier words and the status after an error. */
+int fsvd_model_reset_sync(fsvd_model* m, void* stream);
+/* Kernel launches enqueued by this library since load (for launch accounting). */
+long long fsvd_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHSVD_B200_H_ */
