@@ -71,7 +71,7 @@ def load() -> C.CDLL:
     lib.fsvd_version.restype = ip
     lib.fsvd_last_error_string.restype = C.c_char_p
     lib.fsvd_device_props.argtypes = [C.POINTER(ip), C.POINTER(ip)]
-    lib.fsvd_set_launch_config.argtypes = [ip, ip, ip, ip, ip]
+    lib.fsvd_set_launch_config.argtypes = [ip, ip, ip]
     lib.fsvd_workspace_bytes.argtypes = [C.POINTER(FsvdDims)]
     lib.fsvd_workspace_bytes.restype = sz
     lib.fsvd_workspace_init.argtypes = [vp, sz, vp]

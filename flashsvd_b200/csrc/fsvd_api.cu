@@ -15,9 +15,7 @@
 
 using namespace fsvd;
 
-static constexpr int kRowsPerTile = 4;
-static constexpr int kRowBytes = 1024;
-static constexpr int kSlotBytes = kRowsPerTile * kRowBytes;
+static constexpr int kRowsPerTile = 8;  // factor rows per unit
 
 // ------------------------------------------------------------------------------- errors
 static thread_local char g_err[512] = "";
@@ -41,9 +39,9 @@ static int fail(int code, const char* fmt, ...) {
 
 // ------------------------------------------------------------------------------- geometry
 struct LaunchCfg {
-  int nw, nd, direct, grid, inflight;
+  int nw, depth, grid;
 };
-static LaunchCfg g_cfg = {0, 0, 0, 0, 0};
+static LaunchCfg g_cfg = {0, 0, 0};
 static std::once_flag g_cfg_once;
 
 static int env_int(const char* name, int dflt) {
@@ -51,11 +49,9 @@ static int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 static void cfg_from_env() {
-  g_cfg.nw = env_int("FSVD_NW", 16);
-  g_cfg.nd = env_int("FSVD_ND", 3);
-  g_cfg.direct = env_int("FSVD_DIRECT", 0);
+  g_cfg.nw = env_int("FSVD_NW", 8);
+  g_cfg.depth = env_int("FSVD_DEPTH", 16);
   g_cfg.grid = env_int("FSVD_GRID", 0);
-  g_cfg.inflight = env_int("FSVD_INFLIGHT", 1);
 }
 static LaunchCfg current_cfg() {
   std::call_once(g_cfg_once, cfg_from_env);
@@ -80,60 +76,40 @@ static int get_props(DevProps& p) {
   return 0;
 }
 
-static constexpr int hdr_bytes(int nw, int nd) { return smem_header_bytes(nw, nd); }
-
 // ------------------------------------------------------------------------------- kernel table
 // The kernel instantiations live in fsvd_inst_*.cu (one translation unit per element type and
 // batch width, so they compile in parallel); each exports a table of launchers.
 #include "fsvd_launch.h"
-extern const KernelEntry g_kernels_bf16_b1[];
-extern const KernelEntry g_kernels_bf16_b4[];
-extern const KernelEntry g_kernels_f32_b1[];
-extern const KernelEntry g_kernels_f32_b4[];
-static const KernelEntry* const g_kernel_tables[] = {g_kernels_bf16_b1, g_kernels_bf16_b4,
-                                                     g_kernels_f32_b1, g_kernels_f32_b4};
+extern const KernelEntry g_kernels_bf16[];
+extern const KernelEntry g_kernels_f32[];
+static const KernelEntry* const g_kernel_tables[] = {g_kernels_bf16, g_kernels_f32};
 
-// Resolved launch: kernel + sizes for a given dtype / batch / vector length.
+// Resolved launch: kernel + geometry for a given dtype / batch.
 struct Resolved {
   LaunchFn fn = nullptr;
-  int nw = 0, nd = 0, bulk = 0, grid = 0, nb = 0, inflight = 0;
-  size_t smem = 0;
-  int total_warps() const { return grid * nw; }
+  int nw = 0, depth = 0, grid = 0, smem_optin = 0;
 };
 
-static int resolve(int dtype, int B, int max_vec_len, Resolved& r) {
+static int resolve(int dtype, int B, Resolved& r) {
   const LaunchCfg c = current_cfg();
   DevProps p;
   if (int e = get_props(p)) return e;
-  if (B < 1 || B > 4) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..4)", B);
-  const int nb = B == 1 ? 1 : 4;
-  const int esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
-  const size_t vec = (size_t)B * ((max_vec_len + 7) / 8 * 8) * esize;
+  const int bmax = dtype == FSVD_DTYPE_BF16 ? 8 : 4;
+  if (B < 1 || B > bmax) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..%d)", B, bmax);
   r.grid = c.grid > 0 ? (c.grid < p.sms ? c.grid : p.sms) : p.sms;
-  r.nb = nb;
-  r.inflight = c.inflight;
-  // Prefer the requested warp count with the most slots (not above the request) that fit in
-  // shared memory next to the staged vector; otherwise any variant that fits.
+  r.smem_optin = p.smem_optin;
   const KernelEntry* best = nullptr;
-  for (int pass = 0; pass < 2 && !best; ++pass) {
+  for (int pass = 0; pass < 2 && !best; ++pass)
     for (const KernelEntry* tab : g_kernel_tables)
-    for (const KernelEntry* kp = tab; kp->fn; ++kp) {
-      const KernelEntry& k = *kp;
-      if (k.dtype != dtype || k.nb != nb || k.bulk != (c.direct ? 0 : 1)) continue;
-      if (pass == 0 && (k.nw != c.nw || (k.bulk && k.nd > c.nd))) continue;
-      const size_t need = hdr_bytes(k.nw, k.nd) + (k.bulk ? (size_t)k.nw * k.nd * kSlotBytes : 0) + vec;
-      if (need > (size_t)p.smem_optin) continue;
-      if (!best || k.nd > best->nd) best = &k;
-    }
-  }
-  if (!best)
-    return fail(FSVD_ERR_UNSUPPORTED, "no kernel variant fits: vector of %zu bytes, %d bytes of shared memory",
-                vec, p.smem_optin);
+      for (const KernelEntry* kp = tab; kp->fn; ++kp) {
+        if (kp->dtype != dtype) continue;
+        if (pass == 0 && (kp->nw != c.nw || kp->depth != c.depth)) continue;
+        if (!best) best = kp;
+      }
+  if (!best) return fail(FSVD_ERR_UNSUPPORTED, "no kernel variant for dtype %d", dtype);
   r.fn = best->fn;
   r.nw = best->nw;
-  r.nd = best->nd;
-  r.bulk = best->bulk;
-  r.smem = hdr_bytes(best->nw, best->nd) + (best->bulk ? (size_t)best->nw * best->nd * kSlotBytes : 0) + vec;
+  r.depth = best->depth;
   return 0;
 }
 
@@ -174,14 +150,17 @@ static WsLayout ws_layout(const fsvd_dims& D) {
 // ------------------------------------------------------------------------------- builder
 struct Builder {
   std::vector<Stage> st;
-  int TW, KC, B, esize;
-  long long cum = 0;
+  int grid, NW, TW, CB, B, esize;
+  long long cum_units = 0;   // GEMV units handed out so far (rotates the unit -> CTA map)
+  long long cum_items = 0;   // attention items handed out so far (item -> warp map)
   int max_vec = 8;
 
   Builder(const Resolved& r, int dtype, int B_) {
-    TW = r.total_warps();
+    grid = r.grid;
+    NW = r.nw;
+    TW = r.grid * r.nw;
     esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
-    KC = kRowBytes / esize;
+    CB = 64 / esize;   // columns of one block: 4 lanes x 16 bytes
     B = B_;
   }
   Stage blank() {
@@ -191,11 +170,12 @@ struct Builder {
     s.segs = 1;
     return s;
   }
-  void finish_items(Stage& s, long long items) {
-    s.rot = (int)(cum % TW);
-    cum += items;
+  void finish_items(Stage& s, long long items) {   // ST_ATTN
+    s.rot = (int)(cum_items % TW);
+    cum_items += items;
   }
-  // generic GEMV stage; segs chosen when split_k
+  // GEMV stage.  Units (8 rows x one K segment) go round-robin to the CTAs; with split_k the K
+  // range is cut into the smallest number of segments that loads the CTAs evenly (>= 90 %).
   Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k) {
     Stage s = blank();
     s.type = ST_GEMV;
@@ -205,37 +185,123 @@ struct Builder {
     s.K = K;
     s.ldw = ldw;
     const int groups = (P + kRowsPerTile - 1) / kRowsPerTile;
-    int segs = 1;
+    const int kalign = K >= 4 * CB * NW ? CB * NW : CB;   // whole blocks for every warp if K allows
+    int best_segs = 1, best_kseg = (K + kalign - 1) / kalign * kalign;
     if (split_k) {
-      const int maxsegs = imax(1, (K + KC - 1) / KC) < kMaxSegs ? imax(1, (K + KC - 1) / KC) : kMaxSegs;
-      while (segs < maxsegs && (long long)groups * segs * 10 < (long long)TW * 9) ++segs;
+      double best_eff = 0;
+      for (int segs = 1; segs <= kMaxSegs; ++segs) {
+        int kseg = (K + segs - 1) / segs;
+        kseg = (kseg + kalign - 1) / kalign * kalign;
+        const int real = (K + kseg - 1) / kseg;
+        if (real != segs) continue;
+        const long long units = (long long)groups * real;
+        const double eff = (double)units / (double)(((units + grid - 1) / grid) * grid);
+        if (eff > best_eff + 1e-9) {
+          best_eff = eff;
+          best_segs = real;
+          best_kseg = kseg;
+        }
+        if (eff >= 0.9) break;
+      }
     }
-    int kseg = (K + segs - 1) / segs;
-    kseg = (kseg + KC - 1) / KC * KC;
-    segs = (K + kseg - 1) / kseg;
-    s.segs = segs;
-    s.kseg = kseg;
-    finish_items(s, (long long)groups * segs);
+    s.segs = best_segs;
+    s.kseg = best_kseg;
+    {
+      // warps per unit: long slices amortise the per-unit work, more unit slots keep all warps
+      // busy; cost in block-equivalents, ~6 for switching unit or operand
+      const long long units = (long long)groups * best_segs;
+      const int nu = (int)((units + grid - 1) / grid);
+      const int nblk = ((best_kseg < K ? best_kseg : K) + CB - 1) / CB;
+      const int nops = WB ? 2 : 1;
+      long long best_cost = -1;
+      for (int ks = 1; ks <= NW; ks *= 2) {
+        const int slots = NW / ks;
+        const long long rounds = (nu + slots - 1) / slots;
+        const long long cost = rounds * nops * ((nblk + ks - 1) / ks + 6);
+        if (best_cost < 0 || cost < best_cost) {
+          best_cost = cost;
+          s.ksplit = ks;
+        }
+      }
+    }
+    s.rot = (int)(cum_units % grid);
+    cum_units += (long long)groups * best_segs;
     st.push_back(s);
     return st.back();
   }
-  // Input vector from a caller tensor or a buffer that is complete when the stage starts.
+  // Input vector of the stage just appended (s must be st.back()).  `barrier`: the vector is
+  // produced by earlier stages of this program, so the stage waits at a grid barrier and the
+  // stage before it arrives there.
   void vec(Stage& s, int mode, const void* src, int len, int nseg, bool barrier) {
     s.vl_mode = mode;
     s.vl_src = src;
     s.vl_len = len;
     s.vl_nseg = nseg;
-    if (barrier) s.flags |= SF_BARRIER;
+    if (barrier) need_barrier(s);
     if (len > max_vec) max_vec = len;
   }
-  // Input vector of (fp32, tag) pairs produced by stage `producer` of this program: the
-  // consumer polls the tags, no barrier.
-  void vec_tagged(Stage& s, int mode, const void* src, int len, int nseg, int producer) {
-    vec(s, mode, src, len, nseg, false);
-    s.flags |= SF_IN_TAG;
-    s.vl_tag = producer;
+  void need_barrier(Stage& s) {
+    s.flags |= SF_BARRIER;
+    if (st.size() >= 2) st[st.size() - 2].flags |= SF_ARRIVE;
   }
   int last() const { return (int)st.size() - 1; }
+
+  static long long stage_bytes(const Stage& s, int esize) {
+    if (s.type != ST_GEMV) return 0;
+    return (long long)s.P * s.K * esize * (s.WB ? 2 : 1);
+  }
+  // Decide which later stages each stage prefetches into L2: every GEMV stage is prefetched
+  // once, as early as possible while the bytes prefetched but not yet consumed stay in budget.
+  void plan_prefetch() {
+    const long long budget = (long long)env_int("FSVD_PF_MB", 48) << 20;
+    const int n = (int)st.size();
+    if (budget <= 0) {
+      for (Stage& s : st) s.pf_begin = s.pf_end = 0;
+      return;
+    }
+    std::vector<int> by(n, -1);
+    int next = 1;
+    long long outstanding = 0;
+    for (int s = 0; s < n; ++s) {
+      if (by[s] >= 0) outstanding -= stage_bytes(st[s], esize);   // s is being consumed now
+      if (next <= s) next = s + 1;
+      st[s].pf_begin = next;
+      while (next < n) {
+        const long long b = stage_bytes(st[next], esize);
+        if (b > 0 && outstanding + b > budget && next > s + 1) break;
+        by[next] = s;
+        outstanding += b;
+        ++next;
+        if (b > 0 && outstanding > budget) break;
+      }
+      st[s].pf_end = next;
+      if (st[s].type != ST_GEMV) st[s].pf_begin = st[s].pf_end = 0;   // only GEMV stages prefetch
+    }
+    // stages skipped because a non-GEMV stage "owned" them are picked up by the next GEMV stage
+    int covered = 1;
+    for (int s = 0; s < n; ++s) {
+      if (st[s].type != ST_GEMV) continue;
+      if (st[s].pf_begin > covered) st[s].pf_begin = covered > s + 1 ? covered : s + 1;
+      if (st[s].pf_end < st[s].pf_begin) st[s].pf_end = st[s].pf_begin;
+      if (st[s].pf_end > covered) covered = st[s].pf_end;
+    }
+  }
+  // Shared memory the program needs beyond the header: warps' partial sums and the staged vector.
+  int part_bytes() const {
+    long long mx = 0;
+    for (const Stage& s : st) {
+      if (s.type != ST_GEMV) continue;
+      const long long units = (long long)((s.P + kRowsPerTile - 1) / kRowsPerTile) * s.segs;
+      const long long nu = (units + grid - 1) / grid;
+      const long long b = nu * (s.WB ? 2 : 1) * (s.ksplit > 0 ? s.ksplit : NW) * 64 * 4;
+      if (b > mx) mx = b;
+    }
+    return (int)((mx + 255) / 256 * 256);
+  }
+  int xstride() const { return (max_vec + 7) / 8 * 8; }
+  size_t smem_bytes() const {
+    return (size_t)smem_header_bytes() + part_bytes() + (size_t)B * xstride() * esize;
+  }
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -256,21 +322,19 @@ static int check_dims(const fsvd_dims& D) {
 }
 
 struct LayerIO {
-  const void* x_in;    // hidden state read by the first RMSNorm and the first residual
-  int x_in_producer;   // >= 0: x_in holds (fp32, tag) pairs written by that stage; -1: tensor of T
-  void* x_out;         // destination of the last residual
-  int x_out_tagged;    // 1: (fp32, tag) pairs, 0: tensor of T
+  const void* x_in;    // hidden state [B, d] of type T read by the first RMSNorm and residual
+  bool x_in_barrier;   // x_in is written by the preceding stage of the same program
+  void* x_out;         // hidden state [B, d] of type T written by the last residual
   const int* seqlens;
   const void* cos_tab;
   const void* sin_tab;
 };
 
-// Appends the stages of one decoder layer and returns the index of the stage that writes
-// x_out.  `mid` (in the workspace) holds the hidden state between the attention and MLP halves.
-// Every vector handed from one stage to the next is tagged, so the only grid barrier of a layer
-// is the one in front of the attention stage (q and the new cache row are plain stores).
-static int build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, const LayerIO& io,
-                       char* ws, const WsLayout& L) {
+// Appends the stages of one decoder layer.  Rank-space partial sums travel as fp32, every other
+// activation (attention output, SwiGLU activation, hidden state) as T, which is where the
+// PyTorch path rounds them.
+static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, const LayerIO& io,
+                        char* ws, const WsLayout& L) {
   void* pa = ws + L.pa;
   void* pb = ws + L.pb;
   void* hact = ws + L.hact;
@@ -281,23 +345,18 @@ static int build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, con
 
   {  // 1. rank projection of q/k/v on the normalised hidden state
     Stage& s = b.gemv(Lw.qkv_v, nullptr, Rqkv, D.d, D.d, true);
-    if (io.x_in_producer >= 0) {
-      b.vec_tagged(s, VL_RMSNORM, io.x_in, D.d, 1, io.x_in_producer);
-    } else {
-      b.vec(s, VL_RMSNORM, io.x_in, D.d, 1, false);
-      s.flags |= SF_IN_T;
-    }
+    b.vec(s, VL_RMSNORM, io.x_in, D.d, 1, io.x_in_barrier);
+    s.flags |= SF_IN_T;
     s.vl_w = Lw.ln1_w;
     s.eps = D.eps;
     s.epi = EPI_PARTIAL;
-    s.flags |= SF_OUT_TAG;
     s.out = pa;
   }
-  const int i1 = b.last(), segs1 = b.st.back().segs;
+  const int segs1 = b.st.back().segs;
   {  // 2. lift q with rotary
     Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
                       D.H * half, D.Rq, D.Rq, false);
-    b.vec_tagged(s, VL_SUM, pa, Rqkv, segs1, i1);
+    b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
     s.rope_half = half;
     s.xA_off = s.xB_off = 0;
     s.epi = EPI_ROPE_Q;
@@ -326,7 +385,7 @@ static int build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, con
   {  // 5. attention over the cache including the token just appended
     Stage s = b.blank();
     s.type = ST_ATTN;
-    s.flags = SF_BARRIER | SF_OUT_TAG;
+    s.flags = SF_OUT_T;
     s.q = qbuf;
     s.kcache = Lw.k_cache;
     s.vcache = Lw.v_cache;
@@ -344,62 +403,59 @@ static int build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, con
     s.nsplit = ns;
     b.finish_items(s, (long long)D.B * D.Hk * ns);
     b.st.push_back(s);
+    b.need_barrier(b.st.back());
   }
-  const int i5 = b.last();
   {  // 6. o rank projection
     Stage& s = b.gemv(Lw.o_v, nullptr, D.Ro, HD, HD, true);
-    b.vec_tagged(s, VL_SUM, attn, HD, 1, i5);
+    b.vec(s, VL_SUM, attn, HD, 1, true);
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
-    s.flags |= SF_OUT_TAG;
     s.out = pb;
   }
-  const int i6 = b.last(), segs6 = b.st.back().segs;
+  const int segs6 = b.st.back().segs;
   {  // 7. o lift + residual
     Stage& s = b.gemv(Lw.o_u, nullptr, D.d, D.Ro, D.Ro, false);
-    b.vec_tagged(s, VL_SUM, pb, D.Ro, segs6, i6);
+    b.vec(s, VL_SUM, pb, D.Ro, segs6, true);
     s.epi = EPI_RESID;
     s.resid = io.x_in;
-    s.flags |= (io.x_in_producer >= 0 ? SF_RESID_TAG : SF_RESID_T) | SF_OUT_TAG;
+    s.flags |= SF_RESID_T | SF_OUT_T;
     s.out = mid;
   }
-  const int i7 = b.last();
   {  // 8. MLP rank projection on the normalised hidden state: [p_up | p_gate]
     Stage& s = b.gemv(Lw.upgate_v, nullptr, D.Ru + D.Rg, D.d, D.d, true);
-    b.vec_tagged(s, VL_RMSNORM, mid, D.d, 1, i7);
+    b.vec(s, VL_RMSNORM, mid, D.d, 1, true);
+    s.flags |= SF_IN_T;
     s.vl_w = Lw.ln2_w;
     s.eps = D.eps;
     s.epi = EPI_PARTIAL;
-    s.flags |= SF_OUT_TAG;
     s.out = pa;
   }
-  const int i8 = b.last(), segs8 = b.st.back().segs;
+  const int segs8 = b.st.back().segs;
   {  // 9. gate/up lift + SiLU·mul
     Stage& s = b.gemv(Lw.gate_u, Lw.up_u, D.I, D.Rg, D.Rg, false);
-    b.vec_tagged(s, VL_SUM, pa, D.Ru + D.Rg, segs8, i8);
+    b.vec(s, VL_SUM, pa, D.Ru + D.Rg, segs8, true);
     s.xA_off = D.Ru;  // gate input follows the up input
     s.xB_off = 0;
     s.epi = EPI_SWIGLU;
-    s.flags |= SF_OUT_TAG;
+    s.flags |= SF_OUT_T;
     s.out = hact;
   }
-  const int i9 = b.last();
   {  // 10. down rank projection
     Stage& s = b.gemv(Lw.down_v, nullptr, D.Rd, D.I, D.I, true);
-    b.vec_tagged(s, VL_SUM, hact, D.I, 1, i9);
+    b.vec(s, VL_SUM, hact, D.I, 1, true);
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
-    s.flags |= SF_OUT_TAG;
     s.out = pb;
   }
-  const int i10 = b.last(), segs10 = b.st.back().segs;
+  const int segs10 = b.st.back().segs;
   {  // 11. down lift + residual
     Stage& s = b.gemv(Lw.down_u, nullptr, D.d, D.Rd, D.Rd, false);
-    b.vec_tagged(s, VL_SUM, pb, D.Rd, segs10, i10);
+    b.vec(s, VL_SUM, pb, D.Rd, segs10, true);
     s.epi = EPI_RESID;
     s.resid = mid;
-    s.flags |= SF_RESID_TAG | (io.x_out_tagged ? SF_OUT_TAG : SF_OUT_T);
+    s.flags |= SF_RESID_T | SF_OUT_T;
     s.out = io.x_out;
   }
-  return b.last();
 }
 
 static int check_layer_ptrs(const fsvd_layer& Lw) {
@@ -412,14 +468,29 @@ static int check_layer_ptrs(const fsvd_layer& Lw) {
   return 0;
 }
 
-static int launch_small(const Resolved& r, const Builder& b, SyncState* sync, cudaStream_t stream) {
+static int check_units(const Builder& b) {
+  for (const Stage& s : b.st) {
+    if (s.type != ST_GEMV) continue;
+    const long long units = (long long)((s.P + kRowsPerTile - 1) / kRowsPerTile) * s.segs;
+    if ((units + b.grid - 1) / b.grid > 64)
+      return fail(FSVD_ERR_UNSUPPORTED, "a stage of %d rows has more than 64 units per CTA", s.P);
+  }
+  return 0;
+}
+
+static int launch_small(const Resolved& r, Builder& b, SyncState* sync, cudaStream_t stream) {
   if ((int)b.st.size() > kMaxSmallStages) return fail(FSVD_ERR_UNSUPPORTED, "program too long");
+  if (int e = check_units(b)) return e;
+  b.plan_prefetch();
+  const size_t smem = b.smem_bytes();
+  if (smem > (size_t)r.smem_optin)
+    return fail(FSVD_ERR_UNSUPPORTED, "%zu bytes of shared memory needed, %d available", smem, r.smem_optin);
   SmallProgram sp;
   memset(&sp, 0, sizeof(sp));
   for (size_t i = 0; i < b.st.size(); ++i) sp.st[i] = b.st[i];
-  const int xstride = (b.max_vec + 7) / 8 * 8;
-  unsigned long long* tr = g_trace_bytes >= b.st.size() * (size_t)r.grid * 64 ? g_trace : nullptr;
-  cudaError_t e = r.fn(nullptr, &sp, 1, (int)b.st.size(), sync, xstride, tr, r.inflight, r.grid, r.smem, stream);
+  unsigned long long* tr = g_trace_bytes >= b.st.size() * (size_t)r.grid * 128 ? g_trace : nullptr;
+  cudaError_t e = r.fn(nullptr, &sp, 1, (int)b.st.size(), sync, b.xstride(), b.part_bytes(), tr, r.grid,
+                       smem, stream);
   if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   g_launches.fetch_add(1);
   return 0;
@@ -446,17 +517,13 @@ int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes) {
   return 0;
 }
 
-int fsvd_model_num_stages(fsvd_model* m);
-
-int fsvd_set_launch_config(int warps, int slots, int direct, int grid, int inflight) {
+int fsvd_set_launch_config(int warps, int depth, int grid) {
   current_cfg();
   if (warps != 8 && warps != 16) return fail(FSVD_ERR_ARG, "warps must be 8 or 16");
-  if (slots < 1) return fail(FSVD_ERR_ARG, "slots must be >= 1");
+  if (depth < 1) return fail(FSVD_ERR_ARG, "depth must be >= 1");
   g_cfg.nw = warps;
-  g_cfg.nd = slots;
-  g_cfg.direct = direct ? 1 : 0;
+  g_cfg.depth = depth;
   g_cfg.grid = grid < 0 ? 0 : grid;
-  g_cfg.inflight = inflight < 0 ? 0 : inflight;
   return 0;
 }
 
@@ -514,20 +581,20 @@ int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* r
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
-  if (int e = resolve(dtype, B, imax(d_in, R), r)) return e;
+  if (int e = resolve(dtype, B, r)) return e;
   Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
   {
     Stage& s = b.gemv(v, nullptr, R, d_in, d_in, true);
     b.vec(s, VL_SUM, x, d_in, 1, false);
-    s.flags |= SF_IN_T | SF_OUT_TAG;
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
     s.out = w + L.pb;
   }
   const int segs = b.st.back().segs;
   {
     Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
-    b.vec_tagged(s, VL_SUM, w + L.pb, R, segs, 0);
+    b.vec(s, VL_SUM, w + L.pb, R, segs, true);
     s.epi = residual ? EPI_RESID : EPI_STORE;
     s.resid = residual;
     s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
@@ -554,7 +621,7 @@ int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const v
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
-  if (int e = resolve(dtype, B, imax(imax(d, I), Ru + Rg), r)) return e;
+  if (int e = resolve(dtype, B, r)) return e;
   Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
   int segs_rank = 1;
@@ -563,7 +630,7 @@ int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const v
   if (upgate_v) {
     Stage& s = b.gemv(upgate_v, nullptr, Ru + Rg, d, d, true);
     b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, false);
-    s.flags |= SF_IN_T | SF_OUT_TAG;
+    s.flags |= SF_IN_T;
     s.vl_w = norm_w;
     s.eps = eps;
     s.epi = EPI_PARTIAL;
@@ -578,27 +645,25 @@ int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const v
       b.vec(s, VL_SUM, pcat, Ru + Rg, 1, false);
       s.flags |= SF_IN_T;
     } else {
-      b.vec_tagged(s, VL_SUM, pcat, Ru + Rg, segs_rank, 0);
+      b.vec(s, VL_SUM, pcat, Ru + Rg, segs_rank, true);
     }
     s.xA_off = Ru;
     s.xB_off = 0;
     s.epi = EPI_SWIGLU;
-    s.flags |= SF_OUT_TAG;
+    s.flags |= SF_OUT_T;
     s.out = w + L.hact;
   }
-  const int i_act = b.last();
   {
     Stage& s = b.gemv(down_v, nullptr, Rd, I, I, true);
-    b.vec_tagged(s, VL_SUM, w + L.hact, I, 1, i_act);
+    b.vec(s, VL_SUM, w + L.hact, I, 1, true);
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
-    s.flags |= SF_OUT_TAG;
     s.out = w + L.pb;
   }
-  const int i_down = b.last();
   const int segs = b.st.back().segs;
   {
     Stage& s = b.gemv(down_u, nullptr, d, Rd, Rd, false);
-    b.vec_tagged(s, VL_SUM, w + L.pb, Rd, segs, i_down);
+    b.vec(s, VL_SUM, w + L.pb, Rd, segs, true);
     s.epi = residual ? EPI_RESID : EPI_STORE;
     s.resid = residual;
     s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
@@ -625,14 +690,14 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
-  if (int e = resolve(dtype, B, imax(d, Rq + Rk + Rv), r)) return e;
+  if (int e = resolve(dtype, B, r)) return e;
   Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
   const int half = Dh / 2, Rqkv = Rq + Rk + Rv;
   {
     Stage& s = b.gemv(qkv_v, nullptr, Rqkv, d, d, true);
     b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, false);
-    s.flags |= SF_IN_T | SF_OUT_TAG;
+    s.flags |= SF_IN_T;
     s.vl_w = norm_w;
     s.eps = eps;
     s.epi = EPI_PARTIAL;
@@ -641,7 +706,7 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
   const int segs = b.st.back().segs;
   {
     Stage& s = b.gemv(q_u, reinterpret_cast<const char*>(q_u) + (size_t)half * Rq * b.esize, H * half, Rq, Rq, false);
-    b.vec_tagged(s, VL_SUM, w + L.pa, Rqkv, segs, 0);
+    b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, true);
     s.rope_half = half;
     s.epi = EPI_ROPE_Q;
     s.flags |= SF_OUT_T;
@@ -680,7 +745,7 @@ int fsvd_flash_decode(const void* q, const void* k_cache, const void* v_cache,
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
-  if (int e = resolve(dtype, B, 8, r)) return e;
+  if (int e = resolve(dtype, B, r)) return e;
   Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
   Stage s = b.blank();
@@ -717,10 +782,9 @@ int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
-  const int maxvec = imax(imax(D.d, D.I), imax(D.Rq + D.Rk + D.Rv, imax(D.Ru + D.Rg, D.H * D.Dh)));
-  if (int e = resolve(D.dtype, D.B, maxvec, r)) return e;
+  if (int e = resolve(D.dtype, D.B, r)) return e;
   Builder b(r, D.dtype, D.B);
-  LayerIO io = {x_in, -1, x_out, 0, cache_seqlens, cos_tab, sin_tab};
+  LayerIO io = {x_in, false, x_out, cache_seqlens, cos_tab, sin_tab};
   build_layer(b, D, *layer, io, reinterpret_cast<char*>(ws), L);
   return launch_small(r, b, reinterpret_cast<SyncState*>(reinterpret_cast<char*>(ws) + L.sync),
                       (cudaStream_t)stream);
@@ -733,15 +797,18 @@ struct fsvd_model {
   WsLayout L;
   char* ws = nullptr;
   Stage* prog = nullptr;
-  int nstages = 0, xstride = 0, max_steps = 0;
+  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0;
+  size_t smem = 0;
   int* tokens = nullptr;
   int* seqlens = nullptr;
   int* token_log = nullptr;
   int* step_counter = nullptr;
   float* logits = nullptr;
-  float* xbuf = nullptr;  // hidden state between layers, (fp32, tag) pairs
+  float* xbuf = nullptr;  // hidden state between layers, [B, d] of type T
   char* extra = nullptr;
 };
+
+int fsvd_model_destroy(fsvd_model* m);
 
 int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const void* embed,
                       const void* final_norm_w, const void* lm_head, const void* cos_tab,
@@ -761,8 +828,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   m->D = D;
   m->max_steps = max_steps;
   m->L = ws_layout(D);
-  const int maxvec = imax(imax(D.d, D.I), imax(D.Rq + D.Rk + D.Rv, imax(D.Ru + D.Rg, D.H * D.Dh)));
-  if (int e = resolve(D.dtype, D.B, maxvec, m->r)) { delete m; return e; }
+  if (int e = resolve(D.dtype, D.B, m->r)) { delete m; return e; }
 
   const size_t extra_bytes = al256((size_t)D.B * 4) * 2 + al256(4) + al256((size_t)max_steps * D.B * 4) +
                              al256((size_t)D.B * D.vocab * 4);
@@ -798,23 +864,19 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     s.WA = embed;
     s.P = D.d;
     s.out = xbuf;
-    s.flags = SF_OUT_TAG;
+    s.flags = SF_OUT_T;
     s.tokens = m->tokens;
     s.vocab = D.vocab;
     b.st.push_back(s);
   }
-  int producer = b.last();
   for (int l = 0; l < D.n_layers; ++l) {
-    LayerIO io = {xbuf, producer, xbuf, 1, m->seqlens, cos_tab, sin_tab};
-    producer = build_layer(b, D, layers[l], io, m->ws, m->L);
-  }
-  if ((unsigned)b.st.size() + 2 >= kTagStride) {
-    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); delete m;
-    return fail(FSVD_ERR_UNSUPPORTED, "program of %zu stages is too long", b.st.size());
+    LayerIO io = {xbuf, true, xbuf, m->seqlens, cos_tab, sin_tab};
+    build_layer(b, D, layers[l], io, m->ws, m->L);
   }
   {
     Stage& s = b.gemv(lm_head, nullptr, D.vocab, D.d, D.d, false);
-    b.vec_tagged(s, VL_RMSNORM, xbuf, D.d, 1, producer);
+    b.vec(s, VL_RMSNORM, xbuf, D.d, 1, true);
+    s.flags |= SF_IN_T;
     s.vl_w = final_norm_w;
     s.eps = D.eps;
     s.epi = EPI_STORE;
@@ -823,7 +885,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   {
     Stage s = b.blank();
     s.type = ST_ARGMAX;
-    s.flags = SF_BARRIER;
+    s.flags = 0;
     s.vl_src = m->logits;
     s.vocab = D.vocab;
     s.tokens = m->tokens;
@@ -832,9 +894,17 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     s.seqlens_rw = m->seqlens;
     s.max_steps = max_steps;
     b.st.push_back(s);
+    b.need_barrier(b.st.back());
   }
+  if (int e = check_units(b)) {
+    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); delete m;
+    return e;
+  }
+  b.plan_prefetch();
   m->nstages = (int)b.st.size();
-  m->xstride = (b.max_vec + 7) / 8 * 8;
+  m->xstride = b.xstride();
+  m->part_bytes = b.part_bytes();
+  m->smem = b.smem_bytes();
   ce = cudaMalloc(&m->prog, sizeof(Stage) * b.st.size());
   if (ce == cudaSuccess)
     ce = cudaMemcpy(m->prog, b.st.data(), sizeof(Stage) * b.st.size(), cudaMemcpyHostToDevice);
@@ -843,6 +913,11 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     return fail(FSVD_ERR_CUDA, "uploading the stage program failed: %s", cudaGetErrorString(ce));
   }
   m->xbuf = xbuf;
+  if (m->smem > (size_t)m->r.smem_optin) {
+    const size_t need = m->smem;
+    fsvd_model_destroy(m);
+    return fail(FSVD_ERR_UNSUPPORTED, "%zu bytes of shared memory needed", need);
+  }
   *out = m;
   return 0;
 }
@@ -861,9 +936,9 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
   SyncState* sync = reinterpret_cast<SyncState*>(m->ws + m->L.sync);
   for (int i = 0; i < n_steps; ++i) {
-    unsigned long long* tr = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 64 ? g_trace : nullptr;
-    cudaError_t e = m->r.fn(m->prog, nullptr, 0, m->nstages, sync, m->xstride, tr, m->r.inflight,
-                            m->r.grid, m->r.smem, (cudaStream_t)stream);
+    unsigned long long* tr = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
+    cudaError_t e = m->r.fn(m->prog, nullptr, 0, m->nstages, sync, m->xstride, m->part_bytes, tr,
+                            m->r.grid, m->smem, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);
   }

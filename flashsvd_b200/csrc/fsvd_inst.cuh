@@ -1,15 +1,15 @@
-// Instantiates the interpreter for one element type and batch width; included by fsvd_inst_*.cu
-// after defining FSVD_INST_T, FSVD_INST_DTYPE, FSVD_INST_NB and FSVD_INST_TABLE.
+// Instantiates the interpreter for one element type; included by fsvd_inst_*.cu after defining
+// FSVD_INST_T, FSVD_INST_DTYPE and FSVD_INST_TABLE.
 #include "fsvd_kernel.cuh"
 #include "fsvd_launch.h"
 
 namespace {
 
-template <typename T, int NB, int NW, int ND, bool BULK>
+template <typename T, int NW, int D>
 cudaError_t launch_impl(const fsvd::Stage* prog, const fsvd::SmallProgram* small, int use_small,
-                        int nstages, fsvd::SyncState* sync, int xstride, unsigned long long* trace,
-                        int max_inflight, int grid, size_t smem, cudaStream_t stream) {
-  auto kern = fsvd::fsvd_decode_kernel<T, NB, NW, ND, BULK>;
+                        int nstages, fsvd::SyncState* sync, int xstride, int part_bytes,
+                        unsigned long long* trace, int grid, size_t smem, cudaStream_t stream) {
+  auto kern = fsvd::fsvd_decode_kernel<T, NW, D>;
   static size_t attr_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -32,14 +32,12 @@ cudaError_t launch_impl(const fsvd::Stage* prog, const fsvd::SmallProgram* small
   cfg.attrs = at;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, prog, small ? *small : empty, use_small, nstages, sync,
-                            xstride, trace, max_inflight);
+                            xstride, part_bytes, trace);
 }
 
 }  // namespace
 
-#define FSVD_K(NW, ND, BULK) \
-  {FSVD_INST_DTYPE, FSVD_INST_NB, NW, ND, BULK, &launch_impl<FSVD_INST_T, FSVD_INST_NB, NW, ND, BULK != 0>}
+#define FSVD_K(NW, D) {FSVD_INST_DTYPE, NW, D, &launch_impl<FSVD_INST_T, NW, D>}
 
-extern const KernelEntry FSVD_INST_TABLE[] = {
-    FSVD_K(16, 2, 1), FSVD_K(16, 3, 1), FSVD_K(8, 4, 1), FSVD_K(8, 6, 1),
-    FSVD_K(16, 1, 0), FSVD_K(8, 1, 0),  {0, 0, 0, 0, 0, nullptr}};
+extern const KernelEntry FSVD_INST_TABLE[] = {FSVD_K(8, 16), FSVD_K(8, 8), FSVD_K(8, 24),
+                                              FSVD_K(16, 8), {0, 0, 0, nullptr}};

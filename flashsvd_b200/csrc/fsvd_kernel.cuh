@@ -1,11 +1,31 @@
 // Persistent stage interpreter for single-token decode of low-rank (W = U·V) transformers.
 //
-// Launch geometry: one CTA per SM (cooperative launch), NW warps per CTA.  Every warp owns a
-// private ring of ND shared-memory slots; a slot holds a tile of 4 factor rows x KC elements
-// fetched with four `cp.async.bulk` copies that complete on the slot's mbarrier.  The fetch
-// cursor of a warp walks the same deterministic item sequence as its compute cursor but runs
-// up to ND tiles ahead, across stage boundaries, so the HBM stream does not drain while the
-// CTAs synchronise between two dependent stages.
+// Launch geometry: one CTA per SM (cooperative launch), NW warps per CTA.  A GEMV stage is cut
+// into units of 8 factor rows x one K segment; units go round-robin to the CTAs and inside a
+// CTA the warps split the K range of every unit, so every warp of every SM streams factor bytes
+// in every stage.  A lane loads its 16-byte fragment of a factor row straight from global
+// memory into registers (ld.global.nc, D loads in flight per lane) and feeds it to the tensor
+// cores; the partial sums of the warps meet in shared memory, are added in warp order and the
+// stage's epilogue (RoPE + cache append, SiLU·up, residual, ...) runs on the result.
+//
+// The factors of a stage do not depend on the activations, so a warp issues its first D loads
+// before it waits for the grid barrier in front of the stage, and prefetches the rows it will
+// read in the following stage(s) into L2 (prefetch.global.L2): the HBM stream keeps running
+// while the CTAs synchronise.
+//
+// (Measured on B200 before settling on this: per-warp shared-memory rings filled by
+// cp.async.bulk stall the issuing warp ~320 cycles per copy and deliver after ~1 us; rings
+// filled by 16-byte cp.async issue faster but still cost ~1700 cycles per 4 KB tile in issue,
+// wait and shared-memory reads.  Direct loads cost ~10 instructions per 512 bytes and reach
+// 6.5 TB/s with 8 warps x 16 loads in flight.)
+//
+// Arithmetic.  bf16: 8 factor rows x 32 columns are the B operand of two mma.sync.m16n8k16
+// (fp32 accumulate) and the staged activation vector the A operand, batch rows as M.  A dot
+// product does not care about the order of k, so lane (g, t) feeds the k-slots it owns with 8
+// consecutive columns: one 16-byte load of factor row g and one of activation row g.  The four
+// lanes of a quad cover 32 columns, the MMA adds them, and lane (g, t) holds the sums of
+// factor rows 2t, 2t+1 for batch row g: no unpacking, no shuffles.  fp32 (parity mode): lane
+// (g, t) multiplies 4 columns of row g with plain FMAs and the quad is reduced by shuffles.
 //
 // All waits are bounded: a wait that runs out records an error code in SyncState::status and
 // the kernel carries on without waiting again, so a fault in the protocol ends in an error
@@ -20,10 +40,8 @@
 
 namespace fsvd {
 
-constexpr int kRowsPerTile = 4;
-constexpr int kRowBytes = 1024;                      // bytes of one row piece inside a slot
-constexpr int kSlotBytes = kRowsPerTile * kRowBytes; // 4 KB
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr int kTileRows = 8;
+constexpr long long kWaitLimitClk = 4000000000ll;  // ~2 s of SM clocks
 
 // ----------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -81,6 +99,13 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -88,7 +113,28 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
                : "l"(p));
   return v;
 }
-
+// Byte offset of 16-byte chunk `chunk` of row `row` inside a slot whose rows are RB bytes long.
+template <int RB>
+__device__ __forceinline__ uint32_t slot_off(int row, int chunk) {
+  return (uint32_t)row * RB + (uint32_t)((chunk ^ ((row & 1) << 2)) << 4);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // ----------------------------------------------------------------------------- type traits
 template <typename T>
 struct TT;
@@ -100,6 +146,10 @@ struct TT<__nv_bfloat16> {
   }
   static __device__ __forceinline__ float ld(const void* p, size_t i) {
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  }
+  static __device__ __forceinline__ float ldcg(const void* p, size_t i) {
+    const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(p) + i);
+    return __uint_as_float((unsigned)u << 16);
   }
   static __device__ __forceinline__ void st(void* p, size_t i, float v) {
     reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
@@ -122,6 +172,9 @@ struct TT<float> {
   static __device__ __forceinline__ float ld(const void* p, size_t i) {
     return reinterpret_cast<const float*>(p)[i];
   }
+  static __device__ __forceinline__ float ldcg(const void* p, size_t i) {
+    return __ldcg(reinterpret_cast<const float*>(p) + i);
+  }
   static __device__ __forceinline__ void st(void* p, size_t i, float v) {
     reinterpret_cast<float*>(p)[i] = v;
   }
@@ -131,207 +184,24 @@ struct TT<float> {
     f[2] = __uint_as_float(v.z);
     f[3] = __uint_as_float(v.w);
   }
-};
-
-// ----------------------------------------------------------------------------- cursors
-// Geometry of a GEMV stage as the item walker needs it.
-struct GemvGeom {
-  const char* WA;
-  const char* WB;
-  int P, K, ldw, segs, kseg, rope_half, rot;
-  int nkch;    // KC-chunks per full K segment
-  int items;   // row groups x segments
-};
-
-struct Cursor {
-  int s;    // stage index (nstages = exhausted)
-  int it;   // item index inside the stage
-  int j;    // tile index inside the item
-  int nsub; // tiles of the current item
-};
-
-struct Tile {
-  int p0;       // first logical row
-  int g;        // operand group 0 = A, 1 = B
-  int k0;       // first column
-  int kc;       // columns in this tile
-  int seg;      // K segment
-};
-
-template <typename T>
-__device__ __forceinline__ void load_geom(const Stage* st, GemvGeom& g) {
-  constexpr int KC = kRowBytes / (int)sizeof(T);
-  g.WA = reinterpret_cast<const char*>(st->WA);
-  g.WB = reinterpret_cast<const char*>(st->WB);
-  g.P = st->P;
-  g.K = st->K;
-  g.ldw = st->ldw;
-  g.segs = st->segs;
-  g.kseg = st->kseg;
-  g.rope_half = st->rope_half;
-  g.rot = st->rot;
-  g.nkch = (g.kseg + KC - 1) / KC;
-  g.items = ((g.P + kRowsPerTile - 1) / kRowsPerTile) * g.segs;
-}
-
-template <typename T>
-__device__ __forceinline__ int item_tiles(const GemvGeom& g, int it) {
-  constexpr int KC = kRowBytes / (int)sizeof(T);
-  const int seg = it % g.segs;
-  const int klen = min(g.kseg, g.K - seg * g.kseg);
-  const int n = (klen + KC - 1) / KC;
-  return g.WB ? 2 * n : n;
-}
-
-template <typename T>
-__device__ __forceinline__ void decode_tile(const GemvGeom& g, int it, int j, int nsub, Tile& t) {
-  constexpr int KC = kRowBytes / (int)sizeof(T);
-  const int grp = it / g.segs;
-  t.seg = it - grp * g.segs;
-  const int nk = g.WB ? (nsub >> 1) : nsub;
-  t.g = (j >= nk) ? 1 : 0;
-  const int kci = j - t.g * nk;
-  const int kbeg = t.seg * g.kseg;
-  const int kend = min(g.K, kbeg + g.kseg);
-  t.k0 = kbeg + kci * KC;
-  t.kc = min(KC, kend - t.k0);
-  t.p0 = grp * kRowsPerTile;
-}
-
-__device__ __forceinline__ int phys_row(const GemvGeom& g, int p) {
-  if (g.rope_half > 0) {
-    const int h = p / g.rope_half;
-    return h * 2 * g.rope_half + (p - h * g.rope_half);
+};// ----------------------------------------------------------------------------- small helpers
+__device__ __forceinline__ int phys_row(int rope_half, int p) {
+  if (rope_half > 0) {
+    const int h = p / rope_half;
+    return h * 2 * rope_half + (p - h * rope_half);
   }
   return p;
 }
 
-// First item of this warp in a stage whose assignment is rotated by `rot`.
-__device__ __forceinline__ int first_item(int wrank, int rot, int total_warps) {
-  int f = wrank - rot;
-  if (f < 0) f += total_warps;
+// First unit / item of rank `r` when the assignment is rotated by `rot` over `n` ranks.
+__device__ __forceinline__ int first_item(int r, int rot, int n) {
+  int f = r - rot;
+  if (f < 0) f += n;
   return f;
 }
 
-// ----------------------------------------------------------------------------- warp state
-template <typename T, int ND, bool BULK>
-struct WarpCtx {
-  const Stage* prog;
-  int nstages;
-  int wrank, total_warps, lane;
-  uint32_t ring;      // shared address of this warp's first slot
-  uint32_t bars;      // shared address of this warp's first mbarrier
-  const char* ring_ptr;
-  unsigned fetch_seq, cons_seq;
-  unsigned landed_seq;   // tiles [cons_seq, landed_seq) are known to have arrived
-  unsigned max_inflight; // cap on fetch_seq - landed_seq: bounds the bytes this warp keeps queued
-                         // in the memory system, and with it the latency of every other access
-  Cursor fc;          // fetch cursor
-  GemvGeom fg;        // geometry of the fetch cursor's stage
-  SyncState* sync;
-  unsigned long long* trow;  // trace row of (current stage, this CTA) for thread 0, else null
-};
-
 __device__ __forceinline__ void trace_mark(unsigned long long* trow, int k) {
   if (trow) trow[k] = gtimer();
-}
-
-// Position the cursor on the first item of the first GEMV stage at or after stage s.
-template <typename T, int ND, bool BULK>
-__device__ __forceinline__ void fetch_seek(WarpCtx<T, ND, BULK>& w, int s) {
-  for (; s < w.nstages; ++s) {
-    const Stage* st = w.prog + s;
-    if (st->type != ST_GEMV) continue;
-    load_geom<T>(st, w.fg);
-    const int f = first_item(w.wrank, w.fg.rot, w.total_warps);
-    if (f < w.fg.items) {
-      w.fc.s = s;
-      w.fc.it = f;
-      w.fc.j = 0;
-      w.fc.nsub = item_tiles<T>(w.fg, f);
-      return;
-    }
-  }
-  w.fc.s = w.nstages;
-}
-
-// Issue the bulk copies of as many tiles as the ring has free slots for.
-template <typename T, int ND, bool BULK>
-__device__ __forceinline__ void top_up(WarpCtx<T, ND, BULK>& w) {
-  if (!BULK) return;
-  while (w.landed_seq < w.fetch_seq &&
-         mbar_test_wait(w.bars + (w.landed_seq % ND) * 8, (w.landed_seq / ND) & 1u))
-    ++w.landed_seq;
-  while (w.fc.s < w.nstages && (w.fetch_seq - w.cons_seq) < (unsigned)ND &&
-         (w.fetch_seq - w.landed_seq) < w.max_inflight) {
-    Tile t;
-    decode_tile<T>(w.fg, w.fc.it, w.fc.j, w.fc.nsub, t);
-    const int slot = w.fetch_seq % ND;
-    const uint32_t bar = w.bars + slot * 8;
-    const uint32_t dst = w.ring + slot * kSlotBytes;
-    const int nrows = min(kRowsPerTile, w.fg.P - t.p0);
-    const uint32_t row_bytes = (uint32_t)t.kc * (uint32_t)sizeof(T);
-    if (w.lane == 0) {
-      // The slot was last read through the generic proxy by this warp; order those reads
-      // before the async-proxy writes of the new copies.
-      fence_proxy_async_smem();
-      mbar_expect_tx(bar, row_bytes * nrows);
-    }
-    __syncwarp();
-    if (w.lane < nrows) {
-      const char* base = t.g ? w.fg.WB : w.fg.WA;
-      const size_t row = (size_t)phys_row(w.fg, t.p0) + w.lane;
-      const char* src = base + (row * (size_t)w.fg.ldw + (size_t)t.k0) * sizeof(T);
-      bulk_g2s(dst + w.lane * kRowBytes, src, row_bytes, bar);
-    }
-    ++w.fetch_seq;
-    // advance the fetch cursor
-    if (++w.fc.j == w.fc.nsub) {
-      w.fc.j = 0;
-      w.fc.it += w.total_warps;
-      if (w.fc.it < w.fg.items) {
-        w.fc.nsub = item_tiles<T>(w.fg, w.fc.it);
-      } else {
-        fetch_seek(w, w.fc.s + 1);
-      }
-    }
-  }
-}
-
-template <typename T, int ND, bool BULK>
-__device__ __forceinline__ void wait_slot(WarpCtx<T, ND, BULK>& w) {
-  if (!BULK) return;
-  const int slot = w.cons_seq % ND;
-  const uint32_t parity = (w.cons_seq / ND) & 1u;
-  const uint32_t bar = w.bars + slot * 8;
-  if (!mbar_try_wait(bar, parity)) {
-    const unsigned long long t0 = gtimer();
-    while (!mbar_try_wait(bar, parity)) {
-      if (gtimer() - t0 > kWaitLimitNs) {
-        if (w.lane == 0) atomicCAS(&w.sync->status, DS_OK, DS_COPY_TIMEOUT);
-        break;
-      }
-    }
-  }
-  if (w.landed_seq <= w.cons_seq) w.landed_seq = w.cons_seq + 1;
-}
-
-// Reduce acc[r] (r<4) over the warp.  Afterwards every lane holds the sum for row lane>>3.
-__device__ __forceinline__ float reduce_rows4(const float* a, int lane) {
-  const bool b4 = lane & 16, b3 = lane & 8;
-  float keep0 = b4 ? a[2] : a[0];
-  float keep1 = b4 ? a[3] : a[1];
-  const float send0 = b4 ? a[0] : a[2];
-  const float send1 = b4 ? a[1] : a[3];
-  keep0 += __shfl_xor_sync(0xffffffffu, send0, 16);
-  keep1 += __shfl_xor_sync(0xffffffffu, send1, 16);
-  float k = b3 ? keep1 : keep0;
-  const float s = b3 ? keep0 : keep1;
-  k += __shfl_xor_sync(0xffffffffu, s, 8);
-  k += __shfl_xor_sync(0xffffffffu, k, 4);
-  k += __shfl_xor_sync(0xffffffffu, k, 2);
-  k += __shfl_xor_sync(0xffffffffu, k, 1);
-  return k;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -346,13 +216,6 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // ----------------------------------------------------------------------------- GEMV stage
-__device__ __forceinline__ void st_tag(void* base, size_t i, float v, unsigned tag) {
-  uint2 w2;
-  w2.x = __float_as_uint(v);
-  w2.y = tag;
-  reinterpret_cast<uint2*>(base)[i] = w2;
-}
-
 // Operands of an item's epilogue that do not depend on the accumulators; fetched when the item
 // starts so that their latency hides behind the item's tiles.
 struct EpiAux {
@@ -368,8 +231,7 @@ __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiA
   switch (st.epi) {
     case EPI_RESID: {
       const size_t i = (size_t)b * st.P + p;
-      if (st.flags & SF_RESID_TAG) ax.a0 = __uint_as_float(__ldcg(reinterpret_cast<const uint2*>(st.resid) + i).x);
-      else if (st.flags & SF_RESID_T) ax.a0 = X::ld(st.resid, i);
+      if (st.flags & SF_RESID_T) ax.a0 = X::ldcg(st.resid, i);
       else ax.a0 = __ldcg(reinterpret_cast<const float*>(st.resid) + i);
     } break;
     case EPI_ROPE_Q:
@@ -390,27 +252,24 @@ __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiA
 
 template <typename T>
 __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int seg, float a,
-                                              float bsum, const EpiAux& ax, unsigned tag) {
+                                              float bsum, const EpiAux& ax) {
   using X = TT<T>;
   const int P = st.P;
   switch (st.epi) {
     case EPI_PARTIAL: {
       const size_t i = ((size_t)seg * st.B + b) * P + p;
-      if (st.flags & SF_OUT_TAG) st_tag(st.out, i, a, tag);
-      else reinterpret_cast<float*>(st.out)[i] = a;
+      reinterpret_cast<float*>(st.out)[i] = a;
     } break;
     case EPI_STORE: {
       const float v = X::rnd(a);
       const size_t i = (size_t)b * P + p;
       if (st.flags & SF_OUT_T) X::st(st.out, i, v);
-      else if (st.flags & SF_OUT_TAG) st_tag(st.out, i, v, tag);
       else reinterpret_cast<float*>(st.out)[i] = v;
     } break;
     case EPI_RESID: {
       const size_t i = (size_t)b * P + p;
       const float v = X::rnd(ax.a0 + X::rnd(a));
       if (st.flags & SF_OUT_T) X::st(st.out, i, v);
-      else if (st.flags & SF_OUT_TAG) st_tag(st.out, i, v, tag);
       else reinterpret_cast<float*>(st.out)[i] = v;
     } break;
     case EPI_SWIGLU: {
@@ -418,7 +277,7 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
       const float sg = X::rnd(g / (1.0f + expf(-g)));
       const float v = X::rnd(sg * u);
       const size_t i = (size_t)b * P + p;
-      if (st.flags & SF_OUT_TAG) st_tag(st.out, i, v, tag);
+      if (st.flags & SF_OUT_T) X::st(st.out, i, v);
       else reinterpret_cast<float*>(st.out)[i] = v;
     } break;
     case EPI_ROPE_Q:
@@ -453,115 +312,6 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
     } break;
     default:
       break;
-  }
-}
-
-template <typename T, int NB, int ND, bool BULK>
-__device__ __forceinline__ void run_gemv(WarpCtx<T, ND, BULK>& w, const Stage& st,
-                                         const char* xvec, int xstride, unsigned tag) {
-  using X = TT<T>;
-  constexpr int VEC = X::kVec;
-  GemvGeom g;
-  load_geom<T>(&st, g);
-  const int lane = w.lane;
-  const int B = st.B;
-
-  for (int it = first_item(w.wrank, g.rot, w.total_warps); it < g.items; it += w.total_warps) {
-    float acc[2][kRowsPerTile][NB];
-#pragma unroll
-    for (int gi = 0; gi < 2; ++gi)
-#pragma unroll
-      for (int r = 0; r < kRowsPerTile; ++r)
-#pragma unroll
-        for (int b = 0; b < NB; ++b) acc[gi][r][b] = 0.f;
-
-    const int nsub = item_tiles<T>(g, it);
-    Tile t;
-    EpiAux ax;
-    {
-      const int p = (it / g.segs) * kRowsPerTile + (lane >> 3);
-      const int b = lane & 7;
-      if (b < B && p < g.P) epi_prefetch<T>(st, p, b, ax);
-    }
-    for (int j = 0; j < nsub; ++j) {
-      top_up(w);
-      decode_tile<T>(g, it, j, nsub, t);
-      const int xoff = (t.g ? st.xB_off : st.xA_off) + t.k0;
-      const char* wbase;
-      size_t wstride;
-      if (BULK) {
-        wait_slot(w);
-        if (j == 0) trace_mark(w.trow, 6);
-        wbase = w.ring_ptr + (w.cons_seq % ND) * kSlotBytes;
-        wstride = kRowBytes;
-      } else {
-        const char* base = t.g ? g.WB : g.WA;
-        const int nrows_ok = min(kRowsPerTile, g.P - t.p0);
-        (void)nrows_ok;
-        wbase = base + ((size_t)phys_row(g, t.p0) * g.ldw + t.k0) * sizeof(T);
-        wstride = (size_t)g.ldw * sizeof(T);
-      }
-      const int nrows = min(kRowsPerTile, g.P - t.p0);
-      for (int c = lane * VEC; c < t.kc; c += 32 * VEC) {
-        float xs[NB][VEC];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          if (b < B) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(
-                xvec + ((size_t)b * xstride + xoff + c) * sizeof(T));
-            X::unpack(xv, xs[b]);
-          } else {
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) xs[b][e] = 0.f;
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < kRowsPerTile; ++r) {
-          uint4 wv;
-          if (BULK) {
-            wv = *reinterpret_cast<const uint4*>(wbase + r * wstride + (size_t)c * sizeof(T));
-          } else {
-            wv = (r < nrows) ? ld_nc_v4(wbase + r * wstride + (size_t)c * sizeof(T))
-                             : make_uint4(0, 0, 0, 0);
-          }
-          float wf[VEC];
-          X::unpack(wv, wf);
-          if (t.g == 0) {
-#pragma unroll
-            for (int b = 0; b < NB; ++b)
-#pragma unroll
-              for (int e = 0; e < VEC; ++e) acc[0][r][b] = fmaf(wf[e], xs[b][e], acc[0][r][b]);
-          } else {
-#pragma unroll
-            for (int b = 0; b < NB; ++b)
-#pragma unroll
-              for (int e = 0; e < VEC; ++e) acc[1][r][b] = fmaf(wf[e], xs[b][e], acc[1][r][b]);
-          }
-        }
-      }
-      if (BULK) {
-        __syncwarp();
-        ++w.cons_seq;
-      }
-    }
-    trace_mark(w.trow, 7);
-    // item epilogue: lane (r*8 + b) finishes logical row p0+r of batch row b
-    const bool hasB = g.WB != nullptr;
-    const int r_own = lane >> 3;
-    const int b_own = lane & 7;
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      float ta[kRowsPerTile], tb[kRowsPerTile];
-#pragma unroll
-      for (int r = 0; r < kRowsPerTile; ++r) {
-        ta[r] = acc[0][r][b];
-        tb[r] = acc[1][r][b];
-      }
-      const float sa = reduce_rows4(ta, lane);
-      const float sb = hasB ? reduce_rows4(tb, lane) : 0.f;
-      const int p = t.p0 + r_own;
-      if (b_own == b && b < B && p < g.P) gemv_epilogue<T>(st, p, b, t.seg, sa, sb, ax, tag);
-    }
   }
 }
 
@@ -623,39 +373,7 @@ template <>
 __device__ __forceinline__ void ld_row<float, 2>(const void* base, size_t i, float* o) {
   const float2 v = __ldcg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(base) + i));
   o[0] = v.x; o[1] = v.y;
-}
-
-// ----------------------------------------------------------------------------- vector stage-in
-// Bounded poll helper: returns true when the caller should give up.
-struct SpinGuard {
-  unsigned spins = 0;
-  unsigned long long t0 = 0;
-  __device__ __forceinline__ bool expired(SyncState* sync) {
-    if ((++spins & 255u) != 0) return false;
-    if (*reinterpret_cast<volatile int*>(&sync->status) != DS_OK) return true;
-    const unsigned long long now = gtimer();
-    if (t0 == 0) {
-      t0 = now;
-      return false;
-    }
-    if (now - t0 > kWaitLimitNs) {
-      atomicCAS(&sync->status, DS_OK, DS_TAG_TIMEOUT);
-      return true;
-    }
-    return false;
-  }
-};
-
-// Polling load of two (value, tag) words.  Volatile so that the compiler re-issues it on every
-// iteration of a spin loop; it is served by L2.
-__device__ __forceinline__ uint4 ldcg_u4(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
+}// ----------------------------------------------------------------------------- vector stage-in
 template <typename T>
 __device__ __forceinline__ void st2(char* xvec, size_t i, float a, float b);
 template <>
@@ -668,126 +386,91 @@ __device__ __forceinline__ void st2<__nv_bfloat16>(char* xvec, size_t i, float a
   *reinterpret_cast<__nv_bfloat162*>(xvec + i * 2) = v;
 }
 
+// 16 raw bytes of a T array (8 bf16 / 4 fp32) at element index i, served by L2.
+template <typename T>
+__device__ __forceinline__ uint4 ld_raw16(const void* base, size_t i) {
+  return __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(base) + i));
+}
+
 // Brings the stage's input vector into shared memory as T.  All global loads of a thread are
-// issued before the first use so that their L2 latencies overlap.  Tagged sources are polled
-// until every word carries the tag of the producing stage.
-template <typename T, int ND, bool BULK>
-__device__ __noinline__ void stage_vector(WarpCtx<T, ND, BULK>& w, const Stage& st, char* xvec,
-                                          int xstride, float* red, int tid, int nthreads,
-                                          unsigned tag_base) {
-  SyncState* sync = w.sync;
+// issued before the first use so that their L2 latencies overlap.  Sources of type T are copied
+// or normalised in 16-byte units; fp32 partial sums are added in segment order, then rounded.
+template <typename T>
+__device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xstride, float* red,
+                                          int tid, int nthreads, unsigned long long* trow) {
   using X = TT<T>;
+  constexpr int VEC = X::kVec;  // elements per 16 bytes of T
   const int len = st.vl_len, B = st.B;
   const bool inT = (st.flags & SF_IN_T) != 0;
-  const bool tagged = (st.flags & SF_IN_TAG) != 0;
-  const unsigned want = tag_base + (unsigned)st.vl_tag + 1u;
-  if (tagged && st.vl_mode == VL_SUM) {
-    const int upr = len >> 1;  // 2-element units (one 16-byte load) per row
-    const int units = B * upr;
-    const int nseg = st.vl_nseg;
-    const size_t segstride = (size_t)B * len * 8;  // bytes between partial sums
-    const char* src = reinterpret_cast<const char*>(st.vl_src);
-    if (nseg == 1) {
-      constexpr int U = 8;
-      for (int u0 = tid; u0 - (tid & 31) < units; u0 += nthreads * U) {  // warp-uniform trip count
-        uint4 wv[U];
-        SpinGuard sg;
-        bool ok;
-        do {
-          ok = true;
+  if (st.vl_mode == VL_SUM && inT) {
+    // T -> T copy (nseg is 1 for every T source)
+    constexpr int U = 4;
+    const int upr = len / VEC, units = B * upr;
+    for (int u0 = tid; u0 < units; u0 += nthreads * U) {
+      uint4 v[U];
 #pragma unroll
-          for (int q = 0; q < U; ++q) {
-            const int u = u0 + q * nthreads;
-            if (u < units) wv[q] = ldcg_u4(src + (size_t)u * 16);
-          }
-#pragma unroll
-          for (int q = 0; q < U; ++q) {
-            const int u = u0 + q * nthreads;
-            if (u < units) ok = ok && wv[q].y == want && wv[q].w == want;
-          }
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) top_up(w);
-        } while (!ok && !sg.expired(sync));
-#pragma unroll
-        for (int q = 0; q < U; ++q) {
-          const int u = u0 + q * nthreads;
-          if (u < units) {
-            const int b = u / upr, k = (u - b * upr) * 2;
-            st2<T>(xvec, (size_t)b * xstride + k, __uint_as_float(wv[q].x), __uint_as_float(wv[q].z));
-          }
-        }
+      for (int q = 0; q < U; ++q) {
+        const int u = u0 + q * nthreads;
+        if (u < units) v[q] = ld_raw16<T>(st.vl_src, (size_t)u * VEC);
       }
-    } else {
-      constexpr int SMAX = 8;  // kMaxSegs of the program builder
-      for (int u = tid; u - (tid & 31) < units; u += nthreads) {  // warp-uniform trip count
-        const bool act = u < units;
-        uint4 wv[SMAX];
-        SpinGuard sg;
-        bool ok;
-        do {
-          ok = true;
 #pragma unroll
-          for (int q = 0; q < SMAX; ++q)
-            if (act && q < nseg) wv[q] = ldcg_u4(src + q * segstride + (size_t)u * 16);
-#pragma unroll
-          for (int q = 0; q < SMAX; ++q)
-            if (act && q < nseg) ok = ok && wv[q].y == want && wv[q].w == want;
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) top_up(w);
-        } while (!ok && !sg.expired(sync));
-        if (act) {
-          float a0 = __uint_as_float(wv[0].x), a1 = __uint_as_float(wv[0].z);
-#pragma unroll
-          for (int q = 1; q < SMAX; ++q)
-            if (q < nseg) {
-              a0 += __uint_as_float(wv[q].x);
-              a1 += __uint_as_float(wv[q].z);
-            }
-          const int b = u / upr, k = (u - b * upr) * 2;
-          st2<T>(xvec, (size_t)b * xstride + k, a0, a1);
+      for (int q = 0; q < U; ++q) {
+        const int u = u0 + q * nthreads;
+        if (u < units) {
+          const int b = u / upr, k = (u - b * upr) * VEC;
+          *reinterpret_cast<uint4*>(xvec + ((size_t)b * xstride + k) * sizeof(T)) = v[q];
         }
       }
     }
-    return;
-  }
-  if (tagged && st.vl_mode == VL_RMSNORM) {
-    constexpr int U = 8;
-    const int upr = len >> 1;
+  } else if (st.vl_mode == VL_SUM) {
+    // fp32 partial sums [nseg][B][len]
+    constexpr int SMAX = 8;  // kMaxSegs of the program builder
+    const int nseg = st.vl_nseg;
+    const int upr = len >> 2, units = B * upr;
+    const size_t segstride = (size_t)B * len;
+    const float* src = reinterpret_cast<const float*>(st.vl_src);
+    for (int u = tid; u < units; u += nthreads) {
+      float4 v[SMAX];
+#pragma unroll
+      for (int q = 0; q < SMAX; ++q)
+        if (q < nseg) v[q] = ldcg_f4(src + q * segstride + (size_t)u * 4);
+      float4 a = v[0];
+#pragma unroll
+      for (int q = 1; q < SMAX; ++q)
+        if (q < nseg) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
+      const int b = u / upr, k = (u - b * upr) * 4;
+      st4<T>(xvec, (size_t)b * xstride + k, a);
+    }
+  } else if (st.vl_mode == VL_RMSNORM) {
+    // T source, weight of type T; a row longer than the register window is read twice
+    constexpr int U = 4;
     const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+    const int upr = len / VEC;
     const bool fits = upr <= nthreads * U;
-    const char* src = reinterpret_cast<const char*>(st.vl_src);
     for (int b = 0; b < B; ++b) {
-      const char* row = src + (size_t)b * len * 8;
-      uint4 wv[U];
+      uint4 v[U], wv[U];
       float ss = 0.f;
-      for (int u0 = tid; u0 - (tid & 31) < upr; u0 += nthreads * U) {  // warp-uniform trip count
-        SpinGuard sg;
-        bool ok;
-        do {
-          ok = true;
-#pragma unroll
-          for (int q = 0; q < U; ++q) {
-            const int u = u0 + q * nthreads;
-            if (u < upr) wv[q] = ldcg_u4(row + (size_t)u * 16);
-          }
-#pragma unroll
-          for (int q = 0; q < U; ++q) {
-            const int u = u0 + q * nthreads;
-            if (u < upr) ok = ok && wv[q].y == want && wv[q].w == want;
-          }
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) top_up(w);
-        } while (!ok && !sg.expired(sync));
+      for (int u0 = tid; u0 < upr; u0 += nthreads * U) {
 #pragma unroll
         for (int q = 0; q < U; ++q) {
           const int u = u0 + q * nthreads;
           if (u < upr) {
-            const float x0 = __uint_as_float(wv[q].x), x1 = __uint_as_float(wv[q].z);
-            ss += x0 * x0 + x1 * x1;
+            v[q] = ld_raw16<T>(st.vl_src, (size_t)b * len + (size_t)u * VEC);
+            wv[q] = ld_raw16<T>(st.vl_w, (size_t)u * VEC);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < U; ++q) {
+          const int u = u0 + q * nthreads;
+          if (u < upr) {
+            float f[VEC];
+            X::unpack(v[q], f);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) ss = fmaf(f[e], f[e], ss);
           }
         }
       }
-      trace_mark(w.trow, 4);
+      trace_mark(trow, 4);
       ss = warp_sum(ss);
       if (lane == 0) red[warp] = ss;
       __syncthreads();
@@ -795,130 +478,366 @@ __device__ __noinline__ void stage_vector(WarpCtx<T, ND, BULK>& w, const Stage& 
       for (int i = 0; i < nwarps; ++i) tot += red[i];
       const float inv = rsqrtf(tot / (float)len + st.eps);
       __syncthreads();
-      trace_mark(w.trow, 5);
-      auto finish = [&](int u, float x0, float x1) {
-        float w0, w1;
-        {
-          float tmp[2];
-          ld_row<T, 2>(st.vl_w, (size_t)u * 2, tmp);
-          w0 = tmp[0];
-          w1 = tmp[1];
-        }
-        st2<T>(xvec, (size_t)b * xstride + (size_t)u * 2, w0 * X::rnd(x0 * inv), w1 * X::rnd(x1 * inv));
+      trace_mark(trow, 5);
+      auto finish = [&](int u, const uint4& xr, const uint4& wr) {
+        float f[VEC], g[VEC];
+        X::unpack(xr, f);
+        X::unpack(wr, g);
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4)
+          st4<T>(xvec, (size_t)b * xstride + (size_t)u * VEC + e,
+                 make_float4(g[e] * X::rnd(f[e] * inv), g[e + 1] * X::rnd(f[e + 1] * inv),
+                             g[e + 2] * X::rnd(f[e + 2] * inv), g[e + 3] * X::rnd(f[e + 3] * inv)));
       };
       if (fits) {
 #pragma unroll
         for (int q = 0; q < U; ++q) {
           const int u = tid + q * nthreads;
-          if (u < upr) finish(u, __uint_as_float(wv[q].x), __uint_as_float(wv[q].z));
-        }
-      } else {
-        for (int u = tid; u < upr; u += nthreads) {
-          const uint4 t = ldcg_u4(row + (size_t)u * 16);
-          finish(u, __uint_as_float(t.x), __uint_as_float(t.z));
-        }
-      }
-    }
-    return;
-  }
-  const int upr = len >> 2;          // 4-element units per batch row
-  const int units = B * upr;
-  if (st.vl_mode == VL_SUM) {
-    const int nseg = st.vl_nseg;
-    const size_t segstride = (size_t)B * len;
-    if (nseg == 1) {
-      constexpr int U = 8;
-      for (int u0 = tid; u0 < units; u0 += nthreads * U) {
-        float4 v[U];
-#pragma unroll
-        for (int q = 0; q < U; ++q) {
-          const int u = u0 + q * nthreads;
-          if (u < units) v[q] = ld4<T>(st.vl_src, (size_t)u * 4, inT);
-        }
-#pragma unroll
-        for (int q = 0; q < U; ++q) {
-          const int u = u0 + q * nthreads;
-          if (u < units) {
-            const int b = u / upr, k = (u - b * upr) * 4;
-            st4<T>(xvec, (size_t)b * xstride + k, v[q]);
-          }
-        }
-      }
-    } else {
-      constexpr int SMAX = 8;  // kMaxSegs of the program builder
-      for (int u = tid; u < units; u += nthreads) {
-        float4 v[SMAX];
-#pragma unroll
-        for (int sgi = 0; sgi < SMAX; ++sgi)
-          if (sgi < nseg) v[sgi] = ld4<T>(st.vl_src, sgi * segstride + (size_t)u * 4, inT);
-        float4 a = v[0];
-#pragma unroll
-        for (int sgi = 1; sgi < SMAX; ++sgi)
-          if (sgi < nseg) { a.x += v[sgi].x; a.y += v[sgi].y; a.z += v[sgi].z; a.w += v[sgi].w; }
-        const int b = u / upr, k = (u - b * upr) * 4;
-        st4<T>(xvec, (size_t)b * xstride + k, a);
-      }
-    }
-  } else if (st.vl_mode == VL_RMSNORM) {
-    constexpr int U = 8;  // register-resident units per thread; longer rows are re-read
-    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
-    const bool fits = upr <= nthreads * U;
-    for (int b = 0; b < B; ++b) {
-      float4 v[U];
-      float ss = 0.f;
-      if (fits) {
-#pragma unroll
-        for (int q = 0; q < U; ++q) {
-          const int u = tid + q * nthreads;
-          if (u < upr) v[q] = ld4<T>(st.vl_src, (size_t)b * len + (size_t)u * 4, inT);
-        }
-#pragma unroll
-        for (int q = 0; q < U; ++q) {
-          const int u = tid + q * nthreads;
-          if (u < upr) ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
-        }
-      } else {
-        for (int u = tid; u < upr; u += nthreads) {
-          const float4 t = ld4<T>(st.vl_src, (size_t)b * len + (size_t)u * 4, inT);
-          ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
-        }
-      }
-      trace_mark(w.trow, 4);
-      ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
-      __syncthreads();
-      float tot = 0.f;
-      for (int i = 0; i < nwarps; ++i) tot += red[i];
-      const float inv = rsqrtf(tot / (float)len + st.eps);
-      __syncthreads();
-      trace_mark(w.trow, 5);
-      auto finish = [&](int u, float4 t) {
-        const float4 wv = ld4<T>(st.vl_w, (size_t)u * 4, true);
-        t.x = wv.x * X::rnd(t.x * inv);
-        t.y = wv.y * X::rnd(t.y * inv);
-        t.z = wv.z * X::rnd(t.z * inv);
-        t.w = wv.w * X::rnd(t.w * inv);
-        st4<T>(xvec, (size_t)b * xstride + (size_t)u * 4, t);
-      };
-      if (fits) {
-#pragma unroll
-        for (int q = 0; q < U; ++q) {
-          const int u = tid + q * nthreads;
-          if (u < upr) finish(u, v[q]);
+          if (u < upr) finish(u, v[q], wv[q]);
         }
       } else {
         for (int u = tid; u < upr; u += nthreads)
-          finish(u, ld4<T>(st.vl_src, (size_t)b * len + (size_t)u * 4, inT));
+          finish(u, ld_raw16<T>(st.vl_src, (size_t)b * len + (size_t)u * VEC),
+                 ld_raw16<T>(st.vl_w, (size_t)u * VEC));
       }
     }
+  }
+}// ----------------------------------------------------------------------------- GEMV engine
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// The same load under a predicate; the registers are zero when it is off.  Written as one asm
+// block: `pred ? load : 0` in C++ becomes a select on the loaded value, and the select makes the
+// warp wait for the load, which serialises all loads in flight (measured ~800 cycles per load).
+__device__ __forceinline__ uint4 ldg_stream_if(const void* p, bool pred) {
+  uint4 v;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.u32 q, %5, 0;\n\t"
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+      : "=&r"(v.x), "=&r"(v.y), "=&r"(v.z), "=&r"(v.w)
+      : "l"(p), "r"((unsigned)pred));
+  return v;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// One unit of a GEMV stage as this CTA sees it: 8 logical rows x one K segment.
+struct UnitInfo {
+  unsigned long long row_off;  // byte offset of the unit's first factor row
+  int p0, seg, kbeg, kend;
+  int nblk;                    // blocks (one 16-byte load per lane each) in [kbeg, kend)
+  int pad;
+};
+constexpr int kMaxUnitsPerCta = 64;
+
+// L2 prefetch of the whole factor matrices of stage `st`, spread over every thread of the grid.
+template <typename T>
+__device__ __forceinline__ void prefetch_stage(const Stage& st, size_t gtid, size_t gthreads) {
+  if (st.type != ST_GEMV) return;
+  const size_t pitch = (size_t)st.ldw * sizeof(T);
+  if (st.rope_half > 0) {
+    // both rotary halves live in one matrix of 2*P rows starting at WA
+    const size_t lines = ((size_t)2 * st.P * pitch + 127) >> 7;
+    for (size_t l = gtid; l < lines; l += gthreads) prefetch_l2(reinterpret_cast<const char*>(st.WA) + (l << 7));
+  } else {
+    const size_t lines = ((size_t)st.P * pitch + 127) >> 7;
+    for (size_t l = gtid; l < lines; l += gthreads) {
+      prefetch_l2(reinterpret_cast<const char*>(st.WA) + (l << 7));
+      if (st.WB) prefetch_l2(reinterpret_cast<const char*>(st.WB) + (l << 7));
+    }
+  }
+}
+
+// Grid barrier wait (one polling lane per CTA) in front of a stage with SF_BARRIER.
+__device__ __forceinline__ void barrier_wait(SyncState* sync, unsigned long long target, int s, int tid) {
+  if (tid == 0) {
+    if (ld_acquire_u64(&sync->arrivals) < target) {
+      const long long c0 = clock64();
+      unsigned spins = 0;
+      while (ld_acquire_u64(&sync->arrivals) < target) {
+        if ((++spins & 63u) == 0) {
+          if (*reinterpret_cast<volatile int*>(&sync->status) != DS_OK) break;
+          if (clock64() - c0 > kWaitLimitClk) {
+            atomicCAS(&sync->status, DS_OK, DS_BARRIER_TIMEOUT);
+            sync->status_detail = s;
+            break;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// Per-stage context handed to the stage functions.
+struct StageCtx {
+  const Stage* prog;
+  int s, nstages;
+  SyncState* sync;
+  unsigned long long bar_target;   // arrival count that opens this stage's barrier
+  char* xvec;
+  int xstride;
+  float* red;
+  float* part;                     // partial sums: [unit ordinal][operand][k slice][batch 8][row 8]
+  UnitInfo* units;                 // this CTA's units of the stage
+  unsigned long long* trow;
+};
+
+// Walks the blocks of one warp: unit ordinal i (stepping by the number of unit slots), operand
+// group g, block j of the warp's K slice.  `p` is the lane's load address, `kcol` the first
+// column of the lane's 16 bytes.
+struct BlockCursor {
+  int i, g, j, jend;
+  int kcol, kend;
+  const char* p;
+};
+
+template <typename T>
+struct WarpGeo {
+  const char* W[2];
+  size_t pitch;
+  int nops, nu, P;
+  int ks, kslice, slot, nslots;   // warps per unit, this warp's slice and unit slot
+  int qg, qt;
+};
+
+template <typename T>
+__device__ __forceinline__ void cursor_seek(const WarpGeo<T>& wg, const UnitInfo* units, BlockCursor& c) {
+  constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
+  while (c.i < wg.nu) {
+    const UnitInfo u = units[c.i];
+    const int bps = (u.nblk + wg.ks - 1) / wg.ks;
+    const int j0 = wg.kslice * bps, j1 = min(u.nblk, j0 + bps);
+    if (j0 < j1) {
+      // a row past the end of the matrix is replaced by the unit's first row; its sums land in
+      // accumulator columns that are never stored
+      const int r = (u.p0 + wg.qg < wg.P) ? wg.qg : 0;
+      c.j = j0;
+      c.jend = j1;
+      c.kend = u.kend;
+      c.kcol = u.kbeg + j0 * CB + wg.qt * VEC;
+      c.p = wg.W[c.g] + u.row_off + (size_t)r * wg.pitch + (size_t)c.kcol * sizeof(T);
+      return;
+    }
+    c.i += wg.nslots;
+    c.g = 0;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void cursor_next(const WarpGeo<T>& wg, const UnitInfo* units, BlockCursor& c) {
+  constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
+  ++c.j;
+  c.kcol += CB;
+  c.p += 64;
+  if (c.j >= c.jend) {
+    if (++c.g >= wg.nops) {
+      c.g = 0;
+      c.i += wg.nslots;
+    }
+    cursor_seek<T>(wg, units, c);
+  }
+}
+
+// One GEMV stage, all warps of the CTA.
+template <typename T, int NW, int D>
+__device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
+  using X = TT<T>;
+  constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nthreads = NW * 32;
+  const int B = st.B;
+  const int grid = gridDim.x;
+
+  const long long k0 = clock64();
+  // ---- 0. this CTA's units of the stage, computed once into shared memory
+  const int total_units = ((st.P + kTileRows - 1) / kTileRows) * st.segs;
+  const int first = first_item(blockIdx.x, st.rot % grid, grid);
+  const int nu = first < total_units ? min(kMaxUnitsPerCta, (total_units - first + grid - 1) / grid) : 0;
+  if (tid < nu) {
+    const int uidx = first + tid * grid;
+    UnitInfo u;
+    const int grp = uidx / st.segs;
+    u.seg = uidx - grp * st.segs;
+    u.p0 = grp * kTileRows;
+    u.kbeg = u.seg * st.kseg;
+    u.kend = min(st.K, u.kbeg + st.kseg);
+    u.nblk = (u.kend - u.kbeg + CB - 1) / CB;
+    u.row_off = (unsigned long long)phys_row(st.rope_half, u.p0) * st.ldw * sizeof(T);
+    u.pad = 0;
+    cx.units[tid] = u;
+  }
+  __syncthreads();
+
+  const long long k1 = clock64();
+  WarpGeo<T> wg;
+  wg.W[0] = reinterpret_cast<const char*>(st.WA);
+  wg.W[1] = reinterpret_cast<const char*>(st.WB);
+  wg.pitch = (size_t)st.ldw * sizeof(T);
+  wg.nops = st.WB ? 2 : 1;
+  wg.nu = nu;
+  wg.P = st.P;
+  wg.ks = st.ksplit > 0 ? st.ksplit : NW;
+  wg.kslice = warp % wg.ks;
+  wg.slot = warp / wg.ks;
+  wg.nslots = NW / wg.ks;
+  wg.qg = lane >> 2;
+  wg.qt = lane & 3;
+
+  // ---- 1. first D loads of this warp, before any waiting
+  BlockCursor fc;
+  fc.i = wg.slot;
+  fc.g = 0;
+  cursor_seek<T>(wg, cx.units, fc);
+  uint4 buf[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) {
+    const bool live = fc.i < nu;
+    buf[i] = ldg_stream_if(fc.p, live && fc.kcol < fc.kend);
+    if (live) cursor_next<T>(wg, cx.units, fc);
+  }
+  const long long k2 = clock64();
+  // ---- 2. L2 prefetch of the stages the host assigned to this one
+  for (int t = st.pf_begin; t < st.pf_end; ++t)
+    prefetch_stage<T>(cx.prog[t], (size_t)blockIdx.x * nthreads + tid, (size_t)grid * nthreads);
+
+  const long long k3 = clock64();
+  // ---- 3. wait for the producers of the input vector, stage it
+  if (st.flags & SF_BARRIER) barrier_wait(cx.sync, cx.bar_target, cx.s, tid);
+  trace_mark(cx.trow, 1);
+  if (st.vl_mode != VL_NONE) {
+    stage_vector<T>(st, cx.xvec, cx.xstride, cx.red, tid, nthreads, cx.trow);
+    __syncthreads();
+  }
+  trace_mark(cx.trow, 2);
+
+  const long long k4 = clock64();
+  int nblocks = 0;
+  // ---- 4. stream this warp's blocks
+  BlockCursor cc;
+  cc.i = wg.slot;
+  cc.g = 0;
+  cursor_seek<T>(wg, cx.units, cc);
+  const bool xact = wg.qg < B;
+  const unsigned char* xlane = reinterpret_cast<const unsigned char*>(cx.xvec) +
+                               (size_t)(xact ? wg.qg : 0) * cx.xstride * sizeof(T);
+  float acc[2][4];
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+
+  while (cc.i < nu) {
+#pragma unroll
+    for (int i = 0; i < D; ++i) {
+      if (cc.i < nu) {
+        const uint4 wv = buf[i];
+        ++nblocks;
+        // refill the slot with the block D ahead
+        {
+          const bool live = fc.i < nu;
+          buf[i] = ldg_stream_if(fc.p, live && fc.kcol < fc.kend);
+          if (live) cursor_next<T>(wg, cx.units, fc);
+        }
+        const bool ok = cc.kcol < cc.kend;
+        const int xcol = (cc.g ? st.xB_off : st.xA_off) + (ok ? cc.kcol : 0);
+        if constexpr (sizeof(T) == 2) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xlane + (size_t)xcol * sizeof(T));
+          mma_bf16_16816(acc[0], xv.x, 0u, xv.y, 0u, wv.x, wv.y);
+          mma_bf16_16816(acc[1], xv.z, 0u, xv.w, 0u, wv.z, wv.w);
+        } else {
+          // fp32: 4 columns of factor row qg times activation rows 0..3; acc[0][b] per batch row
+          float wf[4], xf[4];
+          X::unpack(wv, wf);
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            if (b < B) {
+              const uint4 xb = *reinterpret_cast<const uint4*>(
+                  reinterpret_cast<const unsigned char*>(cx.xvec) + ((size_t)b * cx.xstride + xcol) * sizeof(T));
+              X::unpack(xb, xf);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) acc[0][b] = fmaf(wf[e], xf[e], acc[0][b]);
+            }
+          }
+        }
+        // last block of this warp's slice of (unit, operand): publish the partial sums
+        const int ci = cc.i, cg = cc.g;
+        cursor_next<T>(wg, cx.units, cc);
+        if (cc.i != ci || cc.g != cg) {
+          float* dst = cx.part + ((size_t)(ci * wg.nops + cg) * wg.ks + wg.kslice) * 64;
+          if constexpr (sizeof(T) == 2) {
+            // lane (qg, qt): batch row qg, factor rows 2qt, 2qt+1
+            if (xact) {
+              dst[wg.qg * 8 + 2 * wg.qt] = acc[0][0] + acc[1][0];
+              dst[wg.qg * 8 + 2 * wg.qt + 1] = acc[0][1] + acc[1][1];
+            }
+          } else {
+            // quad reduction: lanes (qg, 0..3) hold 4 columns each of factor row qg
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              float v = acc[0][b];
+              v += __shfl_xor_sync(0xffffffffu, v, 1);
+              v += __shfl_xor_sync(0xffffffffu, v, 2);
+              if (wg.qt == b && b < B) dst[b * 8 + wg.qg] = v;
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+        }
+      }
+    }
+  }
+  trace_mark(cx.trow, 7);
+  const long long k5 = clock64();
+  __syncthreads();
+  const long long k6 = clock64();
+
+  // ---- 5. add the slices' partial sums in slice order and run the epilogue
+  const int nout = nu * kTileRows * B;
+  for (int o = tid; o < nout; o += nthreads) {
+    const int i = o / (kTileRows * B);
+    const int rem = o - i * (kTileRows * B);
+    const int b = rem / kTileRows, r = rem - b * kTileRows;
+    const UnitInfo u = cx.units[i];
+    const int p = u.p0 + r;
+    if (p >= st.P) continue;
+    EpiAux ax;
+    epi_prefetch<T>(st, p, b, ax);
+    const int bps = (u.nblk + wg.ks - 1) / wg.ks;
+    const int nsl = (u.nblk + bps - 1) / bps;   // slices that own blocks of this unit
+    float sum[2] = {0.f, 0.f};
+    for (int g = 0; g < wg.nops; ++g) {
+      const float* src = cx.part + ((size_t)(i * wg.nops + g) * wg.ks) * 64 + b * 8 + r;
+      float a = 0.f;
+      for (int w2 = 0; w2 < nsl; ++w2) a += src[w2 * 64];
+      sum[g] = a;
+    }
+    gemv_epilogue<T>(st, p, b, u.seg, sum[0], sum[1], ax);
+  }
+  if (cx.trow) {
+    cx.trow[8] = k1 - k0;
+    cx.trow[9] = k2 - k1;
+    cx.trow[10] = k3 - k2;
+    cx.trow[11] = k4 - k3;
+    cx.trow[12] = k5 - k4;
+    cx.trow[13] = k6 - k5;
+    cx.trow[14] = clock64() - k6;
+    cx.trow[15] = nblocks;
   }
 }
 
 // ----------------------------------------------------------------------------- attention stage
 // One item = (batch row, kv head, key split).  Lane l owns dims [l*DPL, (l+1)*DPL) of the head.
 template <typename T, int G, int DPL>
-__device__ __noinline__ void attn_items(const Stage& st, int wrank, int total_warps, int lane,
-                                        unsigned tag) {
+__device__ __noinline__ void attn_items(const Stage& st, int wrank, int total_warps, int lane) {
   using X = TT<T>;
   constexpr int UNR = (G * DPL >= 16) ? 4 : 8;  // keys in flight per warp, bounded by registers
   const int Dh = st.Dh, Hk = st.Hk, H = st.H, nsplit = st.nsplit, B = st.B;
@@ -1041,7 +960,6 @@ __device__ __noinline__ void attn_items(const Stage& st, int wrank, int total_wa
         for (int d = 0; d < DPL; ++d) {
           const float v = X::rnd(o[d] * invL);
           if (st.flags & SF_OUT_T) X::st(st.out, oi + d, v);
-          else if (st.flags & SF_OUT_TAG) st_tag(st.out, oi + d, v, tag);
           else reinterpret_cast<float*>(st.out)[oi + d] = v;
         }
       }
@@ -1051,12 +969,11 @@ __device__ __noinline__ void attn_items(const Stage& st, int wrank, int total_wa
 }
 
 template <typename T>
-__device__ __forceinline__ void run_attn(const Stage& st, int wrank, int total_warps, int lane,
-                                         unsigned tag) {
+__device__ __forceinline__ void run_attn(const Stage& st, int wrank, int total_warps, int lane) {
   const int G = st.H / st.Hk;
   const int dpl = st.Dh / 32;
 #define FSVD_ATTN_CASE(GG, DD) \
-  if (G == GG && dpl == DD) { attn_items<T, GG, DD>(st, wrank, total_warps, lane, tag); return; }
+  if (G == GG && dpl == DD) { attn_items<T, GG, DD>(st, wrank, total_warps, lane); return; }
   FSVD_ATTN_CASE(1, 4)
   FSVD_ATTN_CASE(2, 4)
   FSVD_ATTN_CASE(4, 4)
@@ -1066,11 +983,9 @@ __device__ __forceinline__ void run_attn(const Stage& st, int wrank, int total_w
   FSVD_ATTN_CASE(4, 2)
   FSVD_ATTN_CASE(8, 2)
 #undef FSVD_ATTN_CASE
-}
-
-// ----------------------------------------------------------------------------- small stages
+}// ----------------------------------------------------------------------------- small stages
 template <typename T>
-__device__ __noinline__ void run_embed(const Stage& st, int gtid, int gthreads, unsigned tag) {
+__device__ __noinline__ void run_embed(const Stage& st, int gtid, int gthreads) {
   using X = TT<T>;
   const int d = st.P, B = st.B;
   for (int i = gtid; i < B * d; i += gthreads) {
@@ -1078,7 +993,7 @@ __device__ __noinline__ void run_embed(const Stage& st, int gtid, int gthreads, 
     int tok = st.tokens[b];
     tok = min(max(tok, 0), st.vocab - 1);
     const float v = X::ld(st.WA, (size_t)tok * d + k);
-    if (st.flags & SF_OUT_TAG) st_tag(st.out, i, v, tag);
+    if (st.flags & SF_OUT_T) X::st(st.out, i, v);
     else reinterpret_cast<float*>(st.out)[i] = v;
   }
 }
@@ -1137,36 +1052,34 @@ static __device__ __noinline__ void run_argmax(const Stage& st, float* redv, int
     __syncthreads();
   }
   if (tid == 0) *st.step_counter = step + 1;
-}
-
-// ----------------------------------------------------------------------------- the kernel
+}// ----------------------------------------------------------------------------- the kernel
 // Dynamic shared memory layout:
-//   [0, NW*ND*8)                mbarriers
-//   [.., +2*sizeof(Stage))      current and next stage descriptor
-//   [.., +512)                  reduction scratch
+//   [0, 2*sizeof(Stage))        current and next stage descriptor
+//   [.., +512)                  reduction scratch and the CTA's barrier arrival count
 //   [.., +kSmallProgBytes)      copy of a by-value program (per-op launches)
-//   [.., +NW*ND*kSlotBytes)     rings (1024-byte aligned)
+//   [.., +kMaxUnitsPerCta*32)   this CTA's units of the running stage
+//   [.., +part_bytes)           partial sums of the warps (sized by the host for the program)
 //   [.., +vec_bytes)            staged input vector, B rows of xstride elements
-// Stage timeline (optional): trace[(s*grid + cta)*8 + k] = globaltimer at: 0 stage entry, 1 after
-// the grid barrier, 2 vector staged, 3 body done (thread 0's warp), 4 vector words arrived,
-// 5 norm reduced, 6 first tile of thread 0's warp landed, 7 last tile consumed.
-template <typename T, int NB, int NW, int ND, bool BULK>
+// Stage timeline (optional): trace[(s*grid + cta)*16 + k] = globaltimer at: 0 stage entry,
+// 1 grid barrier passed, 2 vector staged, 3 stage done, 4 vector words arrived, 5 norm reduced,
+// 7 blocks streamed.
+template <typename T, int NW, int D>
 __global__ void __launch_bounds__(NW * 32, 1)
 fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant__ SmallProgram small,
-                   int use_small, int nstages, SyncState* sync, int xstride,
-                   unsigned long long* trace, int max_inflight) {
+                   int use_small, int nstages, SyncState* sync, int xstride, int part_bytes,
+                   unsigned long long* trace) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nthreads = NW * 32;
 
-  constexpr int kBarBytes = ((NW * ND * 8 + 15) / 16) * 16;
-  constexpr int kHdr = smem_header_bytes(NW, ND);
-  unsigned char* cur_base = smem + kBarBytes;
-  float* red = reinterpret_cast<float*>(smem + kBarBytes + 2 * kStageBytesAl);
-  int* flags_sh = reinterpret_cast<int*>(smem + kBarBytes + 2 * kStageBytesAl + 256);
-  Stage* small_sh = reinterpret_cast<Stage*>(smem + kBarBytes + 2 * kStageBytesAl + 512);
-  unsigned char* rings = smem + kHdr;
-  char* xvec = reinterpret_cast<char*>(rings + (BULK ? (size_t)NW * ND * kSlotBytes : 0));
+  unsigned char* cur_base = smem;
+  float* red = reinterpret_cast<float*>(smem + 2 * kStageBytesAl);
+  int* flags_sh = reinterpret_cast<int*>(smem + 2 * kStageBytesAl + 256);
+  Stage* small_sh = reinterpret_cast<Stage*>(smem + 2 * kStageBytesAl + 512);
+  UnitInfo* units = reinterpret_cast<UnitInfo*>(smem + 2 * kStageBytesAl + 512 + kSmallProgBytes);
+  static_assert(sizeof(UnitInfo) == 32, "unit table entry size");
+  float* part = reinterpret_cast<float*>(smem + smem_header_bytes());
+  char* xvec = reinterpret_cast<char*>(smem + smem_header_bytes() + part_bytes);
 
   const Stage* prog = prog_global;
   if (use_small) {
@@ -1178,96 +1091,74 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
     prog = small_sh;
     __syncthreads();
   }
-
-  WarpCtx<T, ND, BULK> w;
-  w.prog = prog;
-  w.nstages = nstages;
-  w.lane = lane;
-  w.total_warps = gridDim.x * NW;
-  w.wrank = warp * gridDim.x + blockIdx.x;
-  w.ring = smem_u32(rings + (size_t)warp * ND * kSlotBytes);
-  w.ring_ptr = reinterpret_cast<const char*>(rings + (size_t)warp * ND * kSlotBytes);
-  w.bars = smem_u32(smem + warp * ND * 8);
-  w.fetch_seq = 0;
-  w.cons_seq = 0;
-  w.landed_seq = 0;
-  w.max_inflight = max_inflight > 0 ? (unsigned)max_inflight : (unsigned)ND;
-  w.sync = sync;
-  w.trow = nullptr;
-
-  if (BULK) {
-    if (lane == 0) {
-      for (int i = 0; i < ND; ++i) mbar_init(w.bars + i * 8, 1);
-      fence_mbar_init();
-      fence_proxy_async_smem();
-    }
-    __syncwarp();
-  }
-  fetch_seek(w, 0);
-  top_up(w);
+  const int wrank = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * NW;
 
   const unsigned long long bar_base = __ldcg(&sync->bar_base);
-  const unsigned epoch = __ldcg(&sync->epoch);
-  const unsigned tag_base = epoch * kTagStride;
   unsigned nbar = 0;
   constexpr int kStageWords = (int)(sizeof(Stage) / 4);
-
-  // descriptor of stage 0
+  // flags_sh[0]: warps of this CTA that have arrived at the pending grid barrier
+  if (tid == 0) flags_sh[0] = 0;
   if (tid < kStageWords)
     reinterpret_cast<int*>(cur_base)[tid] = reinterpret_cast<const int*>(prog)[tid];
 
   for (int s = 0; s < nstages; ++s) {
-    __syncthreads();  // everybody is done with the previous stage's vector; descriptor s landed
+    __syncthreads();  // everybody is done with the previous stage's buffers; descriptor s landed
     const Stage& st = *reinterpret_cast<const Stage*>(cur_base + (s & 1) * kStageBytesAl);
-    if (trace && tid == 0) trace[((size_t)s * gridDim.x + blockIdx.x) * 8 + 0] = gtimer();
-    w.trow = (trace && tid == 0) ? trace + ((size_t)s * gridDim.x + blockIdx.x) * 8 : nullptr;
+    unsigned long long* trow =
+        (trace && tid == 0) ? trace + ((size_t)s * gridDim.x + blockIdx.x) * 16 : nullptr;
+    trace_mark(trow, 0);
     // the last warp fetches the next descriptor while the others go on
     if (warp == NW - 1 && s + 1 < nstages) {
       int* dst = reinterpret_cast<int*>(cur_base + ((s + 1) & 1) * kStageBytesAl);
       const int* src = reinterpret_cast<const int*>(prog + s + 1);
       for (int i = lane; i < kStageWords; i += 32) dst[i] = src[i];
     }
-    if (st.flags & SF_BARRIER) {
-      // Arrive once per CTA (the __syncthreads above ordered every warp's stores before it),
-      // then every warp polls for itself and keeps its prefetch going meanwhile.
-      if (tid == 0) {
-        __threadfence();
-        atomicAdd(&sync->arrivals, 1ull);
-      }
-      const unsigned long long target = (bar_base + nbar + 1ull) * gridDim.x;
-      SpinGuard sg;
-      bool ok;
-      do {
-        unsigned long long seen = 0;
-        if (lane == 0) seen = ld_acquire_u64(&sync->arrivals);
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        ok = seen >= target;
-        if (!ok) top_up(w);
-      } while (!ok && !sg.expired(sync));
-      if (!ok && tid == 0) sync->status_detail = s;
-      __threadfence();
-      ++nbar;
-    }
-    if (trace && tid == 0) trace[((size_t)s * gridDim.x + blockIdx.x) * 8 + 1] = gtimer();
+    const unsigned long long target = (bar_base + nbar + 1ull) * gridDim.x;
+    if (st.flags & SF_BARRIER) ++nbar;
     if (st.type == ST_GEMV) {
-      if (st.vl_mode != VL_NONE) {
-        stage_vector<T, ND, BULK>(w, st, xvec, xstride, red, tid, nthreads, tag_base);
-        __syncthreads();
+      StageCtx cx;
+      cx.prog = prog;
+      cx.s = s;
+      cx.nstages = nstages;
+      cx.sync = sync;
+      cx.bar_target = target;
+      cx.xvec = xvec;
+      cx.xstride = xstride;
+      cx.red = red;
+      cx.part = part;
+      cx.units = units;
+      cx.trow = trow;
+      gemv_stage<T, NW, D>(st, cx);
+    } else {
+      if (st.flags & SF_BARRIER) barrier_wait(sync, target, s, tid);
+      trace_mark(trow, 1);
+      if (st.type == ST_ATTN) {
+        run_attn<T>(st, wrank, total_warps, lane);
+      } else if (st.type == ST_EMBED) {
+        run_embed<T>(st, blockIdx.x * nthreads + tid, gridDim.x * nthreads);
+      } else if (st.type == ST_ARGMAX) {
+        if (blockIdx.x == 0) run_argmax(st, red, flags_sh + 8, tid, nthreads);
       }
-      if (trace && tid == 0) trace[((size_t)s * gridDim.x + blockIdx.x) * 8 + 2] = gtimer();
-      run_gemv<T, NB, ND, BULK>(w, st, xvec, xstride, tag_base + (unsigned)s + 1u);
-    } else if (st.type == ST_ATTN) {
-      run_attn<T>(st, w.wrank, w.total_warps, lane, tag_base + (unsigned)s + 1u);
-    } else if (st.type == ST_EMBED) {
-      run_embed<T>(st, blockIdx.x * nthreads + tid, gridDim.x * nthreads, tag_base + (unsigned)s + 1u);
-    } else if (st.type == ST_ARGMAX) {
-      if (blockIdx.x == 0) run_argmax(st, red, flags_sh, tid, nthreads);
     }
-    top_up(w);
-    if (trace && tid == 0) trace[((size_t)s * gridDim.x + blockIdx.x) * 8 + 3] = gtimer();
+    if (st.flags & SF_ARRIVE) {
+      // Grid-barrier arrival, warp by warp: each warp publishes its own stores and counts itself
+      // in shared memory; the last warp of the CTA adds the CTA to the global count.
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        unsigned old;
+        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
+                     : "=r"(old) : "r"(smem_u32(flags_sh)) : "memory");
+        if (old == (unsigned)NW - 1u) {
+          flags_sh[0] = 0;
+          asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
+        }
+      }
+    }
+    trace_mark(trow, 3);
   }
-  // The last CTA to finish publishes the barrier count and the next tag epoch; every CTA has
-  // read both words before it can get here.
+  // The last CTA to finish publishes the barrier count for the next launch; every CTA has read
+  // it before it can get here.
   __syncthreads();
   if (tid == 0) {
     __threadfence();
@@ -1275,7 +1166,6 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
     if (done == gridDim.x - 1) {
       sync->done_ctas = 0;
       sync->bar_base = bar_base + nbar;
-      sync->epoch = epoch + 1u;
     }
   }
 }

@@ -42,21 +42,12 @@ enum VecLoad : int {
 };
 
 enum StageFlags : int {
-  SF_BARRIER = 1,    // grid-wide barrier before this stage
+  SF_BARRIER = 1,    // grid-wide barrier before this stage: waits for every warp's SF_ARRIVE
   SF_IN_T = 2,       // vl_src (or q for ST_ATTN) holds T instead of fp32
   SF_OUT_T = 4,      // out holds T instead of fp32
   SF_RESID_T = 8,    // resid holds T instead of fp32
-  SF_IN_TAG = 16,    // vl_src holds (fp32, tag) pairs written by stage vl_tag of this launch
-  SF_OUT_TAG = 32,   // out receives (fp32, tag) pairs
-  SF_RESID_TAG = 64, // resid holds (fp32, tag) pairs (the tag is not checked)
+  SF_ARRIVE = 16,    // arrive at the grid barrier after this stage (the next one has SF_BARRIER)
 };
-
-// Tagged vectors: a value that another CTA consumes in the same launch is stored as one aligned
-// 8-byte word {fp32 bits, tag}, tag = launch epoch * kTagStride + producing stage + 1.  The
-// consumer polls the words themselves until every tag matches, so a dependent stage starts one
-// store and one load after its last producer, without a separate grid barrier; 8-byte accesses
-// are single-copy atomic, so a matching tag implies the value beside it.
-constexpr unsigned kTagStride = 2048;  // > number of stages of any program
 
 // `rnd` above rounds to the storage type T (bf16) and is the identity when T is fp32: these
 // are the points at which the PyTorch low-rank path materialises a tensor in the model dtype.
@@ -73,8 +64,9 @@ struct alignas(16) Stage {
   int rope_half;         // >0: physical row of logical row p is (p/half)*2*half + p%half
   int vl_len;            // staged vector length per batch row
   int vl_nseg;           // partial sums to add when staging
-  int vl_tag;            // SF_IN_TAG: index of the stage that produces vl_src
-  int rot;               // rotation of the item -> warp assignment
+  int rot;               // rotation of the unit -> CTA assignment (ST_ATTN: item -> warp)
+  int pf_begin, pf_end;  // stages whose factor matrices this stage prefetches into L2
+  int ksplit;            // warps that share one unit's K range (1, 2, 4 or 8)
   int B;                 // batch rows
   const void* vl_src;    // fp32 (or T with SF_IN_T) [vl_nseg, B, vl_len]
   const void* vl_w;      // RMSNorm weight, type T
@@ -108,7 +100,7 @@ struct SyncState {
   unsigned long long bar_base;   // barriers completed by earlier launches
   int status;                    // 0 = ok, else first error code raised on the device
   int status_detail;
-  unsigned epoch;                // launches completed on this workspace (tag generation)
+  unsigned reserved;
   unsigned done_ctas;            // CTAs that have finished the running launch
 };
 
@@ -116,7 +108,6 @@ enum DeviceStatus : int {
   DS_OK = 0,
   DS_BARRIER_TIMEOUT = 1,
   DS_COPY_TIMEOUT = 2,
-  DS_TAG_TIMEOUT = 3,
 };
 
 constexpr int kMaxSmallStages = 14;
@@ -124,12 +115,12 @@ struct SmallProgram {
   Stage st[kMaxSmallStages];
 };
 
-// Shared-memory header of the interpreter (mbarriers, two stage descriptors, reduction scratch,
-// the copy of a by-value program), rounded so that the rings that follow are 1 KB aligned.
+// Shared-memory header of the interpreter (two stage descriptors, reduction scratch, the copy
+// of a by-value program), rounded to 1 KB.
 constexpr int kStageBytesAl = ((int)sizeof(Stage) + 15) / 16 * 16;
 constexpr int kSmallProgBytes = kMaxSmallStages * kStageBytesAl;
-FSVD_HD constexpr int smem_header_bytes(int nw, int nd) {
-  return ((((nw * nd * 8 + 15) / 16) * 16 + 2 * kStageBytesAl + 512 + kSmallProgBytes + 1023) / 1024) * 1024;
+FSVD_HD constexpr int smem_header_bytes() {
+  return ((2 * kStageBytesAl + 512 + kSmallProgBytes + 64 * 32 + 1023) / 1024) * 1024;
 }
 
 }  // namespace fsvd

@@ -38,10 +38,9 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def set_launch_config(warps: int = 16, slots: int = 3, direct: bool = False, grid: int = 0,
-                      inflight: int = 1) -> None:
-    check(_lib.load().fsvd_set_launch_config(int(warps), int(slots), int(bool(direct)), int(grid),
-                                             int(inflight)))
+def set_launch_config(warps: int = 8, depth: int = 16, grid: int = 0) -> None:
+    """Pick the kernel geometry (see fsvd_set_launch_config in include/flashsvd_b200.h)."""
+    check(_lib.load().fsvd_set_launch_config(int(warps), int(depth), int(grid)))
 
 
 def launch_count() -> int:

@@ -76,18 +76,17 @@ int fsvd_version(void);
 const char* fsvd_last_error_string(void);
 /* SM count and opt-in shared memory per block of the current device. */
 int fsvd_device_props(int* sm_count, int* smem_optin_bytes);
-/* Launch geometry: warps per CTA (8 or 16), ring slots per warp, direct != 0 reads the factors
- * with plain global loads instead of the bulk-copy rings, grid = number of CTAs (0 = one per
- * SM), inflight = tiles a warp may have outstanding in the memory system at once (0 = as many
- * as it has slots).  Defaults come from FSVD_NW / FSVD_ND / FSVD_DIRECT / FSVD_GRID /
- * FSVD_INFLIGHT or (16, 3, 0, 0, 1). */
-int fsvd_set_launch_config(int warps, int slots, int direct, int grid, int inflight);
+/* Launch geometry: warps per CTA (8 or 16), 16-byte factor loads each lane keeps in flight,
+ * grid = number of CTAs (0 = one per SM).  Only compiled (warps, depth) pairs are used as given,
+ * otherwise the first variant of the element type.  Defaults: FSVD_NW / FSVD_DEPTH / FSVD_GRID or
+ * (8, 16, 0). */
+int fsvd_set_launch_config(int warps, int depth, int grid);
 
 /* Stage timeline for profiling (the analogue of the reference's per-module CUDA-event hooks,
- * utils/evaluator.py:553-689).  While a device buffer of at least nstages * grid * 64 bytes is
- * set, every launch records for each (stage, CTA) eight %globaltimer slots: 0 stage entry,
- * 1 grid barrier passed, 2 input vector staged, 3 body done, 4-7 finer marks inside the vector
- * stage-in and the tile loop.  NULL switches it off. */
+ * utils/evaluator.py:553-689).  While a device buffer of at least nstages * grid * 128 bytes is
+ * set, every launch records for each (stage, CTA) sixteen 8-byte slots of %globaltimer values:
+ * 0 stage entry, 1 grid barrier passed, 2 input vector staged, 3 stage done, 4 vector words
+ * arrived, 5 norm reduced, 7 factor blocks streamed.  NULL switches it off. */
 int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes);
 
 /* ---- workspace -------------------------------------------------------------------------- */
