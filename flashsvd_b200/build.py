@@ -18,7 +18,7 @@ OUT = PKG / "libflashsvd_b200.so"
 OBJ = CSRC / "build"
 
 NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20",
     "-Xcompiler", "-fPIC",
 ]
 

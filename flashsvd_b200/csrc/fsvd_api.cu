@@ -150,7 +150,7 @@ static WsLayout ws_layout(const fsvd_dims& D) {
 // ------------------------------------------------------------------------------- builder
 struct Builder {
   std::vector<Stage> st;
-  int grid, NW, TW, CB, B, esize;
+  int grid, NW, TW, CB, B, esize, depth;
   long long cum_units = 0;   // GEMV units handed out so far (rotates the unit -> CTA map)
   long long cum_items = 0;   // attention items handed out so far (item -> warp map)
   int max_vec = 8;
@@ -158,6 +158,7 @@ struct Builder {
   Builder(const Resolved& r, int dtype, int B_) {
     grid = r.grid;
     NW = r.nw;
+    depth = r.depth;
     TW = r.grid * r.nw;
     esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
     CB = 64 / esize;   // columns of one block: 4 lanes x 16 bytes
@@ -217,7 +218,10 @@ struct Builder {
       for (int ks = 1; ks <= NW; ks *= 2) {
         const int slots = NW / ks;
         const long long rounds = (nu + slots - 1) / slots;
-        const long long cost = rounds * nops * ((nblk + ks - 1) / ks + 6);
+        const int bps = (nblk + ks - 1) / ks;
+        // time of the busiest warp in padded blocks (+2 per run for its switch); all warps wait
+        // for it, so this also rewards an even spread of the units over the warps
+        const long long cost = rounds * nops * ((bps + depth - 1) / depth * depth + 2);
         if (best_cost < 0 || cost < best_cost) {
           best_cost = cost;
           s.ksplit = ks;
@@ -299,8 +303,11 @@ struct Builder {
     return (int)((mx + 255) / 256 * 256);
   }
   int xstride() const { return (max_vec + 7) / 8 * 8; }
+  // staged vector plus slack: the activation loads of a run's padding blocks run up to one
+  // round past the K range
+  int vec_bytes() const { return (B * xstride() * esize + depth * 64 + 128 + 15) / 16 * 16; }
   size_t smem_bytes() const {
-    return (size_t)smem_header_bytes() + part_bytes() + (size_t)B * xstride() * esize;
+    return (size_t)smem_header_bytes() + part_bytes() + vec_bytes();
   }
 };
 
@@ -489,7 +496,7 @@ static int launch_small(const Resolved& r, Builder& b, SyncState* sync, cudaStre
   memset(&sp, 0, sizeof(sp));
   for (size_t i = 0; i < b.st.size(); ++i) sp.st[i] = b.st[i];
   unsigned long long* tr = g_trace_bytes >= b.st.size() * (size_t)r.grid * 128 ? g_trace : nullptr;
-  cudaError_t e = r.fn(nullptr, &sp, 1, (int)b.st.size(), sync, b.xstride(), b.part_bytes(), tr, r.grid,
+  cudaError_t e = r.fn(nullptr, &sp, 1, (int)b.st.size(), sync, b.xstride(), b.part_bytes(), b.vec_bytes(), tr, r.grid,
                        smem, stream);
   if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   g_launches.fetch_add(1);
@@ -797,7 +804,7 @@ struct fsvd_model {
   WsLayout L;
   char* ws = nullptr;
   Stage* prog = nullptr;
-  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0;
+  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0;
   size_t smem = 0;
   int* tokens = nullptr;
   int* seqlens = nullptr;
@@ -904,6 +911,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   m->nstages = (int)b.st.size();
   m->xstride = b.xstride();
   m->part_bytes = b.part_bytes();
+  m->vec_bytes = b.vec_bytes();
   m->smem = b.smem_bytes();
   ce = cudaMalloc(&m->prog, sizeof(Stage) * b.st.size());
   if (ce == cudaSuccess)
@@ -937,7 +945,7 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
   SyncState* sync = reinterpret_cast<SyncState*>(m->ws + m->L.sync);
   for (int i = 0; i < n_steps; ++i) {
     unsigned long long* tr = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
-    cudaError_t e = m->r.fn(m->prog, nullptr, 0, m->nstages, sync, m->xstride, m->part_bytes, tr,
+    cudaError_t e = m->r.fn(m->prog, nullptr, 0, m->nstages, sync, m->xstride, m->part_bytes, m->vec_bytes, tr,
                             m->r.grid, m->smem, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);

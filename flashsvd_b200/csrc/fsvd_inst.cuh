@@ -7,7 +7,7 @@ namespace {
 
 template <typename T, int NW, int D>
 cudaError_t launch_impl(const fsvd::Stage* prog, const fsvd::SmallProgram* small, int use_small,
-                        int nstages, fsvd::SyncState* sync, int xstride, int part_bytes,
+                        int nstages, fsvd::SyncState* sync, int xstride, int part_bytes, int vec_bytes,
                         unsigned long long* trace, int grid, size_t smem, cudaStream_t stream) {
   auto kern = fsvd::fsvd_decode_kernel<T, NW, D>;
   static size_t attr_smem[16] = {0};
@@ -32,7 +32,7 @@ cudaError_t launch_impl(const fsvd::Stage* prog, const fsvd::SmallProgram* small
   cfg.attrs = at;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, prog, small ? *small : empty, use_small, nstages, sync,
-                            xstride, part_bytes, trace);
+                            xstride, part_bytes, vec_bytes, trace);
 }
 
 }  // namespace

@@ -36,6 +36,9 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <type_traits>
+#include <utility>
+
 #include "fsvd_stage.h"
 
 namespace fsvd {
@@ -524,6 +527,33 @@ __device__ __forceinline__ uint4 ldg_stream_if(const void* p, bool pred) {
       : "l"(p), "r"((unsigned)pred));
   return v;
 }
+// Refill of pipeline slot I while run `cur` is consumed (see gemv_stage): block b0 + I + D of
+// the current run when it exists (I < r1 also says the lane's columns are inside the K range),
+// else block I of the next run (I >= r2 and I < nl), else zeros.  Addresses are a base plus an
+// immediate, the predicates compare round counters with immediates: no per-block arithmetic.
+template <int I, int D>
+__device__ __forceinline__ uint4 ldg_refill(const char* pb, const char* pn, int r1, int r2, int nl) {
+  uint4 v;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.gt.s32 p, %6, %9;\n\t"          // I < r1
+      "setp.le.s32 q, %7, %9;\n\t"          // I >= r2
+      "setp.gt.and.s32 q, %8, %9, q;\n\t"   // ... and I < nl
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@p ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%10];\n\t"
+      "@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%5+%11];\n\t}"
+      : "=&r"(v.x), "=&r"(v.y), "=&r"(v.z), "=&r"(v.w)
+      : "l"(pb), "l"(pn), "r"(r1), "r"(r2), "r"(nl), "n"(I), "n"((I + D) * 64), "n"(I * 64));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_imm(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(OFF));
+  return v;
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
@@ -537,22 +567,26 @@ struct UnitInfo {
 };
 constexpr int kMaxUnitsPerCta = 64;
 
-// L2 prefetch of the whole factor matrices of stage `st`, spread over every thread of the grid.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// L2 prefetch of the whole factor matrices of stage `st`: every warp of the grid asks for one
+// contiguous share with a single bulk prefetch (per-line prefetches cost one LSU cycle per line,
+// as much as the loads themselves).
 template <typename T>
-__device__ __forceinline__ void prefetch_stage(const Stage& st, size_t gtid, size_t gthreads) {
-  if (st.type != ST_GEMV) return;
+__device__ __forceinline__ void prefetch_stage(const Stage& st, int gwarp, int gwarps, int lane) {
+  if (st.type != ST_GEMV || lane != 0) return;
   const size_t pitch = (size_t)st.ldw * sizeof(T);
-  if (st.rope_half > 0) {
-    // both rotary halves live in one matrix of 2*P rows starting at WA
-    const size_t lines = ((size_t)2 * st.P * pitch + 127) >> 7;
-    for (size_t l = gtid; l < lines; l += gthreads) prefetch_l2(reinterpret_cast<const char*>(st.WA) + (l << 7));
-  } else {
-    const size_t lines = ((size_t)st.P * pitch + 127) >> 7;
-    for (size_t l = gtid; l < lines; l += gthreads) {
-      prefetch_l2(reinterpret_cast<const char*>(st.WA) + (l << 7));
-      if (st.WB) prefetch_l2(reinterpret_cast<const char*>(st.WB) + (l << 7));
-    }
-  }
+  const size_t rows = st.rope_half > 0 ? (size_t)2 * st.P : (size_t)st.P;
+  const size_t total = rows * pitch;                       // multiple of 16
+  size_t share = (total / gwarps + 15) & ~(size_t)15;
+  if (share < 2048) share = 2048;
+  const size_t beg = (size_t)gwarp * share;
+  if (beg >= total) return;
+  const uint32_t n = (uint32_t)min(share, total - beg);
+  bulk_prefetch_l2(reinterpret_cast<const char*>(st.WA) + beg, n);
+  if (st.WB && st.rope_half == 0) bulk_prefetch_l2(reinterpret_cast<const char*>(st.WB) + beg, n);
 }
 
 // Grid barrier wait (one polling lane per CTA) in front of a stage with SF_BARRIER.
@@ -590,62 +624,69 @@ struct StageCtx {
   unsigned long long* trow;
 };
 
-// Walks the blocks of one warp: unit ordinal i (stepping by the number of unit slots), operand
-// group g, block j of the warp's K slice.  `p` is the lane's load address, `kcol` the first
-// column of the lane's 16 bytes.
-struct BlockCursor {
-  int i, g, j, jend;
-  int kcol, kend;
-  const char* p;
+// A run: the blocks one warp streams for one (unit, operand): its K slice of 8 factor rows.
+// n / ui / g are warp-uniform, p / lim / xcol belong to the lane.
+struct Run {
+  const char* p;   // lane address of block 0 (factor row lane>>2, 16 bytes at column kcol)
+  int n;           // blocks in the run; 0 = no more runs
+  int lim;         // blocks whose 16 bytes of this lane lie inside the K range (ragged last block)
+  int xcol;        // the lane's activation column for block 0, operand offset included
+  int ui, g;       // unit ordinal of this CTA, operand group
 };
 
 template <typename T>
 struct WarpGeo {
   const char* W[2];
   size_t pitch;
+  int xoff[2];
   int nops, nu, P;
-  int ks, kslice, slot, nslots;   // warps per unit, this warp's slice and unit slot
+  int ks, kslice, slot, nslots;   // warps per unit, this warp's K slice and unit slot
   int qg, qt;
 };
 
+// Move `r` to the next (unit, operand) in which this warp owns blocks, starting the search at
+// (ui, g).  Units are visited slot, slot + nslots, ...; operands 0, 1 inside a unit.
 template <typename T>
-__device__ __forceinline__ void cursor_seek(const WarpGeo<T>& wg, const UnitInfo* units, BlockCursor& c) {
+__device__ __forceinline__ void run_seek(const WarpGeo<T>& wg, const UnitInfo* units, Run& r, int ui, int g) {
   constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
-  while (c.i < wg.nu) {
-    const UnitInfo u = units[c.i];
+  for (; ui < wg.nu; ui += wg.nslots, g = 0) {
+    const UnitInfo u = units[ui];
     const int bps = (u.nblk + wg.ks - 1) / wg.ks;
     const int j0 = wg.kslice * bps, j1 = min(u.nblk, j0 + bps);
-    if (j0 < j1) {
-      // a row past the end of the matrix is replaced by the unit's first row; its sums land in
-      // accumulator columns that are never stored
-      const int r = (u.p0 + wg.qg < wg.P) ? wg.qg : 0;
-      c.j = j0;
-      c.jend = j1;
-      c.kend = u.kend;
-      c.kcol = u.kbeg + j0 * CB + wg.qt * VEC;
-      c.p = wg.W[c.g] + u.row_off + (size_t)r * wg.pitch + (size_t)c.kcol * sizeof(T);
-      return;
-    }
-    c.i += wg.nslots;
-    c.g = 0;
+    if (j0 >= j1) continue;
+    // a row past the end of the matrix is replaced by the unit's first row; its sums land in
+    // accumulator columns that are never stored
+    const int row = (u.p0 + wg.qg < wg.P) ? wg.qg : 0;
+    const int kcol = u.kbeg + j0 * CB + wg.qt * VEC;
+    r.p = wg.W[g] + u.row_off + (size_t)row * wg.pitch + (size_t)kcol * sizeof(T);
+    r.n = j1 - j0;
+    r.lim = max(0, min(r.n, (u.kend - kcol + CB - 1) / CB));
+    r.xcol = wg.xoff[g] + kcol;
+    r.ui = ui;
+    r.g = g;
+    return;
   }
+  r.n = 0;
+  r.lim = 0;
+  r.ui = wg.nu;
+  r.g = 0;
 }
 template <typename T>
-__device__ __forceinline__ void cursor_next(const WarpGeo<T>& wg, const UnitInfo* units, BlockCursor& c) {
-  constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
-  ++c.j;
-  c.kcol += CB;
-  c.p += 64;
-  if (c.j >= c.jend) {
-    if (++c.g >= wg.nops) {
-      c.g = 0;
-      c.i += wg.nslots;
-    }
-    cursor_seek<T>(wg, units, c);
+__device__ __forceinline__ void run_next(const WarpGeo<T>& wg, const UnitInfo* units, const Run& cur, Run& nxt) {
+  if (cur.n == 0) {
+    nxt = cur;
+    return;
   }
+  if (cur.g + 1 < wg.nops) run_seek<T>(wg, units, nxt, cur.ui, cur.g + 1);
+  else run_seek<T>(wg, units, nxt, cur.ui + wg.nslots, 0);
 }
 
 // One GEMV stage, all warps of the CTA.
+//
+// Register pipeline: every run is padded to whole rounds of D blocks and slot s of buf[] holds
+// the block with index % D == s, so every index into buf[] is a compile-time constant and a
+// slot is always refilled with the block D ahead in the padded stream: block b + D of the run
+// being consumed or, in its last round, block s of the next run.
 template <typename T, int NW, int D>
 __device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
   using X = TT<T>;
@@ -680,6 +721,8 @@ __device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
   wg.W[0] = reinterpret_cast<const char*>(st.WA);
   wg.W[1] = reinterpret_cast<const char*>(st.WB);
   wg.pitch = (size_t)st.ldw * sizeof(T);
+  wg.xoff[0] = st.xA_off;
+  wg.xoff[1] = st.xB_off;
   wg.nops = st.WB ? 2 : 1;
   wg.nu = nu;
   wg.P = st.P;
@@ -689,23 +732,44 @@ __device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
   wg.nslots = NW / wg.ks;
   wg.qg = lane >> 2;
   wg.qt = lane & 3;
+  const UnitInfo* units = cx.units;
 
-  // ---- 1. first D loads of this warp, before any waiting
-  BlockCursor fc;
-  fc.i = wg.slot;
-  fc.g = 0;
-  cursor_seek<T>(wg, cx.units, fc);
+  // operands of the epilogues this thread will run (outputs tid and tid + nthreads), fetched
+  // now so that their latency hides behind the streaming
+  const int nout = nu * kTileRows * B;
+  EpiAux ax0, ax1;
+  ax0.a0 = ax0.a1 = ax1.a0 = ax1.a1 = 0.f;
+  ax0.pos = ax1.pos = 0;
+  auto out_pos = [&](int o, int& i, int& b, int& r) {
+    i = o / (kTileRows * B);
+    const int rem = o - i * (kTileRows * B);
+    b = rem / kTileRows;
+    r = rem - b * kTileRows;
+  };
+  {
+    int i, b, r;
+    if (tid < nout) {
+      out_pos(tid, i, b, r);
+      const int p = cx.units[i].p0 + r;
+      if (p < st.P) epi_prefetch<T>(st, p, b, ax0);
+    }
+    if (tid + nthreads < nout) {
+      out_pos(tid + nthreads, i, b, r);
+      const int p = cx.units[i].p0 + r;
+      if (p < st.P) epi_prefetch<T>(st, p, b, ax1);
+    }
+  }
+  // ---- 1. first loads of this warp, before any waiting
+  Run cur, nxt;
+  run_seek<T>(wg, units, cur, wg.slot, 0);
+  run_next<T>(wg, units, cur, nxt);
   uint4 buf[D];
 #pragma unroll
-  for (int i = 0; i < D; ++i) {
-    const bool live = fc.i < nu;
-    buf[i] = ldg_stream_if(fc.p, live && fc.kcol < fc.kend);
-    if (live) cursor_next<T>(wg, cx.units, fc);
-  }
+  for (int s = 0; s < D; ++s) buf[s] = ldg_stream_if(cur.p + s * 64, s < cur.lim);
   const long long k2 = clock64();
   // ---- 2. L2 prefetch of the stages the host assigned to this one
   for (int t = st.pf_begin; t < st.pf_end; ++t)
-    prefetch_stage<T>(cx.prog[t], (size_t)blockIdx.x * nthreads + tid, (size_t)grid * nthreads);
+    prefetch_stage<T>(cx.prog[t], warp * grid + blockIdx.x, grid * NW, lane);
 
   const long long k3 = clock64();
   // ---- 3. wait for the producers of the input vector, stage it
@@ -718,82 +782,86 @@ __device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
   trace_mark(cx.trow, 2);
 
   const long long k4 = clock64();
-  int nblocks = 0;
-  // ---- 4. stream this warp's blocks
-  BlockCursor cc;
-  cc.i = wg.slot;
-  cc.g = 0;
-  cursor_seek<T>(wg, cx.units, cc);
+  // ---- 4. stream this warp's runs
   const bool xact = wg.qg < B;
-  const unsigned char* xlane = reinterpret_cast<const unsigned char*>(cx.xvec) +
-                               (size_t)(xact ? wg.qg : 0) * cx.xstride * sizeof(T);
-  float acc[2][4];
+  const uint32_t xvec_s = smem_u32(cx.xvec);
+  const uint32_t xlane_s = xvec_s + (uint32_t)(xact ? wg.qg : 0) * cx.xstride * (uint32_t)sizeof(T);
+  const uint32_t xrow_bytes = (uint32_t)cx.xstride * (uint32_t)sizeof(T);
+  while (cur.n > 0) {
+    float acc[2][4];
 #pragma unroll
-  for (int c = 0; c < 2; ++c)
+    for (int c = 0; c < 2; ++c)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+      for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+    const char* pb = cur.p;                  // lane address of block b0
+    const char* pn = nxt.p;
+    // activation bytes of block b0 for this lane; blocks past `lim` multiply zeros, their
+    // activation loads may run up to one block past the K range (the host pads the vector)
+    uint32_t xs = (sizeof(T) == 2 ? xlane_s : xvec_s) + (uint32_t)cur.xcol * (uint32_t)sizeof(T);
+    // A run is padded to a whole number of rounds of D blocks (the padding blocks load nothing
+    // and multiply zeros), so the block D ahead of block b0 + I is block b0 + I + D of this run
+    // or, in the last round, block I of the next one.
+    const int np = (cur.n + D - 1) / D * D;
+    int r1 = cur.lim - D, r2 = np - D;       // I < r1: own block b0+I+D holds data; I >= r2: next run's turn
+    const int nl = nxt.lim;
 
-  while (cc.i < nu) {
+    auto consume = [&](auto iconst, const uint4& wv) {
+      constexpr int I = decltype(iconst)::value;
+      if constexpr (sizeof(T) == 2) {
+        const uint4 xv = lds128_imm<I * 64>(xs);
+        mma_bf16_16816(acc[I & 1], xv.x, 0u, xv.y, 0u, wv.x, wv.y);
+        mma_bf16_16816(acc[(I & 1) ^ 1], xv.z, 0u, xv.w, 0u, wv.z, wv.w);
+      } else {
+        // fp32: 4 columns of factor row qg times activation rows 0..3; acc[0][b] per batch row
+        float wf[4], xf[4];
+        X::unpack(wv, wf);
 #pragma unroll
-    for (int i = 0; i < D; ++i) {
-      if (cc.i < nu) {
-        const uint4 wv = buf[i];
-        ++nblocks;
-        // refill the slot with the block D ahead
-        {
-          const bool live = fc.i < nu;
-          buf[i] = ldg_stream_if(fc.p, live && fc.kcol < fc.kend);
-          if (live) cursor_next<T>(wg, cx.units, fc);
-        }
-        const bool ok = cc.kcol < cc.kend;
-        const int xcol = (cc.g ? st.xB_off : st.xA_off) + (ok ? cc.kcol : 0);
-        if constexpr (sizeof(T) == 2) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(xlane + (size_t)xcol * sizeof(T));
-          mma_bf16_16816(acc[0], xv.x, 0u, xv.y, 0u, wv.x, wv.y);
-          mma_bf16_16816(acc[1], xv.z, 0u, xv.w, 0u, wv.z, wv.w);
-        } else {
-          // fp32: 4 columns of factor row qg times activation rows 0..3; acc[0][b] per batch row
-          float wf[4], xf[4];
-          X::unpack(wv, wf);
+        for (int bb = 0; bb < 4; ++bb) {
+          if (bb < B) {
+            const uint4 xb = lds128_imm<I * 64>(xs + bb * xrow_bytes);
+            X::unpack(xb, xf);
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            if (b < B) {
-              const uint4 xb = *reinterpret_cast<const uint4*>(
-                  reinterpret_cast<const unsigned char*>(cx.xvec) + ((size_t)b * cx.xstride + xcol) * sizeof(T));
-              X::unpack(xb, xf);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) acc[0][b] = fmaf(wf[e], xf[e], acc[0][b]);
-            }
+            for (int e = 0; e < 4; ++e) acc[0][bb] = fmaf(wf[e], xf[e], acc[0][bb]);
           }
         }
-        // last block of this warp's slice of (unit, operand): publish the partial sums
-        const int ci = cc.i, cg = cc.g;
-        cursor_next<T>(wg, cx.units, cc);
-        if (cc.i != ci || cc.g != cg) {
-          float* dst = cx.part + ((size_t)(ci * wg.nops + cg) * wg.ks + wg.kslice) * 64;
-          if constexpr (sizeof(T) == 2) {
-            // lane (qg, qt): batch row qg, factor rows 2qt, 2qt+1
-            if (xact) {
-              dst[wg.qg * 8 + 2 * wg.qt] = acc[0][0] + acc[1][0];
-              dst[wg.qg * 8 + 2 * wg.qt + 1] = acc[0][1] + acc[1][1];
-            }
-          } else {
-            // quad reduction: lanes (qg, 0..3) hold 4 columns each of factor row qg
+      }
+    };
+    for (int left = np; left > 0; left -= D) {
+      [&]<int... I>(std::integer_sequence<int, I...>) {
+        ((void)([&] {
+           const uint4 wv = buf[I];
+           buf[I] = ldg_refill<I, D>(pb, pn, r1, r2, nl);
+           consume(std::integral_constant<int, I>{}, wv);
+         }()),
+         ...);
+      }(std::make_integer_sequence<int, D>{});
+      pb += D * 64;
+      xs += D * 64;
+      r1 -= D;
+      r2 -= D;
+    }
+    // publish the partial sums of this run
+    {
+      float* dst = cx.part + ((size_t)(cur.ui * wg.nops + cur.g) * wg.ks + wg.kslice) * 64;
+      if constexpr (sizeof(T) == 2) {
+        // lane (qg, qt): batch row qg, factor rows 2qt, 2qt+1
+        if (xact) {
+          dst[wg.qg * 8 + 2 * wg.qt] = acc[0][0] + acc[1][0];
+          dst[wg.qg * 8 + 2 * wg.qt + 1] = acc[0][1] + acc[1][1];
+        }
+      } else {
+        // quad reduction: lanes (qg, 0..3) hold 4 columns each of factor row qg
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              float v = acc[0][b];
-              v += __shfl_xor_sync(0xffffffffu, v, 1);
-              v += __shfl_xor_sync(0xffffffffu, v, 2);
-              if (wg.qt == b && b < B) dst[b * 8 + wg.qg] = v;
-            }
-          }
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+        for (int bb = 0; bb < 4; ++bb) {
+          float v = acc[0][bb];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          if (wg.qt == bb && bb < B) dst[bb * 8 + wg.qg] = v;
         }
       }
     }
+    cur = nxt;
+    run_next<T>(wg, units, cur, nxt);
   }
   trace_mark(cx.trow, 7);
   const long long k5 = clock64();
@@ -801,16 +869,16 @@ __device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
   const long long k6 = clock64();
 
   // ---- 5. add the slices' partial sums in slice order and run the epilogue
-  const int nout = nu * kTileRows * B;
-  for (int o = tid; o < nout; o += nthreads) {
-    const int i = o / (kTileRows * B);
-    const int rem = o - i * (kTileRows * B);
-    const int b = rem / kTileRows, r = rem - b * kTileRows;
-    const UnitInfo u = cx.units[i];
+  for (int o = tid, it = 0; o < nout; o += nthreads, ++it) {
+    int i, b, r;
+    out_pos(o, i, b, r);
+    const UnitInfo u = units[i];
     const int p = u.p0 + r;
     if (p >= st.P) continue;
     EpiAux ax;
-    epi_prefetch<T>(st, p, b, ax);
+    if (it == 0) ax = ax0;
+    else if (it == 1) ax = ax1;
+    else epi_prefetch<T>(st, p, b, ax);
     const int bps = (u.nblk + wg.ks - 1) / wg.ks;
     const int nsl = (u.nblk + bps - 1) / bps;   // slices that own blocks of this unit
     float sum[2] = {0.f, 0.f};
@@ -830,7 +898,7 @@ __device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
     cx.trow[12] = k5 - k4;
     cx.trow[13] = k6 - k5;
     cx.trow[14] = clock64() - k6;
-    cx.trow[15] = nblocks;
+    cx.trow[15] = wg.ks;
   }
 }
 
@@ -1067,7 +1135,7 @@ template <typename T, int NW, int D>
 __global__ void __launch_bounds__(NW * 32, 1)
 fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant__ SmallProgram small,
                    int use_small, int nstages, SyncState* sync, int xstride, int part_bytes,
-                   unsigned long long* trace) {
+                   int vec_bytes, unsigned long long* trace) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nthreads = NW * 32;
@@ -1080,6 +1148,11 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
   static_assert(sizeof(UnitInfo) == 32, "unit table entry size");
   float* part = reinterpret_cast<float*>(smem + smem_header_bytes());
   char* xvec = reinterpret_cast<char*>(smem + smem_header_bytes() + part_bytes);
+
+  // Padding blocks of a run multiply zero factors with whatever follows the K range in the
+  // staged vector, so that memory must hold finite numbers from the start.
+  for (int i = tid; i < vec_bytes / 16; i += nthreads)
+    reinterpret_cast<uint4*>(xvec)[i] = make_uint4(0, 0, 0, 0);
 
   const Stage* prog = prog_global;
   if (use_small) {

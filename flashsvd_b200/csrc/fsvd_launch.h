@@ -6,7 +6,8 @@
 
 typedef cudaError_t (*LaunchFn)(const fsvd::Stage* prog, const fsvd::SmallProgram* small,
                                 int use_small, int nstages, fsvd::SyncState* sync, int xstride,
-                                int part_bytes, unsigned long long* trace, int grid, size_t smem,
+                                int part_bytes, int vec_bytes, unsigned long long* trace, int grid,
+                                size_t smem,
                                 cudaStream_t stream);
 
 struct KernelEntry {
