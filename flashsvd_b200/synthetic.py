@@ -1,0 +1,105 @@
+"""Seeded synthetic models with the shapes of the benchmark configurations.
+
+The reference measures on real checkpoints that are not available offline; the benchmark and the
+large-shape tests use random factors of the same shapes instead: N(0, 1/sqrt(fan_in)) factors,
+unit RMSNorm weights, the scaling of the reference's own kernel harness
+(src/legacy/FlashSVD-V1/decoders/llama/kernels/flashsvdswiglu.py:348-351).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class ModelShape:
+    d: int = 4096
+    H: int = 32
+    Hk: int = 32
+    Dh: int = 128
+    I: int = 11008
+    Rq: int = 1024
+    Rk: int = 1024
+    Rv: int = 1024
+    Ro: int = 1024
+    Rg: int = 1488
+    Ru: int = 1488
+    Rd: int = 1488
+    vocab: int = 32000
+    n_layers: int = 32
+    eps: float = 1e-6
+    theta: float = 10000.0
+
+    def params_per_layer(self) -> int:
+        d, HD, KD, I = self.d, self.H * self.Dh, self.Hk * self.Dh, self.I
+        return (d * self.Rq + HD * self.Rq + d * self.Rk + KD * self.Rk + d * self.Rv + KD * self.Rv
+                + HD * self.Ro + d * self.Ro + d * self.Rg + I * self.Rg + d * self.Ru + I * self.Ru
+                + I * self.Rd + d * self.Rd)
+
+    def bytes_per_step(self, ctx: int, batch: int, esize: int = 2) -> int:
+        """Algorithmic HBM bytes of one decode step: every factor once, the K and V rows of the
+        context, lm_head once."""
+        kv = 2 * batch * ctx * self.Hk * self.Dh * esize
+        return self.n_layers * (self.params_per_layer() * esize + kv) + self.vocab * self.d * esize
+
+
+LLAMA7B_SVD50 = ModelShape()
+
+
+def random_packed_layers(shape: ModelShape, *, device, dtype, seed: int = 0, share_pairs: bool = False):
+    """Per-layer tensors in the layout of ``packing.pack_layer``, drawn directly on the device.
+    ``share_pairs``: layers (2i, 2i+1) share every input-side factor tensor (basis sharing,
+    utils/model_utils.py:366-406)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def w(out_f, in_f):
+        t = torch.randn(out_f, in_f, device=device, dtype=torch.float32, generator=gen)
+        return (t / math.sqrt(in_f)).to(dtype)
+
+    d, HD, KD, I = shape.d, shape.H * shape.Dh, shape.Hk * shape.Dh, shape.I
+    layers = []
+    for li in range(shape.n_layers):
+        if share_pairs and li % 2 == 1:
+            prev = layers[-1]
+            qkv_v, o_v, upgate_v, down_v = prev["qkv_v"], prev["o_v"], prev["upgate_v"], prev["down_v"]
+        else:
+            qkv_v = w(shape.Rq + shape.Rk + shape.Rv, d)
+            o_v = w(shape.Ro, HD)
+            upgate_v = w(shape.Ru + shape.Rg, d)
+            down_v = w(shape.Rd, I)
+        layers.append({
+            "ln1_w": torch.ones(d, device=device, dtype=dtype),
+            "qkv_v": qkv_v, "q_u": w(HD, shape.Rq), "k_u": w(KD, shape.Rk), "v_u": w(KD, shape.Rv),
+            "o_v": o_v, "o_u": w(d, shape.Ro),
+            "ln2_w": torch.ones(d, device=device, dtype=dtype),
+            "upgate_v": upgate_v, "gate_u": w(I, shape.Rg), "up_u": w(I, shape.Ru),
+            "down_v": down_v, "down_u": w(d, shape.Rd),
+        })
+    embed = w(shape.vocab, d)
+    lm_head = w(shape.vocab, d)
+    final_norm = torch.ones(d, device=device, dtype=dtype)
+    return layers, embed, final_norm, lm_head
+
+
+def make_engine(shape: ModelShape, *, device, dtype=torch.bfloat16, batch=1, ctx=512, max_new=64, seed=0,
+                fill_cache=True, share_pairs=False):
+    """Random model + engine whose caches already hold ``ctx`` tokens of N(0,1) keys / values (the
+    state after a prefill of that length, as far as the cost of a decode step goes)."""
+    from .engine import DecodeEngine
+
+    layers, embed, final_norm, lm_head = random_packed_layers(shape, device=device, dtype=dtype, seed=seed,
+                                                              share_pairs=share_pairs)
+    eng = DecodeEngine(layers=layers, embed=embed, final_norm=final_norm, lm_head=lm_head,
+                       num_heads=shape.H, num_kv_heads=shape.Hk, head_dim=shape.Dh, batch_size=batch,
+                       max_cache_len=ctx + max_new + 4, rope_theta=shape.theta, eps=shape.eps,
+                       max_steps=max_new + 8)
+    if fill_cache and ctx > 0:
+        gen = torch.Generator(device=device).manual_seed(seed + 1)
+        for kc, vc in zip(eng.key_cache, eng.value_cache):
+            kc[:, :ctx].copy_(torch.randn(kc[:, :ctx].shape, device=device, generator=gen).to(dtype))
+            vc[:, :ctx].copy_(torch.randn(vc[:, :ctx].shape, device=device, generator=gen).to(dtype))
+        eng.seqlens.fill_(ctx)
+    eng.tokens.copy_(torch.arange(batch, device=device, dtype=torch.int32) % shape.vocab)
+    return eng
