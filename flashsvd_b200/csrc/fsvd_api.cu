@@ -980,3 +980,74 @@ int fsvd_model_reset_sync(fsvd_model* m, void* stream) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------- built-in scratch
+// fsvd_lowrank_proj_static: the low-rank projection on scratch that is part of the library
+// image instead of a caller-provided workspace.  The scratch holds the grid-barrier words and the
+// rank-space partial sums [segments][B][R] in fp32; one array per device, shared by every call.
+constexpr int kStaticMaxBR = 8192;  // limit on B * R
+constexpr size_t kStaticSyncBytes = 256;
+constexpr size_t kStaticScratchBytes = kStaticSyncBytes + (size_t)kMaxSegs * kStaticMaxBR * sizeof(float);
+static_assert(sizeof(SyncState) <= kStaticSyncBytes, "barrier words must fit the scratch header");
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static void* g_static_ptr[16] = {nullptr};
+static std::mutex g_static_mu;
+
+// Device address of the scratch on the current device.  The first call on a device looks the
+// address up and clears the barrier words (the only part that has to start at zero: the partial
+// sums are fully rewritten by every call, the barrier counters only ever grow).
+static int static_scratch(char** out, cudaStream_t stream) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return fail(FSVD_ERR_UNSUPPORTED, "device ordinal %d unsupported (0..15)", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (!p) return fail(FSVD_ERR_CUDA, "built-in scratch has no device address");
+    CUDA_TRY(cudaMemsetAsync(p, 0, kStaticSyncBytes, stream));
+    g_static_ptr[dev] = p;
+  }
+  *out = reinterpret_cast<char*>(g_static_ptr[dev]);
+  return 0;
+}
+
+extern "C" int fsvd_lowrank_proj_static(const void* x, const void* v, const void* u,
+                                        const void* residual, void* y, int B, int d_in, int R,
+                                        int d_out, int dtype, void* stream) {
+  if (!x || !v || !u || !y) return fail(FSVD_ERR_ARG, "null argument");
+  if (d_in <= 0 || R <= 0 || d_out <= 0 || d_in % 8 || R % 8)
+    return fail(FSVD_ERR_ALIGN, "d_in=%d and R=%d must be positive multiples of 8", d_in, R);
+  if (!aligned16(x) || !aligned16(v) || !aligned16(u) || !aligned16(y))
+    return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  Resolved r;
+  if (int e = resolve(dtype, B, r)) return e;
+  if ((long long)B * R > kStaticMaxBR)
+    return fail(FSVD_ERR_WORKSPACE,
+                "B*R = %lld exceeds the built-in scratch (B*R <= %d); use fsvd_lowrank_proj with a workspace",
+                (long long)B * R, kStaticMaxBR);
+  char* w = nullptr;
+  if (int e = static_scratch(&w, (cudaStream_t)stream)) return e;
+  float* partial = reinterpret_cast<float*>(w + kStaticSyncBytes);
+  Builder b(r, dtype, B);
+  {
+    Stage& s = b.gemv(v, nullptr, R, d_in, d_in, true);
+    b.vec(s, VL_SUM, x, d_in, 1, false);
+    s.flags |= SF_IN_T;
+    s.epi = EPI_PARTIAL;
+    s.out = partial;
+  }
+  const int segs = b.st.back().segs;
+  if (segs > kMaxSegs) return fail(FSVD_ERR_UNSUPPORTED, "%d K segments exceed the built-in scratch", segs);
+  {
+    Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
+    b.vec(s, VL_SUM, partial, R, segs, true);
+    s.epi = residual ? EPI_RESID : EPI_STORE;
+    s.resid = residual;
+    s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
+    s.out = y;
+  }
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w), (cudaStream_t)stream);
+}

@@ -98,6 +98,27 @@ def lowrank_proj(x, v_w, u_w, ws: Workspace, residual=None, out=None):
     return out
 
 
+def lowrank_proj_static(x, v_w, u_w, residual=None, out=None):
+    """lowrank_proj on the library's built-in scratch (B * R <= 8192): no workspace argument and
+    no device allocation inside the call when ``out`` is given.  Calls share one scratch array
+    per device and must not overlap in time."""
+    if x.ndim != 2:
+        raise ValueError(f"x must be [B, d_in], got {tuple(x.shape)}")
+    B, d_in = x.shape
+    if v_w.ndim != 2 or v_w.shape[1] != d_in:
+        raise ValueError(f"v_w must be [R, {d_in}], got {tuple(v_w.shape)}")
+    R = v_w.shape[0]
+    if u_w.ndim != 2 or u_w.shape[1] != R:
+        raise ValueError(f"u_w must be [d_out, {R}], got {tuple(u_w.shape)}")
+    d_out = u_w.shape[0]
+    if out is None:
+        out = torch.empty((B, d_out), dtype=x.dtype, device=x.device)
+    check(_lib.load().fsvd_lowrank_proj_static(
+        _ptr(x), _ptr(v_w), _ptr(u_w), _ptr(residual), _ptr(out), B, d_in, R, d_out,
+        _dtype_code(x.dtype), _stream()))
+    return out
+
+
 def mlp_swiglu_decode(x, gate_u, up_u, down_v, down_u, ws: Workspace, *, upgate_v=None,
                       norm_w=None, eps=1e-6, residual=None, out=None):
     """Fused low-rank SwiGLU MLP for one token per row of x.

@@ -105,6 +105,28 @@ int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* r
                       int B, int d_in, int R, int d_out, int dtype,
                       void* ws, size_t ws_bytes, void* stream);
 
+/* The same projection for callers that cannot hand over a workspace.  This entry point has no
+ * counterpart in the reference.  Its scratch (barrier words + rank-space partial sums) is a
+ * fixed 256 KiB + 256 B array inside the library's device image, so the call performs no device
+ * memory allocation or release of any kind (no cudaMalloc / cudaFree, no memory pool, no
+ * allocating library call); on the host it uses only a few hundred bytes of ordinary heap for the
+ * stage list.  Meant for code that runs where device allocation is off limits or unaffordable: a
+ * serving loop whose memory is fully budgeted up front, a real-time thread that must not take
+ * the allocator's locks, or a plug-in that is handed tensors but no allocator.
+ *  - Limit: B * R <= 8192 (for example B = 1 with R up to 8192, or B = 8 with R up to 1024);
+ *    beyond that the call returns FSVD_ERR_WORKSPACE and launches nothing.
+ *  - The first call on each device looks up the array's device address and clears its barrier
+ *    words on `stream`; make that first call during start-up, outside any stream capture and
+ *    with the target device current.  Later calls do no set-up.
+ *  - One array per device is shared by every call: calls must be ordered one after another
+ *    (same stream, or events between streams).  Two calls that overlap in time race on the
+ *    partial sums and the barrier and give undefined results.
+ *  - The bounded-wait status word of this variant is not readable from the host; use
+ *    fsvd_lowrank_proj with a workspace where fsvd_workspace_status is needed.
+ * Results are bitwise identical to fsvd_lowrank_proj with the same launch configuration. */
+int fsvd_lowrank_proj_static(const void* x, const void* v, const void* u, const void* residual,
+                             void* y, int B, int d_in, int R, int d_out, int dtype, void* stream);
+
 /* y[B,d] = (residual +) down_u(down_v(silu(gate_u(p_gate)) * up_u(p_up))).
  * With upgate_v != NULL: x is the hidden state [B,d], optionally RMS-normalised by norm_w, and
  * [p_up | p_gate] = upgate_v(x).  With upgate_v == NULL: x is PCat [B, Ru+Rg] = [p_up | p_gate],
