@@ -27,6 +27,11 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# DRAM traffic / algorithmic bytes of the decode kernel from one ncu capture of a 4-layer launch
+# (profiles/fsvd_decode_kernel_model_4layers_ncu_full.md); traffic grows with the layer count in
+# proportion to the algorithmic bytes.
+NCU_TRAFFIC_RATIO = 1.050
+
 METRIC = "decode tokens/s (7B-shape SVD 50%, bf16, bs1, ctx512) and % of HBM roofline"
 CTX = 512
 
@@ -146,6 +151,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="flashsvd_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=32,
+                    help="fewer than 32 layers = a small case of the same kernel for profiler captures; "
+                         "its line is marked profile_case and is not a benchmark result")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -167,6 +175,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     shape = synthetic.LLAMA7B_SVD50
+    if args.layers != shape.n_layers:
+        import dataclasses
+
+        shape = dataclasses.replace(shape, n_layers=int(args.layers))
     warm = max(3, args.warmup)
     eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=1, ctx=CTX,
                                 max_new=warm + 2 * args.steps + 16, seed=rank)
@@ -178,6 +190,7 @@ def main():
         torch.cuda.synchronize()
 
     # ---- kernel-only: K steps, inputs resident in HBM, device-side token feedback
+    torch.cuda.profiler.start()   # profiler range = warm-up + timed regions (ncu --profile-from-start off)
     launches0 = ops.launch_count()
     eng.step(warm)
     barrier()
@@ -213,6 +226,7 @@ def main():
     e3.record(stream)
     barrier()
     ms_e2e = e2.elapsed_time(e3)
+    torch.cuda.profiler.stop()
 
     times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
     if world > 1:
@@ -243,10 +257,12 @@ def main():
                             "vocab 32000, batch 1 per GPU, ctx 512, greedy decode; one step = one kernel launch",
                 "l2": "not flushed: a step streams 6.99 GB of factors, far more than the 126 MB L2",
                 "device_status": status,
+                **({"profile_case": f"{shape.n_layers} layers only"} if shape.n_layers != 32 else {}),
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": None,
+                "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_RATIO * bytes_step,
+                "traffic_note": "ncu dram bytes of a 4-layer launch scaled by algorithmic bytes",
                 "bytes_per_launch": bytes_step, "bytes_per_layer": layer_bytes,
                 "us_per_layer_equiv": ms / args.steps * 1e3 * layer_bytes / bytes_step,
             },
