@@ -1,5 +1,6 @@
 // C ABI of the decode path: builds stage programs on the host and launches the persistent
 // interpreter (fsvd_kernel.cuh).  No torch types; see include/flashsvd_b200.h.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -15,7 +16,6 @@
 
 using namespace fsvd;
 
-static constexpr int kRowsPerTile = 8;  // factor rows per unit
 
 // ------------------------------------------------------------------------------- errors
 static thread_local char g_err[512] = "";
@@ -39,9 +39,9 @@ static int fail(int code, const char* fmt, ...) {
 
 // ------------------------------------------------------------------------------- geometry
 struct LaunchCfg {
-  int nw, depth, grid;
+  int slots, grid;   // ring slots (0 = as many as fit), CTAs (0 = one per SM)
 };
-static LaunchCfg g_cfg = {0, 0, 0};
+static LaunchCfg g_cfg = {0, 0};
 static std::once_flag g_cfg_once;
 
 static int env_int(const char* name, int dflt) {
@@ -49,8 +49,7 @@ static int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 static void cfg_from_env() {
-  g_cfg.nw = env_int("FSVD_NW", 8);
-  g_cfg.depth = env_int("FSVD_DEPTH", 16);
+  g_cfg.slots = env_int("FSVD_SLOTS", 0);
   g_cfg.grid = env_int("FSVD_GRID", 0);
 }
 static LaunchCfg current_cfg() {
@@ -87,7 +86,7 @@ static const KernelEntry* const g_kernel_tables[] = {g_kernels_bf16, g_kernels_f
 // Resolved launch: kernel + geometry for a given dtype / batch.
 struct Resolved {
   LaunchFn fn = nullptr;
-  int nw = 0, depth = 0, grid = 0, smem_optin = 0;
+  int grid = 0, smem_optin = 0, max_slots = 0;
 };
 
 static int resolve(int dtype, int B, Resolved& r) {
@@ -98,18 +97,54 @@ static int resolve(int dtype, int B, Resolved& r) {
   if (B < 1 || B > bmax) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..%d)", B, bmax);
   r.grid = c.grid > 0 ? (c.grid < p.sms ? c.grid : p.sms) : p.sms;
   r.smem_optin = p.smem_optin;
-  const KernelEntry* best = nullptr;
-  for (int pass = 0; pass < 2 && !best; ++pass)
-    for (const KernelEntry* tab : g_kernel_tables)
-      for (const KernelEntry* kp = tab; kp->fn; ++kp) {
-        if (kp->dtype != dtype) continue;
-        if (pass == 0 && (kp->nw != c.nw || kp->depth != c.depth)) continue;
-        if (!best) best = kp;
-      }
-  if (!best) return fail(FSVD_ERR_UNSUPPORTED, "no kernel variant for dtype %d", dtype);
-  r.fn = best->fn;
-  r.nw = best->nw;
-  r.depth = best->depth;
+  r.max_slots = c.slots > 0 ? c.slots : kMaxSlots;
+  for (const KernelEntry* tab : g_kernel_tables)
+    for (const KernelEntry* kp = tab; kp->fn; ++kp)
+      if (kp->dtype == dtype && !r.fn) r.fn = kp->fn;
+  if (!r.fn) return fail(FSVD_ERR_UNSUPPORTED, "no kernel for dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------- TMA descriptors
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+static_assert(sizeof(CUtensorMap) == 128, "TMA descriptor size");
+
+// Descriptor of a row-major [rows, cols] matrix with row stride ldw elements, read in boxes of
+// kUnitRows rows x kBoxRowBytes bytes; rows and columns outside the matrix read as zeros.
+static int encode_map(unsigned char* out, int dtype, const void* base, long long rows, long long cols,
+                      long long ldw) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  const int esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
+  if (rows < 1 || cols < 1) return fail(FSVD_ERR_ARG, "empty factor matrix");
+  if ((ldw * esize) % 16 || (reinterpret_cast<uintptr_t>(base) & 15))
+    return fail(FSVD_ERR_ALIGN, "factor rows must start on 16-byte boundaries");
+  CUtensorMap tm;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ldw * esize};
+  cuuint32_t box[2] = {(cuuint32_t)(kBoxRowBytes / esize), (cuuint32_t)kUnitRows};
+  cuuint32_t es[2] = {1, 1};
+  const CUresult r = enc(&tm, dtype == FSVD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                         2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  memcpy(out, &tm, 128);
   return 0;
 }
 
@@ -148,36 +183,63 @@ static WsLayout ws_layout(const fsvd_dims& D) {
 }
 
 // ------------------------------------------------------------------------------- builder
+struct MapPair {
+  unsigned char m[2][128];
+};
+
 struct Builder {
   std::vector<Stage> st;
-  int grid, NW, TW, CB, B, esize, depth;
+  std::vector<MapPair> maps;   // TMA descriptors of st[i] (zeros for stages without factors)
+  int grid, TW, B, esize, dtype, boxcols, max_slots;
   long long cum_units = 0;   // GEMV units handed out so far (rotates the unit -> CTA map)
   long long cum_items = 0;   // attention items handed out so far (item -> warp map)
-  int max_vec = 8;
+  int max_vec = 8;           // elements of the staged vector a lane may touch, per batch row
+  int err = 0;               // first error of gemv()
 
-  Builder(const Resolved& r, int dtype, int B_) {
+  Builder(const Resolved& r, int dtype_, int B_) {
     grid = r.grid;
-    NW = r.nw;
-    depth = r.depth;
-    TW = r.grid * r.nw;
+    TW = r.grid * kConsumerWarps;
+    dtype = dtype_;
     esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
-    CB = 64 / esize;   // columns of one block: 4 lanes x 16 bytes
+    boxcols = kBoxRowBytes / esize;
     B = B_;
+    max_slots = r.max_slots;
   }
   Stage blank() {
     Stage s;
     memset(&s, 0, sizeof(s));
     s.B = B;
     s.segs = 1;
+    s.cps = 1;
     return s;
   }
-  void finish_items(Stage& s, long long items) {   // ST_ATTN
-    s.rot = (int)(cum_items % TW);
-    cum_items += items;
+  void push(const Stage& s) {
+    st.push_back(s);
+    MapPair z;
+    memset(&z, 0, sizeof(z));
+    maps.push_back(z);
   }
-  // GEMV stage.  Units (8 rows x one K segment) go round-robin to the CTAs; with split_k the K
-  // range is cut into the smallest number of segments that loads the CTAs evenly (>= 90 %).
-  Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k) {
+  // ST_ATTN: CTAs per head group (a head group = 1 query head, or 2 that share a kv head) and
+  // the rotation of the slice -> CTA map.  Every CTA cuts its part of the keys into 8 splits.
+  bool has_attn = false;
+  int attn_rec_floats = 0;
+  void attn_geometry(Stage& s) {
+    const int G = s.H / s.Hk, GI = (G % 2 == 0) ? 2 : 1;
+    const long long groups = (long long)s.B * s.H / GI;
+    int cph = (int)(grid / (groups > 0 ? groups : 1));
+    if (cph < 1) cph = 1;
+    if (cph > kMaxSplit / kConsumerWarps) cph = kMaxSplit / kConsumerWarps;
+    s.nsplit = cph * kConsumerWarps;
+    s.rot = (int)(cum_items % grid);
+    cum_items += groups * cph;
+    has_attn = true;
+    const int need = kConsumerWarps * GI * (s.Dh + 2);
+    if (need > attn_rec_floats) attn_rec_floats = need;
+  }
+  // GEMV stage.  Units (16 rows x one K segment) go round-robin to the CTAs; with split_k the K
+  // range is cut into the number of segments (<= kMaxSegs) that gives the busiest CTA the fewest
+  // boxes.  rows_total: rows of the matrices behind WA (and WB) that the descriptors may read.
+  Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k, int rope_half = 0) {
     Stage s = blank();
     s.type = ST_GEMV;
     s.WA = WA;
@@ -185,52 +247,43 @@ struct Builder {
     s.P = P;
     s.K = K;
     s.ldw = ldw;
-    const int groups = (P + kRowsPerTile - 1) / kRowsPerTile;
-    const int kalign = K >= 4 * CB * NW ? CB * NW : CB;   // whole blocks for every warp if K allows
-    int best_segs = 1, best_kseg = (K + kalign - 1) / kalign * kalign;
+    s.rope_half = rope_half;
+    const int groups = (P + kUnitRows - 1) / kUnitRows;
+    const int nchunks = (K + boxcols - 1) / boxcols;
+    int best_segs = 1, best_cps = nchunks;
     if (split_k) {
-      double best_eff = 0;
-      for (int segs = 1; segs <= kMaxSegs; ++segs) {
-        int kseg = (K + segs - 1) / segs;
-        kseg = (kseg + kalign - 1) / kalign * kalign;
-        const int real = (K + kseg - 1) / kseg;
+      long long best_cost = -1;
+      for (int segs = 1; segs <= kMaxSegs && segs <= nchunks; ++segs) {
+        const int cps = (nchunks + segs - 1) / segs;
+        const int real = (nchunks + cps - 1) / cps;
         if (real != segs) continue;
         const long long units = (long long)groups * real;
-        const double eff = (double)units / (double)(((units + grid - 1) / grid) * grid);
-        if (eff > best_eff + 1e-9) {
-          best_eff = eff;
+        // time of the busiest CTA's boxes at an SM's share of HBM bandwidth (44 bytes/ns), plus
+        // the time every CTA of the next stage spends reading `real` partial vectors from L2
+        // (4 bytes/ps over the whole GPU)
+        const long long cost = ((units + grid - 1) / grid) * cps * (kBoxBytes / 44) +
+                               (long long)real * P * 4 * grid / 4000;
+        if (best_cost < 0 || cost < best_cost) {
+          best_cost = cost;
           best_segs = real;
-          best_kseg = kseg;
+          best_cps = cps;
         }
-        if (eff >= 0.9) break;
       }
     }
     s.segs = best_segs;
-    s.kseg = best_kseg;
-    {
-      // warps per unit: long slices amortise the per-unit work, more unit slots keep all warps
-      // busy; cost in block-equivalents, ~6 for switching unit or operand
-      const long long units = (long long)groups * best_segs;
-      const int nu = (int)((units + grid - 1) / grid);
-      const int nblk = ((best_kseg < K ? best_kseg : K) + CB - 1) / CB;
-      const int nops = WB ? 2 : 1;
-      long long best_cost = -1;
-      for (int ks = 1; ks <= NW; ks *= 2) {
-        const int slots = NW / ks;
-        const long long rounds = (nu + slots - 1) / slots;
-        const int bps = (nblk + ks - 1) / ks;
-        // time of the busiest warp in padded blocks (+2 per run for its switch); all warps wait
-        // for it, so this also rewards an even spread of the units over the warps
-        const long long cost = rounds * nops * ((bps + depth - 1) / depth * depth + 2);
-        if (best_cost < 0 || cost < best_cost) {
-          best_cost = cost;
-          s.ksplit = ks;
-        }
-      }
-    }
+    s.cps = best_cps;
+    s.kseg = best_cps * boxcols;
     s.rot = (int)(cum_units % grid);
     cum_units += (long long)groups * best_segs;
-    st.push_back(s);
+    push(s);
+    // rows behind the pointers: a rotary stage reads physical rows [0, 2P) through WA and
+    // [half, 2P) through WB = WA + half rows
+    const long long rowsA = rope_half > 0 ? 2ll * P : P;
+    const long long rowsB = rope_half > 0 ? 2ll * P - rope_half : P;
+    if (rope_half > 0 && rope_half % kUnitRows && !err)
+      err = fail(FSVD_ERR_UNSUPPORTED, "head_dim/2 = %d must be a multiple of %d", rope_half, kUnitRows);
+    if (!err) err = encode_map(maps.back().m[0], dtype, WA, rowsA, K, ldw);
+    if (!err && WB) err = encode_map(maps.back().m[1], dtype, WB, rowsB, K, ldw);
     return st.back();
   }
   // Input vector of the stage just appended (s must be st.back()).  `barrier`: the vector is
@@ -250,64 +303,45 @@ struct Builder {
   }
   int last() const { return (int)st.size() - 1; }
 
-  static long long stage_bytes(const Stage& s, int esize) {
-    if (s.type != ST_GEMV) return 0;
-    return (long long)s.P * s.K * esize * (s.WB ? 2 : 1);
-  }
-  // Decide which later stages each stage prefetches into L2: every GEMV stage is prefetched
-  // once, as early as possible while the bytes prefetched but not yet consumed stay in budget.
-  void plan_prefetch() {
-    const long long budget = (long long)env_int("FSVD_PF_MB", 48) << 20;
-    const int n = (int)st.size();
-    if (budget <= 0) {
-      for (Stage& s : st) s.pf_begin = s.pf_end = 0;
-      return;
-    }
-    std::vector<int> by(n, -1);
-    int next = 1;
-    long long outstanding = 0;
-    for (int s = 0; s < n; ++s) {
-      if (by[s] >= 0) outstanding -= stage_bytes(st[s], esize);   // s is being consumed now
-      if (next <= s) next = s + 1;
-      st[s].pf_begin = next;
-      while (next < n) {
-        const long long b = stage_bytes(st[next], esize);
-        if (b > 0 && outstanding + b > budget && next > s + 1) break;
-        by[next] = s;
-        outstanding += b;
-        ++next;
-        if (b > 0 && outstanding > budget) break;
-      }
-      st[s].pf_end = next;
-      if (st[s].type != ST_GEMV) st[s].pf_begin = st[s].pf_end = 0;   // only GEMV stages prefetch
-    }
-    // stages skipped because a non-GEMV stage "owned" them are picked up by the next GEMV stage
-    int covered = 1;
-    for (int s = 0; s < n; ++s) {
-      if (st[s].type != ST_GEMV) continue;
-      if (st[s].pf_begin > covered) st[s].pf_begin = covered > s + 1 ? covered : s + 1;
-      if (st[s].pf_end < st[s].pf_begin) st[s].pf_end = st[s].pf_begin;
-      if (st[s].pf_end > covered) covered = st[s].pf_end;
-    }
-  }
-  // Shared memory the program needs beyond the header: warps' partial sums and the staged vector.
+  // Shared memory the program needs beyond the header and the ring: warps' partial sums and the
+  // staged vector.
   int part_bytes() const {
     long long mx = 0;
     for (const Stage& s : st) {
       if (s.type != ST_GEMV) continue;
-      const long long units = (long long)((s.P + kRowsPerTile - 1) / kRowsPerTile) * s.segs;
+      const long long units = (long long)((s.P + kUnitRows - 1) / kUnitRows) * s.segs;
       const long long nu = (units + grid - 1) / grid;
-      const long long b = nu * (s.WB ? 2 : 1) * (s.ksplit > 0 ? s.ksplit : NW) * 64 * 4;
+      const long long kk = s.cps < kConsumerWarps ? s.cps : kConsumerWarps;
+      const long long b = nu * (s.WB ? 2 : 1) * kk * kUnitRows * B * 4;
       if (b > mx) mx = b;
     }
+    if (has_attn && (long long)attn_rec_floats * 4 > mx) mx = (long long)attn_rec_floats * 4;
     return (int)((mx + 255) / 256 * 256);
   }
-  int xstride() const { return (max_vec + 7) / 8 * 8; }
-  // staged vector plus slack: the activation loads of a run's padding blocks run up to one
-  // round past the K range
-  int vec_bytes() const { return (B * xstride() * esize + depth * 64 + 128 + 15) / 16 * 16; }
-  size_t smem_bytes() const {
-    return (size_t)smem_header_bytes() + part_bytes() + vec_bytes();
+  // Row stride of the staged vector: the longest vector, or the furthest column a box of a K
+  // segment can reach (boxes run past K in whole boxes and read zeros from the factor side).
+  int xstride() const {
+    long long mx = max_vec;
+    for (const Stage& s : st) {
+      if (s.type != ST_GEMV) continue;
+      const long long reach = (long long)(s.xA_off > s.xB_off ? s.xA_off : s.xB_off) + (long long)s.segs * s.cps * boxcols;
+      if (reach > mx) mx = reach;
+    }
+    return (int)((mx + 7) / 8 * 8) + 8;   // + 16 bytes so that batch rows start in different banks
+  }
+  int vec_bytes() const { return (B * xstride() * esize + 15) / 16 * 16; }
+  // Ring slots: as many as fit beside the rest; a multiple of the consumer warps, or fewer than
+  // that when a huge input vector leaves less room (then one warp per slot works).
+  int nslots(int smem_optin) const {
+    const long long rest = (long long)smem_optin - smem_header_bytes() - part_bytes() - vec_bytes();
+    long long n = rest / kBoxBytes;
+    if (n > max_slots) n = max_slots;
+    if (n > kMaxSlots) n = kMaxSlots;
+    if (n >= kConsumerWarps) n = n / kConsumerWarps * kConsumerWarps;
+    return n < 0 ? 0 : (int)n;
+  }
+  size_t smem_bytes(int slots) const {
+    return (size_t)smem_header_bytes() + (size_t)slots * kBoxBytes + part_bytes() + vec_bytes();
   }
 };
 
@@ -324,7 +358,7 @@ static int check_dims(const fsvd_dims& D) {
   for (int v : m8)
     if (v <= 0 || v % 8) return fail(FSVD_ERR_ALIGN, "sizes and ranks must be positive multiples of 8 (got %d)", v);
   if (D.S_max < 1) return fail(FSVD_ERR_ARG, "S_max=%d", D.S_max);
-  if ((size_t)D.B * D.Hk * 4 > kCounterBytes) return fail(FSVD_ERR_UNSUPPORTED, "B*Hk=%d too large", D.B * D.Hk);
+  if ((size_t)D.B * D.H * 4 > kCounterBytes) return fail(FSVD_ERR_UNSUPPORTED, "B*H=%d too large", D.B * D.H);
   return 0;
 }
 
@@ -362,7 +396,7 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
   const int segs1 = b.st.back().segs;
   {  // 2. lift q with rotary
     Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
-                      D.H * half, D.Rq, D.Rq, false);
+                      D.H * half, D.Rq, D.Rq, false, half);
     b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
     s.rope_half = half;
     s.xA_off = s.xB_off = 0;
@@ -373,7 +407,7 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
   }
   {  // 3. lift k with rotary into the cache
     Stage& s = b.gemv(Lw.k_u, reinterpret_cast<const char*>(Lw.k_u) + (size_t)half * D.Rk * b.esize,
-                      D.Hk * half, D.Rk, D.Rk, false);
+                      D.Hk * half, D.Rk, D.Rk, false, half);
     s.rope_half = half;
     s.xA_off = s.xB_off = D.Rq;
     s.epi = EPI_ROPE_K;
@@ -404,12 +438,8 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     s.counters = reinterpret_cast<int*>(ws + L.counters);
     s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
     s.scale = 1.0f / sqrtf((float)D.Dh);
-    int ns = b.TW / imax(1, D.B * D.Hk);
-    if (ns < 1) ns = 1;
-    if (ns > kMaxSplit) ns = kMaxSplit;
-    s.nsplit = ns;
-    b.finish_items(s, (long long)D.B * D.Hk * ns);
-    b.st.push_back(s);
+    b.attn_geometry(s);
+    b.push(s);
     b.need_barrier(b.st.back());
   }
   {  // 6. o rank projection
@@ -475,29 +505,49 @@ static int check_layer_ptrs(const fsvd_layer& Lw) {
   return 0;
 }
 
-static int check_units(const Builder& b) {
-  for (const Stage& s : b.st) {
-    if (s.type != ST_GEMV) continue;
-    const long long units = (long long)((s.P + kRowsPerTile - 1) / kRowsPerTile) * s.segs;
-    if ((units + b.grid - 1) / b.grid > 64)
-      return fail(FSVD_ERR_UNSUPPORTED, "a stage of %d rows has more than 64 units per CTA", s.P);
-  }
+// Shared-memory plan of a finished program: ring slots and total bytes.
+static int plan_smem(const Resolved& r, const Builder& b, int& slots, size_t& smem) {
+  if (b.err) return b.err;
+  slots = b.nslots(r.smem_optin);
+  if (slots < 1)
+    return fail(FSVD_ERR_UNSUPPORTED,
+                "shared memory: %d bytes of partial sums and %d bytes of input vector leave no room for the ring (%d available)",
+                b.part_bytes(), b.vec_bytes(), r.smem_optin);
+  smem = b.smem_bytes(slots);
+  if (env_int("FSVD_SMEM_MAX", 0)) smem = (size_t)r.smem_optin;   // experiment: largest carve-out
   return 0;
 }
 
 static int launch_small(const Resolved& r, Builder& b, SyncState* sync, cudaStream_t stream) {
   if ((int)b.st.size() > kMaxSmallStages) return fail(FSVD_ERR_UNSUPPORTED, "program too long");
-  if (int e = check_units(b)) return e;
-  b.plan_prefetch();
-  const size_t smem = b.smem_bytes();
-  if (smem > (size_t)r.smem_optin)
-    return fail(FSVD_ERR_UNSUPPORTED, "%zu bytes of shared memory needed, %d available", smem, r.smem_optin);
+  int slots = 0;
+  size_t smem = 0;
+  if (int e = plan_smem(r, b, slots, smem)) return e;
   SmallProgram sp;
+  SmallMaps sm;
   memset(&sp, 0, sizeof(sp));
-  for (size_t i = 0; i < b.st.size(); ++i) sp.st[i] = b.st[i];
-  unsigned long long* tr = g_trace_bytes >= b.st.size() * (size_t)r.grid * 128 ? g_trace : nullptr;
-  cudaError_t e = r.fn(nullptr, &sp, 1, (int)b.st.size(), sync, b.xstride(), b.part_bytes(), b.vec_bytes(), tr, r.grid,
-                       smem, stream);
+  memset(&sm, 0, sizeof(sm));
+  for (size_t i = 0; i < b.st.size(); ++i) {
+    sp.st[i] = b.st[i];
+    memcpy(sm.m[2 * i], b.maps[i].m[0], 128);
+    memcpy(sm.m[2 * i + 1], b.maps[i].m[1], 128);
+  }
+  LaunchArgs a;
+  memset(&a, 0, sizeof(a));
+  a.small = &sp;
+  a.small_maps = &sm;
+  a.nstages = (int)b.st.size();
+  a.sync = sync;
+  a.xstride = b.xstride();
+  a.part_bytes = b.part_bytes();
+  a.vec_bytes = b.vec_bytes();
+  a.nslots = slots;
+  a.window = env_int("FSVD_QUIET", 0);
+  a.trace = g_trace_bytes >= b.st.size() * (size_t)r.grid * 128 ? g_trace : nullptr;
+  a.grid = r.grid;
+  a.smem = smem;
+  a.stream = stream;
+  cudaError_t e = r.fn(a);
   if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   g_launches.fetch_add(1);
   return 0;
@@ -526,10 +576,9 @@ int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes) {
 
 int fsvd_set_launch_config(int warps, int depth, int grid) {
   current_cfg();
-  if (warps != 8 && warps != 16) return fail(FSVD_ERR_ARG, "warps must be 8 or 16");
-  if (depth < 1) return fail(FSVD_ERR_ARG, "depth must be >= 1");
-  g_cfg.nw = warps;
-  g_cfg.depth = depth;
+  if (warps != 0 && warps != kConsumerWarps) return fail(FSVD_ERR_ARG, "warps must be 0 or %d", kConsumerWarps);
+  if (depth < 0) return fail(FSVD_ERR_ARG, "depth (ring slots) must be >= 0");
+  g_cfg.slots = depth;
   g_cfg.grid = grid < 0 ? 0 : grid;
   return 0;
 }
@@ -712,7 +761,7 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
   }
   const int segs = b.st.back().segs;
   {
-    Stage& s = b.gemv(q_u, reinterpret_cast<const char*>(q_u) + (size_t)half * Rq * b.esize, H * half, Rq, Rq, false);
+    Stage& s = b.gemv(q_u, reinterpret_cast<const char*>(q_u) + (size_t)half * Rq * b.esize, H * half, Rq, Rq, false, half);
     b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, true);
     s.rope_half = half;
     s.epi = EPI_ROPE_Q;
@@ -722,7 +771,7 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
     s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
   }
   {
-    Stage& s = b.gemv(k_u, reinterpret_cast<const char*>(k_u) + (size_t)half * Rk * b.esize, Hk * half, Rk, Rk, false);
+    Stage& s = b.gemv(k_u, reinterpret_cast<const char*>(k_u) + (size_t)half * Rk * b.esize, Hk * half, Rk, Rk, false, half);
     s.rope_half = half;
     s.xA_off = s.xB_off = Rq;
     s.epi = EPI_ROPE_K;
@@ -769,12 +818,8 @@ int fsvd_flash_decode(const void* q, const void* k_cache, const void* v_cache,
   s.counters = reinterpret_cast<int*>(w + L.counters);
   s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
   s.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)Dh);
-  int ns = b.TW / imax(1, B * Hk);
-  if (ns < 1) ns = 1;
-  if (ns > kMaxSplit) ns = kMaxSplit;
-  s.nsplit = ns;
-  b.finish_items(s, (long long)B * Hk * ns);
-  b.st.push_back(s);
+  b.attn_geometry(s);
+  b.push(s);
   return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
@@ -804,7 +849,8 @@ struct fsvd_model {
   WsLayout L;
   char* ws = nullptr;
   Stage* prog = nullptr;
-  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0;
+  unsigned char* maps = nullptr;   // TMA descriptors, 2 x 128 bytes per stage
+  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0, nslots = 0;
   size_t smem = 0;
   int* tokens = nullptr;
   int* seqlens = nullptr;
@@ -874,7 +920,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     s.flags = SF_OUT_T;
     s.tokens = m->tokens;
     s.vocab = D.vocab;
-    b.st.push_back(s);
+    b.push(s);
   }
   for (int l = 0; l < D.n_layers; ++l) {
     LayerIO io = {xbuf, true, xbuf, m->seqlens, cos_tab, sin_tab};
@@ -900,32 +946,29 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     s.step_counter = m->step_counter;
     s.seqlens_rw = m->seqlens;
     s.max_steps = max_steps;
-    b.st.push_back(s);
+    b.push(s);
     b.need_barrier(b.st.back());
   }
-  if (int e = check_units(b)) {
+  if (int e = plan_smem(m->r, b, m->nslots, m->smem)) {
     cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); delete m;
     return e;
   }
-  b.plan_prefetch();
   m->nstages = (int)b.st.size();
   m->xstride = b.xstride();
   m->part_bytes = b.part_bytes();
   m->vec_bytes = b.vec_bytes();
-  m->smem = b.smem_bytes();
+  static_assert(sizeof(MapPair) == 256, "two descriptors per stage");
   ce = cudaMalloc(&m->prog, sizeof(Stage) * b.st.size());
+  if (ce == cudaSuccess) ce = cudaMalloc(&m->maps, sizeof(MapPair) * b.maps.size());
   if (ce == cudaSuccess)
     ce = cudaMemcpy(m->prog, b.st.data(), sizeof(Stage) * b.st.size(), cudaMemcpyHostToDevice);
+  if (ce == cudaSuccess)
+    ce = cudaMemcpy(m->maps, b.maps.data(), sizeof(MapPair) * b.maps.size(), cudaMemcpyHostToDevice);
   if (ce != cudaSuccess) {
-    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); cudaFree(m->prog); delete m;
+    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); cudaFree(m->prog); cudaFree(m->maps); delete m;
     return fail(FSVD_ERR_CUDA, "uploading the stage program failed: %s", cudaGetErrorString(ce));
   }
   m->xbuf = xbuf;
-  if (m->smem > (size_t)m->r.smem_optin) {
-    const size_t need = m->smem;
-    fsvd_model_destroy(m);
-    return fail(FSVD_ERR_UNSUPPORTED, "%zu bytes of shared memory needed", need);
-  }
   *out = m;
   return 0;
 }
@@ -935,6 +978,7 @@ int fsvd_model_destroy(fsvd_model* m) {
   cudaFree(m->ws);
   cudaFree(m->extra);
   cudaFree(m->prog);
+  cudaFree(m->maps);
   cudaFree(m->xbuf);
   delete m;
   return 0;
@@ -944,9 +988,22 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
   SyncState* sync = reinterpret_cast<SyncState*>(m->ws + m->L.sync);
   for (int i = 0; i < n_steps; ++i) {
-    unsigned long long* tr = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
-    cudaError_t e = m->r.fn(m->prog, nullptr, 0, m->nstages, sync, m->xstride, m->part_bytes, m->vec_bytes, tr,
-                            m->r.grid, m->smem, (cudaStream_t)stream);
+    LaunchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.prog = m->prog;
+    a.maps = m->maps;
+    a.nstages = m->nstages;
+    a.sync = sync;
+    a.xstride = m->xstride;
+    a.part_bytes = m->part_bytes;
+    a.vec_bytes = m->vec_bytes;
+    a.nslots = m->nslots;
+    a.window = env_int("FSVD_QUIET", 0);
+      a.trace = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
+    a.grid = m->r.grid;
+    a.smem = m->smem;
+    a.stream = (cudaStream_t)stream;
+    cudaError_t e = m->r.fn(a);
     if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);
   }

@@ -5,39 +5,36 @@
 
 namespace {
 
-template <typename T, int NW, int D>
-cudaError_t launch_impl(const fsvd::Stage* prog, const fsvd::SmallProgram* small, int use_small,
-                        int nstages, fsvd::SyncState* sync, int xstride, int part_bytes, int vec_bytes,
-                        unsigned long long* trace, int grid, size_t smem, cudaStream_t stream) {
-  auto kern = fsvd::fsvd_decode_kernel<T, NW, D>;
+template <typename T>
+cudaError_t launch_impl(const LaunchArgs& a) {
+  auto kern = fsvd::fsvd_decode_kernel<T>;
   static size_t attr_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16) dev = 0;
-  if (smem > attr_smem[dev]) {
+  if (a.smem > attr_smem[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
     if (e != cudaSuccess) return e;
-    attr_smem[dev] = smem;
+    attr_smem[dev] = a.smem;
   }
-  static const fsvd::SmallProgram empty = {};
+  static const fsvd::SmallProgram empty_prog = {};
+  static const fsvd::SmallMaps empty_maps = {};
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(NW * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
+  cfg.gridDim = dim3(a.grid);
+  cfg.blockDim = dim3(fsvd::kThreads);
+  cfg.dynamicSmemBytes = a.smem;
+  cfg.stream = a.stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeCooperative;
   at[0].val.cooperative = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, prog, small ? *small : empty, use_small, nstages, sync,
-                            xstride, part_bytes, vec_bytes, trace);
+  return cudaLaunchKernelEx(&cfg, kern, a.prog, a.small ? *a.small : empty_prog, a.maps,
+                            a.small_maps ? *a.small_maps : empty_maps, a.small ? 1 : 0, a.nstages,
+                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.window, a.trace);
 }
 
 }  // namespace
 
-#define FSVD_K(NW, D) {FSVD_INST_DTYPE, NW, D, &launch_impl<FSVD_INST_T, NW, D>}
-
-extern const KernelEntry FSVD_INST_TABLE[] = {FSVD_K(8, 16), FSVD_K(8, 8), FSVD_K(8, 24),
-                                              FSVD_K(16, 8), {0, 0, 0, nullptr}};
+extern const KernelEntry FSVD_INST_TABLE[] = {{FSVD_INST_DTYPE, &launch_impl<FSVD_INST_T>}, {0, nullptr}};

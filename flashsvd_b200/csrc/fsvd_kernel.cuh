@@ -1,31 +1,28 @@
 // Persistent stage interpreter for single-token decode of low-rank (W = U·V) transformers.
 //
-// Launch geometry: one CTA per SM (cooperative launch), NW warps per CTA.  A GEMV stage is cut
-// into units of 8 factor rows x one K segment; units go round-robin to the CTAs and inside a
-// CTA the warps split the K range of every unit, so every warp of every SM streams factor bytes
-// in every stage.  A lane loads its 16-byte fragment of a factor row straight from global
-// memory into registers (ld.global.nc, D loads in flight per lane) and feeds it to the tensor
-// cores; the partial sums of the warps meet in shared memory, are added in warp order and the
-// stage's epilogue (RoPE + cache append, SiLU·up, residual, ...) runs on the result.
+// Launch geometry: one CTA per SM (cooperative launch), 7 consumer warps + 1 producer warp.
 //
-// The factors of a stage do not depend on the activations, so a warp issues its first D loads
-// before it waits for the grid barrier in front of the stage, and prefetches the rows it will
-// read in the following stage(s) into L2 (prefetch.global.L2): the HBM stream keeps running
-// while the CTAs synchronise.
+// Factor stream.  A GEMV stage is cut into units of 16 factor rows x one K segment; units go
+// round-robin to the CTAs.  A unit is a row of boxes, one box = 16 rows x 512 bytes (8 KB), and
+// the boxes of all GEMV stages of the program, in program order, form the CTA's box sequence.
+// The producer warps walk that sequence on their own: box number q goes into ring slot q % NS
+// with one cp.async.bulk.tensor (TMA) as soon as the slot's previous content has been released.
+// The factors do not depend on the activations, so the producers run ahead of the consumers by
+// the whole ring (up to 192 KB per SM), across stage boundaries and grid barriers: HBM keeps
+// streaming while the CTAs synchronise.  Slot s is always consumed by warp s % 7 (NS is a
+// multiple of 7) and always filled by producer lane s % 4, so every mbarrier sees its phases in
+// order from a single waiting thread or warp.
+// (Measured on B200: this ring with real lds + mma consumers streams 6.4-6.9 TB/s; a single
+// issuing thread tops out near 3.4 TB/s with 8 KB boxes, two reach the HBM limit.)
 //
-// (Measured on B200 before settling on this: per-warp shared-memory rings filled by
-// cp.async.bulk stall the issuing warp ~320 cycles per copy and deliver after ~1 us; rings
-// filled by 16-byte cp.async issue faster but still cost ~1700 cycles per 4 KB tile in issue,
-// wait and shared-memory reads.  Direct loads cost ~10 instructions per 512 bytes and reach
-// 6.5 TB/s with 8 warps x 16 loads in flight.)
-//
-// Arithmetic.  bf16: 8 factor rows x 32 columns are the B operand of two mma.sync.m16n8k16
-// (fp32 accumulate) and the staged activation vector the A operand, batch rows as M.  A dot
-// product does not care about the order of k, so lane (g, t) feeds the k-slots it owns with 8
-// consecutive columns: one 16-byte load of factor row g and one of activation row g.  The four
-// lanes of a quad cover 32 columns, the MMA adds them, and lane (g, t) holds the sums of
-// factor rows 2t, 2t+1 for batch row g: no unpacking, no shuffles.  fp32 (parity mode): lane
-// (g, t) multiplies 4 columns of row g with plain FMAs and the quad is reduced by shuffles.
+// Arithmetic.  bf16: a box is the A operand (16 rows) of mma.sync.m16n8k16, the staged
+// activation vector the B operand with the batch as N.  A dot product does not care about the
+// order of k, so lane (g, t) feeds the k-slots it owns with 8 consecutive columns: one 16-byte
+// shared-memory load of factor row g, one of row g + 8 and one of activation row g.  fp32
+// (parity mode): the same loads, plain FMAs and a quad reduction by shuffles.  A warp adds its
+// boxes of one (unit, operand) in registers and leaves the sum in shared memory; the sums of the
+// warps are added in a fixed order and the stage's epilogue (RoPE + cache append, SiLU·up,
+// residual, ...) runs on the result, so results do not depend on timing.
 //
 // All waits are bounded: a wait that runs out records an error code in SyncState::status and
 // the kernel carries on without waiting again, so a fault in the protocol ends in an error
@@ -43,7 +40,10 @@
 
 namespace fsvd {
 
-constexpr int kTileRows = 8;
+constexpr int kNWC = kConsumerWarps;
+constexpr int kNPROD = kProducerLanes;   // producer lanes; a power of two
+constexpr int kConsThreads = kNWC * 32;
+constexpr int kThreads = (kNWC + kProducerWarps) * 32;
 constexpr long long kWaitLimitClk = 4000000000ll;  // ~2 s of SM clocks
 
 // ----------------------------------------------------------------------------- PTX helpers
@@ -55,12 +55,19 @@ __device__ __forceinline__ unsigned long long gtimer() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+// Barrier of the consumer warps only (the producer warps never join it).
+__device__ __forceinline__ void cons_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -73,22 +80,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
+// One 2-D box of a tiled tensor map into shared memory; completion is counted on `bar`.
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int col, int row, uint32_t bar) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                         uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(col), "r"(row), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -109,27 +105,13 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
                : "r"(addr));
   return v;
 }
-__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_imm(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
+               : "r"(addr), "n"(OFF));
   return v;
-}
-// Byte offset of 16-byte chunk `chunk` of row `row` inside a slot whose rows are RB bytes long.
-template <int RB>
-__device__ __forceinline__ uint32_t slot_off(int row, int chunk) {
-  return (uint32_t)row * RB + (uint32_t)((chunk ^ ((row & 1) << 2)) << 4);
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -187,7 +169,8 @@ struct TT<float> {
     f[2] = __uint_as_float(v.z);
     f[3] = __uint_as_float(v.w);
   }
-};// ----------------------------------------------------------------------------- small helpers
+};
+// ----------------------------------------------------------------------------- small helpers
 __device__ __forceinline__ int phys_row(int rope_half, int p) {
   if (rope_half > 0) {
     const int h = p / rope_half;
@@ -225,9 +208,18 @@ struct EpiAux {
   float a0, a1;
   int pos;
 };
+// Cache positions seqlens[b] of the program's sequence-length array, read once per launch into
+// shared memory (the array only changes in the last stage of a step).
+struct PosCache {
+  const int* ptr;   // the array the cached values come from
+  const int* pos;   // shared memory, one entry per batch row
+};
+__device__ __forceinline__ int cached_pos(const PosCache& pc, const int* seqlens, int b) {
+  return seqlens == pc.ptr ? pc.pos[b] : seqlens[b];
+}
 
 template <typename T>
-__device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiAux& ax) {
+__device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiAux& ax, const PosCache pc) {
   using X = TT<T>;
   ax.a0 = ax.a1 = 0.f;
   ax.pos = 0;
@@ -241,12 +233,12 @@ __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiA
     case EPI_ROPE_K: {
       const int half = st.rope_half;
       const int j = p % half;
-      ax.pos = st.seqlens[b];
+      ax.pos = cached_pos(pc, st.seqlens, b);
       ax.a0 = X::ld(st.cos_tab, (size_t)ax.pos * half + j);
       ax.a1 = X::ld(st.sin_tab, (size_t)ax.pos * half + j);
     } break;
     case EPI_V:
-      ax.pos = st.seqlens[b];
+      ax.pos = cached_pos(pc, st.seqlens, b);
       break;
     default:
       break;
@@ -376,7 +368,8 @@ template <>
 __device__ __forceinline__ void ld_row<float, 2>(const void* base, size_t i, float* o) {
   const float2 v = __ldcg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(base) + i));
   o[0] = v.x; o[1] = v.y;
-}// ----------------------------------------------------------------------------- vector stage-in
+}
+// ----------------------------------------------------------------------------- vector stage-in
 template <typename T>
 __device__ __forceinline__ void st2(char* xvec, size_t i, float a, float b);
 template <>
@@ -476,11 +469,11 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
       trace_mark(trow, 4);
       ss = warp_sum(ss);
       if (lane == 0) red[warp] = ss;
-      __syncthreads();
+      cons_sync();
       float tot = 0.f;
       for (int i = 0; i < nwarps; ++i) tot += red[i];
       const float inv = rsqrtf(tot / (float)len + st.eps);
-      __syncthreads();
+      cons_sync();
       trace_mark(trow, 5);
       auto finish = [&](int u, const uint4& xr, const uint4& wr) {
         float f[VEC], g[VEC];
@@ -505,90 +498,9 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
       }
     }
   }
-}// ----------------------------------------------------------------------------- GEMV engine
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-// The same load under a predicate; the registers are zero when it is off.  Written as one asm
-// block: `pred ? load : 0` in C++ becomes a select on the loaded value, and the select makes the
-// warp wait for the load, which serialises all loads in flight (measured ~800 cycles per load).
-__device__ __forceinline__ uint4 ldg_stream_if(const void* p, bool pred) {
-  uint4 v;
-  asm volatile(
-      "{\n\t.reg .pred q;\n\t"
-      "setp.ne.u32 q, %5, 0;\n\t"
-      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
-      "@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-      : "=&r"(v.x), "=&r"(v.y), "=&r"(v.z), "=&r"(v.w)
-      : "l"(p), "r"((unsigned)pred));
-  return v;
-}
-// Refill of pipeline slot I while run `cur` is consumed (see gemv_stage): block b0 + I + D of
-// the current run when it exists (I < r1 also says the lane's columns are inside the K range),
-// else block I of the next run (I >= r2 and I < nl), else zeros.  Addresses are a base plus an
-// immediate, the predicates compare round counters with immediates: no per-block arithmetic.
-template <int I, int D>
-__device__ __forceinline__ uint4 ldg_refill(const char* pb, const char* pn, int r1, int r2, int nl) {
-  uint4 v;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.gt.s32 p, %6, %9;\n\t"          // I < r1
-      "setp.le.s32 q, %7, %9;\n\t"          // I >= r2
-      "setp.gt.and.s32 q, %8, %9, q;\n\t"   // ... and I < nl
-      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
-      "@p ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%10];\n\t"
-      "@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%5+%11];\n\t}"
-      : "=&r"(v.x), "=&r"(v.y), "=&r"(v.z), "=&r"(v.w)
-      : "l"(pb), "l"(pn), "r"(r1), "r"(r2), "r"(nl), "n"(I), "n"((I + D) * 64), "n"(I * 64));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ uint4 lds128_imm(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr), "n"(OFF));
-  return v;
-}
-__device__ __forceinline__ void prefetch_l2(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
-// One unit of a GEMV stage as this CTA sees it: 8 logical rows x one K segment.
-struct UnitInfo {
-  unsigned long long row_off;  // byte offset of the unit's first factor row
-  int p0, seg, kbeg, kend;
-  int nblk;                    // blocks (one 16-byte load per lane each) in [kbeg, kend)
-  int pad;
-};
-constexpr int kMaxUnitsPerCta = 64;
-
-__device__ __forceinline__ void bulk_prefetch_l2(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-// L2 prefetch of the whole factor matrices of stage `st`: every warp of the grid asks for one
-// contiguous share with a single bulk prefetch (per-line prefetches cost one LSU cycle per line,
-// as much as the loads themselves).
-template <typename T>
-__device__ __forceinline__ void prefetch_stage(const Stage& st, int gwarp, int gwarps, int lane) {
-  if (st.type != ST_GEMV || lane != 0) return;
-  const size_t pitch = (size_t)st.ldw * sizeof(T);
-  const size_t rows = st.rope_half > 0 ? (size_t)2 * st.P : (size_t)st.P;
-  const size_t total = rows * pitch;                       // multiple of 16
-  size_t share = (total / gwarps + 15) & ~(size_t)15;
-  if (share < 2048) share = 2048;
-  const size_t beg = (size_t)gwarp * share;
-  if (beg >= total) return;
-  const uint32_t n = (uint32_t)min(share, total - beg);
-  bulk_prefetch_l2(reinterpret_cast<const char*>(st.WA) + beg, n);
-  if (st.WB && st.rope_half == 0) bulk_prefetch_l2(reinterpret_cast<const char*>(st.WB) + beg, n);
-}
-
+// ----------------------------------------------------------------------------- waits
 // Grid barrier wait (one polling lane per CTA) in front of a stage with SF_BARRIER.
 __device__ __forceinline__ void barrier_wait(SyncState* sync, unsigned long long target, int s, int tid) {
   if (tid == 0) {
@@ -607,324 +519,425 @@ __device__ __forceinline__ void barrier_wait(SyncState* sync, unsigned long long
       }
     }
   }
-  __syncthreads();
+  cons_sync();
+}
+
+// Bounded wait on a ring mbarrier.  False: the wait ran out (recorded in SyncState::status) or
+// this CTA has already given up; the caller goes on without the data.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, SyncState* sync,
+                                          volatile int* giveup, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*giveup) return false;
+  const long long c0 = clock64();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 127u) == 0) {
+      if (*giveup) return false;
+      if (clock64() - c0 > kWaitLimitClk) {
+        atomicCAS(&sync->status, DS_OK, DS_COPY_TIMEOUT);
+        sync->status_detail = detail;
+        *giveup = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ----------------------------------------------------------------------------- GEMV engine
+// This CTA's share of a GEMV stage.  Unit j of the CTA is global unit first + j * grid =
+// (row group, K segment); its boxes are ordered operand-major, then by column chunk.
+struct BoxPlan {
+  int first, nu;   // first global unit, number of units of this CTA
+  int nops, cps;   // operands per unit, boxes per (unit, operand)
+  int nbox;        // nu * nops * cps
+};
+__device__ __forceinline__ BoxPlan plan_boxes(int P, int segs, int cps, int rot, bool two_ops, int cta, int grid) {
+  BoxPlan bp;
+  const int total = ((P + kUnitRows - 1) / kUnitRows) * segs;
+  bp.first = first_item(cta, rot % grid, grid);
+  bp.nu = bp.first < total ? (total - bp.first + grid - 1) / grid : 0;
+  bp.nops = two_ops ? 2 : 1;
+  bp.cps = cps;
+  bp.nbox = bp.nu * bp.nops * cps;
+  return bp;
+}
+
+struct Ring {
+  uint32_t full, empty;   // shared-memory addresses of the mbarrier arrays
+  uint32_t data;          // shared-memory address of slot 0
+  int ns;                 // slots, a multiple of kNWC (or fewer than kNWC)
+  int window;             // 1: producers pause while the consumers are in a latency-bound phase
+};
+
+// One lane of each producer warp: walks the CTA's box sequence of the whole program and issues
+// the TMA copy of every box that goes into a slot it owns (slot % kNPROD) as soon as the slot is
+// free.  Like the consumers, a producer sees the phases of "its" mbarriers in order.
+template <typename T>
+__device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, const unsigned char* maps,
+                                           const Ring rg, int which, SyncState* sync, volatile int* giveup) {
+  constexpr int BOXCOLS = kBoxRowBytes / (int)sizeof(T);
+  const int grid = gridDim.x, cta = blockIdx.x;
+  // Every lane waits only on the mbarriers of its own slots, whose phases it sees in order: a
+  // parity wait cannot tell phase k from phase k + 2, so a lane must never wait on a barrier that
+  // another lane may have advanced by more than one phase (that would block for ever).
+  // Quiet phases: while the consumers are in a latency-bound phase (epilogue stores, grid
+  // barrier, staging of the next input vector, attention) they raise giveup[3] and the producers
+  // stop issuing.  Measured on B200: with bulk copies saturating HBM every L2 round trip of those
+  // phases takes 1.5-2 us instead of 0.5 us, which costs more than the overlap gains.
+  unsigned seq = 0;
+  int slot = 0, round = 0;
+  const int quiet_mode = rg.window;      // 0: never pause
+  for (int s = 0; s < nstages; ++s) {
+    const Stage& st = prog[s];
+    if (st.type != ST_GEMV) continue;
+    const int segs = st.segs, cps = st.cps, half = st.rope_half;
+    const BoxPlan bp = plan_boxes(st.P, segs, cps, st.rot, st.WB != nullptr, cta, grid);
+    const unsigned char* mapA = maps + (size_t)(2 * s) * 128;
+    const unsigned char* mapB = mapA + 128;
+    for (int j = 0; j < bp.nu; ++j) {
+      const int uidx = bp.first + j * grid;
+      const int grp = uidx / segs, seg = uidx - grp * segs;
+      const int row = phys_row(half, grp * kUnitRows);
+      const int col0 = seg * cps * BOXCOLS;
+      for (int op = 0; op < bp.nops; ++op) {
+        const unsigned char* map = op ? mapB : mapA;
+        for (int c = 0; c < cps; ++c) {
+          if ((slot & (kNPROD - 1)) == which) {
+            const uint32_t fb = rg.full + slot * 8;
+            if (round > 0 && !mbar_wait(rg.empty + slot * 8, (uint32_t)(round - 1) & 1u, sync, giveup, s)) return;
+            if (quiet_mode && giveup[3]) {
+              const long long c0 = clock64();
+              while (giveup[3] && !giveup[0] && clock64() - c0 < kWaitLimitClk) __nanosleep(64);
+            }
+            mbar_expect_tx(fb, kBoxBytes);
+            tma_box_2d(rg.data + (uint32_t)slot * kBoxBytes, map, col0 + c * BOXCOLS, row, fb);
+            giveup[1 + (which & 1)] = (int)seq + 1;   // boxes issued so far (read by the stage timeline)
+          }
+          ++seq;
+          if (++slot == rg.ns) {
+            slot = 0;
+            ++round;
+          }
+        }
+      }
+    }
+  }
 }
 
 // Per-stage context handed to the stage functions.
 struct StageCtx {
-  const Stage* prog;
-  int s, nstages;
+  int s;
   SyncState* sync;
   unsigned long long bar_target;   // arrival count that opens this stage's barrier
   char* xvec;
   int xstride;
   float* red;
-  float* part;                     // partial sums: [unit ordinal][operand][k slice][batch 8][row 8]
-  UnitInfo* units;                 // this CTA's units of the stage
+  float* part;                     // partial sums: [unit ordinal * nops + operand][kk][batch][16 rows]
+  Ring ring;
+  unsigned seq_base;               // boxes of this CTA in the stages before this one
+  volatile int* giveup;
+  PosCache pc;
   unsigned long long* trow;
 };
 
-// A run: the blocks one warp streams for one (unit, operand): its K slice of 8 factor rows.
-// n / ui / g are warp-uniform, p / lim / xcol belong to the lane.
-struct Run {
-  const char* p;   // lane address of block 0 (factor row lane>>2, 16 bytes at column kcol)
-  int n;           // blocks in the run; 0 = no more runs
-  int lim;         // blocks whose 16 bytes of this lane lie inside the K range (ragged last block)
-  int xcol;        // the lane's activation column for block 0, operand offset included
-  int ui, g;       // unit ordinal of this CTA, operand group
-};
-
+// One GEMV stage, consumer warps.  Returns the number of boxes of this CTA in the stage.
 template <typename T>
-struct WarpGeo {
-  const char* W[2];
-  size_t pitch;
-  int xoff[2];
-  int nops, nu, P;
-  int ks, kslice, slot, nslots;   // warps per unit, this warp's K slice and unit slot
-  int qg, qt;
-};
-
-// Move `r` to the next (unit, operand) in which this warp owns blocks, starting the search at
-// (ui, g).  Units are visited slot, slot + nslots, ...; operands 0, 1 inside a unit.
-template <typename T>
-__device__ __forceinline__ void run_seek(const WarpGeo<T>& wg, const UnitInfo* units, Run& r, int ui, int g) {
-  constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
-  for (; ui < wg.nu; ui += wg.nslots, g = 0) {
-    const UnitInfo u = units[ui];
-    const int bps = (u.nblk + wg.ks - 1) / wg.ks;
-    const int j0 = wg.kslice * bps, j1 = min(u.nblk, j0 + bps);
-    if (j0 >= j1) continue;
-    // a row past the end of the matrix is replaced by the unit's first row; its sums land in
-    // accumulator columns that are never stored
-    const int row = (u.p0 + wg.qg < wg.P) ? wg.qg : 0;
-    const int kcol = u.kbeg + j0 * CB + wg.qt * VEC;
-    r.p = wg.W[g] + u.row_off + (size_t)row * wg.pitch + (size_t)kcol * sizeof(T);
-    r.n = j1 - j0;
-    r.lim = max(0, min(r.n, (u.kend - kcol + CB - 1) / CB));
-    r.xcol = wg.xoff[g] + kcol;
-    r.ui = ui;
-    r.g = g;
-    return;
-  }
-  r.n = 0;
-  r.lim = 0;
-  r.ui = wg.nu;
-  r.g = 0;
-}
-template <typename T>
-__device__ __forceinline__ void run_next(const WarpGeo<T>& wg, const UnitInfo* units, const Run& cur, Run& nxt) {
-  if (cur.n == 0) {
-    nxt = cur;
-    return;
-  }
-  if (cur.g + 1 < wg.nops) run_seek<T>(wg, units, nxt, cur.ui, cur.g + 1);
-  else run_seek<T>(wg, units, nxt, cur.ui + wg.nslots, 0);
-}
-
-// One GEMV stage, all warps of the CTA.
-//
-// Register pipeline: every run is padded to whole rounds of D blocks and slot s of buf[] holds
-// the block with index % D == s, so every index into buf[] is a compile-time constant and a
-// slot is always refilled with the block D ahead in the padded stream: block b + D of the run
-// being consumed or, in its last round, block s of the next run.
-template <typename T, int NW, int D>
-__device__ __noinline__ void gemv_stage(const Stage& st, const StageCtx& cx) {
+__device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
   using X = TT<T>;
-  constexpr int VEC = 16 / (int)sizeof(T), CB = 4 * VEC;
+  constexpr int BOXCOLS = kBoxRowBytes / (int)sizeof(T);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nthreads = NW * 32;
-  const int B = st.B;
-  const int grid = gridDim.x;
+  const int B = st.B, grid = gridDim.x, segs = st.segs;
+  const BoxPlan bp = plan_boxes(st.P, segs, st.cps, st.rot, st.WB != nullptr, blockIdx.x, grid);
+  const int cps = bp.cps, nops = bp.nops;
+  const int rowsB = kUnitRows * B;
 
-  const long long k0 = clock64();
-  // ---- 0. this CTA's units of the stage, computed once into shared memory
-  const int total_units = ((st.P + kTileRows - 1) / kTileRows) * st.segs;
-  const int first = first_item(blockIdx.x, st.rot % grid, grid);
-  const int nu = first < total_units ? min(kMaxUnitsPerCta, (total_units - first + grid - 1) / grid) : 0;
-  if (tid < nu) {
-    const int uidx = first + tid * grid;
-    UnitInfo u;
-    const int grp = uidx / st.segs;
-    u.seg = uidx - grp * st.segs;
-    u.p0 = grp * kTileRows;
-    u.kbeg = u.seg * st.kseg;
-    u.kend = min(st.K, u.kbeg + st.kseg);
-    u.nblk = (u.kend - u.kbeg + CB - 1) / CB;
-    u.row_off = (unsigned long long)phys_row(st.rope_half, u.p0) * st.ldw * sizeof(T);
-    u.pad = 0;
-    cx.units[tid] = u;
-  }
-  __syncthreads();
-
-  const long long k1 = clock64();
-  WarpGeo<T> wg;
-  wg.W[0] = reinterpret_cast<const char*>(st.WA);
-  wg.W[1] = reinterpret_cast<const char*>(st.WB);
-  wg.pitch = (size_t)st.ldw * sizeof(T);
-  wg.xoff[0] = st.xA_off;
-  wg.xoff[1] = st.xB_off;
-  wg.nops = st.WB ? 2 : 1;
-  wg.nu = nu;
-  wg.P = st.P;
-  wg.ks = st.ksplit > 0 ? st.ksplit : NW;
-  wg.kslice = warp % wg.ks;
-  wg.slot = warp / wg.ks;
-  wg.nslots = NW / wg.ks;
-  wg.qg = lane >> 2;
-  wg.qt = lane & 3;
-  const UnitInfo* units = cx.units;
-
-  // operands of the epilogues this thread will run (outputs tid and tid + nthreads), fetched
-  // now so that their latency hides behind the streaming
-  const int nout = nu * kTileRows * B;
+  // operands of the epilogues this thread will run (outputs tid and tid + 256), fetched now so
+  // that their latency hides behind the barrier and the streaming
+  const int nout = bp.nu * rowsB;
+  auto out_pos = [&](int o, int& j, int& b, int& r, int& seg, int& p) {
+    j = o / rowsB;
+    const int rem = o - j * rowsB;
+    b = rem >> 4;
+    r = rem & 15;
+    const int uidx = bp.first + j * grid;
+    const int grp = uidx / segs;
+    seg = uidx - grp * segs;
+    p = grp * kUnitRows + r;
+  };
   EpiAux ax0, ax1;
   ax0.a0 = ax0.a1 = ax1.a0 = ax1.a1 = 0.f;
   ax0.pos = ax1.pos = 0;
-  auto out_pos = [&](int o, int& i, int& b, int& r) {
-    i = o / (kTileRows * B);
-    const int rem = o - i * (kTileRows * B);
-    b = rem / kTileRows;
-    r = rem - b * kTileRows;
-  };
   {
-    int i, b, r;
+    int j, b, r, seg, p;
     if (tid < nout) {
-      out_pos(tid, i, b, r);
-      const int p = cx.units[i].p0 + r;
-      if (p < st.P) epi_prefetch<T>(st, p, b, ax0);
+      out_pos(tid, j, b, r, seg, p);
+      if (p < st.P) epi_prefetch<T>(st, p, b, ax0, cx.pc);
     }
-    if (tid + nthreads < nout) {
-      out_pos(tid + nthreads, i, b, r);
-      const int p = cx.units[i].p0 + r;
-      if (p < st.P) epi_prefetch<T>(st, p, b, ax1);
+    if (tid + kConsThreads < nout) {
+      out_pos(tid + kConsThreads, j, b, r, seg, p);
+      if (p < st.P) epi_prefetch<T>(st, p, b, ax1, cx.pc);
     }
   }
-  // ---- 1. first loads of this warp, before any waiting
-  Run cur, nxt;
-  run_seek<T>(wg, units, cur, wg.slot, 0);
-  run_next<T>(wg, units, cur, nxt);
-  uint4 buf[D];
-#pragma unroll
-  for (int s = 0; s < D; ++s) buf[s] = ldg_stream_if(cur.p + s * 64, s < cur.lim);
-  const long long k2 = clock64();
-  // ---- 2. L2 prefetch of the stages the host assigned to this one
-  for (int t = st.pf_begin; t < st.pf_end; ++t)
-    prefetch_stage<T>(cx.prog[t], warp * grid + blockIdx.x, grid * NW, lane);
 
-  const long long k3 = clock64();
-  // ---- 3. wait for the producers of the input vector, stage it
+  trace_mark(cx.trow, 8);
+  // ---- wait for the producers of the input vector, stage it
   if (st.flags & SF_BARRIER) barrier_wait(cx.sync, cx.bar_target, cx.s, tid);
   trace_mark(cx.trow, 1);
   if (st.vl_mode != VL_NONE) {
-    stage_vector<T>(st, cx.xvec, cx.xstride, cx.red, tid, nthreads, cx.trow);
-    __syncthreads();
+    stage_vector<T>(st, cx.xvec, cx.xstride, cx.red, tid, kConsThreads, cx.trow);
+    cons_sync();
   }
   trace_mark(cx.trow, 2);
+  if (tid == 0) cx.giveup[3] = 0;   // quiet phase over: the producers may issue again
+  if (cx.trow) {
+    const int i0 = cx.giveup[1], i1 = cx.giveup[2];
+    cx.trow[14] = (unsigned long long)((i0 > i1 ? i0 : i1) - (int)cx.seq_base);   // boxes issued ahead
+    cx.trow[15] = (unsigned long long)bp.nbox;
+  }
 
-  const long long k4 = clock64();
-  // ---- 4. stream this warp's runs
-  const bool xact = wg.qg < B;
-  const uint32_t xvec_s = smem_u32(cx.xvec);
-  const uint32_t xlane_s = xvec_s + (uint32_t)(xact ? wg.qg : 0) * cx.xstride * (uint32_t)sizeof(T);
+  // ---- this warp's boxes: local box l belongs to warp (seq_base + l) % 8
+  const int g = lane >> 2, t = lane & 3;
   const uint32_t xrow_bytes = (uint32_t)cx.xstride * (uint32_t)sizeof(T);
-  while (cur.n > 0) {
-    float acc[2][4];
+  const uint32_t xvec_s = smem_u32(cx.xvec) + t * 16;
+  const uint32_t xlane_s = xvec_s + (uint32_t)(g < B ? g : 0) * xrow_bytes;
+  const uint32_t wlane = (uint32_t)g * kBoxRowBytes + t * 16;
+  // Box number q is consumed by warp q % step: step = 7 for a ring of 7, 14 or 21 slots; a ring
+  // of fewer than 7 slots (huge input vectors) has one warp per slot and leaves the others idle.
+  const int step = cx.ring.ns < kNWC ? cx.ring.ns : kNWC;
+  const int KK = cps < step ? cps : step;   // warps that hold partial sums of one (unit, operand)
+  int l = warp < step ? (warp - (int)(cx.seq_base % step) + step) % step : bp.nbox;
+  int slot, round;
+  {
+    const unsigned seq0 = cx.seq_base + (unsigned)l;
+    round = (int)(seq0 / (unsigned)cx.ring.ns);
+    slot = (int)(seq0 - (unsigned)round * cx.ring.ns);
+  }
+  int io = l / cps, c = l - io * cps;   // (unit ordinal * nops + operand), chunk inside it
+  int cur_io = -1, cur_kk = 0, xcol0 = 0;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};          // bf16: mma accumulators (rows g, g+8; batch 2t, 2t+1)
+  float accf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // fp32: [row half][batch]
+  auto flush = [&]() {
+    float* dst = cx.part + ((size_t)cur_io * KK + cur_kk) * rowsB;
+    if constexpr (sizeof(T) == 2) {
+      if (2 * t < B) {
+        dst[(2 * t) * 16 + g] = acc[0];
+        dst[(2 * t) * 16 + g + 8] = acc[2];
+      }
+      if (2 * t + 1 < B) {
+        dst[(2 * t + 1) * 16 + g] = acc[1];
+        dst[(2 * t + 1) * 16 + g + 8] = acc[3];
+      }
 #pragma unroll
-    for (int c = 0; c < 2; ++c)
+      for (int e = 0; e < 4; ++e) acc[e] = 0.f;
+    } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
-    const char* pb = cur.p;                  // lane address of block b0
-    const char* pn = nxt.p;
-    // activation bytes of block b0 for this lane; blocks past `lim` multiply zeros, their
-    // activation loads may run up to one block past the K range (the host pads the vector)
-    uint32_t xs = (sizeof(T) == 2 ? xlane_s : xvec_s) + (uint32_t)cur.xcol * (uint32_t)sizeof(T);
-    // A run is padded to a whole number of rounds of D blocks (the padding blocks load nothing
-    // and multiply zeros), so the block D ahead of block b0 + I is block b0 + I + D of this run
-    // or, in the last round, block I of the next one.
-    const int np = (cur.n + D - 1) / D * D;
-    int r1 = cur.lim - D, r2 = np - D;       // I < r1: own block b0+I+D holds data; I >= r2: next run's turn
-    const int nl = nxt.lim;
-
-    auto consume = [&](auto iconst, const uint4& wv) {
-      constexpr int I = decltype(iconst)::value;
-      if constexpr (sizeof(T) == 2) {
-        const uint4 xv = lds128_imm<I * 64>(xs);
-        mma_bf16_16816(acc[I & 1], xv.x, 0u, xv.y, 0u, wv.x, wv.y);
-        mma_bf16_16816(acc[(I & 1) ^ 1], xv.z, 0u, xv.w, 0u, wv.z, wv.w);
-      } else {
-        // fp32: 4 columns of factor row qg times activation rows 0..3; acc[0][b] per batch row
-        float wf[4], xf[4];
-        X::unpack(wv, wf);
+      for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int bb = 0; bb < 4; ++bb) {
-          if (bb < B) {
-            const uint4 xb = lds128_imm<I * 64>(xs + bb * xrow_bytes);
-            X::unpack(xb, xf);
+          float v = accf[h][bb];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          if (t == 0 && bb < B) dst[bb * 16 + g + 8 * h] = v;
+          accf[h][bb] = 0.f;
+        }
+    }
+  };
+  for (; l < bp.nbox; l += step) {
+    if (io != cur_io) {
+      if (cur_io >= 0) flush();
+      cur_io = io;
+      cur_kk = c % step;
+      const int j = nops == 2 ? (io >> 1) : io, op = nops == 2 ? (io & 1) : 0;
+      const int uidx = bp.first + j * grid;
+      const int seg = uidx % segs;
+      xcol0 = (op ? st.xB_off : st.xA_off) + seg * cps * BOXCOLS;
+    }
+    bool ok = mbar_wait(cx.ring.full + slot * 8, (uint32_t)round & 1u, cx.sync, cx.giveup, cx.s);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const uint32_t wb = cx.ring.data + (uint32_t)slot * kBoxBytes + wlane;
+      const uint32_t xoff = (uint32_t)(xcol0 + c * BOXCOLS) * (uint32_t)sizeof(T);
+      if constexpr (sizeof(T) == 2) {
+        const uint32_t xb = xlane_s + xoff;
+        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[0][bb] = fmaf(wf[e], xf[e], acc[0][bb]);
+        for (int q = 0; q < 8; ++q) {
+          const uint4 xv = lds128(xb + q * 64);
+          const uint4 lo = lds128(wb + q * 64);
+          const uint4 hi = lds128(wb + 8 * kBoxRowBytes + q * 64);
+          mma_bf16_16816(a0, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+          mma_bf16_16816(a1, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += a0[e] + a1[e];
+      } else {
+        const uint32_t xb = xvec_s + xoff;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float lo[4], hi[4], xf[4];
+          X::unpack(lds128(wb + q * 64), lo);
+          X::unpack(lds128(wb + 8 * kBoxRowBytes + q * 64), hi);
+#pragma unroll
+          for (int bb = 0; bb < 4; ++bb) {
+            if (bb < B) {
+              X::unpack(lds128(xb + bb * xrow_bytes + q * 64), xf);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                accf[0][bb] = fmaf(lo[e], xf[e], accf[0][bb]);
+                accf[1][bb] = fmaf(hi[e], xf[e], accf[1][bb]);
+              }
+            }
           }
         }
       }
-    };
-    for (int left = np; left > 0; left -= D) {
-      [&]<int... I>(std::integer_sequence<int, I...>) {
-        ((void)([&] {
-           const uint4 wv = buf[I];
-           buf[I] = ldg_refill<I, D>(pb, pn, r1, r2, nl);
-           consume(std::integral_constant<int, I>{}, wv);
-         }()),
-         ...);
-      }(std::make_integer_sequence<int, D>{});
-      pb += D * 64;
-      xs += D * 64;
-      r1 -= D;
-      r2 -= D;
     }
-    // publish the partial sums of this run
-    {
-      float* dst = cx.part + ((size_t)(cur.ui * wg.nops + cur.g) * wg.ks + wg.kslice) * 64;
-      if constexpr (sizeof(T) == 2) {
-        // lane (qg, qt): batch row qg, factor rows 2qt, 2qt+1
-        if (xact) {
-          dst[wg.qg * 8 + 2 * wg.qt] = acc[0][0] + acc[1][0];
-          dst[wg.qg * 8 + 2 * wg.qt + 1] = acc[0][1] + acc[1][1];
-        }
-      } else {
-        // quad reduction: lanes (qg, 0..3) hold 4 columns each of factor row qg
-#pragma unroll
-        for (int bb = 0; bb < 4; ++bb) {
-          float v = acc[0][bb];
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          if (wg.qt == bb && bb < B) dst[bb * 8 + wg.qg] = v;
-        }
-      }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(cx.ring.empty + slot * 8);
+    slot += step;
+    if (slot >= cx.ring.ns) {
+      slot -= cx.ring.ns;
+      ++round;
     }
-    cur = nxt;
-    run_next<T>(wg, units, cur, nxt);
+    c += step;
+    while (c >= cps) {
+      c -= cps;
+      ++io;
+    }
   }
+  if (cur_io >= 0) flush();
   trace_mark(cx.trow, 7);
-  const long long k5 = clock64();
-  __syncthreads();
-  const long long k6 = clock64();
+  cons_sync();
+  // every warp has consumed its boxes: the quiet phase begins (it ends when the next GEMV stage
+  // starts to consume)
+  if (tid == 0) cx.giveup[3] = 1;
+  trace_mark(cx.trow, 10);
 
-  // ---- 5. add the slices' partial sums in slice order and run the epilogue
-  for (int o = tid, it = 0; o < nout; o += nthreads, ++it) {
-    int i, b, r;
-    out_pos(o, i, b, r);
-    const UnitInfo u = units[i];
-    const int p = u.p0 + r;
+  // ---- add the warps' partial sums in chunk order and run the epilogue
+  for (int o = tid, it = 0; o < nout; o += kConsThreads, ++it) {
+    int j, b, r, seg, p;
+    out_pos(o, j, b, r, seg, p);
     if (p >= st.P) continue;
     EpiAux ax;
     if (it == 0) ax = ax0;
     else if (it == 1) ax = ax1;
-    else epi_prefetch<T>(st, p, b, ax);
-    const int bps = (u.nblk + wg.ks - 1) / wg.ks;
-    const int nsl = (u.nblk + bps - 1) / bps;   // slices that own blocks of this unit
-    float sum[2] = {0.f, 0.f};
-    for (int g = 0; g < wg.nops; ++g) {
-      const float* src = cx.part + ((size_t)(i * wg.nops + g) * wg.ks) * 64 + b * 8 + r;
-      float a = 0.f;
-      for (int w2 = 0; w2 < nsl; ++w2) a += src[w2 * 64];
-      sum[g] = a;
-    }
-    gemv_epilogue<T>(st, p, b, u.seg, sum[0], sum[1], ax);
+    else epi_prefetch<T>(st, p, b, ax, cx.pc);
+    const float* src = cx.part + ((size_t)(j * nops) * KK) * rowsB + b * 16 + r;
+    float sum0 = 0.f, sum1 = 0.f;
+    for (int k2 = 0; k2 < KK; ++k2) sum0 += src[(size_t)k2 * rowsB];
+    if (nops == 2)
+      for (int k2 = 0; k2 < KK; ++k2) sum1 += src[(size_t)(KK + k2) * rowsB];
+    gemv_epilogue<T>(st, p, b, seg, sum0, sum1, ax);
   }
-  if (cx.trow) {
-    cx.trow[8] = k1 - k0;
-    cx.trow[9] = k2 - k1;
-    cx.trow[10] = k3 - k2;
-    cx.trow[11] = k4 - k3;
-    cx.trow[12] = k5 - k4;
-    cx.trow[13] = k6 - k5;
-    cx.trow[14] = clock64() - k6;
-    cx.trow[15] = wg.ks;
-  }
+  trace_mark(cx.trow, 11);
+  return bp.nbox;
 }
 
 // ----------------------------------------------------------------------------- attention stage
-// One item = (batch row, kv head, key split).  Lane l owns dims [l*DPL, (l+1)*DPL) of the head.
-template <typename T, int G, int DPL>
-__device__ __noinline__ void attn_items(const Stage& st, int wrank, int total_warps, int lane) {
-  using X = TT<T>;
-  constexpr int UNR = (G * DPL >= 16) ? 4 : 8;  // keys in flight per warp, bounded by registers
-  const int Dh = st.Dh, Hk = st.Hk, H = st.H, nsplit = st.nsplit, B = st.B;
-  const int items = B * Hk * nsplit;
-  const size_t kv_row = (size_t)Hk * Dh;
-  const bool qT = (st.flags & SF_IN_T) != 0;
+// Raw cache row piece of one lane: DPL consecutive elements of type T, kept packed in registers
+// until they are used.
+template <typename T, int DPL>
+struct RawRow;
+template <>
+struct RawRow<__nv_bfloat16, 4> {
+  uint2 v;
+  __device__ __forceinline__ void load(const char* p, bool on) {
+    v = make_uint2(0u, 0u);
+    if (on) v = __ldcg(reinterpret_cast<const uint2*>(p));
+  }
+  __device__ __forceinline__ void unpack(float* o) const {
+    o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+    o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+};
+template <>
+struct RawRow<__nv_bfloat16, 2> {
+  uint32_t v;
+  __device__ __forceinline__ void load(const char* p, bool on) {
+    v = 0u;
+    if (on) v = __ldcg(reinterpret_cast<const uint32_t*>(p));
+  }
+  __device__ __forceinline__ void unpack(float* o) const {
+    o[0] = __uint_as_float(v << 16); o[1] = __uint_as_float(v & 0xffff0000u);
+  }
+};
+template <>
+struct RawRow<float, 4> {
+  float4 v;
+  __device__ __forceinline__ void load(const char* p, bool on) {
+    v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (on) v = __ldcg(reinterpret_cast<const float4*>(p));
+  }
+  __device__ __forceinline__ void unpack(float* o) const { o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+};
+template <>
+struct RawRow<float, 2> {
+  float2 v;
+  __device__ __forceinline__ void load(const char* p, bool on) {
+    v = make_float2(0.f, 0.f);
+    if (on) v = __ldcg(reinterpret_cast<const float2*>(p));
+  }
+  __device__ __forceinline__ void unpack(float* o) const { o[0] = v.x; o[1] = v.y; }
+};
 
-  for (int it = first_item(wrank, st.rot, total_warps); it < items; it += total_warps) {
-    const int sp = it % nsplit;
-    const int hk = (it / nsplit) % Hk;
-    const int b = it / (nsplit * Hk);
-    const int n = min(st.seqlens[b] + st.seqlen_add, st.S_max);
+// Attention of the new token over the dense cache, CTA-cooperative.
+//
+// A head group = GI query heads that share one kv head (GI = 1, or 2 when H/Hk is even).  Its keys
+// are cut into nsplit = cph * 8 splits: cph CTAs per head group, and in each of them the 8
+// consumer warps take one split each.  Lane l owns dims [l*DPL, (l+1)*DPL) of the head.  The
+// keys and values of a split are fetched in chunks of KMAX rows whose loads are all issued
+// before the first use (one memory round trip per chunk; a split of the benchmark shape is one
+// chunk); scores of a chunk are independent dot products and softmax runs once per chunk.
+// The 8 partial results of a CTA meet in shared memory and are merged in warp order.  With
+// cph == 1 that is the result; otherwise the CTA publishes its part and the last of the cph
+// CTAs to arrive (atomic counter) merges the parts in part order, so the result does not depend
+// on timing.
+template <typename T, int GI, int DPL>
+__device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCache pc) {
+  using X = TT<T>;
+  constexpr int KBASE = (GI == 1) ? 20 : 12;
+  constexpr int KMAX = sizeof(T) == 2 ? KBASE : KBASE / 2;   // rows in registers
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int Dh = st.Dh, H = st.H, B = st.B, grid = gridDim.x;
+  const int R = (H / st.Hk) / GI;          // head groups per kv head
+  const int Hg = st.Hk * R;                // head groups per batch row
+  const int nsplit = st.nsplit, cph = nsplit / kNWC;
+  const int nslice = B * Hg * cph;         // (batch row, head group, part)
+  const size_t kv_row = (size_t)st.Hk * Dh;
+  const bool qT = (st.flags & SF_IN_T) != 0;
+  const int rec = Dh + 2;                  // floats of one partial result: acc[Dh], max, sum
+
+  for (int hs = first_item(blockIdx.x, st.rot % grid, grid); hs < nslice; hs += grid) {
+    const int part = hs % cph;
+    const int hg = (hs / cph) % Hg;
+    const int b = hs / (cph * Hg);
+    const int hk = hg / R;
+    const int sp = part * kNWC + warp;
+    const int n = min(cached_pos(pc, st.seqlens, b) + st.seqlen_add, st.S_max);
     const int per = (n + nsplit - 1) / nsplit;
     const int j0 = sp * per, j1 = min(n, j0 + per);
+    const size_t base = ((size_t)b * st.S_max) * kv_row + (size_t)hk * Dh + lane * DPL;
+    const size_t row_bytes = kv_row * sizeof(T);
+    const char* kbase = reinterpret_cast<const char*>(st.kcache) + base * sizeof(T);
+    const char* vbase = reinterpret_cast<const char*>(st.vcache) + base * sizeof(T);
 
-    float q[G][DPL], acc[G][DPL], m[G], l[G];
+    // The value row u is requested as soon as key row u has been turned into a score, into
+    // the registers the key row leaves behind.  Rows are addressed by one running pointer and
+    // rows past the split are skipped by predicate (their registers read as zeros).
+    RawRow<T, DPL> kr[KMAX], vr[KMAX];
+    auto fetch = [&](int c0) {
+      const char* kp = kbase + (size_t)c0 * row_bytes;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const size_t qi = ((size_t)b * H + hk * G + g) * Dh + lane * DPL;
+      for (int u = 0; u < KMAX; ++u) {
+        kr[u].load(kp, c0 + u < j1);
+        kp += row_bytes;
+      }
+    };
+    fetch(j0);
+    float q[GI][DPL], acc[GI][DPL], m[GI], l[GI];
+#pragma unroll
+    for (int g = 0; g < GI; ++g) {
+      const size_t qi = ((size_t)b * H + hg * GI + g) * Dh + lane * DPL;
       if (qT) {
         ld_row<T, DPL>(st.q, qi, q[g]);
       } else {
@@ -935,125 +948,167 @@ __device__ __noinline__ void attn_items(const Stage& st, int wrank, int total_wa
       m[g] = -INFINITY;
       l[g] = 0.f;
     }
-    const size_t base = ((size_t)b * st.S_max) * kv_row + (size_t)hk * Dh + lane * DPL;
-    for (int j = j0; j < j1; j += UNR) {
-      float kf[UNR][DPL], vf[UNR][DPL];
+    for (int c0 = j0; c0 < j1; c0 += KMAX) {
+      if (c0 > j0) fetch(c0);
+      float sc[GI][KMAX];
+      const char* vp = vbase + (size_t)c0 * row_bytes;
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int jj = min(j + u, j1 - 1);
-        ld_row<T, DPL>(st.kcache, base + (size_t)jj * kv_row, kf[u]);
-      }
+      for (int u = 0; u < KMAX; ++u) {
+        float kf[DPL];
+        kr[u].unpack(kf);
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int jj = min(j + u, j1 - 1);
-        ld_row<T, DPL>(st.vcache, base + (size_t)jj * kv_row, vf[u]);
-      }
+        for (int g = 0; g < GI; ++g) {
+          float s2 = 0.f;
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        if (j + u < j1) {
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            float s = 0.f;
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) s = fmaf(q[g][d], kf[u][d], s);
-            s = warp_sum(s) * st.scale;
-            const float mn = fmaxf(m[g], s);
-            const float corr = expf(m[g] - mn);
-            const float p = expf(s - mn);
-            l[g] = l[g] * corr + p;
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(p, vf[u][d], acc[g][d] * corr);
-            m[g] = mn;
-          }
+          for (int d = 0; d < DPL; ++d) s2 = fmaf(q[g][d], kf[d], s2);
+          sc[g][u] = s2;
         }
+        vr[u].load(vp, c0 + u < j1);
+        vp += row_bytes;
+      }
+#pragma unroll
+      for (int g = 0; g < GI; ++g) {
+        float cm = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < KMAX; ++u) {
+          sc[g][u] = (c0 + u < j1) ? warp_sum(sc[g][u]) * st.scale : -INFINITY;
+          cm = fmaxf(cm, sc[g][u]);
+        }
+        const float mn = fmaxf(m[g], cm);
+        const float corr = (m[g] == -INFINITY) ? 0.f : expf(m[g] - mn);
+        float ls = 0.f;
+#pragma unroll
+        for (int u = 0; u < KMAX; ++u) {
+          sc[g][u] = (c0 + u < j1) ? expf(sc[g][u] - mn) : 0.f;
+          ls += sc[g][u];
+        }
+        l[g] = l[g] * corr + ls;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] *= corr;
+        m[g] = mn;
+      }
+#pragma unroll
+      for (int u = 0; u < KMAX; ++u) {
+        float vf[DPL];
+        vr[u].unpack(vf);
+#pragma unroll
+        for (int g = 0; g < GI; ++g)
+#pragma unroll
+          for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(sc[g][u], vf[d], acc[g][d]);
       }
     }
-    // publish the partial result of this split
+    // ---- the 8 partial results of the CTA meet in shared memory: sh[(warp * GI + g) * rec ...]
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const size_t pi = (((size_t)b * H + hk * G + g) * nsplit + sp);
+    for (int g = 0; g < GI; ++g) {
+      float* dst = sh + (size_t)(warp * GI + g) * rec;
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) st.part_acc[pi * Dh + lane * DPL + d] = acc[g][d];
+      for (int d = 0; d < DPL; ++d) dst[lane * DPL + d] = acc[g][d];
       if (lane == 0) {
-        st.part_ml[pi * 2 + 0] = m[g];
-        st.part_ml[pi * 2 + 1] = l[g];
+        dst[Dh] = m[g];
+        dst[Dh + 1] = l[g];
       }
     }
-    __threadfence();
-    __syncwarp();
-    int done = 0;
-    if (lane == 0) done = atomicAdd(&st.counters[b * Hk + hk], 1);
-    done = __shfl_sync(0xffffffffu, done, 0);
-    if (done == nsplit - 1) {
-      // Last split of this (b, kv head) to arrive: combine all splits in split order, whoever
-      // the last arriver is, so the result does not depend on timing.  nsplit <= 32: lane s
-      // fetches the (max, sum) pair of split s.
-      __threadfence();
+    cons_sync();
+    if (warp < GI) {
+      // warp g merges the 8 partial results of head g in warp order
+      const int g = warp;
+      float M = -INFINITY;
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const size_t hb = ((size_t)b * H + hk * G + g) * nsplit;
-        float ms = -INFINITY, ls = 0.f;
-        if (lane < nsplit) {
-          const float2 ml = __ldcg(reinterpret_cast<const float2*>(st.part_ml + (hb + lane) * 2));
-          ms = ml.x;
-          ls = ml.y;
-        }
-        const float M = warp_max(ms);
-        const float wgt = ls > 0.f ? expf(ms - M) : 0.f;
-        float L = 0.f, o[DPL];
+      for (int w2 = 0; w2 < kNWC; ++w2) M = fmaxf(M, sh[(size_t)(w2 * GI + g) * rec + Dh]);
+      float L = 0.f, o[DPL];
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) o[d] = 0.f;
-        for (int s0 = 0; s0 < nsplit; s0 += 8) {
-          float pa[8][DPL];
+      for (int d = 0; d < DPL; ++d) o[d] = 0.f;
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int s2 = min(s0 + u, nsplit - 1);
-            ld_row<float, DPL>(st.part_acc, (hb + s2) * Dh + lane * DPL, pa[u]);
-          }
+      for (int w2 = 0; w2 < kNWC; ++w2) {
+        const float* src = sh + (size_t)(w2 * GI + g) * rec;
+        const float lw = src[Dh + 1];
+        const float wgt = lw > 0.f ? expf(src[Dh] - M) : 0.f;
+        L += lw * wgt;
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int s2 = min(s0 + u, 31);
-            const float ws = __shfl_sync(0xffffffffu, wgt, s2);
-            const float lw = __shfl_sync(0xffffffffu, ls, s2) * ws;
-            if (s0 + u < nsplit) {
-              L += lw;
-#pragma unroll
-              for (int d = 0; d < DPL; ++d) o[d] = fmaf(pa[u][d], ws, o[d]);
-            }
-          }
-        }
+        for (int d = 0; d < DPL; ++d) o[d] = fmaf(src[lane * DPL + d], wgt, o[d]);
+      }
+      const int h = hg * GI + g;
+      const size_t oi = ((size_t)b * H + h) * Dh + lane * DPL;
+      if (cph == 1) {
         const float invL = L > 0.f ? 1.f / L : 0.f;
-        const size_t oi = ((size_t)b * H + hk * G + g) * Dh + lane * DPL;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) {
           const float v = X::rnd(o[d] * invL);
           if (st.flags & SF_OUT_T) X::st(st.out, oi + d, v);
           else reinterpret_cast<float*>(st.out)[oi + d] = v;
         }
+      } else {
+        // publish this CTA's part; the last of the cph CTAs merges the parts in part order
+        const size_t pi = ((size_t)b * H + h) * cph + part;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) st.part_acc[pi * Dh + lane * DPL + d] = o[d];
+        if (lane == 0) {
+          st.part_ml[pi * 2 + 0] = M;
+          st.part_ml[pi * 2 + 1] = L;
+        }
+        __threadfence();
+        __syncwarp();
+        int done = 0;
+        if (lane == 0) done = atomicAdd(&st.counters[b * H + h], 1);
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (done == cph - 1) {
+          __threadfence();
+          const size_t hb = ((size_t)b * H + h) * cph;
+          float pm[4], pl[4], pa[4][DPL];   // cph <= 4
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int c2 = min(c, cph - 1);
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(st.part_ml + (hb + c2) * 2));
+            pm[c] = ml.x;
+            pl[c] = ml.y;
+            ld_row<float, DPL>(st.part_acc, (hb + c2) * Dh + lane * DPL, pa[c]);
+          }
+          float M2 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (c < cph) M2 = fmaxf(M2, pm[c]);
+          float L2 = 0.f, o2[DPL];
+#pragma unroll
+          for (int d = 0; d < DPL; ++d) o2[d] = 0.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c < cph) {
+              const float wgt = pl[c] > 0.f ? expf(pm[c] - M2) : 0.f;
+              L2 += pl[c] * wgt;
+#pragma unroll
+              for (int d = 0; d < DPL; ++d) o2[d] = fmaf(pa[c][d], wgt, o2[d]);
+            }
+          }
+          const float invL = L2 > 0.f ? 1.f / L2 : 0.f;
+#pragma unroll
+          for (int d = 0; d < DPL; ++d) {
+            const float v = X::rnd(o2[d] * invL);
+            if (st.flags & SF_OUT_T) X::st(st.out, oi + d, v);
+            else reinterpret_cast<float*>(st.out)[oi + d] = v;
+          }
+          if (lane == 0) st.counters[b * H + h] = 0;
+        }
       }
-      if (lane == 0) st.counters[b * Hk + hk] = 0;
     }
+    cons_sync();   // the partial results in shared memory may be overwritten
   }
 }
 
 template <typename T>
-__device__ __forceinline__ void run_attn(const Stage& st, int wrank, int total_warps, int lane) {
+__device__ __forceinline__ void run_attn(const Stage& st, float* sh, const PosCache pc) {
   const int G = st.H / st.Hk;
   const int dpl = st.Dh / 32;
-#define FSVD_ATTN_CASE(GG, DD) \
-  if (G == GG && dpl == DD) { attn_items<T, GG, DD>(st, wrank, total_warps, lane); return; }
-  FSVD_ATTN_CASE(1, 4)
-  FSVD_ATTN_CASE(2, 4)
-  FSVD_ATTN_CASE(4, 4)
-  FSVD_ATTN_CASE(8, 4)
-  FSVD_ATTN_CASE(1, 2)
-  FSVD_ATTN_CASE(2, 2)
-  FSVD_ATTN_CASE(4, 2)
-  FSVD_ATTN_CASE(8, 2)
-#undef FSVD_ATTN_CASE
-}// ----------------------------------------------------------------------------- small stages
+  if ((G & 1) == 0) {
+    if (dpl == 4) attn_cta<T, 2, 4>(st, sh, pc);
+    else attn_cta<T, 2, 2>(st, sh, pc);
+  } else {
+    if (dpl == 4) attn_cta<T, 1, 4>(st, sh, pc);
+    else attn_cta<T, 1, 2>(st, sh, pc);
+  }
+}
+// ----------------------------------------------------------------------------- small stages
 template <typename T>
-__device__ __noinline__ void run_embed(const Stage& st, int gtid, int gthreads) {
+__device__ __forceinline__ void run_embed(const Stage& st, int gtid, int gthreads) {
   using X = TT<T>;
   const int d = st.P, B = st.B;
   for (int i = gtid; i < B * d; i += gthreads) {
@@ -1067,7 +1122,7 @@ __device__ __noinline__ void run_embed(const Stage& st, int gtid, int gthreads) 
 }
 
 // CTA 0 only.  Lowest index wins among equal maxima.
-static __device__ __noinline__ void run_argmax(const Stage& st, float* redv, int* redi, int tid,
+static __device__ __forceinline__ void run_argmax(const Stage& st, float* redv, int* redi, int tid,
                                            int nthreads) {
   const int V = st.vocab, B = st.B;
   const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
@@ -1105,7 +1160,7 @@ static __device__ __noinline__ void run_argmax(const Stage& st, float* redv, int
       redv[warp] = best;
       redi[warp] = bi;
     }
-    __syncthreads();
+    cons_sync();
     if (tid == 0) {
       for (int i = 1; i < nwarps; ++i)
         if (redv[i] > best || (redv[i] == best && redi[i] < bi)) {
@@ -1117,122 +1172,172 @@ static __device__ __noinline__ void run_argmax(const Stage& st, float* redv, int
       if (st.token_log && step < st.max_steps) st.token_log[(size_t)step * B + b] = bi;
       if (st.seqlens_rw) st.seqlens_rw[b] += 1;
     }
-    __syncthreads();
+    cons_sync();
   }
   if (tid == 0) *st.step_counter = step + 1;
-}// ----------------------------------------------------------------------------- the kernel
+}
+
+// ----------------------------------------------------------------------------- the kernel
 // Dynamic shared memory layout:
 //   [0, 2*sizeof(Stage))        current and next stage descriptor
-//   [.., +512)                  reduction scratch and the CTA's barrier arrival count
+//   [.., +512)                  reduction scratch, the CTA's barrier arrival count, give-up flag
 //   [.., +kSmallProgBytes)      copy of a by-value program (per-op launches)
-//   [.., +kMaxUnitsPerCta*32)   this CTA's units of the running stage
+//   [.., +512)                  ring mbarriers: full[kMaxSlots], empty[kMaxSlots]
+//   -- header rounded to 1 KB --
+//   [.., +nslots*8192)          the ring
 //   [.., +part_bytes)           partial sums of the warps (sized by the host for the program)
 //   [.., +vec_bytes)            staged input vector, B rows of xstride elements
 // Stage timeline (optional): trace[(s*grid + cta)*16 + k] = globaltimer at: 0 stage entry,
 // 1 grid barrier passed, 2 vector staged, 3 stage done, 4 vector words arrived, 5 norm reduced,
-// 7 blocks streamed.
-template <typename T, int NW, int D>
-__global__ void __launch_bounds__(NW * 32, 1)
+// 7 boxes consumed.
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
 fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant__ SmallProgram small,
+                   const unsigned char* __restrict__ maps_global, const __grid_constant__ SmallMaps small_maps,
                    int use_small, int nstages, SyncState* sync, int xstride, int part_bytes,
-                   int vec_bytes, unsigned long long* trace) {
+                   int vec_bytes, int nslots, int window, unsigned long long* trace) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nthreads = NW * 32;
 
   unsigned char* cur_base = smem;
   float* red = reinterpret_cast<float*>(smem + 2 * kStageBytesAl);
   int* flags_sh = reinterpret_cast<int*>(smem + 2 * kStageBytesAl + 256);
   Stage* small_sh = reinterpret_cast<Stage*>(smem + 2 * kStageBytesAl + 512);
-  UnitInfo* units = reinterpret_cast<UnitInfo*>(smem + 2 * kStageBytesAl + 512 + kSmallProgBytes);
-  static_assert(sizeof(UnitInfo) == 32, "unit table entry size");
-  float* part = reinterpret_cast<float*>(smem + smem_header_bytes());
-  char* xvec = reinterpret_cast<char*>(smem + smem_header_bytes() + part_bytes);
+  unsigned char* bars = smem + 2 * kStageBytesAl + 512 + kSmallProgBytes;
+  unsigned char* ring = smem + smem_header_bytes();
+  float* part = reinterpret_cast<float*>(ring + (size_t)nslots * kBoxBytes);
+  char* xvec = reinterpret_cast<char*>(part) + part_bytes;
+  volatile int* giveup = flags_sh + 1;
 
-  // Padding blocks of a run multiply zero factors with whatever follows the K range in the
-  // staged vector, so that memory must hold finite numbers from the start.
-  for (int i = tid; i < vec_bytes / 16; i += nthreads)
+  Ring rg;
+  rg.full = smem_u32(bars);
+  rg.empty = rg.full + kMaxSlots * 8;
+  rg.data = smem_u32(ring);
+  rg.ns = nslots;
+  rg.window = window;
+
+  // Boxes past the K range hold zeros and multiply whatever follows the input in the staged
+  // vector, so that memory must hold finite numbers from the start.
+  for (int i = tid; i < vec_bytes / 16; i += kThreads)
     reinterpret_cast<uint4*>(xvec)[i] = make_uint4(0, 0, 0, 0);
 
   const Stage* prog = prog_global;
+  const unsigned char* maps = maps_global;
   if (use_small) {
-    // by-value program: copy it to shared memory once and walk it there
+    // by-value program: copy it to shared memory once and walk it there; the TMA descriptors
+    // stay in the parameter space
     const int* src = reinterpret_cast<const int*>(small.st);
     int* dst = reinterpret_cast<int*>(small_sh);
     const int nwords = nstages * (int)(sizeof(Stage) / 4);
-    for (int i = tid; i < nwords; i += nthreads) dst[i] = src[i];
+    for (int i = tid; i < nwords; i += kThreads) dst[i] = src[i];
     prog = small_sh;
-    __syncthreads();
+    maps = &small_maps.m[0][0];
   }
-  const int wrank = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * NW;
-
-  const unsigned long long bar_base = __ldcg(&sync->bar_base);
-  unsigned nbar = 0;
+  // flags_sh[16..23]: positions of the batch rows, flags_sh[24..25]: the array they come from
+  if (tid < 8) {
+    // read the descriptors where they came from: the shared-memory copy is still being written
+    const Stage* src = use_small ? small.st : prog_global;
+    const int* sl = nullptr;
+    for (int s = 0; s < nstages && !sl; ++s) sl = src[s].seqlens;
+    int B0 = 0;
+    if (sl) B0 = src[0].B;
+    flags_sh[16 + tid] = (sl && tid < B0) ? sl[tid] : 0;
+    if (tid == 0) *reinterpret_cast<const int**>(flags_sh + 24) = sl;
+  }
+  if (tid == 0) {
+    flags_sh[0] = 0;   // warps of this CTA that have arrived at the pending grid barrier
+    flags_sh[1] = 0;   // set when a ring wait ran out: nobody waits for the ring again
+    flags_sh[2] = flags_sh[3] = 0;   // boxes issued by the producers (timeline aid)
+    flags_sh[4] = 0;                 // quiet phase flag
+    for (int i = 0; i < nslots; ++i) {
+      mbar_init(rg.full + i * 8, 1);
+      mbar_init(rg.empty + i * 8, 1);
+    }
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
   constexpr int kStageWords = (int)(sizeof(Stage) / 4);
-  // flags_sh[0]: warps of this CTA that have arrived at the pending grid barrier
-  if (tid == 0) flags_sh[0] = 0;
+  __syncthreads();
   if (tid < kStageWords)
     reinterpret_cast<int*>(cur_base)[tid] = reinterpret_cast<const int*>(prog)[tid];
 
-  for (int s = 0; s < nstages; ++s) {
-    __syncthreads();  // everybody is done with the previous stage's buffers; descriptor s landed
-    const Stage& st = *reinterpret_cast<const Stage*>(cur_base + (s & 1) * kStageBytesAl);
-    unsigned long long* trow =
-        (trace && tid == 0) ? trace + ((size_t)s * gridDim.x + blockIdx.x) * 16 : nullptr;
-    trace_mark(trow, 0);
-    // the last warp fetches the next descriptor while the others go on
-    if (warp == NW - 1 && s + 1 < nstages) {
-      int* dst = reinterpret_cast<int*>(cur_base + ((s + 1) & 1) * kStageBytesAl);
-      const int* src = reinterpret_cast<const int*>(prog + s + 1);
-      for (int i = lane; i < kStageWords; i += 32) dst[i] = src[i];
-    }
-    const unsigned long long target = (bar_base + nbar + 1ull) * gridDim.x;
-    if (st.flags & SF_BARRIER) ++nbar;
-    if (st.type == ST_GEMV) {
-      StageCtx cx;
-      cx.prog = prog;
-      cx.s = s;
-      cx.nstages = nstages;
-      cx.sync = sync;
-      cx.bar_target = target;
-      cx.xvec = xvec;
-      cx.xstride = xstride;
-      cx.red = red;
-      cx.part = part;
-      cx.units = units;
-      cx.trow = trow;
-      gemv_stage<T, NW, D>(st, cx);
-    } else {
-      if (st.flags & SF_BARRIER) barrier_wait(sync, target, s, tid);
-      trace_mark(trow, 1);
-      if (st.type == ST_ATTN) {
-        run_attn<T>(st, wrank, total_warps, lane);
-      } else if (st.type == ST_EMBED) {
-        run_embed<T>(st, blockIdx.x * nthreads + tid, gridDim.x * nthreads);
-      } else if (st.type == ST_ARGMAX) {
-        if (blockIdx.x == 0) run_argmax(st, red, flags_sh + 8, tid, nthreads);
+  unsigned nbar = 0;
+  const unsigned long long bar_base = __ldcg(&sync->bar_base);
+  if (warp >= kNWC) {
+    // ---------------- producers
+    if (lane < kNPROD) producer_loop<T>(prog, nstages, maps, rg, lane, sync, giveup);
+  } else {
+    // ---------------- consumers
+    const int wrank = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * kNWC;
+    unsigned seq_base = 0;
+    PosCache pc;
+    pc.ptr = *reinterpret_cast<const int* const*>(flags_sh + 24);
+    pc.pos = flags_sh + 16;
+    for (int s = 0; s < nstages; ++s) {
+      cons_sync();  // everybody is done with the previous stage's buffers; descriptor s landed
+      const Stage& st = *reinterpret_cast<const Stage*>(cur_base + (s & 1) * kStageBytesAl);
+      unsigned long long* trow =
+          (trace && tid == 0) ? trace + ((size_t)s * gridDim.x + blockIdx.x) * 16 : nullptr;
+      trace_mark(trow, 0);
+      // the last consumer warp fetches the next descriptor while the others go on
+      if (warp == kNWC - 1 && s + 1 < nstages) {
+        int* dst = reinterpret_cast<int*>(cur_base + ((s + 1) & 1) * kStageBytesAl);
+        const int* src = reinterpret_cast<const int*>(prog + s + 1);
+        for (int i = lane; i < kStageWords; i += 32) dst[i] = src[i];
       }
-    }
-    if (st.flags & SF_ARRIVE) {
-      // Grid-barrier arrival, warp by warp: each warp publishes its own stores and counts itself
-      // in shared memory; the last warp of the CTA adds the CTA to the global count.
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) {
-        unsigned old;
-        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
-                     : "=r"(old) : "r"(smem_u32(flags_sh)) : "memory");
-        if (old == (unsigned)NW - 1u) {
-          flags_sh[0] = 0;
-          asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
+      const unsigned long long target = (bar_base + nbar + 1ull) * gridDim.x;
+      if (st.flags & SF_BARRIER) ++nbar;
+      if (st.type == ST_GEMV) {
+        StageCtx cx;
+        cx.s = s;
+        cx.sync = sync;
+        cx.bar_target = target;
+        cx.xvec = xvec;
+        cx.xstride = xstride;
+        cx.red = red;
+        cx.part = part;
+        cx.ring = rg;
+        cx.seq_base = seq_base;
+        cx.giveup = giveup;
+        cx.pc = pc;
+        cx.trow = trow;
+        seq_base += (unsigned)gemv_stage<T>(st, cx);
+      } else {
+        if (st.flags & SF_BARRIER) barrier_wait(sync, target, s, tid);
+        trace_mark(trow, 1);
+        if (st.type == ST_ATTN) {
+          run_attn<T>(st, part, pc);
+        } else if (st.type == ST_EMBED) {
+          run_embed<T>(st, blockIdx.x * kConsThreads + tid, gridDim.x * kConsThreads);
+        } else if (st.type == ST_ARGMAX) {
+          if (blockIdx.x == 0) run_argmax(st, red, flags_sh + 8, tid, kConsThreads);
         }
       }
+      if (st.flags & SF_ARRIVE) {
+        // Grid-barrier arrival, warp by warp: each warp publishes its own stores and counts itself
+        // in shared memory; the last warp of the CTA adds the CTA to the global count.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          unsigned old;
+          asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
+                       : "=r"(old) : "r"(smem_u32(flags_sh)) : "memory");
+          if (old == (unsigned)kNWC - 1u) {
+            flags_sh[0] = 0;
+            asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
+          }
+        }
+      }
+      trace_mark(trow, 3);
     }
-    trace_mark(trow, 3);
   }
+  __syncthreads();
+  // After a give-up, copies may still be in flight towards this CTA's shared memory: give them
+  // time to land before the CTA retires (bounded).
+  if (*giveup)
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
   // The last CTA to finish publishes the barrier count for the next launch; every CTA has read
   // it before it can get here.
-  __syncthreads();
   if (tid == 0) {
     __threadfence();
     const unsigned done = atomicAdd(&sync->done_ctas, 1u);

@@ -4,15 +4,22 @@
 
 #include "fsvd_stage.h"
 
-typedef cudaError_t (*LaunchFn)(const fsvd::Stage* prog, const fsvd::SmallProgram* small,
-                                int use_small, int nstages, fsvd::SyncState* sync, int xstride,
-                                int part_bytes, int vec_bytes, unsigned long long* trace, int grid,
-                                size_t smem,
-                                cudaStream_t stream);
+struct LaunchArgs {
+  const fsvd::Stage* prog;            // device-resident program, or null with `small`
+  const fsvd::SmallProgram* small;    // by-value program (per-op launches)
+  const unsigned char* maps;          // device-resident TMA descriptors, 2 x 128 bytes per stage
+  const fsvd::SmallMaps* small_maps;  // by-value descriptors of a by-value program
+  int nstages;
+  fsvd::SyncState* sync;
+  int xstride, part_bytes, vec_bytes, nslots, window;
+  unsigned long long* trace;
+  int grid;
+  size_t smem;
+  cudaStream_t stream;
+};
+typedef cudaError_t (*LaunchFn)(const LaunchArgs& a);
 
 struct KernelEntry {
-  int dtype;  // FSVD_DTYPE_*
-  int nw;     // warps per CTA
-  int depth;  // 16-byte loads in flight per lane
+  int dtype;    // FSVD_DTYPE_*
   LaunchFn fn;  // null terminates a table
 };

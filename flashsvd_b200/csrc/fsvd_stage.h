@@ -2,10 +2,11 @@
 //
 // One decode step is a short program of dependent stages (rank projection, lift with a
 // fused epilogue, split-KV attention, ...).  A single persistent kernel, one CTA per SM,
-// walks the program.  Every stage streams its slice of the factor matrices through
-// per-warp shared-memory rings filled by bulk async copies; because the addresses of the
-// factors do not depend on the activations, a warp keeps prefetching the factors of the
-// following stages while it waits at the grid barrier that separates two stages.
+// walks the program.  The factor matrices of all GEMV stages form one long stream of 8 KB
+// boxes (16 rows x 512 bytes) per CTA; producer warps copy the boxes with TMA into a
+// shared-memory ring, in program order and as far ahead as the ring allows.  The addresses of
+// the factors do not depend on the activations, so the stream keeps running while the consumer
+// warps wait at the grid barrier between two stages.
 #pragma once
 #include <stdint.h>
 
@@ -59,14 +60,14 @@ struct alignas(16) Stage {
   int K;                 // reduction length
   int ldw;               // row stride of WA/WB in elements
   int segs;              // number of K segments (partial sums) per row group
-  int kseg;              // elements per K segment
+  int kseg;              // elements per K segment (cps boxes)
   int xA_off, xB_off;    // offset of the operand-group input inside the staged vector
   int rope_half;         // >0: physical row of logical row p is (p/half)*2*half + p%half
   int vl_len;            // staged vector length per batch row
   int vl_nseg;           // partial sums to add when staging
   int rot;               // rotation of the unit -> CTA assignment (ST_ATTN: item -> warp)
-  int pf_begin, pf_end;  // stages whose factor matrices this stage prefetches into L2
-  int ksplit;            // warps that share one unit's K range (1, 2, 4 or 8)
+  int cps;               // boxes (column chunks of 512 bytes) per K segment
+  int reserved0, reserved1;
   int B;                 // batch rows
   const void* vl_src;    // fp32 (or T with SF_IN_T) [vl_nseg, B, vl_len]
   const void* vl_w;      // RMSNorm weight, type T
@@ -110,17 +111,33 @@ enum DeviceStatus : int {
   DS_COPY_TIMEOUT = 2,
 };
 
+// Geometry of the factor stream.
+// 8 warps per CTA: with more, the register file leaves 168 registers per thread and the
+// interpreter spills; 256 threads get 255.
+constexpr int kConsumerWarps = 7;      // warps that multiply
+constexpr int kProducerWarps = 1;      // warp that issues the TMA copies ...
+constexpr int kProducerLanes = 4;      // ... from this many lanes, each owning the slots s % 4
+constexpr int kUnitRows = 16;          // factor rows of one unit = rows of one box
+constexpr int kBoxRowBytes = 512;      // bytes of one box row (256 bf16 / 128 fp32 columns)
+constexpr int kBoxBytes = kUnitRows * kBoxRowBytes;
+constexpr int kMaxSlots = 21;          // ring slots; a multiple of kConsumerWarps
+
 constexpr int kMaxSmallStages = 14;
 struct SmallProgram {
   Stage st[kMaxSmallStages];
 };
 
+// 128-byte TMA descriptors of a by-value program, two per stage (operand A, operand B).
+struct alignas(64) SmallMaps {
+  unsigned char m[2 * kMaxSmallStages][128];
+};
+
 // Shared-memory header of the interpreter (two stage descriptors, reduction scratch, the copy
-// of a by-value program), rounded to 1 KB.
+// of a by-value program, the ring's mbarriers), rounded to 1 KB.
 constexpr int kStageBytesAl = ((int)sizeof(Stage) + 15) / 16 * 16;
 constexpr int kSmallProgBytes = kMaxSmallStages * kStageBytesAl;
 FSVD_HD constexpr int smem_header_bytes() {
-  return ((2 * kStageBytesAl + 512 + kSmallProgBytes + 64 * 32 + 1023) / 1024) * 1024;
+  return ((2 * kStageBytesAl + 512 + kSmallProgBytes + 512 + 1023) / 1024) * 1024;
 }
 
 }  // namespace fsvd

@@ -38,7 +38,7 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def set_launch_config(warps: int = 8, depth: int = 16, grid: int = 0) -> None:
+def set_launch_config(warps: int = 0, depth: int = 0, grid: int = 0) -> None:
     """Pick the kernel geometry (see fsvd_set_launch_config in include/flashsvd_b200.h)."""
     check(_lib.load().fsvd_set_launch_config(int(warps), int(depth), int(grid)))
 
