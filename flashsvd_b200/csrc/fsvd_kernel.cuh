@@ -419,23 +419,51 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
       }
     }
   } else if (st.vl_mode == VL_SUM) {
-    // fp32 partial sums [nseg][B][len]
+    // fp32 partial sums [nseg][B][len]; with few segments a thread handles up to UP float4
+    // positions per pass and issues all their loads before the first add (one memory round trip
+    // per pass instead of one per position)
     constexpr int SMAX = 8;  // kMaxSegs of the program builder
+    constexpr int UP = 4;
     const int nseg = st.vl_nseg;
     const int upr = len >> 2, units = B * upr;
     const size_t segstride = (size_t)B * len;
     const float* src = reinterpret_cast<const float*>(st.vl_src);
-    for (int u = tid; u < units; u += nthreads) {
-      float4 v[SMAX];
+    if (nseg <= 3) {
+      for (int u0 = tid; u0 < units; u0 += nthreads * UP) {
+        float4 v[UP][3];
 #pragma unroll
-      for (int q = 0; q < SMAX; ++q)
-        if (q < nseg) v[q] = ldcg_f4(src + q * segstride + (size_t)u * 4);
-      float4 a = v[0];
+        for (int k = 0; k < UP; ++k) {
+          const int u = u0 + k * nthreads;
 #pragma unroll
-      for (int q = 1; q < SMAX; ++q)
-        if (q < nseg) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
-      const int b = u / upr, k = (u - b * upr) * 4;
-      st4<T>(xvec, (size_t)b * xstride + k, a);
+          for (int q = 0; q < 3; ++q)
+            if (q < nseg && u < units) v[k][q] = ldcg_f4(src + q * segstride + (size_t)u * 4);
+        }
+#pragma unroll
+        for (int k = 0; k < UP; ++k) {
+          const int u = u0 + k * nthreads;
+          if (u < units) {
+            float4 a = v[k][0];
+#pragma unroll
+            for (int q = 1; q < 3; ++q)
+              if (q < nseg) { a.x += v[k][q].x; a.y += v[k][q].y; a.z += v[k][q].z; a.w += v[k][q].w; }
+            const int b = u / upr, k2 = (u - b * upr) * 4;
+            st4<T>(xvec, (size_t)b * xstride + k2, a);
+          }
+        }
+      }
+    } else {
+      for (int u = tid; u < units; u += nthreads) {
+        float4 v[SMAX];
+#pragma unroll
+        for (int q = 0; q < SMAX; ++q)
+          if (q < nseg) v[q] = ldcg_f4(src + q * segstride + (size_t)u * 4);
+        float4 a = v[0];
+#pragma unroll
+        for (int q = 1; q < SMAX; ++q)
+          if (q < nseg) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
+        const int b = u / upr, k = (u - b * upr) * 4;
+        st4<T>(xvec, (size_t)b * xstride + k, a);
+      }
     }
   } else if (st.vl_mode == VL_RMSNORM) {
     // T source, weight of type T; a row longer than the register window is read twice
@@ -760,15 +788,21 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
       const uint32_t xoff = (uint32_t)(xcol0 + c * BOXCOLS) * (uint32_t)sizeof(T);
       if constexpr (sizeof(T) == 2) {
         const uint32_t xb = xlane_s + xoff;
+        // four independent accumulator chains keep the tensor pipe busy
         float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+        float a2[4] = {0.f, 0.f, 0.f, 0.f}, a3[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const uint4 xv = lds128(xb + q * 64);
-          const uint4 lo = lds128(wb + q * 64);
-          const uint4 hi = lds128(wb + 8 * kBoxRowBytes + q * 64);
+        for (int q = 0; q < 8; q += 2) {
+          const uint4 xv = lds128(xb + q * 64), xw = lds128(xb + q * 64 + 64);
+          const uint4 lo = lds128(wb + q * 64), lp = lds128(wb + q * 64 + 64);
+          const uint4 hi = lds128(wb + 8 * kBoxRowBytes + q * 64), hj = lds128(wb + 8 * kBoxRowBytes + q * 64 + 64);
           mma_bf16_16816(a0, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
           mma_bf16_16816(a1, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+          mma_bf16_16816(a2, lp.x, hj.x, lp.y, hj.y, xw.x, xw.y);
+          mma_bf16_16816(a3, lp.z, hj.z, lp.w, hj.w, xw.z, xw.w);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a0[e] += a2[e], a1[e] += a3[e];
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[e] += a0[e] + a1[e];
       } else {
@@ -1324,7 +1358,9 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
                        : "=r"(old) : "r"(smem_u32(flags_sh)) : "memory");
           if (old == (unsigned)kNWC - 1u) {
             flags_sh[0] = 0;
-            asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
+            // every warp fenced its stores before it counted itself (acq_rel above), so a
+            // relaxed add is enough to publish the CTA
+            asm volatile("red.relaxed.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
           }
         }
       }
