@@ -21,7 +21,7 @@ EXPORTS = (
     "fsvd_lowrank_proj", "fsvd_mlp_swiglu_decode", "fsvd_qkv_rope_append", "fsvd_flash_decode",
     "fsvd_decode_layer", "fsvd_model_create", "fsvd_model_destroy", "fsvd_model_step",
     "fsvd_model_buffers", "fsvd_model_status", "fsvd_model_reset_sync", "fsvd_launch_count",
-    "fsvd_set_trace_buffer", "fsvd_model_num_stages", "fsvd_lowrank_proj_static",
+    "fsvd_set_trace_buffer", "fsvd_model_num_stages", "fsvd_lowrank_proj_static", "fsvd_lift",
 )
 
 
@@ -78,6 +78,7 @@ def load() -> C.CDLL:
     lib.fsvd_workspace_status.argtypes = [vp, C.POINTER(ip)]
     lib.fsvd_lowrank_proj.argtypes = [vp, vp, vp, vp, vp, ip, ip, ip, ip, ip, vp, sz, vp]
     lib.fsvd_lowrank_proj_static.argtypes = [vp, vp, vp, vp, vp, ip, ip, ip, ip, ip, vp]
+    lib.fsvd_lift.argtypes = [vp, vp, vp, vp, ip, ip, ip, ip, vp, sz, vp]
     lib.fsvd_mlp_swiglu_decode.argtypes = (
         [vp, vp, C.c_float, vp, vp, vp, vp, vp, vp, vp] + [ip] * 7 + [vp, sz, vp])
     lib.fsvd_qkv_rope_append.argtypes = (

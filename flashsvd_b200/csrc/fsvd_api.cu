@@ -659,6 +659,28 @@ int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* r
   return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
+int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B, int R, int d_out,
+              int dtype, void* ws, size_t ws_bytes, void* stream) {
+  if (!p || !u || !y) return fail(FSVD_ERR_ARG, "null argument");
+  if (R <= 0 || d_out <= 0 || R % 8) return fail(FSVD_ERR_ALIGN, "R=%d must be a positive multiple of 8", R);
+  if (!aligned16(p) || !aligned16(u) || !aligned16(y)) return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  fsvd_dims D = op_dims(dtype, B);
+  WsLayout L;
+  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
+  Resolved r;
+  if (int e = resolve(dtype, B, r)) return e;
+  Builder b(r, dtype, B);
+  char* w = reinterpret_cast<char*>(ws);
+  Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
+  b.vec(s, VL_SUM, p, R, 1, false);
+  s.flags |= SF_IN_T | SF_OUT_T | (residual ? SF_RESID_T : 0);
+  s.epi = residual ? EPI_RESID : EPI_STORE;
+  s.resid = residual;
+  s.out = y;
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
+}
+
 int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const void* upgate_v,
                            const void* gate_u, const void* up_u, const void* down_v,
                            const void* down_u, const void* residual, void* y, int B, int d, int I,

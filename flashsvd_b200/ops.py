@@ -98,6 +98,21 @@ def lowrank_proj(x, v_w, u_w, ws: Workspace, residual=None, out=None):
     return out
 
 
+def lift(p, u_w, ws: Workspace, residual=None, out=None):
+    """y = (residual +) p @ u_w.T for p[B, R], u_w[d_out, R] (one factor, no rank step)."""
+    if p.ndim != 2:
+        raise ValueError(f"p must be [B, R], got {tuple(p.shape)}")
+    B, R = p.shape
+    if u_w.ndim != 2 or u_w.shape[1] != R:
+        raise ValueError(f"u_w must be [d_out, {R}], got {tuple(u_w.shape)}")
+    d_out = u_w.shape[0]
+    if out is None:
+        out = torch.empty((B, d_out), dtype=p.dtype, device=p.device)
+    check(_lib.load().fsvd_lift(_ptr(p), _ptr(u_w), _ptr(residual), _ptr(out), B, R, d_out,
+                                _dtype_code(p.dtype), ws.ptr, ws.nbytes, _stream()))
+    return out
+
+
 def lowrank_proj_static(x, v_w, u_w, residual=None, out=None):
     """lowrank_proj on the library's built-in scratch (B * R <= 8192): no workspace argument and
     no device allocation inside the call when ``out`` is given.  Calls share one scratch array

@@ -1,0 +1,394 @@
+"""Host-side mirror of the reference's runtime surface for the mode="flashsvd" decode path.
+
+Same names, argument meaning and error behaviour as the reference, so that call sites and tests
+written against the reference read the same here:
+
+* ``configure_runtime`` / ``runtime_env_snapshot`` (scripts/demo_support/api.py:20-143),
+* ``FlashSVDV15DenseKVCache`` (runtime/cache/attn_dense_kv.py:7-357),
+* ``flashsvd_mlp_dual_split_triton_pcat_s`` (kernels/mlp/decode/dual_split_triton_pcat_s.py:123-218),
+* ``pack_qkv_shared_bases`` / ``reconstruct_qkv_token_shared_prepacked``
+  (kernels/attn/decode/densekv_reconstruct_triton.py:662-760),
+* ``generate_text`` (scripts/demo_support/api.py:326-400) on a ``DecodeEngine``.
+
+Device work goes through the C ABI (``ops``); there is no CPU compute path: the kernel wrappers
+raise on non-CUDA tensors, as the reference's do.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Optional
+
+import torch
+
+# The 15 switches the reference's serving path reads from the environment, in its order.
+RUNTIME_ENV_VARS = (
+    "SVDLLM_FLASH_FALLBACK",
+    "FLASH_SVD_DISABLE_FFN",
+    "FLASH_SVD_BASELINE_LR_KVCACHE",
+    "FLASH_SVD_ENABLE_DENSE_ATTN_DECODE",
+    "FLASH_SVD_DENSE_DECODE_BACKEND",
+    "FLASH_SVD_DENSE_DECODE_GRAPH",
+    "FLASH_SVD_DENSE_DECODE_AUTOTUNE_SCOPE",
+    "FLASH_SVD_USE_CUTLASS_ROPEATTN",
+    "FLASH_SVD_BASELINE_DENSE_KVCACHE",
+    "FLASH_SVD_REFERENCE_DENSE_ATTN",
+    "FLASH_SVD_ENABLE_EXPERIMENTAL_FFN",
+    "FLASH_SVD_MLP_CUDA_GRAPH",
+    "FLASH_SVD_MLP_CUDA_GRAPH_ALIAS_OUTPUT",
+    "FLASH_SVD_MLP_CUDA_GRAPH_SCOPE",
+    "FLASH_SVD_FFN_BACKEND",
+)
+
+# FFN backends for which the reference also raises FLASH_SVD_ENABLE_EXPERIMENTAL_FFN
+# (scripts/demo_support/api.py:54-69).
+_EXPERIMENTAL_FFN_BACKENDS = frozenset(
+    ["flashsvd_mlp_dual_split_" + s for s in ("prod", "cutlass", "triton_v1", "triton_v2", "triton_v2_sm80", "triton_v3")]
+    + ["dual_split_" + s for s in ("cublas", "cutlass", "kernel", "kernel_v2", "kernel_v2_sm80", "kernel_v3")])
+
+
+def runtime_env_snapshot() -> dict:
+    return {name: os.getenv(name) for name in RUNTIME_ENV_VARS}
+
+
+def _apply_env(settings: dict) -> None:
+    """True -> "1", False / None -> unset, anything else -> str(value)."""
+    for name, value in settings.items():
+        if value is True:
+            os.environ[name] = "1"
+        elif value is False or value is None:
+            os.environ.pop(name, None)
+        else:
+            os.environ[name] = str(value)
+
+
+def configure_runtime(mode: str = "flashsvd", *, ffn_backend: str = "auto", enable_mlp_graph: bool = True,
+                      mlp_graph_scope: str = "layer_tail", graph_alias_output: bool = False,
+                      enable_flash_dense_attn: bool = True, dense_decode_backend: str = "auto",
+                      enable_dense_decode_graph: bool = True, dense_decode_autotune_scope: str = "attention",
+                      enable_cutlass_rope_attn: bool = False) -> dict:
+    """Set the environment switches of the serving path and return their snapshot.
+
+    ``mode="flashsvd"`` selects the dense-KV decode route and the production MLP backend,
+    ``"hf"`` / ``"baseline"`` the plain PyTorch path; any other mode is a ValueError.
+    """
+    key = str(mode).strip().lower().replace("-", "_")
+    if key not in ("flashsvd", "hf", "baseline"):
+        raise ValueError(f"Unsupported runtime mode: {mode}")
+    flash = key == "flashsvd"
+    attn = bool(enable_flash_dense_attn) and flash
+    backend_key = str(ffn_backend).strip().lower().replace("-", "_")
+    _apply_env({
+        "SVDLLM_FLASH_FALLBACK": not flash,
+        "FLASH_SVD_DISABLE_FFN": not flash,
+        "FLASH_SVD_BASELINE_LR_KVCACHE": False,
+        "FLASH_SVD_ENABLE_DENSE_ATTN_DECODE": attn,
+        "FLASH_SVD_DENSE_DECODE_BACKEND": str(dense_decode_backend) if attn else None,
+        "FLASH_SVD_DENSE_DECODE_GRAPH": bool(enable_dense_decode_graph) and attn,
+        "FLASH_SVD_DENSE_DECODE_AUTOTUNE_SCOPE": str(dense_decode_autotune_scope) if attn else None,
+        "FLASH_SVD_USE_CUTLASS_ROPEATTN": bool(enable_cutlass_rope_attn) and flash,
+        "FLASH_SVD_BASELINE_DENSE_KVCACHE": False,
+        "FLASH_SVD_REFERENCE_DENSE_ATTN": False,
+        "FLASH_SVD_ENABLE_EXPERIMENTAL_FFN": flash and backend_key in _EXPERIMENTAL_FFN_BACKENDS,
+        "FLASH_SVD_MLP_CUDA_GRAPH": bool(enable_mlp_graph) and flash,
+        "FLASH_SVD_MLP_CUDA_GRAPH_ALIAS_OUTPUT": bool(graph_alias_output) and flash,
+        "FLASH_SVD_MLP_CUDA_GRAPH_SCOPE": str(mlp_graph_scope) if flash else None,
+        "FLASH_SVD_FFN_BACKEND": str(ffn_backend) if flash else None,
+    })
+    return runtime_env_snapshot()
+
+
+# --------------------------------------------------------------------------------- KV cache
+class FlashSVDV15DenseKVCache:
+    """Dense KV cache in the layout the decode kernels read: ``key_cache[l]`` / ``value_cache[l]``
+    are ``[max_batch, max_cache_len, Hk, Dh]``, zero-initialised, shaped on first use; K is stored
+    after RoPE; the number of tokens seen is advanced by layer 0 only."""
+
+    is_compileable = False
+
+    def __init__(self, config, *, max_batch_size: int, max_cache_len: int, device=None,
+                 dtype: torch.dtype = torch.float16, layer_device_map: Optional[dict] = None) -> None:
+        self._config = config
+        self._max_batch_size = int(max_batch_size)
+        self._max_cache_len = int(max_cache_len)
+        self._dtype = dtype
+        self._rope_theta = float(getattr(config, "rope_theta", 10000.0))
+        self._seen_tokens = 0
+        self.key_cache: list = []
+        self.value_cache: list = []
+        self._layer_initialized: list = []
+        self._layer_device: list = []
+        self._fa2_cache_seqlens: dict = {}
+        self._rope_cache: dict = {}
+        for idx in range(int(getattr(config, "num_hidden_layers", 0))):
+            if layer_device_map is not None:
+                d = layer_device_map[idx]
+                d = torch.device("cuda", d) if isinstance(d, int) else torch.device(d)
+            else:
+                d = torch.device(device) if device is not None else torch.device("cpu")
+            self._layer_device.append(d)
+            empty = torch.zeros((self._max_batch_size, self._max_cache_len, 0, 0), dtype=dtype, device=d)
+            self.key_cache.append(empty)
+            self.value_cache.append(empty.clone())
+            self._layer_initialized.append(False)
+
+    @property
+    def max_batch_size(self) -> int:
+        return self._max_batch_size
+
+    @property
+    def max_cache_len(self) -> int:
+        return self._max_cache_len
+
+    def __len__(self) -> int:
+        return len(self.key_cache)
+
+    def _ensure_layer_spec(self, layer_idx: int, *, h: int, dh: int) -> None:
+        kc = self.key_cache[layer_idx]
+        if (int(kc.shape[2]), int(kc.shape[3])) == (int(h), int(dh)):
+            return
+        if self._layer_initialized[layer_idx]:
+            raise RuntimeError(
+                f"FlashSVDV15DenseKVCache shape changed after init for layer {layer_idx}: "
+                f"old={(int(kc.shape[2]), int(kc.shape[3]))}, new={(int(h), int(dh))}")
+        shape = (self._max_batch_size, self._max_cache_len, int(h), int(dh))
+        self.key_cache[layer_idx] = torch.zeros(shape, dtype=self._dtype, device=self._layer_device[layer_idx])
+        self.value_cache[layer_idx] = torch.zeros_like(self.key_cache[layer_idx])
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
+               cache_kwargs: Optional[dict] = None):
+        """Prefill / baseline write: key_states, value_states are [B, Hk, L, Dh] (K after RoPE),
+        written at ``cache_kwargs["cache_position"]`` (default: appended); returns the valid
+        prefix as [B, Hk, S, Dh] like a transformers cache."""
+        layer_idx = int(layer_idx)
+        B, Hk, L, Dh = (int(v) for v in key_states.shape)
+        self._ensure_layer_spec(layer_idx, h=Hk, dh=Dh)
+        self._layer_initialized[layer_idx] = True
+        if B > self._max_batch_size:
+            raise RuntimeError(f"batch {B} exceeds max_batch_size {self._max_batch_size}")
+        pos = None if cache_kwargs is None else cache_kwargs.get("cache_position")
+        if pos is None:
+            pos = torch.arange(self._seen_tokens, self._seen_tokens + L, device=key_states.device)
+        pos = pos.to(device=self.key_cache[layer_idx].device, dtype=torch.long).reshape(-1)
+        if int(pos.numel()) != L:
+            raise ValueError(f"cache_position has {int(pos.numel())} entries for {L} new tokens")
+        end = int(pos.max().item()) + 1 if L else self._seen_tokens
+        if end > self._max_cache_len:
+            raise IndexError(f"cache position {end - 1} outside max_cache_len {self._max_cache_len}")
+        self.key_cache[layer_idx][:B].index_copy_(1, pos, key_states.transpose(1, 2).to(self._dtype))
+        self.value_cache[layer_idx][:B].index_copy_(1, pos, value_states.transpose(1, 2).to(self._dtype))
+        if layer_idx == 0:
+            self._seen_tokens = max(self._seen_tokens, end)
+        k = self.key_cache[layer_idx][:B, :end].transpose(1, 2)
+        v = self.value_cache[layer_idx][:B, :end].transpose(1, 2)
+        return k, v
+
+    def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
+        return int(self._seen_tokens)
+
+    def get_max_cache_shape(self) -> Optional[int]:
+        return self._max_cache_len
+
+    def get_mask_sizes(self, cache_position, layer_idx: int = 0):
+        q_len = int(cache_position.shape[0]) if torch.is_tensor(cache_position) else int(cache_position)
+        return q_len + self.get_seq_length(), 0
+
+    def _seqlens_buffer(self, layer_idx: int, batch_size: int) -> torch.Tensor:
+        key = (int(layer_idx), int(batch_size))
+        dev = self.key_cache[layer_idx].device
+        buf = self._fa2_cache_seqlens.get(key)
+        if buf is None or buf.device != dev:
+            buf = torch.empty((int(batch_size),), device=dev, dtype=torch.int32)
+            self._fa2_cache_seqlens[key] = buf
+        return buf
+
+    def prepare_fa2_step(self, layer_idx: int, *, batch_size: int, cache_position=None):
+        """(k_cache[:B], v_cache[:B], cache_seqlens int32[B]) for one decode step: the write
+        position is ``cache_position`` when given (scalar, 1 entry or one per row), else the
+        number of tokens seen."""
+        layer_idx = int(layer_idx)
+        B = int(batch_size)
+        sl = self._seqlens_buffer(layer_idx, B)
+        if cache_position is None:
+            sl.fill_(self._seen_tokens)
+        elif torch.is_tensor(cache_position):
+            pos = cache_position.to(device=sl.device, dtype=torch.int32).reshape(-1)
+            if int(pos.numel()) == 0:
+                sl.zero_()
+            elif int(pos.numel()) == 1:
+                sl.copy_(pos.expand_as(sl))
+            else:
+                sl.copy_(pos[:B])
+        else:
+            sl.fill_(int(cache_position))
+        return self.key_cache[layer_idx][:B], self.value_cache[layer_idx][:B], sl
+
+    def get_fa2_kvcache(self, layer_idx: int, *, batch_size: int):
+        return self.prepare_fa2_step(layer_idx, batch_size=batch_size, cache_position=None)
+
+    def advance_after_fa2(self, layer_idx: int, *, q_len: int, cache_position=None) -> None:
+        if int(layer_idx) != 0:
+            return
+        on_host = cache_position is not None and torch.is_tensor(cache_position) and not cache_position.is_cuda
+        if on_host and int(cache_position.numel()) > 0:
+            self._seen_tokens = max(self._seen_tokens, int(cache_position.max().item()) + 1)
+        else:
+            self._seen_tokens = self._seen_tokens + int(q_len)
+
+    def get_rope_tables(self, seqlen: int, head_dim: int, *, device, dtype: torch.dtype):
+        """cos, sin [seqlen, head_dim/2]: fp32 angles pos * theta^(-i/half), cast to ``dtype``."""
+        key = (int(seqlen), int(head_dim), str(device), dtype)
+        hit = self._rope_cache.get(key)
+        if hit is not None:
+            return hit
+        half = int(head_dim) // 2
+        pos = torch.arange(int(seqlen), device=device, dtype=torch.float32)
+        inv_freq = 1.0 / (self._rope_theta ** (torch.arange(0, half, device=device, dtype=torch.float32) / half))
+        ang = torch.einsum("m,d->md", pos, inv_freq)
+        out = (torch.cos(ang).to(dtype).contiguous(), torch.sin(ang).to(dtype).contiguous())
+        self._rope_cache[key] = out
+        return out
+
+
+# --------------------------------------------------------------------------------- kernel wrappers
+_layout_cache: dict = {}
+_workspaces: dict = {}
+
+
+def _as_linear_weight(t: torch.Tensor) -> torch.Tensor:
+    """The reference passes factors transposed ([in, out] = weight.t().contiguous()); the kernels
+    read the nn.Linear layout [out, in].  The transposed copy is made once per tensor object: an
+    entry is valid only while the very tensor it was made from is alive and unmodified (a new
+    tensor may reuse a freed tensor's address)."""
+    import weakref
+
+    key = (t.data_ptr(), tuple(t.shape), t.dtype)
+    hit = _layout_cache.get(key)
+    if hit is not None and hit[0]() is t and hit[1] == t._version:
+        return hit[2]
+    if len(_layout_cache) > 512:
+        _layout_cache.clear()
+    out = t.t().contiguous()
+    _layout_cache[key] = (weakref.ref(t), t._version, out)
+    return out
+
+
+def _workspace(device, dtype, B: int, **sizes):
+    from . import ops
+
+    key = (str(device), dtype, int(B), tuple(sorted(sizes.items())))
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = ops.make_workspace(ops.make_dims(dtype=dtype, B=B, **sizes), device)
+        _workspaces[key] = ws
+    return ws
+
+
+def flashsvd_mlp_dual_split_triton_pcat_s(PCat, GateU, UpU, DownV, DownU, b2=None, *, BT=None, BR=None, BD=None,
+                                          BR2=None, num_warps=None, num_stages=None, workspace_s2d=None):
+    """y[B, L, H] = (silu(p_gate @ GateU) * (p_up @ UpU)) @ DownV @ DownU (+ b2) for PCat =
+    [p_up | p_gate] of one token per sequence.  The tile-size arguments of the reference are
+    accepted and ignored; ``workspace_s2d`` is not needed."""
+    assert PCat.is_cuda and GateU.is_cuda and UpU.is_cuda and DownV.is_cuda and DownU.is_cuda
+    if PCat.ndim != 3:
+        raise ValueError(f"PCat must be [B, L, 2R], got {tuple(PCat.shape)}")
+    B, L, two_r = (int(v) for v in PCat.shape)
+    if two_r % 2 != 0:
+        raise ValueError(f"PCat last dim must be even, got {two_r}")
+    R = two_r // 2
+    if GateU.shape[0] != R:
+        raise ValueError(f"GateU must be [R, D] with R={R}, got {tuple(GateU.shape)}")
+    if UpU.shape != GateU.shape:
+        raise ValueError(f"UpU shape {tuple(UpU.shape)} must match GateU shape {tuple(GateU.shape)}")
+    D = int(GateU.shape[1])
+    if tuple(DownV.shape) != (D, R):
+        raise ValueError(f"DownV must be [D, R]=[{D}, {R}], got {tuple(DownV.shape)}")
+    if DownU.ndim != 2 or DownU.shape[0] != R:
+        raise ValueError(f"DownU must be [R, H] with R={R}, got {tuple(DownU.shape)}")
+    from . import ops
+
+    T = B * L
+    Hd = int(DownU.shape[1])
+    ws = _workspace(PCat.device, PCat.dtype, T, d=Hd, I=D, Ru=R, Rg=R, Rd=R)
+    y = ops.mlp_swiglu_decode(PCat.reshape(T, two_r).contiguous(), _as_linear_weight(GateU), _as_linear_weight(UpU),
+                              _as_linear_weight(DownV), _as_linear_weight(DownU), ws)
+    if b2 is not None:
+        y = y + b2.to(y.dtype)
+    return y.reshape(B, L, Hd)
+
+
+def pack_qkv_shared_bases(Vq, Vk, Vv):
+    """[H|Hk, R, Dh] decode bases -> [R, H*Dh] / [R, Hk*Dh] (rank-major), as the reference packs them."""
+    if not (Vq.is_cuda and Vk.is_cuda and Vv.is_cuda):
+        raise ValueError("pack_qkv_shared_bases expects CUDA tensors.")
+    if Vq.ndim != 3 or Vk.ndim != 3 or Vv.ndim != 3:
+        raise ValueError(f"Expected Vq/Vk/Vv to be 3D [H|Hk,R,Dh], got {tuple(Vq.shape)}/{tuple(Vk.shape)}/{tuple(Vv.shape)}")
+    Dh = int(Vq.shape[2])
+    if Vk.shape[2] != Dh or Vv.shape[2] != Dh:
+        raise ValueError("All bases must share the same head_dim.")
+    return tuple(v.permute(1, 0, 2).reshape(int(v.shape[1]), int(v.shape[0]) * Dh).contiguous() for v in (Vq, Vk, Vv))
+
+
+def reconstruct_qkv_token_shared_prepacked(Pq, Pk, Pv, Vq_flat, Vk_flat, Vv_flat, *, H: int, Hk: int, Dh: int,
+                                           bq=None, bk=None, bv=None):
+    """Q[B,H,Dh], K[B,Hk,Dh], V[B,Hk,Dh] = P* @ V*_flat (+ bias) for the current token."""
+    tensors = (Pq, Pk, Pv, Vq_flat, Vk_flat, Vv_flat)
+    if not all(t.is_cuda for t in tensors):
+        raise ValueError("reconstruct_qkv_token_shared_prepacked expects all tensors on CUDA.")
+    if Pq.ndim != 2 or Pk.ndim != 2 or Pv.ndim != 2:
+        raise ValueError(f"Expected shared Pq/Pk/Pv to be 2D [B,R], got {tuple(Pq.shape)}/{tuple(Pk.shape)}/{tuple(Pv.shape)}")
+    for name, p, v, heads in (("q", Pq, Vq_flat, H), ("k", Pk, Vk_flat, Hk), ("v", Pv, Vv_flat, Hk)):
+        if v.ndim != 2 or tuple(v.shape) != (int(p.shape[1]), int(heads) * int(Dh)):
+            raise ValueError(f"V{name}_flat must be [{int(p.shape[1])}, {int(heads) * int(Dh)}], got {tuple(v.shape)}")
+    from . import ops
+
+    B = int(Pq.shape[0])
+    ws = _workspace(Pq.device, Pq.dtype, B)
+    outs = []
+    for p, v, bias, heads in ((Pq, Vq_flat, bq, H), (Pk, Vk_flat, bk, Hk), (Pv, Vv_flat, bv, Hk)):
+        y = ops.lift(p.contiguous(), _as_linear_weight(v), ws)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        outs.append(y.reshape(B, int(heads), int(Dh)))
+    return tuple(outs)
+
+
+# --------------------------------------------------------------------------------- generation
+@torch.inference_mode()
+def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: int = 64, device=None,
+                  do_sample: bool = False, temperature: float = 0.8, top_p: float = 0.95) -> dict:
+    """Single-prompt greedy generation on a ``DecodeEngine``; returns the reference's result dict
+    (prompt_token_count, generated_token_count, output_ids, completion_ids, text, completion_text).
+    Generation stops after an end-of-sequence token, like the reference loop."""
+    from .engine import DecodeEngine
+
+    if not isinstance(model, DecodeEngine):
+        raise TypeError("generate_text of flashsvd_b200 drives a DecodeEngine")
+    if do_sample:
+        raise NotImplementedError("the decode kernel samples greedily (do_sample=False)")
+    enc = tokenizer(prompt, return_tensors="pt", add_special_tokens=False)
+    input_ids = enc["input_ids"]
+    if int(input_ids.shape[0]) != 1:
+        raise ValueError("generate_text currently supports batch_size=1 only.")
+    prompt_len = int(input_ids.shape[1])
+    max_new_tokens = int(max_new_tokens)
+    if prompt_len + max_new_tokens > model.S_max:
+        raise IndexError(f"prompt of {prompt_len} tokens + {max_new_tokens} new tokens exceeds the cache length {model.S_max}")
+    model.reset()
+    model.prefill(input_ids)
+    if max_new_tokens > 1:
+        model.step(max_new_tokens - 1)
+    new = model.token_log[prompt_len - 1: prompt_len - 1 + max_new_tokens, 0].cpu().tolist() if max_new_tokens else []
+    if model.status() != 0:
+        raise RuntimeError("a device-side wait ran out during generation")
+    eos = getattr(tokenizer, "eos_token_id", None)
+    if eos is not None and int(eos) in new:
+        new = new[: new.index(int(eos)) + 1]
+    output_ids = input_ids[0].tolist() + new
+    return {
+        "prompt_token_count": prompt_len,
+        "generated_token_count": len(new),
+        "output_ids": output_ids,
+        "completion_ids": new,
+        "text": tokenizer.decode(output_ids, skip_special_tokens=False),
+        "completion_text": tokenizer.decode(new, skip_special_tokens=False),
+    }

@@ -33,7 +33,7 @@ extern "C" {
 #define FSVD_ERR_DEVICE_WAIT (-6)
 
 /* Shapes of one model / layer.  Ranks must be multiples of 8, d and I multiples of 8,
- * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}, B <= 4. */
+ * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}, B <= 8 (bf16) / 4 (fp32). */
 typedef struct fsvd_dims {
   int dtype;
   int B;       /* independent sequences */
@@ -76,17 +76,18 @@ int fsvd_version(void);
 const char* fsvd_last_error_string(void);
 /* SM count and opt-in shared memory per block of the current device. */
 int fsvd_device_props(int* sm_count, int* smem_optin_bytes);
-/* Launch geometry: warps per CTA (8 or 16), 16-byte factor loads each lane keeps in flight,
- * grid = number of CTAs (0 = one per SM).  Only compiled (warps, depth) pairs are used as given,
- * otherwise the first variant of the element type.  Defaults: FSVD_NW / FSVD_DEPTH / FSVD_GRID or
- * (8, 16, 0). */
+/* Launch geometry.  warps: 0 or 7 (the kernel runs 7 consumer warps + 1 TMA producer warp per
+ * CTA); depth: slots of the shared-memory ring of 8 KB factor boxes (0 = as many as fit, at most
+ * 21; rounded down to a multiple of 7); grid: number of CTAs (0 = one per SM).  Defaults come
+ * from FSVD_SLOTS / FSVD_GRID or (0, 0). */
 int fsvd_set_launch_config(int warps, int depth, int grid);
 
 /* Stage timeline for profiling (the analogue of the reference's per-module CUDA-event hooks,
  * utils/evaluator.py:553-689).  While a device buffer of at least nstages * grid * 128 bytes is
  * set, every launch records for each (stage, CTA) sixteen 8-byte slots of %globaltimer values:
  * 0 stage entry, 1 grid barrier passed, 2 input vector staged, 3 stage done, 4 vector words
- * arrived, 5 norm reduced, 7 factor blocks streamed.  NULL switches it off. */
+ * arrived, 5 norm reduced, 7 factor boxes consumed, 8 plans made, 10 CTA synchronised,
+ * 11 epilogue done.  NULL switches it off. */
 int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes);
 
 /* ---- workspace -------------------------------------------------------------------------- */
@@ -104,6 +105,13 @@ int fsvd_workspace_status(void* ws, int* device_status);
 int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* residual, void* y,
                       int B, int d_in, int R, int d_out, int dtype,
                       void* ws, size_t ws_bytes, void* stream);
+
+/* y[B,d_out] = (residual +) p[B,R] @ u[d_out,R]^T: one factor, no rank step.  Replaces the
+ * vendor matmuls of reconstruct_qkv_token_shared_prepacked, Q = Pq @ Vq_flat
+ * (reference: kernels/attn/decode/densekv_reconstruct_triton.py:693-760), with u = Vq_flat^T =
+ * the q_u_proj weight as stored. */
+int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B, int R, int d_out,
+              int dtype, void* ws, size_t ws_bytes, void* stream);
 
 /* The same projection for callers that cannot hand over a workspace.  This entry point has no
  * counterpart in the reference.  Its scratch (barrier words + rank-space partial sums) is a
@@ -185,7 +193,7 @@ int fsvd_model_destroy(fsvd_model* m);
 /* Enqueue n_steps greedy decode steps. */
 int fsvd_model_step(fsvd_model* m, int n_steps, void* stream);
 /* Device buffers: tokens[B] (in: token to feed, out: sampled token), seqlens[B],
- * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32, hidden[B,d] fp32. */
+ * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32, hidden[B,d] in the model dtype (returned as an untyped float*). */
 int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
                        int** step_counter, float** logits, float** hidden);
 /* Number of stages of the model's program (sizes the trace buffer). */

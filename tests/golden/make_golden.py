@@ -249,6 +249,59 @@ def main():
     golden["q_zeros"] = pq.zeros.numpy()
     golden["q_dequant"] = d_ref.numpy()
 
+    # 5. host surface: configure_runtime environments and a dense-cache scenario, for the mirror
+    #    in flashsvd_b200/runtime.py
+    import json
+    import os
+
+    from scripts.demo_support import api
+
+    cases = [dict(mode="flashsvd"), dict(mode="hf"), dict(mode="baseline"),
+             dict(mode="FlashSVD", ffn_backend="dual-split-kernel-v2", enable_mlp_graph=False,
+                  enable_flash_dense_attn=False, enable_cutlass_rope_attn=True, graph_alias_output=True,
+                  mlp_graph_scope="mlp", dense_decode_backend="fa2", dense_decode_autotune_scope="layer"),
+             dict(mode="flashsvd", enable_dense_decode_graph=False, dense_decode_backend="triton")]
+    saved = {k: os.environ.get(k) for k in api._RUNTIME_ENV_VARS}
+    env_cases = [{"kwargs": c, "env": api.configure_runtime(**c)} for c in cases]
+    for k, v in saved.items():
+        os.environ.pop(k, None) if v is None else os.environ.__setitem__(k, v)
+    (OUT / "configure_runtime_cases.json").write_text(json.dumps(env_cases, indent=1))
+    report.append(f"configure_runtime: {len(cases)} reference environments saved (15 variables each)")
+
+    class _C2(FlashSVDV15DenseKVCache):
+        def __init__(self, *a, **k):
+            self._seen_tokens = 0
+            super().__init__(*a, **k)
+            self._seen_tokens = 0
+
+    cfg2 = LlamaConfig(hidden_size=32, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2,
+                                    intermediate_size=64, vocab_size=50, rope_theta=10000.0)
+    c2 = _C2(cfg2, max_batch_size=2, max_cache_len=12, device="cpu", dtype=torch.float32)
+    kk = torch.randn(2, 2, 5, 8, generator=gen)
+    vv = torch.randn(2, 2, 5, 8, generator=gen)
+    for li in (0, 1):
+        c2.update(kk + li, vv - li, li, {"cache_position": torch.arange(5)})
+    golden["cache_k_in"] = kk.numpy()
+    golden["cache_v_in"] = vv.numpy()
+    golden["cache_key0"] = c2.key_cache[0].numpy().copy()
+    golden["cache_val1"] = c2.value_cache[1].numpy().copy()
+    golden["cache_seen_after_prefill"] = np.array([c2.get_seq_length()])
+    _, _, sl = c2.prepare_fa2_step(1, batch_size=2, cache_position=None)
+    golden["cache_seqlens_none"] = sl.numpy().copy()
+    _, _, sl = c2.prepare_fa2_step(1, batch_size=2, cache_position=torch.tensor([7]))
+    golden["cache_seqlens_scalar"] = sl.numpy().copy()
+    _, _, sl = c2.prepare_fa2_step(0, batch_size=2, cache_position=torch.tensor([5, 3]))
+    golden["cache_seqlens_rows"] = sl.numpy().copy()
+    c2.advance_after_fa2(1, q_len=1, cache_position=torch.tensor([5]))
+    a1 = c2.get_seq_length()
+    c2.advance_after_fa2(0, q_len=1, cache_position=torch.tensor([5]))
+    a2 = c2.get_seq_length()
+    c2.advance_after_fa2(0, q_len=1, cache_position=None)
+    a3 = c2.get_seq_length()
+    golden["cache_seen_advances"] = np.array([a1, a2, a3])
+    golden["cache_mask_sizes"] = np.array(c2.get_mask_sizes(torch.arange(1), 0))
+    report.append("dense cache scenario (update, prepare_fa2_step x3, advance_after_fa2 x3, get_mask_sizes) saved")
+
     np.savez_compressed(OUT / "reference_pins.npz", **golden)
     (OUT / "PINS.txt").write_text("\n".join(report) + "\n")
     print("\n".join(report))
