@@ -542,7 +542,6 @@ static int launch_small(const Resolved& r, Builder& b, SyncState* sync, cudaStre
   a.part_bytes = b.part_bytes();
   a.vec_bytes = b.vec_bytes();
   a.nslots = slots;
-  a.window = env_int("FSVD_QUIET", 0);
   a.trace = g_trace_bytes >= b.st.size() * (size_t)r.grid * 128 ? g_trace : nullptr;
   a.grid = r.grid;
   a.smem = smem;
@@ -1020,8 +1019,7 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
     a.part_bytes = m->part_bytes;
     a.vec_bytes = m->vec_bytes;
     a.nslots = m->nslots;
-    a.window = env_int("FSVD_QUIET", 0);
-      a.trace = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
+        a.trace = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
     a.grid = m->r.grid;
     a.smem = m->smem;
     a.stream = (cudaStream_t)stream;

@@ -32,7 +32,7 @@ cudaError_t launch_impl(const LaunchArgs& a) {
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, a.prog, a.small ? *a.small : empty_prog, a.maps,
                             a.small_maps ? *a.small_maps : empty_maps, a.small ? 1 : 0, a.nstages,
-                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.window, a.trace);
+                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.trace);
 }
 
 }  // namespace

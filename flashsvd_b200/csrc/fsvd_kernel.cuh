@@ -1,16 +1,17 @@
 // Persistent stage interpreter for single-token decode of low-rank (W = U·V) transformers.
 //
-// Launch geometry: one CTA per SM (cooperative launch), 7 consumer warps + 1 producer warp.
+// Launch geometry: one CTA per SM (cooperative launch), 7 consumer warps + 1 producer warp
+// (7 issuing lanes).
 //
 // Factor stream.  A GEMV stage is cut into units of 16 factor rows x one K segment; units go
 // round-robin to the CTAs.  A unit is a row of boxes, one box = 16 rows x 512 bytes (8 KB), and
 // the boxes of all GEMV stages of the program, in program order, form the CTA's box sequence.
-// The producer warps walk that sequence on their own: box number q goes into ring slot q % NS
+// The producer warp walks that sequence on its own: box number q goes into ring slot q % NS
 // with one cp.async.bulk.tensor (TMA) as soon as the slot's previous content has been released.
 // The factors do not depend on the activations, so the producers run ahead of the consumers by
 // the whole ring (up to 192 KB per SM), across stage boundaries and grid barriers: HBM keeps
 // streaming while the CTAs synchronise.  Slot s is always consumed by warp s % 7 (NS is a
-// multiple of 7) and filled by the one producer lane, so every mbarrier sees its phases in
+// multiple of 7) and filled by producer lane s % 7, so every mbarrier sees its phases in
 // order from a single waiting thread or warp.
 // (Measured on B200: this ring with real lds + mma consumers streams 6.4-6.9 TB/s; a single
 // issuing thread tops out near 3.4 TB/s with 8 KB boxes, two reach the HBM limit.)
@@ -41,7 +42,6 @@
 namespace fsvd {
 
 constexpr int kNWC = kConsumerWarps;
-constexpr int kNPROD = kProducerLanes;   // producer lanes; a power of two
 constexpr int kConsThreads = kNWC * 32;
 constexpr int kThreads = (kNWC + kProducerWarps) * 32;
 constexpr long long kWaitLimitClk = 4000000000ll;  // ~2 s of SM clocks
@@ -595,7 +595,6 @@ struct Ring {
   uint32_t full, empty;   // shared-memory addresses of the mbarrier arrays
   uint32_t data;          // shared-memory address of slot 0
   int ns;                 // slots, a multiple of kNWC (or fewer than kNWC)
-  int window;             // 1: producers pause while the consumers are in a latency-bound phase
 };
 
 // The producer warp.  Lane L < N (N = 7, or the slot count of a smaller ring) owns the boxes
@@ -740,12 +739,6 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
     cons_sync();
   }
   trace_mark(cx.trow, 2);
-  if (tid == 0) cx.giveup[3] = 0;   // quiet phase over: the producers may issue again
-  if (cx.trow) {
-    const int i0 = cx.giveup[1], i1 = cx.giveup[2];
-    cx.trow[14] = (unsigned long long)((i0 > i1 ? i0 : i1) - (int)cx.seq_base);   // boxes issued ahead
-    cx.trow[15] = (unsigned long long)bp.nbox;
-  }
 
   // ---- this warp's boxes: local box l belongs to warp (seq_base + l) % 8
   const int g = lane >> 2, t = lane & 3;
@@ -865,9 +858,6 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
   if (cur_io >= 0) flush();
   trace_mark(cx.trow, 7);
   cons_sync();
-  // every warp has consumed its boxes: the quiet phase begins (it ends when the next GEMV stage
-  // starts to consume)
-  if (tid == 0) cx.giveup[3] = 1;
   trace_mark(cx.trow, 10);
 
   // ---- add the warps' partial sums in chunk order and run the epilogue
@@ -1252,7 +1242,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant__ SmallProgram small,
                    const unsigned char* __restrict__ maps_global, const __grid_constant__ SmallMaps small_maps,
                    int use_small, int nstages, SyncState* sync, int xstride, int part_bytes,
-                   int vec_bytes, int nslots, int window, unsigned long long* trace) {
+                   int vec_bytes, int nslots, unsigned long long* trace) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -1271,7 +1261,6 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
   rg.empty = rg.full + kMaxSlots * 8;
   rg.data = smem_u32(ring);
   rg.ns = nslots;
-  rg.window = window;
 
   // Boxes past the K range hold zeros and multiply whatever follows the input in the staged
   // vector, so that memory must hold finite numbers from the start.
@@ -1304,8 +1293,6 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
   if (tid == 0) {
     flags_sh[0] = 0;   // warps of this CTA that have arrived at the pending grid barrier
     flags_sh[1] = 0;   // set when a ring wait ran out: nobody waits for the ring again
-    flags_sh[2] = flags_sh[3] = 0;   // boxes issued by the producers (timeline aid)
-    flags_sh[4] = 0;                 // quiet phase flag
     for (int i = 0; i < nslots; ++i) {
       mbar_init(rg.full + i * 8, 1);
       mbar_init(rg.empty + i * 8, 1);

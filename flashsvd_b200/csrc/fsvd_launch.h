@@ -11,7 +11,7 @@ struct LaunchArgs {
   const fsvd::SmallMaps* small_maps;  // by-value descriptors of a by-value program
   int nstages;
   fsvd::SyncState* sync;
-  int xstride, part_bytes, vec_bytes, nslots, window;
+  int xstride, part_bytes, vec_bytes, nslots;
   unsigned long long* trace;
   int grid;
   size_t smem;

@@ -115,10 +115,7 @@ enum DeviceStatus : int {
 // 8 warps per CTA: with more, the register file leaves 168 registers per thread and the
 // interpreter spills; 256 threads get 255.
 constexpr int kConsumerWarps = 7;      // warps that multiply
-constexpr int kProducerWarps = 1;      // warp that issues the TMA copies ...
-constexpr int kProducerLanes = 1;      // ... from one lane: lanes of one warp that wait on different
-                                       // barriers diverge and serialise (measured: 1 lane 354, 2 lanes
-                                       // 349, 4 lanes 327, 8 lanes 298 tokens/s on the 7B-shape model)
+constexpr int kProducerWarps = 1;      // warp that issues the TMA copies, from one lane per consumer warp
 constexpr int kUnitRows = 16;          // factor rows of one unit = rows of one box
 constexpr int kBoxRowBytes = 512;      // bytes of one box row (256 bf16 / 128 fp32 columns)
 constexpr int kBoxBytes = kUnitRows * kBoxRowBytes;

@@ -1,0 +1,167 @@
+"""Low-rank Llama attention / MLP modules with the sub-module names of the reference models.
+
+The reference's ``SVD_LlamaAttention`` / ``SVD_LlamaMLP`` (built by
+src/methods/svdllm/SVDLLM_flashsvd.py:264-286, factor shapes utils/model_utils.py:637-643) hold
+every projection as two bias-free ``nn.Linear`` factors: ``*_v_proj`` [d_in -> r] and ``*_u_proj``
+[r -> d_out].  These classes keep that surface (names, shapes, rank formula, call signature) and
+run single-token decode (one new token per sequence, CUDA tensors) through the C ABI; prompts
+longer than one token take plain matmuls on the GPU, which are outside the decode path this
+package accelerates.  There is no CPU compute path: CPU tensors raise.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+
+def svd_rank(out_features: int, in_features: int, ratio: float) -> int:
+    """Rank that keeps ``ratio`` of the dense parameters: int(out * in * ratio / (out + in))
+    (src/methods/svdllm/SVDLLM_flashsvd.py:286)."""
+    return int(out_features * in_features * ratio / (out_features + in_features))
+
+
+def _decode_ok(x: torch.Tensor) -> bool:
+    if not x.is_cuda:
+        raise RuntimeError("flashsvd_b200 modules run on CUDA tensors only (there is no CPU path)")
+    tokens = x.shape[0] * x.shape[1]
+    return x.shape[1] == 1 and x.dtype in (torch.bfloat16, torch.float32) and \
+        tokens <= (8 if x.dtype == torch.bfloat16 else 4)
+
+
+class _WithWorkspace(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self._ws = {}
+        self._packed = {}
+
+    def _workspace(self, x: torch.Tensor, B: int, **sizes):
+        key = (str(x.device), x.dtype, B)
+        ws = self._ws.get(key)
+        if ws is None:
+            ws = ops.make_workspace(ops.make_dims(dtype=x.dtype, B=B, **sizes), x.device)
+            self._ws[key] = ws
+        return ws
+
+    def _cat(self, name: str, *linears):
+        """cat of the input-side factor weights, rebuilt when one of them changes."""
+        key = tuple((l.weight.data_ptr(), l.weight._version, l.weight.dtype) for l in linears)
+        hit = self._packed.get(name)
+        if hit is None or hit[0] != key:
+            hit = (key, torch.cat([l.weight for l in linears], 0).contiguous())
+            self._packed[name] = hit
+        return hit[1]
+
+
+class SVD_LlamaMLP(_WithWorkspace):
+    def __init__(self, hidden_size: int, intermediate_size: int, hidden_act: str = "silu", ratio: float = 1.0,
+                 compat_ranks: bool = False):
+        super().__init__()
+        if hidden_act != "silu":
+            raise ValueError(f"unsupported activation {hidden_act!r} (the fused kernel computes SiLU)")
+        self.hidden_size, self.intermediate_size, self.ratio = hidden_size, intermediate_size, ratio
+        r = svd_rank(intermediate_size, hidden_size, ratio)
+        r -= r % 8 if not compat_ranks else 0
+        self.low_rank = r
+        self.gate_v_proj = nn.Linear(hidden_size, r, bias=False)
+        self.gate_u_proj = nn.Linear(r, intermediate_size, bias=False)
+        self.up_v_proj = nn.Linear(hidden_size, r, bias=False)
+        self.up_u_proj = nn.Linear(r, intermediate_size, bias=False)
+        self.down_v_proj = nn.Linear(intermediate_size, r, bias=False)
+        self.down_u_proj = nn.Linear(r, hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B, L, d = x.shape
+        if _decode_ok(x):
+            ws = self._workspace(x, B, d=d, I=self.intermediate_size, Ru=self.up_u_proj.in_features,
+                                 Rg=self.gate_u_proj.in_features, Rd=self.down_v_proj.out_features)
+            y = ops.mlp_swiglu_decode(x.reshape(B, d), self.gate_u_proj.weight, self.up_u_proj.weight,
+                                      self.down_v_proj.weight, self.down_u_proj.weight, ws,
+                                      upgate_v=self._cat("upgate", self.up_v_proj, self.gate_v_proj))
+            return y.reshape(B, 1, d)
+        gate = self.gate_u_proj(self.gate_v_proj(x))
+        up = self.up_u_proj(self.up_v_proj(x))
+        return self.down_u_proj(self.down_v_proj(F.silu(gate) * up))
+
+
+def _rope_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Half-split rotation of x[..., L, Dh] by cos/sin[L, Dh/2] (first-half angles)."""
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+
+class SVD_LlamaAttention(_WithWorkspace):
+    def __init__(self, config, ratio: float = 1.0, layer_idx: int = 0, compat_ranks: bool = False,
+                 compat_attention: bool = False):
+        super().__init__()
+        self.config, self.layer_idx, self.ratio = config, int(layer_idx), ratio
+        self.hidden_size = d = config.hidden_size
+        self.num_heads = H = config.num_attention_heads
+        self.num_key_value_heads = Hk = getattr(config, "num_key_value_heads", H)
+        self.num_key_value_groups = H // Hk
+        self.head_dim = Dh = getattr(config, "head_dim", None) or d // H
+        self.max_position_embeddings = getattr(config, "max_position_embeddings", 2048)
+        self.use_lowrank_cache = False
+
+        def rank(out_f, in_f):
+            r = svd_rank(out_f, in_f, ratio)
+            return r - (r % 8 if not compat_ranks else 0)
+
+        self.low_rank = rq = rank(H * Dh, d)
+        rk = rank(Hk * Dh, d)
+        self.q_v_proj, self.q_u_proj = nn.Linear(d, rq, bias=False), nn.Linear(rq, H * Dh, bias=False)
+        self.k_v_proj, self.k_u_proj = nn.Linear(d, rk, bias=False), nn.Linear(rk, Hk * Dh, bias=False)
+        self.v_v_proj, self.v_u_proj = nn.Linear(d, rk, bias=False), nn.Linear(rk, Hk * Dh, bias=False)
+        self.o_v_proj, self.o_u_proj = nn.Linear(H * Dh, rq, bias=False), nn.Linear(rq, d, bias=False)
+
+    def _qkv_rank_tuple(self):
+        return self.q_u_proj.in_features, self.k_u_proj.in_features, self.v_u_proj.in_features
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask=None, position_ids=None, past_key_values=None,
+                cache_position: Optional[torch.Tensor] = None, position_embeddings=None, **kwargs):
+        """Returns (attn_output[B, L, d], None) like the transformers attention protocol.
+        ``past_key_values`` is a ``runtime.FlashSVDV15DenseKVCache``."""
+        x, cache = hidden_states, past_key_values
+        if cache is None:
+            raise ValueError("SVD_LlamaAttention needs past_key_values (a FlashSVDV15DenseKVCache)")
+        B, L, d = x.shape
+        H, Hk, Dh, li = self.num_heads, self.num_key_value_heads, self.head_dim, self.layer_idx
+        cache._ensure_layer_spec(li, h=Hk, dh=Dh)
+        cos, sin = cache.get_rope_tables(cache.max_cache_len, Dh, device=x.device, dtype=x.dtype)
+        if _decode_ok(x) and B == cache.max_batch_size:
+            kc, vc, seqlens = cache.prepare_fa2_step(li, batch_size=B, cache_position=cache_position)
+            ws = self._workspace(x, B, d=d, H=H, Hk=Hk, Dh=Dh, Rq=self.q_u_proj.in_features,
+                                 Rk=self.k_u_proj.in_features, Rv=self.v_u_proj.in_features,
+                                 Ro=self.o_v_proj.out_features, S_max=cache.max_cache_len)
+            q = ops.qkv_rope_append(x.reshape(B, d), self._cat("qkv", self.q_v_proj, self.k_v_proj, self.v_v_proj),
+                                    self.q_u_proj.weight, self.k_u_proj.weight, self.v_u_proj.weight, cos, sin,
+                                    kc, vc, seqlens, ws, num_heads=H, num_kv_heads=Hk, head_dim=Dh,
+                                    ranks=self._qkv_rank_tuple())
+            a = ops.flash_decode(q, kc, vc, seqlens, ws, seqlen_add=1)
+            y = ops.lowrank_proj(a.reshape(B, H * Dh), self.o_v_proj.weight, self.o_u_proj.weight, ws)
+            cache.advance_after_fa2(li, q_len=1, cache_position=cache_position)
+            cache._layer_initialized[li] = True
+            return y.reshape(B, 1, d), None
+        # prompt processing: plain matmuls on the GPU, keys stored after RoPE
+        if cache_position is None:
+            cache_position = torch.arange(cache.get_seq_length(), cache.get_seq_length() + L, device=x.device)
+        pos = cache_position.to(x.device).long()
+        q = self.q_u_proj(self.q_v_proj(x)).view(B, L, H, Dh).transpose(1, 2)
+        k = self.k_u_proj(self.k_v_proj(x)).view(B, L, Hk, Dh).transpose(1, 2)
+        v = self.v_u_proj(self.v_v_proj(x)).view(B, L, Hk, Dh).transpose(1, 2)
+        q, k = _rope_half(q, cos[pos], sin[pos]), _rope_half(k, cos[pos], sin[pos])
+        kk, vv = cache.update(k, v, li, {"cache_position": pos})
+        S = kk.shape[2]
+        if Hk != H:
+            kk = kk.repeat_interleave(H // Hk, 1)
+            vv = vv.repeat_interleave(H // Hk, 1)
+        mask = torch.arange(S, device=x.device)[None, :] <= pos[:, None]
+        a = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask[None, None], scale=1.0 / math.sqrt(Dh))
+        y = self.o_u_proj(self.o_v_proj(a.transpose(1, 2).reshape(B, L, H * Dh)))
+        return y, None
