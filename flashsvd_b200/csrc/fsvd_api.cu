@@ -233,7 +233,9 @@ struct Builder {
     s.rot = (int)(cum_items % grid);
     cum_items += groups * cph;
     has_attn = true;
-    const int need = kConsumerWarps * GI * (s.Dh + 2);
+    // partial results of the warps + per-warp score tiles [rows][33] and probabilities [rows]
+    const int rows = GI == 1 ? 20 : 24;
+    const int need = kConsumerWarps * GI * (s.Dh + 2) + kConsumerWarps * rows * 34;
     if (need > attn_rec_floats) attn_rec_floats = need;
   }
   // GEMV stage.  Units (16 rows x one K segment) go round-robin to the CTAs; with split_k the K

@@ -953,6 +953,11 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
   const size_t kv_row = (size_t)st.Hk * Dh;
   const bool qT = (st.flags & SF_IN_T) != 0;
   const int rec = Dh + 2;                  // floats of one partial result: acc[Dh], max, sum
+  constexpr int ROWS = GI * KMAX;          // scores of one chunk
+  static_assert(ROWS <= 32, "one score per lane");
+  // per-warp scratch behind the partial results: score tile [ROWS][33] and probabilities [ROWS]
+  float* const tile = sh + kNWC * GI * rec + warp * (ROWS * 34);
+  float* const pbuf = tile + ROWS * 33;
 
   for (int hs = first_item(blockIdx.x, st.rot % grid, grid); hs < nslice; hs += grid) {
     const int part = hs % cph;
@@ -997,7 +1002,9 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
     }
     for (int c0 = j0; c0 < j1; c0 += KMAX) {
       if (c0 > j0) fetch(c0);
-      float sc[GI][KMAX];
+      // Partial dot products (this lane's dims) go to a [key][lane] tile in shared memory; lane r
+      // then adds row r, so that every lane owns one full score: softmax costs one exp per lane
+      // and 2 x 5 shuffles per head instead of 5 shuffles and one exp per key.
       const char* vp = vbase + (size_t)c0 * row_bytes;
 #pragma unroll
       for (int u = 0; u < KMAX; ++u) {
@@ -1008,41 +1015,55 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
           float s2 = 0.f;
 #pragma unroll
           for (int d = 0; d < DPL; ++d) s2 = fmaf(q[g][d], kf[d], s2);
-          sc[g][u] = s2;
+          tile[(g * KMAX + u) * 33 + lane] = s2;
         }
         vr[u].load(vp, c0 + u < j1);
         vp += row_bytes;
       }
+      __syncwarp();
+      float sa = 0.f, sb = 0.f, sc2 = 0.f, sd = 0.f;
+      if (lane < ROWS) {
+        const float* row = tile + lane * 33;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          sa += row[i];
+          sb += row[i + 1];
+          sc2 += row[i + 2];
+          sd += row[i + 3];
+        }
+      }
+      const int gu = lane / KMAX, uu = lane - gu * KMAX;   // head and key of this lane's score
+      const bool valid = lane < ROWS && c0 + uu < j1;
+      const float score = valid ? ((sa + sb) + (sc2 + sd)) * st.scale : -INFINITY;
+      float pmine = 0.f;
 #pragma unroll
       for (int g = 0; g < GI; ++g) {
-        float cm = -INFINITY;
-#pragma unroll
-        for (int u = 0; u < KMAX; ++u) {
-          sc[g][u] = (c0 + u < j1) ? warp_sum(sc[g][u]) * st.scale : -INFINITY;
-          cm = fmaxf(cm, sc[g][u]);
-        }
+        const bool mine = valid && gu == g;
+        const float cm = warp_max(mine ? score : -INFINITY);
         const float mn = fmaxf(m[g], cm);
         const float corr = (m[g] == -INFINITY) ? 0.f : expf(m[g] - mn);
-        float ls = 0.f;
-#pragma unroll
-        for (int u = 0; u < KMAX; ++u) {
-          sc[g][u] = (c0 + u < j1) ? expf(sc[g][u] - mn) : 0.f;
-          ls += sc[g][u];
-        }
+        const float pg = mine ? expf(score - mn) : 0.f;
+        const float ls = warp_sum(pg);
+        if (mine) pmine = pg;
         l[g] = l[g] * corr + ls;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) acc[g][d] *= corr;
         m[g] = mn;
       }
+      if (lane < ROWS) pbuf[lane] = pmine;
+      __syncwarp();
 #pragma unroll
       for (int u = 0; u < KMAX; ++u) {
         float vf[DPL];
         vr[u].unpack(vf);
 #pragma unroll
-        for (int g = 0; g < GI; ++g)
+        for (int g = 0; g < GI; ++g) {
+          const float pg = pbuf[g * KMAX + u];
 #pragma unroll
-          for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(sc[g][u], vf[d], acc[g][d]);
+          for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(pg, vf[d], acc[g][d]);
+        }
       }
+      __syncwarp();   // the tile is rewritten by the next chunk
     }
     // ---- the 8 partial results of the CTA meet in shared memory: sh[(warp * GI + g) * rec ...]
 #pragma unroll
