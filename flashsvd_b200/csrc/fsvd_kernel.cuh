@@ -1379,20 +1379,12 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
         }
       }
       if (st.flags & SF_ARRIVE) {
-        // Grid-barrier arrival, warp by warp: each warp publishes its own stores and counts itself
-        // in shared memory; the last warp of the CTA adds the CTA to the global count.
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-          unsigned old;
-          asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
-                       : "=r"(old) : "r"(smem_u32(flags_sh)) : "memory");
-          if (old == (unsigned)kNWC - 1u) {
-            flags_sh[0] = 0;
-            // every warp fenced its stores before it counted itself (acq_rel above), so a
-            // relaxed add is enough to publish the CTA
-            asm volatile("red.relaxed.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
-          }
+        // Grid-barrier arrival: one fence and one add per CTA.
+        cons_sync();
+        if (tid == 0) {
+          // the CTA barrier orders every thread's stores before this fence (cumulativity)
+          asm volatile("fence.acq_rel.gpu;" ::: "memory");
+          asm volatile("red.relaxed.gpu.global.add.u64 [%0], 1;" ::"l"(&sync->arrivals) : "memory");
         }
       }
       trace_mark(trow, 3);
