@@ -204,10 +204,26 @@ __device__ __forceinline__ float warp_max(float v) {
 // ----------------------------------------------------------------------------- GEMV stage
 // Operands of an item's epilogue that do not depend on the accumulators; fetched when the item
 // starts so that their latency hides behind the item's tiles.
+// The operands stay as raw bits until the epilogue: converting a loaded bf16 to float right
+// away would stall the warp on the load it was meant to hide.
 struct EpiAux {
-  float a0, a1;
+  unsigned r0, r1;   // raw operand bits: element of type T (bf16 in the low half) or fp32
   int pos;
 };
+template <typename T>
+__device__ __forceinline__ unsigned raw_ld(const void* p, size_t i);
+template <>
+__device__ __forceinline__ unsigned raw_ld<__nv_bfloat16>(const void* p, size_t i) {
+  return (unsigned)__ldcg(reinterpret_cast<const unsigned short*>(p) + i);
+}
+template <>
+__device__ __forceinline__ unsigned raw_ld<float>(const void* p, size_t i) {
+  return __ldcg(reinterpret_cast<const unsigned*>(p) + i);
+}
+template <typename T>
+__device__ __forceinline__ float raw_to_float(unsigned r) {
+  return sizeof(T) == 2 ? __uint_as_float(r << 16) : __uint_as_float(r);
+}
 // Cache positions seqlens[b] of the program's sequence-length array, read once per launch into
 // shared memory (the array only changes in the last stage of a step).
 struct PosCache {
@@ -221,21 +237,21 @@ __device__ __forceinline__ int cached_pos(const PosCache& pc, const int* seqlens
 template <typename T>
 __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiAux& ax, const PosCache pc) {
   using X = TT<T>;
-  ax.a0 = ax.a1 = 0.f;
+  ax.r0 = ax.r1 = 0u;
   ax.pos = 0;
   switch (st.epi) {
     case EPI_RESID: {
       const size_t i = (size_t)b * st.P + p;
-      if (st.flags & SF_RESID_T) ax.a0 = X::ldcg(st.resid, i);
-      else ax.a0 = __ldcg(reinterpret_cast<const float*>(st.resid) + i);
+      if (st.flags & SF_RESID_T) ax.r0 = raw_ld<T>(st.resid, i);
+      else ax.r0 = raw_ld<float>(st.resid, i);
     } break;
     case EPI_ROPE_Q:
     case EPI_ROPE_K: {
       const int half = st.rope_half;
       const int j = p % half;
       ax.pos = cached_pos(pc, st.seqlens, b);
-      ax.a0 = X::ld(st.cos_tab, (size_t)ax.pos * half + j);
-      ax.a1 = X::ld(st.sin_tab, (size_t)ax.pos * half + j);
+      ax.r0 = raw_ld<T>(st.cos_tab, (size_t)ax.pos * half + j);
+      ax.r1 = raw_ld<T>(st.sin_tab, (size_t)ax.pos * half + j);
     } break;
     case EPI_V:
       ax.pos = cached_pos(pc, st.seqlens, b);
@@ -263,7 +279,8 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
     } break;
     case EPI_RESID: {
       const size_t i = (size_t)b * P + p;
-      const float v = X::rnd(ax.a0 + X::rnd(a));
+      const float res = (st.flags & SF_RESID_T) ? raw_to_float<T>(ax.r0) : __uint_as_float(ax.r0);
+      const float v = X::rnd(res + X::rnd(a));
       if (st.flags & SF_OUT_T) X::st(st.out, i, v);
       else reinterpret_cast<float*>(st.out)[i] = v;
     } break;
@@ -280,7 +297,7 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
       const int half = st.rope_half;
       const int h = p / half, j = p - h * half;
       const int pos = ax.pos;
-      const float c = ax.a0, sn = ax.a1;
+      const float c = raw_to_float<T>(ax.r0), sn = raw_to_float<T>(ax.r1);
       const float x1 = X::rnd(a), x2 = X::rnd(bsum);
       const float o1 = X::rnd(X::rnd(x1 * c) - X::rnd(x2 * sn));
       const float o2 = X::rnd(X::rnd(x2 * c) + X::rnd(x1 * sn));
@@ -716,7 +733,7 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
     p = grp * kUnitRows + r;
   };
   EpiAux ax0, ax1;
-  ax0.a0 = ax0.a1 = ax1.a0 = ax1.a1 = 0.f;
+  ax0.r0 = ax0.r1 = ax1.r0 = ax1.r1 = 0u;
   ax0.pos = ax1.pos = 0;
   {
     int j, b, r, seg, p;
@@ -1333,7 +1350,6 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
     producer_loop<T>(prog, nstages, maps, rg, lane, sync, giveup);
   } else {
     // ---------------- consumers
-    const int wrank = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * kNWC;
     unsigned seq_base = 0;
     PosCache pc;
     pc.ptr = *reinterpret_cast<const int* const*>(flags_sh + 24);
