@@ -364,6 +364,18 @@ static int check_dims(const fsvd_dims& D) {
   return 0;
 }
 
+// True when q_u, k_u and v_u lie back to back in memory with one rank: they then form one
+// [(H + 2 Hk) * Dh, R] matrix and the three lifts run as one stage (packing.pack_layer and
+// synthetic.random_packed_layers lay them out like this).
+static bool qkv_lifts_packed(const void* q_u, const void* k_u, const void* v_u, int H, int Hk, int Dh, int Rq,
+                             int Rk, int Rv, int esize) {
+  if (Rq != Rk || Rq != Rv || env_int("FSVD_FUSE_QKV", 1) == 0) return false;
+  const char* q = reinterpret_cast<const char*>(q_u);
+  const char* k = reinterpret_cast<const char*>(k_u);
+  const char* v = reinterpret_cast<const char*>(v_u);
+  return k == q + (size_t)H * Dh * Rq * esize && v == k + (size_t)Hk * Dh * Rq * esize;
+}
+
 struct LayerIO {
   const void* x_in;    // hidden state [B, d] of type T read by the first RMSNorm and residual
   bool x_in_barrier;   // x_in is written by the preceding stage of the same program
@@ -396,34 +408,49 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     s.out = pa;
   }
   const int segs1 = b.st.back().segs;
-  {  // 2. lift q with rotary
+  if (qkv_lifts_packed(Lw.q_u, Lw.k_u, Lw.v_u, D.H, D.Hk, D.Dh, D.Rq, D.Rk, D.Rv, b.esize)) {
+    // 2-4. q, k and v lifts as one stage over the packed [q_u; k_u; v_u] matrix
     Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
-                      D.H * half, D.Rq, D.Rq, false, half);
+                      (D.H + 2 * D.Hk) * half, D.Rq, D.Rq, false, half);
     b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
     s.rope_half = half;
     s.xA_off = s.xB_off = 0;
-    s.epi = EPI_ROPE_Q;
+    s.epi = EPI_QKV;
     s.out = qbuf;
-    s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
-    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
-  }
-  {  // 3. lift k with rotary into the cache
-    Stage& s = b.gemv(Lw.k_u, reinterpret_cast<const char*>(Lw.k_u) + (size_t)half * D.Rk * b.esize,
-                      D.Hk * half, D.Rk, D.Rk, false, half);
-    s.rope_half = half;
-    s.xA_off = s.xB_off = D.Rq;
-    s.epi = EPI_ROPE_K;
     s.cache = Lw.k_cache;
+    s.vcache = Lw.v_cache;
     s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
     s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
-  }
-  {  // 4. lift v into the cache
-    Stage& s = b.gemv(Lw.v_u, nullptr, D.Hk * D.Dh, D.Rv, D.Rv, false);
-    s.xA_off = D.Rq + D.Rk;
-    s.epi = EPI_V;
-    s.cache = Lw.v_cache;
-    s.seqlens = io.seqlens;
-    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+  } else {
+    {  // 2. lift q with rotary
+      Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
+                        D.H * half, D.Rq, D.Rq, false, half);
+      b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
+      s.rope_half = half;
+      s.xA_off = s.xB_off = 0;
+      s.epi = EPI_ROPE_Q;
+      s.out = qbuf;
+      s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+      s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+    }
+    {  // 3. lift k with rotary into the cache
+      Stage& s = b.gemv(Lw.k_u, reinterpret_cast<const char*>(Lw.k_u) + (size_t)half * D.Rk * b.esize,
+                        D.Hk * half, D.Rk, D.Rk, false, half);
+      s.rope_half = half;
+      s.xA_off = s.xB_off = D.Rq;
+      s.epi = EPI_ROPE_K;
+      s.cache = Lw.k_cache;
+      s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+      s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+    }
+    {  // 4. lift v into the cache
+      Stage& s = b.gemv(Lw.v_u, nullptr, D.Hk * D.Dh, D.Rv, D.Rv, false);
+      s.xA_off = D.Rq + D.Rk;
+      s.epi = EPI_V;
+      s.cache = Lw.v_cache;
+      s.seqlens = io.seqlens;
+      s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
+    }
   }
   {  // 5. attention over the cache including the token just appended
     Stage s = b.blank();

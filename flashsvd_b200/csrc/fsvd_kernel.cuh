@@ -256,6 +256,15 @@ __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiA
     case EPI_V:
       ax.pos = cached_pos(pc, st.seqlens, b);
       break;
+    case EPI_QKV: {
+      const int half = st.rope_half;
+      ax.pos = cached_pos(pc, st.seqlens, b);
+      if (p < (st.H + st.Hk) * half) {   // q and k rows rotate
+        const int j = p % half;
+        ax.r0 = raw_ld<T>(st.cos_tab, (size_t)ax.pos * half + j);
+        ax.r1 = raw_ld<T>(st.sin_tab, (size_t)ax.pos * half + j);
+      }
+    } break;
     default:
       break;
   }
@@ -321,6 +330,36 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
       const int pos = ax.pos;
       if (pos < st.S_max)
         X::st(st.cache, ((size_t)b * st.S_max + pos) * ((size_t)st.Hk * st.Dh) + p, X::rnd(a));
+    } break;
+    case EPI_QKV: {
+      const int half = st.rope_half, pos = ax.pos;
+      const int hh = p / half, j = p - hh * half;   // head over [q heads | k heads | v heads]
+      const float x1 = X::rnd(a), x2 = X::rnd(bsum);
+      if (hh < st.H + st.Hk) {
+        const float c = raw_to_float<T>(ax.r0), sn = raw_to_float<T>(ax.r1);
+        const float o1 = X::rnd(X::rnd(x1 * c) - X::rnd(x2 * sn));
+        const float o2 = X::rnd(X::rnd(x2 * c) + X::rnd(x1 * sn));
+        if (hh < st.H) {
+          const size_t base = ((size_t)b * st.H + hh) * st.Dh + j;
+          if (st.flags & SF_OUT_T) {
+            X::st(st.out, base, o1);
+            X::st(st.out, base + half, o2);
+          } else {
+            float* q = reinterpret_cast<float*>(st.out);
+            q[base] = o1;
+            q[base + half] = o2;
+          }
+        } else if (pos < st.S_max) {
+          const size_t base = (((size_t)b * st.S_max + pos) * st.Hk + (hh - st.H)) * st.Dh + j;
+          X::st(st.cache, base, o1);
+          X::st(st.cache, base + half, o2);
+        }
+      } else if (pos < st.S_max) {
+        void* vc = const_cast<void*>(st.vcache);
+        const size_t base = (((size_t)b * st.S_max + pos) * st.Hk + (hh - st.H - st.Hk)) * st.Dh + j;
+        X::st(vc, base, x1);
+        X::st(vc, base + half, x2);
+      }
     } break;
     default:
       break;
@@ -813,6 +852,10 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
       const int uidx = bp.first + j * grid;
       const int seg = uidx % segs;
       xcol0 = (op ? st.xB_off : st.xA_off) + seg * cps * BOXCOLS;
+      if (st.epi == EPI_QKV) {   // segs == 1: uidx is the row group; the part's input starts at part * K
+        const int p0 = uidx * kUnitRows, half = st.rope_half;
+        xcol0 += ((p0 >= st.H * half) + (p0 >= (st.H + st.Hk) * half)) * st.K;
+      }
     }
     bool ok = mbar_wait(cx.ring.full + slot * 8, (uint32_t)round & 1u, cx.sync, cx.giveup, cx.s);
     ok = __all_sync(0xffffffffu, ok);

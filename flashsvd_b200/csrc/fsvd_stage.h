@@ -34,6 +34,9 @@ enum Epilogue : int {
   EPI_ROPE_Q = 4,   // rotate (accA, accB) = dims (j, j+half) of a head, store to q buffer
   EPI_ROPE_K = 5,   // same rotation, store into the key cache at position seqlens[b]
   EPI_V = 6,        // store rnd(acc) into the value cache at position seqlens[b]
+  EPI_QKV = 7,      // q, k and v lifts in one stage over the packed [q_u; k_u; v_u] matrix: logical rows
+                    // [0, H*half) are ROPE_Q, the next Hk*half ROPE_K (cache), the last Hk*half the
+                    // value row halves (vcache); the input of part i starts at element i * K
 };
 
 enum VecLoad : int {

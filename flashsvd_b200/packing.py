@@ -22,12 +22,21 @@ def pack_layer(w: dict, *, device, dtype) -> dict:
     def dev(t):
         return t.detach().to(device=device, dtype=dtype).contiguous()
 
+    # q_u, k_u and v_u back to back in one allocation: with equal ranks the kernels then run the
+    # three lifts as one stage over the packed matrix (the views below are ordinary row slices)
+    q_u, k_u, v_u = w["q_u"], w["k_u"], w["v_u"]
+    if q_u.shape[1] == k_u.shape[1] == v_u.shape[1]:
+        qkv_u = dev(torch.cat([q_u, k_u, v_u], dim=0))
+        nq, nk = q_u.shape[0], k_u.shape[0]
+        q_u, k_u, v_u = qkv_u[:nq], qkv_u[nq:nq + nk], qkv_u[nq + nk:]
+    else:
+        q_u, k_u, v_u = dev(q_u), dev(k_u), dev(v_u)
     return {
         "ln1_w": dev(w["ln1"]),
         "qkv_v": dev(torch.cat([w["q_v"], w["k_v"], w["v_v"]], dim=0)),
-        "q_u": dev(w["q_u"]),
-        "k_u": dev(w["k_u"]),
-        "v_u": dev(w["v_u"]),
+        "q_u": q_u,
+        "k_u": k_u,
+        "v_u": v_u,
         "o_v": dev(w["o_v"]),
         "o_u": dev(w["o_u"]),
         "ln2_w": dev(w["ln2"]),

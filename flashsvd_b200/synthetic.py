@@ -48,6 +48,15 @@ class ModelShape:
 LLAMA7B_SVD50 = ModelShape()
 
 
+def _qkv_u(w, HD, KD, shape):
+    """q_u / k_u / v_u, back to back in one allocation when the ranks agree (packing.pack_layer)."""
+    if shape.Rq == shape.Rk == shape.Rv:
+        t = w(HD + 2 * KD, shape.Rq)
+        t[HD:] *= 1.0   # same distribution for all three parts
+        return {"q_u": t[:HD], "k_u": t[HD:HD + KD], "v_u": t[HD + KD:]}
+    return {"q_u": w(HD, shape.Rq), "k_u": w(KD, shape.Rk), "v_u": w(KD, shape.Rv)}
+
+
 def random_packed_layers(shape: ModelShape, *, device, dtype, seed: int = 0, share_pairs: bool = False):
     """Per-layer tensors in the layout of ``packing.pack_layer``, drawn directly on the device.
     ``share_pairs``: layers (2i, 2i+1) share every input-side factor tensor (basis sharing,
@@ -71,7 +80,7 @@ def random_packed_layers(shape: ModelShape, *, device, dtype, seed: int = 0, sha
             down_v = w(shape.Rd, I)
         layers.append({
             "ln1_w": torch.ones(d, device=device, dtype=dtype),
-            "qkv_v": qkv_v, "q_u": w(HD, shape.Rq), "k_u": w(KD, shape.Rk), "v_u": w(KD, shape.Rv),
+            "qkv_v": qkv_v, **_qkv_u(w, HD, KD, shape),
             "o_v": o_v, "o_u": w(d, shape.Ro),
             "ln2_w": torch.ones(d, device=device, dtype=dtype),
             "upgate_v": upgate_v, "gate_u": w(I, shape.Rg), "up_u": w(I, shape.Ru),
