@@ -14,6 +14,7 @@ LIB_PATH = PKG / "libflashsvd_b200.so"
 
 DTYPE_BF16 = 0
 DTYPE_F32 = 1
+DTYPE_BF16_Q4 = 2   # bf16 activations, int4-g128 factor tile streams
 
 EXPORTS = (
     "fsvd_version", "fsvd_last_error_string", "fsvd_device_props", "fsvd_set_launch_config",
@@ -22,6 +23,7 @@ EXPORTS = (
     "fsvd_decode_layer", "fsvd_model_create", "fsvd_model_destroy", "fsvd_model_step",
     "fsvd_model_buffers", "fsvd_model_status", "fsvd_model_reset_sync", "fsvd_launch_count",
     "fsvd_set_trace_buffer", "fsvd_model_num_stages", "fsvd_lowrank_proj_static", "fsvd_lift",
+    "fsvd_q4_packed_bytes", "fsvd_q4_pack",
 )
 
 
@@ -97,6 +99,9 @@ def load() -> C.CDLL:
     lib.fsvd_launch_count.restype = C.c_longlong
     lib.fsvd_set_trace_buffer.argtypes = [vp, sz]
     lib.fsvd_model_num_stages.argtypes = [vp]
+    lib.fsvd_q4_packed_bytes.argtypes = [ip, ip]
+    lib.fsvd_q4_packed_bytes.restype = sz
+    lib.fsvd_q4_pack.argtypes = [vp, vp, vp, ip, ip, vp, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("fsvd_version",):

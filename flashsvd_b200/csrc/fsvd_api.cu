@@ -81,7 +81,8 @@ static int get_props(DevProps& p) {
 #include "fsvd_launch.h"
 extern const KernelEntry g_kernels_bf16[];
 extern const KernelEntry g_kernels_f32[];
-static const KernelEntry* const g_kernel_tables[] = {g_kernels_bf16, g_kernels_f32};
+extern const KernelEntry g_kernels_bf16_q4[];
+static const KernelEntry* const g_kernel_tables[] = {g_kernels_bf16, g_kernels_f32, g_kernels_bf16_q4};
 
 // Resolved launch: kernel + geometry for a given dtype / batch.
 struct Resolved {
@@ -93,7 +94,7 @@ static int resolve(int dtype, int B, Resolved& r) {
   const LaunchCfg c = current_cfg();
   DevProps p;
   if (int e = get_props(p)) return e;
-  const int bmax = dtype == FSVD_DTYPE_BF16 ? 8 : 4;
+  const int bmax = dtype == FSVD_DTYPE_F32 ? 4 : 8;   // FSVD_DTYPE_BF16_Q4: int4 factors, bf16 everything else
   if (B < 1 || B > bmax) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..%d)", B, bmax);
   r.grid = c.grid > 0 ? (c.grid < p.sms ? c.grid : p.sms) : p.sms;
   r.smem_optin = p.smem_optin;
@@ -148,6 +149,31 @@ static int encode_map(unsigned char* out, int dtype, const void* base, long long
   return 0;
 }
 
+// Bytes of the int4 tile stream of a [rows, K] factor (fsvd_stage.h describes the tile).
+static size_t q4_bytes(long long rows, long long K) {
+  const long long rt = (rows + kUnitRows - 1) / kUnitRows, ct = (K + kQ4BoxCols - 1) / kQ4BoxCols;
+  return (size_t)(rt * ct) * kQ4BoxBytes;
+}
+// Descriptor of an int4 tile stream of `tiles` tiles starting at base: a [tiles * 17, 512 bytes]
+// matrix of 32-bit words read one tile (17 rows) per box.
+static int encode_map_q4(unsigned char* out, const void* base, long long tiles) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  if (tiles < 1) return fail(FSVD_ERR_ARG, "empty factor matrix");
+  if (reinterpret_cast<uintptr_t>(base) & 15) return fail(FSVD_ERR_ALIGN, "int4 tile streams must start on 16-byte boundaries");
+  CUtensorMap tm;
+  cuuint64_t dims[2] = {(cuuint64_t)(kBoxRowBytes / 4), (cuuint64_t)tiles * kQ4TileRows};
+  cuuint64_t strides[1] = {(cuuint64_t)kBoxRowBytes};
+  cuuint32_t box[2] = {(cuuint32_t)(kBoxRowBytes / 4), (cuuint32_t)kQ4TileRows};
+  cuuint32_t es[2] = {1, 1};
+  const CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  memcpy(out, &tm, 128);
+  return 0;
+}
+
 // ------------------------------------------------------------------------------- workspace
 static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 constexpr int kMaxSegs = 8;
@@ -195,11 +221,13 @@ struct Builder {
   long long cum_items = 0;   // attention items handed out so far (item -> warp map)
   int max_vec = 8;           // elements of the staged vector a lane may touch, per batch row
   int err = 0;               // first error of gemv()
+  bool wq4 = false;          // factors are int4 tile streams (FSVD_DTYPE_BF16_Q4)
 
   Builder(const Resolved& r, int dtype_, int B_) {
     grid = r.grid;
     TW = r.grid * kConsumerWarps;
-    dtype = dtype_;
+    wq4 = dtype_ == FSVD_DTYPE_BF16_Q4;
+    dtype = wq4 ? FSVD_DTYPE_BF16 : dtype_;
     esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
     boxcols = kBoxRowBytes / esize;
     B = B_;
@@ -241,8 +269,18 @@ struct Builder {
   // GEMV stage.  Units (16 rows x one K segment) go round-robin to the CTAs; with split_k the K
   // range is cut into the number of segments (<= kMaxSegs) that gives the busiest CTA the fewest
   // boxes.  rows_total: rows of the matrices behind WA (and WB) that the descriptors may read.
-  Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k, int rope_half = 0) {
+  // Pointer to row `rows` (a multiple of 16 for int4) of a [*, K] factor that starts at base.
+  const void* row_ptr(const void* base, long long rows, int K) const {
+    const size_t off = wq4 ? q4_bytes(rows, K) : (size_t)rows * K * esize;
+    return reinterpret_cast<const char*>(base) + off;
+  }
+  Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k, int rope_half = 0,
+              int q4_override = -1) {
+    const bool q4 = q4_override < 0 ? wq4 : q4_override != 0;
+    const int boxcols = q4 ? kQ4BoxCols : this->boxcols;
+    const int boxbytes = q4 ? kQ4BoxBytes : kBoxBytes;
     Stage s = blank();
+    if (q4) s.flags |= SF_Q4;
     s.type = ST_GEMV;
     s.WA = WA;
     s.WB = WB;
@@ -263,7 +301,7 @@ struct Builder {
         // time of the busiest CTA's boxes at an SM's share of HBM bandwidth (44 bytes/ns), plus
         // the time every CTA of the next stage spends reading `real` partial vectors from L2
         // (4 bytes/ps over the whole GPU)
-        const long long cost = ((units + grid - 1) / grid) * cps * (kBoxBytes / 44) +
+        const long long cost = ((units + grid - 1) / grid) * cps * (boxbytes / 44) +
                                (long long)real * P * 4 * grid / 4000;
         if (best_cost < 0 || cost < best_cost) {
           best_cost = cost;
@@ -275,6 +313,7 @@ struct Builder {
     s.segs = best_segs;
     s.cps = best_cps;
     s.kseg = best_cps * boxcols;
+    s.nch = q4 ? nchunks : 0;
     s.rot = (int)(cum_units % grid);
     cum_units += (long long)groups * best_segs;
     push(s);
@@ -284,8 +323,16 @@ struct Builder {
     const long long rowsB = rope_half > 0 ? 2ll * P - rope_half : P;
     if (rope_half > 0 && rope_half % kUnitRows && !err)
       err = fail(FSVD_ERR_UNSUPPORTED, "head_dim/2 = %d must be a multiple of %d", rope_half, kUnitRows);
-    if (!err) err = encode_map(maps.back().m[0], dtype, WA, rowsA, K, ldw);
-    if (!err && WB) err = encode_map(maps.back().m[1], dtype, WB, rowsB, K, ldw);
+    if (q4) {
+      // tile rows behind the pointers (a rotary stage's second operand starts rope_half rows in)
+      const long long trA = (rowsA + kUnitRows - 1) / kUnitRows;
+      const long long trB = rope_half > 0 ? trA - rope_half / kUnitRows : trA;
+      if (!err) err = encode_map_q4(maps.back().m[0], WA, trA * nchunks);
+      if (!err && WB) err = encode_map_q4(maps.back().m[1], WB, trB * nchunks);
+    } else {
+      if (!err) err = encode_map(maps.back().m[0], dtype, WA, rowsA, K, ldw);
+      if (!err && WB) err = encode_map(maps.back().m[1], dtype, WB, rowsB, K, ldw);
+    }
     return st.back();
   }
   // Input vector of the stage just appended (s must be st.back()).  `barrier`: the vector is
@@ -326,7 +373,10 @@ struct Builder {
     long long mx = max_vec;
     for (const Stage& s : st) {
       if (s.type != ST_GEMV) continue;
-      const long long reach = (long long)(s.xA_off > s.xB_off ? s.xA_off : s.xB_off) + (long long)s.segs * s.cps * boxcols;
+      // (the fused q/k/v lift reads the inputs of its three parts at 0, K and 2 K)
+      const long long reach = (long long)(s.xA_off > s.xB_off ? s.xA_off : s.xB_off) +
+                              (s.epi == EPI_QKV ? 2ll * s.K : 0ll) +
+                              (long long)s.segs * s.cps * ((s.flags & SF_Q4) ? kQ4BoxCols : boxcols);
       if (reach > mx) mx = reach;
     }
     return (int)((mx + 7) / 8 * 8) + 8;   // + 16 bytes so that batch rows start in different banks
@@ -334,23 +384,29 @@ struct Builder {
   int vec_bytes() const { return (B * xstride() * esize + 15) / 16 * 16; }
   // Ring slots: as many as fit beside the rest; a multiple of the consumer warps, or fewer than
   // that when a huge input vector leaves less room (then one warp per slot works).
+  int slot_bytes() const {
+    for (const Stage& s : st)
+      if (s.type == ST_GEMV && (s.flags & SF_Q4)) return kQ4BoxBytes;
+    return kBoxBytes;
+  }
   int nslots(int smem_optin) const {
     const long long rest = (long long)smem_optin - smem_header_bytes() - part_bytes() - vec_bytes();
-    long long n = rest / kBoxBytes;
+    long long n = rest / slot_bytes();
     if (n > max_slots) n = max_slots;
     if (n > kMaxSlots) n = kMaxSlots;
     if (n >= kConsumerWarps) n = n / kConsumerWarps * kConsumerWarps;
     return n < 0 ? 0 : (int)n;
   }
   size_t smem_bytes(int slots) const {
-    return (size_t)smem_header_bytes() + (size_t)slots * kBoxBytes + part_bytes() + vec_bytes();
+    return (size_t)smem_header_bytes() + (size_t)slots * slot_bytes() + part_bytes() + vec_bytes();
   }
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int check_dims(const fsvd_dims& D) {
-  if (D.dtype != FSVD_DTYPE_BF16 && D.dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype %d", D.dtype);
+  if (D.dtype != FSVD_DTYPE_BF16 && D.dtype != FSVD_DTYPE_F32 && D.dtype != FSVD_DTYPE_BF16_Q4)
+    return fail(FSVD_ERR_ARG, "bad dtype %d", D.dtype);
   if (D.B < 1 || D.B > 4) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..4)", D.B);
   if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim %d unsupported (64, 128)", D.Dh);
   if (D.Hk < 1 || D.H % D.Hk) return fail(FSVD_ERR_ARG, "H=%d not a multiple of Hk=%d", D.H, D.Hk);
@@ -367,13 +423,10 @@ static int check_dims(const fsvd_dims& D) {
 // True when q_u, k_u and v_u lie back to back in memory with one rank: they then form one
 // [(H + 2 Hk) * Dh, R] matrix and the three lifts run as one stage (packing.pack_layer and
 // synthetic.random_packed_layers lay them out like this).
-static bool qkv_lifts_packed(const void* q_u, const void* k_u, const void* v_u, int H, int Hk, int Dh, int Rq,
-                             int Rk, int Rv, int esize) {
+static bool qkv_lifts_packed(const Builder& b, const void* q_u, const void* k_u, const void* v_u, int H, int Hk,
+                             int Dh, int Rq, int Rk, int Rv) {
   if (Rq != Rk || Rq != Rv || env_int("FSVD_FUSE_QKV", 1) == 0) return false;
-  const char* q = reinterpret_cast<const char*>(q_u);
-  const char* k = reinterpret_cast<const char*>(k_u);
-  const char* v = reinterpret_cast<const char*>(v_u);
-  return k == q + (size_t)H * Dh * Rq * esize && v == k + (size_t)Hk * Dh * Rq * esize;
+  return k_u == b.row_ptr(q_u, (long long)H * Dh, Rq) && v_u == b.row_ptr(k_u, (long long)Hk * Dh, Rq);
 }
 
 struct LayerIO {
@@ -408,9 +461,9 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     s.out = pa;
   }
   const int segs1 = b.st.back().segs;
-  if (qkv_lifts_packed(Lw.q_u, Lw.k_u, Lw.v_u, D.H, D.Hk, D.Dh, D.Rq, D.Rk, D.Rv, b.esize)) {
+  if (qkv_lifts_packed(b, Lw.q_u, Lw.k_u, Lw.v_u, D.H, D.Hk, D.Dh, D.Rq, D.Rk, D.Rv)) {
     // 2-4. q, k and v lifts as one stage over the packed [q_u; k_u; v_u] matrix
-    Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
+    Stage& s = b.gemv(Lw.q_u, b.row_ptr(Lw.q_u, half, D.Rq),
                       (D.H + 2 * D.Hk) * half, D.Rq, D.Rq, false, half);
     b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
     s.rope_half = half;
@@ -423,7 +476,7 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
   } else {
     {  // 2. lift q with rotary
-      Stage& s = b.gemv(Lw.q_u, reinterpret_cast<const char*>(Lw.q_u) + (size_t)half * D.Rq * b.esize,
+      Stage& s = b.gemv(Lw.q_u, b.row_ptr(Lw.q_u, half, D.Rq),
                         D.H * half, D.Rq, D.Rq, false, half);
       b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
       s.rope_half = half;
@@ -434,7 +487,7 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
       s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
     }
     {  // 3. lift k with rotary into the cache
-      Stage& s = b.gemv(Lw.k_u, reinterpret_cast<const char*>(Lw.k_u) + (size_t)half * D.Rk * b.esize,
+      Stage& s = b.gemv(Lw.k_u, b.row_ptr(Lw.k_u, half, D.Rk),
                         D.Hk * half, D.Rk, D.Rk, false, half);
       s.rope_half = half;
       s.xA_off = s.xB_off = D.Rq;
@@ -571,6 +624,7 @@ static int launch_small(const Resolved& r, Builder& b, SyncState* sync, cudaStre
   a.part_bytes = b.part_bytes();
   a.vec_bytes = b.vec_bytes();
   a.nslots = slots;
+  a.slot_bytes = b.slot_bytes();
   a.trace = g_trace_bytes >= b.st.size() * (size_t)r.grid * 128 ? g_trace : nullptr;
   a.grid = r.grid;
   a.smem = smem;
@@ -659,7 +713,8 @@ int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* r
     return fail(FSVD_ERR_ALIGN, "d_in=%d and R=%d must be positive multiples of 8", d_in, R);
   if (!aligned16(x) || !aligned16(v) || !aligned16(u) || !aligned16(y))
     return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
-  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32 && dtype != FSVD_DTYPE_BF16_Q4)
+    return fail(FSVD_ERR_ARG, "bad dtype");
   fsvd_dims D = op_dims(dtype, B);
   D.Ro = R;
   WsLayout L;
@@ -692,7 +747,8 @@ int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B
   if (!p || !u || !y) return fail(FSVD_ERR_ARG, "null argument");
   if (R <= 0 || d_out <= 0 || R % 8) return fail(FSVD_ERR_ALIGN, "R=%d must be a positive multiple of 8", R);
   if (!aligned16(p) || !aligned16(u) || !aligned16(y)) return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
-  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32 && dtype != FSVD_DTYPE_BF16_Q4)
+    return fail(FSVD_ERR_ARG, "bad dtype");
   fsvd_dims D = op_dims(dtype, B);
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
@@ -715,7 +771,8 @@ int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const v
                            int Ru, int Rg, int Rd, int dtype, void* ws, size_t ws_bytes,
                            void* stream) {
   if (!x || !gate_u || !up_u || !down_v || !down_u || !y) return fail(FSVD_ERR_ARG, "null argument");
-  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32) return fail(FSVD_ERR_ARG, "bad dtype");
+  if (dtype != FSVD_DTYPE_BF16 && dtype != FSVD_DTYPE_F32 && dtype != FSVD_DTYPE_BF16_Q4)
+    return fail(FSVD_ERR_ARG, "bad dtype");
   if (d <= 0 || I <= 0 || Ru <= 0 || Rg <= 0 || Rd <= 0 || d % 8 || I % 8 || Ru % 8 || Rg % 8 || Rd % 8)
     return fail(FSVD_ERR_ALIGN, "d, I and the ranks must be positive multiples of 8");
   if (Ru != Rg) return fail(FSVD_ERR_UNSUPPORTED, "gate and up ranks must match (Rg=%d, Ru=%d)", Rg, Ru);
@@ -811,7 +868,7 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
   }
   const int segs = b.st.back().segs;
   {
-    Stage& s = b.gemv(q_u, reinterpret_cast<const char*>(q_u) + (size_t)half * Rq * b.esize, H * half, Rq, Rq, false, half);
+    Stage& s = b.gemv(q_u, b.row_ptr(q_u, half, Rq), H * half, Rq, Rq, false, half);
     b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, true);
     s.rope_half = half;
     s.epi = EPI_ROPE_Q;
@@ -821,7 +878,7 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
     s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
   }
   {
-    Stage& s = b.gemv(k_u, reinterpret_cast<const char*>(k_u) + (size_t)half * Rk * b.esize, Hk * half, Rk, Rk, false, half);
+    Stage& s = b.gemv(k_u, b.row_ptr(k_u, half, Rk), Hk * half, Rk, Rk, false, half);
     s.rope_half = half;
     s.xA_off = s.xB_off = Rq;
     s.epi = EPI_ROPE_K;
@@ -900,7 +957,7 @@ struct fsvd_model {
   char* ws = nullptr;
   Stage* prog = nullptr;
   unsigned char* maps = nullptr;   // TMA descriptors, 2 x 128 bytes per stage
-  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0, nslots = 0;
+  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0, nslots = 0, slot_bytes = 0;
   size_t smem = 0;
   int* tokens = nullptr;
   int* seqlens = nullptr;
@@ -977,7 +1034,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     build_layer(b, D, layers[l], io, m->ws, m->L);
   }
   {
-    Stage& s = b.gemv(lm_head, nullptr, D.vocab, D.d, D.d, false);
+    Stage& s = b.gemv(lm_head, nullptr, D.vocab, D.d, D.d, false, 0, 0);   // lm_head stays dense
     b.vec(s, VL_RMSNORM, xbuf, D.d, 1, true);
     s.flags |= SF_IN_T;
     s.vl_w = final_norm_w;
@@ -1007,6 +1064,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   m->xstride = b.xstride();
   m->part_bytes = b.part_bytes();
   m->vec_bytes = b.vec_bytes();
+  m->slot_bytes = b.slot_bytes();
   static_assert(sizeof(MapPair) == 256, "two descriptors per stage");
   ce = cudaMalloc(&m->prog, sizeof(Stage) * b.st.size());
   if (ce == cudaSuccess) ce = cudaMalloc(&m->maps, sizeof(MapPair) * b.maps.size());
@@ -1048,6 +1106,7 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
     a.part_bytes = m->part_bytes;
     a.vec_bytes = m->vec_bytes;
     a.nslots = m->nslots;
+    a.slot_bytes = m->slot_bytes;
         a.trace = g_trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? g_trace : nullptr;
     a.grid = m->r.grid;
     a.smem = m->smem;
@@ -1156,4 +1215,73 @@ extern "C" int fsvd_lowrank_proj_static(const void* x, const void* v, const void
     s.out = y;
   }
   return launch_small(r, b, reinterpret_cast<SyncState*>(w), (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------------------- int4 tile streams
+// Repacks one PackedQuantLinear (qweight uint8 [rows, K/2], low nibble = even input; scales fp16
+// [rows, ceil(K/128)]; zeros int16, all 8 for the symmetric format) into the tile stream the
+// kernel reads (fsvd_stage.h).  One thread writes one 16-byte word of the stream.
+__device__ int g_q4_bad_zero;
+
+__global__ void q4_pack_kernel(const unsigned char* __restrict__ qweight, const unsigned short* __restrict__ scales,
+                               const short* __restrict__ zeros, int rows, int K, int nct, long long nwords,
+                               uint4* __restrict__ out) {
+  const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= nwords) return;
+  const int w16 = (int)(w % 32);
+  const long long trow = w / 32;
+  const int r17 = (int)(trow % kQ4TileRows);
+  const long long tile = trow / kQ4TileRows;
+  const int ct = (int)(tile % nct);
+  const long long rt = tile / nct;
+  const int G = (K + kQ4Group - 1) / kQ4Group, rowbytes = K / 2;
+  union {
+    uint4 v;
+    unsigned char b[16];
+    unsigned short h[8];
+  } o;
+  if (r17 < kUnitRows) {
+    const long long row = rt * kUnitRows + r17;
+    for (int i = 0; i < 16; ++i) {
+      const int bcol = ct * kBoxRowBytes + w16 * 16 + i;
+      o.b[i] = (row < rows && bcol < rowbytes) ? qweight[row * rowbytes + bcol] : (unsigned char)0x88;
+    }
+  } else {
+    const long long row = rt * kUnitRows + w16;
+    for (int j = 0; j < 8; ++j) {
+      const int gi = ct * 8 + j;
+      const bool in = w16 < kUnitRows && row < rows && gi < G;
+      o.h[j] = in ? scales[row * G + gi] : (unsigned short)0;
+      if (in && zeros && zeros[row * G + gi] != 8) atomicOr(&g_q4_bad_zero, 1);
+    }
+  }
+  out[w] = o.v;
+}
+
+extern "C" size_t fsvd_q4_packed_bytes(int rows, int K) {
+  if (rows < 1 || K < 1) return 0;
+  return q4_bytes(rows, K);
+}
+
+extern "C" int fsvd_q4_pack(const void* qweight, const void* scales, const void* zeros, int rows, int K,
+                            void* out, void* stream) {
+  if (!qweight || !scales || !out) return fail(FSVD_ERR_ARG, "null argument");
+  if (rows < 1 || K < 8 || K % 8) return fail(FSVD_ERR_ALIGN, "K=%d must be a positive multiple of 8", K);
+  if (!aligned16(out)) return fail(FSVD_ERR_ALIGN, "the tile stream must start on a 16-byte boundary");
+  const int nct = (K + kQ4BoxCols - 1) / kQ4BoxCols;
+  const long long nwords = (long long)(q4_bytes(rows, K) / 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int zero = 0;
+  if (zeros) CUDA_TRY(cudaMemcpyToSymbolAsync(g_q4_bad_zero, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+  q4_pack_kernel<<<(unsigned)((nwords + 255) / 256), 256, 0, st>>>(
+      reinterpret_cast<const unsigned char*>(qweight), reinterpret_cast<const unsigned short*>(scales),
+      reinterpret_cast<const short*>(zeros), rows, K, nct, nwords, reinterpret_cast<uint4*>(out));
+  CUDA_TRY(cudaGetLastError());
+  if (zeros) {
+    int bad = 0;
+    CUDA_TRY(cudaMemcpyFromSymbolAsync(&bad, g_q4_bad_zero, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    if (bad) return fail(FSVD_ERR_UNSUPPORTED, "only the symmetric int4 format (every zero point = 8) is supported");
+  }
+  return 0;
 }

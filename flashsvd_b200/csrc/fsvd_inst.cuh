@@ -1,13 +1,17 @@
 // Instantiates the interpreter for one element type; included by fsvd_inst_*.cu after defining
-// FSVD_INST_T, FSVD_INST_DTYPE and FSVD_INST_TABLE.
+// FSVD_INST_T, FSVD_INST_DTYPE and FSVD_INST_TABLE (and FSVD_INST_Q4 = true for the instance that
+// also understands int4 tile streams).
+#ifndef FSVD_INST_Q4
+#define FSVD_INST_Q4 false
+#endif
 #include "fsvd_kernel.cuh"
 #include "fsvd_launch.h"
 
 namespace {
 
-template <typename T>
+template <typename T, bool Q4>
 cudaError_t launch_impl(const LaunchArgs& a) {
-  auto kern = fsvd::fsvd_decode_kernel<T>;
+  auto kern = fsvd::fsvd_decode_kernel<T, Q4>;
   static size_t attr_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -32,9 +36,9 @@ cudaError_t launch_impl(const LaunchArgs& a) {
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, a.prog, a.small ? *a.small : empty_prog, a.maps,
                             a.small_maps ? *a.small_maps : empty_maps, a.small ? 1 : 0, a.nstages,
-                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.trace);
+                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.slot_bytes, a.trace);
 }
 
 }  // namespace
 
-extern const KernelEntry FSVD_INST_TABLE[] = {{FSVD_INST_DTYPE, &launch_impl<FSVD_INST_T>}, {0, nullptr}};
+extern const KernelEntry FSVD_INST_TABLE[] = {{FSVD_INST_DTYPE, &launch_impl<FSVD_INST_T, FSVD_INST_Q4>}, {0, nullptr}};

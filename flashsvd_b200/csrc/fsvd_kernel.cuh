@@ -650,6 +650,7 @@ __device__ __forceinline__ BoxPlan plan_boxes(int P, int segs, int cps, int rot,
 struct Ring {
   uint32_t full, empty;   // shared-memory addresses of the mbarrier arrays
   uint32_t data;          // shared-memory address of slot 0
+  uint32_t stride;        // bytes between slots (kBoxBytes, or kQ4BoxBytes when the program has int4 stages)
   int ns;                 // slots, a multiple of kNWC (or fewer than kNWC)
 };
 
@@ -661,7 +662,7 @@ struct Ring {
 // slot, and then all lanes issue their TMA copies with one instruction.  (Lanes that ran their
 // own loops and met at different barriers serialised: 1 such lane gave 354, 4 lanes 327, 8 lanes
 // 298 tokens/s on the 7B-shape model.)
-template <typename T>
+template <typename T, bool Q4>
 __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, const unsigned char* maps,
                                            const Ring rg, int lane, SyncState* sync, volatile int* giveup) {
   constexpr int BOXCOLS = kBoxRowBytes / (int)sizeof(T);
@@ -672,6 +673,7 @@ __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, co
   // cursor of this lane
   int s = -1, j = 0, op = 0, c = 0;          // stage, unit ordinal, operand, chunk
   int nu = 0, nops = 1, cps = 1, first = 0, segs = 1, half = 0;
+  int nch = 0;                               // > 0: the stage streams int4 tiles, nch per tile row
   const unsigned char* mapA = maps;
   bool done = false;
   // moves the cursor to the first box of the next GEMV stage with boxes for this CTA
@@ -682,6 +684,7 @@ __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, co
       const BoxPlan bp = plan_boxes(st.P, st.segs, st.cps, st.rot, st.WB != nullptr, cta, grid);
       if (bp.nbox == 0) continue;
       nu = bp.nu; nops = bp.nops; cps = bp.cps; first = bp.first; segs = st.segs; half = st.rope_half;
+      nch = (Q4 && (st.flags & SF_Q4)) ? st.nch : 0;
       mapA = maps + (size_t)(2 * s) * 128;
       j = op = c = 0;
       return;
@@ -716,9 +719,20 @@ __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, co
       const int uidx = first + j * grid;
       const int grp = uidx / segs, seg = uidx - grp * segs;
       const uint32_t fb = rg.full + slot * 8;
-      mbar_expect_tx(fb, kBoxBytes);
-      tma_box_2d(rg.data + (uint32_t)slot * kBoxBytes, mapA + (op ? 128 : 0), (seg * cps + c) * BOXCOLS,
-                 phys_row(half, grp * kUnitRows), fb);
+      const uint32_t dst = rg.data + (uint32_t)slot * (Q4 ? rg.stride : (uint32_t)kBoxBytes);
+      if (Q4 && nch > 0) {
+        // tile (row group, chunk) of the int4 stream; a chunk past the last tile of the row (the
+        // tail of the last K segment) is fetched from outside the tensor and arrives as zeros
+        // (zero scales)
+        const int chunk = seg * cps + c;
+        const int trow = phys_row(half, grp * kUnitRows) / kUnitRows;
+        const int y = chunk < nch ? (trow * nch + chunk) * kQ4TileRows : 0x40000000;
+        mbar_expect_tx(fb, kQ4BoxBytes);
+        tma_box_2d(dst, mapA + (op ? 128 : 0), 0, y, fb);
+      } else {
+        mbar_expect_tx(fb, kBoxBytes);
+        tma_box_2d(dst, mapA + (op ? 128 : 0), (seg * cps + c) * BOXCOLS, phys_row(half, grp * kUnitRows), fb);
+      }
     } else if (!done) {
       done = true;   // a wait ran out: this lane stops (the consumers give up on their own)
     }
@@ -728,6 +742,50 @@ __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, co
       slot -= rg.ns;
       ++round;
     }
+  }
+}
+
+// One int4 tile (16 rows x 1024 inputs, 8 groups of 128) times the staged bf16 vector.
+// wb: this lane's 16 bytes of code row g (row g + 8 is 8 rows further); sb: the tile's scale
+// row; xq: the lane's 32 inputs of group 0 (64 bytes; group j is 256 bytes further).
+// A warp-wide 16-byte load covers exactly one group of one row: lane t holds the codes of
+// inputs 32 t .. 32 t + 31 of the group.  Word i of those 16 bytes holds inputs 8 i .. 8 i + 7,
+// one per nibble; (w >> 4 n) & 0x000f000f picks inputs (n, n + 4) into the two halves of a
+// register, OR 0x4300 makes each the bf16 number 128 + code, minus 136 gives code - 8 exactly.
+// The k-slots of the MMA are thus inputs (0,4 | 1,5) and (2,6 | 3,7) of a word; the vector side is
+// permuted the same way.  A group's 8 MMAs start from zero; the sum is scaled by the (row, group)
+// scale in fp32: y = sum_groups s * sum_k (code - 8) x.
+__device__ __forceinline__ uint32_t q4_pair(uint32_t w) {
+  const uint32_t v = (w & 0x000f000fu) | 0x43004300u;
+  const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), __floats2bfloat162_rn(136.f, 136.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) {
+  return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu)));
+}
+__device__ __forceinline__ void q4_box(uint32_t wb, uint32_t sb, uint32_t xq, int g, float* acc) {
+  const uint4 sg = lds128(sb + g * 16), sh = lds128(sb + (g + 8) * 16);
+  const uint32_t sgw[4] = {sg.x, sg.y, sg.z, sg.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint4 lo = lds128(wb + j * 64), hi = lds128(wb + 8 * kBoxRowBytes + j * 64);
+    const uint32_t low[4] = {lo.x, lo.y, lo.z, lo.w}, hiw[4] = {hi.x, hi.y, hi.z, hi.w};
+    float ga[4] = {0.f, 0.f, 0.f, 0.f}, gb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 xv = lds128(xq + j * 256 + i * 16);
+      const uint32_t y04 = __byte_perm(xv.x, xv.z, 0x5410), y15 = __byte_perm(xv.x, xv.z, 0x7632);
+      const uint32_t y26 = __byte_perm(xv.y, xv.w, 0x5410), y37 = __byte_perm(xv.y, xv.w, 0x7632);
+      const uint32_t wl = low[i], wh = hiw[i];
+      mma_bf16_16816(ga, q4_pair(wl), q4_pair(wh), q4_pair(wl >> 4), q4_pair(wh >> 4), y04, y15);
+      mma_bf16_16816(gb, q4_pair(wl >> 8), q4_pair(wh >> 8), q4_pair(wl >> 12), q4_pair(wh >> 12), y26, y37);
+    }
+    const float s0 = half_bits_to_float(sgw[j >> 1] >> ((j & 1) * 16));
+    const float s1 = half_bits_to_float(shw[j >> 1] >> ((j & 1) * 16));
+    acc[0] = fmaf(s0, ga[0] + gb[0], acc[0]);
+    acc[1] = fmaf(s0, ga[1] + gb[1], acc[1]);
+    acc[2] = fmaf(s1, ga[2] + gb[2], acc[2]);
+    acc[3] = fmaf(s1, ga[3] + gb[3], acc[3]);
   }
 }
 
@@ -748,7 +806,7 @@ struct StageCtx {
 };
 
 // One GEMV stage, consumer warps.  Returns the number of boxes of this CTA in the stage.
-template <typename T>
+template <typename T, bool Q4>
 __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
   using X = TT<T>;
   constexpr int BOXCOLS = kBoxRowBytes / (int)sizeof(T);
@@ -757,6 +815,8 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
   const BoxPlan bp = plan_boxes(st.P, segs, st.cps, st.rot, st.WB != nullptr, blockIdx.x, grid);
   const int cps = bp.cps, nops = bp.nops;
   const int rowsB = kUnitRows * B;
+  const bool q4 = Q4 && sizeof(T) == 2 && (st.flags & SF_Q4);
+  const int boxcols = (Q4 && q4) ? kQ4BoxCols : BOXCOLS;
 
   // operands of the epilogues this thread will run (outputs tid and tid + 256), fetched now so
   // that their latency hides behind the barrier and the streaming
@@ -851,7 +911,7 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
       const int j = nops == 2 ? (io >> 1) : io, op = nops == 2 ? (io & 1) : 0;
       const int uidx = bp.first + j * grid;
       const int seg = uidx % segs;
-      xcol0 = (op ? st.xB_off : st.xA_off) + seg * cps * BOXCOLS;
+      xcol0 = (op ? st.xB_off : st.xA_off) + seg * cps * boxcols;
       if (st.epi == EPI_QKV) {   // segs == 1: uidx is the row group; the part's input starts at part * K
         const int p0 = uidx * kUnitRows, half = st.rope_half;
         xcol0 += ((p0 >= st.H * half) + (p0 >= (st.H + st.Hk) * half)) * st.K;
@@ -860,9 +920,12 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
     bool ok = mbar_wait(cx.ring.full + slot * 8, (uint32_t)round & 1u, cx.sync, cx.giveup, cx.s);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
-      const uint32_t wb = cx.ring.data + (uint32_t)slot * kBoxBytes + wlane;
-      const uint32_t xoff = (uint32_t)(xcol0 + c * BOXCOLS) * (uint32_t)sizeof(T);
+      const uint32_t wb = cx.ring.data + (uint32_t)slot * (Q4 ? cx.ring.stride : (uint32_t)kBoxBytes) + wlane;
+      const uint32_t xoff = (uint32_t)(xcol0 + c * boxcols) * (uint32_t)sizeof(T);
       if constexpr (sizeof(T) == 2) {
+       if (Q4 && q4) {
+        q4_box(wb, wb - wlane + kUnitRows * kBoxRowBytes, xlane_s + xoff + t * 48, g, acc);
+       } else {
         const uint32_t xb = xlane_s + xoff;
         // four independent accumulator chains keep the tensor pipe busy
         float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -881,6 +944,7 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
         for (int e = 0; e < 4; ++e) a0[e] += a2[e], a1[e] += a3[e];
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[e] += a0[e] + a1[e];
+       }
       } else {
         const uint32_t xb = xvec_s + xoff;
 #pragma unroll
@@ -1312,18 +1376,18 @@ static __device__ __forceinline__ void run_argmax(const Stage& st, float* redv, 
 //   [.., +kSmallProgBytes)      copy of a by-value program (per-op launches)
 //   [.., +512)                  ring mbarriers: full[kMaxSlots], empty[kMaxSlots]
 //   -- header rounded to 1 KB --
-//   [.., +nslots*8192)          the ring
+//   [.., +nslots*slot_bytes)    the ring (8192-byte slots; 8704 when the program streams int4 tiles)
 //   [.., +part_bytes)           partial sums of the warps (sized by the host for the program)
 //   [.., +vec_bytes)            staged input vector, B rows of xstride elements
 // Stage timeline (optional): trace[(s*grid + cta)*16 + k] = globaltimer at: 0 stage entry,
 // 1 grid barrier passed, 2 vector staged, 3 stage done, 4 vector words arrived, 5 norm reduced,
 // 7 boxes consumed.
-template <typename T>
+template <typename T, bool Q4>
 __global__ void __launch_bounds__(kThreads, 1)
 fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant__ SmallProgram small,
                    const unsigned char* __restrict__ maps_global, const __grid_constant__ SmallMaps small_maps,
                    int use_small, int nstages, SyncState* sync, int xstride, int part_bytes,
-                   int vec_bytes, int nslots, unsigned long long* trace) {
+                   int vec_bytes, int nslots, int slot_bytes, unsigned long long* trace) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -1333,7 +1397,7 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
   Stage* small_sh = reinterpret_cast<Stage*>(smem + 2 * kStageBytesAl + 512);
   unsigned char* bars = smem + 2 * kStageBytesAl + 512 + kSmallProgBytes;
   unsigned char* ring = smem + smem_header_bytes();
-  float* part = reinterpret_cast<float*>(ring + (size_t)nslots * kBoxBytes);
+  float* part = reinterpret_cast<float*>(ring + (size_t)nslots * (Q4 ? slot_bytes : kBoxBytes));
   char* xvec = reinterpret_cast<char*>(part) + part_bytes;
   volatile int* giveup = flags_sh + 1;
 
@@ -1341,6 +1405,7 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
   rg.full = smem_u32(bars);
   rg.empty = rg.full + kMaxSlots * 8;
   rg.data = smem_u32(ring);
+  rg.stride = (uint32_t)slot_bytes;
   rg.ns = nslots;
 
   // Boxes past the K range hold zeros and multiply whatever follows the input in the staged
@@ -1390,7 +1455,7 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
   const unsigned long long bar_base = __ldcg(&sync->bar_base);
   if (warp >= kNWC) {
     // ---------------- producers
-    producer_loop<T>(prog, nstages, maps, rg, lane, sync, giveup);
+    producer_loop<T, Q4>(prog, nstages, maps, rg, lane, sync, giveup);
   } else {
     // ---------------- consumers
     unsigned seq_base = 0;
@@ -1425,7 +1490,7 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
         cx.giveup = giveup;
         cx.pc = pc;
         cx.trow = trow;
-        seq_base += (unsigned)gemv_stage<T>(st, cx);
+        seq_base += (unsigned)gemv_stage<T, Q4>(st, cx);
       } else {
         if (st.flags & SF_BARRIER) barrier_wait(sync, target, s, tid);
         trace_mark(trow, 1);

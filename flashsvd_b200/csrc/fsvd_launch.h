@@ -12,6 +12,7 @@ struct LaunchArgs {
   int nstages;
   fsvd::SyncState* sync;
   int xstride, part_bytes, vec_bytes, nslots;
+  int slot_bytes;                     // bytes of one ring slot: kBoxBytes, or kQ4BoxBytes with int4 stages
   unsigned long long* trace;
   int grid;
   size_t smem;

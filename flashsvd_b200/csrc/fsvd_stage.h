@@ -51,6 +51,7 @@ enum StageFlags : int {
   SF_OUT_T = 4,      // out holds T instead of fp32
   SF_RESID_T = 8,    // resid holds T instead of fp32
   SF_ARRIVE = 16,    // arrive at the grid barrier after this stage (the next one has SF_BARRIER)
+  SF_Q4 = 32,        // WA / WB are int4 tile streams (see kQ4*), activations stay T = bf16
 };
 
 // `rnd` above rounds to the storage type T (bf16) and is the identity when T is fp32: these
@@ -70,7 +71,8 @@ struct alignas(16) Stage {
   int vl_nseg;           // partial sums to add when staging
   int rot;               // rotation of the unit -> CTA assignment (ST_ATTN: item -> warp)
   int cps;               // boxes (column chunks of 512 bytes) per K segment
-  int reserved0, reserved1;
+  int nch;               // SF_Q4: column tiles per tile row, ceil(K / kQ4BoxCols)
+  int reserved1;
   int B;                 // batch rows
   const void* vl_src;    // fp32 (or T with SF_IN_T) [vl_nseg, B, vl_len]
   const void* vl_w;      // RMSNorm weight, type T
@@ -123,6 +125,17 @@ constexpr int kUnitRows = 16;          // factor rows of one unit = rows of one 
 constexpr int kBoxRowBytes = 512;      // bytes of one box row (256 bf16 / 128 fp32 columns)
 constexpr int kBoxBytes = kUnitRows * kBoxRowBytes;
 constexpr int kMaxSlots = 21;          // ring slots; a multiple of kConsumerWarps
+
+// int4 factors (4-bit codes, symmetric, one fp16 scale per row and group of 128 inputs) are
+// stored as a stream of tiles, one tile per box: tile (rt, ct) covers rows [16 rt, 16 rt + 16) and
+// inputs [1024 ct, 1024 ct + 1024) and is 17 rows of 512 bytes: rows 0..15 hold the codes of the
+// 16 factor rows (two per byte, low nibble = even input), row 16 holds the 16 x 8 scales
+// (fp16, [row][group], 256 bytes) and 256 bytes of zeros.  Codes past the matrix are 8 (= 0 after
+// the offset) and scales past it are 0.  Tiles are stored row-major over (rt, ct).
+constexpr int kQ4TileRows = kUnitRows + 1;
+constexpr int kQ4BoxBytes = kQ4TileRows * kBoxRowBytes;   // 8704
+constexpr int kQ4BoxCols = 2 * kBoxRowBytes;              // 1024 inputs per tile
+constexpr int kQ4Group = 128;
 
 constexpr int kMaxSmallStages = 14;
 struct SmallProgram {

@@ -51,8 +51,13 @@ class DecodeEngine:
         Rv = L0["v_u"].shape[1]
         if L0["qkv_v"].shape[0] != Rq + Rk + Rv:
             raise ValueError("qkv_v rows must equal Rq + Rk + Rv")
+        # int4 factors (quant.Q4Factor tile streams): bf16 everything else
+        q4 = hasattr(L0["q_u"], "packed")
+        if q4 and dtype != torch.bfloat16:
+            raise ValueError("int4 factors need a bfloat16 model")
+        self.quantized = q4
         self.dims = ops.make_dims(
-            dtype=dtype, B=int(batch_size), d=d, H=H, Hk=Hk, Dh=Dh, I=L0["gate_u"].shape[0],
+            dtype=_lib.DTYPE_BF16_Q4 if q4 else dtype, B=int(batch_size), d=d, H=H, Hk=Hk, Dh=Dh, I=L0["gate_u"].shape[0],
             Rq=Rq, Rk=Rk, Rv=Rv, Ro=L0["o_v"].shape[0], Rg=L0["gate_u"].shape[1],
             Ru=L0["up_u"].shape[1], Rd=L0["down_v"].shape[0], S_max=int(max_cache_len),
             vocab=embed.shape[0], n_layers=len(layers), eps=float(eps))
@@ -70,7 +75,9 @@ class DecodeEngine:
             t["k_cache"], t["v_cache"] = kc, vc
             for name in LAYER_FIELDS:
                 x = t[name]
-                if not (x.is_cuda and x.is_contiguous() and x.dtype == dtype):
+                if hasattr(x, "packed") != (q4 and name not in ("ln1_w", "ln2_w", "k_cache", "v_cache")):
+                    raise ValueError(f"layer {i} tensor {name}: int4 and dense factors cannot be mixed")
+                if not (x.is_cuda and x.is_contiguous() and (hasattr(x, "packed") or x.dtype == dtype)):
                     raise ValueError(f"layer {i} tensor {name}: need a contiguous {dtype} CUDA tensor")
                 setattr(arr[i], name, x.data_ptr())
         for name, x in (("embed", embed), ("final_norm", final_norm), ("lm_head", lm_head)):

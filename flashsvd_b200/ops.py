@@ -24,9 +24,26 @@ def _dtype_code(dtype: torch.dtype) -> int:
     raise ValueError(f"flashsvd_b200 supports bfloat16 and float32 tensors, got {dtype}")
 
 
-def _ptr(t: torch.Tensor | None) -> int | None:
+def _is_q4(w) -> bool:
+    return hasattr(w, "packed")
+
+
+def _code(x: torch.Tensor, *factors) -> int:
+    """dtype code of a call: the activations' type, or DTYPE_BF16_Q4 when the factors are int4
+    tile streams (quant.Q4Factor; all of them must be, and the activations bfloat16)."""
+    nq = sum(1 for w in factors if w is not None and _is_q4(w))
+    if nq == 0:
+        return _dtype_code(x.dtype)
+    if nq != sum(1 for w in factors if w is not None) or x.dtype != torch.bfloat16:
+        raise ValueError("int4 factors need bfloat16 activations and every factor of the call quantised")
+    return _lib.DTYPE_BF16_Q4
+
+
+def _ptr(t) -> int | None:
     if t is None:
         return None
+    if _is_q4(t):
+        t = t.packed
     if not t.is_cuda:
         raise ValueError("flashsvd_b200 ops need CUDA tensors (there is no CPU path)")
     if not t.is_contiguous():
@@ -84,17 +101,17 @@ def lowrank_proj(x, v_w, u_w, ws: Workspace, residual=None, out=None):
     if x.ndim != 2:
         raise ValueError(f"x must be [B, d_in], got {tuple(x.shape)}")
     B, d_in = x.shape
-    if v_w.ndim != 2 or v_w.shape[1] != d_in:
+    if len(v_w.shape) != 2 or v_w.shape[1] != d_in:
         raise ValueError(f"v_w must be [R, {d_in}], got {tuple(v_w.shape)}")
     R = v_w.shape[0]
-    if u_w.ndim != 2 or u_w.shape[1] != R:
+    if len(u_w.shape) != 2 or u_w.shape[1] != R:
         raise ValueError(f"u_w must be [d_out, {R}], got {tuple(u_w.shape)}")
     d_out = u_w.shape[0]
     if out is None:
         out = torch.empty((B, d_out), dtype=x.dtype, device=x.device)
     check(_lib.load().fsvd_lowrank_proj(
         _ptr(x), _ptr(v_w), _ptr(u_w), _ptr(residual), _ptr(out), B, d_in, R, d_out,
-        _dtype_code(x.dtype), ws.ptr, ws.nbytes, _stream()))
+        _code(x, v_w, u_w), ws.ptr, ws.nbytes, _stream()))
     return out
 
 
@@ -103,13 +120,13 @@ def lift(p, u_w, ws: Workspace, residual=None, out=None):
     if p.ndim != 2:
         raise ValueError(f"p must be [B, R], got {tuple(p.shape)}")
     B, R = p.shape
-    if u_w.ndim != 2 or u_w.shape[1] != R:
+    if len(u_w.shape) != 2 or u_w.shape[1] != R:
         raise ValueError(f"u_w must be [d_out, {R}], got {tuple(u_w.shape)}")
     d_out = u_w.shape[0]
     if out is None:
         out = torch.empty((B, d_out), dtype=p.dtype, device=p.device)
     check(_lib.load().fsvd_lift(_ptr(p), _ptr(u_w), _ptr(residual), _ptr(out), B, R, d_out,
-                                _dtype_code(p.dtype), ws.ptr, ws.nbytes, _stream()))
+                                _code(p, u_w), ws.ptr, ws.nbytes, _stream()))
     return out
 
 
@@ -145,13 +162,13 @@ def mlp_swiglu_decode(x, gate_u, up_u, down_v, down_u, ws: Workspace, *, upgate_
         raise ValueError(f"x must be 2-D, got {tuple(x.shape)}")
     B = x.shape[0]
     I, Rg = gate_u.shape
-    if up_u.shape != gate_u.shape:
+    if tuple(up_u.shape) != tuple(gate_u.shape):
         raise ValueError(f"up_u shape {tuple(up_u.shape)} must match gate_u shape {tuple(gate_u.shape)}")
     Ru = up_u.shape[1]
-    if down_v.ndim != 2 or down_v.shape[1] != I:
+    if len(down_v.shape) != 2 or down_v.shape[1] != I:
         raise ValueError(f"down_v must be [Rd, {I}], got {tuple(down_v.shape)}")
     Rd = down_v.shape[0]
-    if down_u.ndim != 2 or down_u.shape[1] != Rd:
+    if len(down_u.shape) != 2 or down_u.shape[1] != Rd:
         raise ValueError(f"down_u must be [d, {Rd}], got {tuple(down_u.shape)}")
     d = down_u.shape[0]
     if upgate_v is not None:
@@ -163,8 +180,8 @@ def mlp_swiglu_decode(x, gate_u, up_u, down_v, down_u, ws: Workspace, *, upgate_
         out = torch.empty((B, d), dtype=x.dtype, device=x.device)
     check(_lib.load().fsvd_mlp_swiglu_decode(
         _ptr(x), _ptr(norm_w), float(eps), _ptr(upgate_v), _ptr(gate_u), _ptr(up_u), _ptr(down_v),
-        _ptr(down_u), _ptr(residual), _ptr(out), B, d, I, Ru, Rg, Rd, _dtype_code(x.dtype),
-        ws.ptr, ws.nbytes, _stream()))
+        _ptr(down_u), _ptr(residual), _ptr(out), B, d, I, Ru, Rg, Rd,
+        _code(x, upgate_v, gate_u, up_u, down_v, down_u), ws.ptr, ws.nbytes, _stream()))
     return out
 
 
@@ -196,7 +213,7 @@ def qkv_rope_append(x, qkv_v, q_u, k_u, v_u, cos, sin, k_cache, v_cache, cache_s
     check(_lib.load().fsvd_qkv_rope_append(
         _ptr(x), _ptr(norm_w), float(eps), _ptr(qkv_v), _ptr(q_u), _ptr(k_u), _ptr(v_u),
         _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), _ptr(cache_seqlens), _ptr(q_out),
-        B, d, num_heads, num_kv_heads, head_dim, Rq, Rk, Rv, S_max, _dtype_code(x.dtype),
+        B, d, num_heads, num_kv_heads, head_dim, Rq, Rk, Rv, S_max, _code(x, qkv_v, q_u, k_u, v_u),
         ws.ptr, ws.nbytes, _stream()))
     return q_out
 

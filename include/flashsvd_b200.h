@@ -23,6 +23,11 @@ extern "C" {
 
 #define FSVD_DTYPE_BF16 0 /* bf16 storage, fp32 accumulation, outputs rounded to bf16 */
 #define FSVD_DTYPE_F32 1  /* fp32 storage and arithmetic (greedy-parity mode) */
+#define FSVD_DTYPE_BF16_Q4 2 /* as FSVD_DTYPE_BF16, but every U and V factor pointer is an int4-g128
+                                tile stream made by fsvd_q4_pack (norm weights, embedding, lm_head,
+                                caches, rope tables and activations stay bf16).  Accepted by
+                                fsvd_lowrank_proj, fsvd_lift, fsvd_mlp_swiglu_decode,
+                                fsvd_qkv_rope_append, fsvd_decode_layer and fsvd_model_create. */
 
 #define FSVD_OK 0
 #define FSVD_ERR_ARG (-1)
@@ -202,6 +207,23 @@ int fsvd_model_num_stages(fsvd_model* m);
 int fsvd_model_status(fsvd_model* m, int* device_status);
 /* Clears the barrier words and the status after an error. */
 int fsvd_model_reset_sync(fsvd_model* m, void* stream);
+/* int4 factors: src/quant/packed_quant_linear.py:18-35 (format), :126-171 (pack_weight), :285-300
+ * (dequantize: w = scale * (q - zero), groups of 128 along the input dimension).  The reference
+ * keeps a dense dequantised copy for decode; here the codes are multiplied as they stream in
+ * (y = sum over groups of scale * sum_k (q - 8) x_k, fp32 accumulation) and nothing dense is made.
+ * fsvd_q4_pack copies one PackedQuantLinear ([rows, K]: qweight uint8 [rows, K/2] with the low
+ * nibble = even input index, scales fp16 [rows, ceil(K/128)], zeros int16 [rows, ceil(K/128)] or
+ * NULL) into a stream of fsvd_q4_packed_bytes(rows, K) bytes that the kernels read with TMA: tiles
+ * of 16 rows x 1024 inputs, each 16 x 512 bytes of codes followed by 512 bytes holding the tile's
+ * 16 x 8 scales.  Only the symmetric format is supported: with zeros != NULL the call
+ * synchronises the stream and returns FSVD_ERR_UNSUPPORTED when a zero point differs from 8.
+ * K must be a multiple of 8.  A matrix made by concatenating factors along rows (qkv_v, upgate_v,
+ * [q_u; k_u; v_u]) is packed after concatenation, or part by part at byte offsets
+ * fsvd_q4_packed_bytes(rows_before, K) when rows_before is a multiple of 16. */
+size_t fsvd_q4_packed_bytes(int rows, int K);
+int fsvd_q4_pack(const void* qweight, const void* scales, const void* zeros, int rows, int K,
+                 void* out, void* stream);
+
 /* Kernel launches enqueued by this library since load (for launch accounting). */
 long long fsvd_launch_count(void);
 

@@ -1,0 +1,214 @@
+"""GPU parity tests of the int4-g128 factor path (FSVD_DTYPE_BF16_Q4) through the C ABI.
+
+Oracle: the reference's own dequantisation (w = scale * (q - 8) per group of 128 inputs, cast to
+bf16; src/quant/packed_quant_linear.py:285-300, restated in oracle.lowrank_llama.dequantize_int4)
+followed by the bf16 low-rank path.  The kernel multiplies the codes as they stream in and applies
+the scale per group in fp32, so it differs from the oracle by the bf16 rounding of each dequantised
+weight: tolerance rel_linf <= 2e-2, the bf16 per-layer bound."""
+import pytest
+import torch
+
+from oracle import lowrank_llama as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+BF = torch.bfloat16
+
+
+def rel_linf(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from flashsvd_b200 import _lib
+
+    _lib.load()
+    return torch.device("cuda:0")
+
+
+def _rand_q4(out_f, in_f, gen, *, benign=True):
+    """CPU (qweight, scales, zeros) + the dequantised bf16 weight.  benign: scales that give
+    weights of std 1/sqrt(in) (keeps a whole layer well conditioned); otherwise the benchmark
+    configuration's scales, uniform in [0.005, 0.02]."""
+    from flashsvd_b200 import quant
+
+    lo, hi = (0.5 / (4.6 * in_f ** 0.5), 1.5 / (4.6 * in_f ** 0.5)) if benign else (0.005, 0.02)
+    qw, s, z = quant.random_q4(out_f, in_f, generator=gen, device="cpu", scale_lo=lo, scale_hi=hi)
+    return (qw, s, z), O.dequantize_int4(qw, s, z, in_f, 128, BF)
+
+
+def _to_dev(triple, dev):
+    return tuple(t.to(dev) for t in triple)
+
+
+def test_pack_layout_round_trip(dev):
+    # the tile stream holds exactly the codes and scales it was given, at the documented places
+    from flashsvd_b200 import quant
+
+    gen = torch.Generator().manual_seed(1)
+    rows, K = 40, 1488          # 2.5 row tiles, 1.45 column tiles, 11.6 groups
+    (qw, s, z), _ = _rand_q4(rows, K, gen)
+    f = quant.pack_q4(*_to_dev((qw, s, z), dev), K)
+    nrt, nct = (rows + 15) // 16, (K + 1023) // 1024
+    t = f.packed.cpu().view(nrt, nct, 17, 512)
+    codes = t[:, :, :16, :].permute(0, 2, 1, 3).reshape(nrt * 16, nct * 512)
+    assert torch.equal(codes[:rows, :K // 2], qw)
+    assert bool((codes[rows:] == 0x88).all()) and bool((codes[:rows, K // 2:] == 0x88).all())
+    sc = t[:, :, 16, :256].contiguous().view(torch.float16).view(nrt, nct, 16, 8)
+    sc = sc.permute(0, 2, 1, 3).reshape(nrt * 16, nct * 8)
+    assert torch.equal(sc[:rows, :s.shape[1]], s)
+    assert bool((sc[rows:] == 0).all()) and bool((sc[:rows, s.shape[1]:] == 0).all())
+    assert bool((t[:, :, 16, 256:] == 0).all())
+
+
+def test_pack_rejects_asymmetric_zero_points(dev):
+    from flashsvd_b200 import quant
+
+    gen = torch.Generator().manual_seed(2)
+    (qw, s, z), _ = _rand_q4(16, 256, gen)
+    z[3, 1] = 7
+    with pytest.raises(ValueError, match="symmetric"):
+        quant.pack_q4(*_to_dev((qw, s, z), dev), 256)
+
+
+@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("d_in,R,d_out,benign", [(4096, 1024, 4096, False), (11008, 1488, 4096, False),
+                                                 (264, 72, 200, True), (1024, 128, 48, True)])
+def test_lowrank_proj_q4(dev, B, d_in, R, d_out, benign):
+    from flashsvd_b200 import ops, quant
+
+    gen = torch.Generator().manual_seed(B * 1000 + d_in)
+    vq, v_w = _rand_q4(R, d_in, gen, benign=benign)
+    uq, u_w = _rand_q4(d_out, R, gen, benign=benign)
+    x = torch.randn(B, d_in, generator=gen).to(BF)
+    res = torch.randn(B, d_out, generator=gen).to(BF)
+    dims = ops.make_dims(dtype=BF, B=B, d=max(d_in, d_out), I=max(d_in, d_out), Ro=R, Rd=R, Rg=R, Ru=R,
+                         Rq=R, Rk=R, Rv=R)
+    ws = ops.make_workspace(dims, dev)
+    fv, fu = quant.pack_q4(*_to_dev(vq, dev), d_in), quant.pack_q4(*_to_dev(uq, dev), R)
+    y = ops.lowrank_proj(x.to(dev), fv, fu, ws)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert rel_linf(y, O.lowrank(x, v_w, u_w)) <= TOL
+    y = ops.lowrank_proj(x.to(dev), fv, fu, ws, residual=res.to(dev))
+    assert rel_linf(y, res + O.lowrank(x, v_w, u_w)) <= TOL
+    # the lift alone, from a rank-space vector
+    p = torch.randn(B, R, generator=gen).to(BF)
+    y = ops.lift(p.to(dev), fu, ws)
+    assert rel_linf(y, torch.nn.functional.linear(p, u_w)) <= TOL
+    assert ws.status() == 0
+
+
+def test_lowrank_proj_q4_is_linear_in_the_scales(dev):
+    # size-independent property at the full width: doubling every scale doubles the output exactly
+    from flashsvd_b200 import ops, quant
+
+    gen = torch.Generator().manual_seed(11)
+    d_in, R, d_out = 4096, 1024, 4096
+    (vq, vs, vz), _ = _rand_q4(R, d_in, gen, benign=True)
+    (uq, us, uz), _ = _rand_q4(d_out, R, gen, benign=True)
+    x = torch.randn(1, d_in, generator=gen).to(BF).to(dev)
+    dims = ops.make_dims(dtype=BF, B=1, d=d_in, I=d_in, Ro=R, Rd=R, Rg=R, Ru=R, Rq=R, Rk=R, Rv=R)
+    ws = ops.make_workspace(dims, dev)
+    fv = quant.pack_q4(*_to_dev((vq, vs, vz), dev), d_in)
+    fu = quant.pack_q4(*_to_dev((uq, us, uz), dev), R)
+    fu2 = quant.pack_q4(*_to_dev((uq, us * 2, uz), dev), R)
+    y1 = ops.lowrank_proj(x, fv, fu, ws)
+    y2 = ops.lowrank_proj(x, fv, fu2, ws)
+    y1b = ops.lowrank_proj(x, fv, fu, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y1b)                       # run-to-run bitwise determinism
+    assert torch.equal(y2.float(), 2 * y1.float())    # powers of two commute with every rounding
+
+
+def _q4_layer(shape, gen, dev, *, benign=True):
+    """Quantised layer: (fields for fsvd_layer with Q4Factor factors, dense bf16 weights for the oracle)."""
+    from flashsvd_b200 import quant
+
+    q, w = {}, {}
+    for key, (out_f, in_f) in shape.factor_shapes().items():
+        triple, dense = _rand_q4(out_f, in_f, gen, benign=benign)
+        q[key] = (*_to_dev(triple, dev), in_f)
+        w[key] = dense
+    w["ln1"] = (1.0 + 0.1 * torch.randn(shape.d, generator=gen)).to(BF)
+    w["ln2"] = (1.0 + 0.1 * torch.randn(shape.d, generator=gen)).to(BF)
+    return quant.pack_layer_q4(q, ln1=w["ln1"].to(dev), ln2=w["ln2"].to(dev)), w
+
+
+@pytest.mark.parametrize("shape,B,ctx,S_max", [(O.TINY, 1, 37, 64), (O.TINY_GQA, 2, 50, 64), (O.TINY, 3, 0, 16),
+                                               (O.LLAMA7B_SVD50, 1, 512, 516)])
+def test_decode_layer_q4_matches_oracle(dev, shape, B, ctx, S_max):
+    from flashsvd_b200 import _lib, ops
+
+    gen = torch.Generator().manual_seed(7 + B)
+    pk, w = _q4_layer(shape, gen, dev)
+    x = torch.randn(B, shape.d, generator=gen).to(BF)
+    kc = torch.zeros(B, S_max, shape.Hk, shape.Dh, dtype=BF)
+    vc = torch.zeros_like(kc)
+    if ctx:
+        kc[:, :ctx] = torch.randn(B, ctx, shape.Hk, shape.Dh, generator=gen).to(BF)
+        vc[:, :ctx] = torch.randn(B, ctx, shape.Hk, shape.Dh, generator=gen).to(BF)
+    seqlens = torch.full((B,), ctx, dtype=torch.int32)
+    cos, sin = O.rope_tables(S_max, shape.Dh, shape.theta, BF)
+    kc_o, vc_o = kc.clone(), vc.clone()
+    ref = O.decode_layer(shape, w, x, kc_o, vc_o, seqlens, cos, sin)
+    pk["k_cache"], pk["v_cache"] = kc.to(dev), vc.to(dev)
+    dims = ops.make_dims(dtype=_lib.DTYPE_BF16_Q4, B=B, d=shape.d, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, I=shape.I,
+                         Rq=shape.Rq, Rk=shape.Rk, Rv=shape.Rv, Ro=shape.Ro, Rg=shape.Rg, Ru=shape.Ru, Rd=shape.Rd,
+                         S_max=S_max, eps=shape.eps)
+    ws = ops.make_workspace(dims, dev)
+    out = torch.empty(B, shape.d, dtype=BF, device=dev)
+    ops.decode_layer(dims, ops.make_layer_struct(pk), cos.to(dev), sin.to(dev), seqlens.to(dev), x.to(dev), out, ws)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert rel_linf(out, ref) <= TOL
+    assert rel_linf(pk["k_cache"][:, ctx], kc_o[:, ctx]) <= TOL
+    assert rel_linf(pk["v_cache"][:, ctx], vc_o[:, ctx]) <= TOL
+
+
+def test_mlp_q4_from_hidden_state(dev):
+    from flashsvd_b200 import ops
+
+    shape, B = O.TINY_GQA, 2
+    gen = torch.Generator().manual_seed(21)
+    pk, w = _q4_layer(shape, gen, dev)
+    x = torch.randn(B, shape.d, generator=gen).to(BF)
+    dims = ops.make_dims(dtype=BF, B=B, d=shape.d, I=shape.I, Rg=shape.Rg, Ru=shape.Ru, Rd=shape.Rd)
+    ws = ops.make_workspace(dims, dev)
+    y = ops.mlp_swiglu_decode(x.to(dev), pk["gate_u"], pk["up_u"], pk["down_v"], pk["down_u"], ws,
+                              upgate_v=pk["upgate_v"], norm_w=pk["ln2_w"], eps=shape.eps, residual=x.to(dev))
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    h = O.rmsnorm(x, w["ln2"], shape.eps)
+    pcat = torch.cat([torch.nn.functional.linear(h, w["up_v"]), torch.nn.functional.linear(h, w["gate_v"])], 1)
+    assert rel_linf(y, x + O.mlp_from_pcat(pcat, w)) <= TOL
+
+
+def test_model_q4_greedy_matches_oracle(dev):
+    # whole quantised model (dense embedding and lm_head): logits of every step against the oracle
+    from flashsvd_b200.engine import DecodeEngine
+
+    shape, B, n_new, L = O.TINY, 2, 6, 5
+    gen = torch.Generator().manual_seed(33)
+    layers, model = [], {"layers": []}
+    for _ in range(shape.n_layers):
+        pk, w = _q4_layer(shape, gen, dev)
+        layers.append(pk)
+        model["layers"].append(w)
+    model["embed"] = torch.randn(shape.vocab, shape.d, generator=gen).to(BF)
+    model["lm_head"] = (torch.randn(shape.vocab, shape.d, generator=gen) / shape.d ** 0.5).to(BF)
+    model["norm"] = torch.ones(shape.d, dtype=BF)
+    prompt = torch.randint(0, shape.vocab, (B, L), generator=gen)
+    toks_ref, logits_ref, _ = O.greedy_decode(shape, model, prompt, n_new, S_max=32)
+    eng = DecodeEngine(layers=layers, embed=model["embed"].to(dev), final_norm=model["norm"].to(dev),
+                       lm_head=model["lm_head"].to(dev), num_heads=shape.H, num_kv_heads=shape.Hk,
+                       head_dim=shape.Dh, batch_size=B, max_cache_len=32, rope_theta=shape.theta, eps=shape.eps,
+                       max_steps=64)
+    assert eng.quantized
+    eng.prefill(prompt)
+    torch.cuda.synchronize()
+    assert eng.status() == 0
+    assert rel_linf(eng.logits, logits_ref[0]) <= TOL
