@@ -154,6 +154,9 @@ def main():
     ap.add_argument("--layers", type=int, default=32,
                     help="fewer than 32 layers = a small case of the same kernel for profiler captures; "
                          "its line is marked profile_case and is not a benchmark result")
+    ap.add_argument("--factors", choices=("bf16", "int4"), default="bf16",
+                    help="int4: the same model with every U and V factor int4-g128 (codes uniform in [-8, 7], fp16 "
+                         "scales uniform in [0.005, 0.02]); a second workload, not the headline line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -181,7 +184,8 @@ def main():
         shape = dataclasses.replace(shape, n_layers=int(args.layers))
     warm = max(3, args.warmup)
     eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=1, ctx=CTX,
-                                max_new=warm + 2 * args.steps + 16, seed=rank)
+                                max_new=warm + 2 * args.steps + 16, seed=rank,
+                                factors="int4" if args.factors == "int4" else "dense")
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -236,11 +240,13 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         ctx_mid = CTX + warm + args.steps // 2
-        bytes_step = shape.bytes_per_step(ctx_mid, 1)
+        q4 = args.factors == "int4"
+        bytes_step = shape.q4_bytes_per_step(ctx_mid, 1) if q4 else shape.bytes_per_step(ctx_mid, 1)
         achieved = bytes_step / (ms / args.steps * 1e-3) / 1e9
-        layer_bytes = shape.params_per_layer() * 2 + 2 * ctx_mid * shape.Hk * shape.Dh * 2
+        layer_bytes = (shape.q4_bytes_per_layer() if q4 else shape.params_per_layer() * 2) + \
+            2 * ctx_mid * shape.Hk * shape.Dh * 2
         line = {
-            "metric": METRIC,
+            "metric": METRIC + (" [int4-g128 factors]" if q4 else ""),
             "value": world * args.steps / (ms * 1e-3),
             "unit": "tokens/s",
             "n_gpus": world,
@@ -258,10 +264,12 @@ def main():
                 "l2": "not flushed: a step streams 6.99 GB of factors, far more than the 126 MB L2",
                 "device_status": status,
                 **({"profile_case": f"{shape.n_layers} layers only"} if shape.n_layers != 32 else {}),
+                **({"factors": "int4-g128 symmetric, fp16 scales, dequantised inside the kernel; "
+                               f"{bytes_step / 1e9:.2f} GB per step"} if q4 else {}),
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_RATIO * bytes_step,
+                "peak_kind": f"of {peak_kind}", "traffic": None if q4 else NCU_TRAFFIC_RATIO * bytes_step,
                 "traffic_note": "ncu dram bytes of a 4-layer launch scaled by algorithmic bytes",
                 "bytes_per_launch": bytes_step, "bytes_per_layer": layer_bytes,
                 "us_per_layer_equiv": ms / args.steps * 1e3 * layer_bytes / bytes_step,

@@ -1239,12 +1239,24 @@ __global__ void q4_pack_kernel(const unsigned char* __restrict__ qweight, const 
     uint4 v;
     unsigned char b[16];
     unsigned short h[8];
+    unsigned int u[4];
   } o;
   if (r17 < kUnitRows) {
     const long long row = rt * kUnitRows + r17;
     for (int i = 0; i < 16; ++i) {
       const int bcol = ct * kBoxRowBytes + w16 * 16 + i;
       o.b[i] = (row < rows && bcol < rowbytes) ? qweight[row * rowbytes + bcol] : (unsigned char)0x88;
+    }
+    // inside every 32-bit word (inputs 8 i .. 8 i + 7): even inputs to the low half, odd inputs to
+    // the high half, so that (w >> 4 n) & 0x000f000f is the pair of inputs (2 n, 2 n + 1)
+    for (int i = 0; i < 4; ++i) {
+      const unsigned int w = o.u[i];
+      unsigned int r = 0;
+      for (int n = 0; n < 4; ++n) {
+        r |= ((w >> (8 * n)) & 0xfu) << (4 * n);             // input 2 n
+        r |= ((w >> (8 * n + 4)) & 0xfu) << (16 + 4 * n);    // input 2 n + 1
+      }
+      o.u[i] = r;
     }
   } else {
     const long long row = rt * kUnitRows + w16;

@@ -750,11 +750,12 @@ __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, co
 // row; xq: the lane's 32 inputs of group 0 (64 bytes; group j is 256 bytes further).
 // A warp-wide 16-byte load covers exactly one group of one row: lane t holds the codes of
 // inputs 32 t .. 32 t + 31 of the group.  Word i of those 16 bytes holds inputs 8 i .. 8 i + 7,
-// one per nibble; (w >> 4 n) & 0x000f000f picks inputs (n, n + 4) into the two halves of a
+// even inputs in the nibbles of the low half, odd inputs in the high half (fsvd_q4_pack orders
+// them so): (w >> 4 n) & 0x000f000f is the pair of inputs (2 n, 2 n + 1) in the two halves of a
 // register, OR 0x4300 makes each the bf16 number 128 + code, minus 136 gives code - 8 exactly.
-// The k-slots of the MMA are thus inputs (0,4 | 1,5) and (2,6 | 3,7) of a word; the vector side is
-// permuted the same way.  A group's 8 MMAs start from zero; the sum is scaled by the (row, group)
-// scale in fp32: y = sum_groups s * sum_k (code - 8) x.
+// The pairs line up with the bf16 pairs of the staged vector, so the vector side needs no
+// shuffling.  A group's 8 MMAs start from zero; the sum is scaled by the (row, group) scale in
+// fp32: y = sum_groups s * sum_k (code - 8) x.
 __device__ __forceinline__ uint32_t q4_pair(uint32_t w) {
   const uint32_t v = (w & 0x000f000fu) | 0x43004300u;
   const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), __floats2bfloat162_rn(136.f, 136.f));
@@ -774,11 +775,9 @@ __device__ __forceinline__ void q4_box(uint32_t wb, uint32_t sb, uint32_t xq, in
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 xv = lds128(xq + j * 256 + i * 16);
-      const uint32_t y04 = __byte_perm(xv.x, xv.z, 0x5410), y15 = __byte_perm(xv.x, xv.z, 0x7632);
-      const uint32_t y26 = __byte_perm(xv.y, xv.w, 0x5410), y37 = __byte_perm(xv.y, xv.w, 0x7632);
       const uint32_t wl = low[i], wh = hiw[i];
-      mma_bf16_16816(ga, q4_pair(wl), q4_pair(wh), q4_pair(wl >> 4), q4_pair(wh >> 4), y04, y15);
-      mma_bf16_16816(gb, q4_pair(wl >> 8), q4_pair(wh >> 8), q4_pair(wl >> 12), q4_pair(wh >> 12), y26, y37);
+      mma_bf16_16816(ga, q4_pair(wl), q4_pair(wh), q4_pair(wl >> 4), q4_pair(wh >> 4), xv.x, xv.y);
+      mma_bf16_16816(gb, q4_pair(wl >> 8), q4_pair(wh >> 8), q4_pair(wl >> 12), q4_pair(wh >> 12), xv.z, xv.w);
     }
     const float s0 = half_bits_to_float(sgw[j >> 1] >> ((j & 1) * 16));
     const float s1 = half_bits_to_float(shw[j >> 1] >> ((j & 1) * 16));

@@ -129,7 +129,8 @@ constexpr int kMaxSlots = 21;          // ring slots; a multiple of kConsumerWar
 // int4 factors (4-bit codes, symmetric, one fp16 scale per row and group of 128 inputs) are
 // stored as a stream of tiles, one tile per box: tile (rt, ct) covers rows [16 rt, 16 rt + 16) and
 // inputs [1024 ct, 1024 ct + 1024) and is 17 rows of 512 bytes: rows 0..15 hold the codes of the
-// 16 factor rows (two per byte, low nibble = even input), row 16 holds the 16 x 8 scales
+// 16 factor rows (eight per 32-bit word: inputs 8 i .. 8 i + 7 in word i, the even ones in the
+// nibbles of the low half-word, the odd ones in the high half-word), row 16 holds the 16 x 8 scales
 // (fp16, [row][group], 256 bytes) and 256 bytes of zeros.  Codes past the matrix are 8 (= 0 after
 // the offset) and scales past it are 0.  Tiles are stored row-major over (rt, ct).
 constexpr int kQ4TileRows = kUnitRows + 1;

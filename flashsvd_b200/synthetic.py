@@ -44,6 +44,22 @@ class ModelShape:
         kv = 2 * batch * ctx * self.Hk * self.Dh * esize
         return self.n_layers * (self.params_per_layer() * esize + kv) + self.vocab * self.d * esize
 
+    def factor_dims(self):
+        """(rows, in_features) of the 14 factors of a layer."""
+        d, HD, KD, I = self.d, self.H * self.Dh, self.Hk * self.Dh, self.I
+        return [(self.Rq, d), (HD, self.Rq), (self.Rk, d), (KD, self.Rk), (self.Rv, d), (KD, self.Rv),
+                (self.Ro, HD), (d, self.Ro), (self.Rg, d), (I, self.Rg), (self.Ru, d), (I, self.Ru),
+                (self.Rd, I), (d, self.Rd)]
+
+    def q4_bytes_per_layer(self, group: int = 128) -> int:
+        """Algorithmic bytes of a layer's int4-g128 factors: half a byte per code and one fp16
+        scale per row and group."""
+        return sum(r * k // 2 + r * ((k + group - 1) // group) * 2 for r, k in self.factor_dims())
+
+    def q4_bytes_per_step(self, ctx: int, batch: int) -> int:
+        kv = 2 * batch * ctx * self.Hk * self.Dh * 2
+        return self.n_layers * (self.q4_bytes_per_layer() + kv) + self.vocab * self.d * 2
+
 
 LLAMA7B_SVD50 = ModelShape()
 
@@ -92,14 +108,47 @@ def random_packed_layers(shape: ModelShape, *, device, dtype, seed: int = 0, sha
     return layers, embed, final_norm, lm_head
 
 
+def random_q4_layers(shape: ModelShape, *, device, seed: int = 0, scale_lo: float = 0.005, scale_hi: float = 0.02):
+    """Per-layer int4-g128 factors as tile streams (quant.pack_layer_q4), drawn on the device:
+    codes uniform in [-8, 7], fp16 scales uniform in [scale_lo, scale_hi]; dense bf16 embedding,
+    lm_head and unit norm weights."""
+    from . import quant
+    from .packing import FACTOR_KEYS
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    d, HD, KD, I = shape.d, shape.H * shape.Dh, shape.Hk * shape.Dh, shape.I
+    dims = {"q_v": (shape.Rq, d), "q_u": (HD, shape.Rq), "k_v": (shape.Rk, d), "k_u": (KD, shape.Rk),
+            "v_v": (shape.Rv, d), "v_u": (KD, shape.Rv), "o_v": (shape.Ro, HD), "o_u": (d, shape.Ro),
+            "gate_v": (shape.Rg, d), "gate_u": (I, shape.Rg), "up_v": (shape.Ru, d), "up_u": (I, shape.Ru),
+            "down_v": (shape.Rd, I), "down_u": (d, shape.Rd)}
+    layers = []
+    for _ in range(shape.n_layers):
+        q = {}
+        for key in FACTOR_KEYS:
+            out_f, in_f = dims[key]
+            q[key] = (*quant.random_q4(out_f, in_f, generator=gen, device=device, scale_lo=scale_lo,
+                                       scale_hi=scale_hi), in_f)
+        ones = torch.ones(d, device=device, dtype=torch.bfloat16)
+        layers.append(quant.pack_layer_q4(q, ln1=ones, ln2=ones.clone()))
+
+    def w(out_f, in_f):
+        t = torch.randn(out_f, in_f, device=device, dtype=torch.float32, generator=gen)
+        return (t / math.sqrt(in_f)).to(torch.bfloat16)
+
+    return layers, w(shape.vocab, d), torch.ones(d, device=device, dtype=torch.bfloat16), w(shape.vocab, d)
+
+
 def make_engine(shape: ModelShape, *, device, dtype=torch.bfloat16, batch=1, ctx=512, max_new=64, seed=0,
-                fill_cache=True, share_pairs=False):
+                fill_cache=True, share_pairs=False, factors="dense"):
     """Random model + engine whose caches already hold ``ctx`` tokens of N(0,1) keys / values (the
     state after a prefill of that length, as far as the cost of a decode step goes)."""
     from .engine import DecodeEngine
 
-    layers, embed, final_norm, lm_head = random_packed_layers(shape, device=device, dtype=dtype, seed=seed,
-                                                              share_pairs=share_pairs)
+    if factors == "int4":
+        layers, embed, final_norm, lm_head = random_q4_layers(shape, device=device, seed=seed)
+    else:
+        layers, embed, final_norm, lm_head = random_packed_layers(shape, device=device, dtype=dtype, seed=seed,
+                                                                  share_pairs=share_pairs)
     eng = DecodeEngine(layers=layers, embed=embed, final_norm=final_norm, lm_head=lm_head,
                        num_heads=shape.H, num_kv_heads=shape.Hk, head_dim=shape.Dh, batch_size=batch,
                        max_cache_len=ctx + max_new + 4, rope_theta=shape.theta, eps=shape.eps,

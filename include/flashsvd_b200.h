@@ -214,7 +214,8 @@ int fsvd_model_reset_sync(fsvd_model* m, void* stream);
  * fsvd_q4_pack copies one PackedQuantLinear ([rows, K]: qweight uint8 [rows, K/2] with the low
  * nibble = even input index, scales fp16 [rows, ceil(K/128)], zeros int16 [rows, ceil(K/128)] or
  * NULL) into a stream of fsvd_q4_packed_bytes(rows, K) bytes that the kernels read with TMA: tiles
- * of 16 rows x 1024 inputs, each 16 x 512 bytes of codes followed by 512 bytes holding the tile's
+ * of 16 rows x 1024 inputs, each 16 x 512 bytes of codes (nibbles regrouped inside every 32-bit word: even inputs in the
+ * low half-word, odd inputs in the high one) followed by 512 bytes holding the tile's
  * 16 x 8 scales.  Only the symmetric format is supported: with zeros != NULL the call
  * synchronises the stream and returns FSVD_ERR_UNSUPPORTED when a zero point differs from 8.
  * K must be a multiple of 8.  A matrix made by concatenating factors along rows (qkv_v, upgate_v,

@@ -55,6 +55,11 @@ def test_pack_layout_round_trip(dev):
     nrt, nct = (rows + 15) // 16, (K + 1023) // 1024
     t = f.packed.cpu().view(nrt, nct, 17, 512)
     codes = t[:, :, :16, :].permute(0, 2, 1, 3).reshape(nrt * 16, nct * 512)
+    # undo the regrouping inside every 32-bit word (even inputs in the low half, odd in the high)
+    wd = codes.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    nib = torch.stack([(wd >> (4 * n)) & 0xF for n in range(8)], dim=-1)          # stored nibble order
+    orig = torch.stack([nib[..., [0, 4][i % 2] + i // 2] for i in range(8)], dim=-1)   # input 0..7
+    codes = (orig[..., 0::2] | (orig[..., 1::2] << 4)).to(torch.uint8).reshape(nrt * 16, nct * 512)
     assert torch.equal(codes[:rows, :K // 2], qw)
     assert bool((codes[rows:] == 0x88).all()) and bool((codes[:rows, K // 2:] == 0x88).all())
     sc = t[:, :, 16, :256].contiguous().view(torch.float16).view(nrt, nct, 16, 8)
