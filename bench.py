@@ -157,6 +157,10 @@ def main():
     ap.add_argument("--factors", choices=("bf16", "int4"), default="bf16",
                     help="int4: the same model with every U and V factor int4-g128 (codes uniform in [-8, 7], fp16 "
                          "scales uniform in [0.005, 0.02]); a second workload, not the headline line")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per GPU (1..8); other than 1 = a second workload")
+    ap.add_argument("--ctx", type=int, default=CTX, help="cached positions before the first timed step")
+    ap.add_argument("--share-pairs", action="store_true",
+                    help="basis sharing: layers (2i, 2i+1) share their input-side factors")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -183,9 +187,11 @@ def main():
 
         shape = dataclasses.replace(shape, n_layers=int(args.layers))
     warm = max(3, args.warmup)
-    eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=1, ctx=CTX,
+    B, ctx0 = int(args.batch), int(args.ctx)
+    eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=B, ctx=ctx0,
                                 max_new=warm + 2 * args.steps + 16, seed=rank,
-                                factors="int4" if args.factors == "int4" else "dense")
+                                factors="int4" if args.factors == "int4" else "dense",
+                                share_pairs=bool(args.share_pairs))
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -213,8 +219,8 @@ def main():
     launches = ops.launch_count() - launches0 - warm
 
     # ---- end to end: the host feeds every token and reads every sampled token back
-    pin_in = torch.zeros(1, dtype=torch.int32).pin_memory()
-    pin_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+    pin_in = torch.zeros(B, dtype=torch.int32).pin_memory()
+    pin_out = torch.zeros(B, dtype=torch.int32).pin_memory()
     tok = eng.tokens
     pin_in.copy_(tok.cpu())
     barrier()
@@ -239,15 +245,16 @@ def main():
 
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
-        ctx_mid = CTX + warm + args.steps // 2
+        ctx_mid = ctx0 + warm + args.steps // 2
         q4 = args.factors == "int4"
-        bytes_step = shape.q4_bytes_per_step(ctx_mid, 1) if q4 else shape.bytes_per_step(ctx_mid, 1)
+        bytes_step = shape.q4_bytes_per_step(ctx_mid, B) if q4 else shape.bytes_per_step(ctx_mid, B)
+        variant = B != 1 or ctx0 != CTX or args.share_pairs
         achieved = bytes_step / (ms / args.steps * 1e-3) / 1e9
         layer_bytes = (shape.q4_bytes_per_layer() if q4 else shape.params_per_layer() * 2) + \
-            2 * ctx_mid * shape.Hk * shape.Dh * 2
+            2 * B * ctx_mid * shape.Hk * shape.Dh * 2
         line = {
             "metric": METRIC + (" [int4-g128 factors]" if q4 else ""),
-            "value": world * args.steps / (ms * 1e-3),
+            "value": world * B * args.steps / (ms * 1e-3),
             "unit": "tokens/s",
             "n_gpus": world,
             "steps": args.steps,
@@ -264,18 +271,20 @@ def main():
                 "l2": "not flushed: a step streams 6.99 GB of factors, far more than the 126 MB L2",
                 "device_status": status,
                 **({"profile_case": f"{shape.n_layers} layers only"} if shape.n_layers != 32 else {}),
+                **({"variant": f"batch {B} per GPU, ctx {ctx0}" + (", layer pairs share input-side factors"
+                                                                     if args.share_pairs else "")} if variant else {}),
                 **({"factors": "int4-g128 symmetric, fp16 scales, dequantised inside the kernel; "
                                f"{bytes_step / 1e9:.2f} GB per step"} if q4 else {}),
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": None if q4 else NCU_TRAFFIC_RATIO * bytes_step,
+                "peak_kind": f"of {peak_kind}", "traffic": None if (q4 or variant) else NCU_TRAFFIC_RATIO * bytes_step,
                 "traffic_note": "ncu dram bytes of a 4-layer launch scaled by algorithmic bytes",
                 "bytes_per_launch": bytes_step, "bytes_per_layer": layer_bytes,
                 "us_per_layer_equiv": ms / args.steps * 1e3 * layer_bytes / bytes_step,
             },
-            "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "e2e": {"value": world * B * args.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }

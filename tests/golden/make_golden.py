@@ -244,6 +244,13 @@ def main():
     d_or = O.dequantize_int4(pq.qweight, pq.scales, pq.zeros, 200, 128, torch.float32)
     assert torch.equal(d_ref, d_or), "int4 dequantisation differs from PackedQuantLinear.dequantize"
     report.append("int4: oracle dequantize == PackedQuantLinear.dequantize (bit-exact, ragged last group)")
+    from flashsvd_b200 import quant
+
+    qw2, sc2, z2 = quant.quantize_symmetric(wq)
+    assert torch.equal(qw2, pq.qweight) and torch.equal(sc2, pq.scales) and torch.equal(z2, pq.zeros), \
+        "quant.quantize_symmetric differs from PackedQuantLinear.pack_weight(sym=True)"
+    report.append("int4: quant.quantize_symmetric == PackedQuantLinear.pack_weight(sym=True) (bit-exact)")
+    golden["q_weight"] = wq.numpy()
     golden["q_qweight"] = pq.qweight.numpy()
     golden["q_scales"] = pq.scales.float().numpy()
     golden["q_zeros"] = pq.zeros.numpy()

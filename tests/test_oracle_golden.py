@@ -46,6 +46,17 @@ def test_int4_dequantize_matches_reference(golden):
     assert np.array_equal(d.numpy(), golden["q_dequant"])
 
 
+def test_int4_quantiser_matches_reference(golden):
+    # flashsvd_b200.quant.quantize_symmetric against PackedQuantLinear.pack_weight(sym=True)
+    # (src/quant/packed_quant_linear.py:126-171): codes, fp16 scales and zero points bit-exact
+    from flashsvd_b200 import quant
+
+    qw, sc, z = quant.quantize_symmetric(torch.from_numpy(golden["q_weight"]))
+    assert np.array_equal(qw.numpy(), golden["q_qweight"])
+    assert np.array_equal(sc.float().numpy(), golden["q_scales"])
+    assert np.array_equal(z.numpy(), golden["q_zeros"])
+
+
 def test_layer_matches_dense_transformers_layer(golden):
     shape = O.TINY
     gen = torch.Generator().manual_seed(7)
