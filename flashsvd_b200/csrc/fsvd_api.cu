@@ -178,7 +178,7 @@ static int encode_map_q4(unsigned char* out, const void* base, long long tiles) 
 static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 constexpr int kMaxSegs = 8;
 constexpr int kMaxSplit = 32;
-constexpr size_t kCounterBytes = 4096;  // B * Hk ints, B <= 4
+constexpr size_t kCounterBytes = 4096;  // B * Hk ints
 
 struct WsLayout {
   size_t sync, pa, pb, hact, qbuf, attn, hidden, part_acc, part_ml, counters, total;
@@ -274,8 +274,12 @@ struct Builder {
     const size_t off = wq4 ? q4_bytes(rows, K) : (size_t)rows * K * esize;
     return reinterpret_cast<const char*>(base) + off;
   }
+  // seg_x: the input is a T vector copied as it is (VL_SUM with SF_IN_T); when it is long and there
+  // are several batch rows, the K segments are restricted to divisors of the grid so that every CTA
+  // works in one segment and stages only that part of the input (SF_SEG_X): the staged vector then
+  // no longer takes the shared memory the ring needs.
   Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k, int rope_half = 0,
-              int q4_override = -1) {
+              int q4_override = -1, bool seg_x = false) {
     const bool q4 = q4_override < 0 ? wq4 : q4_override != 0;
     const int boxcols = q4 ? kQ4BoxCols : this->boxcols;
     const int boxbytes = q4 ? kQ4BoxBytes : kBoxBytes;
@@ -291,12 +295,14 @@ struct Builder {
     const int groups = (P + kUnitRows - 1) / kUnitRows;
     const int nchunks = (K + boxcols - 1) / boxcols;
     int best_segs = 1, best_cps = nchunks;
+    const bool local = seg_x && split_k && B > 1 && (long long)K * esize > 8192 && env_int("FSVD_SEG_X", 1) != 0;
     if (split_k) {
       long long best_cost = -1;
-      for (int segs = 1; segs <= kMaxSegs && segs <= nchunks; ++segs) {
+      for (int segs = local ? 2 : 1; segs <= kMaxSegs && segs <= nchunks; ++segs) {
         const int cps = (nchunks + segs - 1) / segs;
         const int real = (nchunks + cps - 1) / cps;
         if (real != segs) continue;
+        if (local && grid % segs) continue;
         const long long units = (long long)groups * real;
         // time of the busiest CTA's boxes at an SM's share of HBM bandwidth (44 bytes/ns), plus
         // the time every CTA of the next stage spends reading `real` partial vectors from L2
@@ -312,6 +318,7 @@ struct Builder {
     }
     s.segs = best_segs;
     s.cps = best_cps;
+    if (local && best_segs > 1 && grid % best_segs == 0) s.flags |= SF_SEG_X;
     s.kseg = best_cps * boxcols;
     s.nch = q4 ? nchunks : 0;
     s.rot = (int)(cum_units % grid);
@@ -344,7 +351,8 @@ struct Builder {
     s.vl_len = len;
     s.vl_nseg = nseg;
     if (barrier) need_barrier(s);
-    if (len > max_vec) max_vec = len;
+    const int staged = (s.flags & SF_SEG_X) ? (len < s.kseg ? len : s.kseg) : len;
+    if (staged > max_vec) max_vec = staged;
   }
   void need_barrier(Stage& s) {
     s.flags |= SF_BARRIER;
@@ -376,7 +384,8 @@ struct Builder {
       // (the fused q/k/v lift reads the inputs of its three parts at 0, K and 2 K)
       const long long reach = (long long)(s.xA_off > s.xB_off ? s.xA_off : s.xB_off) +
                               (s.epi == EPI_QKV ? 2ll * s.K : 0ll) +
-                              (long long)s.segs * s.cps * ((s.flags & SF_Q4) ? kQ4BoxCols : boxcols);
+                              (long long)((s.flags & SF_SEG_X) ? 1 : s.segs) * s.cps *
+                                  ((s.flags & SF_Q4) ? kQ4BoxCols : boxcols);
       if (reach > mx) mx = reach;
     }
     return (int)((mx + 7) / 8 * 8) + 8;   // + 16 bytes so that batch rows start in different banks
@@ -407,7 +416,11 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int check_dims(const fsvd_dims& D) {
   if (D.dtype != FSVD_DTYPE_BF16 && D.dtype != FSVD_DTYPE_F32 && D.dtype != FSVD_DTYPE_BF16_Q4)
     return fail(FSVD_ERR_ARG, "bad dtype %d", D.dtype);
-  if (D.B < 1 || D.B > 4) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..4)", D.B);
+  const int bmax = D.dtype == FSVD_DTYPE_F32 ? 4 : 8;
+  if (D.B < 1 || D.B > bmax) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..%d)", D.B, bmax);
+  if ((size_t)D.B * D.Hk * sizeof(int) > kCounterBytes)
+    return fail(FSVD_ERR_UNSUPPORTED, "B * Hk = %d exceeds the attention counters (%d)", D.B * D.Hk,
+                (int)(kCounterBytes / sizeof(int)));
   if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim %d unsupported (64, 128)", D.Dh);
   if (D.Hk < 1 || D.H % D.Hk) return fail(FSVD_ERR_ARG, "H=%d not a multiple of Hk=%d", D.H, D.Hk);
   const int G = D.H / D.Hk;
@@ -525,7 +538,7 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     b.need_barrier(b.st.back());
   }
   {  // 6. o rank projection
-    Stage& s = b.gemv(Lw.o_v, nullptr, D.Ro, HD, HD, true);
+    Stage& s = b.gemv(Lw.o_v, nullptr, D.Ro, HD, HD, true, 0, -1, true);
     b.vec(s, VL_SUM, attn, HD, 1, true);
     s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
@@ -560,7 +573,7 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     s.out = hact;
   }
   {  // 10. down rank projection
-    Stage& s = b.gemv(Lw.down_v, nullptr, D.Rd, D.I, D.I, true);
+    Stage& s = b.gemv(Lw.down_v, nullptr, D.Rd, D.I, D.I, true, 0, -1, true);
     b.vec(s, VL_SUM, hact, D.I, 1, true);
     s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
@@ -724,7 +737,7 @@ int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* r
   Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
   {
-    Stage& s = b.gemv(v, nullptr, R, d_in, d_in, true);
+    Stage& s = b.gemv(v, nullptr, R, d_in, d_in, true, 0, -1, true);
     b.vec(s, VL_SUM, x, d_in, 1, false);
     s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
@@ -817,7 +830,7 @@ int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const v
     s.out = w + L.hact;
   }
   {
-    Stage& s = b.gemv(down_v, nullptr, Rd, I, I, true);
+    Stage& s = b.gemv(down_v, nullptr, Rd, I, I, true, 0, -1, true);
     b.vec(s, VL_SUM, w + L.hact, I, 1, true);
     s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;

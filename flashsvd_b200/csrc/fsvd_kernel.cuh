@@ -455,15 +455,27 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
   const int len = st.vl_len, B = st.B;
   const bool inT = (st.flags & SF_IN_T) != 0;
   if (st.vl_mode == VL_SUM && inT) {
-    // T -> T copy (nseg is 1 for every T source)
+    // T -> T copy (nseg is 1 for every T source); with SF_SEG_X only the K segment of this CTA
     constexpr int U = 4;
-    const int upr = len / VEC, units = B * upr;
+    int col0 = 0, lenS = len;
+    if (st.flags & SF_SEG_X) {
+      const int grid = gridDim.x;
+      const int seg = first_item(blockIdx.x, st.rot % grid, grid) % st.segs;
+      const int kseg = st.cps * (kBoxRowBytes / (int)sizeof(T)) * ((st.flags & SF_Q4) ? 4 : 1);
+      col0 = seg * kseg;
+      lenS = len - col0 < kseg ? len - col0 : kseg;
+      if (lenS < 0) lenS = 0;
+    }
+    const int upr = lenS / VEC, units = B * upr;
     for (int u0 = tid; u0 < units; u0 += nthreads * U) {
       uint4 v[U];
 #pragma unroll
       for (int q = 0; q < U; ++q) {
         const int u = u0 + q * nthreads;
-        if (u < units) v[q] = ld_raw16<T>(st.vl_src, (size_t)u * VEC);
+        if (u < units) {
+          const int b = u / upr, k = (u - b * upr) * VEC;
+          v[q] = ld_raw16<T>(st.vl_src, (size_t)b * len + col0 + k);
+        }
       }
 #pragma unroll
       for (int q = 0; q < U; ++q) {
@@ -910,7 +922,7 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
       const int j = nops == 2 ? (io >> 1) : io, op = nops == 2 ? (io & 1) : 0;
       const int uidx = bp.first + j * grid;
       const int seg = uidx % segs;
-      xcol0 = (op ? st.xB_off : st.xA_off) + seg * cps * boxcols;
+      xcol0 = (op ? st.xB_off : st.xA_off) + ((st.flags & SF_SEG_X) ? 0 : seg * cps * boxcols);
       if (st.epi == EPI_QKV) {   // segs == 1: uidx is the row group; the part's input starts at part * K
         const int p0 = uidx * kUnitRows, half = st.rope_half;
         xcol0 += ((p0 >= st.H * half) + (p0 >= (st.H + st.Hk) * half)) * st.K;

@@ -52,6 +52,8 @@ enum StageFlags : int {
   SF_RESID_T = 8,    // resid holds T instead of fp32
   SF_ARRIVE = 16,    // arrive at the grid barrier after this stage (the next one has SF_BARRIER)
   SF_Q4 = 32,        // WA / WB are int4 tile streams (see kQ4*), activations stay T = bf16
+  SF_SEG_X = 64,     // segs divides the grid, so a CTA's units all lie in K segment (first unit % segs):
+                     // only that segment of the input (a T vector) is staged, at offset 0
 };
 
 // `rnd` above rounds to the storage type T (bf16) and is the identity when T is fp32: these

@@ -248,3 +248,30 @@ def test_argument_errors_raise_before_launch(dev):
     small = ops.Workspace(torch.zeros(64, dtype=torch.uint8, device=dev), 64)
     with pytest.raises(ValueError):
         ops.lowrank_proj(x, torch.zeros(16, 64, device=dev), torch.zeros(64, 16, device=dev), small)
+
+
+@pytest.mark.parametrize("dtype,B,d_in,R,d_out", [(torch.bfloat16, 4, 11008, 1488, 4096), (torch.bfloat16, 8, 11008, 1488, 4096),
+                                                  (torch.float32, 2, 4096, 1024, 4096), (torch.bfloat16, 2, 4352, 64, 72)])
+def test_lowrank_proj_long_input_several_rows(dev, dtype, B, d_in, R, d_out):
+    # a long input vector with several batch rows is staged one K segment per CTA
+    from flashsvd_b200 import ops
+
+    gen = torch.Generator().manual_seed(B + d_in)
+    v_w = (torch.randn(R, d_in, generator=gen) / d_in ** 0.5).to(dtype)
+    u_w = (torch.randn(d_out, R, generator=gen) / R ** 0.5).to(dtype)
+    x = torch.randn(B, d_in, generator=gen).to(dtype)
+    dims = ops.make_dims(dtype=dtype, B=B, d=max(d_in, d_out), I=max(d_in, d_out), Ro=R, Rd=R, Rg=R, Ru=R, Rq=R,
+                         Rk=R, Rv=R)
+    ws = ops.make_workspace(dims, dev)
+    y = ops.lowrank_proj(x.to(dev), v_w.to(dev), u_w.to(dev), ws)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert rel_linf(y, O.lowrank(x, v_w, u_w)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("shape,B,ctx,S_max", [(O.LLAMA7B_SVD50, 4, 300, 304), (O.TINY, 8, 20, 32), (O.TINY_GQA, 7, 9, 16)])
+def test_decode_layer_wide_batches(dev, shape, B, ctx, S_max):
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, shape, torch.bfloat16, B, ctx, S_max=S_max, seed=3)
+    assert rel_linf(out, ref) <= TOL[torch.bfloat16]
+    assert rel_linf(pk["k_cache"], kc_o) <= TOL[torch.bfloat16]
+    assert rel_linf(pk["v_cache"], vc_o) <= TOL[torch.bfloat16]
