@@ -33,6 +33,7 @@ class FsvdDims(C.Structure):
         ("Dh", C.c_int), ("I", C.c_int), ("Rq", C.c_int), ("Rk", C.c_int), ("Rv", C.c_int),
         ("Ro", C.c_int), ("Rg", C.c_int), ("Ru", C.c_int), ("Rd", C.c_int), ("S_max", C.c_int),
         ("vocab", C.c_int), ("n_layers", C.c_int), ("eps", C.c_float),
+        ("rows_are_positions", C.c_int),
     ]
 
 

@@ -456,6 +456,7 @@ struct LayerIO {
 // PyTorch path rounds them.
 static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, const LayerIO& io,
                         char* ws, const WsLayout& L) {
+  const size_t first_stage = b.st.size();
   void* pa = ws + L.pa;
   void* pb = ws + L.pb;
   void* hact = ws + L.hact;
@@ -588,6 +589,10 @@ static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, co
     s.flags |= SF_RESID_T | SF_OUT_T;
     s.out = io.x_out;
   }
+  // a chunk of one sequence's prompt: every row uses cache row 0
+  if (D.rows_are_positions)
+    for (size_t i = first_stage; i < b.st.size(); ++i)
+      if (b.st[i].cache || b.st[i].kcache) b.st[i].flags |= SF_SHARED_CACHE;
 }
 
 static int check_layer_ptrs(const fsvd_layer& Lw) {

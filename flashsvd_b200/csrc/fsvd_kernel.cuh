@@ -179,6 +179,10 @@ __device__ __forceinline__ int phys_row(int rope_half, int p) {
   return p;
 }
 
+// Row of the KV cache that batch row b reads and writes: its own, or row 0 for all when the batch
+// rows are consecutive positions of one sequence (chunked prompt pass).
+__device__ __forceinline__ int cache_row(const Stage& st, int b) { return (st.flags & SF_SHARED_CACHE) ? 0 : b; }
+
 // First unit / item of rank `r` when the assignment is rotated by `rot` over `n` ranks.
 __device__ __forceinline__ int first_item(int r, int rot, int n) {
   int f = r - rot;
@@ -321,7 +325,7 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
           q[base + half] = o2;
         }
       } else if (pos < st.S_max) {
-        const size_t base = (((size_t)b * st.S_max + pos) * st.Hk + h) * st.Dh + j;
+        const size_t base = (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + h) * st.Dh + j;
         X::st(st.cache, base, o1);
         X::st(st.cache, base + half, o2);
       }
@@ -329,7 +333,7 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
     case EPI_V: {
       const int pos = ax.pos;
       if (pos < st.S_max)
-        X::st(st.cache, ((size_t)b * st.S_max + pos) * ((size_t)st.Hk * st.Dh) + p, X::rnd(a));
+        X::st(st.cache, ((size_t)cache_row(st, b) * st.S_max + pos) * ((size_t)st.Hk * st.Dh) + p, X::rnd(a));
     } break;
     case EPI_QKV: {
       const int half = st.rope_half, pos = ax.pos;
@@ -350,13 +354,13 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
             q[base + half] = o2;
           }
         } else if (pos < st.S_max) {
-          const size_t base = (((size_t)b * st.S_max + pos) * st.Hk + (hh - st.H)) * st.Dh + j;
+          const size_t base = (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + (hh - st.H)) * st.Dh + j;
           X::st(st.cache, base, o1);
           X::st(st.cache, base + half, o2);
         }
       } else if (pos < st.S_max) {
         void* vc = const_cast<void*>(st.vcache);
-        const size_t base = (((size_t)b * st.S_max + pos) * st.Hk + (hh - st.H - st.Hk)) * st.Dh + j;
+        const size_t base = (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + (hh - st.H - st.Hk)) * st.Dh + j;
         X::st(vc, base, x1);
         X::st(vc, base + half, x2);
       }
@@ -1103,7 +1107,7 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
     const int n = min(cached_pos(pc, st.seqlens, b) + st.seqlen_add, st.S_max);
     const int per = (n + nsplit - 1) / nsplit;
     const int j0 = sp * per, j1 = min(n, j0 + per);
-    const size_t base = ((size_t)b * st.S_max) * kv_row + (size_t)hk * Dh + lane * DPL;
+    const size_t base = ((size_t)cache_row(st, b) * st.S_max) * kv_row + (size_t)hk * Dh + lane * DPL;
     const size_t row_bytes = kv_row * sizeof(T);
     const char* kbase = reinterpret_cast<const char*>(st.kcache) + base * sizeof(T);
     const char* vbase = reinterpret_cast<const char*>(st.vcache) + base * sizeof(T);

@@ -52,6 +52,7 @@ enum StageFlags : int {
   SF_RESID_T = 8,    // resid holds T instead of fp32
   SF_ARRIVE = 16,    // arrive at the grid barrier after this stage (the next one has SF_BARRIER)
   SF_Q4 = 32,        // WA / WB are int4 tile streams (see kQ4*), activations stay T = bf16
+  SF_SHARED_CACHE = 128,  // the B rows are consecutive positions of one sequence: all use cache row 0
   SF_SEG_X = 64,     // segs divides the grid, so a CTA's units all lie in K segment (first unit % segs):
                      // only that segment of the input (a T vector) is staged, at offset 0
 };

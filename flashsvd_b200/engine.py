@@ -36,7 +36,7 @@ class DecodeEngine:
 
     def __init__(self, *, layers, embed, final_norm, lm_head, num_heads, num_kv_heads, head_dim,
                  batch_size, max_cache_len, rope_theta=10000.0, eps=1e-6, max_steps=4096,
-                 share_cache_alloc=True):
+                 share_cache_alloc=True, prefill_chunk=None):
         self.lib = _lib.load()
         dev = embed.device
         if dev.type != "cuda":
@@ -90,6 +90,14 @@ class DecodeEngine:
                 self.cos.data_ptr(), self.sin.data_ptr(), int(max_steps), C.byref(handle)))
         self.handle = handle
         self.max_steps = int(max_steps)
+        # Prompt pass of a single sequence: a second program over the same weights and caches takes
+        # `prefill_chunk` consecutive prompt positions per launch (rows_are_positions of fsvd_dims);
+        # it is created on the first prompt that is long enough.
+        cmax = 4 if dtype == torch.float32 else 8
+        self.prefill_chunk = (cmax if prefill_chunk is None else max(1, min(int(prefill_chunk), cmax))) \
+            if self.B == 1 else 1
+        self._layer_array, self._model_args = arr, (embed, final_norm, lm_head)
+        self._chunk_handle = None
         ptrs = [C.c_void_p() for _ in range(6)]
         check(self.lib.fsvd_model_buffers(self.handle, *[C.byref(p) for p in ptrs]))
         self._ptrs = dict(zip(("tokens", "seqlens", "token_log", "step_counter", "logits", "hidden"),
@@ -129,23 +137,72 @@ class DecodeEngine:
         self.seqlens.zero_()
         self.step_counter.zero_()
 
+    def _chunk_model(self):
+        """The program that takes `prefill_chunk` prompt positions of the one sequence per launch."""
+        if self._chunk_handle is None:
+            d = self.dims
+            self._chunk_dims = _lib.FsvdDims(d.dtype, self.prefill_chunk, d.d, d.H, d.Hk, d.Dh, d.I, d.Rq, d.Rk, d.Rv,
+                                             d.Ro, d.Rg, d.Ru, d.Rd, d.S_max, d.vocab, d.n_layers, d.eps, 1)
+            embed, final_norm, lm_head = self._model_args
+            handle = C.c_void_p()
+            with torch.cuda.device(self.device):
+                check(self.lib.fsvd_model_create(
+                    C.byref(self._chunk_dims), self._layer_array, embed.data_ptr(), final_norm.data_ptr(),
+                    lm_head.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), 1, C.byref(handle)))
+            ptrs = [C.c_void_p() for _ in range(6)]
+            check(self.lib.fsvd_model_buffers(handle, *[C.byref(p) for p in ptrs]))
+            self._chunk_handle = handle
+            self._chunk_tokens = _from_ptr(ptrs[0].value, (self.prefill_chunk,), torch.int32, self.device)
+            self._chunk_seqlens = _from_ptr(ptrs[1].value, (self.prefill_chunk,), torch.int32, self.device)
+        return self._chunk_handle
+
     def prefill(self, prompt: torch.Tensor) -> None:
-        """Feed prompt[B, L] token by token through the decode kernel (fills the caches and leaves
-        the first generated token in ``tokens``)."""
+        """Feed prompt[B, L] through the decode kernel: fills the caches and leaves the first
+        generated token in ``tokens`` and its logits in ``logits``.  A single sequence goes
+        `prefill_chunk` positions per launch (causal inside the chunk) as long as more than one
+        chunk is left, the rest token by token; several sequences go token by token."""
         prompt = prompt.to(device=self.device, dtype=torch.int32).contiguous()
         if prompt.shape[0] != self.B:
             raise ValueError(f"prompt batch {prompt.shape[0]} != engine batch {self.B}")
+        L, t0 = prompt.shape[1], 0
+        Cn = self.prefill_chunk
+        if self.B == 1 and Cn > 1 and L > Cn:
+            handle = self._chunk_model()
+            pos0 = int(self.seqlens[0].item())
+            if pos0 + L > self.S_max:
+                raise ValueError(f"prompt of {L} tokens at position {pos0} exceeds the cache ({self.S_max})")
+            offs = torch.arange(Cn, device=self.device, dtype=torch.int32)
+            stream = torch.cuda.current_stream().cuda_stream
+            while L - t0 > Cn:
+                self._chunk_tokens.copy_(prompt[0, t0:t0 + Cn])
+                self._chunk_seqlens.copy_(offs + (pos0 + t0))
+                check(self.lib.fsvd_model_step(handle, 1, stream))
+                t0 += Cn
+            self.seqlens.fill_(pos0 + t0)
         tok = self.tokens
-        for t in range(prompt.shape[1]):
+        for t in range(t0, L):
             tok.copy_(prompt[:, t])
             self.step(1)
+
+    def last_tokens(self, n: int) -> torch.Tensor:
+        """The tokens sampled by the last n single-token launches, [n, B] (blocking).  After
+        ``prefill`` + ``step(n - 1)`` these are the n generated tokens."""
+        steps = int(self.step_counter.item())
+        if n > steps or steps > self.max_steps:
+            raise IndexError(f"{n} tokens asked, {steps} logged (log capacity {self.max_steps})")
+        return self.token_log[steps - n: steps].clone()
 
     def status(self) -> int:
         st = C.c_int(0)
         check(self.lib.fsvd_model_status(self.handle, C.byref(st)))
+        if st.value == 0 and self._chunk_handle is not None:
+            check(self.lib.fsvd_model_status(self._chunk_handle, C.byref(st)))
         return int(st.value)
 
     def close(self) -> None:
+        if getattr(self, "_chunk_handle", None) is not None and self._chunk_handle.value:
+            self.lib.fsvd_model_destroy(self._chunk_handle)
+            self._chunk_handle = None
         if getattr(self, "handle", None) is not None and self.handle.value:
             self.lib.fsvd_model_destroy(self.handle)
             self.handle = C.c_void_p()

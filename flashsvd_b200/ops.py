@@ -84,9 +84,12 @@ class Workspace:
 
 
 def make_dims(*, dtype, B=1, d=8, H=1, Hk=1, Dh=64, I=8, Rq=8, Rk=8, Rv=8, Ro=8, Rg=8, Ru=8,
-              Rd=8, S_max=1, vocab=0, n_layers=0, eps=1e-6) -> FsvdDims:
+              Rd=8, S_max=1, vocab=0, n_layers=0, eps=1e-6, rows_are_positions=0) -> FsvdDims:
+    """rows_are_positions=1: the B rows are consecutive positions of one sequence (a chunk of its
+    prompt) that share cache row 0; cache_seqlens[b] must be first + b."""
     return FsvdDims(_dtype_code(dtype) if isinstance(dtype, torch.dtype) else int(dtype), B, d, H,
-                    Hk, Dh, I, Rq, Rk, Rv, Ro, Rg, Ru, Rd, S_max, vocab, n_layers, eps)
+                    Hk, Dh, I, Rq, Rk, Rv, Ro, Rg, Ru, Rd, S_max, vocab, n_layers, eps,
+                    int(rows_are_positions))
 
 
 def make_workspace(dims: FsvdDims, device) -> Workspace:

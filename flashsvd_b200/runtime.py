@@ -377,7 +377,7 @@ def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: in
     model.prefill(input_ids)
     if max_new_tokens > 1:
         model.step(max_new_tokens - 1)
-    new = model.token_log[prompt_len - 1: prompt_len - 1 + max_new_tokens, 0].cpu().tolist() if max_new_tokens else []
+    new = model.last_tokens(max_new_tokens)[:, 0].cpu().tolist() if max_new_tokens else []
     if model.status() != 0:
         raise RuntimeError("a device-side wait ran out during generation")
     eos = getattr(tokenizer, "eos_token_id", None)

@@ -52,6 +52,15 @@ typedef struct fsvd_dims {
   int vocab;
   int n_layers;
   float eps;   /* RMSNorm epsilon */
+  int rows_are_positions; /* 0: the B rows are independent sequences with cache rows 0..B-1.
+                             1: the B rows are consecutive positions of ONE sequence (a chunk of
+                             its prompt): every row reads and writes cache row 0, row b at position
+                             cache_seqlens[b] (the caller sets cache_seqlens[b] = first + b), and
+                             attends positions <= its own, i.e. causally over the chunk.  Accepted
+                             by fsvd_decode_layer and fsvd_model_create; the caches are then
+                             [1, S_max, Hk, Dh].  The reference fills the cache with its prefill
+                             kernels (kernels/flashsvdropeattn.py:67-427) + cache.update
+                             (runtime/cache/attn_dense_kv.py:138-191). */
 } fsvd_dims;
 
 /* Device pointers of one decoder layer. */

@@ -162,7 +162,9 @@ def _greedy(dev, shape, dtype, prompt, n_new, seed=0):
     logits0 = eng.logits.clone().cpu()
     eng.step(n_new - 1)
     torch.cuda.synchronize()
-    toks = eng.token_log[L - 1: L - 1 + n_new].t().cpu().long()
+    # the log has one row per single-token launch (a single sequence's prompt goes in chunks, which
+    # are not logged): the last n_new rows are the generated tokens
+    toks = eng.last_tokens(n_new).t().cpu().long()
     assert eng.status() == 0
     eng.close()
     return toks, logits0, w
