@@ -274,10 +274,10 @@ struct Builder {
     const size_t off = wq4 ? q4_bytes(rows, K) : (size_t)rows * K * esize;
     return reinterpret_cast<const char*>(base) + off;
   }
-  // seg_x: the input is a T vector copied as it is (VL_SUM with SF_IN_T); when it is long and there
-  // are several batch rows, the K segments are restricted to divisors of the grid so that every CTA
-  // works in one segment and stages only that part of the input (SF_SEG_X): the staged vector then
-  // no longer takes the shared memory the ring needs.
+  // seg_x: the input is a T vector copied as it is (VL_SUM with SF_IN_T); when it is longer than
+  // 4 KB the K segments are restricted to divisors of the grid so that every CTA works in one
+  // segment and stages only that part of the input (SF_SEG_X): a shorter stage-in, and with several
+  // batch rows the staged vector no longer takes the shared memory the ring needs.
   Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k, int rope_half = 0,
               int q4_override = -1, bool seg_x = false) {
     const bool q4 = q4_override < 0 ? wq4 : q4_override != 0;
@@ -295,7 +295,7 @@ struct Builder {
     const int groups = (P + kUnitRows - 1) / kUnitRows;
     const int nchunks = (K + boxcols - 1) / boxcols;
     int best_segs = 1, best_cps = nchunks;
-    const bool local = seg_x && split_k && B > 1 && (long long)K * esize > 8192 && env_int("FSVD_SEG_X", 1) != 0;
+    const bool local = seg_x && split_k && (long long)K * esize > 4096 && env_int("FSVD_SEG_X", 1) != 0;
     if (split_k) {
       long long best_cost = -1;
       for (int segs = local ? 2 : 1; segs <= kMaxSegs && segs <= nchunks; ++segs) {
