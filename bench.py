@@ -151,7 +151,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="flashsvd_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--layers", type=int, default=32,
+    ap.add_argument("--shape", choices=("7b", "70b"), default="7b",
+                    help="70b: the Llama-2-70B-shaped model (80 layers, GQA 64/8, ranks 1312/224/2704) as one replica "
+                         "per GPU; a second workload, not the headline line")
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer than 32 layers = a small case of the same kernel for profiler captures; "
                          "its line is marked profile_case and is not a benchmark result")
     ap.add_argument("--factors", choices=("bf16", "int4"), default="bf16",
@@ -181,7 +184,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    shape = synthetic.LLAMA7B_SVD50
+    shape = synthetic.LLAMA70B_SVD40 if args.shape == "70b" else synthetic.LLAMA7B_SVD50
+    if args.layers is None:
+        args.layers = shape.n_layers
     if args.layers != shape.n_layers:
         import dataclasses
 
@@ -248,7 +253,7 @@ def main():
         ctx_mid = ctx0 + warm + args.steps // 2
         q4 = args.factors == "int4"
         bytes_step = shape.q4_bytes_per_step(ctx_mid, B) if q4 else shape.bytes_per_step(ctx_mid, B)
-        variant = B != 1 or ctx0 != CTX or args.share_pairs
+        variant = B != 1 or ctx0 != CTX or args.share_pairs or args.shape != "7b"
         achieved = bytes_step / (ms / args.steps * 1e-3) / 1e9
         layer_bytes = (shape.q4_bytes_per_layer() if q4 else shape.params_per_layer() * 2) + \
             2 * B * ctx_mid * shape.Hk * shape.Dh * 2
@@ -270,8 +275,10 @@ def main():
                             "vocab 32000, batch 1 per GPU, ctx 512, greedy decode; one step = one kernel launch",
                 "l2": "not flushed: a step streams 6.99 GB of factors, far more than the 126 MB L2",
                 "device_status": status,
-                **({"profile_case": f"{shape.n_layers} layers only"} if shape.n_layers != 32 else {}),
-                **({"variant": f"batch {B} per GPU, ctx {ctx0}" + (", layer pairs share input-side factors"
+                **({"profile_case": f"{shape.n_layers} layers only"}
+                   if shape.n_layers != (80 if args.shape == "70b" else 32) else {}),
+                **({"variant": ("llama2-70b shape (80 layers, ranks 1312/224/2704), " if args.shape == "70b" else "") +
+                    f"batch {B} per GPU, ctx {ctx0}" + (", layer pairs share input-side factors"
                                                                      if args.share_pairs else "")} if variant else {}),
                 **({"factors": "int4-g128 symmetric, fp16 scales, dequantised inside the kernel; "
                                f"{bytes_step / 1e9:.2f} GB per step"} if q4 else {}),

@@ -62,6 +62,9 @@ class ModelShape:
 
 
 LLAMA7B_SVD50 = ModelShape()
+# Llama-2-70B shape with ~40 % of the dense parameters: 55 GB of bf16 factors, one replica fits a GPU
+LLAMA70B_SVD40 = ModelShape(d=8192, H=64, Hk=8, Dh=128, I=28672, Rq=1312, Rk=224, Rv=224, Ro=1312, Rg=2704,
+                            Ru=2704, Rd=2704, vocab=32000, n_layers=80)
 
 
 def _qkv_u(w, HD, KD, shape):

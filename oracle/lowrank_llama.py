@@ -73,6 +73,9 @@ class Shape:
 
 
 LLAMA7B_SVD50 = Shape()
+# Llama-2-70B shape with ~40 % of the dense parameters (80 layers, GQA 64/8)
+LLAMA70B_SVD40 = Shape(d=8192, H=64, Hk=8, Dh=128, I=28672, Rq=1312, Rk=224, Rv=224, Ro=1312, Rg=2704, Ru=2704,
+                       Rd=2704, vocab=32000, n_layers=80)
 TINY = Shape(d=256, H=4, Hk=4, Dh=64, I=512, Rq=64, Rk=64, Rv=64, Ro=64, Rg=96, Ru=96, Rd=96,
              vocab=512, n_layers=2)
 TINY_GQA = Shape(d=256, H=8, Hk=2, Dh=64, I=640, Rq=96, Rk=32, Rv=32, Ro=96, Rg=120, Ru=120,

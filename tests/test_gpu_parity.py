@@ -277,3 +277,13 @@ def test_decode_layer_wide_batches(dev, shape, B, ctx, S_max):
     assert rel_linf(out, ref) <= TOL[torch.bfloat16]
     assert rel_linf(pk["k_cache"], kc_o) <= TOL[torch.bfloat16]
     assert rel_linf(pk["v_cache"], vc_o) <= TOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_decode_layer_70b_shape(dev, B):
+    # one Llama-2-70B-shaped layer: GQA 64/8, ranks 1312 / 224 / 2704 (unequal q/k/v ranks, so three
+    # lift stages), 28672-wide MLP input staged one K segment per CTA
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, O.LLAMA70B_SVD40, torch.bfloat16, B, ctx=300, S_max=304, seed=5)
+    assert rel_linf(out, ref) <= TOL[torch.bfloat16]
+    assert rel_linf(pk["k_cache"][:, 300], kc_o[:, 300]) <= TOL[torch.bfloat16]
+    assert rel_linf(pk["v_cache"][:, 300], vc_o[:, 300]) <= TOL[torch.bfloat16]
