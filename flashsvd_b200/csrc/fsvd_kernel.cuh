@@ -460,7 +460,9 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
   const bool inT = (st.flags & SF_IN_T) != 0;
   if (st.vl_mode == VL_SUM && inT) {
     // T -> T copy (nseg is 1 for every T source); with SF_SEG_X only the K segment of this CTA
-    constexpr int U = 4;
+    // (no unrolling: with segments staged per CTA a thread copies one or two 16-byte pieces, and
+    // the interpreter's code has to stay small - its cold paths are bound by instruction fetch)
+    constexpr int U = 1;
     int col0 = 0, lenS = len;
     if (st.flags & SF_SEG_X) {
       const int grid = gridDim.x;
@@ -539,7 +541,7 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
     }
   } else if (st.vl_mode == VL_RMSNORM) {
     // T source, weight of type T; a row longer than the register window is read twice
-    constexpr int U = 4;
+    constexpr int U = 3;
     const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
     const int upr = len / VEC;
     const bool fits = upr <= nthreads * U;
@@ -1081,7 +1083,10 @@ struct RawRow<float, 2> {
 template <typename T, int GI, int DPL>
 __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCache pc) {
   using X = TT<T>;
-  constexpr int KBASE = (GI == 1) ? 20 : 12;
+  // Rows per chunk: a split of the benchmark shape (18 keys) takes two chunks of 10 rather than one
+  // of 20 - half the unrolled code; the stage is bound by instruction fetch, not by the loads
+  // (measured: 20 rows 407.7, 10 rows 411.5, 9 rows 405.8, 6 rows 401.7 tokens/s).
+  constexpr int KBASE = (GI == 1) ? 10 : 12;
   constexpr int KMAX = sizeof(T) == 2 ? KBASE : KBASE / 2;   // rows in registers
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Dh = st.Dh, H = st.H, B = st.B, grid = gridDim.x;
