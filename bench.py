@@ -30,7 +30,7 @@ sys.path.insert(0, str(ROOT))
 # DRAM traffic / algorithmic bytes of the decode kernel from one ncu capture of a 4-layer launch
 # (profiles/fsvd_decode_kernel_model_4layers_ncu_full.md); traffic grows with the layer count in
 # proportion to the algorithmic bytes.
-NCU_TRAFFIC_RATIO = 1.009
+NCU_TRAFFIC_RATIO = 1.003
 
 METRIC = "decode tokens/s (7B-shape SVD 50%, bf16, bs1, ctx512) and % of HBM roofline"
 CTX = 512
