@@ -69,6 +69,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Quotient and remainder of small non-negative integers (a < 2^22, b > 0) without the long
+// integer-division sequence: (a + 0.5) / b in fp32 is at least 0.5 / b away from an integer,
+// further than the error of the approximate division, and one correction step covers the rest.
+// The interpreter's cold paths are bound by instruction fetch, and they are full of these.
+__device__ __forceinline__ int qdiv(int a, int b) {
+  int q = (int)__fdividef((float)a + 0.5f, (float)b);
+  const int r = a - q * b;
+  q += (r >= b ? 1 : 0) - (r < 0 ? 1 : 0);
+  return q;
+}
+__device__ __forceinline__ int qmod(int a, int b) { return a - qdiv(a, b) * b; }
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -173,7 +185,7 @@ struct TT<float> {
 // ----------------------------------------------------------------------------- small helpers
 __device__ __forceinline__ int phys_row(int rope_half, int p) {
   if (rope_half > 0) {
-    const int h = p / rope_half;
+    const int h = qdiv(p, rope_half);
     return h * 2 * rope_half + (p - h * rope_half);
   }
   return p;
@@ -252,7 +264,7 @@ __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiA
     case EPI_ROPE_Q:
     case EPI_ROPE_K: {
       const int half = st.rope_half;
-      const int j = p % half;
+      const int j = qmod(p, half);
       ax.pos = cached_pos(pc, st.seqlens, b);
       ax.r0 = raw_ld<T>(st.cos_tab, (size_t)ax.pos * half + j);
       ax.r1 = raw_ld<T>(st.sin_tab, (size_t)ax.pos * half + j);
@@ -264,7 +276,7 @@ __device__ __forceinline__ void epi_prefetch(const Stage& st, int p, int b, EpiA
       const int half = st.rope_half;
       ax.pos = cached_pos(pc, st.seqlens, b);
       if (p < (st.H + st.Hk) * half) {   // q and k rows rotate
-        const int j = p % half;
+        const int j = qmod(p, half);
         ax.r0 = raw_ld<T>(st.cos_tab, (size_t)ax.pos * half + j);
         ax.r1 = raw_ld<T>(st.sin_tab, (size_t)ax.pos * half + j);
       }
@@ -308,7 +320,7 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
     case EPI_ROPE_Q:
     case EPI_ROPE_K: {
       const int half = st.rope_half;
-      const int h = p / half, j = p - h * half;
+      const int h = qdiv(p, half), j = p - h * half;
       const int pos = ax.pos;
       const float c = raw_to_float<T>(ax.r0), sn = raw_to_float<T>(ax.r1);
       const float x1 = X::rnd(a), x2 = X::rnd(bsum);
@@ -337,7 +349,7 @@ __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int
     } break;
     case EPI_QKV: {
       const int half = st.rope_half, pos = ax.pos;
-      const int hh = p / half, j = p - hh * half;   // head over [q heads | k heads | v heads]
+      const int hh = qdiv(p, half), j = p - hh * half;   // head over [q heads | k heads | v heads]
       const float x1 = X::rnd(a), x2 = X::rnd(bsum);
       if (hh < st.H + st.Hk) {
         const float c = raw_to_float<T>(ax.r0), sn = raw_to_float<T>(ax.r1);
@@ -466,7 +478,7 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
     int col0 = 0, lenS = len;
     if (st.flags & SF_SEG_X) {
       const int grid = gridDim.x;
-      const int seg = first_item(blockIdx.x, st.rot % grid, grid) % st.segs;
+      const int seg = qmod(first_item(blockIdx.x, qmod(st.rot, grid), grid), st.segs);
       const int kseg = st.cps * (kBoxRowBytes / (int)sizeof(T)) * ((st.flags & SF_Q4) ? 4 : 1);
       col0 = seg * kseg;
       lenS = len - col0 < kseg ? len - col0 : kseg;
@@ -479,7 +491,7 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
       for (int q = 0; q < U; ++q) {
         const int u = u0 + q * nthreads;
         if (u < units) {
-          const int b = u / upr, k = (u - b * upr) * VEC;
+          const int b = qdiv(u, upr), k = (u - b * upr) * VEC;
           v[q] = ld_raw16<T>(st.vl_src, (size_t)b * len + col0 + k);
         }
       }
@@ -487,7 +499,7 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
       for (int q = 0; q < U; ++q) {
         const int u = u0 + q * nthreads;
         if (u < units) {
-          const int b = u / upr, k = (u - b * upr) * VEC;
+          const int b = qdiv(u, upr), k = (u - b * upr) * VEC;
           *reinterpret_cast<uint4*>(xvec + ((size_t)b * xstride + k) * sizeof(T)) = v[q];
         }
       }
@@ -520,7 +532,7 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
 #pragma unroll
             for (int q = 1; q < 3; ++q)
               if (q < nseg) { a.x += v[k][q].x; a.y += v[k][q].y; a.z += v[k][q].z; a.w += v[k][q].w; }
-            const int b = u / upr, k2 = (u - b * upr) * 4;
+            const int b = qdiv(u, upr), k2 = (u - b * upr) * 4;
             st4<T>(xvec, (size_t)b * xstride + k2, a);
           }
         }
@@ -535,7 +547,7 @@ __device__ __forceinline__ void stage_vector(const Stage& st, char* xvec, int xs
 #pragma unroll
         for (int q = 1; q < SMAX; ++q)
           if (q < nseg) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
-        const int b = u / upr, k = (u - b * upr) * 4;
+        const int b = qdiv(u, upr), k = (u - b * upr) * 4;
         st4<T>(xvec, (size_t)b * xstride + k, a);
       }
     }
@@ -657,8 +669,8 @@ struct BoxPlan {
 __device__ __forceinline__ BoxPlan plan_boxes(int P, int segs, int cps, int rot, bool two_ops, int cta, int grid) {
   BoxPlan bp;
   const int total = ((P + kUnitRows - 1) / kUnitRows) * segs;
-  bp.first = first_item(cta, rot % grid, grid);
-  bp.nu = bp.first < total ? (total - bp.first + grid - 1) / grid : 0;
+  bp.first = first_item(cta, qmod(rot, grid), grid);
+  bp.nu = bp.first < total ? qdiv(total - bp.first + grid - 1, grid) : 0;
   bp.nops = two_ops ? 2 : 1;
   bp.cps = cps;
   bp.nbox = bp.nu * bp.nops * cps;
@@ -735,7 +747,7 @@ __device__ __forceinline__ void producer_loop(const Stage* prog, int nstages, co
     __syncwarp(mask);
     if (ok) {
       const int uidx = first + j * grid;
-      const int grp = uidx / segs, seg = uidx - grp * segs;
+      const int grp = qdiv(uidx, segs), seg = uidx - grp * segs;
       const uint32_t fb = rg.full + slot * 8;
       const uint32_t dst = rg.data + (uint32_t)slot * (Q4 ? rg.stride : (uint32_t)kBoxBytes);
       if (Q4 && nch > 0) {
@@ -839,12 +851,12 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
   // that their latency hides behind the barrier and the streaming
   const int nout = bp.nu * rowsB;
   auto out_pos = [&](int o, int& j, int& b, int& r, int& seg, int& p) {
-    j = o / rowsB;
+    j = qdiv(o, rowsB);
     const int rem = o - j * rowsB;
     b = rem >> 4;
     r = rem & 15;
     const int uidx = bp.first + j * grid;
-    const int grp = uidx / segs;
+    const int grp = qdiv(uidx, segs);
     seg = uidx - grp * segs;
     p = grp * kUnitRows + r;
   };
@@ -883,14 +895,14 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
   // of fewer than 7 slots (huge input vectors) has one warp per slot and leaves the others idle.
   const int step = cx.ring.ns < kNWC ? cx.ring.ns : kNWC;
   const int KK = cps < step ? cps : step;   // warps that hold partial sums of one (unit, operand)
-  int l = warp < step ? (warp - (int)(cx.seq_base % step) + step) % step : bp.nbox;
+  int l = warp < step ? qmod(warp - qmod((int)cx.seq_base, step) + step, step) : bp.nbox;
   int slot, round;
   {
     const unsigned seq0 = cx.seq_base + (unsigned)l;
-    round = (int)(seq0 / (unsigned)cx.ring.ns);
+    round = qdiv((int)seq0, cx.ring.ns);
     slot = (int)(seq0 - (unsigned)round * cx.ring.ns);
   }
-  int io = l / cps, c = l - io * cps;   // (unit ordinal * nops + operand), chunk inside it
+  int io = qdiv(l, cps), c = l - io * cps;   // (unit ordinal * nops + operand), chunk inside it
   int cur_io = -1, cur_kk = 0, xcol0 = 0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};          // bf16: mma accumulators (rows g, g+8; batch 2t, 2t+1)
   float accf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // fp32: [row half][batch]
@@ -924,10 +936,10 @@ __device__ __forceinline__ int gemv_stage(const Stage& st, const StageCtx cx) {
     if (io != cur_io) {
       if (cur_io >= 0) flush();
       cur_io = io;
-      cur_kk = c % step;
+      cur_kk = qmod(c, step);
       const int j = nops == 2 ? (io >> 1) : io, op = nops == 2 ? (io & 1) : 0;
       const int uidx = bp.first + j * grid;
-      const int seg = uidx % segs;
+      const int seg = qmod(uidx, segs);
       xcol0 = (op ? st.xB_off : st.xA_off) + ((st.flags & SF_SEG_X) ? 0 : seg * cps * boxcols);
       if (st.epi == EPI_QKV) {   // segs == 1: uidx is the row group; the part's input starts at part * K
         const int p0 = uidx * kUnitRows, half = st.rope_half;
@@ -1103,14 +1115,13 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
   float* const tile = sh + kNWC * GI * rec + warp * (ROWS * 34);
   float* const pbuf = tile + ROWS * 33;
 
-  for (int hs = first_item(blockIdx.x, st.rot % grid, grid); hs < nslice; hs += grid) {
-    const int part = hs % cph;
-    const int hg = (hs / cph) % Hg;
-    const int b = hs / (cph * Hg);
-    const int hk = hg / R;
+  for (int hs = first_item(blockIdx.x, qmod(st.rot, grid), grid); hs < nslice; hs += grid) {
+    const int hq = qdiv(hs, cph), part = hs - hq * cph;
+    const int b = qdiv(hq, Hg), hg = hq - b * Hg;
+    const int hk = qdiv(hg, R);
     const int sp = part * kNWC + warp;
     const int n = min(cached_pos(pc, st.seqlens, b) + st.seqlen_add, st.S_max);
-    const int per = (n + nsplit - 1) / nsplit;
+    const int per = qdiv(n + nsplit - 1, nsplit);
     const int j0 = sp * per, j1 = min(n, j0 + per);
     const size_t base = ((size_t)cache_row(st, b) * st.S_max) * kv_row + (size_t)hk * Dh + lane * DPL;
     const size_t row_bytes = kv_row * sizeof(T);
