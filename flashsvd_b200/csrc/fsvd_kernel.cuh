@@ -1102,7 +1102,7 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
   constexpr int KMAX = sizeof(T) == 2 ? KBASE : KBASE / 2;   // rows in registers
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Dh = st.Dh, H = st.H, B = st.B, grid = gridDim.x;
-  const int R = (H / st.Hk) / GI;          // head groups per kv head
+  const int R = qdiv(H, st.Hk) / GI;       // head groups per kv head
   const int Hg = st.Hk * R;                // head groups per batch row
   const int nsplit = st.nsplit, cph = nsplit / kNWC;
   const int nslice = B * Hg * cph;         // (batch row, head group, part)
@@ -1319,7 +1319,7 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
 
 template <typename T>
 __device__ __forceinline__ void run_attn(const Stage& st, float* sh, const PosCache pc) {
-  const int G = st.H / st.Hk;
+  const int G = qdiv(st.H, st.Hk);
   const int dpl = st.Dh / 32;
   if ((G & 1) == 0) {
     if (dpl == 4) attn_cta<T, 2, 4>(st, sh, pc);
