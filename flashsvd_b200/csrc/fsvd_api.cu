@@ -421,6 +421,10 @@ static int check_dims(const fsvd_dims& D) {
   if ((size_t)D.B * D.Hk * sizeof(int) > kCounterBytes)
     return fail(FSVD_ERR_UNSUPPORTED, "B * Hk = %d exceeds the attention counters (%d)", D.B * D.Hk,
                 (int)(kCounterBytes / sizeof(int)));
+  // the kernel's index arithmetic divides through fp32 reciprocals, exact below 2^22
+  const int big[] = {D.d, D.I, D.S_max, D.vocab, D.H * D.Dh};
+  for (int v : big)
+    if (v >= (1 << 21)) return fail(FSVD_ERR_UNSUPPORTED, "dimension %d is beyond the supported 2^21", v);
   if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim %d unsupported (64, 128)", D.Dh);
   if (D.Hk < 1 || D.H % D.Hk) return fail(FSVD_ERR_ARG, "H=%d not a multiple of Hk=%d", D.H, D.Hk);
   const int G = D.H / D.Hk;
