@@ -11,11 +11,16 @@ the cached keys / values are seeded random tensors of those shapes.
 N > 1 (torchrun): every rank decodes its own sequence on its own replica, no collective on the
 data path; the printed value is the sum over ranks divided by the slowest rank's time.
 
+At N = 1 the line also carries: `parity_check` (the timed engine stepped beside the CPU oracle,
+outside the timed region), `cpu_baseline` (the oracle timed on the host cores), and `secondary`
+(the other workloads of the benchmark configurations, each timed the same way on a fresh engine).
+
 `--impl reference` times the CPU oracle (the restated PyTorch low-rank path) on the host cores.
 """
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import subprocess
@@ -27,13 +32,28 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# DRAM traffic / algorithmic bytes of the decode kernel from one ncu capture of a 4-layer launch
-# (profiles/fsvd_decode_kernel_model_4layers_ncu_full.md); traffic grows with the layer count in
-# proportion to the algorithmic bytes.
-NCU_TRAFFIC_RATIO = 1.003
-
 METRIC = "decode tokens/s (7B-shape SVD 50%, bf16, bs1, ctx512) and % of HBM roofline"
 CTX = 512
+
+# DRAM traffic / algorithmic bytes of the decode kernel, from the ncu capture summarised in the file
+# named here (a 4-layer launch of the same program; traffic grows with the layer count in
+# proportion to the algorithmic bytes).  Reported as an estimate with its source, not as a
+# measurement of the run that prints it.
+NCU_TRAFFIC_RATIO = 1.003
+NCU_TRAFFIC_SOURCE = "profiles/fsvd_decode_kernel_model_4layers_ncu_full.md"
+
+
+def workload_string(shape_name: str, layers: int, batch: int, ctx: int, share_pairs: bool, factors: str) -> str:
+    """One description of the workload, shared by both arms of the benchmark."""
+    model = ("llama2-7b shape (d 4096, 32 heads, I 11008), every projection W=U·V, ranks 1024/1488 (0.499 of dense)"
+             if shape_name == "7b" else
+             "llama2-70b shape (d 8192, GQA 64/8, I 28672), every projection W=U·V, ranks 1312/224/2704 (0.405 of dense)")
+    s = f"{model}, {layers} layers, vocab 32000, batch {batch} per GPU, ctx {ctx}, greedy decode"
+    if share_pairs:
+        s += ", layer pairs share their input-side factors"
+    if factors == "int4":
+        s += ", int4-g128 factors (fp16 scales)"
+    return s
 
 
 def measured_hbm_peak():
@@ -78,70 +98,173 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons}
 
 
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_reference_tokens_per_s(budget_s: float = 20.0):
-    """The oracle on the host cores, bounded sample: a few of the 32 layers at full width, one
-    token at ctx 512, scaled to 32 layers plus lm_head.  Returns (tok/s, cores, sample text)."""
+    """The oracle on the host cores: whole tokens of the 32-layer 7B-shape model at ctx 512 (32 layer
+    evaluations + final norm + lm_head per token), as many as fit the time budget (at least 2).
+    The 32 layer evaluations cycle through 8 distinct sets of full-width factors (1.6 GB, far beyond
+    the CPU caches), each layer with its own cache.  Returns (tok/s, threads, sample text)."""
     import torch
 
     from oracle import lowrank_llama as O
 
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
+    threads = host_threads()
+    torch.set_num_threads(threads)
     shape = O.LLAMA7B_SVD50
-    n_l = 2
-    # bf16 storage as on the GPU; fp32 arithmetic (bf16 GEMV on this CPU is slower), values bf16-rounded
+    n_sets = 8
     gen = torch.Generator().manual_seed(0)
-    layers = [{k: v.to(torch.bfloat16).float() for k, v in O.make_layer_weights(shape, gen, torch.float32).items()}
-              for _ in range(n_l)]
-    lm_head = (torch.randn(shape.vocab, shape.d, generator=gen) / shape.d ** 0.5).to(torch.bfloat16).float()
+    # bf16 storage and arithmetic, as the reference's PyTorch low-rank path runs a bf16 checkpoint
+    dt = torch.bfloat16
+    sets = [O.make_layer_weights(shape, gen, dt) for _ in range(n_sets)]
+    lm_head = (torch.randn(shape.vocab, shape.d, generator=gen) / shape.d ** 0.5).to(dt)
+    norm = torch.ones(shape.d, dtype=dt)
     S_max = CTX + 8
-    ks = [torch.randn(1, S_max, shape.Hk, shape.Dh, generator=gen) for _ in range(n_l)]
-    vs = [torch.randn(1, S_max, shape.Hk, shape.Dh, generator=gen) for _ in range(n_l)]
-    cos, sin = O.rope_tables(S_max, shape.Dh, shape.theta, torch.float32)
-    x = torch.randn(1, shape.d, generator=gen)
+    ks = [torch.randn(1, S_max, shape.Hk, shape.Dh, generator=gen).to(dt) for _ in range(shape.n_layers)]
+    vs = [torch.randn(1, S_max, shape.Hk, shape.Dh, generator=gen).to(dt) for _ in range(shape.n_layers)]
+    cos, sin = O.rope_tables(S_max, shape.Dh, shape.theta, dt)
+    x0 = torch.randn(1, shape.d, generator=gen).to(dt)
     seq = torch.tensor([CTX], dtype=torch.int32)
 
     def one_token():
-        h = x
-        for w, k, v in zip(layers, ks, vs):
-            h = O.decode_layer(shape, w, h, k, v, seq, cos, sin)
-        return torch.nn.functional.linear(O.rmsnorm(h, torch.ones(shape.d), shape.eps), lm_head)
+        h = x0
+        for li in range(shape.n_layers):
+            h = O.decode_layer(shape, sets[li % n_sets], h, ks[li], vs[li], seq, cos, sin)
+        return torch.argmax(torch.nn.functional.linear(O.rmsnorm(h, norm, shape.eps), lm_head).float(), dim=-1)
 
     one_token()
+    times = []
     t0 = time.perf_counter()
-    n = 0
-    while True:
+    while len(times) < 2 or (time.perf_counter() - t0 < budget_s and len(times) < 64):
         t1 = time.perf_counter()
-        for w, k, v in zip(layers, ks, vs):
-            O.decode_layer(shape, w, x, k, v, seq, cos, sin)
-        t_layers = time.perf_counter() - t1
-        t2 = time.perf_counter()
-        torch.nn.functional.linear(x, lm_head)
-        t_head = time.perf_counter() - t2
-        n += 1
-        if time.perf_counter() - t0 > budget_s or n >= 8:
-            break
-    per_token = t_layers / n_l * shape.n_layers + t_head
-    sample = (f"{n_l} of {shape.n_layers} layers at full width + lm_head, 1 token at ctx {CTX}, repeated {n}x, "
-              f"scaled to {shape.n_layers} layers; bf16-rounded weights, fp32 arithmetic")
-    return 1.0 / per_token, cores, sample
+        one_token()
+        times.append(time.perf_counter() - t1)
+    times.sort()
+    per_token = times[len(times) // 2]
+    sample = (f"{len(times)} whole tokens (median), each 32 layer evaluations at full width over {n_sets} distinct "
+              f"factor sets + final norm + lm_head + argmax, ctx {CTX}, bf16 storage and arithmetic, "
+              f"torch {torch.__version__} with {threads} threads")
+    return 1.0 / per_token, threads, sample
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    v, cores, sample = cpu_reference_tokens_per_s(budget_s=max(5.0, min(60.0, 5.0 * args.steps)))
+    v, threads, sample = cpu_reference_tokens_per_s(budget_s=max(5.0, min(60.0, 2.0 * args.steps)))
     line = {
         "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
-        "config": {"workload": "llama2-7b-shape, every projection W=U·V (ranks 1024/1488), 32 layers, batch 1, ctx 512, greedy decode",
-                   "l2": "n/a (CPU)"},
-        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload_string("7b", 32, 1, CTX, False, "bf16"), "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def time_workload(dev, *, shape_name, layers, batch, ctx, share_pairs, factors, steps, warm, seed, world=1,
+                  clocks_index=None, e2e=True, parity_steps=0):
+    """Builds one engine and times it: K kernel-only steps with everything resident, then (e2e)
+    K steps in which the host feeds every token from pinned memory and reads every sampled token
+    back.  Returns a dict of raw measurements (times are this rank's)."""
+    import torch
+    import torch.distributed as dist
+
+    from flashsvd_b200 import ops, synthetic
+
+    base = synthetic.LLAMA70B_SVD40 if shape_name == "70b" else synthetic.LLAMA7B_SVD50
+    shape = dataclasses.replace(base, n_layers=int(layers))
+    eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=batch, ctx=ctx,
+                                max_new=warm + 2 * steps + parity_steps + 16, seed=seed,
+                                factors="int4" if factors == "int4" else "dense", share_pairs=bool(share_pairs),
+                                keep_raw=(factors == "int4" and parity_steps > 0))
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches0 = ops.launch_count()
+    eng.step(warm)
+    barrier()
+    sampler = ClockSampler(clocks_index) if clocks_index is not None else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    eng.step(steps)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    status = eng.status()
+    launches = ops.launch_count() - launches0 - warm
+
+    ms_e2e = None
+    if e2e:
+        pin_in = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        pin_out = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        tok = eng.tokens
+        pin_in.copy_(tok.cpu())
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(stream)
+        for _ in range(steps):
+            tok.copy_(pin_in, non_blocking=True)      # H2D: the token to feed
+            eng.step(1)
+            pin_out.copy_(tok, non_blocking=True)     # D2H: the sampled token
+            stream.synchronize()
+            pin_in.copy_(pin_out)
+        e3.record(stream)
+        barrier()
+        ms_e2e = e2.elapsed_time(e3)
+
+    parity = None
+    if parity_steps > 0:
+        # the timed engine itself, stepped beside the CPU oracle from its current state (outside
+        # every timed region)
+        from oracle import check as OC
+
+        res = OC.teacher_forced(eng, shape, parity_steps)
+        parity = {"steps": parity_steps, "tokens_equal": res["tokens_equal"],
+                  "tokens_explained_by_top2_gap": res["tokens_explained"], "rel_linf": max(res["rel_linf"]),
+                  "against": "CPU oracle on the engine's own weights and caches, teacher-forced",
+                  "device_status": eng.status()}
+    q4 = factors == "int4"
+    ctx_mid = ctx + warm + steps // 2
+    bytes_step = shape.q4_bytes_per_step(ctx_mid, batch) if q4 else shape.bytes_per_step(ctx_mid, batch)
+    layer_bytes = (shape.q4_bytes_per_layer() if q4 else shape.params_per_layer() * 2) + \
+        2 * batch * ctx_mid * shape.Hk * shape.Dh * 2
+    eng.close()
+    del eng
+    torch.cuda.empty_cache()
+    return {"ms": ms, "ms_e2e": ms_e2e, "clocks": clocks, "status": status, "launches": int(launches),
+            "bytes_step": bytes_step, "layer_bytes": layer_bytes, "parity": parity}
+
+
+def roofline_of(r, steps, peak, peak_kind):
+    achieved = r["bytes_step"] / (r["ms"] / steps * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "peak_kind": f"of {peak_kind}", "bytes_per_launch": r["bytes_step"], "bytes_per_layer": r["layer_bytes"],
+            "us_per_layer_equiv": r["ms"] / steps * 1e3 * r["layer_bytes"] / r["bytes_step"]}
+
+
+SECONDARY = (
+    # (name, shape, layers, batch, ctx, share_pairs, factors)
+    ("int4_b1_ctx512", "7b", 32, 1, 512, False, "int4"),
+    ("bf16_b8_ctx512", "7b", 32, 8, 512, False, "bf16"),
+    ("shared_bases_b1_ctx2048", "7b", 32, 1, 2048, True, "bf16"),
+    ("shared_bases_b8_ctx2048", "7b", 32, 8, 2048, True, "bf16"),
+    ("70b_shape_replica_b1_ctx512", "70b", 80, 1, 512, False, "bf16"),
+)
 
 
 def main():
@@ -151,16 +274,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="flashsvd_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity-check", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (N = 1 only runs them)")
     ap.add_argument("--shape", choices=("7b", "70b"), default="7b",
                     help="70b: the Llama-2-70B-shaped model (80 layers, GQA 64/8, ranks 1312/224/2704) as one replica "
                          "per GPU; a second workload, not the headline line")
     ap.add_argument("--layers", type=int, default=None,
-                    help="fewer than 32 layers = a small case of the same kernel for profiler captures; "
+                    help="fewer layers than the model has = a small case of the same kernel for profiler captures; "
                          "its line is marked profile_case and is not a benchmark result")
     ap.add_argument("--factors", choices=("bf16", "int4"), default="bf16",
                     help="int4: the same model with every U and V factor int4-g128 (codes uniform in [-8, 7], fp16 "
                          "scales uniform in [0.005, 0.02]); a second workload, not the headline line")
-    ap.add_argument("--batch", type=int, default=1, help="sequences per GPU (1..8); other than 1 = a second workload")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per GPU; other than 1 = a second workload")
     ap.add_argument("--ctx", type=int, default=CTX, help="cached positions before the first timed step")
     ap.add_argument("--share-pairs", action="store_true",
                     help="basis sharing: layers (2i, 2i+1) share their input-side factors")
@@ -175,8 +300,6 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from flashsvd_b200 import ops, synthetic
-
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: flashsvd_b200 has no CPU path (use --impl reference for the CPU oracle)")
     torch.cuda.set_device(local)
@@ -184,81 +307,33 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    shape = synthetic.LLAMA70B_SVD40 if args.shape == "70b" else synthetic.LLAMA7B_SVD50
-    if args.layers is None:
-        args.layers = shape.n_layers
-    if args.layers != shape.n_layers:
-        import dataclasses
-
-        shape = dataclasses.replace(shape, n_layers=int(args.layers))
+    full_layers = 80 if args.shape == "70b" else 32
+    layers = full_layers if args.layers is None else int(args.layers)
     warm = max(3, args.warmup)
     B, ctx0 = int(args.batch), int(args.ctx)
-    eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=B, ctx=ctx0,
-                                max_new=warm + 2 * args.steps + 16, seed=rank,
-                                factors="int4" if args.factors == "int4" else "dense",
-                                share_pairs=bool(args.share_pairs))
-    stream = torch.cuda.current_stream()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- kernel-only: K steps, inputs resident in HBM, device-side token feedback
+    headline = (args.shape == "7b" and layers == 32 and B == 1 and ctx0 == CTX and not args.share_pairs
+                and args.factors == "bf16")
+    do_parity = headline and world == 1 and not args.no_parity_check
     torch.cuda.profiler.start()   # profiler range = warm-up + timed regions (ncu --profile-from-start off)
-    launches0 = ops.launch_count()
-    eng.step(warm)
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
-    eng.step(args.steps)
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
-    status = eng.status()
-    launches = ops.launch_count() - launches0 - warm
-
-    # ---- end to end: the host feeds every token and reads every sampled token back
-    pin_in = torch.zeros(B, dtype=torch.int32).pin_memory()
-    pin_out = torch.zeros(B, dtype=torch.int32).pin_memory()
-    tok = eng.tokens
-    pin_in.copy_(tok.cpu())
-    barrier()
-    t0 = time.perf_counter()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record(stream)
-    for _ in range(args.steps):
-        tok.copy_(pin_in, non_blocking=True)      # H2D: the token to feed
-        eng.step(1)
-        pin_out.copy_(tok, non_blocking=True)     # D2H: the sampled token
-        stream.synchronize()
-        pin_in.copy_(pin_out)
-    e3.record(stream)
-    barrier()
-    ms_e2e = e2.elapsed_time(e3)
+    r = time_workload(dev, shape_name=args.shape, layers=layers, batch=B, ctx=ctx0, share_pairs=args.share_pairs,
+                      factors=args.factors, steps=args.steps, warm=warm, seed=rank, world=world,
+                      clocks_index=local if rank == 0 else None, e2e=True, parity_steps=4 if do_parity else 0)
     torch.cuda.profiler.stop()
 
-    times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    times = torch.tensor([r["ms"], r["ms_e2e"]], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(times[0]), float(times[1])
+    r["ms"] = ms
 
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
-        ctx_mid = ctx0 + warm + args.steps // 2
-        q4 = args.factors == "int4"
-        bytes_step = shape.q4_bytes_per_step(ctx_mid, B) if q4 else shape.bytes_per_step(ctx_mid, B)
-        variant = B != 1 or ctx0 != CTX or args.share_pairs or args.shape != "7b"
-        achieved = bytes_step / (ms / args.steps * 1e-3) / 1e9
-        layer_bytes = (shape.q4_bytes_per_layer() if q4 else shape.params_per_layer() * 2) + \
-            2 * B * ctx_mid * shape.Hk * shape.Dh * 2
+        roof = roofline_of(r, args.steps, peak, peak_kind)
+        roof["traffic"] = NCU_TRAFFIC_RATIO * r["bytes_step"] if headline else None
+        roof["traffic_source"] = (f"estimate: algorithmic bytes x {NCU_TRAFFIC_RATIO} (ncu dram bytes of a 4-layer "
+                                  f"launch, {NCU_TRAFFIC_SOURCE})") if headline else None
         line = {
-            "metric": METRIC + (" [int4-g128 factors]" if q4 else ""),
+            "metric": METRIC if headline else METRIC + " [secondary workload, see config.workload]",
             "value": world * B * args.steps / (ms * 1e-3),
             "unit": "tokens/s",
             "n_gpus": world,
@@ -271,37 +346,39 @@ def main():
             "dtype": "bf16",
             "data": "synthetic",
             "config": {
-                "workload": "llama2-7b-shape, every projection W=U·V (ranks 1024/1488, 0.499 of dense), 32 layers, "
-                            "vocab 32000, batch 1 per GPU, ctx 512, greedy decode; one step = one kernel launch",
-                "l2": "not flushed: a step streams 6.99 GB of factors, far more than the 126 MB L2",
-                "device_status": status,
-                **({"profile_case": f"{shape.n_layers} layers only"}
-                   if shape.n_layers != (80 if args.shape == "70b" else 32) else {}),
-                **({"variant": ("llama2-70b shape (80 layers, ranks 1312/224/2704), " if args.shape == "70b" else "") +
-                    f"batch {B} per GPU, ctx {ctx0}" + (", layer pairs share input-side factors"
-                                                                     if args.share_pairs else "")} if variant else {}),
-                **({"factors": "int4-g128 symmetric, fp16 scales, dequantised inside the kernel; "
-                               f"{bytes_step / 1e9:.2f} GB per step"} if q4 else {}),
+                "workload": workload_string(args.shape, layers, B, ctx0, args.share_pairs, args.factors),
+                "l2": "not flushed: a step streams its factors once, far more than the 126 MB L2",
+                "one_step": "one kernel launch",
+                "device_status": r["status"],
+                **({"profile_case": f"{layers} of {full_layers} layers"} if layers != full_layers else {}),
             },
-            "roofline": {
-                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": None if (q4 or variant) else NCU_TRAFFIC_RATIO * bytes_step,
-                "traffic_note": "ncu dram bytes of a 4-layer launch scaled by algorithmic bytes",
-                "bytes_per_launch": bytes_step, "bytes_per_layer": layer_bytes,
-                "us_per_layer_equiv": ms / args.steps * 1e3 * layer_bytes / bytes_step,
-            },
+            "roofline": roof,
             "e2e": {"value": world * B * args.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
-            "gpu_launches": int(launches),
-            "clocks": clocks,
+            "gpu_launches": r["launches"],
+            "clocks": r["clocks"],
+            "parity_check": r["parity"] if do_parity else None,
         }
         if not args.no_cpu_baseline and world == 1:
-            v, cores, sample = cpu_reference_tokens_per_s(budget_s=15.0)
-            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+            v, threads, sample = cpu_reference_tokens_per_s(budget_s=15.0)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
         else:
             line["cpu_baseline"] = None
+        if headline and world == 1 and not args.no_secondary:
+            sec = {}
+            for name, sname, lay, b2, c2, share, fac in SECONDARY:
+                try:
+                    s = time_workload(dev, shape_name=sname, layers=lay, batch=b2, ctx=c2, share_pairs=share,
+                                      factors=fac, steps=8, warm=3, seed=0, e2e=False)
+                    ro = roofline_of(s, 8, peak, peak_kind)
+                    sec[name] = {"workload": workload_string(sname, lay, b2, c2, share, fac),
+                                 "value": b2 * 8 / (s["ms"] * 1e-3), "unit": "tokens/s", "ms_per_step": s["ms"] / 8,
+                                 "steps": 8, "warmup": 3, "roofline_frac": ro["frac"], "achieved_gbs": ro["achieved"],
+                                 "bytes_per_launch": ro["bytes_per_launch"], "device_status": s["status"]}
+                except Exception as e:   # a secondary workload must not cost the headline line
+                    sec[name] = {"error": f"{type(e).__name__}: {e}"}
+            line["secondary"] = sec
         print(json.dumps(line), flush=True)
-    eng.close()
     if world > 1:
         dist.destroy_process_group()
 

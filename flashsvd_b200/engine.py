@@ -64,7 +64,8 @@ class DecodeEngine:
         self.B, self.S_max, self.vocab, self.d = int(batch_size), int(max_cache_len), embed.shape[0], d
         self.cos, self.sin = rope_tables(self.S_max, Dh, rope_theta, dtype, dev)
         self.key_cache, self.value_cache = [], []
-        self._keep = [embed, final_norm, lm_head, layers]
+        # the tensors the device program points into (kept alive here)
+        self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
         arr = (FsvdLayer * len(layers))()
         for i, lw in enumerate(layers):
             kc = torch.zeros(self.B, self.S_max, Hk, Dh, dtype=dtype, device=dev)

@@ -25,6 +25,7 @@ class Q4Factor:
 
     packed: torch.Tensor          # uint8, the bytes fsvd_q4_pack wrote
     shape: tuple[int, int]
+    raw: tuple | None = None      # optional (qweight, scales, zeros) the stream was packed from
 
     @property
     def is_cuda(self) -> bool:
@@ -48,7 +49,8 @@ class Q4Factor:
         lib = _lib.load()
         o0 = int(lib.fsvd_q4_packed_bytes(r0, K)) if r0 else 0
         o1 = o0 + int(lib.fsvd_q4_packed_bytes(r1 - r0, K))
-        return Q4Factor(self.packed[o0:o1], (r1 - r0, K))
+        raw = None if self.raw is None else tuple(None if t is None else t[r0:r1] for t in self.raw)
+        return Q4Factor(self.packed[o0:o1], (r1 - r0, K), raw)
 
 
 def pack_int4_codes(q: torch.Tensor) -> torch.Tensor:
@@ -94,8 +96,11 @@ def cat_rows(parts):
     return tuple(torch.cat([p[i] for p in parts], dim=0).contiguous() for i in range(3))
 
 
-def pack_q4(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor | None, in_features: int) -> Q4Factor:
-    """Copy PackedQuantLinear buffers (CUDA tensors) into the tile stream the kernels read."""
+def pack_q4(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor | None, in_features: int,
+            keep_raw: bool = False) -> Q4Factor:
+    """Copy PackedQuantLinear buffers (CUDA tensors) into the tile stream the kernels read.
+    ``keep_raw`` keeps references to the source buffers on the factor (for checks against a
+    dequantised copy); the kernels never read them."""
     if not (qweight.is_cuda and scales.is_cuda):
         raise ValueError("pack_q4 needs CUDA tensors (there is no CPU path)")
     rows = qweight.shape[0]
@@ -114,23 +119,23 @@ def pack_q4(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor | N
             qweight.contiguous().data_ptr(), scales.contiguous().data_ptr(),
             None if zeros is None else zeros.contiguous().data_ptr(), rows, in_features, out.data_ptr(),
             torch.cuda.current_stream().cuda_stream))
-    return Q4Factor(out, (rows, in_features))
+    return Q4Factor(out, (rows, in_features), (qweight, scales, zeros) if keep_raw else None)
 
 
-def pack_layer_q4(q: dict, *, ln1: torch.Tensor, ln2: torch.Tensor) -> dict:
+def pack_layer_q4(q: dict, *, ln1: torch.Tensor, ln2: torch.Tensor, keep_raw: bool = False) -> dict:
     """q maps packing.FACTOR_KEYS to (qweight, scales, zeros, in_features); returns the fields of
     ``fsvd_layer`` (without the caches) with every factor as a Q4Factor.  q_u, k_u and v_u share
     one stream when their ranks agree, so the three lifts run as one stage."""
     def one(key):
         qw, s, z, k = q[key]
-        return pack_q4(qw, s, z, k)
+        return pack_q4(qw, s, z, k, keep_raw)
 
     def cat(keys):
         k = q[keys[0]][3]
         if any(q[x][3] != k for x in keys):
             raise ValueError(f"{keys} must share in_features")
         qw, s, z = cat_rows([q[x][:3] for x in keys])
-        return pack_q4(qw, s, z, k)
+        return pack_q4(qw, s, z, k, keep_raw)
 
     nq, nk = q["q_u"][0].shape[0], q["k_u"][0].shape[0]
     if q["q_u"][3] == q["k_u"][3] == q["v_u"][3] and nq % 16 == 0 and nk % 16 == 0:

@@ -111,7 +111,8 @@ def random_packed_layers(shape: ModelShape, *, device, dtype, seed: int = 0, sha
     return layers, embed, final_norm, lm_head
 
 
-def random_q4_layers(shape: ModelShape, *, device, seed: int = 0, scale_lo: float = 0.005, scale_hi: float = 0.02):
+def random_q4_layers(shape: ModelShape, *, device, seed: int = 0, scale_lo: float = 0.005, scale_hi: float = 0.02,
+                     keep_raw: bool = False):
     """Per-layer int4-g128 factors as tile streams (quant.pack_layer_q4), drawn on the device:
     codes uniform in [-8, 7], fp16 scales uniform in [scale_lo, scale_hi]; dense bf16 embedding,
     lm_head and unit norm weights."""
@@ -132,7 +133,7 @@ def random_q4_layers(shape: ModelShape, *, device, seed: int = 0, scale_lo: floa
             q[key] = (*quant.random_q4(out_f, in_f, generator=gen, device=device, scale_lo=scale_lo,
                                        scale_hi=scale_hi), in_f)
         ones = torch.ones(d, device=device, dtype=torch.bfloat16)
-        layers.append(quant.pack_layer_q4(q, ln1=ones, ln2=ones.clone()))
+        layers.append(quant.pack_layer_q4(q, ln1=ones, ln2=ones.clone(), keep_raw=keep_raw))
 
     def w(out_f, in_f):
         t = torch.randn(out_f, in_f, device=device, dtype=torch.float32, generator=gen)
@@ -142,13 +143,13 @@ def random_q4_layers(shape: ModelShape, *, device, seed: int = 0, scale_lo: floa
 
 
 def make_engine(shape: ModelShape, *, device, dtype=torch.bfloat16, batch=1, ctx=512, max_new=64, seed=0,
-                fill_cache=True, share_pairs=False, factors="dense"):
+                fill_cache=True, share_pairs=False, factors="dense", keep_raw=False):
     """Random model + engine whose caches already hold ``ctx`` tokens of N(0,1) keys / values (the
     state after a prefill of that length, as far as the cost of a decode step goes)."""
     from .engine import DecodeEngine
 
     if factors == "int4":
-        layers, embed, final_norm, lm_head = random_q4_layers(shape, device=device, seed=seed)
+        layers, embed, final_norm, lm_head = random_q4_layers(shape, device=device, seed=seed, keep_raw=keep_raw)
     else:
         layers, embed, final_norm, lm_head = random_packed_layers(shape, device=device, dtype=dtype, seed=seed,
                                                                   share_pairs=share_pairs)
