@@ -70,16 +70,41 @@ def state_from_engine(eng) -> O.DecodeState:
     return st
 
 
-def teacher_forced(eng, shape: O.Shape, n_steps: int, model: dict | None = None) -> dict:
+def _layer_fp32(w: dict) -> dict:
+    return {k: v.float() for k, v in w.items()}
+
+
+def _decode_step_fp32(shape, model, tokens, st, cos, sin):
+    """O.decode_step in fp32 arithmetic on the model's own (bf16-valued) weights, converting one
+    layer at a time so that the host never holds a second copy of the whole model."""
+    x = model["embed"][tokens.long()].float()
+    for li, w in enumerate(model["layers"]):
+        x = O.decode_layer(shape, _layer_fp32(w), x, st.k[li], st.v[li], st.seqlens, cos, sin)
+    x = O.rmsnorm(x, model["norm"].float(), shape.eps)
+    logits = torch.nn.functional.linear(x, model["lm_head"].float())
+    st.seqlens += 1
+    return logits
+
+
+def teacher_forced(eng, shape: O.Shape, n_steps: int, model: dict | None = None, exact_steps: int = 0) -> dict:
     """Steps the engine n_steps times from its current state; the oracle starts from a copy of
     that state and receives the GPU's token at every step.  Returns per-step rel_linf of the
     logits, both argmax streams, and for every step the oracle's top-2 logit gap and the largest
-    absolute logit difference (a token may differ only where the gap is within the error)."""
+    absolute logit difference (a token may differ only where the gap is within the error).
+
+    exact_steps > 0 (bf16 engines): for the first steps the same layers are also evaluated in fp32
+    arithmetic on the same weights ("exact").  ``rel_exact_gpu`` and ``rel_exact_oracle`` are the
+    distances of the GPU and of the bf16 oracle from it: both round activations to bf16 at the
+    same points, so the GPU must not be further from the exact result than the oracle is."""
     model = model_from_engine(eng, shape) if model is None else model
     st = state_from_engine(eng)
     cos, sin = O.rope_tables(eng.S_max, shape.Dh, shape.theta, eng.dtype)
-    rel, gap, err, tok_gpu, tok_ref = [], [], [], [], []
-    for _ in range(n_steps):
+    st32 = None
+    if exact_steps > 0:
+        st32 = O.DecodeState()
+        st32.k, st32.v, st32.seqlens = [k.float() for k in st.k], [v.float() for v in st.v], st.seqlens.clone()
+    rel, gap, err, tok_gpu, tok_ref, rel_eg, rel_eo = [], [], [], [], [], [], []
+    for step in range(n_steps):
         tok_in = eng.tokens.cpu().clone()
         eng.step(1)
         torch.cuda.synchronize()
@@ -91,10 +116,16 @@ def teacher_forced(eng, shape: O.Shape, n_steps: int, model: dict | None = None)
         top2 = torch.topk(lr, 2, dim=-1).values
         gap.append((top2[:, 0] - top2[:, 1]))
         err.append((lg - lr).abs().max(dim=-1).values)
+        if step < exact_steps:
+            le = _decode_step_fp32(shape, model, tok_in, st32, cos.float(), sin.float())
+            den = le.abs().max().clamp_min(1e-30)
+            rel_eg.append(float((lg - le).abs().max() / den))
+            rel_eo.append(float((lr - le).abs().max() / den))
     tok_gpu, tok_ref = torch.stack(tok_gpu), torch.stack(tok_ref)
     gap, err = torch.stack(gap), torch.stack(err)
     # a differing argmax is explained when the oracle's own top-2 gap is below twice the error
     explained = (tok_gpu == tok_ref) | (gap <= 2.0 * err)
     return {"rel_linf": rel, "tokens_gpu": tok_gpu, "tokens_ref": tok_ref, "gap": gap, "err": err,
             "tokens_equal": bool((tok_gpu == tok_ref).all()), "tokens_explained": bool(explained.all()),
-            "n_equal": int((tok_gpu == tok_ref).sum()), "n_tokens": int(tok_gpu.numel())}
+            "n_equal": int((tok_gpu == tok_ref).sum()), "n_tokens": int(tok_gpu.numel()),
+            "rel_exact_gpu": rel_eg, "rel_exact_oracle": rel_eo}

@@ -249,7 +249,7 @@ def test_model_q4_greedy_matches_oracle(dev):
     toks = []
     for t in range(n_new):
         # later steps also read the cache rows the earlier steps wrote, each within TOL of the oracle's
-        assert rel_linf(eng.logits, logits_ref[t]) <= (TOL if t == 0 else 2 * TOL)
+        assert rel_linf(eng.logits, logits_ref[t]) <= (TOL if t == 0 else 3 * TOL)
         toks.append(eng.tokens.cpu().long().clone())
         if t + 1 < n_new:
             eng.tokens.copy_(toks_ref[:, t].to(dev, torch.int32))
