@@ -23,7 +23,8 @@ EXPORTS = (
     "fsvd_decode_layer", "fsvd_model_create", "fsvd_model_destroy", "fsvd_model_step",
     "fsvd_model_buffers", "fsvd_model_status", "fsvd_model_reset_sync", "fsvd_launch_count",
     "fsvd_set_trace_buffer", "fsvd_model_num_stages", "fsvd_lowrank_proj_static", "fsvd_lift",
-    "fsvd_q4_packed_bytes", "fsvd_q4_pack",
+    "fsvd_q4_packed_bytes", "fsvd_q4_pack", "fsvd_set_wait_limit", "fsvd_workspace_clear_status",
+    "fsvd_selftest_wait_timeout", "fsvd_static_status", "fsvd_model_num_barriers",
 )
 
 
@@ -103,6 +104,11 @@ def load() -> C.CDLL:
     lib.fsvd_q4_packed_bytes.argtypes = [ip, ip]
     lib.fsvd_q4_packed_bytes.restype = sz
     lib.fsvd_q4_pack.argtypes = [vp, vp, vp, ip, ip, vp, vp]
+    lib.fsvd_set_wait_limit.argtypes = [C.c_longlong]
+    lib.fsvd_workspace_clear_status.argtypes = [vp, vp]
+    lib.fsvd_selftest_wait_timeout.argtypes = [vp, sz, vp]
+    lib.fsvd_static_status.argtypes = [C.POINTER(ip), ip]
+    lib.fsvd_model_num_barriers.argtypes = [vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("fsvd_version",):
@@ -118,4 +124,6 @@ def check(status: int) -> None:
     msg = load().fsvd_last_error_string().decode("utf-8", "replace")
     if status in (-1, -2, -3, -4):
         raise ValueError(f"flashsvd_b200: {msg}")
+    if status == -7:   # the reference's dense cache raises IndexError when it is full
+        raise IndexError(f"flashsvd_b200: {msg}")
     raise FsvdError(status, msg)

@@ -4,6 +4,8 @@
 #ifndef FSVD_INST_Q4
 #define FSVD_INST_Q4 false
 #endif
+#include <mutex>
+
 #include "fsvd_kernel.cuh"
 #include "fsvd_launch.h"
 
@@ -12,15 +14,20 @@ namespace {
 template <typename T, bool Q4>
 cudaError_t launch_impl(const LaunchArgs& a) {
   auto kern = fsvd::fsvd_decode_kernel<T, Q4>;
+  // largest dynamic shared-memory size the kernel has been opted into, per device
   static size_t attr_smem[16] = {0};
+  static std::mutex attr_mu;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16) dev = 0;
-  if (a.smem > attr_smem[dev]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
-    if (e != cudaSuccess) return e;
-    attr_smem[dev] = a.smem;
+  {
+    std::lock_guard<std::mutex> lock(attr_mu);
+    if (a.smem > attr_smem[dev]) {
+      cudaError_t e =
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
+      if (e != cudaSuccess) return e;
+      attr_smem[dev] = a.smem;
+    }
   }
   static const fsvd::SmallProgram empty_prog = {};
   static const fsvd::SmallMaps empty_maps = {};
@@ -36,7 +43,8 @@ cudaError_t launch_impl(const LaunchArgs& a) {
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, a.prog, a.small ? *a.small : empty_prog, a.maps,
                             a.small_maps ? *a.small_maps : empty_maps, a.small ? 1 : 0, a.nstages,
-                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.slot_bytes, a.trace);
+                            a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.slot_bytes, a.trace,
+                            a.wait_limit, a.tune);
 }
 
 }  // namespace

@@ -91,6 +91,7 @@ class DecodeEngine:
                 self.cos.data_ptr(), self.sin.data_ptr(), int(max_steps), C.byref(handle)))
         self.handle = handle
         self.max_steps = int(max_steps)
+        self._pos_bound = 0   # host-side upper bound of the cache positions in use
         # Prompt pass of a single sequence: a second program over the same weights and caches takes
         # `prefill_chunk` consecutive prompt positions per launch (rows_are_positions of fsvd_dims);
         # it is created on the first prompt that is long enough.
@@ -115,6 +116,8 @@ class DecodeEngine:
 
     @property
     def seqlens(self):
+        # the caller may write through this view: the host-side position bound is no longer known
+        self._pos_bound = None
         return self._view("seqlens", (self.B,), torch.int32)
 
     @property
@@ -130,13 +133,27 @@ class DecodeEngine:
         return self._view("logits", (self.B, self.vocab), torch.float32)
 
     # ---- stepping ---------------------------------------------------------------------------
+    def _reserve_positions(self, n: int) -> None:
+        """Raises IndexError when n more tokens do not fit the cache, as the reference's dense
+        cache does (runtime/cache/attn_dense_kv.py:295-298).  The largest position is tracked on
+        the host; it is read from the device (one synchronisation) only after the caller has
+        touched ``seqlens``."""
+        if self._pos_bound is None:
+            self._pos_bound = int(self._view("seqlens", (self.B,), torch.int32).max().item())
+        if self._pos_bound + n > self.S_max:
+            raise IndexError(f"{n} more token(s) at position {self._pos_bound} exceed the cache "
+                             f"(max_cache_len={self.S_max})")
+        self._pos_bound += n
+
     def step(self, n_steps: int = 1) -> None:
         """Enqueue n greedy decode steps on the current stream (no synchronisation)."""
+        self._reserve_positions(int(n_steps))
         check(self.lib.fsvd_model_step(self.handle, int(n_steps), torch.cuda.current_stream().cuda_stream))
 
     def reset(self) -> None:
         self.seqlens.zero_()
         self.step_counter.zero_()
+        self._pos_bound = 0
 
     def _chunk_model(self):
         """The program that takes `prefill_chunk` prompt positions of the one sequence per launch."""

@@ -5,7 +5,12 @@
  *     0  ok
  *    <0  argument / shape / alignment / launch error (text via fsvd_last_error_string())
  * Device-side waits are bounded; if one runs out, a non-zero word is left in the workspace and
- * is returned by fsvd_workspace_status() / fsvd_model_status().
+ * is returned by fsvd_workspace_status() / fsvd_model_status().  The word is sticky until it is
+ * cleared (fsvd_workspace_clear_status / fsvd_workspace_init / fsvd_model_reset_sync); the launch
+ * that set it still ends by itself and later launches on the same workspace work normally.
+ *
+ * Launches that share one workspace (or one model) must be ordered one after another on the
+ * device (one stream, or events): the workspace holds the vectors the stages hand to each other.
  *
  * Factor naming follows the reference: for a projection d_in -> r -> d_out the input-side
  * factor is `*_v` with nn.Linear weight layout [r, d_in] and the output-side factor is `*_u`
@@ -36,6 +41,7 @@ extern "C" {
 #define FSVD_ERR_WORKSPACE (-4)
 #define FSVD_ERR_CUDA (-5)
 #define FSVD_ERR_DEVICE_WAIT (-6)
+#define FSVD_ERR_CACHE_FULL (-7)
 
 /* Shapes of one model / layer.  Ranks must be multiples of 8, d and I multiples of 8,
  * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}, B <= 8 (bf16) / 4 (fp32). */
@@ -91,10 +97,16 @@ const char* fsvd_last_error_string(void);
 /* SM count and opt-in shared memory per block of the current device. */
 int fsvd_device_props(int* sm_count, int* smem_optin_bytes);
 /* Launch geometry.  warps: 0 or 7 (the kernel runs 7 consumer warps + 1 TMA producer warp per
- * CTA); depth: slots of the shared-memory ring of 8 KB factor boxes (0 = as many as fit, at most
+ * CTA); depth: slots of the shared-memory ring of 7 KB boxes (0 = as many as fit, at most
  * 21; rounded down to a multiple of 7); grid: number of CTAs (0 = one per SM).  Defaults come
- * from FSVD_SLOTS / FSVD_GRID or (0, 0). */
+ * from FSVD_SLOTS / FSVD_GRID or (0, 0).  The grid may be changed between launches on the same
+ * workspace: no device-side word depends on it from one launch to the next. */
 int fsvd_set_launch_config(int warps, int depth, int grid);
+/* Budget of every device-side wait (for tagged words of another CTA, a ring box, the grid
+ * barrier) in SM clocks; default 4e9 (about 2 s) or FSVD_WAIT_CLOCKS.  A wait that runs out sets the status word and
+ * the launch goes on without waiting again.  The reference has no counterpart (its kernels do
+ * not wait for each other). */
+int fsvd_set_wait_limit(long long sm_clocks);
 
 /* Stage timeline for profiling (the analogue of the reference's per-module CUDA-event hooks,
  * utils/evaluator.py:553-689).  While a device buffer of at least nstages * grid * 128 bytes is
@@ -109,8 +121,17 @@ int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes);
  * fsvd_decode_layer; zero it once with fsvd_workspace_init before first use. */
 size_t fsvd_workspace_bytes(const fsvd_dims* dims);
 int fsvd_workspace_init(void* ws, size_t ws_bytes, void* stream);
-/* Blocking: copies the device status word back. 0 = no device-side wait ran out. */
+/* Blocking: copies the device status word back.  0 = nothing happened; 1 / 2 / 3 = a wait for
+ * the grid barrier / a ring box / tagged words ran out (FSVD_ERR_DEVICE_WAIT); 4 = a token arrived
+ * at a cache position >= S_max and its key / value were dropped (FSVD_ERR_CACHE_FULL; the
+ * reference raises IndexError there, runtime/cache/attn_dense_kv.py:295-298). */
 int fsvd_workspace_status(void* ws, int* device_status);
+/* Clears the status word on `stream` (the rest of the workspace is left as it is). */
+int fsvd_workspace_clear_status(void* ws, void* stream);
+/* Self-test of the bounded waits: launches a two-stage program whose second stage waits for words
+ * that nothing writes.  The launch ends by itself after the wait budget (fsvd_set_wait_limit) and
+ * leaves status 3 with stage index 1; the workspace stays usable.  Nothing faults or hangs. */
+int fsvd_selftest_wait_timeout(void* ws, size_t ws_bytes, void* stream);
 
 /* ---- per-op entry points ------------------------------------------------------------------
  * y[B,d_out] = (residual +) u(v(x)).  Replaces the two F.linear GEMVs of the low-rank output
@@ -128,26 +149,30 @@ int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B
               int dtype, void* ws, size_t ws_bytes, void* stream);
 
 /* The same projection for callers that cannot hand over a workspace.  This entry point has no
- * counterpart in the reference.  Its scratch (barrier words + rank-space partial sums) is a
- * fixed 256 KiB + 256 B array inside the library's device image, so the call performs no device
+ * counterpart in the reference.  Its scratch (sync words + rank-space partial sums) is a
+ * fixed 512 KiB + 256 B array inside the library's device image, so the call performs no device
  * memory allocation or release of any kind (no cudaMalloc / cudaFree, no memory pool, no
- * allocating library call); on the host it uses only a few hundred bytes of ordinary heap for the
- * stage list.  Meant for code that runs where device allocation is off limits or unaffordable: a
- * serving loop whose memory is fully budgeted up front, a real-time thread that must not take
- * the allocator's locks, or a plug-in that is handed tensors but no allocator.
+ * allocating library call); on the host it uses ordinary heap for the stage list the first time a
+ * given set of arguments is seen.  Meant for code that runs where device allocation is off limits
+ * or unaffordable: a serving loop whose memory is fully budgeted up front, a real-time thread that
+ * must not take the allocator's locks, or a plug-in that is handed tensors but no allocator.
  *  - Limit: B * R <= 8192 (for example B = 1 with R up to 8192, or B = 8 with R up to 1024);
  *    beyond that the call returns FSVD_ERR_WORKSPACE and launches nothing.
- *  - The first call on each device looks up the array's device address and clears its barrier
+ *  - The first call on each device looks up the array's device address and clears its sync
  *    words on `stream`; make that first call during start-up, outside any stream capture and
  *    with the target device current.  Later calls do no set-up.
  *  - One array per device is shared by every call: calls must be ordered one after another
  *    (same stream, or events between streams).  Two calls that overlap in time race on the
- *    partial sums and the barrier and give undefined results.
- *  - The bounded-wait status word of this variant is not readable from the host; use
- *    fsvd_lowrank_proj with a workspace where fsvd_workspace_status is needed.
- * Results are bitwise identical to fsvd_lowrank_proj with the same launch configuration. */
+ *    partial sums and give undefined results.
+ *  - fsvd_static_status reads (and optionally clears) the bounded-wait status word of the array.
+ * Both entry points build their stages with the same routine (same K segments, same summation
+ * order), so the results are bitwise identical to fsvd_lowrank_proj with the same launch
+ * configuration. */
 int fsvd_lowrank_proj_static(const void* x, const void* v, const void* u, const void* residual,
                              void* y, int B, int d_in, int R, int d_out, int dtype, void* stream);
+/* Blocking: status word of the built-in scratch of the current device (see fsvd_workspace_status
+ * for the codes); clear != 0 also clears it.  Allocates nothing. */
+int fsvd_static_status(int* device_status, int clear);
 
 /* y[B,d] = (residual +) down_u(down_v(silu(gate_u(p_gate)) * up_u(p_up))).
  * With upgate_v != NULL: x is the hidden state [B,d], optionally RMS-normalised by norm_w, and
@@ -207,14 +232,17 @@ int fsvd_model_destroy(fsvd_model* m);
 /* Enqueue n_steps greedy decode steps. */
 int fsvd_model_step(fsvd_model* m, int n_steps, void* stream);
 /* Device buffers: tokens[B] (in: token to feed, out: sampled token), seqlens[B],
- * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32, hidden[B,d] in the model dtype (returned as an untyped float*). */
+ * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32; `hidden` is the library's internal
+ * hidden-state buffer between layers ([B,d] 8-byte words {fp32 value, tag}), exposed for debugging. */
 int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
                        int** step_counter, float** logits, float** hidden);
 /* Number of stages of the model's program (sizes the trace buffer). */
 int fsvd_model_num_stages(fsvd_model* m);
+/* Grid barriers per launch of the model's program (1: in front of the argmax). */
+int fsvd_model_num_barriers(fsvd_model* m);
 /* Blocking: 0 when no device-side wait ran out since the last reset. */
 int fsvd_model_status(fsvd_model* m, int* device_status);
-/* Clears the barrier words and the status after an error. */
+/* Clears the status and the barrier count after an error. */
 int fsvd_model_reset_sync(fsvd_model* m, void* stream);
 /* int4 factors: src/quant/packed_quant_linear.py:18-35 (format), :126-171 (pack_weight), :285-300
  * (dequantize: w = scale * (q - zero), groups of 128 along the input dimension).  The reference

@@ -22,7 +22,10 @@ def _call_static(lib, x, v, u, res, y):
 
 @pytest.mark.parametrize("dtype,B,d_in,R,d_out", [(torch.bfloat16, 1, 4096, 1024, 4096),
                                                  (torch.float32, 2, 264, 88, 520),
-                                                 (torch.bfloat16, 8, 11008, 1024, 4096)])
+                                                 (torch.bfloat16, 8, 11008, 1024, 4096),
+                                                 # few rank rows and a long input: the K-segment plan is
+                                                 # what decides the summation order here
+                                                 (torch.bfloat16, 1, 8192, 88, 512)])
 def test_static_scratch_matches_workspace_variant(dtype, B, d_in, R, d_out):
     from flashsvd_b200 import _lib, ops
 
@@ -48,6 +51,9 @@ def test_static_scratch_matches_workspace_variant(dtype, B, d_in, R, d_out):
         err = float((got.float() - ref).abs().max() / ref.abs().max())
         assert err <= (2e-2 if dtype == torch.bfloat16 else 2e-5)
     assert ws.status() == 0
+    st = C.c_int(-1)
+    _lib.check(lib.fsvd_static_status(C.byref(st), 0))
+    assert st.value == 0
 
 
 def test_static_scratch_rejects_oversize():
