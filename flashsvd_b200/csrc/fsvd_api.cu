@@ -326,6 +326,9 @@ struct Builder {
     s.nch = q4 ? nchunks : 0;
     s.rot = (int)(cum_units % grid);
     cum_units += (long long)groups * best_segs;
+    if (((long long)groups * best_segs + grid - 1) / grid * (WB ? 2 : 1) > kMaxUnitOps && !err)
+      err = fail(FSVD_ERR_UNSUPPORTED, "%d output rows are more than a launch of %d CTAs takes (%d rows per CTA and operand)",
+                 P, grid, kMaxUnitOps * kUnitRows);
     push(s);
     // rows behind the pointers: a rotary stage reads physical rows [0, 2P) through WA and
     // [half, 2P) through WB = WA + half rows
@@ -388,8 +391,8 @@ struct Builder {
     s.attn_rb = rb;
     s.rot = (int)(cum_items % grid);
     cum_items += groups * cph;
-    // states of the warps + per-warp score tiles [rows][33] and probabilities [rows]
-    const int need = kConsumerWarps * GI * (s.Dh + 2) + kConsumerWarps * kAttnMaxRows * 34;
+    // states of the warps + per-warp score tiles [33][33] and probabilities [32]
+    const int need = kConsumerWarps * GI * (s.Dh + 2) + kConsumerWarps * (33 * 33 + 32);
     if (need > attn_rec_floats) attn_rec_floats = need;
     const int i = push(s);
     const long long rows = (long long)(shared_cache ? 1 : s.B) * s.S_max;

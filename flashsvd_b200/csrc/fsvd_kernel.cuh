@@ -47,10 +47,10 @@
 
 #include "fsvd_stage.h"
 
-// Stage-level functions that run once per stage (input staging, attention, the producer loop):
-// compiled as real calls, which keeps their register allocation apart from the GEMV inner loop.
+// Stage-level functions that run once per stage (input staging, attention, the producer loop).
+// Inlined: as real calls they measured slower (317 against 382 tokens/s at the same source).
 #ifndef FSVD_COLD
-#define FSVD_COLD __noinline__
+#define FSVD_COLD __forceinline__
 #endif
 
 namespace fsvd {
@@ -111,6 +111,12 @@ __device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int c
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(tmap), "r"(col), "r"(row), "r"(bar)
       : "memory");
+}
+// Asks L2 for the 128-byte lines of [p, p + bytes), one line per lane and round.
+__device__ __forceinline__ void prefetch_l2(const void* p, int bytes, int lane) {
+  const char* c = reinterpret_cast<const char*>(p);
+  for (int off = lane * 128; off < bytes; off += 32 * 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -291,6 +297,7 @@ struct CtaConst {
   char* xvec;                 // staged input vector
   float* red;                 // reduction scratch
   float* part;                // warps' partial sums / attention scratch
+  int* xtab;                  // first input column of every (unit, operand) of the running GEMV stage
   int xstride;
   int backoff_ns;             // pause after a failed poll of tagged words
   int gate;                   // 1: a thread polls one sample of its words before it asks for all of them
@@ -307,7 +314,8 @@ struct Spin {
   __device__ __forceinline__ Spin() : c0(0), n(0) {}
 };
 // Called after a failed poll.  False: stop waiting (the budget ran out, now or earlier).
-__device__ __forceinline__ bool spin_again(const Waiter& w, Spin& sp, int code) {
+// (A real call: it sits behind every poll of the kernel and only runs when a poll failed.)
+static __device__ __noinline__ bool spin_again(const Waiter& w, Spin& sp, int code) {
   const CtaConst& cc = *w.cc;
   if (sp.n == 0) {
     if (*cc.giveup) return false;
@@ -415,86 +423,59 @@ template <typename T>
 __device__ __forceinline__ void gemv_epilogue(const Stage& st, int p, int b, int seg, float a, float bsum,
                                               const EpiAux& ax, uint32_t tag, SyncState* sync) {
   using X = TT<T>;
-  const int P = st.P;
-  switch (st.epi) {
-    case EPI_PARTIAL:
-      st_tword(st.out, ((size_t)seg * st.B + b) * P + p, a, tag);
-      break;
-    case EPI_STORE:
-      out_store<T>(st, st.out, (size_t)b * P + p, X::rnd(a), tag);
-      break;
-    case EPI_RESID: {
-      const float res = (st.flags & SF_RESID_TAG) ? __uint_as_float(ax.r0)
-                        : (st.flags & SF_RESID_T) ? raw_to_float<T>(ax.r0) : __uint_as_float(ax.r0);
-      out_store<T>(st, st.out, (size_t)b * P + p, X::rnd(res + X::rnd(a)), tag);
-    } break;
-    case EPI_SWIGLU: {
-      const float g = X::rnd(a), u = X::rnd(bsum);
-      const float sg = X::rnd(g / (1.0f + expf(-g)));
-      out_store<T>(st, st.out, (size_t)b * P + p, X::rnd(sg * u), tag);
-    } break;
-    case EPI_ROPE_Q:
-    case EPI_ROPE_K:
-    case EPI_V:
-    case EPI_QKV: {
-      // head index over [q heads | k heads | v heads] for EPI_QKV
-      const int half = st.epi == EPI_V ? (st.Dh >> 1) : st.rope_half, pos = ax.pos;
-      int hh, j;
-      if (st.epi == EPI_V) {   // logical row = element of [Hk, Dh]
-        hh = qdiv(p, st.Dh);
-        j = p - hh * st.Dh;
-        hh += st.H + st.Hk;
-      } else {
-        hh = qdiv(p, half);
-        j = p - hh * half;
-        if (st.epi == EPI_ROPE_K) hh += st.H;
-      }
-      const float x1 = X::rnd(a), x2 = X::rnd(bsum);
-      if (pos >= st.S_max && hh >= st.H) atomicCAS(&sync->status, (int)DS_OK, (int)DS_CACHE_FULL);
-      if (hh < st.H + st.Hk) {
-        const float c = raw_to_float<T>(ax.r0), sn = raw_to_float<T>(ax.r1);
-        const float o1 = X::rnd(X::rnd(x1 * c) - X::rnd(x2 * sn));
-        const float o2 = X::rnd(X::rnd(x2 * c) + X::rnd(x1 * sn));
-        if (hh < st.H) {
-          const size_t base = ((size_t)b * st.H + hh) * st.Dh + j;
-          out_store<T>(st, st.out, base, o1, tag);
-          out_store<T>(st, st.out, base + half, o2, tag);
-        } else {
-          const int hk = hh - st.H;
-          if (pos < st.S_max) {
-            const size_t base = (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + hk) * st.Dh + j;
-            X::st(st.cache, base, o1);
-            X::st(st.cache, base + half, o2);
-          }
-          if (st.knew) {
-            const size_t nb = ((size_t)b * st.Hk + hk) * st.Dh + j;
-            st_tword(st.knew, nb, o1, tag);
-            st_tword(st.knew, nb + half, o2, tag);
-          }
-        }
-      } else {
-        const int hk = hh - st.H - st.Hk;
-        void* vc = st.epi == EPI_V ? st.cache : const_cast<void*>(st.vcache);
-        if (st.epi == EPI_V) {
-          if (pos < st.S_max)
-            X::st(vc, (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + hk) * st.Dh + j, x1);
-          if (st.vnew) st_tword(st.vnew, ((size_t)b * st.Hk + hk) * st.Dh + j, x1, tag);
-        } else {
-          if (pos < st.S_max) {
-            const size_t base = (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + hk) * st.Dh + j;
-            X::st(vc, base, x1);
-            X::st(vc, base + half, x2);
-          }
-          if (st.vnew) {
-            const size_t nb = ((size_t)b * st.Hk + hk) * st.Dh + j;
-            st_tword(st.vnew, nb, x1, tag);
-            st_tword(st.vnew, nb + half, x2, tag);
-          }
-        }
-      }
-    } break;
-    default:
-      break;
+  const int P = st.P, epi = st.epi;
+  if (epi == EPI_PARTIAL) {
+    st_tword(st.out, ((size_t)seg * st.B + b) * P + p, a, tag);
+    return;
+  }
+  float v = X::rnd(a);
+  if (epi <= EPI_SWIGLU) {   // one value for out[b, p]
+    if (epi == EPI_RESID) {
+      const float res = (st.flags & SF_RESID_T) ? raw_to_float<T>(ax.r0) : __uint_as_float(ax.r0);
+      v = X::rnd(res + v);
+    } else if (epi == EPI_SWIGLU) {
+      const float sg = X::rnd(v / (1.0f + expf(-v)));
+      v = X::rnd(sg * X::rnd(bsum));
+    }
+    out_store<T>(st, st.out, (size_t)b * P + p, v, tag);
+    return;
+  }
+  // Head stages.  hh = head over [q heads | k heads | v heads]; a rotary row carries two values, dims
+  // (j, j + half) of its head; a row of the separate value lift carries one, dim j.
+  const bool one = epi == EPI_V;
+  const int half = one ? st.Dh : st.rope_half, pos = ax.pos;
+  int hh = qdiv(p, half);
+  const int j = p - hh * half;
+  if (epi == EPI_ROPE_K) hh += st.H;
+  else if (one) hh += st.H + st.Hk;
+  float v2 = X::rnd(bsum);
+  const bool isk = hh < st.H + st.Hk;   // q and k heads rotate
+  if (isk) {
+    const float c = raw_to_float<T>(ax.r0), sn = raw_to_float<T>(ax.r1);
+    const float o1 = X::rnd(X::rnd(v * c) - X::rnd(v2 * sn));
+    v2 = X::rnd(X::rnd(v2 * c) + X::rnd(v * sn));
+    v = o1;
+  }
+  if (hh < st.H) {
+    const size_t base = ((size_t)b * st.H + hh) * st.Dh + j;
+    out_store<T>(st, st.out, base, v, tag);
+    out_store<T>(st, st.out, base + half, v2, tag);
+    return;
+  }
+  const int hk = hh - st.H - (isk ? 0 : st.Hk);
+  void* const cache = (isk || one) ? st.cache : const_cast<void*>(st.vcache);
+  void* const nw = isk ? st.knew : st.vnew;
+  if (pos < st.S_max) {
+    const size_t base = (((size_t)cache_row(st, b) * st.S_max + pos) * st.Hk + hk) * st.Dh + j;
+    X::st(cache, base, v);
+    if (!one) X::st(cache, base + half, v2);
+  } else {
+    atomicCAS(&sync->status, (int)DS_OK, (int)DS_CACHE_FULL);
+  }
+  if (nw) {
+    const size_t nb = ((size_t)b * st.Hk + hk) * st.Dh + j;
+    st_tword(nw, nb, v, tag);
+    if (!one) st_tword(nw, nb + half, v2, tag);
   }
 }
 
@@ -533,40 +514,55 @@ __device__ __forceinline__ uint4 ld_raw16(const void* base, size_t i) {
 
 // Sum of the nseg tagged partial vectors [nseg][B][len], columns [col0, col0 + lenS), rounded to T.
 // Per batch row a thread owns up to UP positions of two words; it walks the partial vectors in
-// segment order (a fixed summation order) and per vector issues the loads of all its positions
-// before looking at a tag, repeating them until every word carries `tag`.  One small loop body for
-// every nseg: the stage-in code runs once per stage and is bound by instruction fetch.
-template <typename T>
+// segment order (a fixed summation order), SG vectors per round, and per round issues the loads of
+// all its positions before looking at a tag, repeating them until every word carries `tag`.
+// (UP x SG = 16 loads of 16 bytes in flight; every further round is another round trip to L2 on
+// the critical path.)
+template <typename T, int UP, int SG>
 __device__ __forceinline__ void stage_sum_tagged(const Stage& st, char* xvec, int xstride, int col0, int lenS,
                                                  int tid, uint32_t tag, const Waiter& w) {
-  constexpr int NT = kConsThreads, UP = 8;
+  constexpr int NT = kConsThreads;
   const int B = st.B, len = st.vl_len, nseg = st.vl_nseg;
   const int upr = lenS >> 1;
   const size_t segstride = (size_t)B * len;
+#pragma unroll 1
   for (int b = 0; b < B; ++b) {
+#pragma unroll 1
     for (int u0 = tid; u0 < upr; u0 += NT * UP) {
       const tword* base = reinterpret_cast<const tword*>(st.vl_src) + (size_t)b * len + col0 + u0 * 2;
       float a0[UP], a1[UP];
 #pragma unroll
       for (int k = 0; k < UP; ++k) a0[k] = a1[k] = 0.f;
-      for (int q = 0; q < nseg; ++q, base += segstride) {
-        ulonglong2 v[UP];
+#pragma unroll 1
+      for (int q = 0; q < nseg; q += SG, base += SG * segstride) {
+        ulonglong2 v[SG][UP];
         Spin sp;
         for (;;) {
           bool ok = true;
 #pragma unroll
-          for (int k = 0; k < UP; ++k)
-            if (u0 + k * NT < upr) v[k] = ld_tword2(base, (size_t)(k * NT * 2));
+          for (int g = 0; g < SG; ++g) {
+            // (a round past the last vector repeats the last one and is not added)
+            const tword* bg = base + (q + g < nseg ? g : 0) * segstride;
 #pragma unroll
-          for (int k = 0; k < UP; ++k)
-            if (u0 + k * NT < upr) ok = ok & tw_ok(v[k], tag);
+            for (int k = 0; k < UP; ++k)
+              if (u0 + k * NT < upr) v[g][k] = ld_tword2(bg, (size_t)(k * NT * 2));
+          }
+#pragma unroll
+          for (int g = 0; g < SG; ++g)
+#pragma unroll
+            for (int k = 0; k < UP; ++k)
+              if (u0 + k * NT < upr) ok = ok & tw_ok(v[g][k], tag);
           if (ok || !spin_again(w, sp, DS_TAG_TIMEOUT)) break;
         }
 #pragma unroll
-        for (int k = 0; k < UP; ++k) {
-          a0[k] += tw_val(v[k].x);
-          a1[k] += tw_val(v[k].y);
-        }
+        for (int g = 0; g < SG; ++g)
+          if (q + g < nseg) {
+#pragma unroll
+            for (int k = 0; k < UP; ++k) {
+              a0[k] += tw_val(v[g][k].x);
+              a1[k] += tw_val(v[g][k].y);
+            }
+          }
       }
 #pragma unroll
       for (int k = 0; k < UP; ++k)
@@ -577,7 +573,8 @@ __device__ __forceinline__ void stage_sum_tagged(const Stage& st, char* xvec, in
 
 // Merge of the nsplit part records of one head at dims (dim, dim + 1) of batch row b (VL_ATTN and
 // ST_ATTN_OUT): polls the records until they carry `tag`, then combines them in part order.
-__device__ __forceinline__ float2 attn_merge2(const Stage& st, int b, int h, int dim, uint32_t tag, const Waiter& w) {
+// A real call with rolled loops: it runs a handful of times per stage.
+static __device__ __noinline__ float2 attn_merge2(const Stage& st, int b, int h, int dim, uint32_t tag, const Waiter& w) {
   const int cph = st.nsplit;   // <= 4
   const size_t rec0 = ((size_t)b * st.H + h) * cph;
   ulonglong2 a[4], ml[4];
@@ -585,30 +582,27 @@ __device__ __forceinline__ float2 attn_merge2(const Stage& st, int b, int h, int
   for (;;) {
     bool ok = true;
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
-      if (c < cph) {
-        a[c] = ld_tword2(st.part_acc, (rec0 + c) * st.Dh + dim);
-        ml[c] = ld_tword2(st.part_ml, (rec0 + c) * 2);
-      }
+    for (int c = 0; c < 4; ++c) {
+      const size_t r = rec0 + (c < cph ? c : 0);   // (unused slots repeat part 0: no branches around the loads)
+      a[c] = ld_tword2(st.part_acc, r * st.Dh + dim);
+      ml[c] = ld_tword2(st.part_ml, r * 2);
+    }
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
-      if (c < cph) ok = ok && tw_ok(a[c], tag) && tw_ok(ml[c], tag);
+    for (int c = 0; c < 4; ++c) ok = ok & tw_ok(a[c], tag) & tw_ok(ml[c], tag);
     if (ok || !spin_again(w, sp, DS_TAG_TIMEOUT)) break;
   }
   float M = -INFINITY;
 #pragma unroll
-  for (int c = 0; c < 4; ++c)
-    if (c < cph) M = fmaxf(M, tw_val(ml[c].x));
+  for (int c = 0; c < 4; ++c) M = fmaxf(M, tw_val(ml[c].x));
   float L = 0.f, o0 = 0.f, o1 = 0.f;
 #pragma unroll
-  for (int c = 0; c < 4; ++c)
-    if (c < cph) {
-      const float lc = tw_val(ml[c].y);
-      const float wgt = lc > 0.f ? expf(tw_val(ml[c].x) - M) : 0.f;
-      L += lc * wgt;
-      o0 = fmaf(tw_val(a[c].x), wgt, o0);
-      o1 = fmaf(tw_val(a[c].y), wgt, o1);
-    }
+  for (int c = 0; c < 4; ++c) {
+    const float lc = c < cph ? tw_val(ml[c].y) : 0.f;
+    const float wgt = lc > 0.f ? expf(tw_val(ml[c].x) - M) : 0.f;
+    L += lc * wgt;
+    o0 = fmaf(tw_val(a[c].x), wgt, o0);
+    o1 = fmaf(tw_val(a[c].y), wgt, o1);
+  }
   const float invL = L > 0.f ? 1.f / L : 0.f;
   return make_float2(o0 * invL, o1 * invL);
 }
@@ -634,95 +628,17 @@ __device__ FSVD_COLD void stage_vector(const Stage& st, char* xvec, int xstride,
     if (lenS < 0) lenS = 0;
   }
   if (st.vl_mode == VL_ATTN) {
-    // Merged attention output of columns [col0, col0 + lenS).  The (max, sum) words of the part
-    // records of the heads in that range go to shared memory (one record per thread) while every
-    // thread also asks for the accumulator words of its first positions: one round trip to L2 for
-    // both.  Then every position is the weighted sum of its head's parts, in part order.
-    constexpr int NT = kConsThreads, U = 3;
-    const int cph = st.nsplit, Dh = st.Dh, H = st.H;   // cph <= 4
-    const int hf = qdiv(col0, Dh), nh = qdiv(col0 + lenS - 1, Dh) - hf + 1;
-    const int nrec = B * nh * cph;
+    // merged attention output of columns [col0, col0 + lenS): two dims per thread and pass
     const int upr = lenS >> 1, units = B * upr;
-    float2* const mlsh = reinterpret_cast<float2*>(scratch);
-    auto rec_index = [&](int r) -> size_t {   // r = (b * nh + head - hf) * cph + part
-      const int bh = qdiv(r, cph), b = qdiv(bh, nh);
-      return ((size_t)b * H + hf + (bh - b * nh)) * cph + (r - bh * cph);
-    };
-    auto unit_rec0 = [&](int u, int& b, int& e) -> size_t {   // first part record of the unit's head
-      b = qdiv(u, upr);
-      e = col0 + (u - b * upr) * 2;
-      return ((size_t)b * H + qdiv(e, Dh)) * cph;
-    };
-    for (int u0 = tid; u0 < units || u0 == tid; u0 += NT * U) {
-      const bool first = u0 == tid;
-      ulonglong2 a[U][4], ml;
-      Spin sp;
-      for (;;) {
-        bool ok = true;
-        if (first && tid < nrec) ml = ld_tword2(st.part_ml, rec_index(tid) * 2);
-#pragma unroll
-        for (int k = 0; k < U; ++k) {
-          const int u = u0 + k * NT;
-          if (u < units) {
-            int b, e;
-            const size_t r0 = unit_rec0(u, b, e);
-            const int dim = e - qdiv(e, Dh) * Dh;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              if (c < cph) a[k][c] = ld_tword2(st.part_acc, (r0 + c) * Dh + dim);
-          }
-        }
-        if (first && tid < nrec) ok = tw_ok(ml, tag);
-#pragma unroll
-        for (int k = 0; k < U; ++k)
-          if (u0 + k * NT < units) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              if (c < cph) ok = ok & tw_ok(a[k][c], tag);
-          }
-        if (ok || !spin_again(w, sp, DS_TAG_TIMEOUT)) break;
-      }
-      if (first) {
-        if (tid < nrec) mlsh[tid] = make_float2(tw_val(ml.x), tw_val(ml.y));
-        for (int r = tid + NT; r < nrec; r += NT) {   // more records than threads: further round trips
-          Spin sp2;
-          ulonglong2 m2;
-          for (;;) {
-            m2 = ld_tword2(st.part_ml, rec_index(r) * 2);
-            if (tw_ok(m2, tag) || !spin_again(w, sp2, DS_TAG_TIMEOUT)) break;
-          }
-          mlsh[r] = make_float2(tw_val(m2.x), tw_val(m2.y));
-        }
-        cons_sync();
-      }
-#pragma unroll
-      for (int k = 0; k < U; ++k) {
-        const int u = u0 + k * NT;
-        if (u < units) {
-          int b, e;
-          unit_rec0(u, b, e);
-          const float2* mlr = mlsh + ((size_t)b * nh + qdiv(e, Dh) - hf) * cph;
-          float M = -INFINITY;
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (c < cph) M = fmaxf(M, mlr[c].x);
-          float L = 0.f, o0 = 0.f, o1 = 0.f;
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (c < cph) {
-              const float2 mc = mlr[c];
-              const float wgt = mc.y > 0.f ? expf(mc.x - M) : 0.f;
-              L += mc.y * wgt;
-              o0 = fmaf(tw_val(a[k][c].x), wgt, o0);
-              o1 = fmaf(tw_val(a[k][c].y), wgt, o1);
-            }
-          const float invL = L > 0.f ? 1.f / L : 0.f;
-          st2<T>(xvec, (size_t)b * xstride + (e - col0), o0 * invL, o1 * invL);
-        }
-      }
+#pragma unroll 1
+    for (int u = tid; u < units; u += nthreads) {
+      const int b = qdiv(u, upr), e = col0 + (u - b * upr) * 2;
+      const int h = qdiv(e, st.Dh);
+      const float2 o = attn_merge2(st, b, h, e - h * st.Dh, tag, w);
+      st2<T>(xvec, (size_t)b * xstride + (e - col0), o.x, o.y);
     }
   } else if (st.vl_mode == VL_SUM && tagged) {
-    stage_sum_tagged<T>(st, xvec, xstride, col0, lenS, tid, tag, w);
+    stage_sum_tagged<T, 8, 1>(st, xvec, xstride, col0, lenS, tid, tag, w);
   } else if (st.vl_mode == VL_SUM) {
     // plain T -> T copy of an input of the call
     const int upr = lenS / VEC, units = B * upr;
@@ -733,56 +649,67 @@ __device__ FSVD_COLD void stage_vector(const Stage& st, char* xvec, int xstride,
     }
   } else if (st.vl_mode == VL_RMSNORM && tagged) {
     // tagged source: a thread keeps up to U positions of two words; a longer row is read twice
-    constexpr int U = 10;
-    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+    constexpr int U = 10, NT = kConsThreads;
+    const int warp = tid >> 5, lane = tid & 31;
     const int upr = len >> 1;
-    const bool fits = upr <= nthreads * U;
+    const bool fits = upr <= NT * U;
+    // the weights of this thread's positions, asked for before the wait (they do not depend on it)
+    float2 wg[U];
+    if (fits) {
+#pragma unroll
+      for (int q = 0; q < U; ++q)
+        if (tid + q * NT < upr) wg[q] = X::ldg2(st.vl_w, (size_t)(tid + q * NT) * 2);
+    }
+#pragma unroll 1
     for (int b = 0; b < B; ++b) {
       ulonglong2 v[U];
       float ss = 0.f;
-      for (int u0 = tid; u0 < upr; u0 += nthreads * U) {
+      const tword* row = reinterpret_cast<const tword*>(st.vl_src) + (size_t)b * len + tid * 2;
+#pragma unroll 1
+      for (int u0 = tid; u0 < upr; u0 += NT * U, row += NT * U * 2) {
         Spin sp;
         for (;;) {
           bool ok = true;
 #pragma unroll
-          for (int q = 0; q < U; ++q) {
-            const int u = u0 + q * nthreads;
-            if (u < upr) v[q] = ld_tword2(st.vl_src, (size_t)b * len + (size_t)u * 2);
-          }
+          for (int q = 0; q < U; ++q)
+            if (u0 + q * NT < upr) v[q] = ld_tword2(row, (size_t)(q * NT * 2));
 #pragma unroll
           for (int q = 0; q < U; ++q)
-            if (u0 + q * nthreads < upr) ok = ok && tw_ok(v[q], tag);
+            if (u0 + q * NT < upr) ok = ok & tw_ok(v[q], tag);
           if (ok || !spin_again(w, sp, DS_TAG_TIMEOUT)) break;
         }
 #pragma unroll
         for (int q = 0; q < U; ++q)
-          if (u0 + q * nthreads < upr) {
+          if (u0 + q * NT < upr) {
             const float f0 = tw_val(v[q].x), f1 = tw_val(v[q].y);
             ss = fmaf(f0, f0, fmaf(f1, f1, ss));
           }
       }
       trace_mark(trow, 4);
       ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
+      float* const rb = red + (b & 1) * 8;   // two sets of warp sums: one CTA barrier per row is enough
+      if (lane == 0) rb[warp] = ss;
       cons_sync();
       float tot = 0.f;
-      for (int i = 0; i < nwarps; ++i) tot += red[i];
+#pragma unroll
+      for (int i = 0; i < kNWC; ++i) tot += rb[i];
       const float inv = rsqrtf(tot / (float)len + st.eps);
-      cons_sync();
       trace_mark(trow, 5);
-      auto finish = [&](int u, float f0, float f1, const float2 g) {
-        st2<T>(xvec, (size_t)b * xstride + (size_t)u * 2, g.x * X::rnd(f0 * inv), g.y * X::rnd(f1 * inv));
-      };
       if (fits) {
 #pragma unroll
         for (int q = 0; q < U; ++q) {
-          const int u = tid + q * nthreads;
-          if (u < upr) finish(u, tw_val(v[q].x), tw_val(v[q].y), X::ldg2(st.vl_w, (size_t)u * 2));
+          const int u = tid + q * NT;
+          if (u < upr)
+            st2<T>(xvec, (size_t)b * xstride + (size_t)u * 2, wg[q].x * X::rnd(tw_val(v[q].x) * inv),
+                   wg[q].y * X::rnd(tw_val(v[q].y) * inv));
         }
       } else {
-        for (int u = tid; u < upr; u += nthreads) {
+#pragma unroll 1
+        for (int u = tid; u < upr; u += NT) {
           const ulonglong2 x2 = ld_tword2(st.vl_src, (size_t)b * len + (size_t)u * 2);
-          finish(u, tw_val(x2.x), tw_val(x2.y), X::ldg2(st.vl_w, (size_t)u * 2));
+          const float2 g = X::ldg2(st.vl_w, (size_t)u * 2);
+          st2<T>(xvec, (size_t)b * xstride + (size_t)u * 2, g.x * X::rnd(tw_val(x2.x) * inv),
+                 g.y * X::rnd(tw_val(x2.y) * inv));
         }
       }
     }
@@ -945,98 +872,57 @@ template <typename T, bool Q4>
 __device__ FSVD_COLD void producer_loop(const Stage* prog, int nstages, const unsigned char* maps,
                                         const CtaConst& cc, int lane) {
   const Ring rg = cc.ring;
-  const PosCache pc = cc.pc;
   Waiter w = {&cc, 0};
-  int cap = cc.cap;
   constexpr int BOXCOLS = kBoxRowBytes / (int)sizeof(T);
   const int grid = gridDim.x, cta = blockIdx.x;
   const int N = rg.ns < kNWC ? rg.ns : kNWC;
   const unsigned mask = (1u << N) - 1u;
   if (lane >= N) return;
-  int s = -1;
+  // Cursor: stage s, box l of the current run of `lim` boxes (a GEMV stage's boxes of this CTA, or
+  // the boxes of one attention item).  One loop moves it; the code of a move exists once.
+  int s = -1, l = 0, lim = 0;
   bool done = false, attn = false;
-  // cursor inside a GEMV stage: unit ordinal, operand, chunk
-  int j = 0, op = 0, c = 0;
-  int nu = 0, nops = 1, cps = 1, first = 0, segs = 1, half = 0;
+  int nops = 1, cps = 1, first = 0, segs = 1, half = 0;
   int nch = 0;                               // > 0: the stage streams int4 tiles, nch per tile row
-  // cursor inside an attention stage: item, box of the item
   AttnP ap = {};
   AttnItem ai = {};
-  int hs = 0, abox = 0;
+  int hs = 0;
   const unsigned char* mapA = maps;
-  // positions the attention cursor on the first item from hs on that has boxes
-  auto load_item = [&]() -> bool {
-    for (; hs < ap.nslice; hs += grid) {
-      attn_item(ap, hs, pc, ai);
-      if (ai.nb > 0) {
-        abox = 0;
-        return true;
+  int slot = lane, round = 0, issue = 0;
+  // cap > 0: at most `cap` boxes of a lane are in flight (issued and not yet landed)
+  const int spl = rg.ns / N;   // slots per lane
+  const int cap = cc.cap >= spl ? 0 : cc.cap;
+  int k = lane;   // boxes to move before the next issue
+  for (;;) {
+    l += k;
+#pragma unroll 1
+    while (!done && l >= lim) {
+      l -= lim;
+      lim = 0;
+      if (attn && (hs += grid) < ap.nslice) {
+        attn_item(ap, hs, cc.pc, ai);
+        lim = ai.nb;
+        continue;
       }
-    }
-    return false;
-  };
-  // moves the cursor to the first box of the next stage with boxes for this CTA
-  auto next_stage = [&]() {
-    for (++s; s < nstages; ++s) {
+      attn = false;
+      if (++s >= nstages) {
+        done = true;
+        break;
+      }
       const Stage& st = prog[s];
+      mapA = maps + (size_t)(2 * s) * 128;
       if (st.type == ST_GEMV) {
         const BoxPlan bp = plan_boxes(st.P, st.segs, st.cps, st.rot, st.WB != nullptr, cta, grid);
-        if (bp.nbox == 0) continue;
-        nu = bp.nu; nops = bp.nops; cps = bp.cps; first = bp.first; segs = st.segs; half = st.rope_half;
+        nops = bp.nops; cps = bp.cps; first = bp.first; segs = st.segs; half = st.rope_half;
         nch = (Q4 && (st.flags & SF_Q4)) ? st.nch : 0;
-        mapA = maps + (size_t)(2 * s) * 128;
-        j = op = c = 0;
-        attn = false;
-        return;
-      }
-      if (st.type == ST_ATTN) {
+        lim = bp.nbox;
+      } else if (st.type == ST_ATTN) {
         ap = attn_params(st, rg.ns);
-        hs = first_item(cta, qmod(st.rot, grid), grid);
-        mapA = maps + (size_t)(2 * s) * 128;
+        hs = first_item(cta, qmod(st.rot, grid), grid) - grid;   // the loop steps to the first item
         attn = true;
-        if (load_item()) return;
       }
     }
-    done = true;
-  };
-  // advances the cursor by k boxes
-  auto advance = [&](int k) {
-    while (k > 0 && !done) {
-      if (attn) {
-        const int room = ai.nb - abox;
-        if (k < room) {
-          abox += k;
-          k = 0;
-        } else {
-          k -= room;
-          hs += grid;
-          if (!load_item()) next_stage();
-        }
-      } else {
-        const int room = cps - c;
-        if (k < room) {
-          c += k;
-          k = 0;
-        } else {
-          k -= room;
-          c = 0;
-          if (++op == nops) {
-            op = 0;
-            if (++j == nu) next_stage();
-          }
-        }
-      }
-    }
-  };
-  next_stage();
-  advance(lane);
-  int slot = lane, round = 0;
-  // cap > 0: at most `cap` boxes of a lane are in flight (issued and not yet landed): more than
-  // the bandwidth-delay product only lengthens every queue of the memory system
-  const int spl = rg.ns / N;   // slots per lane
-  if (cap >= spl) cap = 0;
-  int issue = 0;
-  while (__any_sync(mask, !done)) {
+    if (!__any_sync(mask, !done)) break;
     bool ok = !done;
     w.stage = s;
     if (ok && cap > 0 && issue >= cap) {
@@ -1050,39 +936,42 @@ __device__ FSVD_COLD void producer_loop(const Stage* prog, int nstages, const un
       const uint32_t fb = rg.full + slot * 8;
       const uint32_t dst = rg.data + (uint32_t)slot * (Q4 ? rg.stride : (uint32_t)kBoxBytes);
       if (attn) {
-        // box abox of the item: chunk c, key box i (or value box i) = rbmax rows of one kv head
-        // from row i * rb of the chunk on (rows past the cache arrive as zeros)
-        int c = qdiv(abox, 2 * ai.kb), kbc = ai.kb;
+        // box l of the item: chunk c, key box i (or value box i) = rbmax rows of one kv head from
+        // row i * rb of the chunk on (rows past the cache arrive as zeros)
+        int c = qdiv(l, 2 * ai.kb), kbc = ai.kb;
         if (c >= ai.nch - 1) {
           c = ai.nch - 1;
           kbc = ai.kbl;
         }
-        const int r = abox - c * 2 * ai.kb;
+        const int r = l - c * 2 * ai.kb;
         const int isv = r >= kbc ? 1 : 0;
         const int row = ai.row0 + c * ai.rpc + (r - isv * kbc) * ai.rb;
         mbar_expect_tx(fb, (uint32_t)(ap.rbmax * ap.Dh) * (uint32_t)sizeof(T));
         tma_box_2d(dst, mapA + isv * 128, ai.hk * ap.Dh, row, fb);
       } else {
+        // box l of the stage: (unit ordinal, operand, chunk), unit = (row group, K segment)
+        const int io = qdiv(l, cps), c = l - io * cps;
+        const int j = nops == 2 ? (io >> 1) : io, op = nops == 2 ? (io & 1) : 0;
         const int uidx = first + j * grid;
         const int grp = qdiv(uidx, segs), seg = uidx - grp * segs;
+        int x = (seg * cps + c) * BOXCOLS, y = phys_row(half, grp * kUnitRows);
+        uint32_t bytes = kBoxBytes;
         if (Q4 && nch > 0) {
           // tile (row group, chunk) of the int4 stream; a chunk past the last tile of the row (the
           // tail of the last K segment) is fetched from outside the tensor and arrives as zeros
           // (zero scales)
           const int chunk = seg * cps + c;
-          const int trow = phys_row(half, grp * kUnitRows) / kUnitRows;
-          const int y = chunk < nch ? (trow * nch + chunk) * kQ4TileRows : 0x40000000;
-          mbar_expect_tx(fb, kQ4BoxBytes);
-          tma_box_2d(dst, mapA + (op ? 128 : 0), 0, y, fb);
-        } else {
-          mbar_expect_tx(fb, kBoxBytes);
-          tma_box_2d(dst, mapA + (op ? 128 : 0), (seg * cps + c) * BOXCOLS, phys_row(half, grp * kUnitRows), fb);
+          y = chunk < nch ? ((y / kUnitRows) * nch + chunk) * kQ4TileRows : 0x40000000;
+          x = 0;
+          bytes = kQ4BoxBytes;
         }
+        mbar_expect_tx(fb, bytes);
+        tma_box_2d(dst, mapA + (op ? 128 : 0), x, y, fb);
       }
     } else if (!done) {
       done = true;   // a wait ran out: this lane stops (the consumers give up on their own)
     }
-    advance(N);
+    k = N;
     ++issue;
     slot += N;
     if (slot >= rg.ns) {
@@ -1164,6 +1053,22 @@ __device__ FSVD_COLD int gemv_stage(const Stage& st, const CtaConst& cc, int s, 
   trace_mark(trow, 1);
   // A CTA without units neither reads the stage's input nor writes anything.
   if (bp.nu == 0) return 0;
+  // First input column of every (unit, operand) of this CTA, as a table in shared memory: the box
+  // loop below then has no index arithmetic.  Written before the wait for the input (it does not
+  // depend on it) and published by the CTA barrier behind the stage-in.
+  int* const xtab = cc.xtab;
+  const int nio = bp.nu * nops;   // <= kMaxUnitOps (checked by the program builder)
+  for (int i = tid; i < nio; i += kConsThreads) {
+    const int j = nops == 2 ? (i >> 1) : i, op = nops == 2 ? (i & 1) : 0;
+    const int uidx = bp.first + j * grid;
+    const int seg = qmod(uidx, segs);
+    int x0 = (op ? st.xB_off : st.xA_off) + ((st.flags & SF_SEG_X) ? 0 : seg * cps * boxcols);
+    if (st.epi == EPI_QKV) {   // segs == 1: uidx is the row group; the part's input starts at part * K
+      const int p0 = uidx * kUnitRows, half = st.rope_half;
+      x0 += ((p0 >= st.H * half) + (p0 >= (st.H + st.Hk) * half)) * st.K;
+    }
+    xtab[i] = x0;
+  }
   // ---- wait for the words of the input vector, stage it
   if (st.vl_mode != VL_NONE) {
     stage_vector<T>(st, cc.xvec, cc.xstride, cc.red, cc.part, tid, kConsThreads, stage_tag(cc.tag_base, st.in_stage),
@@ -1251,15 +1156,8 @@ __device__ FSVD_COLD int gemv_stage(const Stage& st, const CtaConst& cc, int s, 
     if (io != cur_io) {
       if (cur_io >= 0) flush();
       cur_io = io;
-      cur_kk = qmod(c, step);
-      const int j = nops == 2 ? (io >> 1) : io, op = nops == 2 ? (io & 1) : 0;
-      const int uidx = bp.first + j * grid;
-      const int seg = qmod(uidx, segs);
-      xcol0 = (op ? st.xB_off : st.xA_off) + ((st.flags & SF_SEG_X) ? 0 : seg * cps * boxcols);
-      if (st.epi == EPI_QKV) {   // segs == 1: uidx is the row group; the part's input starts at part * K
-        const int p0 = uidx * kUnitRows, half = st.rope_half;
-        xcol0 += ((p0 >= st.H * half) + (p0 >= (st.H + st.Hk) * half)) * st.K;
-      }
+      cur_kk = c;   // the first chunk of a warp in a (unit, operand) is below step
+      xcol0 = xtab[io];
     }
     bool ok = mbar_wait(cc.ring.full + slot * 8, (uint32_t)round & 1u, w);
     ok = __all_sync(0xffffffffu, ok);
@@ -1418,35 +1316,35 @@ __device__ __forceinline__ void attn_scores(uint32_t ka, int nrows, uint32_t row
                                             float (&acc)[GI][DPL], float (&m)[GI], float (&l)[GI], float* tile,
                                             float* pbuf, float scale, int lane) {
   constexpr int RBM = 32 / GI;
-#pragma unroll 4
-  for (int u = 0; u < RBM; ++u) {
-    if (u < nrows) {
-      float kf[DPL];
-      lds_row<T, DPL>(ka + u * rowb, kf);
+  // (rolled loops: this code runs once per stage and is bound by instruction fetch)
+#pragma unroll 1
+  for (int u = 0; u < nrows; u += 2) {
+    float kf[2][DPL];
+    lds_row<T, DPL>(ka + u * rowb, kf[0]);
+    lds_row<T, DPL>(ka + (u + 1 < nrows ? u + 1 : u) * rowb, kf[1]);
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
 #pragma unroll
       for (int g = 0; g < GI; ++g) {
         float s2 = 0.f;
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) s2 = fmaf(q[g][d], kf[d], s2);
-        tile[(g * RBM + u) * 33 + lane] = s2;
+        for (int d = 0; d < DPL; ++d) s2 = fmaf(q[g][d], kf[r][d], s2);
+        tile[(g * RBM + u + r) * 33 + lane] = s2;   // (row u + 1 of the tile may be past nrows: never read)
       }
-    }
   }
   __syncwarp();
-  float sa = 0.f, sb = 0.f, sc2 = 0.f, sd = 0.f;
+  float sa = 0.f, sb = 0.f;
   const int gu = lane / RBM, uu = lane - gu * RBM;   // head and key of this lane's score
   const bool valid = uu < nrows;
   if (valid) {
     const float* row = tile + lane * 33;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 32; i += 4) {
-      sa += row[i];
-      sb += row[i + 1];
-      sc2 += row[i + 2];
-      sd += row[i + 3];
+      sa += row[i] + row[i + 2];
+      sb += row[i + 1] + row[i + 3];
     }
   }
-  const float score = valid ? ((sa + sb) + (sc2 + sd)) * scale : -INFINITY;
+  const float score = valid ? (sa + sb) * scale : -INFINITY;
   float pmine = 0.f;
 #pragma unroll
   for (int g = 0; g < GI; ++g) {
@@ -1471,17 +1369,17 @@ template <typename T, int GI, int DPL>
 __device__ __forceinline__ void attn_values(uint32_t va, int nrows, uint32_t rowb, float (&acc)[GI][DPL],
                                             const float* pbuf) {
   constexpr int RBM = 32 / GI;
-#pragma unroll 4
-  for (int u = 0; u < RBM; ++u) {
-    if (u < nrows) {
-      float vf[DPL];
-      lds_row<T, DPL>(va + u * rowb, vf);
+#pragma unroll 1
+  for (int u = 0; u < nrows; u += 2) {
+    const bool two = u + 1 < nrows;
+    float vf[2][DPL];
+    lds_row<T, DPL>(va + u * rowb, vf[0]);
+    lds_row<T, DPL>(va + (two ? u + 1 : u) * rowb, vf[1]);
 #pragma unroll
-      for (int g = 0; g < GI; ++g) {
-        const float pg = pbuf[g * RBM + u];
+    for (int g = 0; g < GI; ++g) {
+      const float p0 = pbuf[g * RBM + u], p1 = two ? pbuf[g * RBM + u + 1] : 0.f;
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(pg, vf[d], acc[g][d]);
-      }
+      for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(p1, two ? vf[1][d] : 0.f, fmaf(p0, vf[0][d], acc[g][d]));
     }
   }
   __syncwarp();   // the tile and pbuf are rewritten by the next box
@@ -1506,9 +1404,9 @@ __device__ FSVD_COLD int attn_stage(const Stage& st, const CtaConst& cc, int s, 
   const int Dh = ap.Dh, H = ap.H, grid = gridDim.x;
   const int rec = Dh + 2;                  // floats of one partial result: acc[Dh], max, sum
   float* const sh = cc.part;
-  // per-warp scratch behind the partial results: score tile [32][33] and probabilities [32]
-  float* const tile = sh + kNWC * GI * rec + warp * (32 * 34);
-  float* const pbuf = tile + 32 * 33;
+  // per-warp scratch behind the partial results: score tile [33][33] and probabilities [32]
+  float* const tile = sh + kNWC * GI * rec + warp * (33 * 33 + 32);
+  float* const pbuf = tile + 33 * 33;
   const uint32_t rowb = (uint32_t)Dh * (uint32_t)sizeof(T);
   const uint32_t laneoff = (uint32_t)(lane * DPL) * (uint32_t)sizeof(T);
   const bool qT = (st.flags & SF_IN_T) != 0;
@@ -1516,6 +1414,7 @@ __device__ FSVD_COLD int attn_stage(const Stage& st, const CtaConst& cc, int s, 
                  tag_v = stage_tag(cc.tag_base, st.v_stage), tag_out = stage_tag(cc.tag_base, s);
   unsigned seq = seq_base;
   int total = 0;
+#pragma unroll 1
   for (int hs = first_item(blockIdx.x, qmod(st.rot, grid), grid); hs < ap.nslice; hs += grid) {
     AttnItem it;
     attn_item(ap, hs, cc.pc, it);
@@ -1532,6 +1431,7 @@ __device__ FSVD_COLD int attn_stage(const Stage& st, const CtaConst& cc, int s, 
     }
     trace_mark(trow, 4);
     // ---- this warp's key box and value box of every chunk
+#pragma unroll 1
     for (int c = 0; c < it.nch; ++c) {
       const int kbc = c == it.nch - 1 ? it.kbl : it.kb;
       if (warp < kbc) {
@@ -1563,6 +1463,7 @@ __device__ FSVD_COLD int attn_stage(const Stage& st, const CtaConst& cc, int s, 
     trace_mark(trow, 5);
     // ---- the rows this launch appends, from the tagged side buffers
     if (it.nfresh > 0 && it.part == ap.cph - 1 && warp == (it.kbl < ap.step ? it.kbl : 0)) {
+#pragma unroll 1
       for (int r = 0; r < it.nfresh; ++r) {
         const int sr = ap.shared ? r : it.b;
         const size_t ki = ((size_t)sr * ap.Hk + it.hk) * Dh + lane * DPL;
@@ -1605,12 +1506,12 @@ __device__ FSVD_COLD int attn_stage(const Stage& st, const CtaConst& cc, int s, 
       // warp g merges the 7 states of head g in warp order and publishes the part record
       const int g = warp;
       float M = -INFINITY;
-#pragma unroll
+#pragma unroll 1
       for (int w2 = 0; w2 < kNWC; ++w2) M = fmaxf(M, sh[(size_t)(w2 * GI + g) * rec + Dh]);
       float L = 0.f, o[DPL];
 #pragma unroll
       for (int d = 0; d < DPL; ++d) o[d] = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int w2 = 0; w2 < kNWC; ++w2) {
         const float* src = sh + (size_t)(w2 * GI + g) * rec;
         const float lw = src[Dh + 1];
@@ -1737,7 +1638,8 @@ static __device__ FSVD_COLD void run_argmax(const Stage& st, float* redv, int* r
 // ----------------------------------------------------------------------------- the kernel
 // Dynamic shared memory layout:
 //   [0, 2*sizeof(Stage))        current and next stage descriptor
-//   [.., +1024)                 reduction scratch (256), flags and cache positions (256), CtaConst (512)
+//   [.., +2048)                 reduction scratch (256), flags and cache positions (256), CtaConst (512),
+//                               column table of the running GEMV stage (1024)
 //   [.., +kSmallProgBytes)      copy of a by-value program (per-op launches)
 //   [.., +512)                  ring mbarriers: full[kMaxSlots], empty[kMaxSlots]
 //   -- header rounded to 1 KB --
@@ -1814,6 +1716,7 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
     c.xvec = xvec;
     c.red = red;
     c.part = part;
+    c.xtab = reinterpret_cast<int*>(smem + 2 * kStageBytesAl + 1024);
     c.xstride = xstride;
     c.backoff_ns = ((tune >> 4) & 15) * 32;
     c.gate = (tune >> 8) & 1;
@@ -1847,6 +1750,20 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
         int* dst = reinterpret_cast<int*>(cur_base + ((s + 1) & 1) * kStageBytesAl);
         const int* src = reinterpret_cast<const int*>(prog + s + 1);
         for (int i = lane; i < kStageWords; i += 32) dst[i] = src[i];
+        __syncwarp();
+        // What the next stage reads from HBM besides its boxes (norm weights, the rotary table rows
+        // of the batch rows' positions) is asked for now: a cold read on the critical path costs
+        // microseconds while the box stream saturates the memory system.
+        const Stage& nx = *reinterpret_cast<const Stage*>(dst);
+        if (nx.type == ST_GEMV) {
+          if (nx.vl_mode == VL_RMSNORM) prefetch_l2(nx.vl_w, nx.vl_len * (int)sizeof(T), lane);
+          if (nx.cos_tab && lane < nx.B) {
+            const int half = nx.Dh >> 1;
+            const size_t off = (size_t)min(cached_pos(cc.pc, nx.seqlens, lane), nx.S_max - 1) * half * sizeof(T);
+            prefetch_l2(reinterpret_cast<const char*>(nx.cos_tab) + off, half * (int)sizeof(T), 0);
+            prefetch_l2(reinterpret_cast<const char*>(nx.sin_tab) + off, half * (int)sizeof(T), 0);
+          }
+        }
       }
       const unsigned long long bar_target = (unsigned long long)(nbar + 1u) * gridDim.x;
       if (st.flags & SF_BARRIER) ++nbar;

@@ -140,8 +140,8 @@ enum DeviceStatus : int {
 };
 
 // Geometry of the box stream.
-// 8 warps per CTA: with more, the register file leaves 168 registers per thread and the
-// interpreter spills; 256 threads get 255.
+// 8 warps per CTA: registers are handed out in groups of four warps, so a ninth warp would leave
+// 168 registers per thread and the interpreter would spill; 256 threads get 255.
 constexpr int kConsumerWarps = 7;      // warps that multiply
 constexpr int kProducerWarps = 1;      // warp that issues the TMA copies, from one lane per consumer warp
 constexpr int kUnitRows = 16;          // factor rows of one unit = rows of one box
@@ -181,7 +181,8 @@ struct alignas(64) SmallMaps {
 // program, the ring's mbarriers), rounded to 1 KB.
 constexpr int kStageBytesAl = ((int)sizeof(Stage) + 15) / 16 * 16;
 constexpr int kSmallProgBytes = kMaxSmallStages * kStageBytesAl;
-constexpr int kHeaderScratchBytes = 1024;   // reduction scratch, flags, the CTA's launch constants
+constexpr int kHeaderScratchBytes = 2048;   // reduction scratch, flags, the CTA's launch constants, column table
+constexpr int kMaxUnitOps = 256;            // (unit, operand) pairs of one CTA in one GEMV stage, at most
 FSVD_HD constexpr int smem_header_bytes() {
   return ((2 * kStageBytesAl + kHeaderScratchBytes + kSmallProgBytes + 512 + 1023) / 1024) * 1024;
 }
