@@ -516,8 +516,8 @@ __device__ __forceinline__ uint4 ld_raw16(const void* base, size_t i) {
 // Per batch row a thread owns up to UP positions of two words; it walks the partial vectors in
 // segment order (a fixed summation order), SG vectors per round, and per round issues the loads of
 // all its positions before looking at a tag, repeating them until every word carries `tag`.
-// (UP x SG = 16 loads of 16 bytes in flight; every further round is another round trip to L2 on
-// the critical path.)
+// UP x SG = 8 loads of 16 bytes in flight: every further round is another round trip to L2 on the
+// critical path, more loads in flight cost registers the interpreter does not have.
 template <typename T, int UP, int SG>
 __device__ __forceinline__ void stage_sum_tagged(const Stage& st, char* xvec, int xstride, int col0, int lenS,
                                                  int tid, uint32_t tag, const Waiter& w) {
@@ -541,7 +541,7 @@ __device__ __forceinline__ void stage_sum_tagged(const Stage& st, char* xvec, in
           bool ok = true;
 #pragma unroll
           for (int g = 0; g < SG; ++g) {
-            // (a round past the last vector repeats the last one and is not added)
+            // (a round past the last vector repeats the round's first one and is not added)
             const tword* bg = base + (q + g < nseg ? g : 0) * segstride;
 #pragma unroll
             for (int k = 0; k < UP; ++k)
@@ -638,7 +638,9 @@ __device__ FSVD_COLD void stage_vector(const Stage& st, char* xvec, int xstride,
       st2<T>(xvec, (size_t)b * xstride + (e - col0), o.x, o.y);
     }
   } else if (st.vl_mode == VL_SUM && tagged) {
-    stage_sum_tagged<T, 8, 1>(st, xvec, xstride, col0, lenS, tid, tag, w);
+    // short vectors in several parts: 4 positions x 2 partial vectors per round; else 8 x 1
+    if (st.vl_nseg > 1 && (lenS >> 1) <= kConsThreads * 4) stage_sum_tagged<T, 4, 2>(st, xvec, xstride, col0, lenS, tid, tag, w);
+    else stage_sum_tagged<T, 8, 1>(st, xvec, xstride, col0, lenS, tid, tag, w);
   } else if (st.vl_mode == VL_SUM) {
     // plain T -> T copy of an input of the call
     const int upr = lenS / VEC, units = B * upr;
@@ -704,12 +706,23 @@ __device__ FSVD_COLD void stage_vector(const Stage& st, char* xvec, int xstride,
                    wg[q].y * X::rnd(tw_val(v[q].y) * inv));
         }
       } else {
+        // second pass over the row (its words are known to be there): U positions per round trip
+        row = reinterpret_cast<const tword*>(st.vl_src) + (size_t)b * len + tid * 2;
 #pragma unroll 1
-        for (int u = tid; u < upr; u += NT) {
-          const ulonglong2 x2 = ld_tword2(st.vl_src, (size_t)b * len + (size_t)u * 2);
-          const float2 g = X::ldg2(st.vl_w, (size_t)u * 2);
-          st2<T>(xvec, (size_t)b * xstride + (size_t)u * 2, g.x * X::rnd(tw_val(x2.x) * inv),
-                 g.y * X::rnd(tw_val(x2.y) * inv));
+        for (int u0 = tid; u0 < upr; u0 += NT * U, row += NT * U * 2) {
+#pragma unroll
+          for (int q = 0; q < U; ++q)
+            if (u0 + q * NT < upr) {
+              v[q] = ld_tword2(row, (size_t)(q * NT * 2));
+              wg[q] = X::ldg2(st.vl_w, (size_t)(u0 + q * NT) * 2);
+            }
+#pragma unroll
+          for (int q = 0; q < U; ++q) {
+            const int u = u0 + q * NT;
+            if (u < upr)
+              st2<T>(xvec, (size_t)b * xstride + (size_t)u * 2, wg[q].x * X::rnd(tw_val(v[q].x) * inv),
+                     wg[q].y * X::rnd(tw_val(v[q].y) * inv));
+          }
         }
       }
     }
