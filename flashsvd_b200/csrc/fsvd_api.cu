@@ -9,7 +9,6 @@
 
 #include <atomic>
 #include <mutex>
-#include <set>
 #include <vector>
 
 #include "../../include/flashsvd_b200.h"
@@ -42,10 +41,9 @@ static int fail(int code, const char* fmt, ...) {
 struct Settings {
   int slots = 0, grid = 0;   // ring slots (0 = as many as fit), CTAs (0 = one per SM)
   long long wait_limit = 4000000000ll;   // ~2 s of SM clocks
-  int tune = 0;              // kernel tuning word (fsvd_launch.h)
   unsigned long long* trace = nullptr;
   size_t trace_bytes = 0;
-  unsigned generation = 0;   // bumped by every change: cached programs of an older generation are stale
+  unsigned generation = 0;   // bumped by every change of the geometry: cached programs of an older one are stale
 };
 static Settings g_set;
 static std::mutex g_set_mu;
@@ -61,7 +59,6 @@ static Settings current_settings() {
     g_set.grid = env_int("FSVD_GRID", 0);
     const char* wl = getenv("FSVD_WAIT_CLOCKS");
     if (wl && *wl && atoll(wl) >= 1000) g_set.wait_limit = atoll(wl);
-    g_set.tune = env_int("FSVD_TUNE", 0);
   });
   std::lock_guard<std::mutex> lock(g_set_mu);
   return g_set;
@@ -88,8 +85,8 @@ static int get_props(DevProps& p) {
 }
 
 // ------------------------------------------------------------------------------- kernel table
-// The kernel instantiations live in fsvd_inst_*.cu (one translation unit per element type, so
-// they compile in parallel); each exports a table of launchers.
+// The kernel instantiations live in fsvd_inst_*.cu (one translation unit per element type and
+// batch width, so they compile in parallel); each exports a table of launchers.
 #include "fsvd_launch.h"
 extern const KernelEntry g_kernels_bf16[];
 extern const KernelEntry g_kernels_f32[];
@@ -105,14 +102,15 @@ struct Resolved {
 
 static int resolve(int dtype, int B, Resolved& r) {
   r.set = current_settings();
+  const Settings& c = r.set;
   DevProps p;
   if (int e = get_props(p)) return e;
+  r.device = p.device;
   const int bmax = dtype == FSVD_DTYPE_F32 ? 4 : 8;   // FSVD_DTYPE_BF16_Q4: int4 factors, bf16 everything else
   if (B < 1 || B > bmax) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..%d)", B, bmax);
-  r.grid = r.set.grid > 0 ? (r.set.grid < p.sms ? r.set.grid : p.sms) : p.sms;
+  r.grid = c.grid > 0 ? (c.grid < p.sms ? c.grid : p.sms) : p.sms;
   r.smem_optin = p.smem_optin;
-  r.device = p.device;
-  r.max_slots = r.set.slots > 0 ? r.set.slots : kMaxSlots;
+  r.max_slots = c.slots > 0 ? c.slots : kMaxSlots;
   for (const KernelEntry* tab : g_kernel_tables)
     for (const KernelEntry* kp = tab; kp->fn; ++kp)
       if (kp->dtype == dtype && !r.fn) r.fn = kp->fn;
@@ -140,19 +138,19 @@ static EncodeTiledFn encode_fn() {
 static_assert(sizeof(CUtensorMap) == 128, "TMA descriptor size");
 
 // Descriptor of a row-major [rows, cols] matrix with row stride ldw elements, read in boxes of
-// box_rows rows x box_cols columns; rows and columns outside the matrix read as zeros.
-static int encode_map_box(unsigned char* out, int dtype, const void* base, long long rows, long long cols,
-                          long long ldw, int box_cols, int box_rows) {
+// kUnitRows rows x kBoxRowBytes bytes; rows and columns outside the matrix read as zeros.
+static int encode_map(unsigned char* out, int dtype, const void* base, long long rows, long long cols,
+                      long long ldw) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
   const int esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
-  if (rows < 1 || cols < 1) return fail(FSVD_ERR_ARG, "empty matrix");
+  if (rows < 1 || cols < 1) return fail(FSVD_ERR_ARG, "empty factor matrix");
   if ((ldw * esize) % 16 || (reinterpret_cast<uintptr_t>(base) & 15))
-    return fail(FSVD_ERR_ALIGN, "matrix rows must start on 16-byte boundaries");
+    return fail(FSVD_ERR_ALIGN, "factor rows must start on 16-byte boundaries");
   CUtensorMap tm;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ldw * esize};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)(kBoxRowBytes / esize), (cuuint32_t)kUnitRows};
   cuuint32_t es[2] = {1, 1};
   const CUresult r = enc(&tm, dtype == FSVD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                          2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -161,12 +159,6 @@ static int encode_map_box(unsigned char* out, int dtype, const void* base, long 
   if (r != CUDA_SUCCESS) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   memcpy(out, &tm, 128);
   return 0;
-}
-// A factor matrix, read in boxes of kUnitRows rows x kBoxRowBytes bytes.
-static int encode_map(unsigned char* out, int dtype, const void* base, long long rows, long long cols,
-                      long long ldw) {
-  const int esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
-  return encode_map_box(out, dtype, base, rows, cols, ldw, kBoxRowBytes / esize, kUnitRows);
 }
 
 // Bytes of the int4 tile stream of a [rows, K] factor (fsvd_stage.h describes the tile).
@@ -197,32 +189,33 @@ static int encode_map_q4(unsigned char* out, const void* base, long long tiles) 
 // ------------------------------------------------------------------------------- workspace
 static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 constexpr int kMaxSegs = 8;
-constexpr int kMaxParts = 4;   // CTAs per attention head group
-constexpr size_t kWord = 8;    // bytes of a tagged word
+constexpr int kMaxSplit = 32;
+constexpr size_t kCounterBytes = 4096;  // B * Hk ints
 
 struct WsLayout {
-  size_t sync, pa, pb, hact, qbuf, knew, vnew, hidden, part_acc, part_ml, total;
+  size_t sync, pa, pb, hact, qbuf, attn, hidden, part_acc, part_ml, counters, total;
 };
 static int imax(int a, int b) { return a > b ? a : b; }
 
-// Every buffer but the first holds tagged words (8 bytes per element).
 static WsLayout ws_layout(const fsvd_dims& D) {
   WsLayout L;
   size_t o = 0;
   const int B = D.B;
   const int maxrank = imax(imax(D.Rq + D.Rk + D.Rv, D.Ru + D.Rg), imax(D.Ro, D.Rd));
-  // The sync words sit at offset 0, whatever the shapes: every entry point that shares one
-  // workspace finds them where the others left them.
+  // The barrier words and the attention arrival counters sit at fixed offsets, whatever the
+  // shapes: every entry point that shares one workspace finds them where the others left them
+  // (zero between launches).
   L.sync = o;      o += al256(sizeof(SyncState));
-  L.pa = o;        o += al256((size_t)kMaxSegs * B * maxrank * kWord);
-  L.pb = o;        o += al256((size_t)kMaxSegs * B * maxrank * kWord);
-  L.hact = o;      o += al256((size_t)B * imax(D.I, 8) * kWord);
-  L.qbuf = o;      o += al256((size_t)B * D.H * D.Dh * kWord);
-  L.knew = o;      o += al256((size_t)B * D.Hk * D.Dh * kWord);
-  L.vnew = o;      o += al256((size_t)B * D.Hk * D.Dh * kWord);
-  L.hidden = o;    o += al256((size_t)B * D.d * kWord);
-  L.part_acc = o;  o += al256((size_t)B * D.H * kMaxParts * D.Dh * kWord);
-  L.part_ml = o;   o += al256((size_t)B * D.H * kMaxParts * 2 * kWord);
+  L.counters = o;  o += kCounterBytes;
+  // pa, pb, hact, attn and hidden hold (fp32, tag) pairs: 8 bytes per element
+  L.pa = o;        o += al256((size_t)kMaxSegs * B * maxrank * 8);
+  L.pb = o;        o += al256((size_t)kMaxSegs * B * maxrank * 8);
+  L.hact = o;      o += al256((size_t)B * imax(D.I, 8) * 8);
+  L.qbuf = o;      o += al256((size_t)B * D.H * D.Dh * 4);
+  L.attn = o;      o += al256((size_t)B * D.H * D.Dh * 8);
+  L.hidden = o;    o += al256((size_t)B * D.d * 8);
+  L.part_acc = o;  o += al256((size_t)B * D.H * kMaxSplit * D.Dh * 4);
+  L.part_ml = o;   o += al256((size_t)B * D.H * kMaxSplit * 2 * 4);
   L.total = o;
   return L;
 }
@@ -231,20 +224,29 @@ static WsLayout ws_layout(const fsvd_dims& D) {
 struct MapPair {
   unsigned char m[2][128];
 };
+// What a TMA descriptor of a stage will be made from.  The descriptors are encoded when a program
+// is finished and not found among the cached ones: a per-op call that repeats an earlier call
+// (same pointers and sizes) then costs no driver call.
+struct MapReq {
+  int kind = 0;   // 0 none, 1 dense [rows, cols] with row stride ldw, 2 int4 tile stream of `rows` tiles
+  const void* base = nullptr;
+  long long rows = 0, cols = 0, ldw = 0;
+};
 
 struct Builder {
   std::vector<Stage> st;
-  std::vector<MapPair> maps;   // TMA descriptors of st[i] (zeros for stages without boxes)
-  int grid, B, esize, dtype, boxcols, max_slots;
+  std::vector<MapPair> maps;   // TMA descriptors of st[i] (zeros for stages without factors)
+  std::vector<MapReq> reqs;    // two per stage: what maps[i].m[0] / m[1] are encoded from
+  int grid, TW, B, esize, dtype, boxcols, max_slots;
   long long cum_units = 0;   // GEMV units handed out so far (rotates the unit -> CTA map)
-  long long cum_items = 0;   // attention items handed out so far (item -> CTA map)
+  long long cum_items = 0;   // attention items handed out so far (item -> warp map)
   int max_vec = 8;           // elements of the staged vector a lane may touch, per batch row
-  int err = 0;               // first error of gemv() / attn()
+  int err = 0;               // first error of gemv()
   bool wq4 = false;          // factors are int4 tile streams (FSVD_DTYPE_BF16_Q4)
-  int attn_rec_floats = 0;   // shared-memory floats an attention stage of this program needs
 
   Builder(const Resolved& r, int dtype_, int B_) {
     grid = r.grid;
+    TW = r.grid * kConsumerWarps;
     wq4 = dtype_ == FSVD_DTYPE_BF16_Q4;
     dtype = wq4 ? FSVD_DTYPE_BF16 : dtype_;
     esize = dtype == FSVD_DTYPE_BF16 ? 2 : 4;
@@ -258,29 +260,53 @@ struct Builder {
     s.B = B;
     s.segs = 1;
     s.cps = 1;
-    s.in_stage = s.k_stage = s.v_stage = -1;
     return s;
   }
-  int push(const Stage& s) {
+  void push(const Stage& s) {
     st.push_back(s);
     MapPair z;
     memset(&z, 0, sizeof(z));
     maps.push_back(z);
-    return last();
+    reqs.push_back(MapReq());
+    reqs.push_back(MapReq());
   }
-  int last() const { return (int)st.size() - 1; }
-
+  void request(int which, int kind, const void* base, long long rows, long long cols, long long ldw) {
+    MapReq& q = reqs[2 * (st.size() - 1) + which];
+    q.kind = kind; q.base = base; q.rows = rows; q.cols = cols; q.ldw = ldw;
+  }
+  // ST_ATTN: CTAs per head group (a head group = 1 query head, or 2 that share a kv head) and
+  // the rotation of the slice -> CTA map.  Every CTA cuts its part of the keys into 7 splits, one
+  // per consumer warp.
+  bool has_attn = false;
+  int attn_rec_floats = 0;
+  void attn_geometry(Stage& s) {
+    const int G = s.H / s.Hk, GI = (G % 2 == 0) ? 2 : 1;
+    const long long groups = (long long)s.B * s.H / GI;
+    int cph = (int)(grid / (groups > 0 ? groups : 1));
+    if (cph < 1) cph = 1;
+    if (cph > kMaxSplit / kConsumerWarps) cph = kMaxSplit / kConsumerWarps;
+    s.nsplit = cph * kConsumerWarps;
+    s.rot = (int)(cum_items % grid);
+    cum_items += groups * cph;
+    has_attn = true;
+    // partial results of the warps + per-warp score tiles [rows][33] and probabilities [rows]
+    // (rows = query heads of the group x cache rows per chunk: 10 for one head, 2 x 12 for two)
+    const int rows = GI == 1 ? 10 : 24;
+    const int need = kConsumerWarps * GI * (s.Dh + 2) + kConsumerWarps * rows * 34;
+    if (need > attn_rec_floats) attn_rec_floats = need;
+  }
+  // GEMV stage.  Units (16 rows x one K segment) go round-robin to the CTAs; with split_k the K
+  // range is cut into the number of segments (<= kMaxSegs) that gives the busiest CTA the fewest
+  // boxes.  rows_total: rows of the matrices behind WA (and WB) that the descriptors may read.
   // Pointer to row `rows` (a multiple of 16 for int4) of a [*, K] factor that starts at base.
   const void* row_ptr(const void* base, long long rows, int K) const {
     const size_t off = wq4 ? q4_bytes(rows, K) : (size_t)rows * K * esize;
     return reinterpret_cast<const char*>(base) + off;
   }
-  // GEMV stage.  Units (16 rows x one K segment) go round-robin to the CTAs; with split_k the K
-  // range is cut into the number of segments (<= kMaxSegs) that gives the busiest CTA the fewest
-  // boxes.  seg_x: the input is a vector of T values taken as it is (no sum, no norm); when it is
-  // longer than 4 KB the K segments are restricted to divisors of the grid so that every CTA
-  // works in one segment and stages only that part of the input (SF_SEG_X): a shorter stage-in,
-  // and with several batch rows the staged vector no longer takes the shared memory the ring needs.
+  // seg_x: the input is a T vector copied as it is (VL_SUM with SF_IN_T); when it is longer than
+  // 4 KB the K segments are restricted to divisors of the grid so that every CTA works in one
+  // segment and stages only that part of the input (SF_SEG_X): a shorter stage-in, and with several
+  // batch rows the staged vector no longer takes the shared memory the ring needs.
   Stage& gemv(const void* WA, const void* WB, int P, int K, int ldw, bool split_k, int rope_half = 0,
               int q4_override = -1, bool seg_x = false) {
     const bool q4 = q4_override < 0 ? wq4 : q4_override != 0;
@@ -308,10 +334,10 @@ struct Builder {
         if (local && grid % segs) continue;
         const long long units = (long long)groups * real;
         // time of the busiest CTA's boxes at an SM's share of HBM bandwidth (44 bytes/ns), plus
-        // the time every CTA of the next stage spends reading `real` partial vectors of tagged
-        // words from L2 (4 bytes/ps over the whole GPU)
+        // the time every CTA of the next stage spends reading `real` partial vectors from L2
+        // (4 bytes/ps over the whole GPU)
         const long long cost = ((units + grid - 1) / grid) * cps * (boxbytes / 44) +
-                               (long long)real * P * (long long)kWord * grid / 4000;
+                               (long long)real * P * 4 * grid / 4000;
         if (best_cost < 0 || cost < best_cost) {
           best_cost = cost;
           best_segs = real;
@@ -326,9 +352,6 @@ struct Builder {
     s.nch = q4 ? nchunks : 0;
     s.rot = (int)(cum_units % grid);
     cum_units += (long long)groups * best_segs;
-    if (((long long)groups * best_segs + grid - 1) / grid * (WB ? 2 : 1) > kMaxUnitOps && !err)
-      err = fail(FSVD_ERR_UNSUPPORTED, "%d output rows are more than a launch of %d CTAs takes (%d rows per CTA and operand)",
-                 P, grid, kMaxUnitOps * kUnitRows);
     push(s);
     // rows behind the pointers: a rotary stage reads physical rows [0, 2P) through WA and
     // [half, 2P) through WB = WA + half rows
@@ -340,175 +363,34 @@ struct Builder {
       // tile rows behind the pointers (a rotary stage's second operand starts rope_half rows in)
       const long long trA = (rowsA + kUnitRows - 1) / kUnitRows;
       const long long trB = rope_half > 0 ? trA - rope_half / kUnitRows : trA;
-      if (!err) err = encode_map_q4(maps.back().m[0], WA, trA * nchunks);
-      if (!err && WB) err = encode_map_q4(maps.back().m[1], WB, trB * nchunks);
+      request(0, 2, WA, trA * nchunks, 0, 0);
+      if (WB) request(1, 2, WB, trB * nchunks, 0, 0);
     } else {
-      if (!err) err = encode_map(maps.back().m[0], dtype, WA, rowsA, K, ldw);
-      if (!err && WB) err = encode_map(maps.back().m[1], dtype, WB, rowsB, K, ldw);
+      request(0, 1, WA, rowsA, K, ldw);
+      if (WB) request(1, 1, WB, rowsB, K, ldw);
     }
     return st.back();
   }
-  // Input vector of the stage just appended (s must be st.back()).  src_stage >= 0: src holds
-  // tagged words written by that stage of this program (the stage polls them); -1: src is a plain
-  // T input of the call.
-  void vec(Stage& s, int mode, const void* src, int len, int nseg, int src_stage) {
+  // Input vector of the stage just appended (s must be st.back()).  `barrier`: the vector is
+  // produced by earlier stages of this program, so the stage waits at a grid barrier and the
+  // stage before it arrives there.
+  void vec(Stage& s, int mode, const void* src, int len, int nseg, bool barrier) {
     s.vl_mode = mode;
     s.vl_src = src;
     s.vl_len = len;
     s.vl_nseg = nseg;
-    if (src_stage >= 0) {
-      s.flags |= SF_TAG_IN;
-      s.in_stage = src_stage;
-    } else {
-      s.flags |= SF_IN_T;
-    }
+    if (barrier) need_barrier(s);
     const int staged = (s.flags & SF_SEG_X) ? (len < s.kseg ? len : s.kseg) : len;
     if (staged > max_vec) max_vec = staged;
   }
-  void need_barrier(int i) {
-    st[i].flags |= SF_BARRIER;
-    if (i >= 1) st[i - 1].flags |= SF_ARRIVE;
+  void need_barrier(Stage& s) {
+    s.flags |= SF_BARRIER;
+    if (st.size() >= 2) st[st.size() - 2].flags |= SF_ARRIVE;
   }
+  int last() const { return (int)st.size() - 1; }
 
-  // ST_ATTN stage over caches [rowsB, S_max, Hk, Dh] (rowsB = 1 for a prompt chunk, else B).
-  // CTAs per head group (a head group = 1 query head, or 2 that share a kv head) = cph <= 4; every
-  // CTA cuts its part of the keys into chunks of up to 7 key boxes + 7 value boxes, one pair per warp.
-  // Returns the stage index.
-  int attn(Stage s, const void* kcache, const void* vcache, bool shared_cache) {
-    s.type = ST_ATTN;
-    s.kcache = kcache;
-    s.vcache = vcache;
-    if (shared_cache) s.flags |= SF_SHARED_CACHE;
-    const int G = s.H / s.Hk, GI = (G % 2 == 0) ? 2 : 1;
-    const long long groups = (long long)s.B * s.H / GI;
-    int cph = (int)(grid / (groups > 0 ? groups : 1));
-    if (cph < 1) cph = 1;
-    if (cph > kMaxParts) cph = kMaxParts;
-    s.nsplit = cph;
-    // rows per box: what a ring slot holds, at most one score per lane and query head of the group
-    int rb = kBoxBytes / (s.Dh * esize);
-    if (rb > kAttnMaxRows / GI) rb = kAttnMaxRows / GI;
-    s.attn_rb = rb;
-    s.rot = (int)(cum_items % grid);
-    cum_items += groups * cph;
-    // states of the warps + per-warp score tiles [33][33] and probabilities [32]
-    const int need = kConsumerWarps * GI * (s.Dh + 2) + kConsumerWarps * (33 * 33 + 32);
-    if (need > attn_rec_floats) attn_rec_floats = need;
-    const int i = push(s);
-    const long long rows = (long long)(shared_cache ? 1 : s.B) * s.S_max;
-    const long long cols = (long long)s.Hk * s.Dh;
-    if (!err) err = encode_map_box(maps.back().m[0], dtype, kcache, rows, cols, cols, s.Dh, rb);
-    if (!err) err = encode_map_box(maps.back().m[1], dtype, vcache, rows, cols, cols, s.Dh, rb);
-    return i;
-  }
-
-  // ---- program order instead of barriers -------------------------------------------------
-  // A stage starts when the tagged words it reads have arrived; nothing else orders the CTAs.
-  // Two accesses that no tag orders must therefore be ordered by the chain of arrivals: when a
-  // CTA overwrites a buffer, every CTA that still had to read the previous content must be known
-  // to have done so; when a CTA reads a residual without looking at tags, its writers must be
-  // known to have finished.  "Known" is derived from what the CTA has waited for: a stage that
-  // polls the whole output of its producers knows them finished, and a finished stage implies its
-  // own producers finished (its CTAs together polled everything).  check_order() verifies this
-  // for every reuse in the program and puts a grid barrier in front of a stage where it fails.
-  std::vector<int> producers(int i) const {
-    std::vector<int> p;
-    const Stage& s = st[i];
-    if (s.type == ST_GEMV || s.type == ST_ATTN_OUT) {
-      if (s.flags & SF_TAG_IN) p.push_back(s.in_stage);
-    } else if (s.type == ST_ATTN) {
-      if (s.flags & SF_TAG_IN) p.push_back(s.in_stage);
-      if (s.knew) {
-        p.push_back(s.k_stage);
-        p.push_back(s.v_stage);
-      }
-    }
-    return p;
-  }
-  bool polls_everything(int i) const {
-    const Stage& s = st[i];
-    return s.type == ST_GEMV && (s.flags & SF_TAG_IN) && !(s.flags & SF_SEG_X);
-  }
-  void closure(int i, std::set<int>& out) const {
-    if (i < 0 || out.count(i)) return;
-    out.insert(i);
-    for (int p : producers(i)) closure(p, out);
-  }
-  // stages known finished once some CTA has completed a unit of stage i
-  void known_after_unit(int i, std::set<int>& out, int depth = 0) const {
-    if (i < 0 || depth > (int)st.size()) return;
-    for (int p : producers(i)) {
-      if (polls_everything(i)) closure(p, out);
-      else known_after_unit(p, out, depth + 1);
-    }
-  }
-  bool barrier_between(int r, int w) const {   // a grid barrier in front of a stage in (r, w]
-    for (int t = r + 1; t <= w; ++t)
-      if (st[t].flags & SF_BARRIER) return true;
-    return false;
-  }
-  static void add(std::vector<const void*>& v, const void* p) {
-    if (p) v.push_back(p);
-  }
-  std::vector<const void*> reads(int i) const {
-    std::vector<const void*> v;
-    const Stage& s = st[i];
-    if (s.type == ST_GEMV) {
-      if ((s.flags & SF_TAG_IN) && s.vl_mode != VL_ATTN) add(v, s.vl_src);
-      if (s.flags & SF_RESID_TAG) add(v, s.resid);
-    }
-    if ((s.type == ST_GEMV && s.vl_mode == VL_ATTN) || s.type == ST_ATTN_OUT) {
-      add(v, s.part_acc);
-      add(v, s.part_ml);
-    }
-    if (s.type == ST_ATTN) {
-      if (s.flags & SF_TAG_IN) add(v, s.q);
-      add(v, s.knew);
-      add(v, s.vnew);
-    }
-    return v;
-  }
-  std::vector<const void*> writes(int i) const {
-    std::vector<const void*> v;
-    const Stage& s = st[i];
-    if (s.type == ST_GEMV) {
-      if ((s.flags & SF_TAG_OUT) || s.epi == EPI_PARTIAL) add(v, s.out);
-      add(v, s.knew);
-      add(v, s.vnew);
-    } else if (s.type == ST_ATTN) {
-      add(v, s.part_acc);
-      add(v, s.part_ml);
-    } else if (s.type == ST_EMBED && (s.flags & SF_TAG_OUT)) {
-      add(v, s.out);
-    }
-    return v;
-  }
-  static bool has(const std::vector<const void*>& v, const void* p) {
-    for (const void* q : v)
-      if (q == p) return true;
-    return false;
-  }
-  void check_order() {
-    const int n = (int)st.size();
-    for (int i = 0; i < n; ++i) {
-      std::set<int> known;
-      known_after_unit(i, known);
-      bool need = false;
-      const std::vector<const void*> wr = writes(i), rd = reads(i);
-      for (int r = 0; r < i && !need; ++r) {
-        if (known.count(r) || barrier_between(r, i)) continue;
-        // r is not known finished while stage i's epilogue runs
-        const std::vector<const void*> rr = reads(r), rw = writes(r);
-        for (const void* p : wr)
-          if (has(rr, p) || has(rw, p)) need = true;          // overwrite before r read / wrote it
-        if ((st[i].flags & SF_RESID_TAG) && has(rw, st[i].resid)) need = true;   // untagged read of r's output
-      }
-      if (need) need_barrier(i);
-    }
-  }
-
-  // Shared memory the program needs beyond the header and the ring: warps' partial sums (or the
-  // attention scratch) and the staged vector.
+  // Shared memory the program needs beyond the header and the ring: warps' partial sums and the
+  // staged vector.
   int part_bytes() const {
     long long mx = 0;
     for (const Stage& s : st) {
@@ -519,7 +401,7 @@ struct Builder {
       const long long b = nu * (s.WB ? 2 : 1) * kk * kUnitRows * B * 4;
       if (b > mx) mx = b;
     }
-    if ((long long)attn_rec_floats * 4 > mx) mx = (long long)attn_rec_floats * 4;
+    if (has_attn && (long long)attn_rec_floats * 4 > mx) mx = (long long)attn_rec_floats * 4;
     return (int)((mx + 255) / 256 * 256);
   }
   // Row stride of the staged vector: the longest vector, or the furthest column a box of a K
@@ -570,6 +452,9 @@ static int check_dims(const fsvd_dims& D) {
     return fail(FSVD_ERR_ARG, "bad dtype %d", D.dtype);
   const int bmax = D.dtype == FSVD_DTYPE_F32 ? 4 : 8;
   if (D.B < 1 || D.B > bmax) return fail(FSVD_ERR_UNSUPPORTED, "B=%d unsupported (1..%d)", D.B, bmax);
+  if ((size_t)D.B * D.Hk * sizeof(int) > kCounterBytes)
+    return fail(FSVD_ERR_UNSUPPORTED, "B * Hk = %d exceeds the attention counters (%d)", D.B * D.Hk,
+                (int)(kCounterBytes / sizeof(int)));
   // the kernel's index arithmetic divides through fp32 reciprocals, exact below 2^22
   const int big[] = {D.d, D.I, D.S_max, D.vocab, D.H * D.Dh};
   for (int v : big)
@@ -582,7 +467,7 @@ static int check_dims(const fsvd_dims& D) {
   for (int v : m8)
     if (v <= 0 || v % 8) return fail(FSVD_ERR_ALIGN, "sizes and ranks must be positive multiples of 8 (got %d)", v);
   if (D.S_max < 1) return fail(FSVD_ERR_ARG, "S_max=%d", D.S_max);
-  if ((long long)D.B * D.S_max >= (1ll << 31)) return fail(FSVD_ERR_UNSUPPORTED, "B * S_max too large");
+  if ((size_t)D.B * D.H * 4 > kCounterBytes) return fail(FSVD_ERR_UNSUPPORTED, "B*H=%d too large", D.B * D.H);
   return 0;
 }
 
@@ -596,168 +481,156 @@ static bool qkv_lifts_packed(const Builder& b, const void* q_u, const void* k_u,
 }
 
 struct LayerIO {
-  const void* x_in;    // hidden state [B, d] read by the first RMSNorm and the first residual
-  int x_in_stage;      // >= 0: x_in holds tagged words written by that stage; -1: plain T input
-  void* x_out;         // hidden state [B, d] written by the last residual
-  bool x_out_tagged;   // tagged words (read by a later stage of the program) or plain T
+  const void* x_in;    // hidden state [B, d] of type T read by the first RMSNorm and residual
+  bool x_in_barrier;   // x_in is written by the preceding stage of the same program
+  void* x_out;         // hidden state [B, d] of type T written by the last residual
   const int* seqlens;
   const void* cos_tab;
   const void* sin_tab;
 };
 
-// Appends the stages of one decoder layer; returns the index of its last stage.  Rank-space
-// partial sums travel as fp32, every other activation (attention output, SwiGLU activation,
-// hidden state) as a value already rounded to T, which is where the PyTorch path rounds them.
-static int build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, const LayerIO& io,
-                       char* ws, const WsLayout& L) {
+// Appends the stages of one decoder layer.  Rank-space partial sums travel as fp32, every other
+// activation (attention output, SwiGLU activation, hidden state) as T, which is where the
+// PyTorch path rounds them.
+static void build_layer(Builder& b, const fsvd_dims& D, const fsvd_layer& Lw, const LayerIO& io,
+                        char* ws, const WsLayout& L) {
+  const size_t first_stage = b.st.size();
   void* pa = ws + L.pa;
   void* pb = ws + L.pb;
   void* hact = ws + L.hact;
-  void* qbuf = ws + L.qbuf;
-  void* knew = ws + L.knew;
-  void* vnew = ws + L.vnew;
+  float* qbuf = reinterpret_cast<float*>(ws + L.qbuf);
+  void* attn = ws + L.attn;
   void* mid = ws + L.hidden;
-  void* part_acc = ws + L.part_acc;
-  void* part_ml = ws + L.part_ml;
   const int Rqkv = D.Rq + D.Rk + D.Rv, HD = D.H * D.Dh, half = D.Dh / 2;
-  const bool shared = D.rows_are_positions != 0;
 
-  {  // rank projection of q/k/v on the normalised hidden state
+  {  // 1. rank projection of q/k/v on the normalised hidden state
     Stage& s = b.gemv(Lw.qkv_v, nullptr, Rqkv, D.d, D.d, true);
-    b.vec(s, VL_RMSNORM, io.x_in, D.d, 1, io.x_in_stage);
+    b.vec(s, VL_RMSNORM, io.x_in, D.d, 1, io.x_in_barrier);
+    s.flags |= SF_IN_T;
     s.vl_w = Lw.ln1_w;
     s.eps = D.eps;
     s.epi = EPI_PARTIAL;
     s.out = pa;
   }
-  const int s_rank = b.last(), segs1 = b.st.back().segs;
-  int s_q, s_k, s_v;
-  auto head_fields = [&](Stage& s) {
-    s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
-    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
-    if (shared) s.flags |= SF_SHARED_CACHE;
-  };
+  const int segs1 = b.st.back().segs;
   if (qkv_lifts_packed(b, Lw.q_u, Lw.k_u, Lw.v_u, D.H, D.Hk, D.Dh, D.Rq, D.Rk, D.Rv)) {
-    // q, k and v lifts as one stage over the packed [q_u; k_u; v_u] matrix
+    // 2-4. q, k and v lifts as one stage over the packed [q_u; k_u; v_u] matrix
     Stage& s = b.gemv(Lw.q_u, b.row_ptr(Lw.q_u, half, D.Rq),
                       (D.H + 2 * D.Hk) * half, D.Rq, D.Rq, false, half);
-    b.vec(s, VL_SUM, pa, Rqkv, segs1, s_rank);
+    b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
+    s.rope_half = half;
     s.xA_off = s.xB_off = 0;
     s.epi = EPI_QKV;
-    s.flags |= SF_TAG_OUT;
     s.out = qbuf;
     s.cache = Lw.k_cache;
     s.vcache = Lw.v_cache;
-    s.knew = knew;
-    s.vnew = vnew;
-    head_fields(s);
-    s_q = s_k = s_v = b.last();
+    s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+    s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
   } else {
-    {  // lift q with rotary
-      Stage& s = b.gemv(Lw.q_u, b.row_ptr(Lw.q_u, half, D.Rq), D.H * half, D.Rq, D.Rq, false, half);
-      b.vec(s, VL_SUM, pa, Rqkv, segs1, s_rank);
+    {  // 2. lift q with rotary
+      Stage& s = b.gemv(Lw.q_u, b.row_ptr(Lw.q_u, half, D.Rq),
+                        D.H * half, D.Rq, D.Rq, false, half);
+      b.vec(s, VL_SUM, pa, Rqkv, segs1, true);
+      s.rope_half = half;
       s.xA_off = s.xB_off = 0;
       s.epi = EPI_ROPE_Q;
-      s.flags |= SF_TAG_OUT;
       s.out = qbuf;
-      head_fields(s);
-      s_q = b.last();
+      s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+      s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
     }
-    {  // lift k with rotary into the cache
-      Stage& s = b.gemv(Lw.k_u, b.row_ptr(Lw.k_u, half, D.Rk), D.Hk * half, D.Rk, D.Rk, false, half);
-      b.vec(s, VL_SUM, pa, Rqkv, segs1, s_rank);
+    {  // 3. lift k with rotary into the cache
+      Stage& s = b.gemv(Lw.k_u, b.row_ptr(Lw.k_u, half, D.Rk),
+                        D.Hk * half, D.Rk, D.Rk, false, half);
+      s.rope_half = half;
       s.xA_off = s.xB_off = D.Rq;
       s.epi = EPI_ROPE_K;
       s.cache = Lw.k_cache;
-      s.knew = knew;
-      head_fields(s);
-      s_k = b.last();
+      s.cos_tab = io.cos_tab; s.sin_tab = io.sin_tab; s.seqlens = io.seqlens;
+      s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
     }
-    {  // lift v into the cache
+    {  // 4. lift v into the cache
       Stage& s = b.gemv(Lw.v_u, nullptr, D.Hk * D.Dh, D.Rv, D.Rv, false);
-      b.vec(s, VL_SUM, pa, Rqkv, segs1, s_rank);
       s.xA_off = D.Rq + D.Rk;
       s.epi = EPI_V;
       s.cache = Lw.v_cache;
-      s.vnew = vnew;
-      head_fields(s);
-      s_v = b.last();
+      s.seqlens = io.seqlens;
+      s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
     }
   }
-  int s_attn;
-  {  // attention over the cached rows and the rows just produced
+  {  // 5. attention over the cache including the token just appended
     Stage s = b.blank();
-    s.flags = SF_TAG_IN;
-    s.in_stage = s_q;
-    s.k_stage = s_k;
-    s.v_stage = s_v;
+    s.type = ST_ATTN;
+    s.flags = SF_OUT_T;
     s.q = qbuf;
-    s.knew = knew;
-    s.vnew = vnew;
+    s.kcache = Lw.k_cache;
+    s.vcache = Lw.v_cache;
     s.seqlens = io.seqlens;
     s.seqlen_add = 1;
-    s.part_acc = part_acc;
-    s.part_ml = part_ml;
+    s.out = attn;
+    s.part_acc = reinterpret_cast<float*>(ws + L.part_acc);
+    s.part_ml = reinterpret_cast<float*>(ws + L.part_ml);
+    s.counters = reinterpret_cast<int*>(ws + L.counters);
     s.H = D.H; s.Hk = D.Hk; s.Dh = D.Dh; s.S_max = D.S_max;
     s.scale = 1.0f / sqrtf((float)D.Dh);
-    s_attn = b.attn(s, Lw.k_cache, Lw.v_cache, shared);
+    b.attn_geometry(s);
+    b.push(s);
+    b.need_barrier(b.st.back());
   }
-  const int cph = b.st[s_attn].nsplit;
-  {  // o rank projection on the merged attention output
+  {  // 6. o rank projection
     Stage& s = b.gemv(Lw.o_v, nullptr, D.Ro, HD, HD, true, 0, -1, true);
-    b.vec(s, VL_ATTN, nullptr, HD, 1, s_attn);
-    s.part_acc = part_acc;
-    s.part_ml = part_ml;
-    s.nsplit = cph;
-    s.H = D.H; s.Dh = D.Dh;
+    b.vec(s, VL_SUM, attn, HD, 1, true);
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
     s.out = pb;
   }
-  const int s_orank = b.last(), segs6 = b.st.back().segs;
-  {  // o lift + residual
+  const int segs6 = b.st.back().segs;
+  {  // 7. o lift + residual
     Stage& s = b.gemv(Lw.o_u, nullptr, D.d, D.Ro, D.Ro, false);
-    b.vec(s, VL_SUM, pb, D.Ro, segs6, s_orank);
+    b.vec(s, VL_SUM, pb, D.Ro, segs6, true);
     s.epi = EPI_RESID;
     s.resid = io.x_in;
-    s.flags |= (io.x_in_stage >= 0 ? SF_RESID_TAG : SF_RESID_T) | SF_TAG_OUT;
+    s.flags |= SF_RESID_T | SF_OUT_T;
     s.out = mid;
   }
-  const int s_olift = b.last();
-  {  // MLP rank projection on the normalised hidden state: [p_up | p_gate]
+  {  // 8. MLP rank projection on the normalised hidden state: [p_up | p_gate]
     Stage& s = b.gemv(Lw.upgate_v, nullptr, D.Ru + D.Rg, D.d, D.d, true);
-    b.vec(s, VL_RMSNORM, mid, D.d, 1, s_olift);
+    b.vec(s, VL_RMSNORM, mid, D.d, 1, true);
+    s.flags |= SF_IN_T;
     s.vl_w = Lw.ln2_w;
     s.eps = D.eps;
     s.epi = EPI_PARTIAL;
     s.out = pa;
   }
-  const int s_mrank = b.last(), segs8 = b.st.back().segs;
-  {  // gate/up lift + SiLU·mul
+  const int segs8 = b.st.back().segs;
+  {  // 9. gate/up lift + SiLU·mul
     Stage& s = b.gemv(Lw.gate_u, Lw.up_u, D.I, D.Rg, D.Rg, false);
-    b.vec(s, VL_SUM, pa, D.Ru + D.Rg, segs8, s_mrank);
+    b.vec(s, VL_SUM, pa, D.Ru + D.Rg, segs8, true);
     s.xA_off = D.Ru;  // gate input follows the up input
     s.xB_off = 0;
     s.epi = EPI_SWIGLU;
-    s.flags |= SF_TAG_OUT;
+    s.flags |= SF_OUT_T;
     s.out = hact;
   }
-  const int s_gateup = b.last();
-  {  // down rank projection
+  {  // 10. down rank projection
     Stage& s = b.gemv(Lw.down_v, nullptr, D.Rd, D.I, D.I, true, 0, -1, true);
-    b.vec(s, VL_SUM, hact, D.I, 1, s_gateup);
+    b.vec(s, VL_SUM, hact, D.I, 1, true);
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
     s.out = pb;
   }
-  const int s_drank = b.last(), segs10 = b.st.back().segs;
-  {  // down lift + residual
+  const int segs10 = b.st.back().segs;
+  {  // 11. down lift + residual
     Stage& s = b.gemv(Lw.down_u, nullptr, D.d, D.Rd, D.Rd, false);
-    b.vec(s, VL_SUM, pb, D.Rd, segs10, s_drank);
+    b.vec(s, VL_SUM, pb, D.Rd, segs10, true);
     s.epi = EPI_RESID;
     s.resid = mid;
-    s.flags |= SF_RESID_TAG | (io.x_out_tagged ? SF_TAG_OUT : SF_OUT_T);
+    s.flags |= SF_RESID_T | SF_OUT_T;
     s.out = io.x_out;
   }
-  return b.last();
+  // a chunk of one sequence's prompt: every row uses cache row 0
+  if (D.rows_are_positions)
+    for (size_t i = first_stage; i < b.st.size(); ++i)
+      if (b.st[i].cache || b.st[i].kcache) b.st[i].flags |= SF_SHARED_CACHE;
 }
 
 static int check_layer_ptrs(const fsvd_layer& Lw) {
@@ -771,9 +644,8 @@ static int check_layer_ptrs(const fsvd_layer& Lw) {
 }
 
 // Shared-memory plan of a finished program: ring slots and total bytes.
-static int plan_smem(const Resolved& r, Builder& b, int& slots, size_t& smem) {
+static int plan_smem(const Resolved& r, const Builder& b, int& slots, size_t& smem) {
   if (b.err) return b.err;
-  b.check_order();
   slots = b.nslots(r.smem_optin);
   if (slots < 1)
     return fail(FSVD_ERR_UNSUPPORTED,
@@ -784,108 +656,93 @@ static int plan_smem(const Resolved& r, Builder& b, int& slots, size_t& smem) {
 }
 
 // ------------------------------------------------------------------------------- per-op launches
-// A by-value program ready to launch.  The per-op entry points keep the programs they built in a
-// small cache keyed by everything a program depends on (the op, its pointers and sizes, the
-// device, the launch settings), so that a decode loop that calls the same op with the same
-// buffers every token builds its stage list and TMA descriptors once.
+// Encodes the TMA descriptors a finished program asked for.
+static int encode_all(Builder& b) {
+  for (size_t i = 0; i < b.reqs.size(); ++i) {
+    const MapReq& q = b.reqs[i];
+    unsigned char* out = b.maps[i / 2].m[i & 1];
+    int e = 0;
+    if (q.kind == 1) e = encode_map(out, b.dtype, q.base, q.rows, q.cols, q.ldw);
+    else if (q.kind == 2) e = encode_map_q4(out, q.base, q.rows);
+    if (e) return e;
+  }
+  return 0;
+}
+
+// A by-value program ready to launch.  The per-op entry points keep the programs they launched in
+// a small cache keyed by the program itself (its stage list holds every pointer and size of the
+// call), the device and the launch settings, so that a decode loop that calls the same op with
+// the same buffers every token plans its shared memory and encodes its TMA descriptors once.
 struct SmallLaunch {
+  std::vector<Stage> key;   // the stage list the entry was built from
+  int device = -1;
+  unsigned generation = 0;
+  SyncState* sync = nullptr;
   SmallProgram sp;
   SmallMaps sm;
   LaunchArgs a;
   LaunchFn fn = nullptr;
 };
-struct CacheKey {
-  unsigned long long w[30];
-  int n = 0;
-  void add(unsigned long long v) {
-    if (n < 30) w[n++] = v;
-  }
-  void add(const void* p) { add((unsigned long long)reinterpret_cast<uintptr_t>(p)); }
-  bool operator==(const CacheKey& o) const { return n == o.n && memcmp(w, o.w, sizeof(unsigned long long) * n) == 0; }
-};
 constexpr int kLaunchCache = 64;
-struct CacheSlot {
-  bool used = false;
-  CacheKey key;
-  SmallLaunch* sl = nullptr;
-};
-static CacheSlot g_cache[kLaunchCache];
+static SmallLaunch* g_cache[kLaunchCache] = {nullptr};
 static int g_cache_next = 0;
 static std::mutex g_cache_mu;
 
-static CacheKey make_key(int op, const Resolved& r, int dtype, int B) {
-  CacheKey k;
-  k.add((unsigned long long)op);
-  k.add((unsigned long long)r.device);
-  k.add((unsigned long long)r.set.generation);
-  k.add((unsigned long long)dtype);
-  k.add((unsigned long long)B);
-  return k;
+static bool same_program(const SmallLaunch& c, const Resolved& r, const Builder& b, SyncState* sync) {
+  return c.device == r.device && c.generation == r.set.generation && c.sync == sync && c.fn == r.fn &&
+         c.key.size() == b.st.size() && memcmp(c.key.data(), b.st.data(), sizeof(Stage) * b.st.size()) == 0;
 }
 
-static int finish_small(const Resolved& r, Builder& b, SyncState* sync, SmallLaunch& sl) {
+static int launch_small(const Resolved& r, Builder& b, SyncState* sync, cudaStream_t stream) {
   if ((int)b.st.size() > kMaxSmallStages) return fail(FSVD_ERR_UNSUPPORTED, "program too long");
-  int slots = 0;
-  size_t smem = 0;
-  if (int e = plan_smem(r, b, slots, smem)) return e;
-  memset(&sl.sp, 0, sizeof(sl.sp));
-  memset(&sl.sm, 0, sizeof(sl.sm));
-  for (size_t i = 0; i < b.st.size(); ++i) {
-    sl.sp.st[i] = b.st[i];
-    memcpy(sl.sm.m[2 * i], b.maps[i].m[0], 128);
-    memcpy(sl.sm.m[2 * i + 1], b.maps[i].m[1], 128);
+  if (b.err) return b.err;
+  std::lock_guard<std::mutex> lock(g_cache_mu);
+  SmallLaunch* sl = nullptr;
+  for (SmallLaunch* c : g_cache)
+    if (c && same_program(*c, r, b, sync)) sl = c;
+  if (!sl) {
+    int slots = 0;
+    size_t smem = 0;
+    if (int e = plan_smem(r, b, slots, smem)) return e;
+    if (int e = encode_all(b)) return e;
+    sl = new SmallLaunch();
+    sl->key = b.st;
+    sl->device = r.device;
+    sl->generation = r.set.generation;
+    sl->sync = sync;
+    sl->fn = r.fn;
+    memset(&sl->sp, 0, sizeof(sl->sp));
+    memset(&sl->sm, 0, sizeof(sl->sm));
+    for (size_t i = 0; i < b.st.size(); ++i) {
+      sl->sp.st[i] = b.st[i];
+      memcpy(sl->sm.m[2 * i], b.maps[i].m[0], 128);
+      memcpy(sl->sm.m[2 * i + 1], b.maps[i].m[1], 128);
+    }
+    LaunchArgs& a = sl->a;
+    memset(&a, 0, sizeof(a));
+    a.nstages = (int)b.st.size();
+    a.sync = sync;
+    a.xstride = b.xstride();
+    a.part_bytes = b.part_bytes();
+    a.vec_bytes = b.vec_bytes();
+    a.nslots = slots;
+    a.slot_bytes = b.slot_bytes();
+    a.grid = r.grid;
+    a.smem = smem;
+    delete g_cache[g_cache_next];
+    g_cache[g_cache_next] = sl;
+    g_cache_next = (g_cache_next + 1) % kLaunchCache;
   }
-  LaunchArgs& a = sl.a;
-  memset(&a, 0, sizeof(a));
-  a.nstages = (int)b.st.size();
-  a.sync = sync;
-  a.xstride = b.xstride();
-  a.part_bytes = b.part_bytes();
-  a.vec_bytes = b.vec_bytes();
-  a.nslots = slots;
-  a.slot_bytes = b.slot_bytes();
-  a.grid = r.grid;
-  a.smem = smem;
-  sl.fn = r.fn;
-  return 0;
-}
-
-static int launch_small(const Resolved& r, SmallLaunch& sl, cudaStream_t stream) {
-  LaunchArgs a = sl.a;
-  a.small = &sl.sp;
-  a.small_maps = &sl.sm;
+  LaunchArgs a = sl->a;
+  a.small = &sl->sp;
+  a.small_maps = &sl->sm;
   a.trace = r.set.trace_bytes >= (size_t)a.nstages * (size_t)a.grid * 128 ? r.set.trace : nullptr;
   a.wait_limit = r.set.wait_limit;
-  a.tune = r.set.tune;
   a.stream = stream;
-  cudaError_t e = sl.fn(a);
+  cudaError_t e = sl->fn(a);
   if (e != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   g_launches.fetch_add(1);
   return 0;
-}
-
-// Looks the program of `key` up, or builds it with `build` (which appends the stages to a fresh
-// Builder and returns 0 or an error), then launches it.
-template <typename BuildFn>
-static int run_cached(const CacheKey& key, const Resolved& r, int dtype, int B, SyncState* sync,
-                      cudaStream_t stream, BuildFn build) {
-  std::lock_guard<std::mutex> lock(g_cache_mu);
-  for (CacheSlot& c : g_cache)
-    if (c.used && c.key == key) return launch_small(r, *c.sl, stream);
-  Builder b(r, dtype, B);
-  if (int e = build(b)) return e;
-  SmallLaunch* sl = new SmallLaunch();
-  if (int e = finish_small(r, b, sync, *sl)) {
-    delete sl;
-    return e;
-  }
-  CacheSlot& c = g_cache[g_cache_next];
-  g_cache_next = (g_cache_next + 1) % kLaunchCache;
-  delete c.sl;
-  c.used = true;
-  c.key = key;
-  c.sl = sl;
-  return launch_small(r, *sl, stream);
 }
 
 static void bump_generation() {   // call with g_set_mu held
@@ -898,14 +755,15 @@ static void build_lowrank(Builder& b, const void* x, const void* v, const void* 
                           int d_in, int R, int d_out, void* partial) {
   {
     Stage& s = b.gemv(v, nullptr, R, d_in, d_in, true, 0, -1, true);
-    b.vec(s, VL_SUM, x, d_in, 1, -1);
+    b.vec(s, VL_SUM, x, d_in, 1, false);
+    s.flags |= SF_IN_T;
     s.epi = EPI_PARTIAL;
     s.out = partial;
   }
-  const int s_rank = b.last(), segs = b.st.back().segs;
+  const int segs = b.st.back().segs;
   {
     Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
-    b.vec(s, VL_SUM, partial, R, segs, s_rank);
+    b.vec(s, VL_SUM, partial, R, segs, true);
     s.epi = residual ? EPI_RESID : EPI_STORE;
     s.resid = residual;
     s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
@@ -1020,14 +878,10 @@ int fsvd_lowrank_proj(const void* x, const void* v, const void* u, const void* r
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
   if (int e = resolve(dtype, B, r)) return e;
+  Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
-  CacheKey key = make_key(1, r, dtype, B);
-  key.add(x); key.add(v); key.add(u); key.add(residual); key.add(y); key.add(ws);
-  key.add((unsigned long long)d_in); key.add((unsigned long long)R); key.add((unsigned long long)d_out);
-  return run_cached(key, r, dtype, B, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream, [&](Builder& b) {
-    build_lowrank(b, x, v, u, residual, y, d_in, R, d_out, w + L.pb);
-    return 0;
-  });
+  build_lowrank(b, x, v, u, residual, y, d_in, R, d_out, w + L.pb);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
 int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B, int R, int d_out,
@@ -1042,19 +896,15 @@ int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
   if (int e = resolve(dtype, B, r)) return e;
+  Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
-  CacheKey key = make_key(2, r, dtype, B);
-  key.add(p); key.add(u); key.add(residual); key.add(y); key.add(ws);
-  key.add((unsigned long long)R); key.add((unsigned long long)d_out);
-  return run_cached(key, r, dtype, B, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream, [&](Builder& b) {
-    Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
-    b.vec(s, VL_SUM, p, R, 1, -1);
-    s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
-    s.epi = residual ? EPI_RESID : EPI_STORE;
-    s.resid = residual;
-    s.out = y;
-    return 0;
-  });
+  Stage& s = b.gemv(u, nullptr, d_out, R, R, false);
+  b.vec(s, VL_SUM, p, R, 1, false);
+  s.flags |= SF_IN_T | SF_OUT_T | (residual ? SF_RESID_T : 0);
+  s.epi = residual ? EPI_RESID : EPI_STORE;
+  s.resid = residual;
+  s.out = y;
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
 int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const void* upgate_v,
@@ -1077,52 +927,54 @@ int fsvd_mlp_swiglu_decode(const void* x, const void* norm_w, float eps, const v
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
   if (int e = resolve(dtype, B, r)) return e;
+  Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
-  CacheKey key = make_key(3, r, dtype, B);
-  key.add(x); key.add(norm_w); key.add((unsigned long long)fbits(eps)); key.add(upgate_v);
-  key.add(gate_u); key.add(up_u); key.add(down_v); key.add(down_u); key.add(residual); key.add(y); key.add(ws);
-  key.add((unsigned long long)d); key.add((unsigned long long)I); key.add((unsigned long long)Ru);
-  key.add((unsigned long long)Rd);
-  return run_cached(key, r, dtype, B, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream, [&](Builder& b) {
-    int s_rank = -1, segs_rank = 1;
-    if (upgate_v) {
-      Stage& s = b.gemv(upgate_v, nullptr, Ru + Rg, d, d, true);
-      b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, -1);
-      s.vl_w = norm_w;
-      s.eps = eps;
-      s.epi = EPI_PARTIAL;
-      s.out = w + L.pa;
-      segs_rank = s.segs;
-      s_rank = b.last();
+  int segs_rank = 1;
+  const void* pcat = x;
+  bool pcat_T = true;
+  if (upgate_v) {
+    Stage& s = b.gemv(upgate_v, nullptr, Ru + Rg, d, d, true);
+    b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, false);
+    s.flags |= SF_IN_T;
+    s.vl_w = norm_w;
+    s.eps = eps;
+    s.epi = EPI_PARTIAL;
+    s.out = w + L.pa;
+    segs_rank = s.segs;
+    pcat = w + L.pa;
+    pcat_T = false;
+  }
+  {
+    Stage& s = b.gemv(gate_u, up_u, I, Rg, Rg, false);
+    if (pcat_T) {
+      b.vec(s, VL_SUM, pcat, Ru + Rg, 1, false);
+      s.flags |= SF_IN_T;
+    } else {
+      b.vec(s, VL_SUM, pcat, Ru + Rg, segs_rank, true);
     }
-    {
-      Stage& s = b.gemv(gate_u, up_u, I, Rg, Rg, false);
-      if (s_rank >= 0) b.vec(s, VL_SUM, w + L.pa, Ru + Rg, segs_rank, s_rank);
-      else b.vec(s, VL_SUM, x, Ru + Rg, 1, -1);   // x is PCat
-      s.xA_off = Ru;
-      s.xB_off = 0;
-      s.epi = EPI_SWIGLU;
-      s.flags |= SF_TAG_OUT;
-      s.out = w + L.hact;
-    }
-    const int s_gateup = b.last();
-    {
-      Stage& s = b.gemv(down_v, nullptr, Rd, I, I, true, 0, -1, true);
-      b.vec(s, VL_SUM, w + L.hact, I, 1, s_gateup);
-      s.epi = EPI_PARTIAL;
-      s.out = w + L.pb;
-    }
-    const int s_drank = b.last(), segs = b.st.back().segs;
-    {
-      Stage& s = b.gemv(down_u, nullptr, d, Rd, Rd, false);
-      b.vec(s, VL_SUM, w + L.pb, Rd, segs, s_drank);
-      s.epi = residual ? EPI_RESID : EPI_STORE;
-      s.resid = residual;
-      s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
-      s.out = y;
-    }
-    return 0;
-  });
+    s.xA_off = Ru;
+    s.xB_off = 0;
+    s.epi = EPI_SWIGLU;
+    s.flags |= SF_OUT_T;
+    s.out = w + L.hact;
+  }
+  {
+    Stage& s = b.gemv(down_v, nullptr, Rd, I, I, true, 0, -1, true);
+    b.vec(s, VL_SUM, w + L.hact, I, 1, true);
+    s.flags |= SF_IN_T;
+    s.epi = EPI_PARTIAL;
+    s.out = w + L.pb;
+  }
+  const int segs = b.st.back().segs;
+  {
+    Stage& s = b.gemv(down_u, nullptr, d, Rd, Rd, false);
+    b.vec(s, VL_SUM, w + L.pb, Rd, segs, true);
+    s.epi = residual ? EPI_RESID : EPI_STORE;
+    s.resid = residual;
+    s.flags |= SF_OUT_T | (residual ? SF_RESID_T : 0);
+    s.out = y;
+  }
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
 int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const void* qkv_v,
@@ -1144,54 +996,47 @@ int fsvd_qkv_rope_append(const void* x, const void* norm_w, float eps, const voi
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
   if (int e = resolve(dtype, B, r)) return e;
+  Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
-  CacheKey key = make_key(4, r, dtype, B);
-  key.add(x); key.add(norm_w); key.add((unsigned long long)fbits(eps)); key.add(qkv_v); key.add(q_u);
-  key.add(k_u); key.add(v_u); key.add(cos_tab); key.add(sin_tab); key.add(k_cache); key.add(v_cache);
-  key.add(cache_seqlens); key.add(q_out); key.add(ws);
-  key.add(((unsigned long long)d << 32) | (unsigned)H); key.add(((unsigned long long)Hk << 32) | (unsigned)Dh);
-  key.add(((unsigned long long)Rq << 32) | (unsigned)Rk); key.add(((unsigned long long)Rv << 32) | (unsigned)S_max);
-  return run_cached(key, r, dtype, B, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream, [&](Builder& b) {
-    const int half = Dh / 2, Rqkv = Rq + Rk + Rv;
-    {
-      Stage& s = b.gemv(qkv_v, nullptr, Rqkv, d, d, true);
-      b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, -1);
-      s.vl_w = norm_w;
-      s.eps = eps;
-      s.epi = EPI_PARTIAL;
-      s.out = w + L.pa;
-    }
-    const int s_rank = b.last(), segs = b.st.back().segs;
-    auto head_fields = [&](Stage& s) {
-      s.cos_tab = cos_tab; s.sin_tab = sin_tab; s.seqlens = cache_seqlens;
-      s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
-    };
-    {
-      Stage& s = b.gemv(q_u, b.row_ptr(q_u, half, Rq), H * half, Rq, Rq, false, half);
-      b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, s_rank);
-      s.epi = EPI_ROPE_Q;
-      s.flags |= SF_OUT_T;
-      s.out = q_out;
-      head_fields(s);
-    }
-    {
-      Stage& s = b.gemv(k_u, b.row_ptr(k_u, half, Rk), Hk * half, Rk, Rk, false, half);
-      b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, s_rank);
-      s.xA_off = s.xB_off = Rq;
-      s.epi = EPI_ROPE_K;
-      s.cache = k_cache;
-      head_fields(s);
-    }
-    {
-      Stage& s = b.gemv(v_u, nullptr, Hk * Dh, Rv, Rv, false);
-      b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, s_rank);
-      s.xA_off = Rq + Rk;
-      s.epi = EPI_V;
-      s.cache = v_cache;
-      head_fields(s);
-    }
-    return 0;
-  });
+  const int half = Dh / 2, Rqkv = Rq + Rk + Rv;
+  {
+    Stage& s = b.gemv(qkv_v, nullptr, Rqkv, d, d, true);
+    b.vec(s, norm_w ? VL_RMSNORM : VL_SUM, x, d, 1, false);
+    s.flags |= SF_IN_T;
+    s.vl_w = norm_w;
+    s.eps = eps;
+    s.epi = EPI_PARTIAL;
+    s.out = w + L.pa;
+  }
+  const int segs = b.st.back().segs;
+  {
+    Stage& s = b.gemv(q_u, b.row_ptr(q_u, half, Rq), H * half, Rq, Rq, false, half);
+    b.vec(s, VL_SUM, w + L.pa, Rqkv, segs, true);
+    s.rope_half = half;
+    s.epi = EPI_ROPE_Q;
+    s.flags |= SF_OUT_T;
+    s.out = q_out;
+    s.cos_tab = cos_tab; s.sin_tab = sin_tab; s.seqlens = cache_seqlens;
+    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  }
+  {
+    Stage& s = b.gemv(k_u, b.row_ptr(k_u, half, Rk), Hk * half, Rk, Rk, false, half);
+    s.rope_half = half;
+    s.xA_off = s.xB_off = Rq;
+    s.epi = EPI_ROPE_K;
+    s.cache = k_cache;
+    s.cos_tab = cos_tab; s.sin_tab = sin_tab; s.seqlens = cache_seqlens;
+    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  }
+  {
+    Stage& s = b.gemv(v_u, nullptr, Hk * Dh, Rv, Rv, false);
+    s.xA_off = Rq + Rk;
+    s.epi = EPI_V;
+    s.cache = v_cache;
+    s.seqlens = cache_seqlens;
+    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  }
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
 int fsvd_flash_decode(const void* q, const void* k_cache, const void* v_cache,
@@ -1202,40 +1047,29 @@ int fsvd_flash_decode(const void* q, const void* k_cache, const void* v_cache,
   fsvd_dims D = op_dims(dtype, B);
   D.H = H; D.Hk = Hk; D.Dh = Dh; D.S_max = S_max;
   if (int e = check_dims(D)) return e;
-  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
-    return fail(FSVD_ERR_ALIGN, "pointers must be 16-byte aligned");
   WsLayout L;
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
   if (int e = resolve(dtype, B, r)) return e;
+  Builder b(r, dtype, B);
   char* w = reinterpret_cast<char*>(ws);
-  CacheKey key = make_key(5, r, dtype, B);
-  key.add(q); key.add(k_cache); key.add(v_cache); key.add(cache_seqlens); key.add(out); key.add(ws);
-  key.add((unsigned long long)(unsigned)seqlen_add); key.add(((unsigned long long)H << 32) | (unsigned)Hk);
-  key.add(((unsigned long long)Dh << 32) | (unsigned)S_max); key.add((unsigned long long)fbits(scale));
-  return run_cached(key, r, dtype, B, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream, [&](Builder& b) {
-    Stage s = b.blank();
-    s.flags = SF_IN_T;
-    s.q = q;
-    s.seqlens = cache_seqlens;
-    s.seqlen_add = seqlen_add;
-    s.part_acc = w + L.part_acc;
-    s.part_ml = w + L.part_ml;
-    s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
-    s.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)Dh);
-    const int s_attn = b.attn(s, k_cache, v_cache, false);
-    Stage m = b.blank();
-    m.type = ST_ATTN_OUT;
-    m.flags = SF_TAG_IN | SF_OUT_T;
-    m.in_stage = s_attn;
-    m.part_acc = w + L.part_acc;
-    m.part_ml = w + L.part_ml;
-    m.nsplit = b.st[s_attn].nsplit;
-    m.H = H; m.Dh = Dh;
-    m.out = out;
-    b.push(m);
-    return 0;
-  });
+  Stage s = b.blank();
+  s.type = ST_ATTN;
+  s.flags = SF_IN_T | SF_OUT_T;
+  s.q = q;
+  s.kcache = k_cache;
+  s.vcache = v_cache;
+  s.seqlens = cache_seqlens;
+  s.seqlen_add = seqlen_add;
+  s.out = out;
+  s.part_acc = reinterpret_cast<float*>(w + L.part_acc);
+  s.part_ml = reinterpret_cast<float*>(w + L.part_ml);
+  s.counters = reinterpret_cast<int*>(w + L.counters);
+  s.H = H; s.Hk = Hk; s.Dh = Dh; s.S_max = S_max;
+  s.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)Dh);
+  b.attn_geometry(s);
+  b.push(s);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream);
 }
 
 int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab,
@@ -1250,59 +1084,11 @@ int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void
   if (int e = check_ws(D, ws, ws_bytes, L)) return e;
   Resolved r;
   if (int e = resolve(D.dtype, D.B, r)) return e;
-  char* w = reinterpret_cast<char*>(ws);
-  CacheKey key = make_key(6, r, D.dtype, D.B);
-  const int di[] = {D.d, D.H, D.Hk, D.Dh, D.I, D.Rq, D.Rk, D.Rv, D.Ro, D.Rg, D.Ru, D.Rd, D.S_max, D.rows_are_positions};
-  unsigned long long h = 1469598103934665603ull;
-  for (int v : di) h = (h ^ (unsigned long long)(unsigned)v) * 1099511628211ull;
-  const void* const* lp = reinterpret_cast<const void* const*>(layer);
-  for (size_t i = 0; i < sizeof(fsvd_layer) / sizeof(void*); ++i)
-    h = (h ^ (unsigned long long)reinterpret_cast<uintptr_t>(lp[i])) * 1099511628211ull;
-  key.add(h);
-  key.add((unsigned long long)fbits(D.eps));
-  // the pointers that matter most are also kept verbatim, so that a hash collision cannot alias two layers
-  key.add(layer->qkv_v); key.add(layer->o_u); key.add(layer->gate_u); key.add(layer->down_u);
-  key.add(layer->k_cache); key.add(layer->v_cache);
-  key.add(cos_tab); key.add(sin_tab); key.add(cache_seqlens); key.add(x_in); key.add(x_out); key.add(ws);
-  key.add(((unsigned long long)D.d << 32) | (unsigned)D.I); key.add(((unsigned long long)D.Rq << 32) | (unsigned)D.Rd);
-  key.add(((unsigned long long)D.S_max << 32) | (unsigned)D.rows_are_positions);
-  return run_cached(key, r, D.dtype, D.B, reinterpret_cast<SyncState*>(w + L.sync), (cudaStream_t)stream,
-                    [&](Builder& b) {
-                      LayerIO io = {x_in, -1, x_out, false, cache_seqlens, cos_tab, sin_tab};
-                      build_layer(b, D, *layer, io, w, L);
-                      return 0;
-                    });
-}
-
-// A one-stage program whose input words nobody writes: its wait must run out within the wait
-// budget, leave DS_TAG_TIMEOUT in the workspace and end the launch by itself.
-int fsvd_selftest_wait_timeout(void* ws, size_t ws_bytes, void* stream) {
-  fsvd_dims D = op_dims(FSVD_DTYPE_F32, 1);
-  D.d = D.I = 64;
-  D.Ro = 64;
-  WsLayout L;
-  if (int e = check_ws(D, ws, ws_bytes, L)) return e;
-  Resolved r;
-  if (int e = resolve(FSVD_DTYPE_F32, 1, r)) return e;
-  char* w = reinterpret_cast<char*>(ws);
-  Builder b(r, FSVD_DTYPE_F32, 1);
-  {
-    // stage 0 does nothing and writes nothing; stage 1 waits for words of stage 0 in pa.  The
-    // "factor" is the workspace's own pb region (any readable memory will do: the result is unused).
-    Stage e = b.blank();
-    e.type = ST_ATTN_OUT;   // with B * H * Dh = 0 units: an empty stage
-    e.flags = SF_TAG_IN;
-    e.in_stage = 0;
-    e.H = 0; e.Dh = 64; e.B = 0; e.nsplit = 1;
-    b.push(e);
-    Stage& s = b.gemv(w + L.pb, nullptr, 16, 64, 64, false);
-    b.vec(s, VL_SUM, w + L.pa, 64, 1, 0);
-    s.epi = EPI_PARTIAL;
-    s.out = w + L.hact;
-  }
-  SmallLaunch sl;
-  if (int e = finish_small(r, b, reinterpret_cast<SyncState*>(w + L.sync), sl)) return e;
-  return launch_small(r, sl, (cudaStream_t)stream);
+  Builder b(r, D.dtype, D.B);
+  LayerIO io = {x_in, false, x_out, cache_seqlens, cos_tab, sin_tab};
+  build_layer(b, D, *layer, io, reinterpret_cast<char*>(ws), L);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(reinterpret_cast<char*>(ws) + L.sync),
+                      (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------- model
@@ -1313,15 +1099,14 @@ struct fsvd_model {
   char* ws = nullptr;
   Stage* prog = nullptr;
   unsigned char* maps = nullptr;   // TMA descriptors, 2 x 128 bytes per stage
-  int nstages = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0, nslots = 0, slot_bytes = 0;
-  int nbarriers = 0;
+  int nstages = 0, nbarriers = 0, xstride = 0, max_steps = 0, part_bytes = 0, vec_bytes = 0, nslots = 0, slot_bytes = 0;
   size_t smem = 0;
   int* tokens = nullptr;
   int* seqlens = nullptr;
   int* token_log = nullptr;
   int* step_counter = nullptr;
   float* logits = nullptr;
-  void* xbuf = nullptr;  // hidden state between layers, [B, d] tagged words
+  float* xbuf = nullptr;  // hidden state between layers, [B, d] of type T
   char* extra = nullptr;
 };
 
@@ -1349,15 +1134,12 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
 
   const size_t extra_bytes = al256((size_t)D.B * 4) * 2 + al256(4) + al256((size_t)max_steps * D.B * 4) +
                              al256((size_t)D.B * D.vocab * 4);
-  const size_t xbuf_bytes = al256((size_t)D.B * D.d * kWord);
   cudaError_t ce = cudaMalloc(&m->ws, m->L.total);
   if (ce == cudaSuccess) ce = cudaMalloc(&m->extra, extra_bytes);
-  if (ce == cudaSuccess) ce = cudaMalloc(&m->xbuf, xbuf_bytes);
   if (ce == cudaSuccess) ce = cudaMemset(m->ws, 0, m->L.total);
   if (ce == cudaSuccess) ce = cudaMemset(m->extra, 0, extra_bytes);
-  if (ce == cudaSuccess) ce = cudaMemset(m->xbuf, 0, xbuf_bytes);
   if (ce != cudaSuccess) {
-    fsvd_model_destroy(m);
+    cudaFree(m->ws); cudaFree(m->extra); delete m;
     return fail(FSVD_ERR_CUDA, "allocating model scratch failed: %s", cudaGetErrorString(ce));
   }
   size_t o = 0;
@@ -1368,29 +1150,35 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   m->logits = reinterpret_cast<float*>(m->extra + o);
 
   Builder b(m->r, D.dtype, D.B);
-  // The hidden state alternates between two buffers of tagged words: `hidden` of the workspace
-  // (between the halves of a layer) and `xbuf` (between layers), so a residual never reads what
-  // its own stage overwrites.
-  void* xbuf = m->xbuf;
+  float* hidden = reinterpret_cast<float*>(m->ws + m->L.hidden);
+  // The hidden state ping-pongs between two fp32 buffers: `hidden` (between the halves of a
+  // layer) and `xbuf` (between layers), so a residual never reads what its stage overwrites.
+  float* xbuf = nullptr;
+  ce = cudaMalloc(&xbuf, al256((size_t)D.B * D.d * 8));
+  if (ce == cudaSuccess) ce = cudaMemset(xbuf, 0, al256((size_t)D.B * D.d * 8));
+  if (ce != cudaSuccess) {
+    cudaFree(m->ws); cudaFree(m->extra); delete m;
+    return fail(FSVD_ERR_CUDA, "allocating model scratch failed: %s", cudaGetErrorString(ce));
+  }
   {
     Stage s = b.blank();
     s.type = ST_EMBED;
     s.WA = embed;
     s.P = D.d;
     s.out = xbuf;
-    s.flags = SF_TAG_OUT;
+    s.flags = SF_OUT_T;
     s.tokens = m->tokens;
     s.vocab = D.vocab;
     b.push(s);
   }
-  int x_stage = 0;
   for (int l = 0; l < D.n_layers; ++l) {
-    LayerIO io = {xbuf, x_stage, xbuf, true, m->seqlens, cos_tab, sin_tab};
-    x_stage = build_layer(b, D, layers[l], io, m->ws, m->L);
+    LayerIO io = {xbuf, true, xbuf, m->seqlens, cos_tab, sin_tab};
+    build_layer(b, D, layers[l], io, m->ws, m->L);
   }
   {
     Stage& s = b.gemv(lm_head, nullptr, D.vocab, D.d, D.d, false, 0, 0);   // lm_head stays dense
-    b.vec(s, VL_RMSNORM, xbuf, D.d, 1, x_stage);
+    b.vec(s, VL_RMSNORM, xbuf, D.d, 1, true);
+    s.flags |= SF_IN_T;
     s.vl_w = final_norm_w;
     s.eps = D.eps;
     s.epi = EPI_STORE;
@@ -1408,18 +1196,20 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
     s.seqlens_rw = m->seqlens;
     s.max_steps = max_steps;
     b.push(s);
-    b.need_barrier(b.last());   // the logits are a plain buffer
+    b.need_barrier(b.st.back());
   }
-  if (int e = plan_smem(m->r, b, m->nslots, m->smem)) {
-    fsvd_model_destroy(m);
-    return e;
+  int pe = plan_smem(m->r, b, m->nslots, m->smem);
+  if (!pe) pe = encode_all(b);
+  if (pe) {
+    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); delete m;
+    return pe;
   }
   m->nstages = (int)b.st.size();
+  for (const Stage& s : b.st) m->nbarriers += (s.flags & SF_BARRIER) ? 1 : 0;
   m->xstride = b.xstride();
   m->part_bytes = b.part_bytes();
   m->vec_bytes = b.vec_bytes();
   m->slot_bytes = b.slot_bytes();
-  for (const Stage& s : b.st) m->nbarriers += (s.flags & SF_BARRIER) ? 1 : 0;
   static_assert(sizeof(MapPair) == 256, "two descriptors per stage");
   ce = cudaMalloc(&m->prog, sizeof(Stage) * b.st.size());
   if (ce == cudaSuccess) ce = cudaMalloc(&m->maps, sizeof(MapPair) * b.maps.size());
@@ -1428,9 +1218,10 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   if (ce == cudaSuccess)
     ce = cudaMemcpy(m->maps, b.maps.data(), sizeof(MapPair) * b.maps.size(), cudaMemcpyHostToDevice);
   if (ce != cudaSuccess) {
-    fsvd_model_destroy(m);
+    cudaFree(m->ws); cudaFree(m->extra); cudaFree(xbuf); cudaFree(m->prog); cudaFree(m->maps); delete m;
     return fail(FSVD_ERR_CUDA, "uploading the stage program failed: %s", cudaGetErrorString(ce));
   }
+  m->xbuf = xbuf;
   *out = m;
   return 0;
 }
@@ -1449,7 +1240,7 @@ int fsvd_model_destroy(fsvd_model* m) {
 int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
   SyncState* sync = reinterpret_cast<SyncState*>(m->ws + m->L.sync);
-  const Settings set = current_settings();
+  const Settings set = current_settings();   // the geometry is the one of fsvd_model_create
   for (int i = 0; i < n_steps; ++i) {
     LaunchArgs a;
     memset(&a, 0, sizeof(a));
@@ -1464,7 +1255,6 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
     a.slot_bytes = m->slot_bytes;
     a.trace = set.trace_bytes >= (size_t)m->nstages * m->r.grid * 128 ? set.trace : nullptr;
     a.wait_limit = set.wait_limit;
-    a.tune = set.tune;
     a.grid = m->r.grid;
     a.smem = m->smem;
     a.stream = (cudaStream_t)stream;
@@ -1483,7 +1273,7 @@ int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_l
   if (token_log) *token_log = m->token_log;
   if (step_counter) *step_counter = m->step_counter;
   if (logits) *logits = m->logits;
-  if (hidden) *hidden = reinterpret_cast<float*>(m->xbuf);
+  if (hidden) *hidden = m->xbuf;
   return 0;
 }
 
@@ -1497,10 +1287,8 @@ int fsvd_model_status(fsvd_model* m, int* device_status) {
 
 int fsvd_model_reset_sync(fsvd_model* m, void* stream) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
-  // arrivals, status and the finished-CTA count; tag_base keeps counting
-  CUDA_TRY(cudaMemsetAsync(m->ws + m->L.sync + offsetof(SyncState, arrivals), 0, sizeof(unsigned long long),
-                           (cudaStream_t)stream));
-  CUDA_TRY(cudaMemsetAsync(m->ws + m->L.sync + offsetof(SyncState, status), 0, 4 * sizeof(int), (cudaStream_t)stream));
+  CUDA_TRY(cudaMemsetAsync(m->ws + m->L.sync, 0, sizeof(SyncState), (cudaStream_t)stream));
+  CUDA_TRY(cudaMemsetAsync(m->ws + m->L.counters, 0, kCounterBytes, (cudaStream_t)stream));
   return 0;
 }
 
@@ -1508,21 +1296,20 @@ int fsvd_model_reset_sync(fsvd_model* m, void* stream) {
 
 // ------------------------------------------------------------------------------- built-in scratch
 // fsvd_lowrank_proj_static: the low-rank projection on scratch that is part of the library
-// image instead of a caller-provided workspace.  The scratch holds the sync words and the
-// rank-space partial sums [segments][B][R] as tagged words; one array per device, shared by every
-// call.
+// image instead of a caller-provided workspace.  The scratch holds the grid-barrier words and the
+// rank-space partial sums [segments][B][R] in fp32; one array per device, shared by every call.
 constexpr int kStaticMaxBR = 8192;  // limit on B * R
 constexpr size_t kStaticSyncBytes = 256;
-constexpr size_t kStaticScratchBytes = kStaticSyncBytes + (size_t)kMaxSegs * kStaticMaxBR * kWord;
-static_assert(sizeof(SyncState) <= kStaticSyncBytes, "sync words must fit the scratch header");
+constexpr size_t kStaticScratchBytes = kStaticSyncBytes + (size_t)kMaxSegs * kStaticMaxBR * sizeof(float);
+static_assert(sizeof(SyncState) <= kStaticSyncBytes, "barrier words must fit the scratch header");
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 static void* g_static_ptr[16] = {nullptr};
 static std::mutex g_static_mu;
 
 // Device address of the scratch on the current device.  The first call on a device looks the
-// address up and clears the sync words (the only part that has to start at zero: the partial
-// sums are rewritten, with fresh tags, by every call).
+// address up and clears the barrier words (the only part that has to start at zero: the partial
+// sums are fully rewritten by every call, the barrier counters only ever grow).
 static int static_scratch(char** out, cudaStream_t stream) {
   int dev = 0;
   CUDA_TRY(cudaGetDevice(&dev));
@@ -1556,28 +1343,47 @@ extern "C" int fsvd_lowrank_proj_static(const void* x, const void* v, const void
                 (long long)B * R, kStaticMaxBR);
   char* w = nullptr;
   if (int e = static_scratch(&w, (cudaStream_t)stream)) return e;
-  CacheKey key = make_key(7, r, dtype, B);
-  key.add(x); key.add(v); key.add(u); key.add(residual); key.add(y);
-  key.add((unsigned long long)d_in); key.add((unsigned long long)R); key.add((unsigned long long)d_out);
-  return run_cached(key, r, dtype, B, reinterpret_cast<SyncState*>(w), (cudaStream_t)stream, [&](Builder& b) {
-    build_lowrank(b, x, v, u, residual, y, d_in, R, d_out, w + kStaticSyncBytes);
-    return 0;
-  });
+  float* partial = reinterpret_cast<float*>(w + kStaticSyncBytes);
+  Builder b(r, dtype, B);
+  build_lowrank(b, x, v, u, residual, y, d_in, R, d_out, partial);
+  if (b.st[0].segs > kMaxSegs) return fail(FSVD_ERR_UNSUPPORTED, "%d K segments exceed the built-in scratch", b.st[0].segs);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w), (cudaStream_t)stream);
 }
 
-// Blocking: copies the status word of the built-in scratch of the current device back and, when
-// `clear` is non-zero, clears it (cudaMemcpyFromSymbol / cudaMemcpyToSymbol: no allocation).
-extern "C" int fsvd_static_status(int* device_status, int clear) {
+// Waits for the stream's work on the built-in scratch, then reads its device status the way
+// fsvd_workspace_status does; `reset` != 0 also zeroes the barrier words and the status (after a
+// wait that ran out the arrival count of the abandoned launch is left behind).
+extern "C" int fsvd_static_status(int* device_status, int reset) {
   if (!device_status) return fail(FSVD_ERR_ARG, "null argument");
-  SyncState s;
-  CUDA_TRY(cudaMemcpyFromSymbol(&s, g_static_scratch, sizeof(s), 0, cudaMemcpyDeviceToHost));
-  *device_status = s.status;
-  if (s.status && clear) {
-    const int zero[2] = {0, 0};
-    CUDA_TRY(cudaMemcpyToSymbol(g_static_scratch, zero, sizeof(zero), offsetof(SyncState, status), cudaMemcpyHostToDevice));
+  char* w = nullptr;
+  if (int e = static_scratch(&w, nullptr)) return e;
+  CUDA_TRY(cudaDeviceSynchronize());
+  const int rc = fsvd_workspace_status(w, device_status);
+  if (reset) {
+    CUDA_TRY(cudaMemset(w, 0, kStaticSyncBytes));
   }
-  if (s.status) return fail(FSVD_ERR_DEVICE_WAIT, "device wait ran out: code %d at stage %d", s.status, s.status_detail);
-  return 0;
+  return rc;
+}
+
+// Launches a one-stage program whose stage stands behind a grid barrier that no stage arrives at:
+// every CTA waits, gives up after the wait budget (fsvd_set_wait_limit) and returns; the stage itself copies nothing.  The
+// launch returns 0; the status words then hold DS_BARRIER_TIMEOUT with stage index 0.  Used by the
+// tests to see a wait run out within its budget without anything hanging.
+extern "C" int fsvd_selftest_wait_timeout(void* ws, size_t ws_bytes, void* stream) {
+  if (!ws || ws_bytes < sizeof(SyncState)) return fail(FSVD_ERR_WORKSPACE, "workspace too small");
+  Resolved r;
+  if (int e = resolve(FSVD_DTYPE_BF16, 1, r)) return e;
+  r.set.trace = nullptr;
+  r.set.trace_bytes = 0;
+  Builder b(r, FSVD_DTYPE_BF16, 1);
+  char* w = reinterpret_cast<char*>(ws);
+  Stage s = b.blank();
+  s.type = ST_EMBED;
+  s.P = 0;   // zero elements to copy
+  s.vocab = 1;
+  s.flags = SF_OUT_T | SF_BARRIER;
+  b.push(s);
+  return launch_small(r, b, reinterpret_cast<SyncState*>(w), (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------- int4 tile streams

@@ -44,7 +44,7 @@ cudaError_t launch_impl(const LaunchArgs& a) {
   return cudaLaunchKernelEx(&cfg, kern, a.prog, a.small ? *a.small : empty_prog, a.maps,
                             a.small_maps ? *a.small_maps : empty_maps, a.small ? 1 : 0, a.nstages,
                             a.sync, a.xstride, a.part_bytes, a.vec_bytes, a.nslots, a.slot_bytes, a.trace,
-                            a.wait_limit, a.tune);
+                            a.wait_limit);
 }
 
 }  // namespace

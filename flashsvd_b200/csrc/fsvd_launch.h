@@ -15,7 +15,6 @@ struct LaunchArgs {
   int slot_bytes;                     // bytes of one ring slot: kBoxBytes, or kQ4BoxBytes with int4 stages
   unsigned long long* trace;
   long long wait_limit;               // budget of every device-side wait, in SM clocks
-  int tune;                           // bits 0-3 boxes in flight per producer lane (0 = ring depth), 4-7 poll pause / 32 ns, 8 sample gate
   int grid;
   size_t smem;
   cudaStream_t stream;

@@ -60,6 +60,11 @@ def set_launch_config(warps: int = 0, depth: int = 0, grid: int = 0) -> None:
     check(_lib.load().fsvd_set_launch_config(int(warps), int(depth), int(grid)))
 
 
+def set_wait_limit(sm_clocks: int) -> None:
+    """Budget of every device-side wait in SM clocks (see fsvd_set_wait_limit)."""
+    check(_lib.load().fsvd_set_wait_limit(int(sm_clocks)))
+
+
 def launch_count() -> int:
     return int(_lib.load().fsvd_launch_count())
 
@@ -81,6 +86,15 @@ class Workspace:
         st = C.c_int(0)
         check(_lib.load().fsvd_workspace_status(self.ptr, C.byref(st)))
         return int(st.value)
+
+    def raw_status(self) -> int:
+        """The status word itself (blocking), without the exception."""
+        st = C.c_int(0)
+        _lib.load().fsvd_workspace_status(self.ptr, C.byref(st))
+        return int(st.value)
+
+    def clear_status(self) -> None:
+        check(_lib.load().fsvd_workspace_clear_status(self.ptr, _stream()))
 
 
 def make_dims(*, dtype, B=1, d=8, H=1, Hk=1, Dh=64, I=8, Rq=8, Rk=8, Rv=8, Ro=8, Rg=8, Ru=8,

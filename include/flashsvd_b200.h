@@ -100,20 +100,21 @@ int fsvd_device_props(int* sm_count, int* smem_optin_bytes);
  * CTA); depth: slots of the shared-memory ring of 7 KB boxes (0 = as many as fit, at most
  * 21; rounded down to a multiple of 7); grid: number of CTAs (0 = one per SM).  Defaults come
  * from FSVD_SLOTS / FSVD_GRID or (0, 0).  The grid may be changed between launches on the same
- * workspace: no device-side word depends on it from one launch to the next. */
+ * workspace: every launch counts its grid barriers from zero.  A model keeps the geometry it
+ * was created with. */
 int fsvd_set_launch_config(int warps, int depth, int grid);
-/* Budget of every device-side wait (for tagged words of another CTA, a ring box, the grid
- * barrier) in SM clocks; default 4e9 (about 2 s) or FSVD_WAIT_CLOCKS.  A wait that runs out sets the status word and
- * the launch goes on without waiting again.  The reference has no counterpart (its kernels do
- * not wait for each other). */
+/* Budget of every device-side wait (at the grid barrier, for a ring box) in SM clocks; default
+ * 4e9 (about 2 s) or FSVD_WAIT_CLOCKS; at least 1000.  A wait that runs out sets the status word,
+ * and the CTA goes through the rest of the launch without waiting again.  The reference has no
+ * counterpart (its kernels do not wait for each other). */
 int fsvd_set_wait_limit(long long sm_clocks);
 
 /* Stage timeline for profiling (the analogue of the reference's per-module CUDA-event hooks,
  * utils/evaluator.py:553-689).  While a device buffer of at least nstages * grid * 128 bytes is
  * set, every launch records for each (stage, CTA) sixteen 8-byte slots of %globaltimer values:
- * 0 stage entry, 1 grid barrier passed, 2 input vector staged, 3 stage done, 4 vector words
- * arrived, 5 norm reduced, 7 factor boxes consumed, 8 plans made, 10 CTA synchronised,
- * 11 epilogue done.  NULL switches it off. */
+ * 0 stage entry, 1 grid barrier passed, 2 input vector staged, 3 stage done, 4 vector loaded,
+ * 5 norm reduced, 7 factor boxes consumed, 8 plans made, 10 CTA synchronised, 11 epilogue done.
+ * NULL switches it off. */
 int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes);
 
 /* ---- workspace -------------------------------------------------------------------------- */
@@ -121,16 +122,18 @@ int fsvd_set_trace_buffer(void* dev_ptr, size_t bytes);
  * fsvd_decode_layer; zero it once with fsvd_workspace_init before first use. */
 size_t fsvd_workspace_bytes(const fsvd_dims* dims);
 int fsvd_workspace_init(void* ws, size_t ws_bytes, void* stream);
-/* Blocking: copies the device status word back.  0 = nothing happened; 1 / 2 / 3 = a wait for
- * the grid barrier / a ring box / tagged words ran out (FSVD_ERR_DEVICE_WAIT); 4 = a token arrived
- * at a cache position >= S_max and its key / value were dropped (FSVD_ERR_CACHE_FULL; the
- * reference raises IndexError there, runtime/cache/attn_dense_kv.py:295-298). */
+/* Blocking: copies the device status word back.  0 = nothing happened; 1 / 2 = a wait at the
+ * grid barrier / for a ring box ran out (FSVD_ERR_DEVICE_WAIT, the message names the stage);
+ * 4 = a token arrived at a cache position >= S_max and its key / value were dropped
+ * (FSVD_ERR_CACHE_FULL; the reference raises IndexError there,
+ * runtime/cache/attn_dense_kv.py:295-298).  The first event wins. */
 int fsvd_workspace_status(void* ws, int* device_status);
 /* Clears the status word on `stream` (the rest of the workspace is left as it is). */
 int fsvd_workspace_clear_status(void* ws, void* stream);
-/* Self-test of the bounded waits: launches a two-stage program whose second stage waits for words
- * that nothing writes.  The launch ends by itself after the wait budget (fsvd_set_wait_limit) and
- * leaves status 3 with stage index 1; the workspace stays usable.  Nothing faults or hangs. */
+/* Self-test of the bounded waits: launches a one-stage program whose stage stands behind a grid
+ * barrier that nothing arrives at.  The launch ends by itself after the wait budget
+ * (fsvd_set_wait_limit) and leaves status 1 with stage index 0; the workspace stays usable (the
+ * barrier count is back at zero).  Nothing faults or hangs. */
 int fsvd_selftest_wait_timeout(void* ws, size_t ws_bytes, void* stream);
 
 /* ---- per-op entry points ------------------------------------------------------------------
@@ -150,10 +153,10 @@ int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B
 
 /* The same projection for callers that cannot hand over a workspace.  This entry point has no
  * counterpart in the reference.  Its scratch (sync words + rank-space partial sums) is a
- * fixed 512 KiB + 256 B array inside the library's device image, so the call performs no device
+ * fixed 256 KiB + 256 B array inside the library's device image, so the call performs no device
  * memory allocation or release of any kind (no cudaMalloc / cudaFree, no memory pool, no
- * allocating library call); on the host it uses ordinary heap for the stage list the first time a
- * given set of arguments is seen.  Meant for code that runs where device allocation is off limits
+ * allocating library call); on the host it uses ordinary heap for the stage list, and the first
+ * time a given set of arguments is seen, for the cached copy of the finished program.  Meant for code that runs where device allocation is off limits
  * or unaffordable: a serving loop whose memory is fully budgeted up front, a real-time thread that
  * must not take the allocator's locks, or a plug-in that is handed tensors but no allocator.
  *  - Limit: B * R <= 8192 (for example B = 1 with R up to 8192, or B = 8 with R up to 1024);
@@ -164,15 +167,16 @@ int fsvd_lift(const void* p, const void* u, const void* residual, void* y, int B
  *  - One array per device is shared by every call: calls must be ordered one after another
  *    (same stream, or events between streams).  Two calls that overlap in time race on the
  *    partial sums and give undefined results.
- *  - fsvd_static_status reads (and optionally clears) the bounded-wait status word of the array.
+ *  - fsvd_static_status reads (and optionally resets) the status word of the array.
  * Both entry points build their stages with the same routine (same K segments, same summation
  * order), so the results are bitwise identical to fsvd_lowrank_proj with the same launch
  * configuration. */
 int fsvd_lowrank_proj_static(const void* x, const void* v, const void* u, const void* residual,
                              void* y, int B, int d_in, int R, int d_out, int dtype, void* stream);
-/* Blocking: status word of the built-in scratch of the current device (see fsvd_workspace_status
- * for the codes); clear != 0 also clears it.  Allocates nothing. */
-int fsvd_static_status(int* device_status, int clear);
+/* Blocking (synchronises the device): status word of the built-in scratch of the current device
+ * (see fsvd_workspace_status for the codes and the return value); reset != 0 also zeroes the
+ * status and the barrier words.  Allocates nothing. */
+int fsvd_static_status(int* device_status, int reset);
 
 /* y[B,d] = (residual +) down_u(down_v(silu(gate_u(p_gate)) * up_u(p_up))).
  * With upgate_v != NULL: x is the hidden state [B,d], optionally RMS-normalised by norm_w, and
@@ -233,16 +237,17 @@ int fsvd_model_destroy(fsvd_model* m);
 int fsvd_model_step(fsvd_model* m, int n_steps, void* stream);
 /* Device buffers: tokens[B] (in: token to feed, out: sampled token), seqlens[B],
  * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32; `hidden` is the library's internal
- * hidden-state buffer between layers ([B,d] 8-byte words {fp32 value, tag}), exposed for debugging. */
+ * hidden-state buffer between layers ([B,d] in the model dtype), exposed for debugging. */
 int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
                        int** step_counter, float** logits, float** hidden);
 /* Number of stages of the model's program (sizes the trace buffer). */
 int fsvd_model_num_stages(fsvd_model* m);
-/* Grid barriers per launch of the model's program (1: in front of the argmax). */
+/* Grid barriers per launch of the model's program (one in front of every stage that reads what
+ * the stage before it wrote: 9 per layer + 2). */
 int fsvd_model_num_barriers(fsvd_model* m);
-/* Blocking: 0 when no device-side wait ran out since the last reset. */
+/* Blocking: as fsvd_workspace_status, for the model's own scratch. */
 int fsvd_model_status(fsvd_model* m, int* device_status);
-/* Clears the status and the barrier count after an error. */
+/* Clears the status, the barrier words and the attention arrival counters after an error. */
 int fsvd_model_reset_sync(fsvd_model* m, void* stream);
 /* int4 factors: src/quant/packed_quant_linear.py:18-35 (format), :126-171 (pack_weight), :285-300
  * (dequantize: w = scale * (q - zero), groups of 128 along the input dimension).  The reference
