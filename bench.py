@@ -39,7 +39,7 @@ CTX = 512
 # named here (a 4-layer launch of the same program; traffic grows with the layer count in
 # proportion to the algorithmic bytes).  Reported as an estimate with its source, not as a
 # measurement of the run that prints it.
-NCU_TRAFFIC_RATIO = 1.003
+NCU_TRAFFIC_RATIO = 1.005
 NCU_TRAFFIC_SOURCE = "profiles/fsvd_decode_kernel_model_4layers_ncu_full.md"
 
 
@@ -169,7 +169,7 @@ def run_reference(args, rank):
 
 
 def time_workload(dev, *, shape_name, layers, batch, ctx, share_pairs, factors, steps, warm, seed, world=1,
-                  clocks_index=None, e2e=True, parity_steps=0):
+                  clocks_index=None, e2e=True, parity_steps=0, profile_range=False):
     """Builds one engine and times it: K kernel-only steps with everything resident, then (e2e)
     K steps in which the host feeds every token from pinned memory and reads every sampled token
     back.  Returns a dict of raw measurements (times are this rank's)."""
@@ -191,6 +191,8 @@ def time_workload(dev, *, shape_name, layers, batch, ctx, share_pairs, factors, 
             dist.barrier()
         torch.cuda.synchronize()
 
+    if profile_range:
+        torch.cuda.profiler.start()   # profiler range = warm-up + timed regions (ncu --profile-from-start off)
     launches0 = ops.launch_count()
     eng.step(warm)
     barrier()
@@ -227,6 +229,8 @@ def time_workload(dev, *, shape_name, layers, batch, ctx, share_pairs, factors, 
         barrier()
         ms_e2e = e2.elapsed_time(e3)
 
+    if profile_range:
+        torch.cuda.profiler.stop()
     parity = None
     if parity_steps > 0:
         # the timed engine itself, stepped beside the CPU oracle from its current state (outside
@@ -314,15 +318,16 @@ def main():
     headline = (args.shape == "7b" and layers == 32 and B == 1 and ctx0 == CTX and not args.share_pairs
                 and args.factors == "bf16")
     do_parity = headline and world == 1 and not args.no_parity_check
-    torch.cuda.profiler.start()   # profiler range = warm-up + timed regions (ncu --profile-from-start off)
     r = time_workload(dev, shape_name=args.shape, layers=layers, batch=B, ctx=ctx0, share_pairs=args.share_pairs,
                       factors=args.factors, steps=args.steps, warm=warm, seed=rank, world=world,
-                      clocks_index=local if rank == 0 else None, e2e=True, parity_steps=4 if do_parity else 0)
-    torch.cuda.profiler.stop()
+                      clocks_index=local if rank == 0 else None, e2e=True, parity_steps=4 if do_parity else 0,
+                      profile_range=True)
 
     times = torch.tensor([r["ms"], r["ms_e2e"]], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    # independent sequences: every rank decodes its own B sequences on a full replica of the factors,
+    # the ranks meet only here (max of the step times); no data-path collective
+    from flashsvd_b200 import partition
+    partition.max_over_ranks(times)
     ms, ms_e2e = float(times[0]), float(times[1])
     r["ms"] = ms
 
@@ -334,7 +339,7 @@ def main():
                                   f"launch, {NCU_TRAFFIC_SOURCE})") if headline else None
         line = {
             "metric": METRIC if headline else METRIC + " [secondary workload, see config.workload]",
-            "value": world * B * args.steps / (ms * 1e-3),
+            "value": partition.aggregate_tokens_per_s([B * args.steps] * world, [ms] * world),
             "unit": "tokens/s",
             "n_gpus": world,
             "steps": args.steps,

@@ -1,8 +1,8 @@
 """Generates tests/golden/*.npz by running what can be run of the reference, and checks the oracle
-against it while doing so.  Needs the reference checkout (default /root/reference) and
+against it while doing so.  Needs a FlashSVD checkout (--reference or $FLASHSVD_REFERENCE) and
 transformers; run once in the build container:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <FlashSVD checkout>
 
 What is taken from the reference / its dependencies (nothing of it is copied into this repo):
   * utils/evaluator.py:_manual_llama_decode_step           the per-token decode loop
@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import argparse
 import math
+import os
 import sys
 from pathlib import Path
 
@@ -147,7 +148,8 @@ def reference_greedy(ref_root: Path, shape: O.Shape, weights: dict, prompt: torc
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("FLASHSVD_REFERENCE"), required="FLASHSVD_REFERENCE" not in os.environ,
+                    help="root of a FlashSVD checkout (or set FLASHSVD_REFERENCE)")
     args = ap.parse_args()
     ref = Path(args.reference)
     report = []
@@ -259,7 +261,6 @@ def main():
     # 5. host surface: configure_runtime environments and a dense-cache scenario, for the mirror
     #    in flashsvd_b200/runtime.py
     import json
-    import os
 
     from scripts.demo_support import api
 
