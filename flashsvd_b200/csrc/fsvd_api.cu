@@ -13,6 +13,7 @@
 
 #include "../../include/flashsvd_b200.h"
 #include "fsvd_stage.h"
+#include "fsvd_tile.h"
 
 using namespace fsvd;
 
@@ -28,6 +29,11 @@ static int fail(int code, const char* fmt, ...) {
   va_end(ap);
   return code;
 }
+// hooks for the tiled path (fsvd_tile.cu): same error text, same launch counter
+void fsvd_tile_set_error(int, const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+void fsvd_tile_count_launch() { g_launches.fetch_add(1); }
+void fsvd_tile_count_launches(long long n) { g_launches.fetch_add(n); }
+long long fsvd_tile_launches() { return g_launches.load(); }
 #define CUDA_TRY(expr)                                                                   \
   do {                                                                                   \
     cudaError_t e_ = (expr);                                                             \
@@ -815,6 +821,7 @@ int fsvd_set_wait_limit(long long sm_clocks) {
 
 size_t fsvd_workspace_bytes(const fsvd_dims* dims) {
   if (!dims) return 0;
+  if (dims->B > 8) return fsvd_tile_workspace_bytes(dims);   // tiled tensor-core path
   return ws_layout(*dims).total;
 }
 
@@ -1078,6 +1085,13 @@ int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void
   if (!dims || !layer || !cos_tab || !sin_tab || !cache_seqlens || !x_in || !x_out)
     return fail(FSVD_ERR_ARG, "null argument");
   const fsvd_dims& D = *dims;
+  if (D.B > 8) {
+    // batches of 9..128 sequences: tiled GEMMs on tcgen05 (fsvd_tile.cu), several launches
+    if (int e = check_layer_ptrs(*layer)) return e;
+    if (!aligned16(ws)) return fail(FSVD_ERR_ALIGN, "workspace is not 16-byte aligned");
+    return fsvd_tile_decode_layer(dims, layer, cos_tab, sin_tab, cache_seqlens, x_in, x_out, ws, ws_bytes,
+                                  current_settings().wait_limit, stream);
+  }
   if (int e = check_dims(D)) return e;
   if (int e = check_layer_ptrs(*layer)) return e;
   WsLayout L;
@@ -1108,6 +1122,7 @@ struct fsvd_model {
   float* logits = nullptr;
   float* xbuf = nullptr;  // hidden state between layers, [B, d] of type T
   char* extra = nullptr;
+  fsvd_tile_model* tile = nullptr;   // batches above 8: the tiled path owns everything
 };
 
 int fsvd_model_destroy(fsvd_model* m);
@@ -1118,6 +1133,22 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   if (!dims || !layers || !embed || !final_norm_w || !lm_head || !cos_tab || !sin_tab || !out)
     return fail(FSVD_ERR_ARG, "null argument");
   const fsvd_dims& D = *dims;
+  if (D.B > 8) {
+    for (int l = 0; l < D.n_layers; ++l)
+      if (int e = check_layer_ptrs(layers[l])) return e;
+    if (!aligned16(embed) || !aligned16(lm_head) || !aligned16(final_norm_w))
+      return fail(FSVD_ERR_ALIGN, "embed / lm_head / norm pointers must be 16-byte aligned");
+    fsvd_tile_model* t = nullptr;
+    if (int e = fsvd_tile_model_create(dims, layers, embed, final_norm_w, lm_head, cos_tab, sin_tab, max_steps,
+                                       current_settings().wait_limit, &t))
+      return e;
+    fsvd_model* m = new fsvd_model();
+    m->D = D;
+    m->tile = t;
+    m->max_steps = max_steps;
+    *out = m;
+    return 0;
+  }
   if (int e = check_dims(D)) return e;
   if (D.n_layers < 1 || D.vocab < 1) return fail(FSVD_ERR_ARG, "n_layers=%d vocab=%d", D.n_layers, D.vocab);
   for (int l = 0; l < D.n_layers; ++l)
@@ -1228,6 +1259,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
 
 int fsvd_model_destroy(fsvd_model* m) {
   if (!m) return 0;
+  if (m->tile) fsvd_tile_model_destroy(m->tile);
   cudaFree(m->ws);
   cudaFree(m->extra);
   cudaFree(m->prog);
@@ -1239,6 +1271,7 @@ int fsvd_model_destroy(fsvd_model* m) {
 
 int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
+  if (m->tile) return fsvd_tile_model_step(m->tile, n_steps, stream);
   SyncState* sync = reinterpret_cast<SyncState*>(m->ws + m->L.sync);
   const Settings set = current_settings();   // the geometry is the one of fsvd_model_create
   for (int i = 0; i < n_steps; ++i) {
@@ -1268,6 +1301,10 @@ int fsvd_model_step(fsvd_model* m, int n_steps, void* stream) {
 int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
                        int** step_counter, float** logits, float** hidden) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
+  if (m->tile) {
+    fsvd_tile_model_buffers(m->tile, tokens, seqlens, token_log, step_counter, logits, hidden);
+    return 0;
+  }
   if (tokens) *tokens = m->tokens;
   if (seqlens) *seqlens = m->seqlens;
   if (token_log) *token_log = m->token_log;
@@ -1277,16 +1314,17 @@ int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_l
   return 0;
 }
 
-int fsvd_model_num_stages(fsvd_model* m) { return m ? m->nstages : 0; }
-int fsvd_model_num_barriers(fsvd_model* m) { return m ? m->nbarriers : 0; }
+int fsvd_model_num_stages(fsvd_model* m) { return !m ? 0 : m->tile ? fsvd_tile_model_launches_per_step(m->tile) : m->nstages; }
+int fsvd_model_num_barriers(fsvd_model* m) { return (m && !m->tile) ? m->nbarriers : 0; }
 
 int fsvd_model_status(fsvd_model* m, int* device_status) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
-  return fsvd_workspace_status(m->ws, device_status);
+  return fsvd_workspace_status(m->tile ? fsvd_tile_model_ws(m->tile) : m->ws, device_status);
 }
 
 int fsvd_model_reset_sync(fsvd_model* m, void* stream) {
   if (!m) return fail(FSVD_ERR_ARG, "null model");
+  if (m->tile) return fsvd_tile_model_reset(m->tile, stream);
   CUDA_TRY(cudaMemsetAsync(m->ws + m->L.sync, 0, sizeof(SyncState), (cudaStream_t)stream));
   CUDA_TRY(cudaMemsetAsync(m->ws + m->L.counters, 0, kCounterBytes, (cudaStream_t)stream));
   return 0;

@@ -1,0 +1,1219 @@
+// Decode for batches of 9..128 sequences (bf16): the factor products as tiled GEMMs on the 5th
+// generation tensor cores.
+//
+// With more than 8 activation rows per factor row the 16 x 8 register tiles of the persistent
+// interpreter (fsvd_kernel.cuh) no longer fit the batch; here a factor product is
+//     D[128 factor rows, N batch columns] = W[128, K] . X[N, K]^T        (N = batch rounded up to 16)
+// issued as tcgen05.mma (cta_group::1, kind::f16, M = 128) by one thread per CTA, with both operands
+// read from shared memory (128-byte swizzled, K-major, filled by TMA) and the fp32 accumulator in
+// tensor memory.  The work is still bound by the factor stream from HBM (each factor byte is used
+// for N <= 128 multiply-adds), so the kernel is organised around keeping TMA busy:
+//   * one CTA = one tile of 128 factor rows x one K segment; the segments of a tile are summed in
+//     segment order by the CTA that finishes last (arrival counter per tile), which also runs the
+//     epilogue, so the result does not depend on the order in which CTAs run;
+//   * a ring of NS stages {W tile 16 KB, (second W tile), X tile(s)}: thread 0 issues the TMA copies
+//     as slots free up, thread 32 issues the MMAs as slots fill and releases a slot with
+//     tcgen05.commit, all four warps read the accumulator back with tcgen05.ld for the epilogue;
+//   * epilogues: store / residual / SwiGLU (two accumulators) / RoPE + q buffer / RoPE + key cache /
+//     value cache, with the rounding points of the PyTorch low-rank path (every nn.Linear output
+//     rounded to bf16), the same as the interpreter's.
+// A decoder layer is 13 launches on the caller's stream (2 RMSNorm, 9 GEMMs over its 13 factors,
+// attention, and the split merge inside the kernels); a model step is captured once into a CUDA graph.
+//
+// Reference functions replaced: kernels/mlp/decode/dual_split_triton_pcat_s.py:39-120 (token-tiled
+// SwiGLU MLP), kernels/attn/decode/densekv_reconstruct_triton.py:464-760 (q/k/v lift),
+// runtime/attn/decode_registry.py:177-211 (rotary + append + attention), for batches > 8.
+//
+// Every wait in these kernels is bounded (clock64 budget); a wait that runs out sets the status word,
+// the CTA frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
+#include "../../include/flashsvd_b200.h"
+#include "fsvd_stage.h"
+#include "fsvd_tile.h"
+
+namespace fsvd_tile {
+
+using fsvd::DS_BARRIER_TIMEOUT;
+using fsvd::DS_CACHE_FULL;
+using fsvd::DS_COPY_TIMEOUT;
+using fsvd::DS_OK;
+using fsvd::SyncState;
+
+constexpr int kTileM = 128;          // factor rows of a tile (UMMA M)
+constexpr int kTileK = 64;           // bf16 elements of a k-block: one 128-byte swizzle span
+constexpr int kThreads = 128;        // 4 warps: warp w reads accumulator lanes 32 w .. 32 w + 31
+constexpr int kWTileBytes = kTileM * kTileK * 2;   // 16 KB
+constexpr int kMaxStages = 8;
+constexpr int kMaxSegs = 16;
+
+enum TileEpi : int {
+  TE_STORE = 0,      // out[b, p] = rnd(acc)                        (bf16)
+  TE_STORE_F32 = 1,  // out[b, p] = rnd(acc) kept in an fp32 container (logits)
+  TE_RESID = 2,      // out[b, p] = rnd(resid[b, p] + rnd(acc))
+  TE_SWIGLU = 3,     // out[b, p] = rnd(rnd(silu(rnd(accA))) * rnd(accB))      A = gate, B = up
+  TE_ROPE_Q = 4,     // rotate the head's (j, j + Dh/2) pair at position seqlens[b], store to out[b, p]
+  TE_ROPE_K = 5,     // same rotation, store into the key cache at position seqlens[b]
+  TE_VCACHE = 6,     // store rnd(acc) into the value cache at position seqlens[b]
+};
+
+struct GemmArgs {
+  int P, K, B, N;          // factor rows, reduction length, batch rows, batch rounded up to 16
+  int tiles, segs, kbs;    // row tiles, K segments, k-blocks per segment
+  int nkb;                 // k-blocks in all
+  int nstages, two, epi;
+  uint32_t tmem_cols;      // power of two >= 32
+  float* scratch;          // [segs][tiles][nacc][N][128] fp32 partial tiles (segs > 1)
+  int* counters;           // [tiles], zero between launches
+  void* out;
+  const void* resid;
+  void* cache;             // TE_ROPE_K / TE_VCACHE: [rows, S_max, Hk, Dh]
+  const void* cos_tab;
+  const void* sin_tab;
+  const int* seqlens;
+  int Dh, HkDh, S_max, shared_cache;
+  int* status;             // SyncState::status of the workspace
+  long long wait_limit;
+};
+
+// ------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int col, int row, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(col), "r"(row), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_alloc(uint32_t slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem]^T, one 128 x N x 16 step
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// the mbarrier gets one arrival when every MMA issued so far by this thread has finished
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 16 consecutive accumulator columns of this thread's lane
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle (the layout a
+// TMA box of 64 columns with CU_TENSOR_MAP_SWIZZLE_128B leaves): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N.
+__device__ __forceinline__ uint32_t umma_idesc(int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+__device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float ldbf(const void* p, size_t i) {
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void stbf(void* p, size_t i, float v) {
+  reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// Bounded mbarrier wait; false when the budget ran out or the CTA has given up already.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* giveup, const GemmArgs& a, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*giveup) return false;
+  const long long c0 = clock64();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*giveup) return false;
+      if (clock64() - c0 > a.wait_limit) {
+        atomicCAS(a.status, (int)DS_OK, code);
+        *giveup = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------- GEMM kernel
+// grid = (tiles, segs).  Dynamic shared memory: [1 KB slack for alignment][NS stages].
+__global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                             const __grid_constant__ CUtensorMap mapA2,
+                                                             const __grid_constant__ CUtensorMap mapX,
+                                                             const __grid_constant__ CUtensorMap mapX2,
+                                                             const GemmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + 1];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int giveup_sh;
+  __shared__ int last_sh;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, seg = blockIdx.y;
+  const int N = a.N, NS = a.nstages;
+  const uint32_t xbytes = (uint32_t)N * 128u;
+  const uint32_t stage_bytes = (uint32_t)kWTileBytes * (a.two ? 2u : 1u) + xbytes * (a.two ? 2u : 1u);
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]), accum = smem_u32(&bars[2 * kMaxStages]);
+  volatile int* giveup = &giveup_sh;
+
+  if (tid == 0) {
+    giveup_sh = 0;
+    last_sh = 0;
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(empty0 + 8 * i, 1);
+    }
+    mbar_init(accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tc_alloc(smem_u32(&tmem_slot), a.tmem_cols);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  const int kb0 = seg * a.kbs, kb1 = min(a.nkb, kb0 + a.kbs);
+  const int nit = kb1 - kb0;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: TMA copies of the stage operands
+      for (int it = 0; it < nit; ++it) {
+        const int s = it % NS, round = it / NS;
+        if (round > 0 && !wait_bar(empty0 + 8 * s, (uint32_t)(round - 1) & 1u, giveup, a, DS_COPY_TIMEOUT)) break;
+        const uint32_t fb = full0 + 8 * s;
+        uint32_t dst = base + (uint32_t)s * stage_bytes;
+        const int kcol = (kb0 + it) * kTileK;
+        mbar_expect_tx(fb, stage_bytes);
+        tma_box_2d(dst, &mapA, kcol, tile * kTileM, fb);
+        dst += kWTileBytes;
+        if (a.two) {
+          tma_box_2d(dst, &mapA2, kcol, tile * kTileM, fb);
+          dst += kWTileBytes;
+        }
+        tma_box_2d(dst, &mapX, kcol, 0, fb);
+        if (a.two) tma_box_2d(dst + xbytes, &mapX2, kcol, 0, fb);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issue: four 16-deep steps per k-block and accumulator
+      const uint32_t idesc = umma_idesc(N);
+      bool ok = true;
+      for (int it = 0; it < nit && ok; ++it) {
+        const int s = it % NS, round = it / NS;
+        ok = wait_bar(full0 + 8 * s, (uint32_t)round & 1u, giveup, a, DS_COPY_TIMEOUT);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = base + (uint32_t)s * stage_bytes;
+        const uint32_t sx = sa + (uint32_t)kWTileBytes * (a.two ? 2u : 1u);
+        const uint64_t da = umma_desc(sa), dx = umma_desc(sx);
+#pragma unroll
+        for (int kk = 0; kk < kTileK / 16; ++kk)
+          tc_mma(tmem, da + 2u * kk, dx + 2u * kk, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        if (a.two) {
+          const uint64_t da2 = umma_desc(sa + kWTileBytes), dx2 = umma_desc(sx + xbytes);
+#pragma unroll
+          for (int kk = 0; kk < kTileK / 16; ++kk)
+            tc_mma(tmem + (uint32_t)N, da2 + 2u * kk, dx2 + 2u * kk, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(empty0 + 8 * s);   // the slot is free when these MMAs have read it
+      }
+      if (ok) tc_commit(accum);      // the accumulators are complete
+    }
+    __syncwarp();
+  }
+
+  // ---- everybody: wait for the accumulators
+  bool have = nit > 0 ? wait_bar(accum, 0u, giveup, a, DS_BARRIER_TIMEOUT) : false;
+  have = __all_sync(0xffffffffu, have);
+  tc_fence_after();
+
+  const int r = tid;                       // accumulator lane = row of the tile
+  const int p = tile * kTileM + r;         // factor row
+  const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+  const int nacc = a.two ? 2 : 1;
+  const bool rope = a.epi == TE_ROPE_Q || a.epi == TE_ROPE_K;
+  float* ftile = reinterpret_cast<float*>(base_ptr);   // [N][128] fp32, reuses the ring (RoPE epilogues)
+
+  bool last = true;
+  if (a.segs > 1) {
+    // partial tile to the scratch, then the arrival count of the tile decides who finishes it
+    if (have) {
+      for (int acc = 0; acc < nacc; ++acc) {
+        float* dst = a.scratch + (((size_t)seg * a.tiles + tile) * nacc + acc) * (size_t)(N * kTileM);
+        for (int c0 = 0; c0 < N; c0 += 16) {
+          float v[16];
+          tc_ld16(trow + (uint32_t)(acc * N + c0), v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) dst[(size_t)(c0 + i) * kTileM + r] = v[i];
+        }
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int old = atomicAdd(&a.counters[tile], 1);
+      last_sh = (old == a.segs - 1) ? 1 : 0;
+      if (old == a.segs - 1) a.counters[tile] = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    last = last_sh != 0;
+    if (last) __threadfence();
+  }
+
+  if (last && (have || a.segs > 1) && !*giveup) {
+    for (int c0 = 0; c0 < N; c0 += 16) {
+      float v[16], u[16];
+      if (a.segs > 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = u[i] = 0.0f;
+        for (int sg = 0; sg < a.segs; ++sg) {
+          const float* src = a.scratch + (((size_t)sg * a.tiles + tile) * nacc) * (size_t)(N * kTileM);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + (size_t)(c0 + i) * kTileM + r);
+          if (a.two) {
+            src += (size_t)(N * kTileM);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) u[i] += __ldcg(src + (size_t)(c0 + i) * kTileM + r);
+          }
+        }
+      } else {
+        tc_ld16(trow + (uint32_t)c0, v);
+        if (a.two) tc_ld16(trow + (uint32_t)(N + c0), u);
+      }
+      if (rope) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ftile[(size_t)(c0 + i) * kTileM + r] = v[i];
+        continue;
+      }
+      if (p >= a.P) continue;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int b = c0 + i;
+        if (b >= a.B) break;
+        const size_t o = (size_t)b * a.P + p;
+        switch (a.epi) {
+          case TE_STORE:
+            stbf(a.out, o, v[i]);
+            break;
+          case TE_STORE_F32:
+            reinterpret_cast<float*>(a.out)[o] = rnd(v[i]);
+            break;
+          case TE_RESID:
+            stbf(a.out, o, ldbf(a.resid, o) + rnd(v[i]));
+            break;
+          case TE_SWIGLU: {
+            const float g = rnd(v[i]), up = rnd(u[i]);
+            const float sg = rnd(g / (1.0f + expf(-g)));
+            stbf(a.out, o, sg * up);
+          } break;
+          case TE_VCACHE: {
+            const int pos = a.seqlens[b];
+            if (pos < a.S_max)
+              stbf(a.cache, ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p, v[i]);
+            else
+              atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
+          } break;
+          default:
+            break;
+        }
+      }
+    }
+    if (rope) {
+      // rows (j, j + Dh/2) of a head sit in this tile (heads are Dh = 64 or 128 rows, tile-aligned)
+      __syncthreads();
+      const int half = a.Dh >> 1;
+      const int j = p % a.Dh;
+      if (p < a.P && j < half) {
+        for (int b = 0; b < a.B; ++b) {
+          const int pos = a.seqlens[b];
+          const int pt = min(pos, a.S_max - 1);
+          const float c = ldbf(a.cos_tab, (size_t)pt * half + j), sn = ldbf(a.sin_tab, (size_t)pt * half + j);
+          const float x1 = rnd(ftile[(size_t)b * kTileM + r]), x2 = rnd(ftile[(size_t)b * kTileM + r + half]);
+          const float o1 = rnd(rnd(x1 * c) - rnd(x2 * sn));
+          const float o2 = rnd(rnd(x2 * c) + rnd(x1 * sn));
+          if (a.epi == TE_ROPE_Q) {
+            stbf(a.out, (size_t)b * a.P + p, o1);
+            stbf(a.out, (size_t)b * a.P + p + half, o2);
+          } else if (pos < a.S_max) {
+            const size_t o = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p;
+            stbf(a.cache, o, o1);
+            stbf(a.cache, o + half, o2);
+          } else {
+            atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- release the tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (*giveup)
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);   // copies in flight towards this CTA land first
+  if (warp == 0) tc_dealloc(tmem, a.tmem_cols);
+}
+
+// ------------------------------------------------------------------------------- RMSNorm rows
+// out[b, :] = rnd(w * rnd(x[b, :] * rsqrt(mean(x[b, :]^2) + eps))), one CTA per row.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ out, int d, float eps) {
+  __shared__ float red[8];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* xr = x + (size_t)b * d;
+  float ss = 0.0f;
+  for (int i = tid; i < d; i += 256) {
+    const float v = __bfloat162float(xr[i]);
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)d + eps);
+  for (int i = tid; i < d; i += 256)
+    out[(size_t)b * d + i] = __float2bfloat16_rn(__bfloat162float(w[i]) * rnd(__bfloat162float(xr[i]) * inv));
+}
+
+// ------------------------------------------------------------------------------- attention
+// Single-query attention of B sequences over their dense caches.  One CTA = (sequence, kv head,
+// key split); its G = H / Hk query heads share the key and value rows it reads.  Keys are taken
+// 128 at a time: thread t scores key t of the chunk for all G heads (its key row comes in 16-byte
+// loads), the chunk's probabilities go through shared memory, and for the value rows every
+// thread owns two output dimensions of every head and a phase of the keys.  Splits of a head are
+// merged in split order by the CTA that arrives last.
+constexpr int kAttnThreads = 128;
+constexpr int kAttnChunk = 128;
+constexpr int kMaxG = 8;
+
+struct AttnArgs {
+  const __nv_bfloat16* q;        // [B, H, Dh], rotated
+  const __nv_bfloat16* kcache;   // [rows, S_max, Hk, Dh]
+  const __nv_bfloat16* vcache;
+  const int* seqlens;
+  __nv_bfloat16* out;            // [B, H, Dh]
+  float* part;                   // [B, Hk, nsplit, G, Dh + 2] (acc, m, l)
+  int* counters;                 // [B, Hk]
+  int B, H, Hk, Dh, S_max, nsplit, seqlen_add, shared_cache;
+  float scale;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs a) {
+  constexpr int LPR = DH / 2;                   // threads per value row (two dims each)
+  constexpr int PH = kAttnThreads / LPR;        // key phases
+  __shared__ float qs[kMaxG][DH];
+  __shared__ float sc[kMaxG][kAttnChunk];
+  __shared__ float red[kMaxG][4];
+  __shared__ float accs[PH][kMaxG][DH];
+  __shared__ int last_sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = a.H / a.Hk;
+  int idx = blockIdx.x;
+  const int split = idx % a.nsplit;
+  idx /= a.nsplit;
+  const int hk = idx % a.Hk, b = idx / a.Hk;
+  const int n = min(a.seqlens[b] + a.seqlen_add, a.S_max);
+  const int per = (n + a.nsplit - 1) / a.nsplit;
+  const int j0 = min(n, split * per), j1 = min(n, j0 + per);
+  const size_t rowstride = (size_t)a.Hk * DH;
+  const size_t cbase = ((size_t)(a.shared_cache ? 0 : b) * a.S_max) * rowstride + (size_t)hk * DH;
+
+  for (int i = tid; i < G * DH; i += kAttnThreads) {
+    const int g = i / DH, dd = i - g * DH;
+    qs[g][dd] = __bfloat162float(a.q[((size_t)b * a.H + hk * G + g) * DH + dd]) * a.scale;
+  }
+  float m[kMaxG], l[kMaxG], acc0[kMaxG], acc1[kMaxG];
+#pragma unroll
+  for (int g = 0; g < kMaxG; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+    acc0[g] = acc1[g] = 0.0f;
+  }
+  const int dim = 2 * (tid % LPR), phase = tid / LPR;
+  __syncthreads();
+
+  for (int c0 = j0; c0 < j1; c0 += kAttnChunk) {
+    const int cn = min(kAttnChunk, j1 - c0);
+    // ---- scores of key c0 + tid
+    float s[kMaxG];
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g) s[g] = 0.0f;
+    if (tid < cn) {
+      const uint4* kr = reinterpret_cast<const uint4*>(a.kcache + cbase + (size_t)(c0 + tid) * rowstride);
+#pragma unroll 4
+      for (int i = 0; i < DH / 8; ++i) {
+        const uint4 w = __ldg(kr + i);
+        float f[8];
+        f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
+        f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
+        f[4] = __uint_as_float(w.z << 16); f[5] = __uint_as_float(w.z & 0xffff0000u);
+        f[6] = __uint_as_float(w.w << 16); f[7] = __uint_as_float(w.w & 0xffff0000u);
+#pragma unroll
+        for (int g = 0; g < kMaxG; ++g)
+          if (g < G) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[g] += f[e] * qs[g][i * 8 + e];
+          }
+      }
+    }
+    // ---- chunk maximum per head
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g)
+      if (g < G) {
+        float v = tid < cn ? s[g] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if (lane == 0) red[g][warp] = v;
+      }
+    __syncthreads();
+    float corr[kMaxG];
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g)
+      if (g < G) {
+        const float cm = fmaxf(fmaxf(red[g][0], red[g][1]), fmaxf(red[g][2], red[g][3]));
+        const float mn = fmaxf(m[g], cm);
+        corr[g] = __expf(m[g] - mn);     // 0 for the first chunk (m = -inf)
+        m[g] = mn;
+        sc[g][tid] = tid < cn ? __expf(s[g] - mn) : 0.0f;
+      }
+    __syncthreads();
+    // ---- probabilities x value rows: this thread's two dims, keys phase, phase + PH, ...
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g)
+      if (g < G) {
+        acc0[g] *= corr[g];
+        acc1[g] *= corr[g];
+        float ps = 0.0f;   // every thread adds the whole chunk's probabilities for the denominator
+        for (int c = 0; c < cn; ++c) ps += sc[g][c];
+        l[g] = l[g] * corr[g] + ps;
+      }
+    for (int c = phase; c < cn; c += PH) {
+      const uint32_t w = __ldg(reinterpret_cast<const unsigned int*>(a.vcache + cbase + (size_t)(c0 + c) * rowstride + dim));
+      const float v0 = __uint_as_float(w << 16), v1 = __uint_as_float(w & 0xffff0000u);
+#pragma unroll
+      for (int g = 0; g < kMaxG; ++g)
+        if (g < G) {
+          const float pr = sc[g][c];
+          acc0[g] += pr * v0;
+          acc1[g] += pr * v1;
+        }
+    }
+    __syncthreads();
+  }
+  // ---- phases meet
+#pragma unroll
+  for (int g = 0; g < kMaxG; ++g)
+    if (g < G) {
+      accs[phase][g][dim] = acc0[g];
+      accs[phase][g][dim + 1] = acc1[g];
+    }
+  __syncthreads();
+  const int nsplit = a.nsplit;
+  if (nsplit == 1) {
+    for (int i = tid; i < G * DH; i += kAttnThreads) {
+      const int g = i / DH, dd = i - g * DH;
+      float v = 0.0f;
+#pragma unroll
+      for (int ph = 0; ph < PH; ++ph) v += accs[ph][g][dd];
+      // (l is the same in every thread)
+      float lg = 0.0f;
+#pragma unroll
+      for (int gg = 0; gg < kMaxG; ++gg)
+        if (gg == g) lg = l[gg];
+      a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(lg > 0.0f ? v / lg : 0.0f);
+    }
+    return;
+  }
+  const int rec = DH + 2;
+  float* mine = a.part + ((((size_t)b * a.Hk + hk) * nsplit + split) * G) * rec;
+  for (int i = tid; i < G * DH; i += kAttnThreads) {
+    const int g = i / DH, dd = i - g * DH;
+    float v = 0.0f;
+#pragma unroll
+    for (int ph = 0; ph < PH; ++ph) v += accs[ph][g][dd];
+    mine[(size_t)g * rec + dd] = v;
+  }
+  if (tid == 0) {
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g)
+      if (g < G) {
+        mine[(size_t)g * rec + DH] = m[g];
+        mine[(size_t)g * rec + DH + 1] = l[g];
+      }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&a.counters[b * a.Hk + hk], 1);
+    last_sh = old == nsplit - 1;
+    if (old == nsplit - 1) a.counters[b * a.Hk + hk] = 0;
+  }
+  __syncthreads();
+  if (!last_sh) return;
+  __threadfence();
+  const float* parts = a.part + (((size_t)b * a.Hk + hk) * nsplit) * G * rec;
+  for (int i = tid; i < G * DH; i += kAttnThreads) {
+    const int g = i / DH, dd = i - g * DH;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) mm = fmaxf(mm, __ldcg(parts + ((size_t)sp * G + g) * rec + DH));
+    float num = 0.0f, den = 0.0f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float* pr = parts + ((size_t)sp * G + g) * rec;
+      const float ms = __ldcg(pr + DH);
+      const float wgt = ms == -INFINITY ? 0.0f : __expf(ms - mm);
+      num += wgt * __ldcg(pr + dd);
+      den += wgt * __ldcg(pr + DH + 1);
+    }
+    a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
+  }
+}
+
+// ------------------------------------------------------------------------------- step head / tail
+__global__ void embed_rows_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
+                                  __nv_bfloat16* __restrict__ out, int d, int vocab) {
+  const int b = blockIdx.x;
+  int tok = tokens[b];
+  tok = min(max(tok, 0), vocab - 1);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)b * d + i] = table[(size_t)tok * d + i];
+}
+
+// token[b] = argmax_v logits[b, v] (lowest index among equal maxima); logs it; CTA 0 of the last
+// row... every row advances its own sequence length, row 0 the step counter.
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* tokens,
+                                                          int* token_log, int* step_counter, int* seqlens,
+                                                          int max_steps, int B) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)b * vocab;
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int i = tid; i < vocab; i += 256) {
+    const float v = row[i];
+    if (v > best || (v == best && i < besti)) {
+      best = v;
+      besti = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ov > best || (ov == best && oi < besti)) {
+      best = ov;
+      besti = oi;
+    }
+  }
+  if ((tid & 31) == 0) {
+    bv[tid >> 5] = best;
+    bi[tid >> 5] = besti;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int i = 1; i < 8; ++i)
+      if (bv[i] > best || (bv[i] == best && bi[i] < besti)) {
+        best = bv[i];
+        besti = bi[i];
+      }
+    if (besti == 0x7fffffff) besti = 0;
+    tokens[b] = besti;
+    const int step = *step_counter;
+    if (token_log && step < max_steps) token_log[(size_t)step * B + b] = besti;
+    seqlens[b] += 1;
+  }
+}
+__global__ void bump_step_kernel(int* step_counter) { *step_counter += 1; }
+
+// ------------------------------------------------------------------------------- host side
+static thread_local char g_err[512];
+static int fail(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  fsvd_tile_set_error(code, g_err);
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// bf16 [rows, cols] row-major with row stride ld elements, boxes of box_rows x 64 columns, 128-byte swizzle
+static int encode_sw128(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return fail(FSVD_ERR_ALIGN, "operand rows must start on 16-byte boundaries");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+  cuuint32_t es[2] = {1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FSVD_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  return 0;
+}
+
+static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
+static int round16(int b) { return b <= 16 ? 16 : (b + 15) / 16 * 16; }
+
+struct GemmPlan {
+  CUtensorMap mapA, mapA2, mapX, mapX2;
+  GemmArgs a;
+  dim3 grid;
+  size_t smem;
+};
+
+static int g_sms = 0, g_smem_optin = 0;
+static int device_limits() {
+  if (g_sms) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(FSVD_ERR_CUDA, "cudaGetDevice failed");
+  cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&g_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (g_sms < 1 || g_smem_optin < 64 * 1024) return fail(FSVD_ERR_CUDA, "device limits unavailable");
+  return 0;
+}
+
+// Segments of the K range: enough CTAs for two per SM, at most kMaxSegs, none empty.
+static void split_k(int tiles, int nkb, int sms, int& segs, int& kbs) {
+  int want = (2 * sms + tiles - 1) / tiles;
+  if (want > kMaxSegs) want = kMaxSegs;
+  if (want > nkb) want = nkb;
+  if (want < 1) want = 1;
+  kbs = (nkb + want - 1) / want;
+  segs = (nkb + kbs - 1) / kbs;
+}
+
+// Scratch floats a GEMM of P rows and K columns needs for its partial tiles.
+static size_t gemm_scratch_floats(int P, int K, int N, int nacc, int sms) {
+  const int tiles = (P + kTileM - 1) / kTileM, nkb = (K + kTileK - 1) / kTileK;
+  int segs, kbs;
+  split_k(tiles, nkb, sms, segs, kbs);
+  return segs > 1 ? (size_t)segs * tiles * nacc * N * kTileM : 0;
+}
+
+struct Scratch {
+  float* part;     // partial tiles
+  int* counters;   // tile arrival counters (>= max tiles ints, zero between launches)
+  int* status;
+  long long wait_limit;
+};
+
+// y[B, P] = epilogue(W[P, K] . x[B, K]^T); W2 / x2: the second accumulator of TE_SWIGLU.
+static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, int ldw, const void* x, const void* x2,
+                     int ldx, int B, int epi, const Scratch& sc) {
+  if (int e = device_limits()) return e;
+  memset(&g, 0, sizeof(g));
+  const int N = round16(B);
+  GemmArgs& a = g.a;
+  a.P = P; a.K = K; a.B = B; a.N = N;
+  a.tiles = (P + kTileM - 1) / kTileM;
+  a.nkb = (K + kTileK - 1) / kTileK;
+  split_k(a.tiles, a.nkb, g_sms, a.segs, a.kbs);
+  a.two = W2 ? 1 : 0;
+  a.epi = epi;
+  const int nacc = a.two ? 2 : 1;
+  uint32_t cols = 32;
+  while (cols < (uint32_t)(nacc * N)) cols <<= 1;
+  a.tmem_cols = cols;
+  const size_t stage = (size_t)kWTileBytes * nacc + (size_t)N * 128 * nacc;
+  int ns = (int)((size_t)(g_smem_optin - 2048) / stage);
+  if (ns > kMaxStages) ns = kMaxStages;
+  if (ns > a.kbs) ns = a.kbs;
+  if (ns < 1) return fail(FSVD_ERR_UNSUPPORTED, "shared memory too small for one stage");
+  a.nstages = ns;
+  size_t smem = 1024 + (size_t)ns * stage;
+  if ((epi == TE_ROPE_Q || epi == TE_ROPE_K) && smem < 1024 + (size_t)N * kTileM * 4) smem = 1024 + (size_t)N * kTileM * 4;
+  // co-resident CTAs must not ask for more than the 512 tensor-memory columns of an SM
+  const size_t floor_smem = (size_t)232448 / (512 / cols + 1) + 1024;
+  if (smem < floor_smem) smem = floor_smem;
+  if (smem > (size_t)g_smem_optin - 1024) return fail(FSVD_ERR_UNSUPPORTED, "shared memory plan exceeds the device limit");
+  g.smem = smem;
+  g.grid = dim3((unsigned)a.tiles, (unsigned)a.segs);
+  a.scratch = sc.part;
+  a.counters = sc.counters;
+  a.status = sc.status;
+  a.wait_limit = sc.wait_limit;
+  if (int e = encode_sw128(&g.mapA, W, P, K, ldw, kTileM)) return e;
+  if (int e = encode_sw128(&g.mapX, x, B, K, ldx, N)) return e;
+  if (W2) {
+    if (int e = encode_sw128(&g.mapA2, W2, P, K, ldw, kTileM)) return e;
+    if (int e = encode_sw128(&g.mapX2, x2, B, K, ldx, N)) return e;
+  } else {
+    g.mapA2 = g.mapA;
+    g.mapX2 = g.mapX;
+  }
+  return 0;
+}
+
+static int launch_gemm(const GemmPlan& g, cudaStream_t st) {
+  static bool attr_set = false;
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g_smem_optin - 1024) != cudaSuccess)
+        return fail(FSVD_ERR_CUDA, "cudaFuncSetAttribute failed for the tile kernel");
+      attr_set = true;
+    }
+  }
+  tile_gemm_kernel<<<g.grid, kThreads, g.smem, st>>>(g.mapA, g.mapA2, g.mapX, g.mapX2, g.a);
+  if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "tile kernel launch failed");
+  fsvd_tile_count_launch();
+  return 0;
+}
+
+// ---- workspace of the tile path (fsvd_dims with B > 8)
+struct TileWs {
+  size_t sync, counters, xn, pbuf, qbuf, attn, mid, hact, apart, part, total;
+  int nsplit;
+};
+static int attn_nsplit(const fsvd_dims& D, int sms) {
+  int ns = (2 * sms + D.B * D.Hk - 1) / (D.B * D.Hk);
+  if (ns > 16) ns = 16;
+  if (ns < 1) ns = 1;
+  return ns;
+}
+static int imax(int a, int b) { return a > b ? a : b; }
+static TileWs tile_layout(const fsvd_dims& D, int sms) {
+  TileWs L;
+  const int B = D.B, N = round16(B);
+  const int HD = D.H * D.Dh, KD = D.Hk * D.Dh;
+  const int Rqkv = D.Rq + D.Rk + D.Rv;
+  size_t o = 0;
+  L.sync = o;      o += al256(sizeof(SyncState));
+  L.counters = o;  o += 4096 * 4;                      // GEMM tiles (<= 4096) ...
+  const size_t acnt = al256((size_t)B * D.Hk * 4);     // ... and attention heads
+  o += acnt;
+  L.xn = o;        o += al256((size_t)B * imax(D.d, 8) * 2);
+  L.pbuf = o;      o += al256((size_t)B * imax(imax(Rqkv, D.Ru + D.Rg), imax(D.Ro, D.Rd)) * 2);
+  L.qbuf = o;      o += al256((size_t)B * HD * 2);
+  L.attn = o;      o += al256((size_t)B * HD * 2);
+  L.mid = o;       o += al256((size_t)B * D.d * 2);
+  L.hact = o;      o += al256((size_t)B * D.I * 2);
+  L.nsplit = attn_nsplit(D, sms);
+  L.apart = o;     o += al256((size_t)B * D.Hk * L.nsplit * (D.H / imax(D.Hk, 1)) * (D.Dh + 2) * 4);
+  size_t fl = 0;
+  auto mx = [&](size_t v) { if (v > fl) fl = v; };
+  mx(gemm_scratch_floats(Rqkv, D.d, N, 1, sms));
+  mx(gemm_scratch_floats(HD, D.Rq, N, 1, sms));
+  mx(gemm_scratch_floats(KD, D.Rk, N, 1, sms));
+  mx(gemm_scratch_floats(KD, D.Rv, N, 1, sms));
+  mx(gemm_scratch_floats(D.Ro, HD, N, 1, sms));
+  mx(gemm_scratch_floats(D.d, D.Ro, N, 1, sms));
+  mx(gemm_scratch_floats(D.Ru + D.Rg, D.d, N, 1, sms));
+  mx(gemm_scratch_floats(D.I, imax(D.Rg, D.Ru), N, 2, sms));
+  mx(gemm_scratch_floats(D.Rd, D.I, N, 1, sms));
+  mx(gemm_scratch_floats(D.d, D.Rd, N, 1, sms));
+  if (D.vocab > 0) mx(gemm_scratch_floats(D.vocab, D.d, N, 1, sms));
+  L.part = o;      o += al256(fl * 4);
+  L.total = o;
+  return L;
+}
+
+static int check_tile_dims(const fsvd_dims& D) {
+  if (D.dtype != FSVD_DTYPE_BF16) return fail(FSVD_ERR_UNSUPPORTED, "batches above 8 need bf16 factors (dtype 0)");
+  if (D.B < 9 || D.B > 128) return fail(FSVD_ERR_UNSUPPORTED, "batch outside 9..128");
+  if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+  if (D.Hk < 1 || D.H % D.Hk || D.H / D.Hk > kMaxG) return fail(FSVD_ERR_UNSUPPORTED, "H / Hk must be 1..8");
+  if (D.Rg != D.Ru) return fail(FSVD_ERR_UNSUPPORTED, "gate and up ranks must be equal for batches above 8");
+  const int m8[] = {D.d, D.I, D.Rq, D.Rk, D.Rv, D.Ro, D.Rg, D.Ru, D.Rd};
+  for (int v : m8)
+    if (v <= 0 || v % 8) return fail(FSVD_ERR_ALIGN, "sizes and ranks must be positive multiples of 8");
+  if ((D.d + kTileM - 1) / kTileM > 4096 || (D.I + kTileM - 1) / kTileM > 4096 || (D.vocab + kTileM - 1) / kTileM > 4096)
+    return fail(FSVD_ERR_UNSUPPORTED, "more than 4096 row tiles");
+  if (D.S_max < 1) return fail(FSVD_ERR_ARG, "S_max");
+  return 0;
+}
+
+struct LayerPlan {
+  GemmPlan g[9];
+  AttnArgs at;
+};
+
+static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, const void* cos_tab, const void* sin_tab,
+                      const int* seqlens, const void* x_in, void* x_out, char* ws, const TileWs& L, long long wait_limit) {
+  const int B = D.B, HD = D.H * D.Dh, KD = D.Hk * D.Dh, Rqkv = D.Rq + D.Rk + D.Rv;
+  Scratch sc = {reinterpret_cast<float*>(ws + L.part), reinterpret_cast<int*>(ws + L.counters),
+                &reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
+  __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
+  __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(ws + L.pbuf);
+  __nv_bfloat16* qb = reinterpret_cast<__nv_bfloat16*>(ws + L.qbuf);
+  __nv_bfloat16* attn = reinterpret_cast<__nv_bfloat16*>(ws + L.attn);
+  __nv_bfloat16* mid = reinterpret_cast<__nv_bfloat16*>(ws + L.mid);
+  __nv_bfloat16* hact = reinterpret_cast<__nv_bfloat16*>(ws + L.hact);
+  auto rope = [&](GemmArgs& a, void* cache) {
+    a.cache = cache; a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.seqlens = seqlens;
+    a.Dh = D.Dh; a.HkDh = KD; a.S_max = D.S_max; a.shared_cache = D.rows_are_positions ? 1 : 0;
+  };
+  int e;
+  // 0: [p_q | p_k | p_v] = rms(x) . qkv_v^T
+  if ((e = plan_gemm(lp.g[0], Lw.qkv_v, nullptr, Rqkv, D.d, D.d, xn, nullptr, D.d, B, TE_STORE, sc))) return e;
+  lp.g[0].a.out = pb;
+  // 1-3: lifts with rotary / cache append
+  if ((e = plan_gemm(lp.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc))) return e;
+  lp.g[1].a.out = qb;
+  rope(lp.g[1].a, nullptr);
+  if ((e = plan_gemm(lp.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sc))) return e;
+  rope(lp.g[2].a, Lw.k_cache);
+  if ((e = plan_gemm(lp.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc))) return e;
+  rope(lp.g[3].a, Lw.v_cache);
+  // attention
+  AttnArgs& at = lp.at;
+  memset(&at, 0, sizeof(at));
+  at.q = qb; at.kcache = reinterpret_cast<const __nv_bfloat16*>(Lw.k_cache);
+  at.vcache = reinterpret_cast<const __nv_bfloat16*>(Lw.v_cache);
+  at.seqlens = seqlens; at.out = attn;
+  at.part = reinterpret_cast<float*>(ws + L.apart);
+  at.counters = reinterpret_cast<int*>(ws + L.counters) + 4096;
+  at.B = B; at.H = D.H; at.Hk = D.Hk; at.Dh = D.Dh; at.S_max = D.S_max; at.nsplit = L.nsplit; at.seqlen_add = 1;
+  at.shared_cache = D.rows_are_positions ? 1 : 0;
+  at.scale = 1.0f / sqrtf((float)D.Dh);
+  // 4-5: o projection + residual
+  if ((e = plan_gemm(lp.g[4], Lw.o_v, nullptr, D.Ro, HD, HD, attn, nullptr, HD, B, TE_STORE, sc))) return e;
+  lp.g[4].a.out = pb;
+  if ((e = plan_gemm(lp.g[5], Lw.o_u, nullptr, D.d, D.Ro, D.Ro, pb, nullptr, D.Ro, B, TE_RESID, sc))) return e;
+  lp.g[5].a.out = mid;
+  lp.g[5].a.resid = x_in;
+  // 6-8: MLP
+  if ((e = plan_gemm(lp.g[6], Lw.upgate_v, nullptr, D.Ru + D.Rg, D.d, D.d, xn, nullptr, D.d, B, TE_STORE, sc))) return e;
+  lp.g[6].a.out = pb;
+  if ((e = plan_gemm(lp.g[7], Lw.gate_u, Lw.up_u, D.I, D.Rg, D.Rg, pb + D.Ru, pb, D.Ru + D.Rg, B, TE_SWIGLU, sc))) return e;
+  lp.g[7].a.out = hact;
+  if ((e = plan_gemm(lp.g[8], Lw.down_v, nullptr, D.Rd, D.I, D.I, hact, nullptr, D.I, B, TE_STORE, sc))) return e;
+  lp.g[8].a.out = pb;
+  (void)mid;
+  return 0;
+}
+
+static int launch_attn(const AttnArgs& at, cudaStream_t st) {
+  const unsigned grid = (unsigned)(at.B * at.Hk * at.nsplit);
+  if (at.Dh == 128) batch_attn_kernel<128><<<grid, kAttnThreads, 0, st>>>(at);
+  else batch_attn_kernel<64><<<grid, kAttnThreads, 0, st>>>(at);
+  if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "attention kernel launch failed");
+  fsvd_tile_count_launch();
+  return 0;
+}
+
+// The last GEMM of a layer (down lift + residual) is planned per call site: its output buffer
+// differs between the per-layer entry point and the model.
+static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_dims& D, const fsvd_layer& Lw,
+                     const void* x_in, char* ws, const TileWs& L, cudaStream_t st) {
+  __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
+  const __nv_bfloat16* mid = reinterpret_cast<const __nv_bfloat16*>(ws + L.mid);
+  int e;
+  rmsnorm_rows_kernel<<<D.B, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x_in),
+                                           reinterpret_cast<const __nv_bfloat16*>(Lw.ln1_w), xn, D.d, D.eps);
+  fsvd_tile_count_launch();
+  for (int i = 0; i < 4; ++i)
+    if ((e = launch_gemm(lp.g[i], st))) return e;
+  if ((e = launch_attn(lp.at, st))) return e;
+  if ((e = launch_gemm(lp.g[4], st))) return e;
+  if ((e = launch_gemm(lp.g[5], st))) return e;
+  rmsnorm_rows_kernel<<<D.B, 256, 0, st>>>(mid, reinterpret_cast<const __nv_bfloat16*>(Lw.ln2_w), xn, D.d, D.eps);
+  fsvd_tile_count_launch();
+  for (int i = 6; i < 9; ++i)
+    if ((e = launch_gemm(lp.g[i], st))) return e;
+  if ((e = launch_gemm(down_lift, st))) return e;
+  if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed");
+  return 0;
+}
+
+static int plan_down_lift(GemmPlan& g, const fsvd_dims& D, const fsvd_layer& Lw, void* x_out, char* ws, const TileWs& L,
+                          long long wait_limit) {
+  Scratch sc = {reinterpret_cast<float*>(ws + L.part), reinterpret_cast<int*>(ws + L.counters),
+                &reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
+  if (int e = plan_gemm(g, Lw.down_u, nullptr, D.d, D.Rd, D.Rd, ws + L.pbuf, nullptr, D.Rd, D.B, TE_RESID, sc)) return e;
+  g.a.out = x_out;
+  g.a.resid = ws + L.mid;
+  return 0;
+}
+
+}  // namespace fsvd_tile
+
+// ------------------------------------------------------------------------------- entry points
+using namespace fsvd_tile;
+
+size_t fsvd_tile_workspace_bytes(const fsvd_dims* dims) {
+  if (!dims || device_limits()) return 0;
+  if (check_tile_dims(*dims)) return 0;
+  return tile_layout(*dims, g_sms).total;
+}
+
+int fsvd_tile_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
+                           const int* cache_seqlens, const void* x_in, void* x_out, void* ws, size_t ws_bytes,
+                           long long wait_limit, void* stream) {
+  const fsvd_dims& D = *dims;
+  if (int e = device_limits()) return e;
+  if (int e = check_tile_dims(D)) return e;
+  const TileWs L = tile_layout(D, g_sms);
+  if (!ws || ws_bytes < L.total) return fail(FSVD_ERR_WORKSPACE, "workspace too small for this batch");
+  if (x_in == x_out) return fail(FSVD_ERR_ARG, "x_in and x_out must differ");
+  // the plans of the last call are kept: a decode loop calls with the same arguments every token
+  struct Cached {
+    fsvd_dims D;
+    fsvd_layer Lw;
+    const void *cos_tab, *sin_tab, *x_in;
+    const int* seqlens;
+    void *x_out, *ws;
+    long long wait_limit;
+    LayerPlan lp;
+    GemmPlan dl;
+    bool valid = false;
+  };
+  static std::mutex mu;
+  static std::vector<Cached*> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  Cached* c = nullptr;
+  for (Cached* k : cache)
+    if (k->valid && !memcmp(&k->D, &D, sizeof(D)) && !memcmp(&k->Lw, layer, sizeof(*layer)) && k->cos_tab == cos_tab &&
+        k->sin_tab == sin_tab && k->x_in == x_in && k->seqlens == cache_seqlens && k->x_out == x_out && k->ws == ws &&
+        k->wait_limit == wait_limit)
+      c = k;
+  if (!c) {
+    if (cache.size() >= 128) {
+      for (Cached* k : cache) delete k;
+      cache.clear();
+    }
+    c = new Cached();
+    c->D = D; c->Lw = *layer; c->cos_tab = cos_tab; c->sin_tab = sin_tab; c->x_in = x_in; c->seqlens = cache_seqlens;
+    c->x_out = x_out; c->ws = ws; c->wait_limit = wait_limit;
+    int e = plan_layer(c->lp, D, *layer, cos_tab, sin_tab, cache_seqlens, x_in, x_out, reinterpret_cast<char*>(ws), L, wait_limit);
+    if (!e) e = plan_down_lift(c->dl, D, *layer, x_out, reinterpret_cast<char*>(ws), L, wait_limit);
+    if (e) {
+      delete c;
+      return e;
+    }
+    c->valid = true;
+    cache.push_back(c);
+  }
+  return run_layer(c->lp, c->dl, D, *layer, x_in, reinterpret_cast<char*>(ws), L, (cudaStream_t)stream);
+}
+
+// ---- whole-model decode for batches above 8: the launches of a step captured once in a CUDA graph
+struct fsvd_tile_model {
+  fsvd_dims D;
+  TileWs L;
+  char* ws = nullptr;
+  char* extra = nullptr;
+  __nv_bfloat16* xbuf[2] = {nullptr, nullptr};
+  int *tokens = nullptr, *seqlens = nullptr, *step_counter = nullptr, *token_log = nullptr;
+  float* logits = nullptr;
+  int max_steps = 0;
+  std::vector<LayerPlan> layers;
+  std::vector<GemmPlan> down;
+  std::vector<fsvd_layer> lw;
+  GemmPlan head;
+  const void *embed = nullptr, *final_norm = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  long long launches_per_step = 0;
+};
+
+static int tile_model_record(fsvd_tile_model* m, cudaStream_t st) {
+  const fsvd_dims& D = m->D;
+  int e;
+  embed_rows_kernel<<<D.B, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(m->embed), m->tokens, m->xbuf[0], D.d, D.vocab);
+  fsvd_tile_count_launch();
+  for (int l = 0; l < D.n_layers; ++l)
+    if ((e = run_layer(m->layers[l], m->down[l], D, m->lw[l], m->xbuf[l & 1], m->ws, m->L, st))) return e;
+  __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(m->ws + m->L.xn);
+  rmsnorm_rows_kernel<<<D.B, 256, 0, st>>>(m->xbuf[D.n_layers & 1], reinterpret_cast<const __nv_bfloat16*>(m->final_norm), xn, D.d, D.eps);
+  fsvd_tile_count_launch();
+  if ((e = launch_gemm(m->head, st))) return e;
+  argmax_rows_kernel<<<D.B, 256, 0, st>>>(m->logits, D.vocab, m->tokens, m->token_log, m->step_counter, m->seqlens, m->max_steps, D.B);
+  bump_step_kernel<<<1, 1, 0, st>>>(m->step_counter);
+  fsvd_tile_count_launch();
+  fsvd_tile_count_launch();
+  if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed");
+  return 0;
+}
+
+int fsvd_tile_model_destroy(fsvd_tile_model* m) {
+  if (!m) return 0;
+  if (m->exec) cudaGraphExecDestroy(m->exec);
+  if (m->graph) cudaGraphDestroy(m->graph);
+  cudaFree(m->ws);
+  cudaFree(m->extra);
+  cudaFree(m->xbuf[0]);
+  cudaFree(m->xbuf[1]);
+  delete m;
+  return 0;
+}
+
+int fsvd_tile_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const void* embed, const void* final_norm_w,
+                           const void* lm_head, const void* cos_tab, const void* sin_tab, int max_steps, long long wait_limit,
+                           fsvd_tile_model** out) {
+  const fsvd_dims& D = *dims;
+  if (int e = device_limits()) return e;
+  if (int e = check_tile_dims(D)) return e;
+  if (D.n_layers < 1 || D.vocab < 1) return fail(FSVD_ERR_ARG, "n_layers / vocab");
+  if (max_steps < 1) max_steps = 1;
+  fsvd_tile_model* m = new fsvd_tile_model();
+  m->D = D;
+  m->L = tile_layout(D, g_sms);
+  m->max_steps = max_steps;
+  m->embed = embed;
+  m->final_norm = final_norm_w;
+  const size_t extra = al256((size_t)D.B * 4) * 2 + al256(4) + al256((size_t)max_steps * D.B * 4) + al256((size_t)D.B * D.vocab * 4);
+  cudaError_t ce = cudaMalloc(&m->ws, m->L.total);
+  if (ce == cudaSuccess) ce = cudaMalloc(&m->extra, extra);
+  if (ce == cudaSuccess) ce = cudaMalloc(&m->xbuf[0], al256((size_t)D.B * D.d * 2));
+  if (ce == cudaSuccess) ce = cudaMalloc(&m->xbuf[1], al256((size_t)D.B * D.d * 2));
+  if (ce == cudaSuccess) ce = cudaMemset(m->ws, 0, m->L.total);
+  if (ce == cudaSuccess) ce = cudaMemset(m->extra, 0, extra);
+  if (ce != cudaSuccess) {
+    fsvd_tile_model_destroy(m);
+    return fail(FSVD_ERR_CUDA, "allocating model scratch failed");
+  }
+  size_t o = 0;
+  m->tokens = reinterpret_cast<int*>(m->extra + o);        o += al256((size_t)D.B * 4);
+  m->seqlens = reinterpret_cast<int*>(m->extra + o);       o += al256((size_t)D.B * 4);
+  m->step_counter = reinterpret_cast<int*>(m->extra + o);  o += al256(4);
+  m->token_log = reinterpret_cast<int*>(m->extra + o);     o += al256((size_t)max_steps * D.B * 4);
+  m->logits = reinterpret_cast<float*>(m->extra + o);
+  m->layers.resize(D.n_layers);
+  m->down.resize(D.n_layers);
+  m->lw.assign(layers, layers + D.n_layers);
+  int e = 0;
+  for (int l = 0; l < D.n_layers && !e; ++l) {
+    e = plan_layer(m->layers[l], D, layers[l], cos_tab, sin_tab, m->seqlens, m->xbuf[l & 1], m->xbuf[(l + 1) & 1], m->ws, m->L, wait_limit);
+    if (!e) e = plan_down_lift(m->down[l], D, layers[l], m->xbuf[(l + 1) & 1], m->ws, m->L, wait_limit);
+  }
+  if (!e) {
+    Scratch sc = {reinterpret_cast<float*>(m->ws + m->L.part), reinterpret_cast<int*>(m->ws + m->L.counters),
+                  &reinterpret_cast<SyncState*>(m->ws + m->L.sync)->status, wait_limit};
+    e = plan_gemm(m->head, lm_head, nullptr, D.vocab, D.d, D.d, m->ws + m->L.xn, nullptr, D.d, D.B, TE_STORE_F32, sc);
+    m->head.a.out = m->logits;
+  }
+  if (e) {
+    fsvd_tile_model_destroy(m);
+    return e;
+  }
+  // capture the launches of one step (nothing runs here; the shared-memory attribute of the GEMM
+  // kernel is raised to the device limit first, outside the capture)
+  if (cudaFuncSetAttribute(tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g_smem_optin - 1024) != cudaSuccess) {
+    fsvd_tile_model_destroy(m);
+    return fail(FSVD_ERR_CUDA, "cudaFuncSetAttribute failed for the tile kernel");
+  }
+  cudaStream_t cs = nullptr;
+  if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) {
+    fsvd_tile_model_destroy(m);
+    return fail(FSVD_ERR_CUDA, "cudaStreamCreate failed");
+  }
+  if (cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal) != cudaSuccess) e = fail(FSVD_ERR_CUDA, "stream capture failed");
+  if (!e) {
+    const long long before = fsvd_tile_launches();
+    e = tile_model_record(m, cs);
+    m->launches_per_step = fsvd_tile_launches() - before;
+    fsvd_tile_count_launches(-m->launches_per_step);   // recorded, not run
+    cudaGraph_t g = nullptr;
+    if (cudaStreamEndCapture(cs, &g) != cudaSuccess || !g) e = e ? e : fail(FSVD_ERR_CUDA, "stream capture failed");
+    m->graph = g;
+  }
+  if (!e && cudaGraphInstantiate(&m->exec, m->graph, 0) != cudaSuccess) e = fail(FSVD_ERR_CUDA, "cudaGraphInstantiate failed");
+  cudaStreamDestroy(cs);
+  if (e) {
+    fsvd_tile_model_destroy(m);
+    return e;
+  }
+  *out = m;
+  return 0;
+}
+
+int fsvd_tile_model_step(fsvd_tile_model* m, int n_steps, void* stream) {
+  for (int i = 0; i < n_steps; ++i) {
+    if (cudaGraphLaunch(m->exec, (cudaStream_t)stream) != cudaSuccess) return fail(FSVD_ERR_CUDA, "cudaGraphLaunch failed");
+    fsvd_tile_count_launches(m->launches_per_step);
+  }
+  return 0;
+}
+
+void fsvd_tile_model_buffers(fsvd_tile_model* m, int** tokens, int** seqlens, int** token_log, int** step_counter,
+                             float** logits, float** hidden) {
+  if (tokens) *tokens = m->tokens;
+  if (seqlens) *seqlens = m->seqlens;
+  if (token_log) *token_log = m->token_log;
+  if (step_counter) *step_counter = m->step_counter;
+  if (logits) *logits = m->logits;
+  if (hidden) *hidden = reinterpret_cast<float*>(m->xbuf[m->D.n_layers & 1]);
+}
+void* fsvd_tile_model_ws(fsvd_tile_model* m) { return m->ws; }
+int fsvd_tile_model_launches_per_step(fsvd_tile_model* m) { return (int)m->launches_per_step; }
+int fsvd_tile_model_reset(fsvd_tile_model* m, void* stream) {
+  if (cudaMemsetAsync(m->ws + m->L.sync, 0, m->L.xn - m->L.sync, (cudaStream_t)stream) != cudaSuccess)
+    return fail(FSVD_ERR_CUDA, "cudaMemsetAsync failed");
+  return 0;
+}

@@ -1,0 +1,84 @@
+"""Batches of 9..128 sequences: the tiled tensor-core path (tcgen05 GEMMs with the accumulators in
+tensor memory, `flashsvd_b200/csrc/fsvd_tile.cu`) against the CPU oracle, through the same C entry
+points as the small batches (`fsvd_decode_layer`, `fsvd_model_*` with `fsvd_dims.B` > 8).
+
+Tolerance: the bf16 per-layer bound 2e-2 (rel_linf), as for the small batches."""
+import pytest
+import torch
+
+from oracle import lowrank_llama as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from flashsvd_b200 import _lib
+
+    _lib.load()
+    return torch.device("cuda:0")
+
+
+def rel_linf(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+def _layer_case(dev, shape, B, ctx, S_max, seed=0, ragged=True):
+    from flashsvd_b200 import ops, packing
+
+    dtype = torch.bfloat16
+    gen = torch.Generator().manual_seed(seed)
+    w = O.make_layer_weights(shape, gen, dtype)
+    x = torch.randn(B, shape.d, generator=gen).to(dtype)
+    kc = torch.zeros(B, S_max, shape.Hk, shape.Dh, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    kc[:, :ctx] = torch.randn(B, ctx, shape.Hk, shape.Dh, generator=gen).to(dtype)
+    vc[:, :ctx] = torch.randn(B, ctx, shape.Hk, shape.Dh, generator=gen).to(dtype)
+    seqlens = torch.full((B,), ctx, dtype=torch.int32)
+    if ragged:
+        for b in range(B):
+            seqlens[b] = max(0, ctx - 3 * (b % 5))   # ragged batch, one sequence possibly short
+    cos, sin = O.rope_tables(S_max, shape.Dh, shape.theta, dtype)
+    kc_o, vc_o = kc.clone(), vc.clone()
+    ref = O.decode_layer(shape, w, x, kc_o, vc_o, seqlens, cos, sin)
+    pk = packing.pack_layer(w, device=dev, dtype=dtype)
+    pk["k_cache"], pk["v_cache"] = kc.to(dev), vc.to(dev)
+    dims = ops.make_dims(dtype=dtype, B=B, d=shape.d, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, I=shape.I, Rq=shape.Rq,
+                         Rk=shape.Rk, Rv=shape.Rv, Ro=shape.Ro, Rg=shape.Rg, Ru=shape.Ru, Rd=shape.Rd,
+                         S_max=S_max, eps=shape.eps)
+    ws = ops.make_workspace(dims, dev)
+    out = torch.empty(B, shape.d, dtype=dtype, device=dev)
+    xd = x.to(dev)
+    ops.decode_layer(dims, ops.make_layer_struct(pk), cos.to(dev), sin.to(dev), seqlens.to(dev), xd, out, ws)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    return out, ref, pk, kc_o, vc_o
+
+
+@pytest.mark.parametrize("shape,B,ctx", [(O.TINY, 16, 37), (O.TINY_GQA, 32, 50), (O.TINY, 9, 20), (O.TINY_GQA, 128, 140)])
+def test_decode_layer_tiles_match_oracle(dev, shape, B, ctx):
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, shape, B, ctx, S_max=ctx + 8)
+    assert rel_linf(pk["k_cache"], kc_o) <= TOL
+    assert rel_linf(pk["v_cache"], vc_o) <= TOL
+    assert rel_linf(out, ref) <= TOL
+
+
+def test_decode_layer_tiles_ragged_ranks(dev):
+    # sizes that are multiples of 8 but of nothing larger: ragged last k-blocks and row tiles
+    shape = O.Shape(d=264, H=4, Hk=2, Dh=64, I=520, Rq=88, Rk=40, Rv=56, Ro=72, Rg=104, Ru=104, Rd=80,
+                    vocab=200, n_layers=1)
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, shape, 24, 21, S_max=32)
+    assert rel_linf(pk["k_cache"], kc_o) <= TOL
+    assert rel_linf(out, ref) <= TOL
+
+
+@pytest.mark.parametrize("B", [16, 32])
+def test_decode_layer_tiles_7b_shape(dev, B):
+    # one Llama-2-7B-shaped layer, ranks 1024 / 1488, 512 cached positions
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, O.LLAMA7B_SVD50, B, ctx=512, S_max=516, seed=2)
+    assert rel_linf(pk["k_cache"][:, 500:], kc_o[:, 500:]) <= TOL
+    assert rel_linf(pk["v_cache"][:, 500:], vc_o[:, 500:]) <= TOL
+    assert rel_linf(out, ref) <= TOL
