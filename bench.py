@@ -268,6 +268,9 @@ SECONDARY = (
     ("shared_bases_b1_ctx2048", "7b", 32, 1, 2048, True, "bf16"),
     ("shared_bases_b8_ctx2048", "7b", 32, 8, 2048, True, "bf16"),
     ("70b_shape_replica_b1_ctx512", "70b", 80, 1, 512, False, "bf16"),
+    # batches above 8 run as tiled tcgen05 GEMMs + batched attention, one CUDA graph launch per step
+    ("tiles_b16_ctx512", "7b", 32, 16, 512, False, "bf16"),
+    ("tiles_shared_bases_b32_ctx2048", "7b", 32, 32, 2048, True, "bf16"),
 )
 
 

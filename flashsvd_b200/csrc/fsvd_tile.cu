@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <utility>
 #include <vector>
 
 #include "../../include/flashsvd_b200.h"
@@ -182,13 +183,30 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return true;
 }
 
+// Programmatic dependent launch: every kernel of this file is launched with the stream-serialization
+// attribute, so its CTAs may start while the kernel before it in the stream is still draining.
+// pdl_wait() returns when that kernel has completed and its writes are visible; nothing that
+// another kernel wrote is read, and nothing in global memory is written, before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Up to three independent GEMMs in one launch (the q, k and v lifts of a layer): blockIdx.z picks
+// the problem, CTAs outside a problem's (tiles, segs) range leave at once.
+constexpr int kMaxGroup = 3;
+struct GemmGroup {
+  CUtensorMap maps[kMaxGroup][4];   // A, A2, X, X2
+  GemmArgs args[kMaxGroup];
+};
+
 // ------------------------------------------------------------------------------- GEMM kernel
-// grid = (tiles, segs).  Dynamic shared memory: [1 KB slack for alignment][NS stages].
-__global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_constant__ CUtensorMap mapA,
-                                                             const __grid_constant__ CUtensorMap mapA2,
-                                                             const __grid_constant__ CUtensorMap mapX,
-                                                             const __grid_constant__ CUtensorMap mapX2,
-                                                             const GemmArgs a) {
+// grid = (tiles, segs, problems).  Dynamic shared memory: [1 KB slack for alignment][NS stages].
+__global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_constant__ GemmGroup grp) {
+  const GemmArgs& a = grp.args[blockIdx.z];
+  if ((int)blockIdx.x >= a.tiles || (int)blockIdx.y >= a.segs) return;
+  const CUtensorMap& mapA = grp.maps[blockIdx.z][0];
+  const CUtensorMap& mapA2 = grp.maps[blockIdx.z][1];
+  const CUtensorMap& mapX = grp.maps[blockIdx.z][2];
+  const CUtensorMap& mapX2 = grp.maps[blockIdx.z][3];
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + 1];
   __shared__ uint32_t tmem_slot;
@@ -224,26 +242,37 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  pdl_launch_dependents();
 
   const int kb0 = seg * a.kbs, kb1 = min(a.nkb, kb0 + a.kbs);
   const int nit = kb1 - kb0;
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---- producer: TMA copies of the stage operands
+      // ---- producer: TMA copies of the stage operands.  The factor tiles of the first NS stages do
+      // not depend on the kernel before this one and are requested before pdl_wait().
+      const int pre = min(nit, NS);
+      for (int it = 0; it < pre; ++it) {
+        const uint32_t fb = full0 + 8 * it;
+        const uint32_t dst = base + (uint32_t)it * stage_bytes;
+        const int kcol = (kb0 + it) * kTileK;
+        mbar_expect_tx(fb, stage_bytes);
+        tma_box_2d(dst, &mapA, kcol, tile * kTileM, fb);
+        if (a.two) tma_box_2d(dst + kWTileBytes, &mapA2, kcol, tile * kTileM, fb);
+      }
+      pdl_wait();
       for (int it = 0; it < nit; ++it) {
         const int s = it % NS, round = it / NS;
         if (round > 0 && !wait_bar(empty0 + 8 * s, (uint32_t)(round - 1) & 1u, giveup, a, DS_COPY_TIMEOUT)) break;
         const uint32_t fb = full0 + 8 * s;
         uint32_t dst = base + (uint32_t)s * stage_bytes;
         const int kcol = (kb0 + it) * kTileK;
-        mbar_expect_tx(fb, stage_bytes);
-        tma_box_2d(dst, &mapA, kcol, tile * kTileM, fb);
-        dst += kWTileBytes;
-        if (a.two) {
-          tma_box_2d(dst, &mapA2, kcol, tile * kTileM, fb);
-          dst += kWTileBytes;
+        if (it >= pre) {
+          mbar_expect_tx(fb, stage_bytes);
+          tma_box_2d(dst, &mapA, kcol, tile * kTileM, fb);
+          if (a.two) tma_box_2d(dst + kWTileBytes, &mapA2, kcol, tile * kTileM, fb);
         }
+        dst += (uint32_t)kWTileBytes * (a.two ? 2u : 1u);
         tma_box_2d(dst, &mapX, kcol, 0, fb);
         if (a.two) tma_box_2d(dst + xbytes, &mapX2, kcol, 0, fb);
       }
@@ -278,7 +307,9 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
     __syncwarp();
   }
 
-  // ---- everybody: wait for the accumulators
+  // ---- everybody: wait for the kernel before this one (the epilogue reads what it wrote), then
+  // for the accumulators
+  pdl_wait();
   bool have = nit > 0 ? wait_bar(accum, 0u, giveup, a, DS_BARRIER_TIMEOUT) : false;
   have = __all_sync(0xffffffffu, have);
   tc_fence_after();
@@ -417,6 +448,8 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
                                                            __nv_bfloat16* __restrict__ out, int d, float eps) {
   __shared__ float red[8];
   const int b = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const __nv_bfloat16* xr = x + (size_t)b * d;
   float ss = 0.0f;
   for (int i = tid; i < d; i += 256) {
@@ -437,13 +470,15 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
 
 // ------------------------------------------------------------------------------- attention
 // Single-query attention of B sequences over their dense caches.  One CTA = (sequence, kv head,
-// key split); its G = H / Hk query heads share the key and value rows it reads.  Keys are taken
-// 128 at a time: thread t scores key t of the chunk for all G heads (its key row comes in 16-byte
-// loads), the chunk's probabilities go through shared memory, and for the value rows every
-// thread owns two output dimensions of every head and a phase of the keys.  Splits of a head are
-// merged in split order by the CTA that arrives last.
+// key split); its G = H / Hk query heads share the key and value rows it reads.  Each of the four
+// warps walks its own groups of 8 keys with its own running softmax: a key (or value) row is one
+// coalesced warp-wide load (lane t holds dims DPL t .. DPL t + DPL - 1), the 8 key rows and the 8
+// value rows of a group are requested together, the 8 x G dot products are reduced with shuffles.
+// The warps meet in shared memory; splits of a head are merged in split order by the CTA that
+// arrives last.
 constexpr int kAttnThreads = 128;
-constexpr int kAttnChunk = 128;
+constexpr int kAttnWarps = 4;
+constexpr int kKeyGroup = 8;
 constexpr int kMaxG = 8;
 
 struct AttnArgs {
@@ -458,17 +493,29 @@ struct AttnArgs {
   float scale;
 };
 
-template <int DH>
+template <int DPL>
+__device__ __forceinline__ void ld_row(const __nv_bfloat16* row, int lane, float (&f)[DPL]);
+template <>
+__device__ __forceinline__ void ld_row<4>(const __nv_bfloat16* row, int lane, float (&f)[4]) {
+  const uint2 w = __ldg(reinterpret_cast<const uint2*>(row) + lane);
+  f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
+  f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void ld_row<2>(const __nv_bfloat16* row, int lane, float (&f)[2]) {
+  const unsigned w = __ldg(reinterpret_cast<const unsigned*>(row) + lane);
+  f[0] = __uint_as_float(w << 16); f[1] = __uint_as_float(w & 0xffff0000u);
+}
+
+template <int DH, int G>
 __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs a) {
-  constexpr int LPR = DH / 2;                   // threads per value row (two dims each)
-  constexpr int PH = kAttnThreads / LPR;        // key phases
-  __shared__ float qs[kMaxG][DH];
-  __shared__ float sc[kMaxG][kAttnChunk];
-  __shared__ float red[kMaxG][4];
-  __shared__ float accs[PH][kMaxG][DH];
+  constexpr int DPL = DH / 32;
+  __shared__ float wm[kAttnWarps][G], wl[kAttnWarps][G];
+  __shared__ float wacc[kAttnWarps][G][DH];
   __shared__ int last_sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int G = a.H / a.Hk;
+  pdl_launch_dependents();
+  pdl_wait();
   int idx = blockIdx.x;
   const int split = idx % a.nsplit;
   idx /= a.nsplit;
@@ -478,130 +525,105 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
   const int j0 = min(n, split * per), j1 = min(n, j0 + per);
   const size_t rowstride = (size_t)a.Hk * DH;
   const size_t cbase = ((size_t)(a.shared_cache ? 0 : b) * a.S_max) * rowstride + (size_t)hk * DH;
+  const __nv_bfloat16* kbase = a.kcache + cbase;
+  const __nv_bfloat16* vbase = a.vcache + cbase;
 
-  for (int i = tid; i < G * DH; i += kAttnThreads) {
-    const int g = i / DH, dd = i - g * DH;
-    qs[g][dd] = __bfloat162float(a.q[((size_t)b * a.H + hk * G + g) * DH + dd]) * a.scale;
-  }
-  float m[kMaxG], l[kMaxG], acc0[kMaxG], acc1[kMaxG];
+  float q[G][DPL], acc[G][DPL], m[G], l[G];
 #pragma unroll
-  for (int g = 0; g < kMaxG; ++g) {
+  for (int g = 0; g < G; ++g) {
+    ld_row<DPL>(a.q + ((size_t)b * a.H + hk * G + g) * DH, lane, q[g]);
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) {
+      q[g][e] *= a.scale;
+      acc[g][e] = 0.0f;
+    }
     m[g] = -INFINITY;
     l[g] = 0.0f;
-    acc0[g] = acc1[g] = 0.0f;
   }
-  const int dim = 2 * (tid % LPR), phase = tid / LPR;
-  __syncthreads();
 
-  for (int c0 = j0; c0 < j1; c0 += kAttnChunk) {
-    const int cn = min(kAttnChunk, j1 - c0);
-    // ---- scores of key c0 + tid
-    float s[kMaxG];
+  for (int c0 = j0 + warp * kKeyGroup; c0 < j1; c0 += kAttnWarps * kKeyGroup) {
+    const int cn = min(kKeyGroup, j1 - c0);
+    float kf[kKeyGroup][DPL], vf[kKeyGroup][DPL];
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g) s[g] = 0.0f;
-    if (tid < cn) {
-      const uint4* kr = reinterpret_cast<const uint4*>(a.kcache + cbase + (size_t)(c0 + tid) * rowstride);
-#pragma unroll 4
-      for (int i = 0; i < DH / 8; ++i) {
-        const uint4 w = __ldg(kr + i);
-        float f[8];
-        f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
-        f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
-        f[4] = __uint_as_float(w.z << 16); f[5] = __uint_as_float(w.z & 0xffff0000u);
-        f[6] = __uint_as_float(w.w << 16); f[7] = __uint_as_float(w.w & 0xffff0000u);
-#pragma unroll
-        for (int g = 0; g < kMaxG; ++g)
-          if (g < G) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) s[g] += f[e] * qs[g][i * 8 + e];
-          }
-      }
+    for (int i = 0; i < kKeyGroup; ++i) {
+      const int row = c0 + (i < cn ? i : cn - 1);   // past the end: the last row again, weighted 0 below
+      ld_row<DPL>(kbase + (size_t)row * rowstride, lane, kf[i]);
+      ld_row<DPL>(vbase + (size_t)row * rowstride, lane, vf[i]);
     }
-    // ---- chunk maximum per head
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g)
-      if (g < G) {
-        float v = tid < cn ? s[g] : -INFINITY;
+    for (int g = 0; g < G; ++g) {
+      float s[kKeyGroup];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        if (lane == 0) red[g][warp] = v;
+      for (int i = 0; i < kKeyGroup; ++i) {
+        float d = 0.0f;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) d += kf[i][e] * q[g][e];
+        s[i] = d;
       }
-    __syncthreads();
-    float corr[kMaxG];
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g)
-      if (g < G) {
-        const float cm = fmaxf(fmaxf(red[g][0], red[g][1]), fmaxf(red[g][2], red[g][3]));
-        const float mn = fmaxf(m[g], cm);
-        corr[g] = __expf(m[g] - mn);     // 0 for the first chunk (m = -inf)
-        m[g] = mn;
-        sc[g][tid] = tid < cn ? __expf(s[g] - mn) : 0.0f;
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int i = 0; i < kKeyGroup; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], o);
       }
-    __syncthreads();
-    // ---- probabilities x value rows: this thread's two dims, keys phase, phase + PH, ...
+      float cm = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g)
-      if (g < G) {
-        acc0[g] *= corr[g];
-        acc1[g] *= corr[g];
-        float ps = 0.0f;   // every thread adds the whole chunk's probabilities for the denominator
-        for (int c = 0; c < cn; ++c) ps += sc[g][c];
-        l[g] = l[g] * corr[g] + ps;
+      for (int i = 0; i < kKeyGroup; ++i) {
+        if (i >= cn) s[i] = -INFINITY;
+        cm = fmaxf(cm, s[i]);
       }
-    for (int c = phase; c < cn; c += PH) {
-      const uint32_t w = __ldg(reinterpret_cast<const unsigned int*>(a.vcache + cbase + (size_t)(c0 + c) * rowstride + dim));
-      const float v0 = __uint_as_float(w << 16), v1 = __uint_as_float(w & 0xffff0000u);
+      const float mn = fmaxf(m[g], cm);
+      const float corr = __expf(m[g] - mn);   // 0 when m is still -inf
+      m[g] = mn;
+      float ps = 0.0f;
 #pragma unroll
-      for (int g = 0; g < kMaxG; ++g)
-        if (g < G) {
-          const float pr = sc[g][c];
-          acc0[g] += pr * v0;
-          acc1[g] += pr * v1;
-        }
+      for (int e = 0; e < DPL; ++e) acc[g][e] *= corr;
+#pragma unroll
+      for (int i = 0; i < kKeyGroup; ++i) {
+        const float pr = __expf(s[i] - mn);   // 0 for the rows past the end
+        ps += pr;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[g][e] += pr * vf[i][e];
+      }
+      l[g] = l[g] * corr + ps;
     }
-    __syncthreads();
   }
-  // ---- phases meet
+  // ---- the warps meet
 #pragma unroll
-  for (int g = 0; g < kMaxG; ++g)
-    if (g < G) {
-      accs[phase][g][dim] = acc0[g];
-      accs[phase][g][dim + 1] = acc1[g];
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      wm[warp][g] = m[g];
+      wl[warp][g] = l[g];
     }
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) wacc[warp][g][lane * DPL + e] = acc[g][e];
+  }
   __syncthreads();
   const int nsplit = a.nsplit;
-  if (nsplit == 1) {
-    for (int i = tid; i < G * DH; i += kAttnThreads) {
-      const int g = i / DH, dd = i - g * DH;
-      float v = 0.0f;
-#pragma unroll
-      for (int ph = 0; ph < PH; ++ph) v += accs[ph][g][dd];
-      // (l is the same in every thread)
-      float lg = 0.0f;
-#pragma unroll
-      for (int gg = 0; gg < kMaxG; ++gg)
-        if (gg == g) lg = l[gg];
-      a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(lg > 0.0f ? v / lg : 0.0f);
-    }
-    return;
-  }
   const int rec = DH + 2;
   float* mine = a.part + ((((size_t)b * a.Hk + hk) * nsplit + split) * G) * rec;
   for (int i = tid; i < G * DH; i += kAttnThreads) {
     const int g = i / DH, dd = i - g * DH;
-    float v = 0.0f;
+    float mm = -INFINITY;
 #pragma unroll
-    for (int ph = 0; ph < PH; ++ph) v += accs[ph][g][dd];
-    mine[(size_t)g * rec + dd] = v;
-  }
-  if (tid == 0) {
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, wm[w][g]);
+    float num = 0.0f, den = 0.0f;
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g)
-      if (g < G) {
-        mine[(size_t)g * rec + DH] = m[g];
-        mine[(size_t)g * rec + DH + 1] = l[g];
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float wgt = wm[w][g] == -INFINITY ? 0.0f : __expf(wm[w][g] - mm);
+      num += wgt * wacc[w][g][dd];
+      den += wgt * wl[w][g];
+    }
+    if (nsplit == 1) {
+      a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
+    } else {
+      mine[(size_t)g * rec + dd] = num;
+      if (dd == 0) {
+        mine[(size_t)g * rec + DH] = mm;
+        mine[(size_t)g * rec + DH + 1] = den;
       }
+    }
   }
+  if (nsplit == 1) return;
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -633,6 +655,8 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
 __global__ void embed_rows_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
                                   __nv_bfloat16* __restrict__ out, int d, int vocab) {
   const int b = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   int tok = tokens[b];
   tok = min(max(tok, 0), vocab - 1);
   for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)b * d + i] = table[(size_t)tok * d + i];
@@ -646,6 +670,8 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
   __shared__ float bv[8];
   __shared__ int bi[8];
   const int b = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const float* row = logits + (size_t)b * vocab;
   float best = -INFINITY;
   int besti = 0x7fffffff;
@@ -683,7 +709,11 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
     seqlens[b] += 1;
   }
 }
-__global__ void bump_step_kernel(int* step_counter) { *step_counter += 1; }
+__global__ void bump_step_kernel(int* step_counter) {
+  pdl_launch_dependents();
+  pdl_wait();
+  *step_counter += 1;
+}
 
 // ------------------------------------------------------------------------------- host side
 static thread_local char g_err[512];
@@ -746,11 +776,12 @@ static int device_limits() {
   return 0;
 }
 
-// Segments of the K range: enough CTAs for two per SM, at most kMaxSegs, none empty.
+// Segments of the K range: about one CTA per SM, at least 4 k-blocks (64 KB of factor) per CTA
+// where the matrix has them, at most kMaxSegs segments, none empty.
 static void split_k(int tiles, int nkb, int sms, int& segs, int& kbs) {
-  int want = (2 * sms + tiles - 1) / tiles;
+  int want = (sms + tiles / 2) / tiles;
   if (want > kMaxSegs) want = kMaxSegs;
-  if (want > nkb) want = nkb;
+  if (want > nkb / 4) want = nkb / 4;
   if (want < 1) want = 1;
   kbs = (nkb + want - 1) / want;
   segs = (nkb + kbs - 1) / kbs;
@@ -792,6 +823,11 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   int ns = (int)((size_t)(g_smem_optin - 2048) / stage);
   if (ns > kMaxStages) ns = kMaxStages;
   if (ns > a.kbs) ns = a.kbs;
+  // more CTAs than SMs: keep the ring small enough for two CTAs per SM
+  if (a.tiles * a.segs > g_sms && ns > 2 && (size_t)ns * stage > 110 * 1024) {
+    ns = (int)((size_t)(110 * 1024) / stage);
+    if (ns < 2) ns = 2;
+  }
   if (ns < 1) return fail(FSVD_ERR_UNSUPPORTED, "shared memory too small for one stage");
   a.nstages = ns;
   size_t smem = 1024 + (size_t)ns * stage;
@@ -818,7 +854,28 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   return 0;
 }
 
+// Launch with the programmatic-stream-serialization attribute (see pdl_wait above).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+static int launch_group(const GemmPlan* const* plans, int n, cudaStream_t st);
 static int launch_gemm(const GemmPlan& g, cudaStream_t st) {
+  const GemmPlan* one[1] = {&g};
+  return launch_group(one, 1, st);
+}
+static int launch_group(const GemmPlan* const* plans, int n, cudaStream_t st) {
   static bool attr_set = false;
   static std::mutex mu;
   {
@@ -829,8 +886,20 @@ static int launch_gemm(const GemmPlan& g, cudaStream_t st) {
       attr_set = true;
     }
   }
-  tile_gemm_kernel<<<g.grid, kThreads, g.smem, st>>>(g.mapA, g.mapA2, g.mapX, g.mapX2, g.a);
-  if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "tile kernel launch failed");
+  GemmGroup grp;
+  memset(&grp, 0, sizeof(grp));
+  dim3 grid(1, 1, (unsigned)n);
+  size_t smem = 0;
+  for (int i = 0; i < n; ++i) {
+    const GemmPlan& g = *plans[i];
+    grp.maps[i][0] = g.mapA; grp.maps[i][1] = g.mapA2; grp.maps[i][2] = g.mapX; grp.maps[i][3] = g.mapX2;
+    grp.args[i] = g.a;
+    if (g.grid.x > grid.x) grid.x = g.grid.x;
+    if (g.grid.y > grid.y) grid.y = g.grid.y;
+    if (g.smem > smem) smem = g.smem;
+  }
+  if (launch_pdl(tile_gemm_kernel, grid, dim3(kThreads), smem, st, grp) != cudaSuccess)
+    return fail(FSVD_ERR_CUDA, "tile kernel launch failed");
   fsvd_tile_count_launch();
   return 0;
 }
@@ -841,7 +910,7 @@ struct TileWs {
   int nsplit;
 };
 static int attn_nsplit(const fsvd_dims& D, int sms) {
-  int ns = (2 * sms + D.B * D.Hk - 1) / (D.B * D.Hk);
+  int ns = (8 * sms + D.B * D.Hk - 1) / (D.B * D.Hk);   // about 8 CTAs of 4 warps per SM
   if (ns > 16) ns = 16;
   if (ns < 1) ns = 1;
   return ns;
@@ -868,9 +937,8 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
   size_t fl = 0;
   auto mx = [&](size_t v) { if (v > fl) fl = v; };
   mx(gemm_scratch_floats(Rqkv, D.d, N, 1, sms));
-  mx(gemm_scratch_floats(HD, D.Rq, N, 1, sms));
-  mx(gemm_scratch_floats(KD, D.Rk, N, 1, sms));
-  mx(gemm_scratch_floats(KD, D.Rv, N, 1, sms));
+  mx(gemm_scratch_floats(HD, D.Rq, N, 1, sms) + gemm_scratch_floats(KD, D.Rk, N, 1, sms) +
+     gemm_scratch_floats(KD, D.Rv, N, 1, sms));   // one launch
   mx(gemm_scratch_floats(D.Ro, HD, N, 1, sms));
   mx(gemm_scratch_floats(D.d, D.Ro, N, 1, sms));
   mx(gemm_scratch_floats(D.Ru + D.Rg, D.d, N, 1, sms));
@@ -887,11 +955,16 @@ static int check_tile_dims(const fsvd_dims& D) {
   if (D.dtype != FSVD_DTYPE_BF16) return fail(FSVD_ERR_UNSUPPORTED, "batches above 8 need bf16 factors (dtype 0)");
   if (D.B < 9 || D.B > 128) return fail(FSVD_ERR_UNSUPPORTED, "batch outside 9..128");
   if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
-  if (D.Hk < 1 || D.H % D.Hk || D.H / D.Hk > kMaxG) return fail(FSVD_ERR_UNSUPPORTED, "H / Hk must be 1..8");
+  {
+    const int G = D.Hk > 0 && D.H % D.Hk == 0 ? D.H / D.Hk : 0;
+    if (G != 1 && G != 2 && G != 4 && G != 8) return fail(FSVD_ERR_UNSUPPORTED, "H / Hk must be 1, 2, 4 or 8");
+  }
   if (D.Rg != D.Ru) return fail(FSVD_ERR_UNSUPPORTED, "gate and up ranks must be equal for batches above 8");
   const int m8[] = {D.d, D.I, D.Rq, D.Rk, D.Rv, D.Ro, D.Rg, D.Ru, D.Rd};
   for (int v : m8)
     if (v <= 0 || v % 8) return fail(FSVD_ERR_ALIGN, "sizes and ranks must be positive multiples of 8");
+  if ((D.H * D.Dh + kTileM - 1) / kTileM > 1024 || (D.Hk * D.Dh + kTileM - 1) / kTileM > 1024)
+    return fail(FSVD_ERR_UNSUPPORTED, "more than 1024 row tiles in a q / k / v lift");
   if ((D.d + kTileM - 1) / kTileM > 4096 || (D.I + kTileM - 1) / kTileM > 4096 || (D.vocab + kTileM - 1) / kTileM > 4096)
     return fail(FSVD_ERR_UNSUPPORTED, "more than 4096 row tiles");
   if (D.S_max < 1) return fail(FSVD_ERR_ARG, "S_max");
@@ -926,9 +999,16 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   if ((e = plan_gemm(lp.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc))) return e;
   lp.g[1].a.out = qb;
   rope(lp.g[1].a, nullptr);
-  if ((e = plan_gemm(lp.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sc))) return e;
+  // (the three lifts run in one launch: each gets its own part of the scratch and of the counters)
+  const int N = round16(B);
+  Scratch sk = sc, sv = sc;
+  sk.part = sc.part + gemm_scratch_floats(HD, D.Rq, N, 1, g_sms);
+  sk.counters = sc.counters + 1024;
+  sv.part = sk.part + gemm_scratch_floats(KD, D.Rk, N, 1, g_sms);
+  sv.counters = sc.counters + 2048;
+  if ((e = plan_gemm(lp.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sk))) return e;
   rope(lp.g[2].a, Lw.k_cache);
-  if ((e = plan_gemm(lp.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc))) return e;
+  if ((e = plan_gemm(lp.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sv))) return e;
   rope(lp.g[3].a, Lw.v_cache);
   // attention
   AttnArgs& at = lp.at;
@@ -958,10 +1038,19 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   return 0;
 }
 
+template <int DH>
+static void launch_attn_g(const AttnArgs& at, unsigned grid, cudaStream_t st) {
+  switch (at.H / at.Hk) {
+    case 1: launch_pdl(batch_attn_kernel<DH, 1>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
+    case 2: launch_pdl(batch_attn_kernel<DH, 2>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
+    case 4: launch_pdl(batch_attn_kernel<DH, 4>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
+    default: launch_pdl(batch_attn_kernel<DH, 8>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
+  }
+}
 static int launch_attn(const AttnArgs& at, cudaStream_t st) {
   const unsigned grid = (unsigned)(at.B * at.Hk * at.nsplit);
-  if (at.Dh == 128) batch_attn_kernel<128><<<grid, kAttnThreads, 0, st>>>(at);
-  else batch_attn_kernel<64><<<grid, kAttnThreads, 0, st>>>(at);
+  if (at.Dh == 128) launch_attn_g<128>(at, grid, st);
+  else launch_attn_g<64>(at, grid, st);
   if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "attention kernel launch failed");
   fsvd_tile_count_launch();
   return 0;
@@ -974,15 +1063,20 @@ static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
   const __nv_bfloat16* mid = reinterpret_cast<const __nv_bfloat16*>(ws + L.mid);
   int e;
-  rmsnorm_rows_kernel<<<D.B, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x_in),
-                                           reinterpret_cast<const __nv_bfloat16*>(Lw.ln1_w), xn, D.d, D.eps);
+  launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(x_in),
+             reinterpret_cast<const __nv_bfloat16*>(Lw.ln1_w), xn, D.d, D.eps);
   fsvd_tile_count_launch();
-  for (int i = 0; i < 4; ++i)
-    if ((e = launch_gemm(lp.g[i], st))) return e;
+  if ((e = launch_gemm(lp.g[0], st))) return e;
+  {
+    // the q, k and v lifts read the same rank vector and write disjoint outputs: one launch
+    const GemmPlan* qkv[3] = {&lp.g[1], &lp.g[2], &lp.g[3]};
+    if ((e = launch_group(qkv, 3, st))) return e;
+  }
   if ((e = launch_attn(lp.at, st))) return e;
   if ((e = launch_gemm(lp.g[4], st))) return e;
   if ((e = launch_gemm(lp.g[5], st))) return e;
-  rmsnorm_rows_kernel<<<D.B, 256, 0, st>>>(mid, reinterpret_cast<const __nv_bfloat16*>(Lw.ln2_w), xn, D.d, D.eps);
+  launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, mid, reinterpret_cast<const __nv_bfloat16*>(Lw.ln2_w), xn,
+             D.d, D.eps);
   fsvd_tile_count_launch();
   for (int i = 6; i < 9; ++i)
     if ((e = launch_gemm(lp.g[i], st))) return e;
@@ -1085,16 +1179,19 @@ struct fsvd_tile_model {
 static int tile_model_record(fsvd_tile_model* m, cudaStream_t st) {
   const fsvd_dims& D = m->D;
   int e;
-  embed_rows_kernel<<<D.B, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(m->embed), m->tokens, m->xbuf[0], D.d, D.vocab);
+  launch_pdl(embed_rows_kernel, dim3(D.B), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(m->embed),
+             (const int*)m->tokens, m->xbuf[0], D.d, D.vocab);
   fsvd_tile_count_launch();
   for (int l = 0; l < D.n_layers; ++l)
     if ((e = run_layer(m->layers[l], m->down[l], D, m->lw[l], m->xbuf[l & 1], m->ws, m->L, st))) return e;
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(m->ws + m->L.xn);
-  rmsnorm_rows_kernel<<<D.B, 256, 0, st>>>(m->xbuf[D.n_layers & 1], reinterpret_cast<const __nv_bfloat16*>(m->final_norm), xn, D.d, D.eps);
+  launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, (const __nv_bfloat16*)m->xbuf[D.n_layers & 1],
+             reinterpret_cast<const __nv_bfloat16*>(m->final_norm), xn, D.d, D.eps);
   fsvd_tile_count_launch();
   if ((e = launch_gemm(m->head, st))) return e;
-  argmax_rows_kernel<<<D.B, 256, 0, st>>>(m->logits, D.vocab, m->tokens, m->token_log, m->step_counter, m->seqlens, m->max_steps, D.B);
-  bump_step_kernel<<<1, 1, 0, st>>>(m->step_counter);
+  launch_pdl(argmax_rows_kernel, dim3(D.B), dim3(256), 0, st, (const float*)m->logits, D.vocab, m->tokens, m->token_log,
+             m->step_counter, m->seqlens, m->max_steps, D.B);
+  launch_pdl(bump_step_kernel, dim3(1), dim3(1), 0, st, m->step_counter);
   fsvd_tile_count_launch();
   fsvd_tile_count_launch();
   if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed");

@@ -82,3 +82,32 @@ def test_decode_layer_tiles_7b_shape(dev, B):
     assert rel_linf(pk["k_cache"][:, 500:], kc_o[:, 500:]) <= TOL
     assert rel_linf(pk["v_cache"][:, 500:], vc_o[:, 500:]) <= TOL
     assert rel_linf(out, ref) <= TOL
+
+
+def _engine(dev, *, n_layers, batch, ctx, share_pairs=False, max_new=16):
+    import dataclasses
+
+    from flashsvd_b200 import synthetic
+
+    shape = dataclasses.replace(synthetic.LLAMA7B_SVD50, n_layers=n_layers)
+    eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=batch, ctx=ctx, max_new=max_new, seed=0,
+                                share_pairs=share_pairs)
+    return eng, shape
+
+
+@pytest.mark.parametrize("batch,ctx,share", [(16, 512, False), (32, 2048, True)])
+def test_model_tiles_teacher_forced(dev, batch, ctx, share):
+    """Whole-model steps (embed, layers, final norm, lm_head, argmax; one CUDA graph launch per
+    step) at the 7B width, 2 layers: logits of every step against the CPU oracle stepped on the GPU's
+    tokens.  (32, 2048, shared bases) is configuration 2's batch, context and factor layout."""
+    from oracle import check as OC
+
+    eng, shape = _engine(dev, n_layers=2, batch=batch, ctx=ctx, share_pairs=share)
+    assert eng.num_stages > 20          # launches per step here, not stages of one kernel
+    res = OC.teacher_forced(eng, shape, 3)
+    assert eng.status() == 0
+    eng.close()
+    print(f"B={batch} ctx={ctx}: logits rel_linf {[f'{v:.3e}' for v in res['rel_linf']]}, tokens equal "
+          f"{res['n_equal']}/{res['n_tokens']}")
+    assert max(res["rel_linf"]) <= 4e-2   # two layers + head; the per-layer bound is 2e-2
+    assert res["tokens_explained"]
