@@ -8,9 +8,10 @@
 // read from shared memory (128-byte swizzled, K-major, filled by TMA) and the fp32 accumulator in
 // tensor memory.  The work is still bound by the factor stream from HBM (each factor byte is used
 // for N <= 128 multiply-adds), so the kernel is organised around keeping TMA busy:
-//   * one CTA = one tile of 128 factor rows x one K segment; the segments of a tile are summed in
-//     segment order by the CTA that finishes last (arrival counter per tile), which also runs the
-//     epilogue, so the result does not depend on the order in which CTAs run;
+//   * one CTA = one tile of 128 factor rows x one K segment; the <= 8 segments of a tile are the CTAs
+//     of a thread-block cluster: they exchange their partial sums through distributed shared memory
+//     (each CTA finishes a slice of the batch columns, adding the segments in segment order), so
+//     no partial sum goes through global memory and the result does not depend on timing;
 //   * a ring of NS stages {W tile 16 KB, (second W tile), X tile(s)}: thread 0 issues the TMA copies
 //     as slots free up, thread 32 issues the MMAs as slots fill and releases a slot with
 //     tcgen05.commit, all four warps read the accumulator back with tcgen05.ld for the epilogue;
@@ -54,7 +55,7 @@ constexpr int kTileK = 64;           // bf16 elements of a k-block: one 128-byte
 constexpr int kThreads = 128;        // 4 warps: warp w reads accumulator lanes 32 w .. 32 w + 31
 constexpr int kWTileBytes = kTileM * kTileK * 2;   // 16 KB
 constexpr int kMaxStages = 8;
-constexpr int kMaxSegs = 16;
+constexpr int kMaxSegs = 8;           // K segments of a tile = CTAs of a cluster (portable size)
 
 enum TileEpi : int {
   TE_STORE = 0,      // out[b, p] = rnd(acc)                        (bf16)
@@ -72,8 +73,7 @@ struct GemmArgs {
   int nkb;                 // k-blocks in all
   int nstages, two, epi;
   uint32_t tmem_cols;      // power of two >= 32
-  float* scratch;          // [segs][tiles][nacc][N][128] fp32 partial tiles (segs > 1)
-  int* counters;           // [tiles], zero between launches
+  int cpo;                 // batch columns finished by each CTA of a tile's cluster, ceil(N / segs)
   void* out;
   const void* resid;
   void* cache;             // TE_ROPE_K / TE_VCACHE: [rows, S_max, Hk, Dh]
@@ -156,6 +156,17 @@ __device__ __forceinline__ uint32_t umma_idesc(int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 }
 
+// Cluster barrier (all threads of all CTAs of the cluster) and a store into the shared memory of
+// the cluster's CTA `rank` at the same offset as the local address `addr`.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float ldbf(const void* p, size_t i) {
   return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
@@ -211,7 +222,6 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + 1];
   __shared__ uint32_t tmem_slot;
   __shared__ int giveup_sh;
-  __shared__ int last_sh;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, seg = blockIdx.y;
@@ -225,7 +235,6 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
 
   if (tid == 0) {
     giveup_sh = 0;
-    last_sh = 0;
     for (int i = 0; i < NS; ++i) {
       mbar_init(full0 + 8 * i, 1);
       mbar_init(empty0 + 8 * i, 1);
@@ -318,117 +327,93 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   const int p = tile * kTileM + r;         // factor row
   const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
   const int nacc = a.two ? 2 : 1;
-  const bool rope = a.epi == TE_ROPE_Q || a.epi == TE_ROPE_K;
-  float* ftile = reinterpret_cast<float*>(base_ptr);   // [N][128] fp32, reuses the ring (RoPE epilogues)
+  const int cpo = a.cpo;                   // batch columns finished by each CTA of the cluster
 
-  bool last = true;
-  if (a.segs > 1) {
-    // partial tile to the scratch, then the arrival count of the tile decides who finishes it
-    if (have) {
-      for (int acc = 0; acc < nacc; ++acc) {
-        float* dst = a.scratch + (((size_t)seg * a.tiles + tile) * nacc + acc) * (size_t)(N * kTileM);
-        for (int c0 = 0; c0 < N; c0 += 16) {
-          float v[16];
-          tc_ld16(trow + (uint32_t)(acc * N + c0), v);
+  // ---- the K segments of a tile are the CTAs of one cluster (rank = segment).  CTA j finishes the
+  // batch columns [j cpo, (j + 1) cpo): every CTA sends its partial sums of those columns to CTA j's
+  // shared memory, slot [accumulator][segment][column][row]; the ring is free for that once every
+  // CTA of the cluster has its accumulators (first cluster barrier), and the sums are complete
+  // after the second.  Every CTA reaches both barriers, whatever happened before.
+  float* recv = reinterpret_cast<float*>(base_ptr);
+  const uint32_t recv_u32 = base;
+  cluster_sync();
+  if (have) {
+    for (int acc = 0; acc < nacc; ++acc) {
+      for (int c0 = 0; c0 < N; c0 += 16) {
+        float v[16];
+        tc_ld16(trow + (uint32_t)(acc * N + c0), v);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) dst[(size_t)(c0 + i) * kTileM + r] = v[i];
+        for (int i = 0; i < 16; ++i) {
+          const int col = c0 + i;
+          const int owner = col / cpo, slot = col - owner * cpo;
+          if (col < a.B && owner < a.segs)
+            st_cluster_f32(recv_u32 + (uint32_t)((((acc * a.segs + seg) * cpo + slot) * kTileM + r) * 4), (uint32_t)owner, v[i]);
         }
       }
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int old = atomicAdd(&a.counters[tile], 1);
-      last_sh = (old == a.segs - 1) ? 1 : 0;
-      if (old == a.segs - 1) a.counters[tile] = 0;   // ready for the next launch
-    }
-    __syncthreads();
-    last = last_sh != 0;
-    if (last) __threadfence();
   }
+  cluster_sync();
 
-  if (last && (have || a.segs > 1) && !*giveup) {
-    for (int c0 = 0; c0 < N; c0 += 16) {
-      float v[16], u[16];
-      if (a.segs > 1) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = u[i] = 0.0f;
-        for (int sg = 0; sg < a.segs; ++sg) {
-          const float* src = a.scratch + (((size_t)sg * a.tiles + tile) * nacc) * (size_t)(N * kTileM);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + (size_t)(c0 + i) * kTileM + r);
-          if (a.two) {
-            src += (size_t)(N * kTileM);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) u[i] += __ldcg(src + (size_t)(c0 + i) * kTileM + r);
-          }
-        }
-      } else {
-        tc_ld16(trow + (uint32_t)c0, v);
-        if (a.two) tc_ld16(trow + (uint32_t)(N + c0), u);
-      }
-      if (rope) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) ftile[(size_t)(c0 + i) * kTileM + r] = v[i];
-        continue;
-      }
-      if (p >= a.P) continue;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int b = c0 + i;
-        if (b >= a.B) break;
-        const size_t o = (size_t)b * a.P + p;
-        switch (a.epi) {
-          case TE_STORE:
-            stbf(a.out, o, v[i]);
-            break;
-          case TE_STORE_F32:
-            reinterpret_cast<float*>(a.out)[o] = rnd(v[i]);
-            break;
-          case TE_RESID:
-            stbf(a.out, o, ldbf(a.resid, o) + rnd(v[i]));
-            break;
-          case TE_SWIGLU: {
-            const float g = rnd(v[i]), up = rnd(u[i]);
-            const float sg = rnd(g / (1.0f + expf(-g)));
-            stbf(a.out, o, sg * up);
-          } break;
-          case TE_VCACHE: {
-            const int pos = a.seqlens[b];
-            if (pos < a.S_max)
-              stbf(a.cache, ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p, v[i]);
-            else
-              atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
-          } break;
-          default:
-            break;
-        }
-      }
-    }
-    if (rope) {
-      // rows (j, j + Dh/2) of a head sit in this tile (heads are Dh = 64 or 128 rows, tile-aligned)
-      __syncthreads();
-      const int half = a.Dh >> 1;
-      const int j = p % a.Dh;
-      if (p < a.P && j < half) {
-        for (int b = 0; b < a.B; ++b) {
+  if (!*giveup && have) {
+    const int half = a.Dh >> 1;
+    const bool rope = a.epi == TE_ROPE_Q || a.epi == TE_ROPE_K;
+    const int j = rope ? p % a.Dh : 0;
+    for (int slot = 0; slot < cpo; ++slot) {
+      const int b = seg * cpo + slot;
+      if (b >= a.B || p >= a.P) break;
+      float v = 0.0f, u = 0.0f;
+      for (int sg = 0; sg < a.segs; ++sg) v += recv[((size_t)(sg * cpo + slot)) * kTileM + r];
+      if (a.two)
+        for (int sg = 0; sg < a.segs; ++sg) u += recv[((size_t)((a.segs + sg) * cpo + slot)) * kTileM + r];
+      const size_t o = (size_t)b * a.P + p;
+      switch (a.epi) {
+        case TE_STORE:
+          stbf(a.out, o, v);
+          break;
+        case TE_STORE_F32:
+          reinterpret_cast<float*>(a.out)[o] = rnd(v);
+          break;
+        case TE_RESID:
+          stbf(a.out, o, ldbf(a.resid, o) + rnd(v));
+          break;
+        case TE_SWIGLU: {
+          const float g = rnd(v), up = rnd(u);
+          const float sg = rnd(g / (1.0f + expf(-g)));
+          stbf(a.out, o, sg * up);
+        } break;
+        case TE_VCACHE: {
+          const int pos = a.seqlens[b];
+          if (pos < a.S_max)
+            stbf(a.cache, ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p, v);
+          else
+            atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
+        } break;
+        case TE_ROPE_Q:
+        case TE_ROPE_K: {
+          // rows (j, j + Dh/2) of a head sit in this tile (heads are Dh = 64 or 128 rows, tile-aligned):
+          // the thread of row j < Dh/2 finishes both
+          if (j >= half) break;
+          float w = 0.0f;
+          for (int sg = 0; sg < a.segs; ++sg) w += recv[((size_t)(sg * cpo + slot)) * kTileM + r + half];
           const int pos = a.seqlens[b];
           const int pt = min(pos, a.S_max - 1);
           const float c = ldbf(a.cos_tab, (size_t)pt * half + j), sn = ldbf(a.sin_tab, (size_t)pt * half + j);
-          const float x1 = rnd(ftile[(size_t)b * kTileM + r]), x2 = rnd(ftile[(size_t)b * kTileM + r + half]);
+          const float x1 = rnd(v), x2 = rnd(w);
           const float o1 = rnd(rnd(x1 * c) - rnd(x2 * sn));
           const float o2 = rnd(rnd(x2 * c) + rnd(x1 * sn));
           if (a.epi == TE_ROPE_Q) {
-            stbf(a.out, (size_t)b * a.P + p, o1);
-            stbf(a.out, (size_t)b * a.P + p + half, o2);
+            stbf(a.out, o, o1);
+            stbf(a.out, o + half, o2);
           } else if (pos < a.S_max) {
-            const size_t o = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p;
-            stbf(a.cache, o, o1);
-            stbf(a.cache, o + half, o2);
+            const size_t oc = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p;
+            stbf(a.cache, oc, o1);
+            stbf(a.cache, oc + half, o2);
           } else {
             atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
           }
-        }
+        } break;
+        default:
+          break;
       }
     }
   }
@@ -787,17 +772,7 @@ static void split_k(int tiles, int nkb, int sms, int& segs, int& kbs) {
   segs = (nkb + kbs - 1) / kbs;
 }
 
-// Scratch floats a GEMM of P rows and K columns needs for its partial tiles.
-static size_t gemm_scratch_floats(int P, int K, int N, int nacc, int sms) {
-  const int tiles = (P + kTileM - 1) / kTileM, nkb = (K + kTileK - 1) / kTileK;
-  int segs, kbs;
-  split_k(tiles, nkb, sms, segs, kbs);
-  return segs > 1 ? (size_t)segs * tiles * nacc * N * kTileM : 0;
-}
-
 struct Scratch {
-  float* part;     // partial tiles
-  int* counters;   // tile arrival counters (>= max tiles ints, zero between launches)
   int* status;
   long long wait_limit;
 };
@@ -831,15 +806,16 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   if (ns < 1) return fail(FSVD_ERR_UNSUPPORTED, "shared memory too small for one stage");
   a.nstages = ns;
   size_t smem = 1024 + (size_t)ns * stage;
-  if ((epi == TE_ROPE_Q || epi == TE_ROPE_K) && smem < 1024 + (size_t)N * kTileM * 4) smem = 1024 + (size_t)N * kTileM * 4;
+  // the ring is reused for the partial sums the cluster's CTAs send each other
+  const size_t recv = (size_t)nacc * a.segs * ((N + a.segs - 1) / a.segs) * kTileM * 4;
+  if (smem < 1024 + recv) smem = 1024 + recv;
   // co-resident CTAs must not ask for more than the 512 tensor-memory columns of an SM
   const size_t floor_smem = (size_t)232448 / (512 / cols + 1) + 1024;
   if (smem < floor_smem) smem = floor_smem;
   if (smem > (size_t)g_smem_optin - 1024) return fail(FSVD_ERR_UNSUPPORTED, "shared memory plan exceeds the device limit");
   g.smem = smem;
   g.grid = dim3((unsigned)a.tiles, (unsigned)a.segs);
-  a.scratch = sc.part;
-  a.counters = sc.counters;
+  a.cpo = (N + a.segs - 1) / a.segs;
   a.status = sc.status;
   a.wait_limit = sc.wait_limit;
   if (int e = encode_sw128(&g.mapA, W, P, K, ldw, kTileM)) return e;
@@ -856,18 +832,30 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
 
 // Launch with the programmatic-stream-serialization attribute (see pdl_wait above).
 template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+static cudaError_t launch_pdl_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, unsigned cluster_y,
+                                      cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
+  if (cluster_y > 0) {
+    at[1].id = cudaLaunchAttributeClusterDimension;
+    at[1].val.clusterDim.x = 1;
+    at[1].val.clusterDim.y = cluster_y;
+    at[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  return launch_pdl_cluster(kern, grid, block, smem, 0u, st, std::forward<Args>(args)...);
 }
 
 static int launch_group(const GemmPlan* const* plans, int n, cudaStream_t st);
@@ -898,7 +886,8 @@ static int launch_group(const GemmPlan* const* plans, int n, cudaStream_t st) {
     if (g.grid.y > grid.y) grid.y = g.grid.y;
     if (g.smem > smem) smem = g.smem;
   }
-  if (launch_pdl(tile_gemm_kernel, grid, dim3(kThreads), smem, st, grp) != cudaSuccess)
+  // grid.y = K segments = CTAs of a cluster (the problems of a group have the same number)
+  if (launch_pdl_cluster(tile_gemm_kernel, grid, dim3(kThreads), smem, grid.y, st, grp) != cudaSuccess)
     return fail(FSVD_ERR_CUDA, "tile kernel launch failed");
   fsvd_tile_count_launch();
   return 0;
@@ -923,9 +912,7 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
   const int Rqkv = D.Rq + D.Rk + D.Rv;
   size_t o = 0;
   L.sync = o;      o += al256(sizeof(SyncState));
-  L.counters = o;  o += 4096 * 4;                      // GEMM tiles (<= 4096) ...
-  const size_t acnt = al256((size_t)B * D.Hk * 4);     // ... and attention heads
-  o += acnt;
+  L.counters = o;  o += al256((size_t)B * D.Hk * 4);   // attention: arrivals of the splits of a head
   L.xn = o;        o += al256((size_t)B * imax(D.d, 8) * 2);
   L.pbuf = o;      o += al256((size_t)B * imax(imax(Rqkv, D.Ru + D.Rg), imax(D.Ro, D.Rd)) * 2);
   L.qbuf = o;      o += al256((size_t)B * HD * 2);
@@ -934,8 +921,7 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
   L.hact = o;      o += al256((size_t)B * D.I * 2);
   L.nsplit = attn_nsplit(D, sms);
   L.apart = o;     o += al256((size_t)B * D.Hk * L.nsplit * (D.H / imax(D.Hk, 1)) * (D.Dh + 2) * 4);
-  size_t fl = 0;
-  auto mx = [&](size_t v) { if (v > fl) fl = v; };
+#if 0
   mx(gemm_scratch_floats(Rqkv, D.d, N, 1, sms));
   mx(gemm_scratch_floats(HD, D.Rq, N, 1, sms) + gemm_scratch_floats(KD, D.Rk, N, 1, sms) +
      gemm_scratch_floats(KD, D.Rv, N, 1, sms));   // one launch
@@ -946,7 +932,8 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
   mx(gemm_scratch_floats(D.Rd, D.I, N, 1, sms));
   mx(gemm_scratch_floats(D.d, D.Rd, N, 1, sms));
   if (D.vocab > 0) mx(gemm_scratch_floats(D.vocab, D.d, N, 1, sms));
-  L.part = o;      o += al256(fl * 4);
+#endif
+  L.part = o;
   L.total = o;
   return L;
 }
@@ -979,8 +966,7 @@ struct LayerPlan {
 static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, const void* cos_tab, const void* sin_tab,
                       const int* seqlens, const void* x_in, void* x_out, char* ws, const TileWs& L, long long wait_limit) {
   const int B = D.B, HD = D.H * D.Dh, KD = D.Hk * D.Dh, Rqkv = D.Rq + D.Rk + D.Rv;
-  Scratch sc = {reinterpret_cast<float*>(ws + L.part), reinterpret_cast<int*>(ws + L.counters),
-                &reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
+  Scratch sc = {&reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
   __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(ws + L.pbuf);
   __nv_bfloat16* qb = reinterpret_cast<__nv_bfloat16*>(ws + L.qbuf);
@@ -999,16 +985,9 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   if ((e = plan_gemm(lp.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc))) return e;
   lp.g[1].a.out = qb;
   rope(lp.g[1].a, nullptr);
-  // (the three lifts run in one launch: each gets its own part of the scratch and of the counters)
-  const int N = round16(B);
-  Scratch sk = sc, sv = sc;
-  sk.part = sc.part + gemm_scratch_floats(HD, D.Rq, N, 1, g_sms);
-  sk.counters = sc.counters + 1024;
-  sv.part = sk.part + gemm_scratch_floats(KD, D.Rk, N, 1, g_sms);
-  sv.counters = sc.counters + 2048;
-  if ((e = plan_gemm(lp.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sk))) return e;
+  if ((e = plan_gemm(lp.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sc))) return e;
   rope(lp.g[2].a, Lw.k_cache);
-  if ((e = plan_gemm(lp.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sv))) return e;
+  if ((e = plan_gemm(lp.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc))) return e;
   rope(lp.g[3].a, Lw.v_cache);
   // attention
   AttnArgs& at = lp.at;
@@ -1017,7 +996,7 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   at.vcache = reinterpret_cast<const __nv_bfloat16*>(Lw.v_cache);
   at.seqlens = seqlens; at.out = attn;
   at.part = reinterpret_cast<float*>(ws + L.apart);
-  at.counters = reinterpret_cast<int*>(ws + L.counters) + 4096;
+  at.counters = reinterpret_cast<int*>(ws + L.counters);
   at.B = B; at.H = D.H; at.Hk = D.Hk; at.Dh = D.Dh; at.S_max = D.S_max; at.nsplit = L.nsplit; at.seqlen_add = 1;
   at.shared_cache = D.rows_are_positions ? 1 : 0;
   at.scale = 1.0f / sqrtf((float)D.Dh);
@@ -1067,10 +1046,14 @@ static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_
              reinterpret_cast<const __nv_bfloat16*>(Lw.ln1_w), xn, D.d, D.eps);
   fsvd_tile_count_launch();
   if ((e = launch_gemm(lp.g[0], st))) return e;
-  {
+  if (lp.g[1].a.segs == lp.g[2].a.segs && lp.g[1].a.segs == lp.g[3].a.segs) {
     // the q, k and v lifts read the same rank vector and write disjoint outputs: one launch
+    // (possible when they cut K into the same number of segments = cluster size)
     const GemmPlan* qkv[3] = {&lp.g[1], &lp.g[2], &lp.g[3]};
     if ((e = launch_group(qkv, 3, st))) return e;
+  } else {
+    for (int i = 1; i < 4; ++i)
+      if ((e = launch_gemm(lp.g[i], st))) return e;
   }
   if ((e = launch_attn(lp.at, st))) return e;
   if ((e = launch_gemm(lp.g[4], st))) return e;
@@ -1087,8 +1070,7 @@ static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_
 
 static int plan_down_lift(GemmPlan& g, const fsvd_dims& D, const fsvd_layer& Lw, void* x_out, char* ws, const TileWs& L,
                           long long wait_limit) {
-  Scratch sc = {reinterpret_cast<float*>(ws + L.part), reinterpret_cast<int*>(ws + L.counters),
-                &reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
+  Scratch sc = {&reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
   if (int e = plan_gemm(g, Lw.down_u, nullptr, D.d, D.Rd, D.Rd, ws + L.pbuf, nullptr, D.Rd, D.B, TE_RESID, sc)) return e;
   g.a.out = x_out;
   g.a.resid = ws + L.mid;
@@ -1250,8 +1232,7 @@ int fsvd_tile_model_create(const fsvd_dims* dims, const fsvd_layer* layers, cons
     if (!e) e = plan_down_lift(m->down[l], D, layers[l], m->xbuf[(l + 1) & 1], m->ws, m->L, wait_limit);
   }
   if (!e) {
-    Scratch sc = {reinterpret_cast<float*>(m->ws + m->L.part), reinterpret_cast<int*>(m->ws + m->L.counters),
-                  &reinterpret_cast<SyncState*>(m->ws + m->L.sync)->status, wait_limit};
+    Scratch sc = {&reinterpret_cast<SyncState*>(m->ws + m->L.sync)->status, wait_limit};
     e = plan_gemm(m->head, lm_head, nullptr, D.vocab, D.d, D.d, m->ws + m->L.xn, nullptr, D.d, D.B, TE_STORE_F32, sc);
     m->head.a.out = m->logits;
   }
