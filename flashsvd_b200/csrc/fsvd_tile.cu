@@ -12,7 +12,7 @@
 //     of a thread-block cluster: they exchange their partial sums through distributed shared memory
 //     (each CTA finishes a slice of the batch columns, adding the segments in segment order), so
 //     no partial sum goes through global memory and the result does not depend on timing;
-//   * a ring of NS stages {W tile 16 KB, (second W tile), X tile(s)}: thread 0 issues the TMA copies
+//   * a ring of NS stages {W tile 16 KB, (second W tile), X tile(s)}: three threads issue the TMA copies
 //     as slots free up, thread 32 issues the MMAs as slots fill and releases a slot with
 //     tcgen05.commit, all four warps read the accumulator back with tcgen05.ld for the epilogue;
 //   * epilogues: store / residual / SwiGLU (two accumulators) / RoPE + q buffer / RoPE + key cache /
@@ -256,12 +256,20 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   const int kb0 = seg * a.kbs, kb1 = min(a.nkb, kb0 + a.kbs);
   const int nit = kb1 - kb0;
 
-  if (warp == 0) {
+  if (warp != 1) {
     if (lane == 0) {
-      // ---- producer: TMA copies of the stage operands.  The factor tiles of the first NS stages do
-      // not depend on the kernel before this one and are requested before pdl_wait().
+      // ---- producers: TMA copies of the stage operands.  One thread sustains about 24 GB/s of
+      // copies (wait, arm, issue per box), so three threads (warps 0, 2, 3) share the stages.  A
+      // ring slot always belongs to the same thread (slot % 3): a parity wait cannot tell phase k of
+      // a slot's barrier from phase k + 2, and only a slot's single owner, which visits its rounds in
+      // order, can never be two phases behind.
+      // The factor tiles of the first NS stages do not depend on the kernel before this one and
+      // are requested before pdl_wait().
+      const int pj = warp == 0 ? 0 : warp - 1;
+      constexpr int kProducers = 3;
       const int pre = min(nit, NS);
       for (int it = 0; it < pre; ++it) {
+        if (it % kProducers != pj) continue;
         const uint32_t fb = full0 + 8 * it;
         const uint32_t dst = base + (uint32_t)it * stage_bytes;
         const int kcol = (kb0 + it) * kTileK;
@@ -272,6 +280,7 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
       pdl_wait();
       for (int it = 0; it < nit; ++it) {
         const int s = it % NS, round = it / NS;
+        if (s % kProducers != pj) continue;
         if (round > 0 && !wait_bar(empty0 + 8 * s, (uint32_t)(round - 1) & 1u, giveup, a, DS_COPY_TIMEOUT)) break;
         const uint32_t fb = full0 + 8 * s;
         uint32_t dst = base + (uint32_t)s * stage_bytes;
@@ -798,8 +807,9 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   int ns = (int)((size_t)(g_smem_optin - 2048) / stage);
   if (ns > kMaxStages) ns = kMaxStages;
   if (ns > a.kbs) ns = a.kbs;
-  // more CTAs than SMs: keep the ring small enough for two CTAs per SM
-  if (a.tiles * a.segs > g_sms && ns > 2 && (size_t)ns * stage > 110 * 1024) {
+  // keep the ring small enough for two CTAs per SM: the clusters of a launch then fit the GPCs in
+  // one wave (with one CTA per SM, 24 clusters of 6 do not fit 8 GPCs of 16-20 SMs)
+  if (ns > 2 && (size_t)ns * stage > 110 * 1024) {
     ns = (int)((size_t)(110 * 1024) / stage);
     if (ns < 2) ns = 2;
   }
