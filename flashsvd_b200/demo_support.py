@@ -1,0 +1,167 @@
+"""The reference's public helper surface (scripts/demo_support/__init__.py:1-24) on top of this
+package: the same names, arguments and result dictionaries, so code written against
+``scripts.demo_support`` runs with ``from flashsvd_b200 import demo_support``.
+
+Loading covers the formats that need no network: a ``torch.save({'model': ..., 'tokenizer': ...})``
+file (utils/model_utils.py:850-901) and a directory with ``config.json`` + a state dict whose keys
+carry the ``*_v_proj`` / ``*_u_proj`` factor names (utils/model_utils.py:637-643).  Models with
+low-rank modules decode through the CUDA library (``generate_text`` builds and keeps a
+``DecodeEngine`` for them); any other transformers model takes the plain token loop.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Any, Optional
+
+import torch
+
+from .runtime import configure_runtime, generate_text, runtime_env_snapshot  # noqa: F401
+
+__version__ = "1.5.0"
+
+_DTYPES = {"fp16": torch.float16, "float16": torch.float16, "half": torch.float16, "bf16": torch.bfloat16,
+           "bfloat16": torch.bfloat16, "fp32": torch.float32, "float32": torch.float32, "float": torch.float32}
+
+
+def cast_model_for_inference(model: Any, *, dtype: str = "auto", device=None):
+    """dtype "auto": bf16 on CUDA, fp32 on CPU (scripts/demo_support/api.py:146-177)."""
+    raw = str(dtype).strip().lower()
+    if device is None:
+        try:
+            target = next(model.parameters()).device
+        except StopIteration:
+            target = torch.device("cpu")
+    else:
+        target = torch.device(device)
+    if raw == "auto":
+        want = torch.bfloat16 if target.type == "cuda" else torch.float32
+    elif raw in _DTYPES:
+        want = _DTYPES[raw]
+    else:
+        raise ValueError(f"Unsupported dtype {dtype!r}")
+    model = model.to(device=target, dtype=want)
+    model.eval()
+    return model
+
+
+def build_svd_llama(config, state_dict: Optional[dict] = None):
+    """A transformers LlamaForCausalLM whose layers hold ``SVD_LlamaAttention`` / ``SVD_LlamaMLP``
+    with the ranks found in ``state_dict`` (or the rank formula at ``config.flash_svd_ratio``)."""
+    from transformers import LlamaForCausalLM
+
+    from .modules import SVD_LlamaAttention, SVD_LlamaMLP
+
+    ratio = float(getattr(config, "flash_svd_ratio", 0.5))
+    model = LlamaForCausalLM(config)
+    for li, layer in enumerate(model.model.layers):
+        attn = SVD_LlamaAttention(config, ratio=ratio, layer_idx=li)
+        mlp = SVD_LlamaMLP(config.hidden_size, config.intermediate_size, getattr(config, "hidden_act", "silu"), ratio=ratio)
+        if state_dict is not None:
+            for mod, holder in ((attn, "self_attn"), (mlp, "mlp")):
+                for name, lin in list(mod.named_children()):
+                    w = state_dict.get(f"model.layers.{li}.{holder}.{name}.weight")
+                    if w is not None and isinstance(lin, torch.nn.Linear) and tuple(w.shape) != tuple(lin.weight.shape):
+                        setattr(mod, name, torch.nn.Linear(w.shape[1], w.shape[0], bias=False))
+            attn.low_rank = attn.q_u_proj.in_features
+        layer.self_attn, layer.mlp = attn, mlp
+    if state_dict is not None:
+        missing, unexpected = model.load_state_dict(state_dict, strict=False)
+        bad = [k for k in missing if "rotary" not in k]
+        if bad:
+            raise ValueError(f"state dict lacks {len(bad)} tensors, e.g. {bad[:3]}")
+    return model
+
+
+def get_model_from_local(path: str):
+    """(model, tokenizer) from a torch.save'd ``{'model', 'tokenizer'}`` file, or from a directory
+    with ``config.json`` and ``pytorch_model.bin`` / ``model.pt`` holding a factored Llama state dict."""
+    p = Path(path).expanduser()
+    if p.is_dir():
+        cfg_path = p / "config.json"
+        if not cfg_path.exists():
+            raise FileNotFoundError(f"{p} has no config.json")
+        from transformers import LlamaConfig
+
+        raw = json.loads(cfg_path.read_text())
+        config = LlamaConfig(**{k: v for k, v in raw.items() if k not in ("architectures", "model_type", "auto_map")})
+        weights = next((p / n for n in ("pytorch_model.bin", "model.pt", "model.bin") if (p / n).exists()), None)
+        if weights is None:
+            raise FileNotFoundError(f"{p} has no pytorch_model.bin / model.pt")
+        sd = torch.load(weights, map_location="cpu", weights_only=True)
+        if not any(k.endswith("q_u_proj.weight") for k in sd):
+            raise ValueError("the state dict has no *_u_proj / *_v_proj factors: not a FlashSVD Llama export")
+        tok = None
+        if any((p / n).exists() for n in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
+            try:
+                from transformers import AutoTokenizer
+
+                tok = AutoTokenizer.from_pretrained(str(p), local_files_only=True)
+            except Exception:
+                tok = None
+        return build_svd_llama(config, sd), tok
+    if not p.exists():
+        raise FileNotFoundError(str(p))
+    obj = torch.load(p, map_location="cpu", weights_only=False)
+    if isinstance(obj, dict) and "model" in obj:
+        return obj["model"], obj.get("tokenizer")
+    raise ValueError("expected torch.save({'model': model, 'tokenizer': tokenizer}, path)")
+
+
+def get_model_from_huggingface(name: str, *, hf_token: Optional[str] = None, torch_dtype=None):
+    raise RuntimeError(f"{name!r} is not a local path: downloading checkpoints is outside this package "
+                       "(pass a local file or directory)")
+
+
+def get_model_from_source(source: str, *, hf_token: Optional[str] = None, torch_dtype=None):
+    raw = str(source).strip()
+    local = Path(raw).expanduser()
+    if local.exists():
+        return get_model_from_local(str(local))
+    return get_model_from_huggingface(raw, hf_token=hf_token, torch_dtype=torch_dtype)
+
+
+def load_for_inference(source: str, *, hf_token: Optional[str] = None, dtype: str = "auto", device="cpu"):
+    model, tokenizer = get_model_from_source(source, hf_token=hf_token)
+    return cast_model_for_inference(model, dtype=dtype, device=device), tokenizer
+
+
+@torch.inference_mode()
+def decode_kvcache_eval(model, *, prompt_len: int = 2048, new_tokens: int = 128, batch_size: int = 1,
+                        device: str = "cuda", warmup: int = 5, max_cache_len: Optional[int] = None, **flags) -> dict:
+    """Decode benchmark with the reference's protocol (utils/evaluator.py:272-540): a prompt of
+    ``prompt_len`` random tokens fills the cache, ``warmup`` untimed steps, then ``new_tokens`` timed
+    single-token steps between CUDA events.  ``model`` is a ``DecodeEngine`` or a model with low-rank
+    modules.  Returns decode_ms_per_token and decode_tokens_per_s (plus the sizes)."""
+    from .engine import DecodeEngine, engine_for_model
+
+    del flags
+    if max_cache_len is None:
+        max_cache_len = int(prompt_len) + int(warmup) + int(new_tokens) + 1
+    eng = model if isinstance(model, DecodeEngine) else engine_for_model(
+        model, batch_size=int(batch_size), max_cache_len=int(max_cache_len),
+        max_steps=int(prompt_len) + int(warmup) + int(new_tokens) + 8)
+    vocab = eng.vocab
+    prompt = torch.randint(0, vocab, (eng.B, int(prompt_len)), device=eng.device, dtype=torch.int32)
+    eng.reset()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    eng.prefill(prompt)
+    e1.record()
+    if warmup > 0:
+        eng.step(int(warmup))
+    torch.cuda.synchronize()
+    e1.record()
+    eng.step(int(new_tokens))
+    e2.record()
+    torch.cuda.synchronize()
+    ms = e1.elapsed_time(e2)
+    if eng.status() != 0:
+        raise RuntimeError("a device-side wait ran out during the benchmark")
+    return {"prompt_len": int(prompt_len), "new_tokens": int(new_tokens), "batch_size": int(eng.B),
+            "decode_ms_per_token": ms / int(new_tokens), "decode_tokens_per_s": eng.B * int(new_tokens) / (ms * 1e-3)}
+
+
+__all__ = ["__version__", "cast_model_for_inference", "configure_runtime", "decode_kvcache_eval", "generate_text",
+           "get_model_from_huggingface", "get_model_from_local", "get_model_from_source", "load_for_inference",
+           "runtime_env_snapshot", "build_svd_llama"]

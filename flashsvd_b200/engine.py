@@ -246,3 +246,94 @@ def _from_ptr(ptr: int, shape, dtype, device) -> torch.Tensor:
     }
     with torch.cuda.device(device):
         return torch.as_tensor(h, device=device)
+
+
+# ---- engines for transformers models that hold low-rank modules ---------------------------------
+_FACTOR_NAMES = (("q", "self_attn"), ("k", "self_attn"), ("v", "self_attn"), ("o", "self_attn"),
+                 ("gate", "mlp"), ("up", "mlp"), ("down", "mlp"))
+
+
+def has_lowrank_modules(model) -> bool:
+    """True for a Llama-shaped transformers model whose layers hold ``*_v_proj`` / ``*_u_proj``
+    factor pairs (the reference's SVD_LlamaAttention / SVD_LlamaMLP, utils/model_utils.py:637-643)."""
+    layers = getattr(getattr(model, "model", None), "layers", None)
+    if not layers:
+        return False
+    attn, mlp = getattr(layers[0], "self_attn", None), getattr(layers[0], "mlp", None)
+    return hasattr(attn, "q_u_proj") and hasattr(attn, "q_v_proj") and hasattr(mlp, "gate_u_proj")
+
+
+def engine_for_model(model, *, batch_size: int = 1, max_cache_len: int = 2048, max_steps: int = 4096):
+    """A ``DecodeEngine`` over the weights of ``model`` (a transformers LlamaForCausalLM whose
+    layers hold low-rank modules), built once and kept on the model; a longer cache or another
+    batch size builds a new one.  Factor weights are packed into the kernels' layout; ``*_v_proj``
+    weights that several layers share (basis sharing: the same storage) are packed once and shared
+    by those layers in the engine too."""
+    from . import packing
+
+    if not has_lowrank_modules(model):
+        raise TypeError("the model has no *_v_proj / *_u_proj factor modules")
+    emb = model.model.embed_tokens.weight
+    if not emb.is_cuda:
+        raise RuntimeError("flashsvd_b200 runs on CUDA tensors only (there is no CPU path): move the model to a GPU")
+    key = (int(batch_size), str(emb.device), emb.dtype)
+    cached = getattr(model, "_flashsvd_b200_engines", None)
+    if cached is None:
+        cached = {}
+        object.__setattr__(model, "_flashsvd_b200_engines", cached)
+    eng = cached.get(key)
+    if eng is not None and eng.S_max >= int(max_cache_len):
+        return eng
+    if eng is not None:
+        eng.close()
+    cfg = model.config
+    dev, dtype = emb.device, emb.dtype
+    shared: dict = {}
+
+    def once(t):   # one device copy per storage: tied input-side factors stay one buffer
+        k = (t.data_ptr(), tuple(t.shape))
+        if k not in shared:
+            shared[k] = t.detach()
+        return shared[k]
+
+    packed_v: dict = {}
+    layers = []
+    for layer in model.model.layers[: cfg.num_hidden_layers]:
+        w = {"ln1": layer.input_layernorm.weight, "ln2": layer.post_attention_layernorm.weight}
+        for name, holder in _FACTOR_NAMES:
+            mod = getattr(layer, holder)
+            w[f"{name}_v"] = once(getattr(mod, f"{name}_v_proj").weight)
+            w[f"{name}_u"] = once(getattr(mod, f"{name}_u_proj").weight)
+        pk = packing.pack_layer(w, device=dev, dtype=dtype)
+        # the concatenated input-side factors of layers that tie all of their parts are shared too
+        for cat_name, parts in (("qkv_v", ("q_v", "k_v", "v_v")), ("upgate_v", ("up_v", "gate_v"))):
+            k = tuple(w[p_].data_ptr() for p_ in parts)
+            if k in packed_v:
+                pk[cat_name] = packed_v[k]
+            else:
+                packed_v[k] = pk[cat_name]
+        for single in ("o_v", "down_v"):
+            k = (w[single].data_ptr(),)
+            if k in packed_v:
+                pk[single] = packed_v[k]
+            else:
+                packed_v[k] = pk[single]
+        layers.append(pk)
+    H = cfg.num_attention_heads
+    eng = DecodeEngine(layers=layers, embed=emb.detach().contiguous(),
+                       final_norm=model.model.norm.weight.detach().contiguous(),
+                       lm_head=model.lm_head.weight.detach().contiguous(), num_heads=H,
+                       num_kv_heads=getattr(cfg, "num_key_value_heads", H),
+                       head_dim=getattr(cfg, "head_dim", None) or cfg.hidden_size // H, batch_size=int(batch_size),
+                       max_cache_len=int(max_cache_len), rope_theta=_rope_theta(cfg),
+                       eps=float(getattr(cfg, "rms_norm_eps", 1e-6)), max_steps=int(max_steps))
+    cached[key] = eng
+    return eng
+
+
+def _rope_theta(cfg) -> float:
+    theta = getattr(cfg, "rope_theta", None)
+    if theta is None:
+        rp = getattr(cfg, "rope_parameters", None) or {}
+        theta = rp.get("rope_theta", 10000.0) if isinstance(rp, dict) else 10000.0
+    return float(theta)

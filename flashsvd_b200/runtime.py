@@ -98,7 +98,15 @@ def configure_runtime(mode: str = "flashsvd", *, ffn_backend: str = "auto", enab
 
 
 # --------------------------------------------------------------------------------- KV cache
-class FlashSVDV15DenseKVCache:
+try:   # the reference's cache is a transformers Cache (runtime/cache/attn_dense_kv.py:4-7)
+    from transformers.cache_utils import Cache as _CacheBase
+except Exception:   # pragma: no cover - transformers is optional for the kernel-level API
+    class _CacheBase:   # type: ignore
+        def __init__(self, *a, **k):
+            pass
+
+
+class FlashSVDV15DenseKVCache(_CacheBase):
     """Dense KV cache in the layout the decode kernels read: ``key_cache[l]`` / ``value_cache[l]``
     are ``[max_batch, max_cache_len, Hk, Dh]``, zero-initialised, shaped on first use; K is stored
     after RoPE; the number of tokens seen is advanced by layer 0 only."""
@@ -107,6 +115,10 @@ class FlashSVDV15DenseKVCache:
 
     def __init__(self, config, *, max_batch_size: int, max_cache_len: int, device=None,
                  dtype: torch.dtype = torch.float16, layer_device_map: Optional[dict] = None) -> None:
+        try:   # transformers 5.x wants the layer list, 4.x takes no argument (attn_dense_kv.py:29-32)
+            super().__init__(layers=[])
+        except TypeError:
+            super().__init__()
         self._config = config
         self._max_batch_size = int(max_batch_size)
         self._max_cache_len = int(max_cache_len)
@@ -221,6 +233,38 @@ class FlashSVDV15DenseKVCache:
         else:
             sl.fill_(int(cache_position))
         return self.key_cache[layer_idx][:B], self.value_cache[layer_idx][:B], sl
+
+    def prepare_fa2_direct_write_step(self, layer_idx: int, *, batch_size: int, num_heads: int, head_dim: int,
+                                      q_len: int, cache_position=None):
+        """(k_cache[:B], v_cache[:B], k_slot, v_slot, cache_seqlens) for a step whose new key / value
+        are written by the caller straight into ``k_slot`` / ``v_slot`` = cache[:, start:start + 1];
+        ``cache_seqlens`` is filled with start + 1 (the keys to attend).  None when q_len != 1 or the
+        positions differ per row; IndexError past the end (runtime/cache/attn_dense_kv.py:258-311)."""
+        layer_idx, B, q_len = int(layer_idx), int(batch_size), int(q_len)
+        if q_len != 1:
+            return None
+        self._ensure_layer_spec(layer_idx, h=int(num_heads), dh=int(head_dim))
+        kc_full, vc_full = self.key_cache[layer_idx], self.value_cache[layer_idx]
+        if cache_position is None:
+            start = int(self.get_seq_length())
+        elif torch.is_tensor(cache_position):
+            pos = cache_position.to(dtype=torch.int64).reshape(-1)
+            if int(pos.numel()) == 0:
+                return None
+            first = int(pos[0].item())
+            if int(pos.numel()) > 1 and bool(torch.any(pos != first).item()):
+                return None
+            start = first
+        else:
+            start = int(cache_position)
+        if start < 0 or start + q_len > self._max_cache_len:
+            raise IndexError(f"FlashSVDV15DenseKVCache write position out of range: start={start} q_len={q_len} "
+                             f"max={self._max_cache_len}")
+        kc, vc = kc_full[:B], vc_full[:B]
+        sl = self._seqlens_buffer(layer_idx, B)
+        sl.fill_(start + q_len)
+        self._layer_initialized[layer_idx] = True
+        return kc, vc, kc[:, start:start + q_len], vc[:, start:start + q_len], sl
 
     def get_fa2_kvcache(self, layer_idx: int, *, batch_size: int):
         return self.prepare_fa2_step(layer_idx, batch_size=batch_size, cache_position=None)
@@ -352,6 +396,131 @@ def reconstruct_qkv_token_shared_prepacked(Pq, Pk, Pv, Vq_flat, Vk_flat, Vv_flat
     return tuple(outs)
 
 
+_head_base_cache: dict = {}
+
+
+def _lift_heads(P, V, ws):
+    """P[B, R] x V[Hx, R, Dh] (per-head bases as the reference modules expose them) -> [B, Hx, Dh].
+    The kernels read the nn.Linear layout [Hx * Dh, R]; that copy is made once per base tensor."""
+    from . import ops
+
+    Hx, R, Dh = V.shape
+    key = (V.data_ptr(), V._version, tuple(V.shape), V.dtype, str(V.device))
+    w = _head_base_cache.get(key)
+    if w is None:
+        if len(_head_base_cache) > 256:
+            _head_base_cache.clear()
+        w = V.permute(0, 2, 1).reshape(Hx * Dh, R).contiguous()
+        _head_base_cache[key] = w
+    return ops.lift(P.contiguous(), w, ws).view(P.shape[0], Hx, Dh)
+
+
+def reconstruct_qkv_token_shared_hetero(Pq, Pk, Pv, Vq, Vk, Vv, *, bq=None, bk=None, bv=None, BD: int = 64,
+                                        BR: int = 64, num_warps: int = 4, num_stages: int = 2):
+    """Current-token q/k/v from rank space with per-head bases Vq[H, Rq, Dh], Vk[Hk, Rk, Dh],
+    Vv[Hk, Rv, Dh] and possibly different ranks; the tile arguments of the reference's Triton
+    launch are accepted and ignored (kernels/attn/decode/densekv_reconstruct_triton.py:559-659)."""
+    if not all(t.is_cuda for t in (Pq, Pk, Pv, Vq, Vk, Vv)):
+        raise ValueError("reconstruct_qkv_token_shared_hetero expects all tensors on CUDA.")
+    if Pq.ndim != 2 or Pk.ndim != 2 or Pv.ndim != 2:
+        raise ValueError(f"Expected Pq/Pk/Pv to be 2D [B,R*], got {tuple(Pq.shape)}/{tuple(Pk.shape)}/{tuple(Pv.shape)}")
+    if Vq.ndim != 3 or Vk.ndim != 3 or Vv.ndim != 3:
+        raise ValueError(f"Expected Vq/Vk/Vv to be 3D [H|Hk,R*,Dh], got {tuple(Vq.shape)}/{tuple(Vk.shape)}/{tuple(Vv.shape)}")
+    B = Pq.shape[0]
+    if Pk.shape[0] != B or Pv.shape[0] != B:
+        raise ValueError("Pq/Pk/Pv batch mismatch")
+    for P, V, n in ((Pq, Vq, "q"), (Pk, Vk, "k"), (Pv, Vv, "v")):
+        if P.shape[1] != V.shape[1]:
+            raise ValueError(f"rank mismatch for {n}: P has {P.shape[1]}, V has {V.shape[1]}")
+    ws = _workspace(Pq.device, Pq.dtype, B, Ro=max(Pq.shape[1], Pk.shape[1], Pv.shape[1]),
+                    d=max(Vq.shape[0] * Vq.shape[2], 8))
+    q, k, v = _lift_heads(Pq, Vq, ws), _lift_heads(Pk, Vk, ws), _lift_heads(Pv, Vv, ws)
+    if bq is not None:
+        q = q + bq.view(1, *q.shape[1:])
+    if bk is not None:
+        k = k + bk.view(1, *k.shape[1:])
+    if bv is not None:
+        v = v + bv.view(1, *v.shape[1:])
+    return q, k, v
+
+
+def reconstruct_qkv_token_shared(Pq, Pk, Pv, Vq, Vk, Vv, **kw):
+    """The equal-rank form of the same reconstruction (densekv_reconstruct_triton.py:464-556)."""
+    if Pq.ndim == 2 and Pk.ndim == 2 and Pv.ndim == 2 and not (Pq.shape[1] == Pk.shape[1] == Pv.shape[1]):
+        raise ValueError("reconstruct_qkv_token_shared expects one shared rank; use the _hetero variant")
+    return reconstruct_qkv_token_shared_hetero(Pq, Pk, Pv, Vq, Vk, Vv, **kw)
+
+
+def reconstruct_qkv_token(Pq, Pk, Pv, Vq, Vk, Vv, **kw):
+    return reconstruct_qkv_token_shared_hetero(Pq, Pk, Pv, Vq, Vk, Vv, **kw)
+
+
+def call_flash_attn_with_kvcache(flash_attn_with_kvcache, q_bmhd, k_cache_bmhd, v_cache_bmhd, *, k_bmhd=None,
+                                 v_bmhd=None, cache_seqlens=None, rotary_cos=None, rotary_sin=None, causal: bool = True):
+    """The reference's call into flash-attn (runtime/attn/decode_registry.py:177-211) served by this
+    library: q[B,1,H,Dh] (and the new k / v [B,1,Hk,Dh]) are rotated at position cache_seqlens[b]
+    when tables are given, k / v are appended to the caches, and attention runs over
+    cache_seqlens[b] + 1 keys (cache_seqlens[b] keys when no new k / v is passed).  The first
+    argument (the library function the reference would call) is accepted and not used."""
+    del flash_attn_with_kvcache, causal
+    if not (q_bmhd.is_cuda and k_cache_bmhd.is_cuda and v_cache_bmhd.is_cuda):
+        raise ValueError("call_flash_attn_with_kvcache expects CUDA tensors")
+    B, L, H, Dh = q_bmhd.shape
+    if L != 1:
+        raise ValueError("decode path: one query token per sequence")
+    Hk, S_max = k_cache_bmhd.shape[2], k_cache_bmhd.shape[1]
+    if cache_seqlens is None:
+        raise ValueError("cache_seqlens is required")
+    sl = cache_seqlens.to(torch.int32)
+    q, k = q_bmhd[:, 0], None if k_bmhd is None else k_bmhd[:, 0]
+    if rotary_cos is not None:
+        pos = sl.long().clamp_max(rotary_cos.shape[0] - 1)
+        cos, sin = rotary_cos[pos][:, None, :].to(q.dtype), rotary_sin[pos][:, None, :].to(q.dtype)
+        half = Dh // 2
+
+        def rot(x):
+            x1, x2 = x[..., :half], x[..., half:]
+            return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+        q = rot(q)
+        k = None if k is None else rot(k)
+    add = 0
+    if k is not None:
+        if bool((sl >= S_max).any().item()):
+            raise IndexError("cache position outside the cache")
+        rows = torch.arange(B, device=q.device)
+        k_cache_bmhd[rows, sl.long()] = k.to(k_cache_bmhd.dtype)
+        v_cache_bmhd[rows, sl.long()] = v_bmhd[:, 0].to(v_cache_bmhd.dtype)
+        add = 1
+    from . import ops
+
+    ws = _workspace(q.device, q.dtype, B, H=H, Hk=Hk, Dh=Dh, S_max=S_max)
+    out = ops.flash_decode(q.contiguous(), k_cache_bmhd, v_cache_bmhd, sl.contiguous(), ws, seqlen_add=add)
+    return out.view(B, 1, H, Dh)
+
+
+def manual_llama_decode_step(model, input_ids: torch.Tensor, *, past_key_values, cache_position: torch.Tensor,
+                             attention_mask=None):
+    """One token through embed -> decoder layers -> norm -> lm_head(last), layer by layer, as the
+    reference's ``_manual_llama_decode_step`` drives a transformers Llama (utils/evaluator.py:39-82).
+    The layers are transformers ``LlamaDecoderLayer``s whose ``self_attn`` / ``mlp`` are this
+    package's modules; the decode arithmetic of every layer runs in the CUDA library."""
+    from types import SimpleNamespace
+
+    inner = model.model
+    hidden_states = inner.embed_tokens(input_ids)
+    position_ids = cache_position.unsqueeze(0)
+    position_embeddings = inner.rotary_emb(hidden_states, position_ids) if hasattr(inner, "rotary_emb") else None
+    for decoder_layer in inner.layers[: model.config.num_hidden_layers]:
+        out = decoder_layer(hidden_states, attention_mask=None, position_ids=position_ids,
+                            past_key_values=past_key_values, cache_position=cache_position,
+                            position_embeddings=position_embeddings)
+        hidden_states = out[0] if isinstance(out, (tuple, list)) else out
+    hidden_states = inner.norm(hidden_states)
+    logits = model.lm_head(hidden_states[:, -1:, :])
+    return SimpleNamespace(logits=logits, past_key_values=past_key_values)
+
+
 # --------------------------------------------------------------------------------- generation
 @torch.inference_mode()
 def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: int = 64, device=None,
@@ -359,10 +528,17 @@ def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: in
     """Single-prompt greedy generation on a ``DecodeEngine``; returns the reference's result dict
     (prompt_token_count, generated_token_count, output_ids, completion_ids, text, completion_text).
     Generation stops after an end-of-sequence token, like the reference loop."""
-    from .engine import DecodeEngine
+    from .engine import DecodeEngine, engine_for_model, has_lowrank_modules
 
     if not isinstance(model, DecodeEngine):
-        raise TypeError("generate_text of flashsvd_b200 drives a DecodeEngine")
+        if not has_lowrank_modules(model):
+            return _generate_text_generic(model, tokenizer, prompt=prompt, max_new_tokens=max_new_tokens, device=device,
+                                          do_sample=do_sample, temperature=temperature, top_p=top_p)
+        if do_sample:
+            raise NotImplementedError("the decode kernel samples greedily (do_sample=False)")
+        enc0 = tokenizer(prompt, return_tensors="pt", add_special_tokens=False)
+        need = int(enc0["input_ids"].shape[1]) + int(max_new_tokens)
+        model = engine_for_model(model, batch_size=1, max_cache_len=need + 4)
     if do_sample:
         raise NotImplementedError("the decode kernel samples greedily (do_sample=False)")
     enc = tokenizer(prompt, return_tensors="pt", add_special_tokens=False)
@@ -383,6 +559,45 @@ def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: in
     eos = getattr(tokenizer, "eos_token_id", None)
     if eos is not None and int(eos) in new:
         new = new[: new.index(int(eos)) + 1]
+    output_ids = input_ids[0].tolist() + new
+    return {
+        "prompt_token_count": prompt_len,
+        "generated_token_count": len(new),
+        "output_ids": output_ids,
+        "completion_ids": new,
+        "text": tokenizer.decode(output_ids, skip_special_tokens=False),
+        "completion_text": tokenizer.decode(new, skip_special_tokens=False),
+    }
+
+
+def _generate_text_generic(model, tokenizer, *, prompt, max_new_tokens, device, do_sample, temperature, top_p):
+    """Models without low-rank modules (anything transformers can run) take the plain token loop
+    of the reference (scripts/demo_support/api.py:285-312): the model's own forward with its own
+    cache, greedy or sampled.  Nothing of this library's decode path is involved."""
+    dev = torch.device(device) if device is not None else next(model.parameters()).device
+    enc = tokenizer(prompt, return_tensors="pt", add_special_tokens=False)
+    input_ids = enc["input_ids"].to(dev)
+    if int(input_ids.shape[0]) != 1:
+        raise ValueError("generate_text currently supports batch_size=1 only.")
+    prompt_len = int(input_ids.shape[1])
+    eos = getattr(tokenizer, "eos_token_id", None)
+    out = model(input_ids=input_ids, use_cache=True)
+    past, logits = out.past_key_values, out.logits[:, -1, :]
+    new = []
+    for _ in range(int(max_new_tokens)):
+        if do_sample:
+            probs = torch.softmax(logits.float() / max(float(temperature), 1e-5), -1)
+            sp, si = torch.sort(probs, descending=True)
+            keep = torch.cumsum(sp, -1) - sp < float(top_p)
+            sp = sp * keep
+            nxt = si.gather(-1, torch.multinomial(sp / sp.sum(-1, keepdim=True), 1))
+        else:
+            nxt = logits.argmax(-1, keepdim=True)
+        new.append(int(nxt[0, 0]))
+        if eos is not None and new[-1] == int(eos):
+            break
+        out = model(input_ids=nxt, past_key_values=past, use_cache=True)
+        past, logits = out.past_key_values, out.logits[:, -1, :]
     output_ids = input_ids[0].tolist() + new
     return {
         "prompt_token_count": prompt_len,
