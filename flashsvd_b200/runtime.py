@@ -532,6 +532,8 @@ def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: in
 
     if not isinstance(model, DecodeEngine):
         if not has_lowrank_modules(model):
+            if not callable(model) or not hasattr(model, "parameters"):
+                raise TypeError("generate_text takes a DecodeEngine, a model with low-rank modules or a transformers model")
             return _generate_text_generic(model, tokenizer, prompt=prompt, max_new_tokens=max_new_tokens, device=device,
                                           do_sample=do_sample, temperature=temperature, top_p=top_p)
         if do_sample:

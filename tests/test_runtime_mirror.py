@@ -96,6 +96,6 @@ def test_kernel_wrappers_validate_before_launch():
         R.reconstruct_qkv_token_shared_prepacked(t(1, 8), t(1, 8), t(1, 8), t(8, 8), t(8, 8), t(8, 8), H=2, Hk=2, Dh=4)
 
 
-def test_generate_text_needs_an_engine():
+def test_generate_text_needs_a_model():
     with pytest.raises(TypeError):
         R.generate_text(object(), None, prompt="x")
