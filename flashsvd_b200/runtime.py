@@ -510,7 +510,10 @@ def manual_llama_decode_step(model, input_ids: torch.Tensor, *, past_key_values,
     inner = model.model
     hidden_states = inner.embed_tokens(input_ids)
     position_ids = cache_position.unsqueeze(0)
-    position_embeddings = inner.rotary_emb(hidden_states, position_ids) if hasattr(inner, "rotary_emb") else None
+    # the attention modules of this package rotate with the cache's own tables at cache_position, so
+    # the transformers rotary embedding is not evaluated (the reference computes it here and its
+    # FlashSVD attention ignores it as well)
+    position_embeddings = None
     for decoder_layer in inner.layers[: model.config.num_hidden_layers]:
         out = decoder_layer(hidden_states, attention_mask=None, position_ids=position_ids,
                             past_key_values=past_key_values, cache_position=cache_position,

@@ -44,7 +44,10 @@ extern "C" {
 #define FSVD_ERR_CACHE_FULL (-7)
 
 /* Shapes of one model / layer.  Ranks must be multiples of 8, d and I multiples of 8,
- * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}, B <= 8 (bf16) / 4 (fp32). */
+ * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}.  Batch: B <= 8 (bf16, int4) / 4 (fp32) runs in the
+ * persistent single-launch kernel; 9 <= B <= 128 (bf16 only, gate and up ranks equal) runs as
+ * tiled tensor-core GEMMs (tcgen05, accumulators in tensor memory) + batched attention, several
+ * launches per layer, accepted by fsvd_workspace_bytes, fsvd_decode_layer and fsvd_model_*. */
 typedef struct fsvd_dims {
   int dtype;
   int B;       /* independent sequences */
@@ -233,14 +236,16 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
                       const void* final_norm_w, const void* lm_head, const void* cos_tab,
                       const void* sin_tab, int max_steps, fsvd_model** out);
 int fsvd_model_destroy(fsvd_model* m);
-/* Enqueue n_steps greedy decode steps. */
+/* Enqueue n_steps greedy decode steps: one kernel launch per step for B <= 8, one CUDA graph launch
+ * per step (captured by fsvd_model_create) for B > 8. */
 int fsvd_model_step(fsvd_model* m, int n_steps, void* stream);
 /* Device buffers: tokens[B] (in: token to feed, out: sampled token), seqlens[B],
  * token_log[max_steps,B], step_counter[1], logits[B,vocab] fp32; `hidden` is the library's internal
  * hidden-state buffer between layers ([B,d] in the model dtype), exposed for debugging. */
 int fsvd_model_buffers(fsvd_model* m, int** tokens, int** seqlens, int** token_log,
                        int** step_counter, float** logits, float** hidden);
-/* Number of stages of the model's program (sizes the trace buffer). */
+/* Number of stages of the model's program (sizes the trace buffer); for B > 8 the number of
+ * kernel launches of a step. */
 int fsvd_model_num_stages(fsvd_model* m);
 /* Grid barriers per launch of the model's program (one in front of every stage that reads what
  * the stage before it wrote: 9 per layer + 2). */
