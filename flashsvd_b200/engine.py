@@ -8,6 +8,7 @@ Token ids and sequence lengths stay on the device between steps, which removes t
 from __future__ import annotations
 
 import ctypes as C
+from typing import Optional
 
 import torch
 
@@ -98,8 +99,14 @@ class DecodeEngine:
         cmax = 4 if dtype == torch.float32 else 8
         self.prefill_chunk = (cmax if prefill_chunk is None else max(1, min(int(prefill_chunk), cmax))) \
             if self.B == 1 else 1
+        # long prompts of a single bf16 sequence first go 128 positions per pass through the tiled
+        # tensor-core path (the same factors as 128-column GEMMs, RoPE and the cache write in their
+        # epilogues, causal attention over the rows already written)
+        self.prefill_tile = 128 if (self.B == 1 and dtype == torch.bfloat16 and not q4 and self.prefill_chunk > 1
+                                    and self.dims.Rg == self.dims.Ru) else 0
         self._layer_array, self._model_args = arr, (embed, final_norm, lm_head)
         self._chunk_handle = None
+        self._chunks: dict = {}
         ptrs = [C.c_void_p() for _ in range(6)]
         check(self.lib.fsvd_model_buffers(self.handle, *[C.byref(p) for p in ptrs]))
         self._ptrs = dict(zip(("tokens", "seqlens", "token_log", "step_counter", "logits", "hidden"),
@@ -155,48 +162,58 @@ class DecodeEngine:
         self.step_counter.zero_()
         self._pos_bound = 0
 
-    def _chunk_model(self):
-        """The program that takes `prefill_chunk` prompt positions of the one sequence per launch."""
-        if self._chunk_handle is None:
+    def _chunk_model(self, rows: Optional[int] = None):
+        """The program that takes `rows` (default `prefill_chunk`) prompt positions of the one
+        sequence per launch; returns (handle, tokens view, seqlens view)."""
+        rows = int(self.prefill_chunk if rows is None else rows)
+        hit = self._chunks.get(rows)
+        if hit is None:
             d = self.dims
-            self._chunk_dims = _lib.FsvdDims(d.dtype, self.prefill_chunk, d.d, d.H, d.Hk, d.Dh, d.I, d.Rq, d.Rk, d.Rv,
-                                             d.Ro, d.Rg, d.Ru, d.Rd, d.S_max, d.vocab, d.n_layers, d.eps, 1)
+            dims = _lib.FsvdDims(d.dtype, rows, d.d, d.H, d.Hk, d.Dh, d.I, d.Rq, d.Rk, d.Rv, d.Ro, d.Rg, d.Ru, d.Rd,
+                                 d.S_max, d.vocab, d.n_layers, d.eps, 1)
             embed, final_norm, lm_head = self._model_args
             handle = C.c_void_p()
             with torch.cuda.device(self.device):
                 check(self.lib.fsvd_model_create(
-                    C.byref(self._chunk_dims), self._layer_array, embed.data_ptr(), final_norm.data_ptr(),
+                    C.byref(dims), self._layer_array, embed.data_ptr(), final_norm.data_ptr(),
                     lm_head.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), 1, C.byref(handle)))
             ptrs = [C.c_void_p() for _ in range(6)]
             check(self.lib.fsvd_model_buffers(handle, *[C.byref(p) for p in ptrs]))
-            self._chunk_handle = handle
-            self._chunk_tokens = _from_ptr(ptrs[0].value, (self.prefill_chunk,), torch.int32, self.device)
-            self._chunk_seqlens = _from_ptr(ptrs[1].value, (self.prefill_chunk,), torch.int32, self.device)
-        return self._chunk_handle
+            hit = (handle, _from_ptr(ptrs[0].value, (rows,), torch.int32, self.device),
+                   _from_ptr(ptrs[1].value, (rows,), torch.int32, self.device), dims)
+            self._chunks[rows] = hit
+            if rows == self.prefill_chunk:
+                self._chunk_handle, self._chunk_tokens, self._chunk_seqlens, self._chunk_dims = hit
+        return hit[:3]
 
     def prefill(self, prompt: torch.Tensor) -> None:
-        """Feed prompt[B, L] through the decode kernel: fills the caches and leaves the first
-        generated token in ``tokens`` and its logits in ``logits``.  A single sequence goes
-        `prefill_chunk` positions per launch (causal inside the chunk) as long as more than one
-        chunk is left, the rest token by token; several sequences go token by token."""
+        """Feed prompt[B, L] through the decode kernels: fills the caches and leaves the first
+        generated token in ``tokens`` and its logits in ``logits``.  A single sequence goes 128
+        positions per pass (bf16; tiled tensor-core path), then `prefill_chunk` positions per launch,
+        causal inside a pass, as long as more than one pass of that size is left, and the rest token
+        by token; several sequences go token by token."""
         prompt = prompt.to(device=self.device, dtype=torch.int32).contiguous()
         if prompt.shape[0] != self.B:
             raise ValueError(f"prompt batch {prompt.shape[0]} != engine batch {self.B}")
         L, t0 = prompt.shape[1], 0
-        Cn = self.prefill_chunk
-        if self.B == 1 and Cn > 1 and L > Cn:
-            handle = self._chunk_model()
+        sizes = [c for c in (self.prefill_tile, self.prefill_chunk) if c > 1 and L > c]
+        if self.B == 1 and sizes:
             pos0 = int(self.seqlens[0].item())
             if pos0 + L > self.S_max:
                 raise ValueError(f"prompt of {L} tokens at position {pos0} exceeds the cache ({self.S_max})")
-            offs = torch.arange(Cn, device=self.device, dtype=torch.int32)
             stream = torch.cuda.current_stream().cuda_stream
-            while L - t0 > Cn:
-                self._chunk_tokens.copy_(prompt[0, t0:t0 + Cn])
-                self._chunk_seqlens.copy_(offs + (pos0 + t0))
-                check(self.lib.fsvd_model_step(handle, 1, stream))
-                t0 += Cn
+            for Cn in sizes:
+                if L - t0 <= Cn:
+                    continue
+                handle, tokens, seqlens = self._chunk_model(Cn)
+                offs = torch.arange(Cn, device=self.device, dtype=torch.int32)
+                while L - t0 > Cn:
+                    tokens.copy_(prompt[0, t0:t0 + Cn])
+                    seqlens.copy_(offs + (pos0 + t0))
+                    check(self.lib.fsvd_model_step(handle, 1, stream))
+                    t0 += Cn
             self.seqlens.fill_(pos0 + t0)
+            self._pos_bound = pos0 + t0
         tok = self.tokens
         for t in range(t0, L):
             tok.copy_(prompt[:, t])
@@ -213,14 +230,17 @@ class DecodeEngine:
     def status(self) -> int:
         st = C.c_int(0)
         check(self.lib.fsvd_model_status(self.handle, C.byref(st)))
-        if st.value == 0 and self._chunk_handle is not None:
-            check(self.lib.fsvd_model_status(self._chunk_handle, C.byref(st)))
+        for hit in self._chunks.values():
+            if st.value == 0:
+                check(self.lib.fsvd_model_status(hit[0], C.byref(st)))
         return int(st.value)
 
     def close(self) -> None:
-        if getattr(self, "_chunk_handle", None) is not None and self._chunk_handle.value:
-            self.lib.fsvd_model_destroy(self._chunk_handle)
-            self._chunk_handle = None
+        for hit in getattr(self, "_chunks", {}).values():
+            if hit[0].value:
+                self.lib.fsvd_model_destroy(hit[0])
+        self._chunks = {}
+        self._chunk_handle = None
         if getattr(self, "handle", None) is not None and self.handle.value:
             self.lib.fsvd_model_destroy(self.handle)
             self.handle = C.c_void_p()

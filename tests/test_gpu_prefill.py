@@ -112,3 +112,26 @@ def test_layer_rows_as_positions_matches_oracle(dev):
     assert ws.status() == 0
     assert rel_linf(out, ref) <= 2e-5
     assert rel_linf(pk["k_cache"], kco) <= 2e-5 and rel_linf(pk["v_cache"], vco) <= 2e-5
+
+
+@pytest.mark.parametrize("shape,L", [(O.TINY, 300), (O.TINY_GQA, 131)])
+def test_tiled_prompt_pass_matches_oracle(dev, shape, L):
+    """Prompts longer than 128 tokens (bf16, one sequence): 128 positions per pass through the tiled
+    tensor-core GEMMs (rows_are_positions with B = 128), then 8 per launch, then token by token;
+    caches and the first logits against the oracle's token-by-token loop."""
+    dtype, n_new, S_max = torch.bfloat16, 2, L + 12
+    w = O.make_model_weights(shape, seed=7, dtype=dtype)
+    prompt = torch.randint(0, shape.vocab, (1, L), generator=torch.Generator().manual_seed(L))
+    toks_ref, logits_ref, st = O.greedy_decode(shape, w, prompt, n_new, S_max=S_max)
+    eng = _engine(dev, shape, dtype, w, S_max, None)
+    assert eng.prefill_tile == 128
+    eng.prefill(prompt)
+    torch.cuda.synchronize()
+    assert eng.status() == 0
+    assert 128 in eng._chunks          # the tiled pass ran
+    assert int(eng.seqlens[0]) == L
+    assert rel_linf(eng.logits, logits_ref[0]) <= 4e-2
+    for li in (0, shape.n_layers - 1):
+        assert rel_linf(eng.key_cache[li][:, :L], st.k[li][:, :L]) <= 4e-2
+        assert rel_linf(eng.value_cache[li][:, :L], st.v[li][:, :L]) <= 4e-2
+    eng.close()
