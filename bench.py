@@ -254,6 +254,36 @@ def time_workload(dev, *, shape_name, layers, batch, ctx, share_pairs, factors, 
             "bytes_step": bytes_step, "layer_bytes": layer_bytes, "parity": parity}
 
 
+def time_prefill(dev, lengths, seed=0):
+    """Prompt pass of one sequence through the 32-layer 7B-shape model (128 positions per pass on the
+    tiled tensor-core path, the tail in smaller passes): ms per prompt and prompt tokens/s."""
+    import torch
+
+    from flashsvd_b200 import synthetic
+
+    shape = synthetic.LLAMA7B_SVD50
+    eng = synthetic.make_engine(shape, device=dev, dtype=torch.bfloat16, batch=1, ctx=0, max_new=max(lengths) + 16,
+                                seed=seed, fill_cache=False)
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    for L in lengths:
+        prompt = torch.randint(0, shape.vocab, (1, L), device=dev, generator=gen, dtype=torch.int32)
+        for it in range(2):      # the first pass builds the 128-row program (CUDA graph capture)
+            eng.reset()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.prefill(prompt)
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        out[f"prompt_{L}"] = {"ms": ms, "prompt_tokens_per_s": L / (ms * 1e-3), "device_status": eng.status()}
+    eng.close()
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
 def roofline_of(r, steps, peak, peak_kind):
     achieved = r["bytes_step"] / (r["ms"] / steps * 1e-3) / 1e9
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -385,6 +415,10 @@ def main():
                                  "bytes_per_launch": ro["bytes_per_launch"], "device_status": s["status"]}
                 except Exception as e:   # a secondary workload must not cost the headline line
                     sec[name] = {"error": f"{type(e).__name__}: {e}"}
+            try:
+                sec["prefill_7b_shape_b1"] = time_prefill(dev, (512, 2048))
+            except Exception as e:
+                sec["prefill_7b_shape_b1"] = {"error": f"{type(e).__name__}: {e}"}
             line["secondary"] = sec
         print(json.dumps(line), flush=True)
     if world > 1:

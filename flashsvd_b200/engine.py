@@ -189,14 +189,15 @@ class DecodeEngine:
     def prefill(self, prompt: torch.Tensor) -> None:
         """Feed prompt[B, L] through the decode kernels: fills the caches and leaves the first
         generated token in ``tokens`` and its logits in ``logits``.  A single sequence goes 128
-        positions per pass (bf16; tiled tensor-core path), then `prefill_chunk` positions per launch,
-        causal inside a pass, as long as more than one pass of that size is left, and the rest token
-        by token; several sequences go token by token."""
+        positions per pass (bf16; tiled tensor-core path), then 64, 32, 16 (same path) and
+        `prefill_chunk` positions per launch, causal inside a pass, each size as long as more than
+        one pass of it is left, and the rest token by token; several sequences go token by token."""
         prompt = prompt.to(device=self.device, dtype=torch.int32).contiguous()
         if prompt.shape[0] != self.B:
             raise ValueError(f"prompt batch {prompt.shape[0]} != engine batch {self.B}")
         L, t0 = prompt.shape[1], 0
-        sizes = [c for c in (self.prefill_tile, self.prefill_chunk) if c > 1 and L > c]
+        tiles = (128, 64, 32, 16) if self.prefill_tile else ()
+        sizes = [c for c in (*tiles, self.prefill_chunk) if c > 1 and L > c]
         if self.B == 1 and sizes:
             pos0 = int(self.seqlens[0].item())
             if pos0 + L > self.S_max:
