@@ -163,5 +163,8 @@ def make_engine(shape: ModelShape, *, device, dtype=torch.bfloat16, batch=1, ctx
             kc[:, :ctx].copy_(torch.randn(kc[:, :ctx].shape, device=device, generator=gen).to(dtype))
             vc[:, :ctx].copy_(torch.randn(vc[:, :ctx].shape, device=device, generator=gen).to(dtype))
         eng.seqlens.fill_(ctx)
+        eng._pos_bound = int(ctx)   # known on the host: no device read at the first step
     eng.tokens.copy_(torch.arange(batch, device=device, dtype=torch.int32) % shape.vocab)
+    if not (fill_cache and ctx > 0):
+        eng._pos_bound = 0
     return eng
