@@ -1,0 +1,108 @@
+"""Tensor-parallel decode of one model over the GPUs of a node (one process per GPU).
+
+Partitioning (configuration 4 of the benchmark, the Llama-2-70B shape): every rank takes H / N
+query heads with their Hk / N key / value heads and I / N columns of the SwiGLU intermediate:
+
+    sharded by rows      q_u, k_u, v_u (the rank's heads), gate_u, up_u (the rank's slice of I)
+    sharded by columns   o_v (inputs = the rank's heads), down_v (inputs = the rank's slice of I)
+    replicated           q_v, k_v, v_v, gate_v, up_v (they read the full hidden state), o_u, down_u
+
+so that every rank produces a partial sum [B, d] of the attention output projection and of the MLP
+output, and two all-reduces per layer (NCCL over NVLink) complete them.  Rank 0 adds the residual
+before the all-reduce, so the sum carries it once.  The KV cache of a rank holds its own heads only.
+
+The per-rank arithmetic is the library's ordinary entry points on the shards
+(``fsvd_qkv_rope_append``, ``fsvd_flash_decode``, ``fsvd_lowrank_proj``, ``fsvd_mlp_swiglu_decode``);
+the collective is ``torch.distributed.all_reduce``.  Rounding differs from the single-GPU path in
+one place: each rank's partial output is rounded to the model dtype before the sum (the
+single-GPU path rounds the rank-space vector once, after the full sum).
+
+Reference: the partitioning is the one the reference's north-star configuration names; its own code
+has no tensor-parallel path (it shards whole layers with ``layer_device_map``,
+runtime/cache/attn_dense_kv.py:52-58).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+
+ROW_SHARDED = ("q_u", "k_u", "v_u", "gate_u", "up_u")
+COL_SHARDED = ("o_v", "down_v")
+
+
+def shard_ranges(H: int, Hk: int, Dh: int, I: int, rank: int, world: int):
+    """(query rows, key/value rows, intermediate columns) of ``rank`` as slices."""
+    if H % world or Hk % world or I % world or (I // world) % 8:
+        raise ValueError(f"H={H}, Hk={Hk} and I={I} must split evenly over {world} ranks (I / ranks a multiple of 8)")
+    hq, hk, ii = H // world * Dh, Hk // world * Dh, I // world
+    return slice(rank * hq, (rank + 1) * hq), slice(rank * hk, (rank + 1) * hk), slice(rank * ii, (rank + 1) * ii)
+
+
+def shard_layer_weights(w: dict, *, H: int, Hk: int, Dh: int, rank: int, world: int) -> dict:
+    """The rank's view of one layer's factors (keys as in the oracle: q_v .. down_u, ln1, ln2)."""
+    I = w["gate_u"].shape[0]
+    sq, sk, si = shard_ranges(H, Hk, Dh, I, rank, world)
+    out = dict(w)
+    out["q_u"], out["k_u"], out["v_u"] = w["q_u"][sq], w["k_u"][sk], w["v_u"][sk]
+    out["o_v"] = w["o_v"][:, sq]
+    out["gate_u"], out["up_u"] = w["gate_u"][si], w["up_u"][si]
+    out["down_v"] = w["down_v"][:, si]
+    return {k: (v.contiguous() if torch.is_tensor(v) else v) for k, v in out.items()}
+
+
+def _all_reduce(t: torch.Tensor) -> torch.Tensor:
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t)
+    return t
+
+
+class TPDecodeLayer:
+    """One decoder layer on this rank's shards."""
+
+    def __init__(self, w_shard: dict, *, H: int, Hk: int, Dh: int, rank: int, world: int, batch: int, S_max: int,
+                 eps: float, device, dtype=torch.bfloat16):
+        if batch > (8 if dtype == torch.bfloat16 else 4):
+            raise ValueError("the tensor-parallel layer takes the batch sizes of the single-launch kernel (<= 8)")
+        self.rank, self.world, self.eps = int(rank), int(world), float(eps)
+        self.Hl, self.Hkl, self.Dh = H // world, Hk // world, Dh
+
+        def dev(t):
+            return t.detach().to(device=device, dtype=dtype).contiguous()
+
+        w = w_shard
+        self.ln1, self.ln2 = dev(w["ln1"]), dev(w["ln2"])
+        self.qkv_v = dev(torch.cat([w["q_v"], w["k_v"], w["v_v"]], 0))
+        self.q_u, self.k_u, self.v_u = dev(w["q_u"]), dev(w["k_u"]), dev(w["v_u"])
+        self.o_v, self.o_u = dev(w["o_v"]), dev(w["o_u"])
+        self.upgate_v = dev(torch.cat([w["up_v"], w["gate_v"]], 0))
+        self.gate_u, self.up_u = dev(w["gate_u"]), dev(w["up_u"])
+        self.down_v, self.down_u = dev(w["down_v"]), dev(w["down_u"])
+        self.ranks = (w["q_u"].shape[1], w["k_u"].shape[1], w["v_u"].shape[1])
+        self.k_cache = torch.zeros(batch, S_max, self.Hkl, Dh, dtype=dtype, device=device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        d, Il = self.o_u.shape[0], self.gate_u.shape[0]
+        dims = ops.make_dims(dtype=dtype, B=batch, d=d, H=self.Hl, Hk=self.Hkl, Dh=Dh, I=Il, Rq=self.ranks[0],
+                             Rk=self.ranks[1], Rv=self.ranks[2], Ro=self.o_v.shape[0], Rg=self.gate_u.shape[1],
+                             Ru=self.up_u.shape[1], Rd=self.down_v.shape[0], S_max=S_max, eps=eps)
+        self.ws = ops.make_workspace(dims, device)
+
+    def bytes_per_step(self, ctx: int, batch: int) -> int:
+        """Factor bytes this rank streams per step plus the K / V rows it reads."""
+        fac = sum(t.numel() * t.element_size() for t in (self.qkv_v, self.q_u, self.k_u, self.v_u, self.o_v, self.o_u,
+                                                         self.upgate_v, self.gate_u, self.up_u, self.down_v, self.down_u))
+        return fac + 2 * batch * ctx * self.Hkl * self.Dh * self.k_cache.element_size()
+
+    def forward(self, x: torch.Tensor, seqlens: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        B = x.shape[0]
+        first = self.rank == 0
+        q = ops.qkv_rope_append(x, self.qkv_v, self.q_u, self.k_u, self.v_u, cos, sin, self.k_cache, self.v_cache,
+                                seqlens, self.ws, num_heads=self.Hl, num_kv_heads=self.Hkl, head_dim=self.Dh,
+                                ranks=self.ranks, norm_w=self.ln1, eps=self.eps)
+        a = ops.flash_decode(q, self.k_cache, self.v_cache, seqlens, self.ws, seqlen_add=1)
+        h = ops.lowrank_proj(a.view(B, self.Hl * self.Dh), self.o_v, self.o_u, self.ws, residual=x if first else None)
+        _all_reduce(h)                                   # partial sums of the output projection
+        y = ops.mlp_swiglu_decode(h, self.gate_u, self.up_u, self.down_v, self.down_u, self.ws, upgate_v=self.upgate_v,
+                                  norm_w=self.ln2, eps=self.eps, residual=h if first else None)
+        return _all_reduce(y)                            # partial sums of the down projection
