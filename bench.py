@@ -284,6 +284,65 @@ def time_prefill(dev, lengths, seed=0):
     return out
 
 
+def run_tensor_parallel(args, dev, rank, world, local):
+    """One model sharded over the ranks (heads and FFN intermediate; NCCL all-reduce of the o_proj and
+    down-projection partial sums): tokens/s of the whole job and this path's bytes per GPU."""
+    import torch
+    import torch.distributed as dist
+
+    from flashsvd_b200 import synthetic
+    from flashsvd_b200 import tensor_parallel as TP
+
+    shape = synthetic.LLAMA70B_SVD40 if args.shape == "70b" else synthetic.LLAMA7B_SVD50
+    layers = shape.n_layers if args.layers is None else int(args.layers)
+    B, ctx0, warm = int(args.batch), int(args.ctx), max(3, args.warmup)
+    model = TP.random_tp_model(shape, rank=rank, world=world, device=dev, batch=B, ctx=ctx0,
+                               max_new=warm + args.steps + 8, seed=0, n_layers=layers)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    model.step(warm)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    model.step(args.steps)
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    status = model.status()
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        per_gpu = model.bytes_per_step(ctx0 + warm + args.steps // 2)
+        achieved = per_gpu / (ms / args.steps * 1e-3) / 1e9
+        line = {
+            "metric": METRIC + " [secondary workload, see config.workload]",
+            "value": B * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_string(args.shape, layers, B, ctx0, False, "bf16").replace(" per GPU", " in all") +
+                       f", ONE model tensor-parallel over {world} GPUs (heads and FFN intermediate sharded, "
+                       "NCCL all-reduce of the o_proj and down-projection partial sums, step replayed as a CUDA graph)",
+                       "device_status": status},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}, per GPU", "bytes_per_launch": per_gpu,
+                         "note": "bytes one GPU reads per step: its factor shards + the replicated factors + its K/V rows + lm_head"},
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+
+
 def roofline_of(r, steps, peak, peak_kind):
     achieved = r["bytes_step"] / (r["ms"] / steps * 1e-3) / 1e9
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -326,6 +385,9 @@ def main():
     ap.add_argument("--ctx", type=int, default=CTX, help="cached positions before the first timed step")
     ap.add_argument("--share-pairs", action="store_true",
                     help="basis sharing: layers (2i, 2i+1) share their input-side factors")
+    ap.add_argument("--tp", action="store_true",
+                    help="tensor-parallel decode of ONE model over the ranks (configuration 4: --shape 70b --batch 8 "
+                         "--ctx 4096 under torchrun); a secondary workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -343,6 +405,12 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.tp:
+        run_tensor_parallel(args, dev, rank, world, local)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     full_layers = 80 if args.shape == "70b" else 32
     layers = full_layers if args.layers is None else int(args.layers)

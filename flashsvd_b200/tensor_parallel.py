@@ -106,3 +106,109 @@ class TPDecodeLayer:
         y = ops.mlp_swiglu_decode(h, self.gate_u, self.up_u, self.down_v, self.down_u, self.ws, upgate_v=self.upgate_v,
                                   norm_w=self.ln2, eps=self.eps, residual=h if first else None)
         return _all_reduce(y)                            # partial sums of the down projection
+
+
+class TPModel:
+    """Whole-model tensor-parallel decode: replicated embedding, final norm and lm_head, sharded
+    layers.  One step = embed -> layers (two all-reduces each) -> norm -> lm_head -> argmax; the
+    step is captured into a CUDA graph (kernels and NCCL collectives) on first use and replayed.
+    Tokens and sequence lengths stay on the device."""
+
+    def __init__(self, layers, embed, final_norm, lm_head, *, batch: int, S_max: int, head_dim: int, theta: float,
+                 eps: float, device, dtype=torch.bfloat16, use_graph: bool = True):
+        from .engine import rope_tables
+
+        self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
+        self.B, self.S_max, self.eps, self.device, self.dtype = int(batch), int(S_max), float(eps), device, dtype
+        self.cos, self.sin = rope_tables(self.S_max, head_dim, theta, dtype, device)
+        self.tokens = torch.zeros(self.B, dtype=torch.int64, device=device)
+        self.seqlens = torch.zeros(self.B, dtype=torch.int32, device=device)
+        self.logits = torch.zeros(self.B, embed.shape[0], dtype=dtype, device=device)
+        dims = ops.make_dims(dtype=dtype, B=self.B, d=embed.shape[0], Ro=embed.shape[1])
+        self._head_ws = ops.make_workspace(dims, device)
+        self._graph = None
+        self._use_graph = bool(use_graph)
+
+    def _step_eager(self) -> None:
+        x = self.embed[self.tokens]
+        for layer in self.layers:
+            x = layer.forward(x, self.seqlens, self.cos, self.sin)
+        xf = x.float()
+        xn = self.final_norm * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(self.dtype)
+        ops.lift(xn, self.lm_head, self._head_ws, out=self.logits)
+        self.tokens.copy_(self.logits.float().argmax(-1))
+        self.seqlens.add_(1)
+
+    def step(self, n: int = 1) -> None:
+        for _ in range(int(n)):
+            if not self._use_graph:
+                self._step_eager()
+                continue
+            if self._graph is None:
+                # one eager step first (workspaces, cached programs, NCCL communicators), undone below
+                tok, sl = self.tokens.clone(), self.seqlens.clone()
+                self._step_eager()
+                torch.cuda.synchronize()
+                self.tokens.copy_(tok)
+                self.seqlens.copy_(sl)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._step_eager()
+                self._graph = g
+                self.tokens.copy_(tok)
+                self.seqlens.copy_(sl)
+                # the captured step has not run: positions written by the eager step are rewritten
+            self._graph.replay()
+
+    def status(self) -> int:
+        for layer in self.layers:
+            st = layer.ws.status()
+            if st:
+                return st
+        return 0
+
+    def bytes_per_step(self, ctx: int) -> int:
+        """Algorithmic bytes this rank reads per step (its factor shards, replicated factors, its K / V
+        rows, lm_head)."""
+        return sum(l.bytes_per_step(ctx, self.B) for l in self.layers) + self.lm_head.numel() * self.lm_head.element_size()
+
+
+def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: int, max_new: int, seed: int = 0,
+                    dtype=torch.bfloat16, n_layers=None, use_graph: bool = True) -> TPModel:
+    """Seeded random model of ``shape`` (a synthetic.ModelShape), every rank drawing the same full
+    factors on its device and keeping its shards; caches pre-filled with ``ctx`` N(0,1) rows."""
+    import math
+
+    L = shape.n_layers if n_layers is None else int(n_layers)
+    d, HD, KD, I = shape.d, shape.H * shape.Dh, shape.Hk * shape.Dh, shape.I
+    S_max = ctx + max_new + 4
+    layers = []
+    for li in range(L):
+        gen = torch.Generator(device=device).manual_seed(seed * 100003 + li)
+
+        def w(out_f, in_f):
+            t = torch.randn(out_f, in_f, device=device, dtype=torch.float32, generator=gen)
+            return (t / math.sqrt(in_f)).to(dtype)
+
+        full = {"q_v": w(shape.Rq, d), "q_u": w(HD, shape.Rq), "k_v": w(shape.Rk, d), "k_u": w(KD, shape.Rk),
+                "v_v": w(shape.Rv, d), "v_u": w(KD, shape.Rv), "o_v": w(shape.Ro, HD), "o_u": w(d, shape.Ro),
+                "gate_v": w(shape.Rg, d), "gate_u": w(I, shape.Rg), "up_v": w(shape.Ru, d), "up_u": w(I, shape.Ru),
+                "down_v": w(shape.Rd, I), "down_u": w(d, shape.Rd),
+                "ln1": torch.ones(d, device=device, dtype=dtype), "ln2": torch.ones(d, device=device, dtype=dtype)}
+        sh = shard_layer_weights(full, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=rank, world=world)
+        layer = TPDecodeLayer(sh, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=rank, world=world, batch=batch, S_max=S_max,
+                              eps=shape.eps, device=device, dtype=dtype)
+        if ctx > 0:
+            g2 = torch.Generator(device=device).manual_seed(seed * 100003 + 7919 + li * world + rank)
+            layer.k_cache[:, :ctx].copy_(torch.randn(layer.k_cache[:, :ctx].shape, device=device, generator=g2).to(dtype))
+            layer.v_cache[:, :ctx].copy_(torch.randn(layer.v_cache[:, :ctx].shape, device=device, generator=g2).to(dtype))
+        layers.append(layer)
+        del full, sh
+    gen = torch.Generator(device=device).manual_seed(seed * 100003 + 999983)
+    embed = (torch.randn(shape.vocab, d, device=device, dtype=torch.float32, generator=gen) / math.sqrt(d)).to(dtype)
+    lm_head = (torch.randn(shape.vocab, d, device=device, dtype=torch.float32, generator=gen) / math.sqrt(d)).to(dtype)
+    model = TPModel(layers, embed, torch.ones(d, device=device, dtype=dtype), lm_head, batch=batch, S_max=S_max,
+                    head_dim=shape.Dh, theta=shape.theta, eps=shape.eps, device=device, dtype=dtype, use_graph=use_graph)
+    model.seqlens.fill_(ctx)
+    model.tokens.copy_(torch.arange(batch, device=device) % shape.vocab)
+    return model
