@@ -1147,16 +1147,22 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
     const char* kbase = reinterpret_cast<const char*>(st.kcache) + base * sizeof(T);
     const char* vbase = reinterpret_cast<const char*>(st.vcache) + base * sizeof(T);
 
-    // The value row u is requested as soon as key row u has been turned into a score, into
-    // the registers the key row leaves behind.  Rows are addressed by one running pointer and
-    // rows past the split are skipped by predicate (their registers read as zeros).
+    // The key and the value rows of a chunk are requested together (one memory round trip per
+    // chunk).  Rows are addressed by one running pointer and rows past the split are skipped by
+    // predicate (their registers read as zeros).
     RawRow<T, DPL> kr[KMAX], vr[KMAX];
     auto fetch = [&](int c0) {
       const char* kp = kbase + (size_t)c0 * row_bytes;
+      const char* vp = vbase + (size_t)c0 * row_bytes;
 #pragma unroll
       for (int u = 0; u < KMAX; ++u) {
         kr[u].load(kp, c0 + u < j1);
         kp += row_bytes;
+      }
+#pragma unroll
+      for (int u = 0; u < KMAX; ++u) {
+        vr[u].load(vp, c0 + u < j1);
+        vp += row_bytes;
       }
     };
     fetch(j0);
@@ -1179,7 +1185,6 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
       // Partial dot products (this lane's dims) go to a [key][lane] tile in shared memory; lane r
       // then adds row r, so that every lane owns one full score: softmax costs one exp per lane
       // and 2 x 5 shuffles per head instead of 5 shuffles and one exp per key.
-      const char* vp = vbase + (size_t)c0 * row_bytes;
 #pragma unroll
       for (int u = 0; u < KMAX; ++u) {
         float kf[DPL];
@@ -1191,8 +1196,6 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
           for (int d = 0; d < DPL; ++d) s2 = fmaf(q[g][d], kf[d], s2);
           tile[(g * KMAX + u) * 33 + lane] = s2;
         }
-        vr[u].load(vp, c0 + u < j1);
-        vp += row_bytes;
       }
       __syncwarp();
       float sa = 0.f, sb = 0.f, sc2 = 0.f, sd = 0.f;

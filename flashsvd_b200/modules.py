@@ -186,6 +186,18 @@ class SVD_LlamaAttention(_WithWorkspace):
         H, Hk, Dh, li = self.num_heads, self.num_key_value_heads, self.head_dim, self.layer_idx
         cache._ensure_layer_spec(li, h=Hk, dh=Dh)
         cos, sin = cache.get_rope_tables(cache.max_cache_len, Dh, device=x.device, dtype=x.dtype)
+        # a token that does not fit the cache raises, as the reference's cache does
+        # (runtime/cache/attn_dense_kv.py:295-298); the position is known on the host unless the
+        # caller passed a device tensor (then the kernel drops the token and flags the workspace)
+        if cache_position is None:
+            start = cache.get_seq_length()
+        elif torch.is_tensor(cache_position):
+            start = int(cache_position.max().item()) if (not cache_position.is_cuda and cache_position.numel()) else None
+        else:
+            start = int(cache_position)
+        if start is not None and start >= cache.max_cache_len:
+            raise IndexError(f"FlashSVDV15DenseKVCache write position out of range: start={start} q_len=1 "
+                             f"max={cache.max_cache_len}")
         kc, vc, seqlens = cache.prepare_fa2_step(li, batch_size=B, cache_position=cache_position)
         ws = self._workspace(x, B, d=d, H=H, Hk=Hk, Dh=Dh, Rq=self.q_u_proj.in_features,
                              Rk=self.k_u_proj.in_features, Rv=self.v_u_proj.in_features,

@@ -71,6 +71,9 @@ def test_hf_layers_with_these_modules_through_the_manual_decode_step(shape):
     ref, ref_logits, _ = O.greedy_decode(shape, w, prompt, n_new)
     assert torch.equal(torch.stack(toks, 1), ref.long())
     assert cache.get_seq_length() == prompt.shape[1] + n_new
+    # a token past the end of the cache raises before anything is launched
+    with torch.inference_mode(), pytest.raises(IndexError):
+        R.manual_llama_decode_step(model, nxt, past_key_values=cache, cache_position=torch.tensor([16]))
 
 
 def test_generate_text_builds_an_engine_from_the_modules_and_keeps_tied_factors_shared():
