@@ -501,11 +501,15 @@ __device__ __forceinline__ void ld_row<2>(const __nv_bfloat16* row, int lane, fl
   f[0] = __uint_as_float(w << 16); f[1] = __uint_as_float(w & 0xffff0000u);
 }
 
-template <int DH, int G>
+// RB > 1 (prompt pass: the batch rows are consecutive positions of one sequence and share its cache):
+// a CTA takes RB consecutive rows of one kv head, so a key / value row is read once for RB x G
+// query vectors; every (row, head) slot has its own causal limit.  RB > 1 runs with one split.
+template <int DH, int G, int RB>
 __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs a) {
   constexpr int DPL = DH / 32;
-  __shared__ float wm[kAttnWarps][G], wl[kAttnWarps][G];
-  __shared__ float wacc[kAttnWarps][G][DH];
+  constexpr int NG = G * RB;                     // query vectors that share the rows this CTA reads
+  __shared__ float wm[kAttnWarps][NG], wl[kAttnWarps][NG];
+  __shared__ float wacc[kAttnWarps][NG][DH];
   __shared__ int last_sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_launch_dependents();
@@ -513,19 +517,28 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
   int idx = blockIdx.x;
   const int split = idx % a.nsplit;
   idx /= a.nsplit;
-  const int hk = idx % a.Hk, b = idx / a.Hk;
-  const int n = min(a.seqlens[b] + a.seqlen_add, a.S_max);
+  const int hk = idx % a.Hk, b = idx / a.Hk;     // b: batch row, or block of RB rows
+  const int row0 = b * RB;
+  int nl[RB];                                    // keys visible to each of the CTA's rows
+  int n = 0;
+#pragma unroll
+  for (int r = 0; r < RB; ++r) {
+    const int row = row0 + r;
+    nl[r] = row < a.B ? min(a.seqlens[row] + a.seqlen_add, a.S_max) : 0;
+    n = max(n, nl[r]);
+  }
   const int per = (n + a.nsplit - 1) / a.nsplit;
   const int j0 = min(n, split * per), j1 = min(n, j0 + per);
   const size_t rowstride = (size_t)a.Hk * DH;
-  const size_t cbase = ((size_t)(a.shared_cache ? 0 : b) * a.S_max) * rowstride + (size_t)hk * DH;
+  const size_t cbase = ((size_t)(a.shared_cache ? 0 : row0) * a.S_max) * rowstride + (size_t)hk * DH;
   const __nv_bfloat16* kbase = a.kcache + cbase;
   const __nv_bfloat16* vbase = a.vcache + cbase;
 
-  float q[G][DPL], acc[G][DPL], m[G], l[G];
+  float q[NG][DPL], acc[NG][DPL], m[NG], l[NG];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    ld_row<DPL>(a.q + ((size_t)b * a.H + hk * G + g) * DH, lane, q[g]);
+  for (int g = 0; g < NG; ++g) {
+    const int row = min(row0 + g / G, a.B - 1);
+    ld_row<DPL>(a.q + ((size_t)row * a.H + hk * G + g % G) * DH, lane, q[g]);
 #pragma unroll
     for (int e = 0; e < DPL; ++e) {
       q[g][e] *= a.scale;
@@ -545,7 +558,7 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
       ld_row<DPL>(vbase + (size_t)row * rowstride, lane, vf[i]);
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
+    for (int g = 0; g < NG; ++g) {
       float s[kKeyGroup];
 #pragma unroll
       for (int i = 0; i < kKeyGroup; ++i) {
@@ -562,18 +575,21 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
       float cm = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kKeyGroup; ++i) {
-        if (i >= cn) s[i] = -INFINITY;
+        if (i >= cn) s[i] = -INFINITY;                          // past the split
+        if (RB > 1 && c0 + i >= nl[g / G]) s[i] = -INFINITY;    // past this query's position
         cm = fmaxf(cm, s[i]);
       }
       const float mn = fmaxf(m[g], cm);
-      const float corr = __expf(m[g] - mn);   // 0 when m is still -inf
+      // (with row blocks a whole group can be invisible to an early row: every weight below is then 0)
+      const float mref = (RB > 1 && mn == -INFINITY) ? 0.0f : mn;
+      const float corr = __expf(m[g] - mref);               // 0 when m is still -inf
       m[g] = mn;
       float ps = 0.0f;
 #pragma unroll
       for (int e = 0; e < DPL; ++e) acc[g][e] *= corr;
 #pragma unroll
       for (int i = 0; i < kKeyGroup; ++i) {
-        const float pr = __expf(s[i] - mn);   // 0 for the rows past the end
+        const float pr = __expf(s[i] - mref);               // 0 for the masked rows
         ps += pr;
 #pragma unroll
         for (int e = 0; e < DPL; ++e) acc[g][e] += pr * vf[i][e];
@@ -583,7 +599,7 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
   }
   // ---- the warps meet
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
+  for (int g = 0; g < NG; ++g) {
     if (lane == 0) {
       wm[warp][g] = m[g];
       wl[warp][g] = l[g];
@@ -594,9 +610,10 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
   __syncthreads();
   const int nsplit = a.nsplit;
   const int rec = DH + 2;
-  float* mine = a.part + ((((size_t)b * a.Hk + hk) * nsplit + split) * G) * rec;
-  for (int i = tid; i < G * DH; i += kAttnThreads) {
+  float* mine = a.part + ((((size_t)b * a.Hk + hk) * nsplit + split) * NG) * rec;
+  for (int i = tid; i < NG * DH; i += kAttnThreads) {
     const int g = i / DH, dd = i - g * DH;
+    const int row = row0 + g / G;
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, wm[w][g]);
@@ -608,7 +625,8 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
       den += wgt * wl[w][g];
     }
     if (nsplit == 1) {
-      a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
+      if (row < a.B)
+        a.out[((size_t)row * a.H + hk * G + g % G) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
     } else {
       mine[(size_t)g * rec + dd] = num;
       if (dd == 0) {
@@ -628,20 +646,22 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
   __syncthreads();
   if (!last_sh) return;
   __threadfence();
-  const float* parts = a.part + (((size_t)b * a.Hk + hk) * nsplit) * G * rec;
-  for (int i = tid; i < G * DH; i += kAttnThreads) {
+  const float* parts = a.part + (((size_t)b * a.Hk + hk) * nsplit) * NG * rec;
+  for (int i = tid; i < NG * DH; i += kAttnThreads) {
     const int g = i / DH, dd = i - g * DH;
+    const int row = row0 + g / G;
     float mm = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) mm = fmaxf(mm, __ldcg(parts + ((size_t)sp * G + g) * rec + DH));
+    for (int sp = 0; sp < nsplit; ++sp) mm = fmaxf(mm, __ldcg(parts + ((size_t)sp * NG + g) * rec + DH));
     float num = 0.0f, den = 0.0f;
     for (int sp = 0; sp < nsplit; ++sp) {
-      const float* pr = parts + ((size_t)sp * G + g) * rec;
+      const float* pr = parts + ((size_t)sp * NG + g) * rec;
       const float ms = __ldcg(pr + DH);
       const float wgt = ms == -INFINITY ? 0.0f : __expf(ms - mm);
       num += wgt * __ldcg(pr + dd);
       den += wgt * __ldcg(pr + DH + 1);
     }
-    a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
+    if (row < a.B)
+      a.out[((size_t)row * a.H + hk * G + g % G) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
   }
 }
 
@@ -909,6 +929,7 @@ struct TileWs {
   int nsplit;
 };
 static int attn_nsplit(const fsvd_dims& D, int sms) {
+  if (D.rows_are_positions) return 1;   // prompt pass: row blocks share the cache rows instead
   int ns = (8 * sms + D.B * D.Hk - 1) / (D.B * D.Hk);   // about 8 CTAs of 4 warps per SM
   if (ns > 16) ns = 16;
   if (ns < 1) ns = 1;
@@ -1028,18 +1049,31 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
 }
 
 template <int DH>
-static void launch_attn_g(const AttnArgs& at, unsigned grid, cudaStream_t st) {
-  switch (at.H / at.Hk) {
-    case 1: launch_pdl(batch_attn_kernel<DH, 1>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
-    case 2: launch_pdl(batch_attn_kernel<DH, 2>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
-    case 4: launch_pdl(batch_attn_kernel<DH, 4>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
-    default: launch_pdl(batch_attn_kernel<DH, 8>, dim3(grid), dim3(kAttnThreads), 0, st, at); break;
+static void launch_attn_g(const AttnArgs& at, cudaStream_t st) {
+  const unsigned threads = kAttnThreads;
+  const int G = at.H / at.Hk;
+  if (at.shared_cache && at.nsplit == 1 && G < 8) {
+    // prompt pass: blocks of 8 / G consecutive rows share the key and value rows they read
+    const int RB = 8 / G;
+    const unsigned grid = (unsigned)(((at.B + RB - 1) / RB) * at.Hk);
+    switch (G) {
+      case 1: launch_pdl(batch_attn_kernel<DH, 1, 8>, dim3(grid), dim3(threads), 0, st, at); break;
+      case 2: launch_pdl(batch_attn_kernel<DH, 2, 4>, dim3(grid), dim3(threads), 0, st, at); break;
+      default: launch_pdl(batch_attn_kernel<DH, 4, 2>, dim3(grid), dim3(threads), 0, st, at); break;
+    }
+    return;
+  }
+  const unsigned grid = (unsigned)(at.B * at.Hk * at.nsplit);
+  switch (G) {
+    case 1: launch_pdl(batch_attn_kernel<DH, 1, 1>, dim3(grid), dim3(threads), 0, st, at); break;
+    case 2: launch_pdl(batch_attn_kernel<DH, 2, 1>, dim3(grid), dim3(threads), 0, st, at); break;
+    case 4: launch_pdl(batch_attn_kernel<DH, 4, 1>, dim3(grid), dim3(threads), 0, st, at); break;
+    default: launch_pdl(batch_attn_kernel<DH, 8, 1>, dim3(grid), dim3(threads), 0, st, at); break;
   }
 }
 static int launch_attn(const AttnArgs& at, cudaStream_t st) {
-  const unsigned grid = (unsigned)(at.B * at.Hk * at.nsplit);
-  if (at.Dh == 128) launch_attn_g<128>(at, grid, st);
-  else launch_attn_g<64>(at, grid, st);
+  if (at.Dh == 128) launch_attn_g<128>(at, st);
+  else launch_attn_g<64>(at, st);
   if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "attention kernel launch failed");
   fsvd_tile_count_launch();
   return 0;
