@@ -73,7 +73,7 @@ struct GemmArgs {
   int nkb;                 // k-blocks in all
   int nstages, two, epi;
   uint32_t tmem_cols;      // power of two >= 32
-  int cpo;                 // batch columns finished by each CTA of a tile's cluster, ceil(N / segs)
+  int cpo;                 // batch columns finished by each CTA of a tile's cluster: ceil(N / segs) rounded up to 4
   void* out;
   const void* resid;
   void* cache;             // TE_ROPE_K / TE_VCACHE: [rows, S_max, Hk, Dh]
@@ -83,6 +83,7 @@ struct GemmArgs {
   int Dh, HkDh, S_max, shared_cache;
   int* status;             // SyncState::status of the workspace
   long long wait_limit;
+  unsigned long long* trace;   // debugging: %globaltimer marks, 16 per CTA (null = off)
 };
 
 // ------------------------------------------------------------------------------- PTX
@@ -161,10 +162,18 @@ __device__ __forceinline__ uint32_t umma_idesc(int N) {
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, float v) {
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t rank, float x, float y, float z, float w) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
+__device__ __forceinline__ void tmark(const GemmArgs& a, int k) {
+  if (a.trace && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    a.trace[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + k] = t;
+  }
 }
 
 __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -225,6 +234,7 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, seg = blockIdx.y;
+  tmark(a, 0);
   const int N = a.N, NS = a.nstages;
   const uint32_t xbytes = (uint32_t)N * 128u;
   const uint32_t stage_bytes = (uint32_t)kWTileBytes * (a.two ? 2u : 1u) + xbytes * (a.two ? 2u : 1u);
@@ -251,6 +261,7 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  tmark(a, 1);
   pdl_launch_dependents();
 
   const int kb0 = seg * a.kbs, kb1 = min(a.nkb, kb0 + a.kbs);
@@ -328,9 +339,22 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   // ---- everybody: wait for the kernel before this one (the epilogue reads what it wrote), then
   // for the accumulators
   pdl_wait();
+  tmark(a, 2);
+  // the residual rows this CTA will add have usually left L2 since they were written (a layer's
+  // factors stream through in between): ask for them now, the epilogue is several microseconds away
+  if (a.epi == TE_RESID && lane == 0) {
+    const int prow = tile * kTileM + warp * 32;
+    if (prow < a.P)
+      for (int sl = 0; sl < a.cpo; ++sl) {
+        const int b = seg * a.cpo + sl;
+        if (b < a.B)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const __nv_bfloat16*>(a.resid) + (size_t)b * a.P + prow));
+      }
+  }
   bool have = nit > 0 ? wait_bar(accum, 0u, giveup, a, DS_BARRIER_TIMEOUT) : false;
   have = __all_sync(0xffffffffu, have);
   tc_fence_after();
+  tmark(a, 3);
 
   const int r = tid;                       // accumulator lane = row of the tile
   const int p = tile * kTileM + r;         // factor row
@@ -339,100 +363,132 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   const int cpo = a.cpo;                   // batch columns finished by each CTA of the cluster
 
   // ---- the K segments of a tile are the CTAs of one cluster (rank = segment).  CTA j finishes the
-  // batch columns [j cpo, (j + 1) cpo): every CTA sends its partial sums of those columns to CTA j's
-  // shared memory, slot [accumulator][segment][column][row]; the ring is free for that once every
-  // CTA of the cluster has its accumulators (first cluster barrier), and the sums are complete
-  // after the second.  Every CTA reaches both barriers, whatever happened before.
+  // batch columns [j cpo, (j + 1) cpo) (cpo a multiple of 4): every CTA sends its partial sums of
+  // those columns to CTA j's shared memory, [accumulator][segment][row][cpo] floats, four columns per
+  // 16-byte store; the ring is free for that once every CTA of the cluster has its accumulators
+  // (first cluster barrier), and the sums are complete after the second.  Every CTA reaches both
+  // barriers, whatever happened before.
   float* recv = reinterpret_cast<float*>(base_ptr);
   const uint32_t recv_u32 = base;
   cluster_sync();
+  tmark(a, 4);
   if (have) {
     for (int acc = 0; acc < nacc; ++acc) {
       for (int c0 = 0; c0 < N; c0 += 16) {
         float v[16];
         tc_ld16(trow + (uint32_t)(acc * N + c0), v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = c0 + i;
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int col = c0 + 4 * q4;
           const int owner = col / cpo, slot = col - owner * cpo;
-          if (col < a.B && owner < a.segs)
-            st_cluster_f32(recv_u32 + (uint32_t)((((acc * a.segs + seg) * cpo + slot) * kTileM + r) * 4), (uint32_t)owner, v[i]);
+          if (owner < a.segs)
+            st_cluster_v4(recv_u32 + (uint32_t)(((((acc * a.segs + seg) * kTileM + r) * cpo) + slot) * 4), (uint32_t)owner,
+                          v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
         }
       }
     }
   }
+  tmark(a, 5);
   cluster_sync();
+  tmark(a, 6);
 
-  if (!*giveup && have) {
+  if (!*giveup && have && p < a.P) {
     const int half = a.Dh >> 1;
     const bool rope = a.epi == TE_ROPE_Q || a.epi == TE_ROPE_K;
     const int j = rope ? p % a.Dh : 0;
-    for (int slot = 0; slot < cpo; ++slot) {
-      const int b = seg * cpo + slot;
-      if (b >= a.B || p >= a.P) break;
-      float v = 0.0f, u = 0.0f;
-      for (int sg = 0; sg < a.segs; ++sg) v += recv[((size_t)(sg * cpo + slot)) * kTileM + r];
-      if (a.two)
-        for (int sg = 0; sg < a.segs; ++sg) u += recv[((size_t)((a.segs + sg) * cpo + slot)) * kTileM + r];
-      const size_t o = (size_t)b * a.P + p;
-      switch (a.epi) {
-        case TE_STORE:
-          stbf(a.out, o, v);
-          break;
-        case TE_STORE_F32:
-          reinterpret_cast<float*>(a.out)[o] = rnd(v);
-          break;
-        case TE_RESID:
-          stbf(a.out, o, ldbf(a.resid, o) + rnd(v));
-          break;
-        case TE_SWIGLU: {
-          const float g = rnd(v), up = rnd(u);
-          const float sg = rnd(g / (1.0f + expf(-g)));
-          stbf(a.out, o, sg * up);
-        } break;
-        case TE_VCACHE: {
-          const int pos = a.seqlens[b];
-          if (pos < a.S_max)
-            stbf(a.cache, ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p, v);
-          else
-            atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
-        } break;
-        case TE_ROPE_Q:
-        case TE_ROPE_K: {
-          // rows (j, j + Dh/2) of a head sit in this tile (heads are Dh = 64 or 128 rows, tile-aligned):
-          // the thread of row j < Dh/2 finishes both
-          if (j >= half) break;
-          float w = 0.0f;
-          for (int sg = 0; sg < a.segs; ++sg) w += recv[((size_t)(sg * cpo + slot)) * kTileM + r + half];
-          const int pos = a.seqlens[b];
-          const int pt = min(pos, a.S_max - 1);
-          const float c = ldbf(a.cos_tab, (size_t)pt * half + j), sn = ldbf(a.sin_tab, (size_t)pt * half + j);
-          const float x1 = rnd(v), x2 = rnd(w);
-          const float o1 = rnd(rnd(x1 * c) - rnd(x2 * sn));
-          const float o2 = rnd(rnd(x2 * c) + rnd(x1 * sn));
-          if (a.epi == TE_ROPE_Q) {
-            stbf(a.out, o, o1);
-            stbf(a.out, o + half, o2);
-          } else if (pos < a.S_max) {
-            const size_t oc = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos) * (size_t)a.HkDh + p;
-            stbf(a.cache, oc, o1);
-            stbf(a.cache, oc + half, o2);
-          } else {
-            atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
-          }
-        } break;
-        default:
-          break;
+    const bool lower = !rope || j < half;      // RoPE: the thread of row j < Dh/2 finishes rows j and j + Dh/2
+    for (int sl = 0; sl < cpo && lower; sl += 4) {
+      const int b0 = seg * cpo + sl;
+      if (b0 >= a.B) break;
+      // sums over the segments, in segment order, of four columns (and of the second accumulator,
+      // or of the RoPE partner row)
+      float v[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int sg = 0; sg < a.segs; ++sg) {
+        const float4 t = *reinterpret_cast<const float4*>(recv + ((size_t)(sg * kTileM + r) * cpo + sl));
+        v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+      }
+      if (a.two || rope) {
+        for (int sg = 0; sg < a.segs; ++sg) {
+          const size_t row2 = a.two ? (size_t)((a.segs + sg) * kTileM + r) : (size_t)(sg * kTileM + r + half);
+          const float4 t = *reinterpret_cast<const float4*>(recv + (row2 * cpo + sl));
+          u[0] += t.x; u[1] += t.y; u[2] += t.z; u[3] += t.w;
+        }
+      }
+      // operands of the four epilogues first (independent loads), then the arithmetic and the stores
+      float res[4];
+      int pos[4];
+      float cs[4], sn[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int b = min(b0 + i, a.B - 1);
+        res[i] = a.epi == TE_RESID ? ldbf(a.resid, (size_t)b * a.P + p) : 0.f;
+        pos[i] = (rope || a.epi == TE_VCACHE) ? a.seqlens[b] : 0;
+      }
+      if (rope) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int pt = min(pos[i], a.S_max - 1);
+          cs[i] = ldbf(a.cos_tab, (size_t)pt * half + j);
+          sn[i] = ldbf(a.sin_tab, (size_t)pt * half + j);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int b = b0 + i;
+        if (b >= a.B) break;
+        const size_t o = (size_t)b * a.P + p;
+        switch (a.epi) {
+          case TE_STORE:
+            stbf(a.out, o, v[i]);
+            break;
+          case TE_STORE_F32:
+            reinterpret_cast<float*>(a.out)[o] = rnd(v[i]);
+            break;
+          case TE_RESID:
+            stbf(a.out, o, res[i] + rnd(v[i]));
+            break;
+          case TE_SWIGLU: {
+            const float g = rnd(v[i]), up = rnd(u[i]);
+            const float sg = rnd(g / (1.0f + expf(-g)));
+            stbf(a.out, o, sg * up);
+          } break;
+          case TE_VCACHE:
+            if (pos[i] < a.S_max)
+              stbf(a.cache, ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos[i]) * (size_t)a.HkDh + p, v[i]);
+            else
+              atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
+            break;
+          case TE_ROPE_Q:
+          case TE_ROPE_K: {
+            const float x1 = rnd(v[i]), x2 = rnd(u[i]);
+            const float o1 = rnd(rnd(x1 * cs[i]) - rnd(x2 * sn[i]));
+            const float o2 = rnd(rnd(x2 * cs[i]) + rnd(x1 * sn[i]));
+            if (a.epi == TE_ROPE_Q) {
+              stbf(a.out, o, o1);
+              stbf(a.out, o + half, o2);
+            } else if (pos[i] < a.S_max) {
+              const size_t oc = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos[i]) * (size_t)a.HkDh + p;
+              stbf(a.cache, oc, o1);
+              stbf(a.cache, oc + half, o2);
+            } else {
+              atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
+            }
+          } break;
+          default:
+            break;
+        }
       }
     }
   }
 
   // ---- release the tensor memory
+  tmark(a, 7);
   tc_fence_before();
   __syncthreads();
   if (*giveup)
     for (int i = 0; i < 100; ++i) __nanosleep(1000);   // copies in flight towards this CTA land first
   if (warp == 0) tc_dealloc(tmem, a.tmem_cols);
+  tmark(a, 8);
 }
 
 // ------------------------------------------------------------------------------- RMSNorm rows
@@ -801,6 +857,7 @@ static void split_k(int tiles, int nkb, int sms, int& segs, int& kbs) {
   segs = (nkb + kbs - 1) / kbs;
 }
 
+static unsigned long long* g_tile_trace = nullptr;
 struct Scratch {
   int* status;
   long long wait_limit;
@@ -823,6 +880,7 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   uint32_t cols = 32;
   while (cols < (uint32_t)(nacc * N)) cols <<= 1;
   a.tmem_cols = cols;
+  a.cpo = ((N + a.segs - 1) / a.segs + 3) / 4 * 4;   // a multiple of 4: partial sums travel four columns per store
   const size_t stage = (size_t)kWTileBytes * nacc + (size_t)N * 128 * nacc;
   int ns = (int)((size_t)(g_smem_optin - 2048) / stage);
   if (ns > kMaxStages) ns = kMaxStages;
@@ -837,7 +895,7 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   a.nstages = ns;
   size_t smem = 1024 + (size_t)ns * stage;
   // the ring is reused for the partial sums the cluster's CTAs send each other
-  const size_t recv = (size_t)nacc * a.segs * ((N + a.segs - 1) / a.segs) * kTileM * 4;
+  const size_t recv = (size_t)nacc * a.segs * a.cpo * kTileM * 4;
   if (smem < 1024 + recv) smem = 1024 + recv;
   // co-resident CTAs must not ask for more than the 512 tensor-memory columns of an SM
   const size_t floor_smem = (size_t)232448 / (512 / cols + 1) + 1024;
@@ -845,9 +903,9 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   if (smem > (size_t)g_smem_optin - 1024) return fail(FSVD_ERR_UNSUPPORTED, "shared memory plan exceeds the device limit");
   g.smem = smem;
   g.grid = dim3((unsigned)a.tiles, (unsigned)a.segs);
-  a.cpo = (N + a.segs - 1) / a.segs;
   a.status = sc.status;
   a.wait_limit = sc.wait_limit;
+  a.trace = g_tile_trace;
   if (int e = encode_sw128(&g.mapA, W, P, K, ldw, kTileM)) return e;
   if (int e = encode_sw128(&g.mapX, x, B, K, ldx, N)) return e;
   if (W2) {
@@ -1339,3 +1397,9 @@ int fsvd_tile_model_reset(fsvd_tile_model* m, void* stream) {
     return fail(FSVD_ERR_CUDA, "cudaMemsetAsync failed");
   return 0;
 }
+
+// Debugging aid: while a device buffer is set, every GEMM CTA planned afterwards records nine
+// %globaltimer marks (entry, set-up done, dependency met, accumulators done, cluster barrier 1,
+// partial sums sent, cluster barrier 2, epilogue done, exit) at [cta][16]; later launches overwrite
+// earlier ones.  Not part of the public header.
+extern "C" void fsvd_tile_debug_trace(void* dev_ptr) { g_tile_trace = reinterpret_cast<unsigned long long*>(dev_ptr); }
