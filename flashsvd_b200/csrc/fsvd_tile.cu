@@ -414,68 +414,70 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
           u[0] += t.x; u[1] += t.y; u[2] += t.z; u[3] += t.w;
         }
       }
-      // operands of the four epilogues first (independent loads), then the arithmetic and the stores
-      float res[4];
-      int pos[4];
-      float cs[4], sn[4];
+      // One compact code path per epilogue kind (this code runs once per CTA, from a cold
+      // instruction cache: the fewer lines it spans, the sooner it is through); within a kind the
+      // operands of the four columns are loaded first, then come the arithmetic and the stores.
+      const int nb = min(4, a.B - b0);
+      const size_t o0 = (size_t)b0 * a.P + p;
+      if (a.epi == TE_STORE) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int b = min(b0 + i, a.B - 1);
-        res[i] = a.epi == TE_RESID ? ldbf(a.resid, (size_t)b * a.P + p) : 0.f;
-        pos[i] = (rope || a.epi == TE_VCACHE) ? a.seqlens[b] : 0;
-      }
-      if (rope) {
+        for (int i = 0; i < 4; ++i)
+          if (i < nb) stbf(a.out, o0 + (size_t)i * a.P, v[i]);
+      } else if (a.epi == TE_RESID) {
+        float res[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) res[i] = ldbf(a.resid, o0 + (size_t)min(i, nb - 1) * a.P);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i < nb) stbf(a.out, o0 + (size_t)i * a.P, res[i] + rnd(v[i]));
+      } else if (a.epi == TE_SWIGLU) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int pt = min(pos[i], a.S_max - 1);
-          cs[i] = ldbf(a.cos_tab, (size_t)pt * half + j);
-          sn[i] = ldbf(a.sin_tab, (size_t)pt * half + j);
+          const float g = rnd(v[i]), up = rnd(u[i]);
+          const float sg = rnd(g / (1.0f + expf(-g)));
+          if (i < nb) stbf(a.out, o0 + (size_t)i * a.P, sg * up);
         }
-      }
+      } else if (a.epi == TE_STORE_F32) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int b = b0 + i;
-        if (b >= a.B) break;
-        const size_t o = (size_t)b * a.P + p;
-        switch (a.epi) {
-          case TE_STORE:
-            stbf(a.out, o, v[i]);
-            break;
-          case TE_STORE_F32:
-            reinterpret_cast<float*>(a.out)[o] = rnd(v[i]);
-            break;
-          case TE_RESID:
-            stbf(a.out, o, res[i] + rnd(v[i]));
-            break;
-          case TE_SWIGLU: {
-            const float g = rnd(v[i]), up = rnd(u[i]);
-            const float sg = rnd(g / (1.0f + expf(-g)));
-            stbf(a.out, o, sg * up);
-          } break;
-          case TE_VCACHE:
-            if (pos[i] < a.S_max)
-              stbf(a.cache, ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos[i]) * (size_t)a.HkDh + p, v[i]);
-            else
-              atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
-            break;
-          case TE_ROPE_Q:
-          case TE_ROPE_K: {
+        for (int i = 0; i < 4; ++i)
+          if (i < nb) reinterpret_cast<float*>(a.out)[o0 + (size_t)i * a.P] = rnd(v[i]);
+      } else {
+        // value cache / rotary epilogues: position of every column, tables, then the stores
+        int pos[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pos[i] = a.seqlens[min(b0 + i, a.B - 1)];
+        float cs[4], sn[4];
+        if (rope) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int pt = min(pos[i], a.S_max - 1);
+            cs[i] = ldbf(a.cos_tab, (size_t)pt * half + j);
+            sn[i] = ldbf(a.sin_tab, (size_t)pt * half + j);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int b = b0 + i;
+          if (i >= nb) continue;
+          if (pos[i] >= a.S_max && a.epi != TE_ROPE_Q) {
+            atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
+            continue;
+          }
+          const size_t oc = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos[i]) * (size_t)a.HkDh + p;
+          if (a.epi == TE_VCACHE) {
+            stbf(a.cache, oc, v[i]);
+          } else {
             const float x1 = rnd(v[i]), x2 = rnd(u[i]);
             const float o1 = rnd(rnd(x1 * cs[i]) - rnd(x2 * sn[i]));
             const float o2 = rnd(rnd(x2 * cs[i]) + rnd(x1 * sn[i]));
             if (a.epi == TE_ROPE_Q) {
-              stbf(a.out, o, o1);
-              stbf(a.out, o + half, o2);
-            } else if (pos[i] < a.S_max) {
-              const size_t oc = ((size_t)(a.shared_cache ? 0 : b) * a.S_max + pos[i]) * (size_t)a.HkDh + p;
+              stbf(a.out, o0 + (size_t)i * a.P, o1);
+              stbf(a.out, o0 + (size_t)i * a.P + half, o2);
+            } else {
               stbf(a.cache, oc, o1);
               stbf(a.cache, oc + half, o2);
-            } else {
-              atomicCAS(a.status, (int)DS_OK, (int)DS_CACHE_FULL);
             }
-          } break;
-          default:
-            break;
+          }
         }
       }
     }
@@ -858,6 +860,7 @@ static void split_k(int tiles, int nkb, int sms, int& segs, int& kbs) {
 }
 
 static unsigned long long* g_tile_trace = nullptr;
+static int g_tile_trace_epi = -1;
 struct Scratch {
   int* status;
   long long wait_limit;
@@ -905,7 +908,7 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   g.grid = dim3((unsigned)a.tiles, (unsigned)a.segs);
   a.status = sc.status;
   a.wait_limit = sc.wait_limit;
-  a.trace = g_tile_trace;
+  a.trace = (g_tile_trace_epi < 0 || g_tile_trace_epi == epi) ? g_tile_trace : nullptr;
   if (int e = encode_sw128(&g.mapA, W, P, K, ldw, kTileM)) return e;
   if (int e = encode_sw128(&g.mapX, x, B, K, ldx, N)) return e;
   if (W2) {
@@ -1403,3 +1406,4 @@ int fsvd_tile_model_reset(fsvd_tile_model* m, void* stream) {
 // partial sums sent, cluster barrier 2, epilogue done, exit) at [cta][16]; later launches overwrite
 // earlier ones.  Not part of the public header.
 extern "C" void fsvd_tile_debug_trace(void* dev_ptr) { g_tile_trace = reinterpret_cast<unsigned long long*>(dev_ptr); }
+extern "C" void fsvd_tile_debug_trace_epilogue(int epi) { g_tile_trace_epi = epi; }   // -1: every GEMM
