@@ -360,6 +360,7 @@ SECONDARY = (
     # batches above 8 run as tiled tcgen05 GEMMs + batched attention, one CUDA graph launch per step
     ("tiles_b16_ctx512", "7b", 32, 16, 512, False, "bf16"),
     ("tiles_shared_bases_b32_ctx2048", "7b", 32, 32, 2048, True, "bf16"),
+    ("tiles_shared_bases_b128_ctx2048", "7b", 32, 128, 2048, True, "bf16"),   # 137 GB of K / V on the device
 )
 
 
