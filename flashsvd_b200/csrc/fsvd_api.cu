@@ -50,6 +50,8 @@ struct Settings {
   unsigned long long* trace = nullptr;
   size_t trace_bytes = 0;
   unsigned generation = 0;   // bumped by every change of the geometry: cached programs of an older one are stale
+  int tile_min_batch = 5;    // bf16 batches from this size on take the tiled tensor-core path (FSVD_TILE_MIN_BATCH);
+                             // measured crossover on the 7B shape: 4 -> 1315 vs 1211 tokens/s, 5 -> 1282 vs 1465
 };
 static Settings g_set;
 static std::mutex g_set_mu;
@@ -63,6 +65,8 @@ static Settings current_settings() {
   std::call_once(g_set_once, [] {
     g_set.slots = env_int("FSVD_SLOTS", 0);
     g_set.grid = env_int("FSVD_GRID", 0);
+    g_set.tile_min_batch = env_int("FSVD_TILE_MIN_BATCH", g_set.tile_min_batch);
+    if (g_set.tile_min_batch < 1) g_set.tile_min_batch = 1;
     const char* wl = getenv("FSVD_WAIT_CLOCKS");
     if (wl && *wl && atoll(wl) >= 1000) g_set.wait_limit = atoll(wl);
   });
@@ -88,6 +92,12 @@ static int get_props(DevProps& p) {
   CUDA_TRY(cudaDeviceGetAttribute(&p.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
   if (dev >= 0 && dev < 16) cache[dev] = p;
   return 0;
+}
+
+// Batches that take the tiled tensor-core path (fsvd_tile.cu): always above 8, and bf16 batches from
+// the configured size on.
+static bool use_tiles(const fsvd_dims& D) {
+  return D.B > 8 || (D.dtype == FSVD_DTYPE_BF16 && D.Rg == D.Ru && D.B >= current_settings().tile_min_batch);
 }
 
 // ------------------------------------------------------------------------------- kernel table
@@ -821,7 +831,16 @@ int fsvd_set_wait_limit(long long sm_clocks) {
 
 size_t fsvd_workspace_bytes(const fsvd_dims* dims) {
   if (!dims) return 0;
-  if (dims->B > 8) return fsvd_tile_workspace_bytes(dims);   // tiled tensor-core path
+  if (use_tiles(*dims)) {   // tiled tensor-core path
+    const size_t t = fsvd_tile_workspace_bytes(dims);
+    // batches of 5..8: the per-op entry points use the single-launch kernel's layout on the same
+    // workspace (both keep the status words first and their counters zero between launches)
+    if (dims->B <= 8 && t) {
+      const size_t s1 = ws_layout(*dims).total;
+      return s1 > t ? s1 : t;
+    }
+    return t;
+  }
   return ws_layout(*dims).total;
 }
 
@@ -1085,7 +1104,7 @@ int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void
   if (!dims || !layer || !cos_tab || !sin_tab || !cache_seqlens || !x_in || !x_out)
     return fail(FSVD_ERR_ARG, "null argument");
   const fsvd_dims& D = *dims;
-  if (D.B > 8) {
+  if (use_tiles(D)) {
     // batches of 9..128 sequences: tiled GEMMs on tcgen05 (fsvd_tile.cu), several launches
     if (int e = check_layer_ptrs(*layer)) return e;
     if (!aligned16(ws)) return fail(FSVD_ERR_ALIGN, "workspace is not 16-byte aligned");
@@ -1133,7 +1152,7 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   if (!dims || !layers || !embed || !final_norm_w || !lm_head || !cos_tab || !sin_tab || !out)
     return fail(FSVD_ERR_ARG, "null argument");
   const fsvd_dims& D = *dims;
-  if (D.B > 8) {
+  if (use_tiles(D)) {
     for (int l = 0; l < D.n_layers; ++l)
       if (int e = check_layer_ptrs(layers[l])) return e;
     if (!aligned16(embed) || !aligned16(lm_head) || !aligned16(final_norm_w))

@@ -1032,7 +1032,7 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
 
 static int check_tile_dims(const fsvd_dims& D) {
   if (D.dtype != FSVD_DTYPE_BF16) return fail(FSVD_ERR_UNSUPPORTED, "batches above 8 need bf16 factors (dtype 0)");
-  if (D.B < 9 || D.B > 128) return fail(FSVD_ERR_UNSUPPORTED, "batch outside 9..128");
+  if (D.B < 1 || D.B > 128) return fail(FSVD_ERR_UNSUPPORTED, "batch outside 1..128");
   if (D.Dh != 64 && D.Dh != 128) return fail(FSVD_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
   {
     const int G = D.Hk > 0 && D.H % D.Hk == 0 ? D.H / D.Hk : 0;

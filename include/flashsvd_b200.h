@@ -47,7 +47,10 @@ extern "C" {
  * Dh in {64, 128}, H/Hk in {1, 2, 4, 8}.  Batch: B <= 8 (bf16, int4) / 4 (fp32) runs in the
  * persistent single-launch kernel; 9 <= B <= 128 (bf16 only, gate and up ranks equal) runs as
  * tiled tensor-core GEMMs (tcgen05, accumulators in tensor memory) + batched attention, several
- * launches per layer, accepted by fsvd_workspace_bytes, fsvd_decode_layer and fsvd_model_*. */
+ * launches per layer, accepted by fsvd_workspace_bytes, fsvd_decode_layer and fsvd_model_*.
+ * Those three entry points also take the tiled path for bf16 batches of 5..8 (it is faster from 5
+ * sequences on; FSVD_TILE_MIN_BATCH moves the threshold, 9 = never); the per-op entry points always
+ * use the single-launch kernel. */
 typedef struct fsvd_dims {
   int dtype;
   int B;       /* independent sequences */
