@@ -353,6 +353,7 @@ def roofline_of(r, steps, peak, peak_kind):
 SECONDARY = (
     # (name, shape, layers, batch, ctx, share_pairs, factors)
     ("int4_b1_ctx512", "7b", 32, 1, 512, False, "int4"),
+    ("int4_b16_ctx512", "7b", 32, 16, 512, False, "int4"),   # two launches of 8 sequences per step
     ("bf16_b8_ctx512", "7b", 32, 8, 512, False, "bf16"),
     ("shared_bases_b1_ctx2048", "7b", 32, 1, 2048, True, "bf16"),
     ("shared_bases_b8_ctx2048", "7b", 32, 8, 2048, True, "bf16"),

@@ -358,3 +358,63 @@ def _rope_theta(cfg) -> float:
         rp = getattr(cfg, "rope_parameters", None) or {}
         theta = rp.get("rope_theta", 10000.0) if isinstance(rp, dict) else 10000.0
     return float(theta)
+
+
+class EngineGroup:
+    """Several ``DecodeEngine``s over the same factor tensors, each with its own caches and at most
+    ``width`` sequences: how a batch runs that is wider than the kernel family of its factor type
+    takes in one launch (int4 and fp32 factors have no tiled path: 8 and 4 sequences per launch).
+    A step launches every engine once on the current stream; the factors are streamed once per
+    engine.  The interface is the subset of ``DecodeEngine`` that decoding needs."""
+
+    def __init__(self, *, batch_size: int, width: int, **engine_kwargs):
+        if batch_size < 1 or width < 1:
+            raise ValueError("batch_size and width must be positive")
+        sizes = [width] * (batch_size // width) + ([batch_size % width] if batch_size % width else [])
+        self.engines = [DecodeEngine(batch_size=b, **engine_kwargs) for b in sizes]
+        self.B = int(batch_size)
+        e0 = self.engines[0]
+        self.S_max, self.vocab, self.device, self.quantized = e0.S_max, e0.vocab, e0.device, e0.quantized
+        self.key_cache = [[e.key_cache[l] for e in self.engines] for l in range(len(e0.key_cache))]
+        self.value_cache = [[e.value_cache[l] for e in self.engines] for l in range(len(e0.value_cache))]
+
+    @property
+    def tokens(self) -> torch.Tensor:
+        """A copy of the current tokens of all sequences (write through ``set_tokens``)."""
+        return torch.cat([e.tokens for e in self.engines])
+
+    def set_tokens(self, tokens: torch.Tensor) -> None:
+        o = 0
+        for e in self.engines:
+            e.tokens.copy_(tokens[o:o + e.B])
+            o += e.B
+
+    def fill_seqlens(self, value: int) -> None:
+        for e in self.engines:
+            e.seqlens.fill_(int(value))
+            e._pos_bound = int(value)
+
+    def step(self, n_steps: int = 1) -> None:
+        for _ in range(int(n_steps)):
+            for e in self.engines:
+                e.step(1)
+
+    def prefill(self, prompt: torch.Tensor) -> None:
+        o = 0
+        for e in self.engines:
+            e.prefill(prompt[o:o + e.B])
+            o += e.B
+
+    def last_tokens(self, n: int) -> torch.Tensor:
+        return torch.cat([e.last_tokens(n) for e in self.engines], dim=1)
+
+    def status(self) -> int:
+        for e in self.engines:
+            st = e.status()
+            if st:
+                return st
+        return 0
+
+    def close(self) -> None:
+        for e in self.engines:
+            e.close()

@@ -153,6 +153,23 @@ def make_engine(shape: ModelShape, *, device, dtype=torch.bfloat16, batch=1, ctx
     else:
         layers, embed, final_norm, lm_head = random_packed_layers(shape, device=device, dtype=dtype, seed=seed,
                                                                   share_pairs=share_pairs)
+    width = 8 if factors == "int4" else (4 if dtype == torch.float32 else 128)
+    if batch > width:
+        # wider than one launch of this factor type takes: a group of engines over the same factors
+        from .engine import EngineGroup
+
+        grp = EngineGroup(batch_size=batch, width=width, layers=layers, embed=embed, final_norm=final_norm,
+                          lm_head=lm_head, num_heads=shape.H, num_kv_heads=shape.Hk, head_dim=shape.Dh,
+                          max_cache_len=ctx + max_new + 4, rope_theta=shape.theta, eps=shape.eps, max_steps=max_new + 8)
+        if fill_cache and ctx > 0:
+            gen = torch.Generator(device=device).manual_seed(seed + 1)
+            for e in grp.engines:
+                for kc, vc in zip(e.key_cache, e.value_cache):
+                    kc[:, :ctx].copy_(torch.randn(kc[:, :ctx].shape, device=device, generator=gen).to(dtype))
+                    vc[:, :ctx].copy_(torch.randn(vc[:, :ctx].shape, device=device, generator=gen).to(dtype))
+            grp.fill_seqlens(ctx)
+        grp.set_tokens(torch.arange(batch, device=device, dtype=torch.int32) % shape.vocab)
+        return grp
     eng = DecodeEngine(layers=layers, embed=embed, final_norm=final_norm, lm_head=lm_head,
                        num_heads=shape.H, num_kv_heads=shape.Hk, head_dim=shape.Dh, batch_size=batch,
                        max_cache_len=ctx + max_new + 4, rope_theta=shape.theta, eps=shape.eps,

@@ -111,3 +111,27 @@ def test_model_tiles_teacher_forced(dev, batch, ctx, share):
           f"{res['n_equal']}/{res['n_tokens']}")
     assert max(res["rel_linf"]) <= 4e-2   # two layers + head; the per-layer bound is 2e-2
     assert res["tokens_explained"]
+
+
+def test_engine_group_runs_a_batch_wider_than_one_launch(dev):
+    """fp32 (and int4) factors have no tiled path; a batch wider than their single launch (4 / 8
+    sequences) runs as a group of engines over the same factors.  fp32, 6 sequences = 4 + 2: greedy
+    tokens identical to the oracle's."""
+    from flashsvd_b200 import engine, packing
+
+    shape, dtype, B, L, n_new = O.TINY, torch.float32, 6, 5, 6
+    w = O.make_model_weights(shape, seed=3, dtype=dtype)
+    layers = [packing.pack_layer(lw, device=dev, dtype=dtype) for lw in w["layers"]]
+    grp = engine.EngineGroup(batch_size=B, width=4, layers=layers, embed=w["embed"].to(dev), final_norm=w["norm"].to(dev),
+                             lm_head=w["lm_head"].to(dev), num_heads=shape.H, num_kv_heads=shape.Hk, head_dim=shape.Dh,
+                             max_cache_len=L + n_new + 4, rope_theta=shape.theta, eps=shape.eps, max_steps=L + n_new + 8)
+    assert [e.B for e in grp.engines] == [4, 2]
+    prompt = torch.randint(0, shape.vocab, (B, L), generator=torch.Generator().manual_seed(1))
+    grp.prefill(prompt)
+    grp.step(n_new - 1)
+    torch.cuda.synchronize()
+    assert grp.status() == 0
+    got = grp.last_tokens(n_new).t().cpu().long()
+    ref, _, _ = O.greedy_decode(shape, w, prompt, n_new)
+    assert torch.equal(got, ref.long())
+    grp.close()
