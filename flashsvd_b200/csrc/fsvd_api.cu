@@ -456,11 +456,6 @@ struct Builder {
   }
 };
 
-static unsigned fbits(float f) {
-  unsigned u;
-  memcpy(&u, &f, 4);
-  return u;
-}
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int check_dims(const fsvd_dims& D) {
@@ -1200,7 +1195,6 @@ int fsvd_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const voi
   m->logits = reinterpret_cast<float*>(m->extra + o);
 
   Builder b(m->r, D.dtype, D.B);
-  float* hidden = reinterpret_cast<float*>(m->ws + m->L.hidden);
   // The hidden state ping-pongs between two fp32 buffers: `hidden` (between the halves of a
   // layer) and `xbuf` (between layers), so a residual never reads what its stage overwrites.
   float* xbuf = nullptr;

@@ -531,7 +531,6 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = 4;
 constexpr int kKeyGroup = 8;
-constexpr int kMaxG = 8;
 
 struct AttnArgs {
   const __nv_bfloat16* q;        // [B, H, Dh], rotated
@@ -1156,7 +1155,7 @@ static int launch_group(const GemmPlan* const* plans, int n, cudaStream_t st) {
 
 // ---- workspace of the tile path (fsvd_dims with B > 8)
 struct TileWs {
-  size_t sync, counters, xn, pbuf, qbuf, attn, mid, hact, apart, part, total;
+  size_t sync, counters, xn, pbuf, qbuf, attn, mid, hact, apart, total;
   int nsplit;
 };
 static int attn_nsplit(const fsvd_dims& D, int sms) {
@@ -1169,8 +1168,8 @@ static int attn_nsplit(const fsvd_dims& D, int sms) {
 static int imax(int a, int b) { return a > b ? a : b; }
 static TileWs tile_layout(const fsvd_dims& D, int sms) {
   TileWs L;
-  const int B = D.B, N = round16(B);
-  const int HD = D.H * D.Dh, KD = D.Hk * D.Dh;
+  const int B = D.B;
+  const int HD = D.H * D.Dh;
   const int Rqkv = D.Rq + D.Rk + D.Rv;
   size_t o = 0;
   L.sync = o;      o += al256(sizeof(SyncState));
@@ -1183,19 +1182,6 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
   L.hact = o;      o += al256((size_t)B * D.I * 2);
   L.nsplit = attn_nsplit(D, sms);
   L.apart = o;     o += al256((size_t)B * D.Hk * L.nsplit * (D.H / imax(D.Hk, 1)) * (D.Dh + 2) * 4);
-#if 0
-  mx(gemm_scratch_floats(Rqkv, D.d, N, 1, sms));
-  mx(gemm_scratch_floats(HD, D.Rq, N, 1, sms) + gemm_scratch_floats(KD, D.Rk, N, 1, sms) +
-     gemm_scratch_floats(KD, D.Rv, N, 1, sms));   // one launch
-  mx(gemm_scratch_floats(D.Ro, HD, N, 1, sms));
-  mx(gemm_scratch_floats(D.d, D.Ro, N, 1, sms));
-  mx(gemm_scratch_floats(D.Ru + D.Rg, D.d, N, 1, sms));
-  mx(gemm_scratch_floats(D.I, imax(D.Rg, D.Ru), N, 2, sms));
-  mx(gemm_scratch_floats(D.Rd, D.I, N, 1, sms));
-  mx(gemm_scratch_floats(D.d, D.Rd, N, 1, sms));
-  if (D.vocab > 0) mx(gemm_scratch_floats(D.vocab, D.d, N, 1, sms));
-#endif
-  L.part = o;
   L.total = o;
   return L;
 }
