@@ -135,3 +135,51 @@ def test_engine_group_runs_a_batch_wider_than_one_launch(dev):
     ref, _, _ = O.greedy_decode(shape, w, prompt, n_new)
     assert torch.equal(got, ref.long())
     grp.close()
+
+
+def test_tiles_flag_a_full_cache_and_leave_it_untouched(dev):
+    """A token at position S_max on the tiled path: the key / value are not stored and the status
+    word says so (FSVD_ERR_CACHE_FULL -> IndexError), as on the single-launch path."""
+    from flashsvd_b200 import ops, packing
+
+    shape, dtype, B, S_max = O.TINY, torch.bfloat16, 12, 16
+    gen = torch.Generator().manual_seed(4)
+    w = O.make_layer_weights(shape, gen, dtype)
+    pk = packing.pack_layer(w, device=dev, dtype=dtype)
+    kc = torch.randn(B, S_max, shape.Hk, shape.Dh, generator=gen).to(dtype).to(dev)
+    vc = torch.randn(B, S_max, shape.Hk, shape.Dh, generator=gen).to(dtype).to(dev)
+    pk["k_cache"], pk["v_cache"] = kc.clone(), vc.clone()
+    seqlens = torch.full((B,), S_max - 1, dtype=torch.int32)
+    seqlens[3] = S_max                      # one sequence is already full
+    dims = ops.make_dims(dtype=dtype, B=B, d=shape.d, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, I=shape.I, Rq=shape.Rq,
+                         Rk=shape.Rk, Rv=shape.Rv, Ro=shape.Ro, Rg=shape.Rg, Ru=shape.Ru, Rd=shape.Rd, S_max=S_max,
+                         eps=shape.eps)
+    ws = ops.make_workspace(dims, dev)
+    cos, sin = O.rope_tables(S_max, shape.Dh, shape.theta, dtype)
+    x = torch.randn(B, shape.d, generator=gen).to(dtype).to(dev)
+    out = torch.empty_like(x)
+    ops.decode_layer(dims, ops.make_layer_struct(pk), cos.to(dev), sin.to(dev), seqlens.to(dev), x, out, ws)
+    torch.cuda.synchronize()
+    assert ws.raw_status() == 4
+    with pytest.raises(IndexError):
+        ws.status()
+    assert torch.equal(pk["k_cache"][3], kc[3]) and torch.equal(pk["v_cache"][3], vc[3])   # nothing written for it
+    assert not torch.equal(pk["k_cache"][0], kc[0])                                         # the others appended
+    ws.clear_status()
+    assert ws.status() == 0
+
+
+def test_small_bf16_batches_take_the_faster_path_and_both_agree(dev):
+    """bf16 batches of 5..8 run on the tiled path through fsvd_decode_layer (it is faster there);
+    the single-launch kernel is still behind the per-op entry points.  Both against the oracle at
+    batch 6, and the launch counts show which path ran."""
+    from flashsvd_b200 import ops
+
+    n0 = ops.launch_count()
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, O.TINY_GQA, 6, 30, S_max=40, seed=9)
+    assert ops.launch_count() - n0 > 5          # several launches: the tiled path
+    assert rel_linf(out, ref) <= TOL and rel_linf(pk["k_cache"], kc_o) <= TOL
+    n0 = ops.launch_count()
+    out4, ref4, *_ = _layer_case(dev, O.TINY_GQA, 4, 30, S_max=40, seed=9)
+    assert ops.launch_count() - n0 == 1         # one cooperative launch: the interpreter
+    assert rel_linf(out4, ref4) <= TOL
