@@ -892,6 +892,179 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_hs_kernel(const AttnA
   }
 }
 
+// ------------------------------------------------------------------------------- prompt-pass attention
+// Causal attention of a block of consecutive prompt rows over the one sequence's cache, on the
+// tensor cores (mma.sync m16n8k16 / bf16, fp32 accumulation): the rows of a pass share the cache
+// rows they read, so a key / value block staged in shared memory serves 32 query vectors
+// (32 / G rows x G heads of one kv head, 16 per warp).  Per block of 64 keys: S = Q K^T (the key rows
+// are the col-major B operand as they lie), causal mask by absolute position, running softmax,
+// O += P V with the value fragments taken through ldmatrix.trans.  Replaces the row-block variant
+// of batch_attn_kernel for the prompt pass (the reference: kernels/attn/prefill/rope_sdpa.py:67-427).
+constexpr int kPfWarps = 2;
+constexpr int kPfSlots = 16 * kPfWarps;     // query vectors per CTA
+constexpr int kPfKeys = 64;                 // keys per block
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int DH>
+__global__ void __launch_bounds__(kPfWarps * 32) prompt_attn_kernel(const AttnArgs a) {
+  constexpr int STRIDE = DH * 2 + 16;                 // bytes of a staged row (16 bytes of padding: no bank conflicts)
+  constexpr int KS = DH / 16;                         // k-steps of Q K^T
+  constexpr int NT = kPfKeys / 8;                     // score tiles per key block
+  constexpr int DT = DH / 8;                          // output tiles
+  __shared__ __align__(16) unsigned char ks_s[kPfKeys * STRIDE];
+  __shared__ __align__(16) unsigned char vs_s[kPfKeys * STRIDE];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int G = a.H / a.Hk;
+  const int rpb = kPfSlots / G;                       // rows per CTA
+  const int hk = blockIdx.y, row0 = blockIdx.x * rpb;
+  // this thread's two query vectors: slots m0 and m0 + 8 of the CTA
+  const int m0 = warp * 16 + g;
+  int rowq[2], headq[2], nl[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + 8 * i;
+    rowq[i] = row0 + m / G;
+    headq[i] = hk * G + m % G;
+    nl[i] = rowq[i] < a.B ? min(a.seqlens[rowq[i]] + a.seqlen_add, a.S_max) : 0;
+  }
+  const int last_row = min(row0 + rpb, a.B) - 1;
+  const int nmax = last_row >= row0 ? min(a.seqlens[last_row] + a.seqlen_add, a.S_max) : 0;   // positions increase with the row
+  // Q fragments (rows g and g + 8 of the warp's 16, dims 16 ks + 2 t .. and + 8)
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const __nv_bfloat16* qp = a.q + ((size_t)min(rowq[i], a.B - 1) * a.H + headq[i]) * DH + ks * 16 + 2 * t;
+      qa[ks][i] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][2 + i] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  float o[DT][4];
+#pragma unroll
+  for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
+  const size_t rowstride = (size_t)a.Hk * DH;
+  const __nv_bfloat16* kbase = a.kcache + (size_t)hk * DH;     // shared cache: row 0 of the cache tensor
+  const __nv_bfloat16* vbase = a.vcache + (size_t)hk * DH;
+
+  for (int k0 = 0; k0 < nmax; k0 += kPfKeys) {
+    // ---- stage 64 key rows and 64 value rows (zeros past the visible range)
+    __syncthreads();
+    for (int i = tid; i < kPfKeys * (DH / 8); i += kPfWarps * 32) {
+      const int r = i / (DH / 8), c = i - r * (DH / 8);
+      uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+      if (k0 + r < nmax) {
+        kv = __ldg(reinterpret_cast<const uint4*>(kbase + (size_t)(k0 + r) * rowstride) + c);
+        vv = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)(k0 + r) * rowstride) + c);
+      }
+      *reinterpret_cast<uint4*>(ks_s + r * STRIDE + c * 16) = kv;
+      *reinterpret_cast<uint4*>(vs_s + r * STRIDE + c * 16) = vv;
+    }
+    __syncthreads();
+    // ---- S = Q K^T for this warp's 16 query vectors x 64 keys
+    float sc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f;
+      const unsigned char* kr = ks_s + (nt * 8 + g) * STRIDE + 4 * t;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 32);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 32 + 16);
+        mma_bf16_16816(sc[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      }
+    }
+    // ---- scale, causal mask, running softmax (rows g and g + 8; a row's 64 scores sit in 4 lanes)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int kj = k0 + nt * 8 + 2 * t + (e & 1);
+        const float v = kj < nl[i] ? sc[nt][e] * a.scale : -INFINITY;
+        sc[nt][e] = v;
+        mx[i] = fmaxf(mx[i], v);
+      }
+    }
+    float corr[2], mref[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float mn = fmaxf(mrow[i], mx[i]);
+      mref[i] = mn == -INFINITY ? 0.0f : mn;          // nothing visible yet: every weight is 0
+      corr[i] = __expf(mrow[i] - mref[i]);
+      mrow[i] = mn;
+    }
+    float ps[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pr = __expf(sc[nt][e] - mref[e >> 1]);
+        sc[nt][e] = pr;
+        ps[e >> 1] += pr;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], 1);
+      ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], 2);
+      lrow[i] = lrow[i] * corr[i] + ps[i];
+    }
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      o[d][0] *= corr[0]; o[d][1] *= corr[0];
+      o[d][2] *= corr[1]; o[d][3] *= corr[1];
+    }
+    // ---- O += P V: 16 keys per step; the P fragments are the score tiles as they lie
+#pragma unroll
+    for (int kk = 0; kk < kPfKeys / 16; ++kk) {
+      const uint32_t pa0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+      const uint32_t pa1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+      const uint32_t pa2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+      const uint32_t pa3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+      // ldmatrix.x4.trans: matrices (keys 16 kk .. + 7, dims 16 j .. + 7), (keys + 8, same dims),
+      // (keys .. + 7, dims + 8), (keys + 8, dims + 8) -> b0, b1 of output tile 2 j and of tile 2 j + 1
+      const int lrow_ = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const unsigned char* vr = vs_s + lrow_ * STRIDE + ((lane >> 4) & 1) * 16;
+#pragma unroll
+      for (int j = 0; j < DT / 2; ++j) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vr + j * 32);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+        mma_bf16_16816(o[2 * j], pa0, pa1, pa2, pa3, b0, b1);
+        mma_bf16_16816(o[2 * j + 1], pa0, pa1, pa2, pa3, b2, b3);
+      }
+    }
+  }
+  // ---- normalise and store: thread holds (row g, dims 8 d + 2 t, + 1) and (row g + 8, same dims)
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (rowq[i] >= a.B) continue;
+    const float inv = lrow[i] > 0.0f ? 1.0f / lrow[i] : 0.0f;
+    __nv_bfloat16* op = a.out + ((size_t)rowq[i] * a.H + headq[i]) * DH + 2 * t;
+#pragma unroll
+    for (int d = 0; d < DT; ++d)
+      *reinterpret_cast<uint32_t*>(op + d * 8) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+  }
+}
+
 // ------------------------------------------------------------------------------- step head / tail
 __global__ void embed_rows_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
                                   __nv_bfloat16* __restrict__ out, int d, int vocab) {
@@ -1269,6 +1442,12 @@ template <int DH>
 static void launch_attn_g(const AttnArgs& at, cudaStream_t st) {
   const unsigned threads = kAttnThreads;
   const int G = at.H / at.Hk;
+  if (at.shared_cache && at.nsplit == 1 && at.B >= 16) {
+    // prompt pass: tensor-core attention, 32 / G rows of one kv head per CTA
+    const int rpb = kPfSlots / G;
+    launch_pdl(prompt_attn_kernel<DH>, dim3((unsigned)((at.B + rpb - 1) / rpb), (unsigned)at.Hk), dim3(kPfWarps * 32), 0, st, at);
+    return;
+  }
   if (at.shared_cache && at.nsplit == 1 && G < 8) {
     // prompt pass: blocks of 8 / G consecutive rows share the key and value rows they read
     const int RB = 8 / G;

@@ -114,11 +114,16 @@ def test_layer_rows_as_positions_matches_oracle(dev):
     assert rel_linf(pk["k_cache"], kco) <= 2e-5 and rel_linf(pk["v_cache"], vco) <= 2e-5
 
 
-@pytest.mark.parametrize("shape,L", [(O.TINY, 300), (O.TINY_GQA, 131)])
+DH128 = O.Shape(d=256, H=2, Hk=2, Dh=128, I=512, Rq=64, Rk=64, Rv=64, Ro=64, Rg=96, Ru=96, Rd=96, vocab=300, n_layers=2)
+DH128_GQA = O.Shape(d=512, H=8, Hk=1, Dh=128, I=512, Rq=96, Rk=32, Rv=32, Ro=96, Rg=96, Ru=96, Rd=96, vocab=300, n_layers=2)
+
+
+@pytest.mark.parametrize("shape,L", [(O.TINY, 300), (O.TINY_GQA, 131), (DH128, 150), (DH128_GQA, 140)])
 def test_tiled_prompt_pass_matches_oracle(dev, shape, L):
     """Prompts longer than 128 tokens (bf16, one sequence): 128 positions per pass through the tiled
-    tensor-core GEMMs (rows_are_positions with B = 128), then 8 per launch, then token by token;
-    caches and the first logits against the oracle's token-by-token loop."""
+    tensor-core GEMMs (rows_are_positions with B = 128) and the tensor-core causal attention
+    (head_dim 64 and 128, 1 / 4 / 8 query heads per kv head), then smaller passes, then token by
+    token; caches and the first logits against the oracle's token-by-token loop."""
     dtype, n_new, S_max = torch.bfloat16, 2, L + 12
     w = O.make_model_weights(shape, seed=7, dtype=dtype)
     prompt = torch.randint(0, shape.vocab, (1, L), generator=torch.Generator().manual_seed(L))
