@@ -1218,33 +1218,47 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   a.P = P; a.K = K; a.B = B; a.N = N;
   a.tiles = (P + kTileM - 1) / kTileM;
   a.nkb = (K + kTileK - 1) / kTileK;
-  split_k(a.tiles, a.nkb, g_sms, a.segs, a.kbs);
   a.two = W2 ? 1 : 0;
   a.epi = epi;
   const int nacc = a.two ? 2 : 1;
   uint32_t cols = 32;
   while (cols < (uint32_t)(nacc * N)) cols <<= 1;
   a.tmem_cols = cols;
-  a.cpo = ((N + a.segs - 1) / a.segs + 3) / 4 * 4;   // a multiple of 4: partial sums travel four columns per store
   const size_t stage = (size_t)kWTileBytes * nacc + (size_t)N * 128 * nacc;
-  int ns = (int)((size_t)(g_smem_optin - 2048) / stage);
-  if (ns > kMaxStages) ns = kMaxStages;
-  if (ns > a.kbs) ns = a.kbs;
-  // keep the ring small enough for two CTAs per SM: the clusters of a launch then fit the GPCs in
-  // one wave (with one CTA per SM, 24 clusters of 6 do not fit 8 GPCs of 16-20 SMs)
-  if (ns > 2 && (size_t)ns * stage > 110 * 1024) {
-    ns = (int)((size_t)(110 * 1024) / stage);
-    if (ns < 2) ns = 2;
+  size_t smem = 0;
+  int cap = kMaxSegs;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    split_k(a.tiles, a.nkb, g_sms, a.segs, a.kbs);
+    if (a.segs > cap) {   // second attempt: fewer, longer segments
+      a.kbs = (a.nkb + cap - 1) / cap;
+      a.segs = (a.nkb + a.kbs - 1) / a.kbs;
+    }
+    a.cpo = ((N + a.segs - 1) / a.segs + 3) / 4 * 4;   // a multiple of 4: partial sums travel four columns per store
+    int ns = (int)((size_t)(g_smem_optin - 2048) / stage);
+    if (ns > kMaxStages) ns = kMaxStages;
+    if (ns > a.kbs) ns = a.kbs;
+    // keep the ring small enough for two CTAs per SM: the clusters of a launch then fit the GPCs in
+    // one wave (with one CTA per SM, 24 clusters of 6 do not fit 8 GPCs of 16-20 SMs)
+    if (ns > 2 && (size_t)ns * stage > 110 * 1024) {
+      ns = (int)((size_t)(110 * 1024) / stage);
+      if (ns < 2) ns = 2;
+    }
+    if (ns < 1) return fail(FSVD_ERR_UNSUPPORTED, "shared memory too small for one stage");
+    a.nstages = ns;
+    smem = 1024 + (size_t)ns * stage;
+    // the ring is reused for the partial sums the cluster's CTAs send each other
+    const size_t recv = (size_t)nacc * a.segs * a.cpo * kTileM * 4;
+    if (smem < 1024 + recv) smem = 1024 + recv;
+    // co-resident CTAs must not ask for more than the 512 tensor-memory columns of an SM
+    const size_t floor_smem = (size_t)232448 / (512 / cols + 1) + 1024;
+    if (smem < floor_smem) smem = floor_smem;
+    // one CTA per SM and more CTAs than SMs would run in two waves: take fewer segments instead
+    if (attempt == 0 && smem > 113 * 1024 && a.tiles * a.segs > g_sms && a.segs > 1) {
+      cap = g_sms / a.tiles > 0 ? g_sms / a.tiles : 1;
+      continue;
+    }
+    break;
   }
-  if (ns < 1) return fail(FSVD_ERR_UNSUPPORTED, "shared memory too small for one stage");
-  a.nstages = ns;
-  size_t smem = 1024 + (size_t)ns * stage;
-  // the ring is reused for the partial sums the cluster's CTAs send each other
-  const size_t recv = (size_t)nacc * a.segs * a.cpo * kTileM * 4;
-  if (smem < 1024 + recv) smem = 1024 + recv;
-  // co-resident CTAs must not ask for more than the 512 tensor-memory columns of an SM
-  const size_t floor_smem = (size_t)232448 / (512 / cols + 1) + 1024;
-  if (smem < floor_smem) smem = floor_smem;
   if (smem > (size_t)g_smem_optin - 1024) return fail(FSVD_ERR_UNSUPPORTED, "shared memory plan exceeds the device limit");
   g.smem = smem;
   g.grid = dim3((unsigned)a.tiles, (unsigned)a.segs);
