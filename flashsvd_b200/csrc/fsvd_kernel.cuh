@@ -1111,8 +1111,17 @@ struct RawRow<float, 2> {
 // cph == 1 that is the result; otherwise the CTA publishes its part and the last of the cph
 // CTAs to arrive (atomic counter) merges the parts in part order, so the result does not depend
 // on timing.
+// What the attention stage needs to wait at its grid barrier itself: the item's index arithmetic
+// (and the instruction fetch of this code) then happens while the CTA would be waiting anyway.
+struct AttnBarrier {
+  bool need;
+  SyncState* sync;
+  volatile int* giveup;
+  unsigned long long target;
+  int s;
+};
 template <typename T, int GI, int DPL>
-__device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCache pc) {
+__device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCache pc, const AttnBarrier ab) {
   using X = TT<T>;
   // Rows per chunk: a split of the benchmark shape (18 keys) takes two chunks of 10 rather than one
   // of 20 - half the unrolled code; the stage is bound by instruction fetch, not by the loads
@@ -1134,6 +1143,7 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
   float* const tile = sh + kNWC * GI * rec + warp * (ROWS * 34);
   float* const pbuf = tile + ROWS * 33;
 
+  bool waited = !ab.need;
   for (int hs = first_item(blockIdx.x, qmod(st.rot, grid), grid); hs < nslice; hs += grid) {
     const int hq = qdiv(hs, cph), part = hs - hq * cph;
     const int b = qdiv(hq, Hg), hg = hq - b * Hg;
@@ -1165,6 +1175,10 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
         vp += row_bytes;
       }
     };
+    if (!waited) {
+      barrier_wait(ab.sync, ab.giveup, ab.target, ab.s, tid);
+      waited = true;
+    }
     fetch(j0);
     float q[GI][DPL], acc[GI][DPL], m[GI], l[GI];
 #pragma unroll
@@ -1337,18 +1351,19 @@ __device__ __forceinline__ void attn_cta(const Stage& st, float* sh, const PosCa
     }
     cons_sync();   // the partial results in shared memory may be overwritten
   }
+  if (!waited) barrier_wait(ab.sync, ab.giveup, ab.target, ab.s, tid);   // a CTA without items
 }
 
 template <typename T>
-__device__ __forceinline__ void run_attn(const Stage& st, float* sh, const PosCache pc) {
+__device__ __forceinline__ void run_attn(const Stage& st, float* sh, const PosCache pc, const AttnBarrier ab) {
   const int G = qdiv(st.H, st.Hk);
   const int dpl = st.Dh / 32;
   if ((G & 1) == 0) {
-    if (dpl == 4) attn_cta<T, 2, 4>(st, sh, pc);
-    else attn_cta<T, 2, 2>(st, sh, pc);
+    if (dpl == 4) attn_cta<T, 2, 4>(st, sh, pc, ab);
+    else attn_cta<T, 2, 2>(st, sh, pc, ab);
   } else {
-    if (dpl == 4) attn_cta<T, 1, 4>(st, sh, pc);
-    else attn_cta<T, 1, 2>(st, sh, pc);
+    if (dpl == 4) attn_cta<T, 1, 4>(st, sh, pc, ab);
+    else attn_cta<T, 1, 2>(st, sh, pc, ab);
   }
 }
 // ----------------------------------------------------------------------------- small stages
@@ -1545,14 +1560,22 @@ fsvd_decode_kernel(const Stage* __restrict__ prog_global, const __grid_constant_
         cx.trow = trow;
         seq_base += (unsigned)gemv_stage<T, Q4>(st, cx);
       } else {
-        if (st.flags & SF_BARRIER) barrier_wait(sync, giveup, target, s, tid);
-        trace_mark(trow, 1);
         if (st.type == ST_ATTN) {
-          run_attn<T>(st, part, pc);
-        } else if (st.type == ST_EMBED) {
-          run_embed<T>(st, blockIdx.x * kConsThreads + tid, gridDim.x * kConsThreads);
-        } else if (st.type == ST_ARGMAX) {
-          if (blockIdx.x == 0) run_argmax(st, red, flags_sh + 8, tid, kConsThreads);
+          AttnBarrier ab;
+          ab.need = (st.flags & SF_BARRIER) != 0;
+          ab.sync = sync;
+          ab.giveup = giveup;
+          ab.target = target;
+          ab.s = s;
+          run_attn<T>(st, part, pc, ab);
+        } else {
+          if (st.flags & SF_BARRIER) barrier_wait(sync, giveup, target, s, tid);
+          trace_mark(trow, 1);
+          if (st.type == ST_EMBED) {
+            run_embed<T>(st, blockIdx.x * kConsThreads + tid, gridDim.x * kConsThreads);
+          } else if (st.type == ST_ARGMAX) {
+            if (blockIdx.x == 0) run_argmax(st, red, flags_sh + 8, tid, kConsThreads);
+          }
         }
       }
       if (st.flags & SF_ARRIVE) {
