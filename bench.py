@@ -297,7 +297,7 @@ def run_tensor_parallel(args, dev, rank, world, local):
     layers = shape.n_layers if args.layers is None else int(args.layers)
     B, ctx0, warm = int(args.batch), int(args.ctx), max(3, args.warmup)
     model = TP.random_tp_model(shape, rank=rank, world=world, device=dev, batch=B, ctx=ctx0,
-                               max_new=warm + args.steps + 8, seed=0, n_layers=layers)
+                               max_new=warm + args.steps + 8, seed=0, n_layers=layers, exchange=args.tp_exchange)
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -322,6 +322,10 @@ def run_tensor_parallel(args, dev, rank, world, local):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0])
     status = model.status()
+    how = ("partial sums of the o_proj and down projection pushed to every rank's memory by the GEMM epilogue "
+           "(peer stores over NVLink) and summed by the next kernel, no collective call"
+           if args.tp_exchange == "peer" else
+           "per-op launches with an NCCL all-reduce of the o_proj and down-projection partial sums")
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         per_gpu = model.bytes_per_step(ctx0 + warm + args.steps // 2)
@@ -333,14 +337,15 @@ def run_tensor_parallel(args, dev, rank, world, local):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_string(args.shape, layers, B, ctx0, False, "bf16").replace(" per GPU", " in all") +
                        f", ONE model tensor-parallel over {world} GPUs (heads and FFN intermediate sharded, "
-                       "NCCL all-reduce of the o_proj and down-projection partial sums, step replayed as a CUDA graph)",
-                       "device_status": status},
+                       f"{how}, step replayed as a CUDA graph)",
+                       "exchange": args.tp_exchange, "device_status": status},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}, per GPU", "bytes_per_launch": per_gpu,
                          "note": "bytes one GPU reads per step: its factor shards + the replicated factors + its K/V rows + lm_head"},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    model.close()
 
 
 def roofline_of(r, steps, peak, peak_kind):
@@ -390,6 +395,9 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="tensor-parallel decode of ONE model over the ranks (configuration 4: --shape 70b --batch 8 "
                          "--ctx 4096 under torchrun); a secondary workload")
+    ap.add_argument("--tp-exchange", default="peer", choices=("peer", "nccl"),
+                    help="--tp: partial sums exchanged inside the kernels over peer memory (peer) or with an NCCL "
+                         "all-reduce between per-op launches (nccl, the baseline)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -25,6 +25,9 @@ EXPORTS = (
     "fsvd_set_trace_buffer", "fsvd_model_num_stages", "fsvd_lowrank_proj_static", "fsvd_lift",
     "fsvd_q4_packed_bytes", "fsvd_q4_pack", "fsvd_set_wait_limit", "fsvd_workspace_clear_status",
     "fsvd_selftest_wait_timeout", "fsvd_static_status", "fsvd_model_num_barriers",
+    "fsvd_exchange_region_bytes", "fsvd_exchange_region_alloc", "fsvd_exchange_region_free",
+    "fsvd_exchange_region_export", "fsvd_exchange_region_import", "fsvd_exchange_region_release",
+    "fsvd_exchange_create", "fsvd_exchange_destroy", "fsvd_tp_workspace_bytes", "fsvd_tp_decode_layer",
 )
 
 
@@ -109,6 +112,19 @@ def load() -> C.CDLL:
     lib.fsvd_selftest_wait_timeout.argtypes = [vp, sz, vp]
     lib.fsvd_static_status.argtypes = [C.POINTER(ip), ip]
     lib.fsvd_model_num_barriers.argtypes = [vp]
+    lib.fsvd_exchange_region_bytes.argtypes = [ip, ip, ip]
+    lib.fsvd_exchange_region_bytes.restype = sz
+    lib.fsvd_exchange_region_alloc.argtypes = [sz, C.POINTER(vp)]
+    lib.fsvd_exchange_region_free.argtypes = [vp]
+    lib.fsvd_exchange_region_export.argtypes = [vp, C.c_char_p]
+    lib.fsvd_exchange_region_import.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.fsvd_exchange_region_release.argtypes = [vp]
+    lib.fsvd_exchange_create.argtypes = [ip, ip, C.POINTER(vp), ip, ip, vp, C.POINTER(vp)]
+    lib.fsvd_exchange_destroy.argtypes = [vp]
+    lib.fsvd_tp_workspace_bytes.argtypes = [C.POINTER(FsvdDims)]
+    lib.fsvd_tp_workspace_bytes.restype = sz
+    lib.fsvd_tp_decode_layer.argtypes = [
+        C.POINTER(FsvdDims), C.POINTER(FsvdLayer), vp, vp, vp, vp, vp, vp, vp, sz, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("fsvd_version",):

@@ -1119,6 +1119,20 @@ int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void
                       (cudaStream_t)stream);
 }
 
+// Tensor-parallel layer on the rank's shards (fsvd_tile.cu; exchange protocol in fsvd_exchange.h).
+size_t fsvd_tp_workspace_bytes(const fsvd_dims* dims) { return fsvd_tile_workspace_bytes(dims); }
+
+int fsvd_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
+                         const int* cache_seqlens, const void* x_in, void* x_out, fsvd_exchange* ex, void* ws,
+                         size_t ws_bytes, void* stream) {
+  if (!dims || !layer || !cos_tab || !sin_tab || !cache_seqlens || !x_in || !x_out || !ex)
+    return fail(FSVD_ERR_ARG, "null argument");
+  if (int e = check_layer_ptrs(*layer)) return e;
+  if (!aligned16(ws)) return fail(FSVD_ERR_ALIGN, "workspace is not 16-byte aligned");
+  return fsvd_tile_tp_decode_layer(dims, layer, cos_tab, sin_tab, cache_seqlens, x_in, x_out, ex, ws, ws_bytes,
+                                   current_settings().wait_limit, stream);
+}
+
 // ------------------------------------------------------------------------------- model
 struct fsvd_model {
   fsvd_dims D;

@@ -39,6 +39,7 @@
 #include <vector>
 
 #include "../../include/flashsvd_b200.h"
+#include "fsvd_exchange.h"
 #include "fsvd_stage.h"
 #include "fsvd_tile.h"
 
@@ -65,6 +66,7 @@ enum TileEpi : int {
   TE_ROPE_Q = 4,     // rotate the head's (j, j + Dh/2) pair at position seqlens[b], store to out[b, p]
   TE_ROPE_K = 5,     // same rotation, store into the key cache at position seqlens[b]
   TE_VCACHE = 6,     // store rnd(acc) into the value cache at position seqlens[b]
+  TE_PUSH = 7,       // tensor-parallel partial sums: rnd(acc) into this rank's slot of every rank's exchange region
 };
 
 struct GemmArgs {
@@ -84,6 +86,8 @@ struct GemmArgs {
   int* status;             // SyncState::status of the workspace
   long long wait_limit;
   unsigned long long* trace;   // debugging: %globaltimer marks, 16 per CTA (null = off)
+  fsvd_exch::Geom ex;          // TE_PUSH: the exchange regions of all ranks (fsvd_exchange.h)
+  const unsigned* ex_seq;      // TE_PUSH: this rank's exchange sequence number
 };
 
 // ------------------------------------------------------------------------------- PTX
@@ -340,6 +344,7 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   // for the accumulators
   pdl_wait();
   tmark(a, 2);
+  const unsigned push_seq = a.epi == TE_PUSH ? *reinterpret_cast<const volatile unsigned*>(a.ex_seq) : 0u;
   // the residual rows this CTA will add have usually left L2 since they were written (a layer's
   // factors stream through in between): ask for them now, the epilogue is several microseconds away
   if (a.epi == TE_RESID && lane == 0) {
@@ -430,6 +435,15 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           if (i < nb) stbf(a.out, o0 + (size_t)i * a.P, res[i] + rnd(v[i]));
+      } else if (a.epi == TE_PUSH) {
+        // the same rounded partial sums into slot [parity][this rank] of every rank's region
+        // (peer stores over NVLink; the rank's own region among them)
+        for (int q = 0; q < a.ex.world; ++q) {
+          unsigned char* dst = fsvd_exch::slot_ptr(a.ex, q, push_seq & 1u, a.ex.rank);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (i < nb) stbf(dst, o0 + (size_t)i * a.P, v[i]);
+        }
       } else if (a.epi == TE_SWIGLU) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -487,6 +501,13 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   tmark(a, 7);
   tc_fence_before();
   __syncthreads();
+  // TE_PUSH: every store of this CTA is ordered before the flags that thread q raises in rank q's
+  // region (the CTA barrier above, then a system-wide fence and a release store)
+  if (a.epi == TE_PUSH && tid < a.ex.world) {
+    __threadfence_system();
+    fsvd_exch::st_release_sys(fsvd_exch::flag_ptr(a.ex, tid, push_seq & 1u, a.ex.rank, tile * a.segs + seg), push_seq);
+  }
+  __syncwarp();
   if (*giveup)
     for (int i = 0; i < 100; ++i) __nanosleep(1000);   // copies in flight towards this CTA land first
   if (warp == 0) tc_dealloc(tmem, a.tmem_cols);
@@ -518,6 +539,126 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
   const float inv = rsqrtf(tot / (float)d + eps);
   for (int i = tid; i < d; i += 256)
     out[(size_t)b * d + i] = __float2bfloat16_rn(__bfloat162float(w[i]) * rnd(__bfloat162float(xr[i]) * inv));
+}
+
+// ------------------------------------------------------------------------------- exchange + RMSNorm rows
+// Second half of a tensor-parallel exchange (protocol: fsvd_exchange.h), one CTA per row b:
+//     wait until every rank's GEMM has posted exchange number seq in this rank's region,
+//     h[b, :]  = rnd(resid[b, :] + rnd(sum over ranks, in rank order, of slot[rank][b, :]))
+//     xn[b, :] = rnd(w * rnd(h[b, :] * rsqrt(mean(h[b, :]^2) + eps)))             (when xn != null)
+// The slots are read past L1 (another GPU wrote them).  The last CTA to finish advances the rank's
+// sequence number.  A wait that runs out records DS_PEER_TIMEOUT and the rank it waited for; the
+// row is then computed from whatever the slots hold.
+struct ReduceArgs {
+  fsvd_exch::Geom ex;
+  fsvd_exch::Ctrl* ctrl;
+  int nflags;                    // CTAs of the pushing GEMM
+  const __nv_bfloat16* resid;
+  __nv_bfloat16* out;
+  const __nv_bfloat16* norm_w;
+  __nv_bfloat16* xn;
+  int d;
+  float eps;
+  int* status;                   // SyncState::status, status_detail of the workspace
+  long long wait_limit;
+};
+
+__global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_constant__ ReduceArgs a) {
+  __shared__ float red[8];
+  __shared__ int giveup_sh;
+  const int b = blockIdx.x, tid = threadIdx.x;
+  if (tid == 0) giveup_sh = 0;
+  pdl_launch_dependents();
+  pdl_wait();
+  __syncthreads();
+  volatile int* giveup = &giveup_sh;
+  const unsigned seq = *reinterpret_cast<const volatile unsigned*>(&a.ctrl->seq);
+  const unsigned par = seq & 1u;
+  {
+    const int total = a.ex.world * a.nflags;
+    const long long c0 = clock64();
+    for (int i = tid; i < total && !*giveup; i += 256) {
+      const int src = i / a.nflags;
+      const unsigned* f = fsvd_exch::flag_ptr(a.ex, a.ex.rank, par, src, i - src * a.nflags);
+      unsigned spins = 0;
+      while ((int)(fsvd_exch::ld_acquire_sys(f) - seq) < 0) {
+        if ((++spins & 15u) == 0) {
+          if (*giveup) break;
+          if (clock64() - c0 > a.wait_limit) {
+            if (atomicCAS(a.status, (int)DS_OK, (int)fsvd_exch::DS_PEER_TIMEOUT) == (int)DS_OK) a.status[1] = src;
+            *giveup = 1;
+            break;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  const size_t row = (size_t)b * a.d;
+  const unsigned char* slot0 = fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, 0);
+  float ss = 0.0f;
+  for (int i = tid * 8; i < a.d; i += 256 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (int q = 0; q < a.ex.world; ++q) {
+      const uint4 t = __ldcg(reinterpret_cast<const uint4*>(slot0 + (size_t)q * a.ex.slot_bytes + (row + i) * 2));
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f2 = __bfloat1622float2(h2[j]);
+        acc[2 * j] += f2.x;
+        acc[2 * j + 1] += f2.y;
+      }
+    }
+    const uint4 rr = *reinterpret_cast<const uint4*>(a.resid + row + i);
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f2 = __bfloat1622float2(r2[j]);
+      const float h0 = rnd(f2.x + rnd(acc[2 * j])), h1 = rnd(f2.y + rnd(acc[2 * j + 1]));
+      ss += h0 * h0 + h1 * h1;
+      o2[j] = __floats2bfloat162_rn(h0, h1);
+    }
+    *reinterpret_cast<uint4*>(a.out + row + i) = o;
+  }
+  if (a.xn) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = rsqrtf(tot / (float)a.d + a.eps);
+    for (int i = tid * 8; i < a.d; i += 256 * 8) {
+      // the thread reads back the eight values it stored above
+      const uint4 hh = *reinterpret_cast<const uint4*>(a.out + row + i);
+      const uint4 ww = *reinterpret_cast<const uint4*>(a.norm_w + i);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hh);
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&ww);
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 hf = __bfloat1622float2(h2[j]), wf = __bfloat1622float2(w2[j]);
+        o2[j] = __floats2bfloat162_rn(wf.x * rnd(hf.x * inv), wf.y * rnd(hf.y * inv));
+      }
+      *reinterpret_cast<uint4*>(a.xn + row + i) = o;
+    }
+  }
+  // every CTA has read the sequence number before it arrives here: the last one moves it on
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&a.ctrl->done, 1u) == gridDim.x - 1) {
+      a.ctrl->done = 0u;
+      *reinterpret_cast<volatile unsigned*>(&a.ctrl->seq) = seq + 1u;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------- attention
@@ -1491,8 +1632,18 @@ static int launch_attn(const AttnArgs& at, cudaStream_t st) {
 
 // The last GEMM of a layer (down lift + residual) is planned per call site: its output buffer
 // differs between the per-layer entry point and the model.
+static int launch_reduce(const ReduceArgs& r, int rows, cudaStream_t st) {
+  if (launch_pdl(exchange_reduce_rows_kernel, dim3((unsigned)rows), dim3(256), 0, st, r) != cudaSuccess)
+    return fail(FSVD_ERR_CUDA, "exchange kernel launch failed");
+  fsvd_tile_count_launch();
+  return 0;
+}
+
+// r1 / r2 (tensor-parallel layer): the o lift and the down lift push their partial sums to every
+// rank; r1 replaces the second RMSNorm (sum + residual + norm), r2 finishes the layer output.
 static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_dims& D, const fsvd_layer& Lw,
-                     const void* x_in, char* ws, const TileWs& L, cudaStream_t st) {
+                     const void* x_in, char* ws, const TileWs& L, cudaStream_t st, const ReduceArgs* r1 = nullptr,
+                     const ReduceArgs* r2 = nullptr) {
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
   const __nv_bfloat16* mid = reinterpret_cast<const __nv_bfloat16*>(ws + L.mid);
   int e;
@@ -1512,12 +1663,17 @@ static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_
   if ((e = launch_attn(lp.at, st))) return e;
   if ((e = launch_gemm(lp.g[4], st))) return e;
   if ((e = launch_gemm(lp.g[5], st))) return e;
-  launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, mid, reinterpret_cast<const __nv_bfloat16*>(Lw.ln2_w), xn,
-             D.d, D.eps);
-  fsvd_tile_count_launch();
+  if (r1) {
+    if ((e = launch_reduce(*r1, D.B, st))) return e;
+  } else {
+    launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, mid, reinterpret_cast<const __nv_bfloat16*>(Lw.ln2_w), xn,
+               D.d, D.eps);
+    fsvd_tile_count_launch();
+  }
   for (int i = 6; i < 9; ++i)
     if ((e = launch_gemm(lp.g[i], st))) return e;
   if ((e = launch_gemm(down_lift, st))) return e;
+  if (r2 && (e = launch_reduce(*r2, D.B, st))) return e;
   if (cudaGetLastError() != cudaSuccess) return fail(FSVD_ERR_CUDA, "kernel launch failed");
   return 0;
 }
@@ -1529,6 +1685,45 @@ static int plan_down_lift(GemmPlan& g, const fsvd_dims& D, const fsvd_layer& Lw,
   g.a.out = x_out;
   g.a.resid = ws + L.mid;
   return 0;
+}
+
+// Tensor-parallel layer: the plans of the single-GPU layer on the rank's shards, with the two
+// residual lifts turned into pushes and the reductions that complete them.
+struct TpPlan {
+  LayerPlan lp;
+  GemmPlan dl;
+  ReduceArgs r1, r2;
+};
+static int plan_tp_layer(TpPlan& tp, const fsvd_dims& D, const fsvd_layer& Lw, const void* cos_tab, const void* sin_tab,
+                         const int* seqlens, const void* x_in, void* x_out, const fsvd_exchange& ex, char* ws, const TileWs& L,
+                         long long wait_limit) {
+  if (int e = plan_layer(tp.lp, D, Lw, cos_tab, sin_tab, seqlens, x_in, x_out, ws, L, wait_limit)) return e;
+  if (int e = plan_down_lift(tp.dl, D, Lw, x_out, ws, L, wait_limit)) return e;
+  fsvd_exch::Ctrl* ctrl = reinterpret_cast<fsvd_exch::Ctrl*>(ex.geom.region[ex.geom.rank]);
+  int* status = &reinterpret_cast<SyncState*>(ws + L.sync)->status;
+  auto to_push = [&](GemmPlan& g, ReduceArgs& r, const void* resid, void* out, const void* norm_w, void* xn) -> int {
+    if ((unsigned)(g.a.tiles * g.a.segs) > ex.geom.flag_cap) return fail(FSVD_ERR_UNSUPPORTED, "more CTAs in a lift than exchange flags");
+    g.a.epi = TE_PUSH;
+    g.a.out = nullptr;
+    g.a.resid = nullptr;
+    g.a.ex = ex.geom;
+    g.a.ex_seq = &ctrl->seq;
+    memset(&r, 0, sizeof(r));
+    r.ex = ex.geom;
+    r.ctrl = ctrl;
+    r.nflags = g.a.tiles * g.a.segs;
+    r.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+    r.out = reinterpret_cast<__nv_bfloat16*>(out);
+    r.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
+    r.xn = reinterpret_cast<__nv_bfloat16*>(xn);
+    r.d = D.d;
+    r.eps = D.eps;
+    r.status = status;
+    r.wait_limit = wait_limit;
+    return 0;
+  };
+  if (int e = to_push(tp.lp.g[5], tp.r1, x_in, ws + L.mid, Lw.ln2_w, ws + L.xn)) return e;
+  return to_push(tp.dl, tp.r2, ws + L.mid, x_out, nullptr, nullptr);
 }
 
 }  // namespace fsvd_tile
@@ -1590,6 +1785,56 @@ int fsvd_tile_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const
     cache.push_back(c);
   }
   return run_layer(c->lp, c->dl, D, *layer, x_in, reinterpret_cast<char*>(ws), L, (cudaStream_t)stream);
+}
+
+int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
+                              const int* cache_seqlens, const void* x_in, void* x_out, fsvd_exchange* ex, void* ws,
+                              size_t ws_bytes, long long wait_limit, void* stream) {
+  const fsvd_dims& D = *dims;
+  if (int e = device_limits()) return e;
+  if (int e = check_tile_dims(D)) return e;
+  if (D.rows_are_positions) return fail(FSVD_ERR_UNSUPPORTED, "the tensor-parallel layer takes one row per sequence");
+  if (D.d != ex->d || D.B > ex->max_rows) return fail(FSVD_ERR_ARG, "the exchange was created for another width or fewer rows");
+  const TileWs L = tile_layout(D, g_sms);
+  if (!ws || ws_bytes < L.total) return fail(FSVD_ERR_WORKSPACE, "workspace too small for this batch");
+  if (x_in == x_out) return fail(FSVD_ERR_ARG, "x_in and x_out must differ");
+  if ((reinterpret_cast<uintptr_t>(x_in) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(layer->ln2_w)) & 15)
+    return fail(FSVD_ERR_ALIGN, "x_in, x_out and the norm weights must be 16-byte aligned");
+  struct Cached {
+    fsvd_dims D;
+    fsvd_layer Lw;
+    const void *cos_tab, *sin_tab, *x_in;
+    const int* seqlens;
+    void *x_out, *ws;
+    const fsvd_exchange* ex;
+    long long wait_limit;
+    TpPlan tp;
+  };
+  static std::mutex mu;
+  static std::vector<Cached*> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  Cached* c = nullptr;
+  for (Cached* k : cache)
+    if (!memcmp(&k->D, &D, sizeof(D)) && !memcmp(&k->Lw, layer, sizeof(*layer)) && k->cos_tab == cos_tab &&
+        k->sin_tab == sin_tab && k->x_in == x_in && k->seqlens == cache_seqlens && k->x_out == x_out && k->ws == ws &&
+        k->ex == ex && k->wait_limit == wait_limit)
+      c = k;
+  if (!c) {
+    if (cache.size() >= 256) {
+      for (Cached* k : cache) delete k;
+      cache.clear();
+    }
+    c = new Cached();
+    c->D = D; c->Lw = *layer; c->cos_tab = cos_tab; c->sin_tab = sin_tab; c->x_in = x_in; c->seqlens = cache_seqlens;
+    c->x_out = x_out; c->ws = ws; c->ex = ex; c->wait_limit = wait_limit;
+    if (int e = plan_tp_layer(c->tp, D, *layer, cos_tab, sin_tab, cache_seqlens, x_in, x_out, *ex, reinterpret_cast<char*>(ws), L,
+                              wait_limit)) {
+      delete c;
+      return e;
+    }
+    cache.push_back(c);
+  }
+  return run_layer(c->tp.lp, c->tp.dl, D, *layer, x_in, reinterpret_cast<char*>(ws), L, (cudaStream_t)stream, &c->tp.r1, &c->tp.r2);
 }
 
 // ---- whole-model decode for batches above 8: the launches of a step captured once in a CUDA graph

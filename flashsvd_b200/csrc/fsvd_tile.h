@@ -6,6 +6,7 @@
 struct fsvd_dims;
 struct fsvd_layer;
 struct fsvd_tile_model;
+struct fsvd_exchange;
 
 // provided by fsvd_api.cu: the library's last-error text and launch counter
 void fsvd_tile_set_error(int code, const char* msg);
@@ -18,6 +19,9 @@ size_t fsvd_tile_workspace_bytes(const fsvd_dims* dims);
 int fsvd_tile_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
                            const int* cache_seqlens, const void* x_in, void* x_out, void* ws, size_t ws_bytes,
                            long long wait_limit, void* stream);
+int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
+                              const int* cache_seqlens, const void* x_in, void* x_out, fsvd_exchange* ex, void* ws,
+                              size_t ws_bytes, long long wait_limit, void* stream);
 int fsvd_tile_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const void* embed, const void* final_norm_w,
                            const void* lm_head, const void* cos_tab, const void* sin_tab, int max_steps, long long wait_limit,
                            fsvd_tile_model** out);

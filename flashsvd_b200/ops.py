@@ -270,3 +270,21 @@ def decode_layer(dims: FsvdDims, layer: FsvdLayer, cos, sin, cache_seqlens, x_in
         C.byref(dims), C.byref(layer), _ptr(cos), _ptr(sin), _ptr(cache_seqlens), _ptr(x_in),
         _ptr(x_out), ws.ptr, ws.nbytes, _stream()))
     return x_out
+
+
+def make_tp_workspace(dims: FsvdDims, device) -> Workspace:
+    """Workspace of the tensor-parallel layer (tiled path at every batch size)."""
+    n = int(_lib.load().fsvd_tp_workspace_bytes(C.byref(dims)))
+    if n == 0:
+        check(-2)
+    return Workspace(torch.zeros(n, dtype=torch.uint8, device=device), n)
+
+
+def tp_decode_layer(dims: FsvdDims, layer: FsvdLayer, cos, sin, cache_seqlens, x_in, x_out, exchange, ws: Workspace):
+    """One decoder layer on this rank's shards; the partial sums of the output projection and of the
+    down projection are exchanged with the other ranks inside the kernels (``exchange``: the handle of
+    a ``tensor_parallel.PeerExchange``).  x_out is the full layer output, the same on every rank."""
+    check(_lib.load().fsvd_tp_decode_layer(
+        C.byref(dims), C.byref(layer), _ptr(cos), _ptr(sin), _ptr(cache_seqlens), _ptr(x_in), _ptr(x_out),
+        exchange, ws.ptr, ws.nbytes, _stream()))
+    return x_out

@@ -8,14 +8,23 @@ query heads with their Hk / N key / value heads and I / N columns of the SwiGLU 
     replicated           q_v, k_v, v_v, gate_v, up_v (they read the full hidden state), o_u, down_u
 
 so that every rank produces a partial sum [B, d] of the attention output projection and of the MLP
-output, and two all-reduces per layer (NCCL over NVLink) complete them.  Rank 0 adds the residual
-before the all-reduce, so the sum carries it once.  The KV cache of a rank holds its own heads only.
+output, and two exchanges per layer complete them.  The KV cache of a rank holds its own heads only.
 
-The per-rank arithmetic is the library's ordinary entry points on the shards
-(``fsvd_qkv_rope_append``, ``fsvd_flash_decode``, ``fsvd_lowrank_proj``, ``fsvd_mlp_swiglu_decode``);
-the collective is ``torch.distributed.all_reduce``.  Rounding differs from the single-GPU path in
-one place: each rank's partial output is rounded to the model dtype before the sum (the
-single-GPU path rounds the rank-space vector once, after the full sum).
+Two ways to run a layer:
+
+``exchange="peer"`` (default for bf16): ``fsvd_tp_decode_layer`` — the layer as tiled tensor-core
+    GEMMs on the shards; the epilogue of the o lift and of the down lift stores every finished tile
+    into an exchange region of EVERY rank (peer stores over NVLink, regions mapped with CUDA IPC) and
+    raises a flag per CTA; the next kernel polls the flags of its own region, adds the partial sums
+    in rank order plus the residual and applies the next RMSNorm.  No collective call on the path.
+``exchange="nccl"``: the library's per-op entry points on the shards (``fsvd_qkv_rope_append``,
+    ``fsvd_flash_decode``, ``fsvd_lowrank_proj``, ``fsvd_mlp_swiglu_decode``) with
+    ``torch.distributed.all_reduce`` of the two partial sums; rank 0 adds the residual before the
+    all-reduce, so the sum carries it once.  The baseline the peer exchange is measured against.
+
+Rounding differs from the single-GPU path in one place: each rank's partial output is rounded to
+the model dtype before the sum (the single-GPU path rounds the rank-space vector once, after the
+full sum).
 
 Reference: the partitioning is the one the reference's north-star configuration names; its own code
 has no tensor-parallel path (it shards whole layers with ``layer_device_map``,
@@ -23,10 +32,13 @@ runtime/cache/attn_dense_kv.py:52-58).
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
-from . import ops
+from . import _lib, ops
+from ._lib import check
 
 ROW_SHARDED = ("q_u", "k_u", "v_u", "gate_u", "up_u")
 COL_SHARDED = ("o_v", "down_v")
@@ -52,19 +64,106 @@ def shard_layer_weights(w: dict, *, H: int, Hk: int, Dh: int, rank: int, world: 
     return {k: (v.contiguous() if torch.is_tensor(v) else v) for k, v in out.items()}
 
 
+def _rendezvous() -> None:
+    """Host barrier of the ranks with the device idle on both sides."""
+    torch.cuda.synchronize()
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
 def _all_reduce(t: torch.Tensor) -> torch.Tensor:
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t)
     return t
 
 
+def region_layout(world: int, max_rows: int, d: int) -> dict:
+    """Byte offsets inside an exchange region (mirror of csrc/fsvd_exchange.h): flags
+    [2 parities][world][flag_cap] uint32 at ``flags``, slots [2 parities][world][slot_bytes] at
+    ``slots`` (a slot = one rank's partial sums, bf16 [rows, d])."""
+    al = lambda n: (n + 255) // 256 * 256
+    flag_cap = (d + 127) // 128 * 8
+    slot_bytes = al(max_rows * d * 2)
+    flags = 256
+    slots = flags + al(2 * world * flag_cap * 4)
+    return {"flag_cap": flag_cap, "slot_bytes": slot_bytes, "flags": flags, "slots": slots,
+            "total": slots + 2 * world * slot_bytes}
+
+
+class PeerExchange:
+    """This rank's exchange region, the other ranks' regions mapped into this process, and the
+    library's exchange object over them (``handle``).
+
+    ``regions=None``: the region is allocated by the library, its 64-byte export handle is gathered
+    over ``group`` (any backend) and the peers' regions are imported; ranks must be the processes
+    of one node with peer access between their GPUs.  ``regions=[...]``: base addresses given by
+    the caller (tests on one GPU)."""
+
+    def __init__(self, *, rank: int, world: int, max_rows: int, d: int, group=None, regions=None):
+        lib = _lib.load()
+        self.rank, self.world, self.group = int(rank), int(world), group
+        self.nbytes = int(lib.fsvd_exchange_region_bytes(self.world, int(max_rows), int(d)))
+        if self.nbytes == 0:
+            raise ValueError(f"exchange of {world} ranks, {max_rows} rows, width {d}: at most 8 ranks, 128 rows")
+        self._own, self._imported, self.handle = None, [], None
+        if regions is None:
+            p = C.c_void_p()
+            check(lib.fsvd_exchange_region_alloc(self.nbytes, C.byref(p)))
+            self._own = p.value
+            mine = C.create_string_buffer(64)
+            check(lib.fsvd_exchange_region_export(self._own, mine))
+            handles = [None] * self.world
+            if self.world > 1:
+                dist.all_gather_object(handles, bytes(mine.raw), group=group)   # also: every region exists and is zero
+            regions = []
+            for q in range(self.world):
+                if q == self.rank:
+                    regions.append(self._own)
+                    continue
+                pp = C.c_void_p()
+                check(lib.fsvd_exchange_region_import(handles[q], C.byref(pp)))
+                self._imported.append(pp.value)
+                regions.append(pp.value)
+        self.regions = [int(r) for r in regions]
+        arr = (C.c_void_p * self.world)(*self.regions)
+        h = C.c_void_p()
+        check(lib.fsvd_exchange_create(self.rank, self.world, arr, int(max_rows), int(d),
+                                       torch.cuda.current_stream().cuda_stream, C.byref(h)))
+        self.handle = h
+
+    def close(self) -> None:
+        """Collective when the regions were exchanged over a group: no rank unmaps while another may
+        still be storing into its region."""
+        lib = _lib.load()
+        if self.handle is not None:
+            torch.cuda.synchronize()
+            if self._own is not None and self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)
+            lib.fsvd_exchange_destroy(self.handle)
+            self.handle = None
+            for p in self._imported:
+                lib.fsvd_exchange_region_release(p)
+            self._imported = []
+            if self._own is not None:
+                if self.world > 1 and dist.is_initialized():
+                    dist.barrier(group=self.group)
+                lib.fsvd_exchange_region_free(self._own)
+                self._own = None
+
+
 class TPDecodeLayer:
-    """One decoder layer on this rank's shards."""
+    """One decoder layer on this rank's shards.  ``exchange``: a PeerExchange (partial sums exchanged
+    inside the kernels) or None (per-op entry points + NCCL all-reduce)."""
 
     def __init__(self, w_shard: dict, *, H: int, Hk: int, Dh: int, rank: int, world: int, batch: int, S_max: int,
-                 eps: float, device, dtype=torch.bfloat16):
-        if batch > (8 if dtype == torch.bfloat16 else 4):
-            raise ValueError("the tensor-parallel layer takes the batch sizes of the single-launch kernel (<= 8)")
+                 eps: float, device, dtype=torch.bfloat16, exchange: PeerExchange | None = None):
+        self.exchange = exchange
+        if exchange is not None:
+            if dtype != torch.bfloat16 or not 1 <= batch <= 128:
+                raise ValueError("the peer-exchange layer takes bf16 and 1..128 sequences")
+        elif batch > (8 if dtype == torch.bfloat16 else 4):
+            raise ValueError("the all-reduce layer takes the batch sizes of the single-launch kernel (<= 8)")
         self.rank, self.world, self.eps = int(rank), int(world), float(eps)
         self.Hl, self.Hkl, self.Dh = H // world, Hk // world, Dh
 
@@ -86,7 +185,16 @@ class TPDecodeLayer:
         dims = ops.make_dims(dtype=dtype, B=batch, d=d, H=self.Hl, Hk=self.Hkl, Dh=Dh, I=Il, Rq=self.ranks[0],
                              Rk=self.ranks[1], Rv=self.ranks[2], Ro=self.o_v.shape[0], Rg=self.gate_u.shape[1],
                              Ru=self.up_u.shape[1], Rd=self.down_v.shape[0], S_max=S_max, eps=eps)
-        self.ws = ops.make_workspace(dims, device)
+        self.dims = dims
+        if exchange is None:
+            self.ws = ops.make_workspace(dims, device)
+        else:
+            self.ws = ops.make_tp_workspace(dims, device)
+            self.out = torch.empty(batch, d, dtype=dtype, device=device)
+            self._struct = ops.make_layer_struct({
+                "ln1_w": self.ln1, "qkv_v": self.qkv_v, "q_u": self.q_u, "k_u": self.k_u, "v_u": self.v_u, "o_v": self.o_v,
+                "o_u": self.o_u, "ln2_w": self.ln2, "upgate_v": self.upgate_v, "gate_u": self.gate_u, "up_u": self.up_u,
+                "down_v": self.down_v, "down_u": self.down_u, "k_cache": self.k_cache, "v_cache": self.v_cache})
 
     def bytes_per_step(self, ctx: int, batch: int) -> int:
         """Factor bytes this rank streams per step plus the K / V rows it reads."""
@@ -96,6 +204,10 @@ class TPDecodeLayer:
 
     def forward(self, x: torch.Tensor, seqlens: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         B = x.shape[0]
+        if self.exchange is not None:
+            if B != self.dims.B:
+                raise ValueError(f"the layer was built for {self.dims.B} sequences")
+            return ops.tp_decode_layer(self.dims, self._struct, cos, sin, seqlens, x, self.out, self.exchange.handle, self.ws)
         first = self.rank == 0
         q = ops.qkv_rope_append(x, self.qkv_v, self.q_u, self.k_u, self.v_u, cos, sin, self.k_cache, self.v_cache,
                                 seqlens, self.ws, num_heads=self.Hl, num_kv_heads=self.Hkl, head_dim=self.Dh,
@@ -128,9 +240,10 @@ class TPModel:
         self._head_ws = ops.make_workspace(dims, device)
         self._graph = None
         self._use_graph = bool(use_graph)
+        self._x0 = torch.zeros(self.B, embed.shape[1], dtype=dtype, device=device)
 
     def _step_eager(self) -> None:
-        x = self.embed[self.tokens]
+        x = torch.index_select(self.embed, 0, self.tokens, out=self._x0)
         for layer in self.layers:
             x = layer.forward(x, self.seqlens, self.cos, self.sin)
         xf = x.float()
@@ -145,8 +258,11 @@ class TPModel:
                 self._step_eager()
                 continue
             if self._graph is None:
-                # one eager step first (workspaces, cached programs, NCCL communicators), undone below
+                # one eager step first (workspaces, cached programs, NCCL communicators), undone below;
+                # the ranks start it together: a wait for a peer's partial sums is bounded by the
+                # library's wait budget (about 2 s), which a rank still building its model would exceed
                 tok, sl = self.tokens.clone(), self.seqlens.clone()
+                _rendezvous()
                 self._step_eager()
                 torch.cuda.synchronize()
                 self.tokens.copy_(tok)
@@ -157,8 +273,18 @@ class TPModel:
                 self._graph = g
                 self.tokens.copy_(tok)
                 self.seqlens.copy_(sl)
+                _rendezvous()
                 # the captured step has not run: positions written by the eager step are rewritten
             self._graph.replay()
+
+    exchange = None
+
+    def close(self) -> None:
+        """Collective: releases the graph and the exchange regions."""
+        self._graph = None
+        if self.exchange is not None:
+            self.exchange.close()
+            self.exchange = None
 
     def status(self) -> int:
         for layer in self.layers:
@@ -174,10 +300,15 @@ class TPModel:
 
 
 def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: int, max_new: int, seed: int = 0,
-                    dtype=torch.bfloat16, n_layers=None, use_graph: bool = True) -> TPModel:
+                    dtype=torch.bfloat16, n_layers=None, use_graph: bool = True, exchange: str = "peer") -> TPModel:
     """Seeded random model of ``shape`` (a synthetic.ModelShape), every rank drawing the same full
-    factors on its device and keeping its shards; caches pre-filled with ``ctx`` N(0,1) rows."""
+    factors on its device and keeping its shards; caches pre-filled with ``ctx`` N(0,1) rows.
+    ``exchange``: "peer" (partial sums exchanged inside the kernels) or "nccl" (all-reduce)."""
     import math
+
+    if exchange not in ("peer", "nccl"):
+        raise ValueError("exchange must be 'peer' or 'nccl'")
+    ex = PeerExchange(rank=rank, world=world, max_rows=batch, d=shape.d) if exchange == "peer" else None
 
     L = shape.n_layers if n_layers is None else int(n_layers)
     d, HD, KD, I = shape.d, shape.H * shape.Dh, shape.Hk * shape.Dh, shape.I
@@ -197,7 +328,7 @@ def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: in
                 "ln1": torch.ones(d, device=device, dtype=dtype), "ln2": torch.ones(d, device=device, dtype=dtype)}
         sh = shard_layer_weights(full, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=rank, world=world)
         layer = TPDecodeLayer(sh, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=rank, world=world, batch=batch, S_max=S_max,
-                              eps=shape.eps, device=device, dtype=dtype)
+                              eps=shape.eps, device=device, dtype=dtype, exchange=ex)
         if ctx > 0:
             g2 = torch.Generator(device=device).manual_seed(seed * 100003 + 7919 + li * world + rank)
             layer.k_cache[:, :ctx].copy_(torch.randn(layer.k_cache[:, :ctx].shape, device=device, generator=g2).to(dtype))
@@ -209,6 +340,7 @@ def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: in
     lm_head = (torch.randn(shape.vocab, d, device=device, dtype=torch.float32, generator=gen) / math.sqrt(d)).to(dtype)
     model = TPModel(layers, embed, torch.ones(d, device=device, dtype=dtype), lm_head, batch=batch, S_max=S_max,
                     head_dim=shape.Dh, theta=shape.theta, eps=shape.eps, device=device, dtype=dtype, use_graph=use_graph)
+    model.exchange = ex
     model.seqlens.fill_(ctx)
     model.tokens.copy_(torch.arange(batch, device=device) % shape.vocab)
     return model

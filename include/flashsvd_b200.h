@@ -275,6 +275,45 @@ size_t fsvd_q4_packed_bytes(int rows, int K);
 int fsvd_q4_pack(const void* qweight, const void* scales, const void* zeros, int rows, int K,
                  void* out, void* stream);
 
+/* ---- Tensor-parallel decode: one model over the GPUs of a node, one process per GPU ----------
+ * No counterpart in the reference (it has no multi-GPU decode path; it places whole layers on
+ * devices, runtime/cache/attn_dense_kv.py:52-58).  Partitioning: each of `world` ranks holds H / world
+ * query heads with their Hk / world key / value heads and I / world columns of the SwiGLU
+ * intermediate: q_u, k_u, v_u, gate_u, up_u sharded by rows, o_v and down_v by columns, the other
+ * factors replicated; fsvd_dims carries the rank's H, Hk and I.  The partial sums [B, d] of the
+ * output projection and of the down projection are exchanged inside the kernels: the epilogue of
+ * the GEMM that produces them stores every finished tile straight into an exchange region of every
+ * rank (peer stores over NVLink) and raises a flag per CTA; the kernel that follows polls the flags
+ * of its own region, adds the `world` partial sums in rank order plus the residual, and applies the
+ * next RMSNorm.  No collective library call is on the path.  Waits for a peer are bounded by
+ * fsvd_set_wait_limit; when one runs out the workspace status reads 8 (FSVD_ERR_DEVICE_WAIT) and the
+ * step completes with whatever arrived.
+ *
+ * Set-up per rank: allocate a region (fsvd_exchange_region_alloc, zero-filled), export it
+ * (fsvd_exchange_region_export: 64 opaque bytes to send to the other processes by any means),
+ * import the other ranks' regions (fsvd_exchange_region_import), and create the exchange from the
+ * `world` base pointers in rank order (regions[rank] = the rank's own).  All ranks must have
+ * allocated before any rank runs a layer.  Every rank must run the same sequence of
+ * fsvd_tp_decode_layer calls on one exchange. */
+typedef struct fsvd_exchange fsvd_exchange;
+size_t fsvd_exchange_region_bytes(int world, int max_rows, int d);
+int fsvd_exchange_region_alloc(size_t bytes, void** region);
+int fsvd_exchange_region_free(void* region);
+int fsvd_exchange_region_export(void* region, unsigned char handle[64]);
+int fsvd_exchange_region_import(const unsigned char handle[64], void** region);
+int fsvd_exchange_region_release(void* imported_region);
+int fsvd_exchange_create(int rank, int world, void* const* regions, int max_rows, int d, void* stream,
+                         fsvd_exchange** out);
+int fsvd_exchange_destroy(fsvd_exchange* ex);
+/* One decoder layer on this rank's shards (bf16, 1 <= B <= max_rows rows, tiled tensor-core path
+ * at every batch size): x_out = the full layer output, identical on every rank.  The workspace is
+ * fsvd_workspace_bytes of the rank's dims with B >= 9 semantics (ask with the same dims).  The
+ * appended key / value rows are the rank's own heads. */
+size_t fsvd_tp_workspace_bytes(const fsvd_dims* dims);
+int fsvd_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab,
+                         const void* sin_tab, const int* cache_seqlens, const void* x_in, void* x_out,
+                         fsvd_exchange* ex, void* ws, size_t ws_bytes, void* stream);
+
 /* Kernel launches enqueued by this library since load (for launch accounting). */
 long long fsvd_launch_count(void);
 
