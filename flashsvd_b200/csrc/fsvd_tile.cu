@@ -313,9 +313,11 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      // ---- MMA issue: four 16-deep steps per k-block and accumulator
+      // ---- MMA issue: four 16-deep steps per k-block and accumulator.  The first activation tile
+      // cannot arrive before the kernel in front has completed: the wait budget starts there.
       const uint32_t idesc = umma_idesc(N);
       bool ok = true;
+      pdl_wait();
       for (int it = 0; it < nit && ok; ++it) {
         const int s = it % NS, round = it / NS;
         ok = wait_bar(full0 + 8 * s, (uint32_t)round & 1u, giveup, a, DS_COPY_TIMEOUT);
