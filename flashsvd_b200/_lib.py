@@ -124,7 +124,7 @@ def load() -> C.CDLL:
     lib.fsvd_tp_workspace_bytes.argtypes = [C.POINTER(FsvdDims)]
     lib.fsvd_tp_workspace_bytes.restype = sz
     lib.fsvd_tp_decode_layer.argtypes = [
-        C.POINTER(FsvdDims), C.POINTER(FsvdLayer), vp, vp, vp, vp, vp, vp, vp, sz, vp]
+        C.POINTER(FsvdDims), C.POINTER(FsvdLayer), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("fsvd_version",):

@@ -1123,14 +1123,15 @@ int fsvd_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void
 size_t fsvd_tp_workspace_bytes(const fsvd_dims* dims) { return fsvd_tile_workspace_bytes(dims); }
 
 int fsvd_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
-                         const int* cache_seqlens, const void* x_in, void* x_out, fsvd_exchange* ex, void* ws,
-                         size_t ws_bytes, void* stream) {
+                         const int* cache_seqlens, const void* x_in, const void* x_norm_in, void* x_out,
+                         const void* next_norm_w, void* x_norm_out, fsvd_exchange* ex, void* ws, size_t ws_bytes,
+                         void* stream) {
   if (!dims || !layer || !cos_tab || !sin_tab || !cache_seqlens || !x_in || !x_out || !ex)
     return fail(FSVD_ERR_ARG, "null argument");
   if (int e = check_layer_ptrs(*layer)) return e;
   if (!aligned16(ws)) return fail(FSVD_ERR_ALIGN, "workspace is not 16-byte aligned");
-  return fsvd_tile_tp_decode_layer(dims, layer, cos_tab, sin_tab, cache_seqlens, x_in, x_out, ex, ws, ws_bytes,
-                                   current_settings().wait_limit, stream);
+  return fsvd_tile_tp_decode_layer(dims, layer, cos_tab, sin_tab, cache_seqlens, x_in, x_norm_in, x_out, next_norm_w,
+                                   x_norm_out, ex, ws, ws_bytes, current_settings().wait_limit, stream);
 }
 
 // ------------------------------------------------------------------------------- model

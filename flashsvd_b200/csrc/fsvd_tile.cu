@@ -34,6 +34,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -544,13 +545,15 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
 }
 
 // ------------------------------------------------------------------------------- exchange + RMSNorm rows
-// Second half of a tensor-parallel exchange (protocol: fsvd_exchange.h), one CTA per row b:
+// Second half of a tensor-parallel exchange (protocol: fsvd_exchange.h).  Row b is shared by the
+// gridDim.y CTAs of a cluster, each with a slice of its columns:
 //     wait until every rank's GEMM has posted exchange number seq in this rank's region,
 //     h[b, :]  = rnd(resid[b, :] + rnd(sum over ranks, in rank order, of slot[rank][b, :]))
 //     xn[b, :] = rnd(w * rnd(h[b, :] * rsqrt(mean(h[b, :]^2) + eps)))             (when xn != null)
-// The slots are read past L1 (another GPU wrote them).  The last CTA to finish advances the rank's
-// sequence number.  A wait that runs out records DS_PEER_TIMEOUT and the rank it waited for; the
-// row is then computed from whatever the slots hold.
+// The slots are read past L1 (another GPU wrote them); the CTAs of a row exchange their sums of
+// squares through distributed shared memory and add them in CTA order.  The last CTA of the grid to
+// finish advances the rank's sequence number.  A wait that runs out records DS_PEER_TIMEOUT and the
+// rank it waited for; the row is then computed from whatever the slots hold.
 struct ReduceArgs {
   fsvd_exch::Geom ex;
   fsvd_exch::Ctrl* ctrl;
@@ -565,10 +568,18 @@ struct ReduceArgs {
   long long wait_limit;
 };
 
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_constant__ ReduceArgs a) {
   __shared__ float red[8];
+  __shared__ float css[kMaxSegs];            // sums of squares of the row's column slices
   __shared__ int giveup_sh;
   const int b = blockIdx.x, tid = threadIdx.x;
+  const int C = gridDim.y, c = blockIdx.y;    // C > 1: launched as clusters of C CTAs along y
   if (tid == 0) giveup_sh = 0;
   pdl_launch_dependents();
   pdl_wait();
@@ -596,11 +607,13 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
     }
   }
   __syncthreads();
+  if (C > 1 && a.xn) cluster_sync();            // every CTA of the row runs before any writes into its shared memory
 
-  const size_t row = (size_t)b * a.d;
+  const int cols = a.d / C, col0 = c * cols;    // the host makes cols a multiple of 8
+  const size_t row = (size_t)b * a.d + col0;
   const unsigned char* slot0 = fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, 0);
   float ss = 0.0f;
-  for (int i = tid * 8; i < a.d; i += 256 * 8) {
+  for (int i = tid * 8; i < cols; i += 256 * 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
@@ -635,11 +648,17 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
     float tot = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += red[i];
+    if (C > 1) {
+      if (tid < C) st_cluster_f32(smem_u32(&css[c]), (uint32_t)tid, tot);
+      cluster_sync();
+      tot = 0.0f;
+      for (int j = 0; j < C; ++j) tot += css[j];
+    }
     const float inv = rsqrtf(tot / (float)a.d + a.eps);
-    for (int i = tid * 8; i < a.d; i += 256 * 8) {
+    for (int i = tid * 8; i < cols; i += 256 * 8) {
       // the thread reads back the eight values it stored above
       const uint4 hh = *reinterpret_cast<const uint4*>(a.out + row + i);
-      const uint4 ww = *reinterpret_cast<const uint4*>(a.norm_w + i);
+      const uint4 ww = *reinterpret_cast<const uint4*>(a.norm_w + col0 + i);
       const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hh);
       const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&ww);
       uint4 o;
@@ -656,7 +675,7 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
   __syncthreads();
   if (tid == 0) {
     __threadfence();
-    if (atomicAdd(&a.ctrl->done, 1u) == gridDim.x - 1) {
+    if (atomicAdd(&a.ctrl->done, 1u) == gridDim.x * gridDim.y - 1) {
       a.ctrl->done = 0u;
       *reinterpret_cast<volatile unsigned*>(&a.ctrl->seq) = seq + 1u;
     }
@@ -1208,6 +1227,238 @@ __global__ void __launch_bounds__(kPfWarps * 32) prompt_attn_kernel(const AttnAr
   }
 }
 
+// ------------------------------------------------------------------------------- grouped-query decode attention
+// Single-query attention for H / Hk = 4 or 8 query heads per kv head on the tensor cores: the G
+// heads that share a kv head are the rows of one m16n8k16 tile (rows G .. 15 are zero), so a key /
+// value row is read once per sequence and multiplied for all its heads at once, instead of one
+// shuffle-reduced dot product per head and key (batch_attn_hs_kernel).  One CTA = (sequence, kv head,
+// key split) as there; each of its 4 warps walks its own blocks of 32 keys: cp.async of the 32 key
+// rows and 32 value rows into the warp's own shared-memory stage, S = Q K^T, running softmax,
+// O += P V with ldmatrix.trans value fragments (the fragment code of prompt_attn_kernel).  The warps
+// merge in shared memory, the splits of a head in split order by the CTA that arrives last.
+constexpr int kGqKeys = 32;      // keys per warp block
+constexpr int kGqMaxSplit = 64;  // key splits of a sequence at most
+
+template <int DH>
+__global__ void __launch_bounds__(kAttnThreads, 3) gqa_decode_attn_kernel(const AttnArgs a) {
+  constexpr int STRIDE = DH * 2 + 16;
+  constexpr int KS = DH / 16, NT = kGqKeys / 8, DT = DH / 8;
+  constexpr int PIECES = DH / 8;                       // 16-byte pieces of a row
+  extern __shared__ __align__(16) unsigned char gq_smem[];
+  __shared__ int last_sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int G = a.H / a.Hk;
+  int idx = blockIdx.x;
+  const int split = idx % a.nsplit;
+  idx /= a.nsplit;
+  const int hk = idx % a.Hk, b = idx / a.Hk;
+  const int n = min(a.seqlens[b] + a.seqlen_add, a.S_max);
+  const int per = ((n + a.nsplit - 1) / a.nsplit + kGqKeys - 1) / kGqKeys * kGqKeys;   // whole blocks per split
+  const int j0 = min(n, split * per), j1 = min(n, j0 + per);
+  const size_t rowstride = (size_t)a.Hk * DH;
+  const size_t cbase = ((size_t)(a.shared_cache ? 0 : b) * a.S_max) * rowstride + (size_t)hk * DH;
+  const __nv_bfloat16* kbase = a.kcache + cbase;
+  const __nv_bfloat16* vbase = a.vcache + cbase;
+  unsigned char* ks_s = gq_smem + (size_t)warp * (2 * kGqKeys * STRIDE);
+  unsigned char* vs_s = ks_s + kGqKeys * STRIDE;
+
+  // Q fragments: row g of the tile = head hk G + g (zero for g >= G), rows 8 .. 15 zero
+  uint32_t qa[KS][2];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qa[ks][0] = qa[ks][1] = 0u;
+    if (g < G) {
+      const __nv_bfloat16* qp = a.q + ((size_t)b * a.H + hk * G + g) * DH + ks * 16 + 2 * t;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  float o[DT][2];
+#pragma unroll
+  for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = 0.0f;
+  float mrow = -INFINITY, lrow = 0.0f;
+
+  for (int k0 = j0 + warp * kGqKeys; k0 < j1; k0 += kAttnWarps * kGqKeys) {
+    // ---- stage this warp's 32 key rows and 32 value rows (rows past the split repeat its last row;
+    // their scores are masked)
+    __syncwarp();
+    for (int i = lane; i < kGqKeys * PIECES; i += 32) {
+      const int r = i / PIECES, c = i - r * PIECES;
+      const size_t src = (size_t)min(k0 + r, j1 - 1) * rowstride + (size_t)c * 8;
+      const uint32_t dk = smem_u32(ks_s + r * STRIDE + c * 16), dv = smem_u32(vs_s + r * STRIDE + c * 16);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk), "l"(kbase + src) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dv), "l"(vbase + src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    // ---- S = Q K^T: 16 (G used) query heads x 32 keys
+    float sc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f;
+      const unsigned char* kr = ks_s + (nt * 8 + g) * STRIDE + 4 * t;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 32);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 32 + 16);
+        mma_bf16_16816(sc[nt], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+      }
+    }
+    // ---- scale, mask, running softmax of row g (its 32 scores sit in the 4 lanes of the group)
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int kj = k0 + nt * 8 + 2 * t + e;
+        const float v = kj < j1 ? sc[nt][e] * a.scale : -INFINITY;
+        sc[nt][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(mrow, mx);           // finite: key k0 is inside the split
+    const float corr = __expf(mrow - mn);
+    mrow = mn;
+    float ps = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pr = __expf(sc[nt][e] - mn);
+        sc[nt][e] = pr;
+        ps += pr;
+      }
+    }
+    ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+    lrow = lrow * corr + ps;
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      o[d][0] *= corr;
+      o[d][1] *= corr;
+    }
+    // ---- O += P V, 16 keys per step (rows 8 .. 15 of P are zero)
+#pragma unroll
+    for (int kk = 0; kk < kGqKeys / 16; ++kk) {
+      const uint32_t pa0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+      const uint32_t pa2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+      const int lr = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const unsigned char* vr = vs_s + lr * STRIDE + ((lane >> 4) & 1) * 16;
+#pragma unroll
+      for (int j = 0; j < DT / 2; ++j) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vr + j * 32);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+        float c0[4] = {o[2 * j][0], o[2 * j][1], 0.0f, 0.0f}, c1[4] = {o[2 * j + 1][0], o[2 * j + 1][1], 0.0f, 0.0f};
+        mma_bf16_16816(c0, pa0, 0u, pa2, 0u, b0, b1);
+        mma_bf16_16816(c1, pa0, 0u, pa2, 0u, b2, b3);
+        o[2 * j][0] = c0[0]; o[2 * j][1] = c0[1];
+        o[2 * j + 1][0] = c1[0]; o[2 * j + 1][1] = c1[1];
+      }
+    }
+  }
+
+  // ---- the four warps meet in shared memory (the stages are free): [warp][head][DH + 4]
+  // (DH values, running maximum, running sum; records stay 16-byte aligned)
+  constexpr int rec = DH + 4;
+  __syncthreads();
+  float* wpart = reinterpret_cast<float*>(gq_smem);
+  if (g < G) {
+    float* mine = wpart + ((size_t)warp * G + g) * rec;
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      mine[d * 8 + 2 * t] = o[d][0];
+      mine[d * 8 + 2 * t + 1] = o[d][1];
+    }
+    if (t == 0) {
+      mine[DH] = mrow;
+      mine[DH + 1] = lrow;
+    }
+  }
+  __syncthreads();
+  const int nsplit = a.nsplit;
+  float* gpart = a.part + ((((size_t)b * a.Hk + hk) * nsplit + split) * G) * rec;
+  for (int i = tid; i < G * DH; i += kAttnThreads) {
+    const int gg = i / DH, dd = i - gg * DH;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, wpart[((size_t)w * G + gg) * rec + DH]);
+    float num = 0.0f, den = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float* pr = wpart + ((size_t)w * G + gg) * rec;
+      const float wgt = pr[DH] == -INFINITY ? 0.0f : __expf(pr[DH] - mm);
+      num += wgt * pr[dd];
+      den += wgt * pr[DH + 1];
+    }
+    if (nsplit == 1) {
+      a.out[((size_t)b * a.H + hk * G + gg) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
+    } else {
+      gpart[(size_t)gg * rec + dd] = num;
+      if (dd == 0) {
+        gpart[(size_t)gg * rec + DH] = mm;
+        gpart[(size_t)gg * rec + DH + 1] = den;
+      }
+    }
+  }
+  if (nsplit == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&a.counters[b * a.Hk + hk], 1);
+    last_sh = old == nsplit - 1;
+    if (old == nsplit - 1) a.counters[b * a.Hk + hk] = 0;
+  }
+  __syncthreads();
+  if (!last_sh) return;
+  __threadfence();
+  // ---- merge of the splits by the last CTA: the weight of every (split, head) once, in shared
+  // memory, then each thread sums four output dims over the splits with independent 16-byte loads
+  const float* parts = a.part + (((size_t)b * a.Hk + hk) * nsplit) * G * rec;
+  float* wgt_s = wpart;                          // [nsplit][G] weights (<= 64 x 8)
+  float* den_s = wpart + kGqMaxSplit * 8;        // [G]
+  for (int i = tid; i < nsplit * G; i += kAttnThreads) wgt_s[i] = __ldcg(parts + (size_t)i * rec + DH);
+  __syncthreads();
+  if (tid < G) {
+    float mm = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) mm = fmaxf(mm, wgt_s[sp * G + tid]);
+    den_s[8 + tid] = mm;
+  }
+  __syncthreads();
+  for (int i = tid; i < nsplit * G; i += kAttnThreads) {
+    const float ms = wgt_s[i];
+    wgt_s[i] = ms == -INFINITY ? 0.0f : __expf(ms - den_s[8 + i % G]);
+  }
+  __syncthreads();
+  if (tid < G) {
+    float den = 0.0f;
+    for (int sp = 0; sp < nsplit; ++sp) den += wgt_s[sp * G + tid] * __ldcg(parts + ((size_t)sp * G + tid) * rec + DH + 1);
+    den_s[tid] = den;
+  }
+  __syncthreads();
+  for (int i = tid; i < G * (DH / 4); i += kAttnThreads) {
+    const int gg = i / (DH / 4), d4 = (i - gg * (DH / 4)) * 4;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(parts + ((size_t)sp * G + gg) * rec + d4));
+      const float wg = wgt_s[sp * G + gg];
+      num.x += wg * v.x; num.y += wg * v.y; num.z += wg * v.z; num.w += wg * v.w;
+    }
+    const float den = den_s[gg];
+    const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    uint2 o2;
+    o2.x = pack_bf16(num.x * inv, num.y * inv);
+    o2.y = pack_bf16(num.z * inv, num.w * inv);
+    *reinterpret_cast<uint2*>(a.out + ((size_t)b * a.H + hk * G + gg) * DH + d4) = o2;
+  }
+}
+
 // ------------------------------------------------------------------------------- step head / tail
 __global__ void embed_rows_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
                                   __nv_bfloat16* __restrict__ out, int d, int vocab) {
@@ -1353,7 +1604,7 @@ struct Scratch {
 
 // y[B, P] = epilogue(W[P, K] . x[B, K]^T); W2 / x2: the second accumulator of TE_SWIGLU.
 static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, int ldw, const void* x, const void* x2,
-                     int ldx, int B, int epi, const Scratch& sc) {
+                     int ldx, int B, int epi, const Scratch& sc, int force_segs = 0) {
   if (int e = device_limits()) return e;
   memset(&g, 0, sizeof(g));
   const int N = round16(B);
@@ -1372,6 +1623,11 @@ static int plan_gemm(GemmPlan& g, const void* W, const void* W2, int P, int K, i
   int cap = kMaxSegs;
   for (int attempt = 0; attempt < 2; ++attempt) {
     split_k(a.tiles, a.nkb, g_sms, a.segs, a.kbs);
+    if (force_segs > 0) {   // the caller wants this many segments (problems of one grouped launch)
+      const int want = force_segs < a.nkb ? force_segs : a.nkb;
+      a.kbs = (a.nkb + want - 1) / want;
+      a.segs = (a.nkb + a.kbs - 1) / a.kbs;
+    }
     if (a.segs > cap) {   // second attempt: fewer, longer segments
       a.kbs = (a.nkb + cap - 1) / cap;
       a.segs = (a.nkb + a.kbs - 1) / a.kbs;
@@ -1490,6 +1746,14 @@ struct TileWs {
 };
 static int attn_nsplit(const fsvd_dims& D, int sms) {
   if (D.rows_are_positions) return 1;   // prompt pass: row blocks share the cache rows instead
+  if (D.Hk > 0 && D.H / D.Hk >= 4) {
+    // grouped-query kernel: 3 CTAs per SM, at least one block of 32 keys for each of a CTA's 4 warps
+    int ns = (3 * sms + D.B * D.Hk - 1) / (D.B * D.Hk);
+    const int most = (D.S_max + 4 * kGqKeys - 1) / (4 * kGqKeys);
+    if (ns > most) ns = most;
+    if (ns > kGqMaxSplit) ns = kGqMaxSplit;
+    return ns < 1 ? 1 : ns;
+  }
   int ns = (8 * sms + D.B * D.Hk - 1) / (D.B * D.Hk);   // about 8 CTAs of 4 warps per SM
   if (ns > 16) ns = 16;
   if (ns < 1) ns = 1;
@@ -1511,7 +1775,7 @@ static TileWs tile_layout(const fsvd_dims& D, int sms) {
   L.mid = o;       o += al256((size_t)B * D.d * 2);
   L.hact = o;      o += al256((size_t)B * D.I * 2);
   L.nsplit = attn_nsplit(D, sms);
-  L.apart = o;     o += al256((size_t)B * D.Hk * L.nsplit * (D.H / imax(D.Hk, 1)) * (D.Dh + 2) * 4);
+  L.apart = o;     o += al256((size_t)B * D.Hk * L.nsplit * (D.H / imax(D.Hk, 1)) * (D.Dh + 4) * 4);
   L.total = o;
   return L;
 }
@@ -1542,7 +1806,8 @@ struct LayerPlan {
 };
 
 static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, const void* cos_tab, const void* sin_tab,
-                      const int* seqlens, const void* x_in, void* x_out, char* ws, const TileWs& L, long long wait_limit) {
+                      const int* seqlens, const void* x_in, void* x_out, char* ws, const TileWs& L, long long wait_limit,
+                      const void* xn_in = nullptr) {
   const int B = D.B, HD = D.H * D.Dh, KD = D.Hk * D.Dh, Rqkv = D.Rq + D.Rk + D.Rv;
   Scratch sc = {&reinterpret_cast<SyncState*>(ws + L.sync)->status, wait_limit};
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
@@ -1557,7 +1822,8 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   };
   int e;
   // 0: [p_q | p_k | p_v] = rms(x) . qkv_v^T
-  if ((e = plan_gemm(lp.g[0], Lw.qkv_v, nullptr, Rqkv, D.d, D.d, xn, nullptr, D.d, B, TE_STORE, sc))) return e;
+  // xn_in: the caller already holds rms(x) . ln1 (the kernel before this layer wrote it)
+  if ((e = plan_gemm(lp.g[0], Lw.qkv_v, nullptr, Rqkv, D.d, D.d, xn_in ? xn_in : xn, nullptr, D.d, B, TE_STORE, sc))) return e;
   lp.g[0].a.out = pb;
   // 1-3: lifts with rotary / cache append
   if ((e = plan_gemm(lp.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc))) return e;
@@ -1567,6 +1833,26 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   rope(lp.g[2].a, Lw.k_cache);
   if ((e = plan_gemm(lp.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc))) return e;
   rope(lp.g[3].a, Lw.v_cache);
+  if (lp.g[1].a.segs != lp.g[2].a.segs || lp.g[1].a.segs != lp.g[3].a.segs) {
+    // the three lifts go out as one launch when they cut K into the same number of segments: look for
+    // a count (>= 2) that all three can take
+    const int nkb_min = std::min(lp.g[1].a.nkb, std::min(lp.g[2].a.nkb, lp.g[3].a.nkb));
+    auto segs_for = [](int nkb, int want) { const int kbs = (nkb + want - 1) / want; return (nkb + kbs - 1) / kbs; };
+    for (int S = std::min(std::max(lp.g[1].a.segs, std::max(lp.g[2].a.segs, lp.g[3].a.segs)), nkb_min); S >= 2; --S) {
+      if (segs_for(lp.g[1].a.nkb, S) != S || segs_for(lp.g[2].a.nkb, S) != S || segs_for(lp.g[3].a.nkb, S) != S) continue;
+      LayerPlan t = lp;
+      if (plan_gemm(t.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc, S)) break;
+      if (plan_gemm(t.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sc, S)) break;
+      if (plan_gemm(t.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc, S)) break;
+      if (t.g[1].a.segs != S || t.g[2].a.segs != S || t.g[3].a.segs != S) break;
+      t.g[1].a.out = qb;
+      rope(t.g[1].a, nullptr);
+      rope(t.g[2].a, Lw.k_cache);
+      rope(t.g[3].a, Lw.v_cache);
+      for (int i = 1; i < 4; ++i) lp.g[i] = t.g[i];
+      break;
+    }
+  }
   // attention
   AttnArgs& at = lp.at;
   memset(&at, 0, sizeof(at));
@@ -1620,8 +1906,16 @@ static void launch_attn_g(const AttnArgs& at, cudaStream_t st) {
   switch (G) {
     case 1: launch_pdl(batch_attn_kernel<DH, 1, 1>, dim3(grid), dim3(threads), 0, st, at); break;
     case 2: launch_pdl(batch_attn_kernel<DH, 2, 1>, dim3(grid), dim3(threads), 0, st, at); break;
-    case 4: launch_pdl(batch_attn_hs_kernel<DH, 4>, dim3(grid), dim3(threads), 0, st, at); break;
-    default: launch_pdl(batch_attn_hs_kernel<DH, 8>, dim3(grid), dim3(threads), 0, st, at); break;
+    default: {
+      // 4 or 8 heads per kv head: the heads as rows of a tensor-core tile
+      constexpr size_t smem = (size_t)kAttnWarps * 2 * kGqKeys * (DH * 2 + 16);
+      static bool attr_set = false;   // per instantiation; set under the planner's lock or at first use
+      if (!attr_set) {
+        cudaFuncSetAttribute(gqa_decode_attn_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+      }
+      launch_pdl(gqa_decode_attn_kernel<DH>, dim3(grid), dim3(threads), smem, st, at);
+    }
   }
 }
 static int launch_attn(const AttnArgs& at, cudaStream_t st) {
@@ -1635,7 +1929,9 @@ static int launch_attn(const AttnArgs& at, cudaStream_t st) {
 // The last GEMM of a layer (down lift + residual) is planned per call site: its output buffer
 // differs between the per-layer entry point and the model.
 static int launch_reduce(const ReduceArgs& r, int rows, cudaStream_t st) {
-  if (launch_pdl(exchange_reduce_rows_kernel, dim3((unsigned)rows), dim3(256), 0, st, r) != cudaSuccess)
+  // wide rows are cut into four column slices (a cluster of four CTAs per row)
+  const unsigned C = (r.d >= 2048 && r.d % 32 == 0) ? 4u : 1u;
+  if (launch_pdl_cluster(exchange_reduce_rows_kernel, dim3((unsigned)rows, C), dim3(256), 0, C > 1 ? C : 0u, st, r) != cudaSuccess)
     return fail(FSVD_ERR_CUDA, "exchange kernel launch failed");
   fsvd_tile_count_launch();
   return 0;
@@ -1645,13 +1941,15 @@ static int launch_reduce(const ReduceArgs& r, int rows, cudaStream_t st) {
 // rank; r1 replaces the second RMSNorm (sum + residual + norm), r2 finishes the layer output.
 static int run_layer(const LayerPlan& lp, const GemmPlan& down_lift, const fsvd_dims& D, const fsvd_layer& Lw,
                      const void* x_in, char* ws, const TileWs& L, cudaStream_t st, const ReduceArgs* r1 = nullptr,
-                     const ReduceArgs* r2 = nullptr) {
+                     const ReduceArgs* r2 = nullptr, bool have_xn = false) {
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws + L.xn);
   const __nv_bfloat16* mid = reinterpret_cast<const __nv_bfloat16*>(ws + L.mid);
   int e;
-  launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(x_in),
-             reinterpret_cast<const __nv_bfloat16*>(Lw.ln1_w), xn, D.d, D.eps);
-  fsvd_tile_count_launch();
+  if (!have_xn) {
+    launch_pdl(rmsnorm_rows_kernel, dim3(D.B), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(x_in),
+               reinterpret_cast<const __nv_bfloat16*>(Lw.ln1_w), xn, D.d, D.eps);
+    fsvd_tile_count_launch();
+  }
   if ((e = launch_gemm(lp.g[0], st))) return e;
   if (lp.g[1].a.segs == lp.g[2].a.segs && lp.g[1].a.segs == lp.g[3].a.segs) {
     // the q, k and v lifts read the same rank vector and write disjoint outputs: one launch
@@ -1697,9 +1995,9 @@ struct TpPlan {
   ReduceArgs r1, r2;
 };
 static int plan_tp_layer(TpPlan& tp, const fsvd_dims& D, const fsvd_layer& Lw, const void* cos_tab, const void* sin_tab,
-                         const int* seqlens, const void* x_in, void* x_out, const fsvd_exchange& ex, char* ws, const TileWs& L,
-                         long long wait_limit) {
-  if (int e = plan_layer(tp.lp, D, Lw, cos_tab, sin_tab, seqlens, x_in, x_out, ws, L, wait_limit)) return e;
+                         const int* seqlens, const void* x_in, const void* xn_in, void* x_out, const void* next_norm_w,
+                         void* xn_out, const fsvd_exchange& ex, char* ws, const TileWs& L, long long wait_limit) {
+  if (int e = plan_layer(tp.lp, D, Lw, cos_tab, sin_tab, seqlens, x_in, x_out, ws, L, wait_limit, xn_in)) return e;
   if (int e = plan_down_lift(tp.dl, D, Lw, x_out, ws, L, wait_limit)) return e;
   fsvd_exch::Ctrl* ctrl = reinterpret_cast<fsvd_exch::Ctrl*>(ex.geom.region[ex.geom.rank]);
   int* status = &reinterpret_cast<SyncState*>(ws + L.sync)->status;
@@ -1725,7 +2023,7 @@ static int plan_tp_layer(TpPlan& tp, const fsvd_dims& D, const fsvd_layer& Lw, c
     return 0;
   };
   if (int e = to_push(tp.lp.g[5], tp.r1, x_in, ws + L.mid, Lw.ln2_w, ws + L.xn)) return e;
-  return to_push(tp.dl, tp.r2, ws + L.mid, x_out, nullptr, nullptr);
+  return to_push(tp.dl, tp.r2, ws + L.mid, x_out, next_norm_w, next_norm_w ? xn_out : nullptr);
 }
 
 }  // namespace fsvd_tile
@@ -1790,8 +2088,9 @@ int fsvd_tile_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const
 }
 
 int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
-                              const int* cache_seqlens, const void* x_in, void* x_out, fsvd_exchange* ex, void* ws,
-                              size_t ws_bytes, long long wait_limit, void* stream) {
+                              const int* cache_seqlens, const void* x_in, const void* x_norm_in, void* x_out,
+                              const void* next_norm_w, void* x_norm_out, fsvd_exchange* ex, void* ws, size_t ws_bytes,
+                              long long wait_limit, void* stream) {
   const fsvd_dims& D = *dims;
   if (int e = device_limits()) return e;
   if (int e = check_tile_dims(D)) return e;
@@ -1802,10 +2101,13 @@ int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, co
   if (x_in == x_out) return fail(FSVD_ERR_ARG, "x_in and x_out must differ");
   if ((reinterpret_cast<uintptr_t>(x_in) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(layer->ln2_w)) & 15)
     return fail(FSVD_ERR_ALIGN, "x_in, x_out and the norm weights must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x_norm_in) | reinterpret_cast<uintptr_t>(next_norm_w) | reinterpret_cast<uintptr_t>(x_norm_out)) & 15)
+    return fail(FSVD_ERR_ALIGN, "x_norm_in, next_norm_w and x_norm_out must be 16-byte aligned");
+  if (next_norm_w && !x_norm_out) return fail(FSVD_ERR_ARG, "next_norm_w needs x_norm_out");
   struct Cached {
     fsvd_dims D;
     fsvd_layer Lw;
-    const void *cos_tab, *sin_tab, *x_in;
+    const void *cos_tab, *sin_tab, *x_in, *xn_in, *next_w, *xn_out;
     const int* seqlens;
     void *x_out, *ws;
     const fsvd_exchange* ex;
@@ -1819,7 +2121,8 @@ int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, co
   for (Cached* k : cache)
     if (!memcmp(&k->D, &D, sizeof(D)) && !memcmp(&k->Lw, layer, sizeof(*layer)) && k->cos_tab == cos_tab &&
         k->sin_tab == sin_tab && k->x_in == x_in && k->seqlens == cache_seqlens && k->x_out == x_out && k->ws == ws &&
-        k->ex == ex && k->wait_limit == wait_limit)
+        k->ex == ex && k->wait_limit == wait_limit && k->xn_in == x_norm_in && k->next_w == next_norm_w &&
+        k->xn_out == x_norm_out)
       c = k;
   if (!c) {
     if (cache.size() >= 256) {
@@ -1829,14 +2132,16 @@ int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, co
     c = new Cached();
     c->D = D; c->Lw = *layer; c->cos_tab = cos_tab; c->sin_tab = sin_tab; c->x_in = x_in; c->seqlens = cache_seqlens;
     c->x_out = x_out; c->ws = ws; c->ex = ex; c->wait_limit = wait_limit;
-    if (int e = plan_tp_layer(c->tp, D, *layer, cos_tab, sin_tab, cache_seqlens, x_in, x_out, *ex, reinterpret_cast<char*>(ws), L,
-                              wait_limit)) {
+    c->xn_in = x_norm_in; c->next_w = next_norm_w; c->xn_out = x_norm_out;
+    if (int e = plan_tp_layer(c->tp, D, *layer, cos_tab, sin_tab, cache_seqlens, x_in, x_norm_in, x_out, next_norm_w, x_norm_out,
+                              *ex, reinterpret_cast<char*>(ws), L, wait_limit)) {
       delete c;
       return e;
     }
     cache.push_back(c);
   }
-  return run_layer(c->tp.lp, c->tp.dl, D, *layer, x_in, reinterpret_cast<char*>(ws), L, (cudaStream_t)stream, &c->tp.r1, &c->tp.r2);
+  return run_layer(c->tp.lp, c->tp.dl, D, *layer, x_in, reinterpret_cast<char*>(ws), L, (cudaStream_t)stream, &c->tp.r1, &c->tp.r2,
+                   x_norm_in != nullptr);
 }
 
 // ---- whole-model decode for batches above 8: the launches of a step captured once in a CUDA graph

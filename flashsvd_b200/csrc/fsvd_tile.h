@@ -20,8 +20,9 @@ int fsvd_tile_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const
                            const int* cache_seqlens, const void* x_in, void* x_out, void* ws, size_t ws_bytes,
                            long long wait_limit, void* stream);
 int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab, const void* sin_tab,
-                              const int* cache_seqlens, const void* x_in, void* x_out, fsvd_exchange* ex, void* ws,
-                              size_t ws_bytes, long long wait_limit, void* stream);
+                              const int* cache_seqlens, const void* x_in, const void* x_norm_in, void* x_out,
+                              const void* next_norm_w, void* x_norm_out, fsvd_exchange* ex, void* ws, size_t ws_bytes,
+                              long long wait_limit, void* stream);
 int fsvd_tile_model_create(const fsvd_dims* dims, const fsvd_layer* layers, const void* embed, const void* final_norm_w,
                            const void* lm_head, const void* cos_tab, const void* sin_tab, int max_steps, long long wait_limit,
                            fsvd_tile_model** out);

@@ -280,11 +280,14 @@ def make_tp_workspace(dims: FsvdDims, device) -> Workspace:
     return Workspace(torch.zeros(n, dtype=torch.uint8, device=device), n)
 
 
-def tp_decode_layer(dims: FsvdDims, layer: FsvdLayer, cos, sin, cache_seqlens, x_in, x_out, exchange, ws: Workspace):
+def tp_decode_layer(dims: FsvdDims, layer: FsvdLayer, cos, sin, cache_seqlens, x_in, x_out, exchange, ws: Workspace, *,
+                    x_norm_in=None, next_norm_w=None, x_norm_out=None):
     """One decoder layer on this rank's shards; the partial sums of the output projection and of the
     down projection are exchanged with the other ranks inside the kernels (``exchange``: the handle of
-    a ``tensor_parallel.PeerExchange``).  x_out is the full layer output, the same on every rank."""
+    a ``tensor_parallel.PeerExchange``).  x_out is the full layer output, the same on every rank.
+    ``x_norm_in``: ln1-normalised x_in the caller already holds; ``next_norm_w`` / ``x_norm_out``: also
+    write rmsnorm(x_out) * next_norm_w (the next layer's input norm, or the final norm)."""
     check(_lib.load().fsvd_tp_decode_layer(
-        C.byref(dims), C.byref(layer), _ptr(cos), _ptr(sin), _ptr(cache_seqlens), _ptr(x_in), _ptr(x_out),
-        exchange, ws.ptr, ws.nbytes, _stream()))
+        C.byref(dims), C.byref(layer), _ptr(cos), _ptr(sin), _ptr(cache_seqlens), _ptr(x_in), _ptr(x_norm_in),
+        _ptr(x_out), _ptr(next_norm_w), _ptr(x_norm_out), exchange, ws.ptr, ws.nbytes, _stream()))
     return x_out

@@ -191,6 +191,7 @@ class TPDecodeLayer:
         else:
             self.ws = ops.make_tp_workspace(dims, device)
             self.out = torch.empty(batch, d, dtype=dtype, device=device)
+            self.out_norm = torch.empty(batch, d, dtype=dtype, device=device)   # rmsnorm(out) . the next norm weight
             self._struct = ops.make_layer_struct({
                 "ln1_w": self.ln1, "qkv_v": self.qkv_v, "q_u": self.q_u, "k_u": self.k_u, "v_u": self.v_u, "o_v": self.o_v,
                 "o_u": self.o_u, "ln2_w": self.ln2, "upgate_v": self.upgate_v, "gate_u": self.gate_u, "up_u": self.up_u,
@@ -202,12 +203,19 @@ class TPDecodeLayer:
                                                          self.upgate_v, self.gate_u, self.up_u, self.down_v, self.down_u))
         return fac + 2 * batch * ctx * self.Hkl * self.Dh * self.k_cache.element_size()
 
-    def forward(self, x: torch.Tensor, seqlens: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, seqlens: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, x_norm=None,
+                next_norm_w=None) -> torch.Tensor:
+        """Peer exchange only: ``x_norm`` = ln1-normalised x the caller holds (``out_norm`` of the
+        layer before); ``next_norm_w``: also leave rmsnorm(output) * next_norm_w in ``self.out_norm``."""
         B = x.shape[0]
         if self.exchange is not None:
             if B != self.dims.B:
                 raise ValueError(f"the layer was built for {self.dims.B} sequences")
-            return ops.tp_decode_layer(self.dims, self._struct, cos, sin, seqlens, x, self.out, self.exchange.handle, self.ws)
+            return ops.tp_decode_layer(self.dims, self._struct, cos, sin, seqlens, x, self.out, self.exchange.handle, self.ws,
+                                       x_norm_in=x_norm, next_norm_w=next_norm_w,
+                                       x_norm_out=self.out_norm if next_norm_w is not None else None)
+        if x_norm is not None or next_norm_w is not None:
+            raise ValueError("x_norm / next_norm_w belong to the peer-exchange layer")
         first = self.rank == 0
         q = ops.qkv_rope_append(x, self.qkv_v, self.q_u, self.k_u, self.v_u, cos, sin, self.k_cache, self.v_cache,
                                 seqlens, self.ws, num_heads=self.Hl, num_kv_heads=self.Hkl, head_dim=self.Dh,
@@ -244,10 +252,19 @@ class TPModel:
 
     def _step_eager(self) -> None:
         x = torch.index_select(self.embed, 0, self.tokens, out=self._x0)
-        for layer in self.layers:
-            x = layer.forward(x, self.seqlens, self.cos, self.sin)
-        xf = x.float()
-        xn = self.final_norm * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(self.dtype)
+        if self.layers and self.layers[0].exchange is not None:
+            # the kernel that finishes a layer also applies the next layer's input norm (the final
+            # norm after the last layer)
+            xn = None
+            for i, layer in enumerate(self.layers):
+                nxt = self.layers[i + 1].ln1 if i + 1 < len(self.layers) else self.final_norm
+                x = layer.forward(x, self.seqlens, self.cos, self.sin, x_norm=xn, next_norm_w=nxt)
+                xn = layer.out_norm
+        else:
+            for layer in self.layers:
+                x = layer.forward(x, self.seqlens, self.cos, self.sin)
+            xf = x.float()
+            xn = self.final_norm * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(self.dtype)
         ops.lift(xn, self.lm_head, self._head_ws, out=self.logits)
         self.tokens.copy_(self.logits.float().argmax(-1))
         self.seqlens.add_(1)

@@ -306,12 +306,16 @@ int fsvd_exchange_create(int rank, int world, void* const* regions, int max_rows
                          fsvd_exchange** out);
 int fsvd_exchange_destroy(fsvd_exchange* ex);
 /* One decoder layer on this rank's shards (bf16, 1 <= B <= max_rows rows, tiled tensor-core path
- * at every batch size): x_out = the full layer output, identical on every rank.  The workspace is
- * fsvd_workspace_bytes of the rank's dims with B >= 9 semantics (ask with the same dims).  The
- * appended key / value rows are the rank's own heads. */
+ * at every batch size): x_out = the full layer output, identical on every rank.  The workspace has
+ * fsvd_tp_workspace_bytes(dims) bytes, zeroed once.  The appended key / value rows are the rank's
+ * own heads.  Optional, to save the RMSNorm launches between layers: x_norm_in (non-NULL) = the
+ * caller already holds ln1-normalised x_in [B, d] (written by the layer before); next_norm_w
+ * (non-NULL) = also write rmsnorm(x_out) * next_norm_w to x_norm_out [B, d] (the next layer's ln1,
+ * or the model's final norm). */
 size_t fsvd_tp_workspace_bytes(const fsvd_dims* dims);
 int fsvd_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, const void* cos_tab,
-                         const void* sin_tab, const int* cache_seqlens, const void* x_in, void* x_out,
+                         const void* sin_tab, const int* cache_seqlens, const void* x_in,
+                         const void* x_norm_in, void* x_out, const void* next_norm_w, void* x_norm_out,
                          fsvd_exchange* ex, void* ws, size_t ws_bytes, void* stream);
 
 /* Kernel launches enqueued by this library since load (for launch accounting). */

@@ -66,6 +66,22 @@ def test_decode_layer_tiles_match_oracle(dev, shape, B, ctx):
     assert rel_linf(out, ref) <= TOL
 
 
+GQA8_DH128 = O.Shape(d=512, H=8, Hk=1, Dh=128, I=512, Rq=96, Rk=32, Rv=32, Ro=96, Rg=96, Ru=96, Rd=96, vocab=300, n_layers=2)
+GQA4_DH128 = O.Shape(d=512, H=8, Hk=2, Dh=128, I=512, Rq=96, Rk=64, Rv=64, Ro=96, Rg=96, Ru=96, Rd=96, vocab=300, n_layers=2)
+
+
+@pytest.mark.parametrize("shape,B,ctx", [(GQA8_DH128, 9, 700), (GQA4_DH128, 10, 391), (O.TINY_GQA, 12, 333),
+                                         (GQA8_DH128, 5, 31)])
+def test_decode_layer_tiles_grouped_query_heads_long_context(dev, shape, B, ctx):
+    """4 and 8 query heads per kv head (the tensor-core decode attention): several key splits per
+    sequence, several 32-key blocks per warp, ragged lengths, a last block that is not full."""
+    out, ref, pk, kc_o, vc_o = _layer_case(dev, shape, B, ctx, S_max=ctx + 12)
+    err = rel_linf(out, ref)
+    print(f"H/Hk={shape.H // shape.Hk} Dh={shape.Dh} B={B} ctx={ctx}: rel_linf {err:.3e}")
+    assert err <= 2e-2
+    assert rel_linf(pk["k_cache"], kc_o) <= 2e-2 and rel_linf(pk["v_cache"], vc_o) <= 2e-2
+
+
 def test_decode_layer_tiles_ragged_ranks(dev):
     # sizes that are multiples of 8 but of nothing larger: ragged last k-blocks and row tiles
     shape = O.Shape(d=264, H=4, Hk=2, Dh=64, I=520, Rq=88, Rk=40, Rv=56, Ro=72, Rg=104, Ru=104, Rd=80,

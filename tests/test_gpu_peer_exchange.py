@@ -146,3 +146,38 @@ def test_a_peer_that_never_posts_ends_in_an_error_status():
     finally:
         ops.set_wait_limit(4_000_000_000)
         ex.close()
+
+
+def test_norms_of_the_neighbouring_layers_fused_into_the_exchange():
+    """x_norm (input already normalised by the layer before) and next_norm_w (the finishing kernel
+    also writes the next layer's normalised input) against the plain call."""
+    from flashsvd_b200 import tensor_parallel as TP
+
+    shape, B, ctx, world = O.TINY_GQA, 6, 25, 1
+    S_max = ctx + 4
+    w, x, kc, vc, seqlens, cos, sin = _case(shape, B, ctx, S_max, seed=21)
+    sh = TP.shard_layer_weights(w, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=0, world=world)
+    sh["ln1"] = (1.0 + 0.1 * torch.randn(shape.d)).to(torch.bfloat16)
+    lay = TP.region_layout(world, B, shape.d)
+    buf = torch.zeros(lay["total"], dtype=torch.uint8, device=DEV)
+    ex = TP.PeerExchange(rank=0, world=world, max_rows=B, d=shape.d, regions=[buf.data_ptr()])
+    layer = TP.TPDecodeLayer(sh, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=0, world=world, batch=B, S_max=S_max,
+                             eps=shape.eps, device=DEV, exchange=ex)
+    layer.k_cache.copy_(kc)
+    layer.v_cache.copy_(vc)
+    xd, sl, cd, sd = x.to(DEV), seqlens.to(DEV), cos.to(DEV), sin.to(DEV)
+    y_plain = layer.forward(xd, sl, cd, sd).clone()
+    nw = (1.0 + 0.1 * torch.randn(shape.d)).to(torch.bfloat16).to(DEV)
+    xn = O.rmsnorm(x, sh["ln1"], shape.eps).to(DEV)
+    y = layer.forward(xd, sl, cd, sd, x_norm=xn, next_norm_w=nw)
+    torch.cuda.synchronize()
+    assert layer.ws.status() == 0
+    assert rel(y, y_plain) <= 4e-3          # the CPU norm and the kernel's may round a value differently
+    want = O.rmsnorm(y.cpu(), nw.cpu(), shape.eps)
+    assert rel(layer.out_norm, want) <= 1e-2
+    ex.close()
+
+
+def rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / b.abs().max())
