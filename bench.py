@@ -297,7 +297,8 @@ def run_tensor_parallel(args, dev, rank, world, local):
     layers = shape.n_layers if args.layers is None else int(args.layers)
     B, ctx0, warm = int(args.batch), int(args.ctx), max(3, args.warmup)
     model = TP.random_tp_model(shape, rank=rank, world=world, device=dev, batch=B, ctx=ctx0,
-                               max_new=warm + args.steps + 8, seed=0, n_layers=layers, exchange=args.tp_exchange)
+                               max_new=warm + args.steps + 8, seed=0, n_layers=layers, exchange=args.tp_exchange,
+                               shard_of=args.tp_shard_of)
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -338,7 +339,9 @@ def run_tensor_parallel(args, dev, rank, world, local):
             "config": {"workload": workload_string(args.shape, layers, B, ctx0, False, "bf16").replace(" per GPU", " in all") +
                        f", ONE model tensor-parallel over {world} GPUs (heads and FFN intermediate sharded, "
                        f"{how}, step replayed as a CUDA graph)",
-                       "exchange": args.tp_exchange, "device_status": status},
+                       "exchange": args.tp_exchange, "device_status": status,
+                       **({"shard_of": args.tp_shard_of, "note": "one rank's share of a larger partition, timed without "
+                           "its peers: not a throughput of the model"} if args.tp_shard_of else {})},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}, per GPU", "bytes_per_launch": per_gpu,
                          "note": "bytes one GPU reads per step: its factor shards + the replicated factors + its K/V rows + lm_head"},
@@ -363,6 +366,8 @@ SECONDARY = (
     ("shared_bases_b1_ctx2048", "7b", 32, 1, 2048, True, "bf16"),
     ("shared_bases_b8_ctx2048", "7b", 32, 8, 2048, True, "bf16"),
     ("70b_shape_replica_b1_ctx512", "70b", 80, 1, 512, False, "bf16"),
+    # configuration 4 on ONE GPU (tiled path, tensor-core grouped-query attention); over 8 GPUs: --tp under torchrun
+    ("70b_shape_one_gpu_b8_ctx4096", "70b", 80, 8, 4096, False, "bf16"),
     # batches above 8 run as tiled tcgen05 GEMMs + batched attention, one CUDA graph launch per step
     ("tiles_b16_ctx512", "7b", 32, 16, 512, False, "bf16"),
     ("tiles_shared_bases_b32_ctx2048", "7b", 32, 32, 2048, True, "bf16"),
@@ -398,6 +403,9 @@ def main():
     ap.add_argument("--tp-exchange", default="peer", choices=("peer", "nccl"),
                     help="--tp: partial sums exchanged inside the kernels over peer memory (peer) or with an NCCL "
                          "all-reduce between per-op launches (nccl, the baseline)")
+    ap.add_argument("--tp-shard-of", type=int, default=None,
+                    help="--tp on fewer GPUs than the partition (profiling): the weights are rank 0's share of a "
+                         "partition over this many ranks, the exchange has the ranks that run")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

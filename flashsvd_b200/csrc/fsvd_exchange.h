@@ -13,7 +13,7 @@
 // Exchange number k (k = 1, 2, ...; parity k & 1): the GEMM that produces a rank's partial sums
 // stores every finished tile into slot [k & 1][rank] of EVERY rank's region (plain stores, its own
 // region included), and each of its CTAs then publishes flag [k & 1][rank][cta] = k in every region
-// (fence + release store).  The reducing kernel of a rank polls the flags of its OWN region until all
+// (a CTA barrier, then a store with release semantics at system scope).  The reducing kernel of a rank polls the flags of its OWN region until all
 // `world` sources have posted k, adds the world slots in rank order (so every rank computes the same
 // bits) plus the residual, and the last of its CTAs advances the rank's sequence number.
 // Two parities suffice: a rank can push exchange k + 2 only after it has reduced k + 1, which needs

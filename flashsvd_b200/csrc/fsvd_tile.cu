@@ -505,9 +505,9 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   tc_fence_before();
   __syncthreads();
   // TE_PUSH: every store of this CTA is ordered before the flags that thread q raises in rank q's
-  // region (the CTA barrier above, then a system-wide fence and a release store)
+  // region: the CTA barrier above, then a store with release semantics at system scope (it orders the
+  // writes the thread has observed through the barrier as well as its own)
   if (a.epi == TE_PUSH && tid < a.ex.world) {
-    __threadfence_system();
     fsvd_exch::st_release_sys(fsvd_exch::flag_ptr(a.ex, tid, push_seq & 1u, a.ex.rank, tile * a.segs + seg), push_seq);
   }
   __syncwarp();
@@ -884,176 +884,6 @@ __global__ void __launch_bounds__(kAttnThreads) batch_attn_kernel(const AttnArgs
   }
 }
 
-// Grouped-query variant for 4 or 8 query heads per kv head: with all of them in every warp the
-// kernel needs ~240 registers and two CTAs per SM cannot hide the row loads (measured 0.74 TB/s on the
-// 70B shape).  Here a warp owns G / 4 of the heads and walks ALL keys of the CTA's split; the four
-// warps read the same rows within a short time, so three of the four reads hit L1.
-// A lane's piece of a cache row as raw bits, requested here and now (a volatile asm is not moved to
-// its use, which is what keeps 16 rows per lane in flight), unpacked when it is used.
-template <int DPL>
-struct RawPiece;
-template <>
-struct RawPiece<4> {
-  uint32_t x, y;
-  __device__ __forceinline__ void load(const __nv_bfloat16* row, int lane) {
-    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "l"(reinterpret_cast<const uint2*>(row) + lane));
-  }
-  __device__ __forceinline__ void unpack(float (&f)[4]) const {
-    f[0] = __uint_as_float(x << 16); f[1] = __uint_as_float(x & 0xffff0000u);
-    f[2] = __uint_as_float(y << 16); f[3] = __uint_as_float(y & 0xffff0000u);
-  }
-};
-template <>
-struct RawPiece<2> {
-  uint32_t x;
-  __device__ __forceinline__ void load(const __nv_bfloat16* row, int lane) {
-    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(x) : "l"(reinterpret_cast<const uint32_t*>(row) + lane));
-  }
-  __device__ __forceinline__ void unpack(float (&f)[2]) const {
-    f[0] = __uint_as_float(x << 16); f[1] = __uint_as_float(x & 0xffff0000u);
-  }
-};
-
-template <int DH, int G>
-__global__ void __launch_bounds__(kAttnThreads) batch_attn_hs_kernel(const AttnArgs a) {
-  constexpr int DPL = DH / 32;
-  constexpr int NGW = G / kAttnWarps;            // heads per warp
-  __shared__ float wm[G], wl[G];
-  __shared__ float wacc[G][DH];
-  __shared__ int last_sh;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  pdl_launch_dependents();
-  pdl_wait();
-  int idx = blockIdx.x;
-  const int split = idx % a.nsplit;
-  idx /= a.nsplit;
-  const int hk = idx % a.Hk, b = idx / a.Hk;
-  const int n = min(a.seqlens[b] + a.seqlen_add, a.S_max);
-  const int per = (n + a.nsplit - 1) / a.nsplit;
-  const int j0 = min(n, split * per), j1 = min(n, j0 + per);
-  const size_t rowstride = (size_t)a.Hk * DH;
-  const size_t cbase = ((size_t)(a.shared_cache ? 0 : b) * a.S_max) * rowstride + (size_t)hk * DH;
-  const __nv_bfloat16* kbase = a.kcache + cbase;
-  const __nv_bfloat16* vbase = a.vcache + cbase;
-
-  float q[NGW][DPL], acc[NGW][DPL], m[NGW], l[NGW];
-#pragma unroll
-  for (int g = 0; g < NGW; ++g) {
-    ld_row<DPL>(a.q + ((size_t)b * a.H + hk * G + warp * NGW + g) * DH, lane, q[g]);
-#pragma unroll
-    for (int e = 0; e < DPL; ++e) {
-      q[g][e] *= a.scale;
-      acc[g][e] = 0.0f;
-    }
-    m[g] = -INFINITY;
-    l[g] = 0.0f;
-  }
-  for (int c0 = j0; c0 < j1; c0 += kKeyGroup) {
-    const int cn = min(kKeyGroup, j1 - c0);
-    RawPiece<DPL> kr[kKeyGroup], vr[kKeyGroup];
-#pragma unroll
-    for (int i = 0; i < kKeyGroup; ++i) {
-      const int row = c0 + (i < cn ? i : cn - 1);
-      kr[i].load(kbase + (size_t)row * rowstride, lane);
-      vr[i].load(vbase + (size_t)row * rowstride, lane);
-    }
-    float kf[kKeyGroup][DPL], vf[kKeyGroup][DPL];
-#pragma unroll
-    for (int i = 0; i < kKeyGroup; ++i) {
-      kr[i].unpack(kf[i]);
-      vr[i].unpack(vf[i]);
-    }
-#pragma unroll
-    for (int g = 0; g < NGW; ++g) {
-      float s[kKeyGroup];
-#pragma unroll
-      for (int i = 0; i < kKeyGroup; ++i) {
-        float d = 0.0f;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) d += kf[i][e] * q[g][e];
-        s[i] = d;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int i = 0; i < kKeyGroup; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], o);
-      }
-      float cm = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < kKeyGroup; ++i) {
-        if (i >= cn) s[i] = -INFINITY;
-        cm = fmaxf(cm, s[i]);
-      }
-      const float mn = fmaxf(m[g], cm);
-      const float corr = __expf(m[g] - mn);
-      m[g] = mn;
-      float ps = 0.0f;
-#pragma unroll
-      for (int e = 0; e < DPL; ++e) acc[g][e] *= corr;
-#pragma unroll
-      for (int i = 0; i < kKeyGroup; ++i) {
-        const float pr = __expf(s[i] - mn);
-        ps += pr;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) acc[g][e] += pr * vf[i][e];
-      }
-      l[g] = l[g] * corr + ps;
-    }
-  }
-#pragma unroll
-  for (int g = 0; g < NGW; ++g) {
-    const int gg = warp * NGW + g;
-    if (lane == 0) {
-      wm[gg] = m[g];
-      wl[gg] = l[g];
-    }
-#pragma unroll
-    for (int e = 0; e < DPL; ++e) wacc[gg][lane * DPL + e] = acc[g][e];
-  }
-  __syncthreads();
-  const int nsplit = a.nsplit;
-  const int rec = DH + 2;
-  float* mine = a.part + ((((size_t)b * a.Hk + hk) * nsplit + split) * G) * rec;
-  for (int i = tid; i < G * DH; i += kAttnThreads) {
-    const int g = i / DH, dd = i - g * DH;
-    if (nsplit == 1) {
-      a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(wl[g] > 0.0f ? wacc[g][dd] / wl[g] : 0.0f);
-    } else {
-      mine[(size_t)g * rec + dd] = wacc[g][dd];
-      if (dd == 0) {
-        mine[(size_t)g * rec + DH] = wm[g];
-        mine[(size_t)g * rec + DH + 1] = wl[g];
-      }
-    }
-  }
-  if (nsplit == 1) return;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&a.counters[b * a.Hk + hk], 1);
-    last_sh = old == nsplit - 1;
-    if (old == nsplit - 1) a.counters[b * a.Hk + hk] = 0;
-  }
-  __syncthreads();
-  if (!last_sh) return;
-  __threadfence();
-  const float* parts = a.part + (((size_t)b * a.Hk + hk) * nsplit) * G * rec;
-  for (int i = tid; i < G * DH; i += kAttnThreads) {
-    const int g = i / DH, dd = i - g * DH;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) mm = fmaxf(mm, __ldcg(parts + ((size_t)sp * G + g) * rec + DH));
-    float num = 0.0f, den = 0.0f;
-    for (int sp = 0; sp < nsplit; ++sp) {
-      const float* pr = parts + ((size_t)sp * G + g) * rec;
-      const float ms = __ldcg(pr + DH);
-      const float wgt = ms == -INFINITY ? 0.0f : __expf(ms - mm);
-      num += wgt * __ldcg(pr + dd);
-      den += wgt * __ldcg(pr + DH + 1);
-    }
-    a.out[((size_t)b * a.H + hk * G + g) * DH + dd] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
-  }
-}
-
 // ------------------------------------------------------------------------------- prompt-pass attention
 // Causal attention of a block of consecutive prompt rows over the one sequence's cache, on the
 // tensor cores (mma.sync m16n8k16 / bf16, fp32 accumulation): the rows of a pass share the cache
@@ -1231,8 +1061,8 @@ __global__ void __launch_bounds__(kPfWarps * 32) prompt_attn_kernel(const AttnAr
 // Single-query attention for H / Hk = 4 or 8 query heads per kv head on the tensor cores: the G
 // heads that share a kv head are the rows of one m16n8k16 tile (rows G .. 15 are zero), so a key /
 // value row is read once per sequence and multiplied for all its heads at once, instead of one
-// shuffle-reduced dot product per head and key (batch_attn_hs_kernel).  One CTA = (sequence, kv head,
-// key split) as there; each of its 4 warps walks its own blocks of 32 keys: cp.async of the 32 key
+// shuffle-reduced dot product per head and key (which ran at 0.9 TB/s for 8 heads per kv head).
+// One CTA = (sequence, kv head, key split) as in batch_attn_kernel; each of its 4 warps walks its own blocks of 32 keys: cp.async of the 32 key
 // rows and 32 value rows into the warp's own shared-memory stage, S = Q K^T, running softmax,
 // O += P V with ldmatrix.trans value fragments (the fragment code of prompt_attn_kernel).  The warps
 // merge in shared memory, the splits of a head in split order by the CTA that arrives last.

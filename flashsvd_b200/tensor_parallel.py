@@ -317,15 +317,20 @@ class TPModel:
 
 
 def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: int, max_new: int, seed: int = 0,
-                    dtype=torch.bfloat16, n_layers=None, use_graph: bool = True, exchange: str = "peer") -> TPModel:
+                    dtype=torch.bfloat16, n_layers=None, use_graph: bool = True, exchange: str = "peer",
+                    shard_of: int | None = None) -> TPModel:
     """Seeded random model of ``shape`` (a synthetic.ModelShape), every rank drawing the same full
     factors on its device and keeping its shards; caches pre-filled with ``ctx`` N(0,1) rows.
-    ``exchange``: "peer" (partial sums exchanged inside the kernels) or "nccl" (all-reduce)."""
+    ``exchange``: "peer" (partial sums exchanged inside the kernels) or "nccl" (all-reduce).
+    ``shard_of`` (profiling on one GPU): the weights are rank 0's share of a partition over
+    ``shard_of`` ranks while the exchange has the ``world`` ranks that really run, so the kernels of
+    one rank of a larger job can be timed without its peers (the outputs are then partial sums only)."""
     import math
 
     if exchange not in ("peer", "nccl"):
         raise ValueError("exchange must be 'peer' or 'nccl'")
     ex = PeerExchange(rank=rank, world=world, max_rows=batch, d=shape.d) if exchange == "peer" else None
+    part_rank, part_world = (0, int(shard_of)) if shard_of else (rank, world)
 
     L = shape.n_layers if n_layers is None else int(n_layers)
     d, HD, KD, I = shape.d, shape.H * shape.Dh, shape.Hk * shape.Dh, shape.I
@@ -343,9 +348,9 @@ def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: in
                 "gate_v": w(shape.Rg, d), "gate_u": w(I, shape.Rg), "up_v": w(shape.Ru, d), "up_u": w(I, shape.Ru),
                 "down_v": w(shape.Rd, I), "down_u": w(d, shape.Rd),
                 "ln1": torch.ones(d, device=device, dtype=dtype), "ln2": torch.ones(d, device=device, dtype=dtype)}
-        sh = shard_layer_weights(full, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=rank, world=world)
-        layer = TPDecodeLayer(sh, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=rank, world=world, batch=batch, S_max=S_max,
-                              eps=shape.eps, device=device, dtype=dtype, exchange=ex)
+        sh = shard_layer_weights(full, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=part_rank, world=part_world)
+        layer = TPDecodeLayer(sh, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=part_rank, world=part_world, batch=batch,
+                              S_max=S_max, eps=shape.eps, device=device, dtype=dtype, exchange=ex)
         if ctx > 0:
             g2 = torch.Generator(device=device).manual_seed(seed * 100003 + 7919 + li * world + rank)
             layer.k_cache[:, :ctx].copy_(torch.randn(layer.k_cache[:, :ctx].shape, device=device, generator=g2).to(dtype))
