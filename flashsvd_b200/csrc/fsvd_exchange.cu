@@ -5,6 +5,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "../../include/flashsvd_b200.h"
 #include "fsvd_exchange.h"
 #include "fsvd_tile.h"
@@ -98,6 +100,8 @@ int fsvd_exchange_create(int rank, int world, void* const* regions, int max_rows
   g.rank = rank;
   ex->max_rows = max_rows;
   ex->d = d;
+  static std::atomic<unsigned long long> next_id{1};
+  ex->id = next_id.fetch_add(1);
   // the first exchange has number 1 (the flags of a fresh region read 0)
   Ctrl c = {1u, 0u};
   const cudaError_t e = cudaMemcpyAsync(regions[rank], &c, sizeof(c), cudaMemcpyHostToDevice, (cudaStream_t)stream);

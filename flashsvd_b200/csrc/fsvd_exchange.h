@@ -76,4 +76,5 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 struct fsvd_exchange {
   fsvd_exch::Geom geom;
   int max_rows, d;
+  unsigned long long id;   // unique per created object: cached launch plans are keyed on it, not on the address alone
 };

@@ -1941,6 +1941,7 @@ int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, co
     const int* seqlens;
     void *x_out, *ws;
     const fsvd_exchange* ex;
+    unsigned long long ex_id;
     long long wait_limit;
     TpPlan tp;
   };
@@ -1951,7 +1952,7 @@ int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, co
   for (Cached* k : cache)
     if (!memcmp(&k->D, &D, sizeof(D)) && !memcmp(&k->Lw, layer, sizeof(*layer)) && k->cos_tab == cos_tab &&
         k->sin_tab == sin_tab && k->x_in == x_in && k->seqlens == cache_seqlens && k->x_out == x_out && k->ws == ws &&
-        k->ex == ex && k->wait_limit == wait_limit && k->xn_in == x_norm_in && k->next_w == next_norm_w &&
+        k->ex == ex && k->ex_id == ex->id && k->wait_limit == wait_limit && k->xn_in == x_norm_in && k->next_w == next_norm_w &&
         k->xn_out == x_norm_out)
       c = k;
   if (!c) {
@@ -1961,7 +1962,7 @@ int fsvd_tile_tp_decode_layer(const fsvd_dims* dims, const fsvd_layer* layer, co
     }
     c = new Cached();
     c->D = D; c->Lw = *layer; c->cos_tab = cos_tab; c->sin_tab = sin_tab; c->x_in = x_in; c->seqlens = cache_seqlens;
-    c->x_out = x_out; c->ws = ws; c->ex = ex; c->wait_limit = wait_limit;
+    c->x_out = x_out; c->ws = ws; c->ex = ex; c->ex_id = ex->id; c->wait_limit = wait_limit;
     c->xn_in = x_norm_in; c->next_w = next_norm_w; c->xn_out = x_norm_out;
     if (int e = plan_tp_layer(c->tp, D, *layer, cos_tab, sin_tab, cache_seqlens, x_in, x_norm_in, x_out, next_norm_w, x_norm_out,
                               *ex, reinterpret_cast<char*>(ws), L, wait_limit)) {
