@@ -298,7 +298,7 @@ def run_tensor_parallel(args, dev, rank, world, local):
     B, ctx0, warm = int(args.batch), int(args.ctx), max(3, args.warmup)
     model = TP.random_tp_model(shape, rank=rank, world=world, device=dev, batch=B, ctx=ctx0,
                                max_new=warm + args.steps + 8, seed=0, n_layers=layers, exchange=args.tp_exchange,
-                               shard_of=args.tp_shard_of)
+                               shard_of=args.tp_shard_of, trace=args.tp_trace)
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -323,6 +323,7 @@ def run_tensor_parallel(args, dev, rank, world, local):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0])
     status = model.status()
+    xtrace = model.exchange.trace_summary() if (args.tp_trace and model.exchange is not None) else None
     how = ("partial sums of the o_proj and down projection pushed to every rank's memory by the GEMM epilogue "
            "(peer stores over NVLink) and summed by the next kernel, no collective call"
            if args.tp_exchange == "peer" else
@@ -347,6 +348,8 @@ def run_tensor_parallel(args, dev, rank, world, local):
                          "note": "bytes one GPU reads per step: its factor shards + the replicated factors + its K/V rows + lm_head"},
             "clocks": clocks,
         }
+        if xtrace:
+            line["exchange_trace_rank0"] = xtrace
         print(json.dumps(line), flush=True)
     model.close()
 
@@ -403,6 +406,9 @@ def main():
     ap.add_argument("--tp-exchange", default="peer", choices=("peer", "nccl"),
                     help="--tp: partial sums exchanged inside the kernels over peer memory (peer) or with an NCCL "
                          "all-reduce between per-op launches (nccl, the baseline)")
+    ap.add_argument("--tp-trace", action="store_true",
+                    help="--tp with the peer exchange: time every reduction on the device (%%globaltimer) and add "
+                         "the wait for the peers and the reduction time of rank 0 to the line")
     ap.add_argument("--tp-shard-of", type=int, default=None,
                     help="--tp on fewer GPUs than the partition (profiling): the weights are rank 0's share of a "
                          "partition over this many ranks, the exchange has the ranks that run")

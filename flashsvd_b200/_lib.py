@@ -27,7 +27,8 @@ EXPORTS = (
     "fsvd_selftest_wait_timeout", "fsvd_static_status", "fsvd_model_num_barriers",
     "fsvd_exchange_region_bytes", "fsvd_exchange_region_alloc", "fsvd_exchange_region_free",
     "fsvd_exchange_region_export", "fsvd_exchange_region_import", "fsvd_exchange_region_release",
-    "fsvd_exchange_create", "fsvd_exchange_destroy", "fsvd_tp_workspace_bytes", "fsvd_tp_decode_layer",
+    "fsvd_exchange_create", "fsvd_exchange_destroy", "fsvd_exchange_set_trace", "fsvd_tp_workspace_bytes",
+    "fsvd_tp_decode_layer",
 )
 
 
@@ -121,6 +122,7 @@ def load() -> C.CDLL:
     lib.fsvd_exchange_region_release.argtypes = [vp]
     lib.fsvd_exchange_create.argtypes = [ip, ip, C.POINTER(vp), ip, ip, vp, C.POINTER(vp)]
     lib.fsvd_exchange_destroy.argtypes = [vp]
+    lib.fsvd_exchange_set_trace.argtypes = [vp, vp, sz]
     lib.fsvd_tp_workspace_bytes.argtypes = [C.POINTER(FsvdDims)]
     lib.fsvd_tp_workspace_bytes.restype = sz
     lib.fsvd_tp_decode_layer.argtypes = [

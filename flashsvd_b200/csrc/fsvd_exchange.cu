@@ -114,6 +114,17 @@ int fsvd_exchange_create(int rank, int world, void* const* regions, int max_rows
   return 0;
 }
 
+int fsvd_exchange_set_trace(fsvd_exchange* ex, void* dev_ptr, size_t bytes) {
+  if (!ex) return fail(FSVD_ERR_ARG, "null argument");
+  if (dev_ptr && ((reinterpret_cast<uintptr_t>(dev_ptr) & 7) || bytes < 24)) return fail(FSVD_ERR_ARG, "trace buffer: 8-byte aligned, at least 24 bytes");
+  ex->trace = reinterpret_cast<unsigned long long*>(dev_ptr);
+  ex->trace_cap = dev_ptr ? (unsigned)(bytes / 24 > 0xffffffffull ? 0xffffffffull : bytes / 24) : 0u;
+  // plans made so far do not know the buffer: a new id, so that none of them matches any more
+  static std::atomic<unsigned long long> next_id{1ull << 40};
+  ex->id = next_id.fetch_add(1);
+  return 0;
+}
+
 int fsvd_exchange_destroy(fsvd_exchange* ex) {
   delete ex;
   return 0;

@@ -77,4 +77,6 @@ struct fsvd_exchange {
   fsvd_exch::Geom geom;
   int max_rows, d;
   unsigned long long id;   // unique per created object: cached launch plans are keyed on it, not on the address alone
+  unsigned long long* trace;   // optional device buffer of trace_cap records of 3 x %globaltimer (fsvd_exchange_set_trace)
+  unsigned trace_cap;
 };

@@ -566,7 +566,15 @@ struct ReduceArgs {
   float eps;
   int* status;                   // SyncState::status, status_detail of the workspace
   long long wait_limit;
+  unsigned long long* trace;     // optional: record [seq % trace_cap] = %globaltimer at {dependency met, all flags seen, done}
+  unsigned trace_cap;            // (written by CTA (0, 0))
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, float v) {
   uint32_t remote;
@@ -587,6 +595,8 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
   volatile int* giveup = &giveup_sh;
   const unsigned seq = *reinterpret_cast<const volatile unsigned*>(&a.ctrl->seq);
   const unsigned par = seq & 1u;
+  unsigned long long* rec = (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) ? a.trace + (size_t)(seq % a.trace_cap) * 3 : nullptr;
+  if (rec) rec[0] = global_ns();
   {
     const int total = a.ex.world * a.nflags;
     const long long c0 = clock64();
@@ -607,6 +617,7 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
     }
   }
   __syncthreads();
+  if (rec) rec[1] = global_ns();
   if (C > 1 && a.xn) cluster_sync();            // every CTA of the row runs before any writes into its shared memory
 
   const int cols = a.d / C, col0 = c * cols;    // the host makes cols a multiple of 8
@@ -673,6 +684,7 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
   }
   // every CTA has read the sequence number before it arrives here: the last one moves it on
   __syncthreads();
+  if (rec) rec[2] = global_ns();
   if (tid == 0) {
     __threadfence();
     if (atomicAdd(&a.ctrl->done, 1u) == gridDim.x * gridDim.y - 1) {
@@ -1850,6 +1862,8 @@ static int plan_tp_layer(TpPlan& tp, const fsvd_dims& D, const fsvd_layer& Lw, c
     r.eps = D.eps;
     r.status = status;
     r.wait_limit = wait_limit;
+    r.trace = ex.trace_cap ? ex.trace : nullptr;
+    r.trace_cap = ex.trace_cap;
     return 0;
   };
   if (int e = to_push(tp.lp.g[5], tp.r1, x_in, ws + L.mid, Lw.ln2_w, ws + L.xn)) return e;

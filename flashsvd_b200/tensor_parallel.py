@@ -106,7 +106,7 @@ class PeerExchange:
         self.nbytes = int(lib.fsvd_exchange_region_bytes(self.world, int(max_rows), int(d)))
         if self.nbytes == 0:
             raise ValueError(f"exchange of {world} ranks, {max_rows} rows, width {d}: at most 8 ranks, 128 rows")
-        self._own, self._imported, self.handle = None, [], None
+        self._own, self._imported, self.handle, self._trace = None, [], None, None
         if regions is None:
             p = C.c_void_p()
             check(lib.fsvd_exchange_region_alloc(self.nbytes, C.byref(p)))
@@ -131,6 +131,26 @@ class PeerExchange:
         check(lib.fsvd_exchange_create(self.rank, self.world, arr, int(max_rows), int(d),
                                        torch.cuda.current_stream().cuda_stream, C.byref(h)))
         self.handle = h
+
+    def start_trace(self, records: int = 4096) -> None:
+        """Record the timing of every reduction from now on (before the first layer call to be traced;
+        launches already captured into a CUDA graph keep their setting)."""
+        self._trace = torch.zeros(int(records), 3, dtype=torch.int64, device=torch.cuda.current_device())
+        check(_lib.load().fsvd_exchange_set_trace(self.handle, self._trace.data_ptr(), self._trace.numel() * 8))
+
+    def trace_summary(self) -> dict:
+        """Of the traced reductions: microseconds between the rank's own GEMM finishing and all ranks'
+        flags being seen (``wait``: peers' lateness + the transfer), and of the reduction itself."""
+        if self._trace is None:
+            return {"exchanges": 0}
+        t = self._trace.cpu()
+        t = t[(t > 0).all(dim=1)]
+        if t.numel() == 0:
+            return {"exchanges": 0}
+        wait, red = (t[:, 1] - t[:, 0]).double() / 1e3, (t[:, 2] - t[:, 1]).double() / 1e3
+        q = lambda v, p: float(torch.quantile(v, p))
+        return {"exchanges": int(t.shape[0]), "wait_us_median": q(wait, 0.5), "wait_us_p90": q(wait, 0.9),
+                "wait_us_max": float(wait.max()), "reduce_us_median": q(red, 0.5)}
 
     def close(self) -> None:
         """Collective when the regions were exchanged over a group: no rank unmaps while another may
@@ -318,7 +338,7 @@ class TPModel:
 
 def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: int, max_new: int, seed: int = 0,
                     dtype=torch.bfloat16, n_layers=None, use_graph: bool = True, exchange: str = "peer",
-                    shard_of: int | None = None) -> TPModel:
+                    shard_of: int | None = None, trace: bool = False) -> TPModel:
     """Seeded random model of ``shape`` (a synthetic.ModelShape), every rank drawing the same full
     factors on its device and keeping its shards; caches pre-filled with ``ctx`` N(0,1) rows.
     ``exchange``: "peer" (partial sums exchanged inside the kernels) or "nccl" (all-reduce).
@@ -330,6 +350,8 @@ def random_tp_model(shape, *, rank: int, world: int, device, batch: int, ctx: in
     if exchange not in ("peer", "nccl"):
         raise ValueError("exchange must be 'peer' or 'nccl'")
     ex = PeerExchange(rank=rank, world=world, max_rows=batch, d=shape.d) if exchange == "peer" else None
+    if ex is not None and trace:
+        ex.start_trace()
     part_rank, part_world = (0, int(shard_of)) if shard_of else (rank, world)
 
     L = shape.n_layers if n_layers is None else int(n_layers)

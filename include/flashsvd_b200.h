@@ -305,6 +305,11 @@ int fsvd_exchange_region_release(void* imported_region);
 int fsvd_exchange_create(int rank, int world, void* const* regions, int max_rows, int d, void* stream,
                          fsvd_exchange** out);
 int fsvd_exchange_destroy(fsvd_exchange* ex);
+/* Timing of the exchanges for profiling: while a device buffer is set, the reduction of exchange
+ * number k writes record k mod (bytes / 24) = three %globaltimer values (ns): its dependency met
+ * (the rank's own GEMM has finished), all ranks' flags seen, reduction done.  Set it before the
+ * first layer call that should be traced; NULL switches it off. */
+int fsvd_exchange_set_trace(fsvd_exchange* ex, void* dev_ptr, size_t bytes);
 /* One decoder layer on this rank's shards (bf16, 1 <= B <= max_rows rows, tiled tensor-core path
  * at every batch size): x_out = the full layer output, identical on every rank.  The workspace has
  * fsvd_tp_workspace_bytes(dims) bytes, zeroed once.  The appended key / value rows are the rank's

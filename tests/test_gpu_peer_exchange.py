@@ -181,3 +181,25 @@ def test_norms_of_the_neighbouring_layers_fused_into_the_exchange():
 def rel(a, b):
     a, b = a.float().cpu(), b.float().cpu()
     return float((a - b).abs().max() / b.abs().max())
+
+
+def test_exchange_trace_records_every_reduction():
+    from flashsvd_b200 import tensor_parallel as TP
+
+    shape, B, ctx = O.TINY_GQA, 4, 12
+    S_max = ctx + 4
+    w, x, kc, vc, seqlens, cos, sin = _case(shape, B, ctx, S_max, seed=9)
+    sh = TP.shard_layer_weights(w, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=0, world=1)
+    lay = TP.region_layout(1, B, shape.d)
+    buf = torch.zeros(lay["total"], dtype=torch.uint8, device=DEV)
+    ex = TP.PeerExchange(rank=0, world=1, max_rows=B, d=shape.d, regions=[buf.data_ptr()])
+    ex.start_trace(records=16)
+    layer = TP.TPDecodeLayer(sh, H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=0, world=1, batch=B, S_max=S_max,
+                             eps=shape.eps, device=DEV, exchange=ex)
+    for _ in range(3):
+        layer.forward(x.to(DEV), seqlens.to(DEV), cos.to(DEV), sin.to(DEV))
+    torch.cuda.synchronize()
+    s = ex.trace_summary()
+    assert s["exchanges"] == 6                       # two per layer call
+    assert 0 <= s["wait_us_median"] < 1e4 and 0 < s["reduce_us_median"] < 1e4
+    ex.close()
