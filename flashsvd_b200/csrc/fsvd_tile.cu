@@ -32,6 +32,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -1428,8 +1429,16 @@ static int device_limits() {
 
 // Segments of the K range: about one CTA per SM, at least 4 k-blocks (64 KB of factor) per CTA
 // where the matrix has them, at most kMaxSegs segments, none empty.
+static int ctas_per_sm_wanted() {
+  static int v = [] {
+    const char* e = getenv("FSVD_TILE_CTAS_PER_SM");
+    const int x = e ? atoi(e) : 1;
+    return x >= 1 && x <= 4 ? x : 1;
+  }();
+  return v;
+}
 static void split_k(int tiles, int nkb, int sms, int& segs, int& kbs) {
-  int want = (sms + tiles / 2) / tiles;
+  int want = (ctas_per_sm_wanted() * sms + tiles / 2) / tiles;
   if (want > kMaxSegs) want = kMaxSegs;
   if (want > nkb / 4) want = nkb / 4;
   if (want < 1) want = 1;
