@@ -1263,9 +1263,14 @@ __global__ void __launch_bounds__(kAttnThreads, 3) gqa_decode_attn_kernel(const 
   // ---- merge of the splits by the last CTA: the weight of every (split, head) once, in shared
   // memory, then each thread sums four output dims over the splits with independent 16-byte loads
   const float* parts = a.part + (((size_t)b * a.Hk + hk) * nsplit) * G * rec;
-  float* wgt_s = wpart;                          // [nsplit][G] weights (<= 64 x 8)
-  float* den_s = wpart + kGqMaxSplit * 8;        // [G]
-  for (int i = tid; i < nsplit * G; i += kAttnThreads) wgt_s[i] = __ldcg(parts + (size_t)i * rec + DH);
+  float* wgt_s = wpart;                          // [nsplit][G] maxima, then weights (<= 64 x 8)
+  float* den_s = wpart + kGqMaxSplit * 8;        // [G] sums, [8 + G] maxima
+  float* l_s = den_s + 16;                       // [nsplit][G] running sums of the splits
+  for (int i = tid; i < nsplit * G; i += kAttnThreads) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(parts + (size_t)i * rec + DH));
+    wgt_s[i] = ml.x;
+    l_s[i] = ml.y;
+  }
   __syncthreads();
   if (tid < G) {
     float mm = -INFINITY;
@@ -1280,14 +1285,14 @@ __global__ void __launch_bounds__(kAttnThreads, 3) gqa_decode_attn_kernel(const 
   __syncthreads();
   if (tid < G) {
     float den = 0.0f;
-    for (int sp = 0; sp < nsplit; ++sp) den += wgt_s[sp * G + tid] * __ldcg(parts + ((size_t)sp * G + tid) * rec + DH + 1);
+    for (int sp = 0; sp < nsplit; ++sp) den += wgt_s[sp * G + tid] * l_s[sp * G + tid];
     den_s[tid] = den;
   }
   __syncthreads();
   for (int i = tid; i < G * (DH / 4); i += kAttnThreads) {
     const int gg = i / (DH / 4), d4 = (i - gg * (DH / 4)) * 4;
     float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 8
+#pragma unroll 16
     for (int sp = 0; sp < nsplit; ++sp) {
       const float4 v = __ldcg(reinterpret_cast<const float4*>(parts + ((size_t)sp * G + gg) * rec + d4));
       const float wg = wgt_s[sp * G + gg];
