@@ -60,13 +60,9 @@ inline size_t region_bytes(int world, int max_rows, int d) {
 __device__ __forceinline__ unsigned long long* slot_ptr(const Geom& g, int dst, unsigned parity, int src) {
   return reinterpret_cast<unsigned long long*>(g.region[dst] + g.slots_off + (size_t)(parity * g.world + src) * g.slot_bytes);
 }
-// One aligned 8-byte store: the word arrives whole.  A plain (weak) store on purpose: stores at system
-// scope (st.relaxed.sys / volatile) left the SM one at a time here (16 per thread towards 8 ranks took
-// 16 us to arrive, 2.3 us per rank), plain stores are posted back to back; nothing is ordered after
-// the word, so it needs no more than to arrive, which the end of the kernel guarantees at the latest.
 __device__ __forceinline__ void st_word(unsigned long long* p, unsigned pair_bits, unsigned seq) {
   const unsigned long long w = (unsigned long long)pair_bits | ((unsigned long long)seq << 32);
-  asm volatile("st.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_word(const unsigned long long* p) {
   unsigned long long w;

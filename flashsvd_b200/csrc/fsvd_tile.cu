@@ -625,21 +625,14 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-    // The words of all ranks are requested together, then taken in rank order.  The first read is a
-    // plain 16-byte load past L1 (two words): loads at system scope complete one after the other
-    // (64 of them per thread took 16 us at 8 ranks); only a word that has not arrived yet is polled
-    // with them (take_word).
+    // the words of all ranks are requested together, then taken in rank order
     unsigned long long w[fsvd_exch::kMaxRanks][8];
 #pragma unroll
     for (int q = 0; q < fsvd_exch::kMaxRanks; ++q) {
       if (q < a.ex.world) {
-        const uint4* wp4 = reinterpret_cast<const uint4*>(fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, q) + wrow + i);
+        const unsigned long long* wp = fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, q) + wrow + i;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 t = __ldcg(wp4 + j);
-          w[q][2 * j] = (unsigned long long)t.x | ((unsigned long long)t.y << 32);
-          w[q][2 * j + 1] = (unsigned long long)t.z | ((unsigned long long)t.w << 32);
-        }
+        for (int j = 0; j < 8; ++j) w[q][j] = fsvd_exch::ld_word(wp + j);
       }
     }
 #pragma unroll
