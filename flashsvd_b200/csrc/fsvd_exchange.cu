@@ -92,8 +92,10 @@ int fsvd_exchange_create(int rank, int world, void* const* regions, int max_rows
   memset(ex, 0, sizeof(*ex));
   Geom& g = ex->geom;
   for (int q = 0; q < world; ++q) g.region[q] = reinterpret_cast<unsigned long long>(regions[q]);
+  g.flag_cap = flag_capacity(d);
   g.slot_bytes = slot_capacity(max_rows, d);
-  g.slots_off = kCtrlBytes;
+  g.flags_off = kCtrlBytes;
+  g.slots_off = kCtrlBytes + al256((size_t)2 * world * g.flag_cap * 4);
   g.world = world;
   g.rank = rank;
   ex->max_rows = max_rows;

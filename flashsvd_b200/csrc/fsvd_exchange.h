@@ -6,22 +6,18 @@
 // Every rank owns one region of device memory with the same layout, mapped into every other rank's
 // process (CUDA IPC, NVLink peer access):
 //
-//     [control block, 256 bytes]                   local only: sequence number, done counter
-//     [slots : 2 parities x world x slot_bytes  ]  slot [parity][src] = src's partial sums as 8-byte words
+//     [control block, 256 bytes]                    local only: sequence number, done counter
+//     [flags   : 2 parities x world x flag_cap u32] flag [parity][src][cta] = sequence number
+//     [slots   : 2 parities x world x slot_bytes  ] slot [parity][src] = src's partial sums, bf16 [rows, d]
 //
-// A word carries its own flag: word [b / 2][p] of a slot = { bf16 of row b (b even), bf16 of row
-// b + 1, sequence number of the exchange (32 bits) }, written with ONE 8-byte store, which the memory
-// system performs as a unit.  Exchange number k (k = 1, 2, ...; parity k & 1): the GEMM that produces
-// a rank's partial sums stores every finished value pair into slot [k & 1][rank] of EVERY rank's
-// region (plain peer stores, its own region included) and is done: no fence, no separate flag, so
-// nothing at system scope holds up the end of the kernel (a release store after the data cost 3.6 us
-// median, 8 us worst, per pushing GEMM).  The reducing kernel of a rank reads the words of its OWN
-// region and takes a word when its sequence number is k (polling it otherwise), adds the `world`
-// slots in rank order (so every rank computes the same bits) plus the residual, and the last of its
-// CTAs advances the rank's sequence number.
+// Exchange number k (k = 1, 2, ...; parity k & 1): the GEMM that produces a rank's partial sums
+// stores every finished tile into slot [k & 1][rank] of EVERY rank's region (plain stores, its own
+// region included), and each of its CTAs then publishes flag [k & 1][rank][cta] = k in every region
+// (a CTA barrier, then a store with release semantics at system scope).  The reducing kernel of a rank polls the flags of its OWN region until all
+// `world` sources have posted k, adds the world slots in rank order (so every rank computes the same
+// bits) plus the residual, and the last of its CTAs advances the rank's sequence number.
 // Two parities suffice: a rank can push exchange k + 2 only after it has reduced k + 1, which needs
-// every peer's push of k + 1, which the peer issues after its own reduction of k has completed; a
-// word left from exchange k - 2 carries k - 2 and is never taken for k.
+// every peer's push of k + 1, which the peer issues after its own reduction of k has completed.
 //
 // Every wait is bounded (clock64 budget); when it runs out the kernel records DS_PEER_TIMEOUT in
 // the workspace status word and carries on with whatever the slots hold.
@@ -45,29 +41,32 @@ struct Ctrl {
 
 struct Geom {
   unsigned long long region[kMaxRanks];   // base of rank q's region as mapped in this process
-  unsigned long long slots_off, slot_bytes;
+  unsigned long long flags_off, slots_off, slot_bytes;
+  unsigned flag_cap;
   int world, rank;
 };
 
 inline size_t al256(size_t x) { return (x + 255) / 256 * 256; }
-inline size_t slot_capacity(int max_rows, int d) { return al256((size_t)((max_rows + 1) / 2) * d * 8); }
+inline unsigned flag_capacity(int d) { return (unsigned)((d + 127) / 128 * 8); }   // row tiles x K segments (<= 8)
+inline size_t slot_capacity(int max_rows, int d) { return al256((size_t)max_rows * d * 2); }
 inline size_t region_bytes(int world, int max_rows, int d) {
-  return (size_t)kCtrlBytes + (size_t)2 * world * slot_capacity(max_rows, d);
+  return (size_t)kCtrlBytes + al256((size_t)2 * world * flag_capacity(d) * 4) + (size_t)2 * world * slot_capacity(max_rows, d);
 }
 
 #ifdef __CUDACC__
-// slot [parity][src] of rank dst's region, as words
-__device__ __forceinline__ unsigned long long* slot_ptr(const Geom& g, int dst, unsigned parity, int src) {
-  return reinterpret_cast<unsigned long long*>(g.region[dst] + g.slots_off + (size_t)(parity * g.world + src) * g.slot_bytes);
+__device__ __forceinline__ unsigned* flag_ptr(const Geom& g, int dst, unsigned parity, int src, int idx) {
+  return reinterpret_cast<unsigned*>(g.region[dst] + g.flags_off) + ((size_t)(parity * g.world + src) * g.flag_cap + idx);
 }
-__device__ __forceinline__ void st_word(unsigned long long* p, unsigned pair_bits, unsigned seq) {
-  const unsigned long long w = (unsigned long long)pair_bits | ((unsigned long long)seq << 32);
-  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+__device__ __forceinline__ unsigned char* slot_ptr(const Geom& g, int dst, unsigned parity, int src) {
+  return reinterpret_cast<unsigned char*>(g.region[dst] + g.slots_off + (size_t)(parity * g.world + src) * g.slot_bytes);
 }
-__device__ __forceinline__ unsigned long long ld_word(const unsigned long long* p) {
-  unsigned long long w;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
-  return w;
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 #endif
 

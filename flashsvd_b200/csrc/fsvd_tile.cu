@@ -183,10 +183,6 @@ __device__ __forceinline__ void tmark(const GemmArgs& a, int k) {
 }
 
 __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
 __device__ __forceinline__ float ldbf(const void* p, size_t i) {
   return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
@@ -444,15 +440,13 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
         for (int i = 0; i < 4; ++i)
           if (i < nb) stbf(a.out, o0 + (size_t)i * a.P, res[i] + rnd(v[i]));
       } else if (a.epi == TE_PUSH) {
-        // the rounded partial sums of two batch rows and the number of the exchange as one 8-byte
-        // word, into slot [parity][this rank] of every rank's region (peer stores over NVLink, the
-        // rank's own region among them); b0 is a multiple of 4, rows past the batch are zero
-        const uint32_t w0 = pack_bf16(v[0], v[1]), w1 = pack_bf16(v[2], v[3]);
-        const size_t wi = (size_t)(b0 >> 1) * a.P + p;
+        // the same rounded partial sums into slot [parity][this rank] of every rank's region
+        // (peer stores over NVLink; the rank's own region among them)
         for (int q = 0; q < a.ex.world; ++q) {
-          unsigned long long* dst = fsvd_exch::slot_ptr(a.ex, q, push_seq & 1u, a.ex.rank) + wi;
-          fsvd_exch::st_word(dst, w0, push_seq);
-          if (nb > 2) fsvd_exch::st_word(dst + a.P, w1, push_seq);
+          unsigned char* dst = fsvd_exch::slot_ptr(a.ex, q, push_seq & 1u, a.ex.rank);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (i < nb) stbf(dst, o0 + (size_t)i * a.P, v[i]);
         }
       } else if (a.epi == TE_SWIGLU) {
 #pragma unroll
@@ -511,6 +505,13 @@ __global__ void __launch_bounds__(kThreads) tile_gemm_kernel(const __grid_consta
   tmark(a, 7);
   tc_fence_before();
   __syncthreads();
+  // TE_PUSH: every store of this CTA is ordered before the flags that thread q raises in rank q's
+  // region: the CTA barrier above, then a store with release semantics at system scope (it orders the
+  // writes the thread has observed through the barrier as well as its own)
+  if (a.epi == TE_PUSH && tid < a.ex.world) {
+    fsvd_exch::st_release_sys(fsvd_exch::flag_ptr(a.ex, tid, push_seq & 1u, a.ex.rank, tile * a.segs + seg), push_seq);
+  }
+  __syncwarp();
   if (*giveup)
     for (int i = 0; i < 100; ++i) __nanosleep(1000);   // copies in flight towards this CTA land first
   if (warp == 0) tc_dealloc(tmem, a.tmem_cols);
@@ -557,6 +558,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
 struct ReduceArgs {
   fsvd_exch::Geom ex;
   fsvd_exch::Ctrl* ctrl;
+  int nflags;                    // CTAs of the pushing GEMM
   const __nv_bfloat16* resid;
   __nv_bfloat16* out;
   const __nv_bfloat16* norm_w;
@@ -565,7 +567,7 @@ struct ReduceArgs {
   float eps;
   int* status;                   // SyncState::status, status_detail of the workspace
   long long wait_limit;
-  unsigned long long* trace;     // optional: record [seq % trace_cap] = %globaltimer at {dependency met, all ranks' words taken, done}
+  unsigned long long* trace;     // optional: record [seq % trace_cap] = %globaltimer at {dependency met, all flags seen, done}
   unsigned trace_cap;            // (written by CTA (0, 0))
 };
 
@@ -579,23 +581,6 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, flo
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
-
-// A word counts when it carries this exchange's number; until then rank q has not stored it: poll,
-// within the wait budget.
-__device__ __forceinline__ unsigned long long take_word(const unsigned long long* p, unsigned long long w, unsigned seq, int q,
-                                                        long long c0, volatile int* giveup, const ReduceArgs& a) {
-  unsigned spins = 0;
-  while ((unsigned)(w >> 32) != seq) {
-    if (*giveup) break;
-    if ((++spins & 15u) == 0 && clock64() - c0 > a.wait_limit) {
-      if (atomicCAS(a.status, (int)DS_OK, (int)fsvd_exch::DS_PEER_TIMEOUT) == (int)DS_OK) a.status[1] = q;
-      *giveup = 1;
-      break;
-    }
-    w = fsvd_exch::ld_word(p);
-  }
-  return w;
 }
 
 __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_constant__ ReduceArgs a) {
@@ -613,37 +598,45 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
   const unsigned par = seq & 1u;
   unsigned long long* rec = (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) ? a.trace + (size_t)(seq % a.trace_cap) * 3 : nullptr;
   if (rec) rec[0] = global_ns();
+  {
+    const int total = a.ex.world * a.nflags;
+    const long long c0 = clock64();
+    for (int i = tid; i < total && !*giveup; i += 256) {
+      const int src = i / a.nflags;
+      const unsigned* f = fsvd_exch::flag_ptr(a.ex, a.ex.rank, par, src, i - src * a.nflags);
+      unsigned spins = 0;
+      while ((int)(fsvd_exch::ld_acquire_sys(f) - seq) < 0) {
+        if ((++spins & 15u) == 0) {
+          if (*giveup) break;
+          if (clock64() - c0 > a.wait_limit) {
+            if (atomicCAS(a.status, (int)DS_OK, (int)fsvd_exch::DS_PEER_TIMEOUT) == (int)DS_OK) a.status[1] = src;
+            *giveup = 1;
+            break;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (rec) rec[1] = global_ns();
   if (C > 1 && a.xn) cluster_sync();            // every CTA of the row runs before any writes into its shared memory
 
   const int cols = a.d / C, col0 = c * cols;    // the host makes cols a multiple of 8
   const size_t row = (size_t)b * a.d + col0;
-  const size_t wrow = (size_t)(b >> 1) * a.d + col0;   // the row's words: two batch rows per word
-  const unsigned sh16 = (b & 1) ? 16u : 0u;
-  const long long c0 = clock64();
+  const unsigned char* slot0 = fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, 0);
   float ss = 0.0f;
   for (int i = tid * 8; i < cols; i += 256 * 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-    // the words of all ranks are requested together, then taken in rank order
-    unsigned long long w[fsvd_exch::kMaxRanks][8];
+    for (int q = 0; q < a.ex.world; ++q) {
+      const uint4 t = __ldcg(reinterpret_cast<const uint4*>(slot0 + (size_t)q * a.ex.slot_bytes + (row + i) * 2));
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&t);
 #pragma unroll
-    for (int q = 0; q < fsvd_exch::kMaxRanks; ++q) {
-      if (q < a.ex.world) {
-        const unsigned long long* wp = fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, q) + wrow + i;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w[q][j] = fsvd_exch::ld_word(wp + j);
-      }
-    }
-#pragma unroll
-    for (int q = 0; q < fsvd_exch::kMaxRanks; ++q) {
-      if (q < a.ex.world) {
-        const unsigned long long* wp = fsvd_exch::slot_ptr(a.ex, a.ex.rank, par, q) + wrow + i;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const unsigned long long wj = take_word(wp + j, w[q][j], seq, q, c0, giveup, a);
-          acc[j] += __uint_as_float(((unsigned)wj >> sh16) << 16);
-        }
+      for (int j = 0; j < 4; ++j) {
+        const float2 f2 = __bfloat1622float2(h2[j]);
+        acc[2 * j] += f2.x;
+        acc[2 * j + 1] += f2.y;
       }
     }
     const uint4 rr = *reinterpret_cast<const uint4*>(a.resid + row + i);
@@ -659,7 +652,6 @@ __global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(const __grid_
     }
     *reinterpret_cast<uint4*>(a.out + row + i) = o;
   }
-  if (rec) rec[1] = global_ns();
   if (a.xn) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -922,6 +914,10 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 template <int DH>
@@ -1862,6 +1858,7 @@ static int plan_tp_layer(TpPlan& tp, const fsvd_dims& D, const fsvd_layer& Lw, c
   fsvd_exch::Ctrl* ctrl = reinterpret_cast<fsvd_exch::Ctrl*>(ex.geom.region[ex.geom.rank]);
   int* status = &reinterpret_cast<SyncState*>(ws + L.sync)->status;
   auto to_push = [&](GemmPlan& g, ReduceArgs& r, const void* resid, void* out, const void* norm_w, void* xn) -> int {
+    if ((unsigned)(g.a.tiles * g.a.segs) > ex.geom.flag_cap) return fail(FSVD_ERR_UNSUPPORTED, "more CTAs in a lift than exchange flags");
     g.a.epi = TE_PUSH;
     g.a.out = nullptr;
     g.a.resid = nullptr;
@@ -1870,6 +1867,7 @@ static int plan_tp_layer(TpPlan& tp, const fsvd_dims& D, const fsvd_layer& Lw, c
     memset(&r, 0, sizeof(r));
     r.ex = ex.geom;
     r.ctrl = ctrl;
+    r.nflags = g.a.tiles * g.a.segs;
     r.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
     r.out = reinterpret_cast<__nv_bfloat16*>(out);
     r.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w);

@@ -14,10 +14,9 @@ Two ways to run a layer:
 
 ``exchange="peer"`` (default for bf16): ``fsvd_tp_decode_layer`` — the layer as tiled tensor-core
     GEMMs on the shards; the epilogue of the o lift and of the down lift stores every finished tile
-    into an exchange region of EVERY rank (peer stores over NVLink, regions mapped with CUDA IPC) as
-    8-byte words that carry the number of the exchange beside two values; the next kernel takes the
-    words of its own region as they arrive, adds the partial sums in rank order plus the residual
-    and applies the next RMSNorm.  No collective call, no fence and no separate flag on the path.
+    into an exchange region of EVERY rank (peer stores over NVLink, regions mapped with CUDA IPC) and
+    raises a flag per CTA; the next kernel polls the flags of its own region, adds the partial sums
+    in rank order plus the residual and applies the next RMSNorm.  No collective call on the path.
 ``exchange="nccl"``: the library's per-op entry points on the shards (``fsvd_qkv_rope_append``,
     ``fsvd_flash_decode``, ``fsvd_lowrank_proj``, ``fsvd_mlp_swiglu_decode``) with
     ``torch.distributed.all_reduce`` of the two partial sums; rank 0 adds the residual before the
@@ -80,31 +79,16 @@ def _all_reduce(t: torch.Tensor) -> torch.Tensor:
 
 
 def region_layout(world: int, max_rows: int, d: int) -> dict:
-    """Byte offsets inside an exchange region (mirror of csrc/fsvd_exchange.h): after a 256-byte
-    control block (sequence number first), slots [2 parities][world][slot_bytes] at ``slots``; a
-    slot = one rank's partial sums as int64 words [ceil(rows / 2), d] (``pack_exchange_words``)."""
+    """Byte offsets inside an exchange region (mirror of csrc/fsvd_exchange.h): flags
+    [2 parities][world][flag_cap] uint32 at ``flags``, slots [2 parities][world][slot_bytes] at
+    ``slots`` (a slot = one rank's partial sums, bf16 [rows, d])."""
     al = lambda n: (n + 255) // 256 * 256
-    slot_bytes = al((max_rows + 1) // 2 * d * 8)
-    return {"slot_bytes": slot_bytes, "slots": 256, "total": 256 + 2 * world * slot_bytes}
-
-
-def pack_exchange_words(rows: torch.Tensor, seq: int) -> torch.Tensor:
-    """bf16 [B, d] -> int64 [ceil(B / 2), d]: bits 0..15 row 2j, bits 16..31 row 2j + 1 (zero past the
-    batch), bits 32..63 the number of the exchange — what the pushing GEMM stores, one 8-byte store
-    per word."""
-    B, d = rows.shape
-    r = rows.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
-    if B % 2:
-        r = torch.cat([r, torch.zeros(1, d, dtype=torch.int64, device=r.device)], 0)
-    return r[0::2] | (r[1::2] << 16) | (int(seq) << 32)
-
-
-def unpack_exchange_words(words: torch.Tensor, rows: int):
-    """int64 [ceil(B / 2), d] -> (bf16 [B, d], int64 [ceil(B / 2), d] exchange numbers)."""
-    lo = (words & 0xFFFF).to(torch.int16).view(torch.bfloat16)
-    hi = ((words >> 16) & 0xFFFF).to(torch.int16).view(torch.bfloat16)
-    out = torch.stack([lo, hi], 1).reshape(-1, words.shape[1])[:rows]
-    return out, (words >> 32) & 0xFFFFFFFF
+    flag_cap = (d + 127) // 128 * 8
+    slot_bytes = al(max_rows * d * 2)
+    flags = 256
+    slots = flags + al(2 * world * flag_cap * 4)
+    return {"flag_cap": flag_cap, "slot_bytes": slot_bytes, "flags": flags, "slots": slots,
+            "total": slots + 2 * world * slot_bytes}
 
 
 class PeerExchange:

@@ -1,5 +1,5 @@
 """The in-kernel exchange of the tensor-parallel layer on ONE GPU: the pushing GEMM epilogue, the
-flag-carrying words, the sequence numbers and the reducing kernel, with the other rank's words
+flags, the sequence numbers and the reducing kernel, with the other rank's partial sums and flags
 written by the host beforehand (kernels that wait for each other never run side by side on one
 GPU); and the bounded wait: a peer that never posts ends in an error status, not a hang."""
 import pytest
@@ -55,11 +55,14 @@ def _oracle_partials(shape, shards, x, kcs, vcs, seqlens, cos, sin):
     return parts, h, parts2, y
 
 
-def _slots(buf, lay, world, B, d):
-    """int64 view [2 parities, world, ceil(B / 2), d] of a region's slots."""
-    nw = (B + 1) // 2 * d
-    v = buf[lay["slots"]: lay["slots"] + 2 * world * lay["slot_bytes"]].view(torch.int64).view(2, world, lay["slot_bytes"] // 8)
-    return v[:, :, :nw].view(2, world, (B + 1) // 2, d)
+def _region_views(buf, lay, world):
+    flags = buf[lay["flags"]: lay["flags"] + 2 * world * lay["flag_cap"] * 4].view(torch.int32).view(2, world, lay["flag_cap"])
+    slots = buf[lay["slots"]: lay["slots"] + 2 * world * lay["slot_bytes"]].view(2, world, lay["slot_bytes"])
+    return flags, slots
+
+
+def _slot_rows(slots, parity, src, B, d):
+    return slots[parity, src, : B * d * 2].view(torch.bfloat16).view(B, d)
 
 
 @pytest.mark.parametrize("shape_name,B,ctx,world", [("TINY_GQA", 3, 20, 1), ("TINY_GQA", 8, 20, 2), ("TINY_GQA", 16, 40, 2)])
@@ -80,11 +83,13 @@ def test_tp_layer_rank0_with_the_peer_preposted(shape_name, B, ctx, world):
     bufs = [torch.zeros(lay["total"], dtype=torch.uint8, device=DEV) for _ in range(world)]
     ex = TP.PeerExchange(rank=0, world=world, max_rows=B, d=shape.d, regions=[b.data_ptr() for b in bufs])
     assert ex.nbytes == lay["total"]
-    slots0 = _slots(bufs[0], lay, world, B, shape.d)
+    flags0, slots0 = _region_views(bufs[0], lay, world)
     if world == 2:
         # what rank 1 would have stored into rank 0's region: exchange 1 (parity 1), exchange 2 (parity 0)
-        slots0[1, 1].copy_(TP.pack_exchange_words(parts[1], 1).to(DEV))
-        slots0[0, 1].copy_(TP.pack_exchange_words(parts2[1], 2).to(DEV))
+        _slot_rows(slots0, 1, 1, B, shape.d).copy_(parts[1].to(DEV))
+        _slot_rows(slots0, 0, 1, B, shape.d).copy_(parts2[1].to(DEV))
+        flags0[1, 1, :] = 1
+        flags0[0, 1, :] = 2
     layer = TP.TPDecodeLayer(shards[0], H=shape.H, Hk=shape.Hk, Dh=shape.Dh, rank=0, world=world, batch=B, S_max=S_max,
                              eps=shape.eps, device=DEV, exchange=ex)
     layer.k_cache.copy_(kc0)
@@ -97,14 +102,18 @@ def test_tp_layer_rank0_with_the_peer_preposted(shape_name, B, ctx, world):
     kerr = float((layer.k_cache.float().cpu() - kcs[0].float()).abs().max() / kcs[0].float().abs().max())
     print(f"{shape_name} B={B} world={world}: rank 0 layer output rel_linf {err:.3e}, keys {kerr:.3e}")
     assert err <= 2e-2 and kerr <= 2e-2
-    # the partial sums rank 0 pushed: the same words in every region, numbered 1 and 2, close to the oracle's
-    for parity, seq, ref in ((1, 1, parts[0]), (0, 2, parts2[0])):
-        mine, seqs = TP.unpack_exchange_words(slots0[parity, 0], B)
-        assert bool((seqs == seq).all())
+    # the partial sums rank 0 pushed: the same bytes in every region, close to the oracle's
+    for parity, ref in ((1, parts[0]), (0, parts2[0])):
+        mine = _slot_rows(slots0, parity, 0, B, shape.d)
         perr = float((mine.float().cpu() - ref.float()).abs().max() / ref.float().abs().max())
         assert perr <= 2e-2, perr
         for b in bufs[1:]:
-            assert torch.equal(_slots(b, lay, world, B, shape.d)[parity, 0], slots0[parity, 0])
+            _, slots_q = _region_views(b, lay, world)
+            assert torch.equal(_slot_rows(slots_q, parity, 0, B, shape.d), mine)
+    # one flag per CTA of the pushing GEMM in every region, and the sequence number moved on by 2
+    for b in bufs:
+        fl, _ = _region_views(b, lay, world)
+        assert int((fl[1, 0] == 1).sum()) >= 1 and int((fl[0, 0] == 2).sum()) >= 1
     assert int(bufs[0][:4].view(torch.int32)[0]) == 3
     ex.close()
 
