@@ -2,9 +2,10 @@
 package: the same names, arguments and result dictionaries, so code written against
 ``scripts.demo_support`` runs with ``from flashsvd_b200 import demo_support``.
 
-Loading covers the formats that need no network: a ``torch.save({'model': ..., 'tokenizer': ...})``
-file (utils/model_utils.py:850-901) and a directory with ``config.json`` + a state dict whose keys
-carry the ``*_v_proj`` / ``*_u_proj`` factor names (utils/model_utils.py:637-643).  Models with
+Loading covers the formats that need no network (``get_model_from_local``, utils/model_utils.py:850-901):
+a ``torch.save({'model': ..., 'tokenizer': ...})`` file (wrapped factor pairs are converted), a
+directory with ``config.json`` + a state dict whose keys carry the ``*_v_proj`` / ``*_u_proj`` factor
+names (utils/model_utils.py:637-643), and a basis-sharing export directory (``checkpoints.py``).  Models with
 low-rank modules decode through the CUDA library (``generate_text`` builds and keeps a
 ``DecodeEngine`` for them); any other transformers model takes the plain token loop.
 """
@@ -73,39 +74,59 @@ def build_svd_llama(config, state_dict: Optional[dict] = None):
     return model
 
 
+def _local_tokenizer(p: Path):
+    if any((p / n).exists() for n in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
+        try:
+            from transformers import AutoTokenizer
+
+            return AutoTokenizer.from_pretrained(str(p), local_files_only=True)
+        except Exception:
+            return None
+    return None
+
+
 def get_model_from_local(path: str):
-    """(model, tokenizer) from a torch.save'd ``{'model', 'tokenizer'}`` file, or from a directory
-    with ``config.json`` and ``pytorch_model.bin`` / ``model.pt`` holding a factored Llama state dict."""
+    """(model, tokenizer) from a local checkpoint, dispatching as utils/model_utils.py:850-901 does:
+    a directory with a basis-sharing export (``checkpoints.load_basis_sharing_dir``); a directory
+    with ``config.json`` and ``pytorch_model.bin`` (one file, shards or an index) / ``model.pt``
+    holding a factored Llama state dict; a ``torch.save({'model', 'tokenizer'})`` file or a pickled
+    model, whose wrapped factor pairs (``u_proj`` / ``v_proj``, ``BLinear`` / ``ALinear``) become
+    this package's modules over the same weights."""
+    from . import checkpoints
+
     p = Path(path).expanduser()
     if p.is_dir():
         cfg_path = p / "config.json"
         if not cfg_path.exists():
             raise FileNotFoundError(f"{p} has no config.json")
+        raw = checkpoints.read_local_config(p)
+        if checkpoints.is_basis_sharing_config(raw):
+            return checkpoints.load_basis_sharing_dir(p, raw), _local_tokenizer(p)
         from transformers import LlamaConfig
 
-        raw = json.loads(cfg_path.read_text())
         config = LlamaConfig(**{k: v for k, v in raw.items() if k not in ("architectures", "model_type", "auto_map")})
-        weights = next((p / n for n in ("pytorch_model.bin", "model.pt", "model.bin") if (p / n).exists()), None)
-        if weights is None:
+        single = next((p / n for n in ("model.pt", "model.bin") if (p / n).exists()), None)
+        try:
+            files = list(checkpoints.iter_weight_shards(p))
+        except FileNotFoundError:
+            files = [single] if single is not None else []
+        if not files:
             raise FileNotFoundError(f"{p} has no pytorch_model.bin / model.pt")
-        sd = torch.load(weights, map_location="cpu", weights_only=True)
+        sd = {}
+        for f in files:
+            sd.update(torch.load(f, map_location="cpu", weights_only=True))
         if not any(k.endswith("q_u_proj.weight") for k in sd):
             raise ValueError("the state dict has no *_u_proj / *_v_proj factors: not a FlashSVD Llama export")
-        tok = None
-        if any((p / n).exists() for n in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
-            try:
-                from transformers import AutoTokenizer
-
-                tok = AutoTokenizer.from_pretrained(str(p), local_files_only=True)
-            except Exception:
-                tok = None
-        return build_svd_llama(config, sd), tok
+        return build_svd_llama(config, sd), _local_tokenizer(p)
     if not p.exists():
         raise FileNotFoundError(str(p))
     obj = torch.load(p, map_location="cpu", weights_only=False)
     if isinstance(obj, dict) and "model" in obj:
-        return obj["model"], obj.get("tokenizer")
-    raise ValueError("expected torch.save({'model': model, 'tokenizer': tokenizer}, path)")
+        return checkpoints.convert_wrapped_factor_pairs(obj["model"]), obj.get("tokenizer")
+    if hasattr(obj, "forward"):
+        raise ValueError(f"Loaded a model object from {path} but could not recover a tokenizer. "
+                         "Please re-save as {'model': model, 'tokenizer': tok}.")
+    raise ValueError(f"Unrecognized checkpoint format at: {path}")
 
 
 def get_model_from_huggingface(name: str, *, hf_token: Optional[str] = None, torch_dtype=None):
