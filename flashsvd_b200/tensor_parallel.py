@@ -258,6 +258,9 @@ class TPModel:
                  eps: float, device, dtype=torch.bfloat16, use_graph: bool = True):
         from .engine import rope_tables
 
+        if batch > (8 if dtype == torch.bfloat16 else 4):
+            raise ValueError("the model step (replicated lm_head through fsvd_lift) takes at most 8 sequences; "
+                             "TPDecodeLayer with a PeerExchange takes up to 128")
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
         self.B, self.S_max, self.eps, self.device, self.dtype = int(batch), int(S_max), float(eps), device, dtype
         self.cos, self.sin = rope_tables(self.S_max, head_dim, theta, dtype, device)

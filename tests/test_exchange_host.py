@@ -48,3 +48,12 @@ def test_shard_ranges_and_layer_constructor_errors():
     sq, sk, si = TP.shard_ranges(64, 8, 128, 28672, 7, 8)
     assert (sq.start, sq.stop) == (7 * 1024, 8 * 1024) and (sk.start, sk.stop) == (7 * 128, 8 * 128)
     assert (si.start, si.stop) == (7 * 3584, 8 * 3584)
+
+
+def test_tp_layer_entry_rejects_null_arguments_before_any_launch():
+    lib = _lib.load()
+    dims = _lib.FsvdDims()
+    layer = _lib.FsvdLayer()
+    assert lib.fsvd_tp_decode_layer(C.byref(dims), C.byref(layer), None, None, None, None, None, None, None, None, None,
+                                    None, 0, None) == -1
+    assert lib.fsvd_exchange_set_trace(None, None, 0) == -1
