@@ -18,12 +18,20 @@ state dict (utils/model_utils.py:850-901 dispatches between them):
   that share the same weight storage.
 * ``torch.save({'model': model, 'tokenizer': tokenizer})`` and a pickled model object: handled in
   ``demo_support.get_model_from_local``, which passes the model through the conversion above.
+  Such files are pickles: ``torch_load_local_checkpoint`` first tries the tensors-only load and
+  unpickles objects only from a file the caller trusts (``FLASH_SVD_TRUST_PICKLE=1``, or a file name
+  that looks like an output of the reference's own compression scripts), as
+  utils/model_utils.py:943-1090 does.
 
 Everything here is host-side Python on CPU tensors; nothing is computed.
 """
 from __future__ import annotations
 
+import contextlib
 import json
+import os
+import sys
+import types
 from pathlib import Path
 from typing import Dict, Iterator, Optional
 
@@ -249,3 +257,83 @@ def convert_wrapped_factor_pairs(model: nn.Module) -> nn.Module:
         new_mlp.ratio = float(0.5 * (ranks["gate"] + ranks["up"]) * (hidden + inter) / max(1.0, hidden * inter))
         layer.self_attn, layer.mlp = new_attn, new_mlp
     return model
+
+
+# ---------------------------------------------------------------------------- pickled checkpoints
+_OWN_OUTPUT_NAMES = ("_whitening_only_", "_whitening_then_update_", "_update_only_", "_profiling_", "svdllm", "flashsvd",
+                     "merge.pt", "dobi")
+
+
+def is_trusted_pickle(path) -> bool:
+    """True when objects may be unpickled from ``path``: the caller said so in the environment, or the
+    file is named like an output of the compression scripts (utils/model_utils.py:943-972, 1075-1079)."""
+    if os.environ.get("FLASH_SVD_TRUST_PICKLE", "").strip().lower() in ("1", "true", "yes", "on"):
+        return True
+    name = Path(path).name.lower()
+    return any(key in name for key in _OWN_OUTPUT_NAMES)
+
+
+@contextlib.contextmanager
+def pickle_compat_shims():
+    """Names that older pickles refer to and today's libraries no longer have, present for the
+    duration of a load and removed afterwards (utils/model_utils.py:975-1040):
+    ``transformers...modeling_llama.LlamaSdpaAttention``, ``transformers.activations.SiLUActivation``
+    and the ``modules.module.SVDTransformLayer`` placeholder of another compression code base."""
+    undo = []
+    added = []
+    try:
+        try:
+            import transformers.models.llama.modeling_llama as lm
+
+            if not hasattr(lm, "LlamaSdpaAttention"):
+                lm.LlamaSdpaAttention = lm.LlamaAttention
+                undo.append((lm, "LlamaSdpaAttention"))
+        except Exception:
+            pass
+        try:
+            import transformers.activations as act
+
+            if not hasattr(act, "SiLUActivation"):
+                act.SiLUActivation = type("SiLUActivation", (nn.Module,), {"forward": lambda self, x: nn.functional.silu(x)})
+                undo.append((act, "SiLUActivation"))
+        except Exception:
+            pass
+        for name in ("modules", "modules.module"):
+            if name not in sys.modules:
+                sys.modules[name] = types.ModuleType(name)
+                added.append(name)
+        pkg, mod = sys.modules["modules"], sys.modules["modules.module"]
+        if not hasattr(mod, "SVDTransformLayer"):
+            mod.SVDTransformLayer = type("SVDTransformLayer", (nn.Module,),
+                                         {"__init__": lambda self, *a, **k: nn.Module.__init__(self), "__module__": "modules.module"})
+            undo.append((mod, "SVDTransformLayer"))
+        if getattr(pkg, "module", None) is not mod and "modules" in added:
+            pkg.module = mod
+        yield
+    finally:
+        for owner, attr in reversed(undo):
+            with contextlib.suppress(Exception):
+                delattr(owner, attr)
+        for name in reversed(added):
+            sys.modules.pop(name, None)
+
+
+def torch_load_local_checkpoint(path):
+    """``torch.load`` of a local file: tensors-only first; objects only from a trusted file
+    (utils/model_utils.py:1043-1090)."""
+    path = Path(path)
+    try:
+        return torch.load(str(path), map_location="cpu", weights_only=True)
+    except Exception as e:
+        msg = str(e)
+        if "Weights only load failed" not in msg and "weights_only" not in msg:
+            raise
+        if not is_trusted_pickle(path):
+            raise RuntimeError(
+                f"Refusing to load pickled checkpoint with weights_only=False: {path}\n"
+                "PyTorch>=2.6 defaults torch.load(weights_only=True), which can't load "
+                "our pickled {'model': model, 'tokenizer': tok} format.\n"
+                "If you trust this checkpoint, re-run with: FLASH_SVD_TRUST_PICKLE=1") from e
+    with pickle_compat_shims():
+        return torch.load(str(path), map_location="cpu", weights_only=False)
+

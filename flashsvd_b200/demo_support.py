@@ -120,7 +120,7 @@ def get_model_from_local(path: str):
         return build_svd_llama(config, sd), _local_tokenizer(p)
     if not p.exists():
         raise FileNotFoundError(str(p))
-    obj = torch.load(p, map_location="cpu", weights_only=False)
+    obj = checkpoints.torch_load_local_checkpoint(p)
     if isinstance(obj, dict) and "model" in obj:
         return checkpoints.convert_wrapped_factor_pairs(obj["model"]), obj.get("tokenizer")
     if hasattr(obj, "forward"):

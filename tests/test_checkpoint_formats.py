@@ -160,10 +160,34 @@ def test_wrapped_factor_pairs_become_native_modules_over_the_same_weights(tmp_pa
     assert CK.convert_wrapped_factor_pairs(again).model.layers[0].self_attn is again.model.layers[0].self_attn
 
 
-def test_unrecognised_local_checkpoints(tmp_path):
+def test_unrecognised_and_untrusted_local_checkpoints(tmp_path, monkeypatch):
+    monkeypatch.delenv("FLASH_SVD_TRUST_PICKLE", raising=False)
     torch.save([1, 2, 3], tmp_path / "x.pt")
     with pytest.raises(ValueError, match="Unrecognized checkpoint format"):
         DS.get_model_from_local(str(tmp_path / "x.pt"))
+    # objects are unpickled only from a file the caller trusts
     torch.save(nn.Linear(2, 2), tmp_path / "m.pt")
+    with pytest.raises(RuntimeError, match="Refusing to load pickled checkpoint"):
+        DS.get_model_from_local(str(tmp_path / "m.pt"))
+    monkeypatch.setenv("FLASH_SVD_TRUST_PICKLE", "1")
     with pytest.raises(ValueError, match="could not recover a tokenizer"):
         DS.get_model_from_local(str(tmp_path / "m.pt"))
+    monkeypatch.delenv("FLASH_SVD_TRUST_PICKLE")
+    torch.save(nn.Linear(2, 2), tmp_path / "llama_svdllm_0.5.pt")        # named like the compression scripts' outputs
+    with pytest.raises(ValueError, match="could not recover a tokenizer"):
+        DS.get_model_from_local(str(tmp_path / "llama_svdllm_0.5.pt"))
+
+
+def test_pickle_shims_exist_only_during_a_load():
+    import sys
+
+    import transformers.activations as act
+
+    had = hasattr(act, "SiLUActivation")
+    with CK.pickle_compat_shims():
+        assert hasattr(act, "SiLUActivation")
+        layer = sys.modules["modules.module"].SVDTransformLayer(1, two=2)
+        assert isinstance(layer, nn.Module)
+        assert float(act.SiLUActivation()(torch.tensor(0.0))) == 0.0
+    assert hasattr(act, "SiLUActivation") == had
+    assert "modules.module" not in sys.modules
