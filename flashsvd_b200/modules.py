@@ -74,6 +74,11 @@ class SVD_LlamaMLP(_WithWorkspace):
         self.up_u_proj = nn.Linear(r, intermediate_size, bias=False)
         self.down_v_proj = nn.Linear(intermediate_size, r, bias=False)
         self.down_u_proj = nn.Linear(r, hidden_size, bias=False)
+        # the reference keeps captured CUDA graphs of its MLP here and its benchmarks clear these
+        # dicts between modes (benchmark/mlp/bench_real_checkpoint_mlp.py:78-86); nothing is captured
+        # per module here (a whole model step is one launch), the dicts stay empty
+        self._flashsvd_graph_cache: dict = {}
+        self._flashsvd_layer_graph_cache: dict = {}
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, L, d = x.shape
@@ -87,6 +92,40 @@ class SVD_LlamaMLP(_WithWorkspace):
         gate = self.gate_u_proj(self.gate_v_proj(x))
         up = self.up_u_proj(self.up_v_proj(x))
         return self.down_u_proj(self.down_v_proj(F.silu(gate) * up))
+
+
+class LlamaRotaryEmbedding(nn.Module):
+    """cos / sin of the rotary embedding in the rotate-half convention, constructed as the reference's
+    loaders do: ``LlamaRotaryEmbedding(head_dim, max_position_embeddings=..., base=rope_theta)``
+    (utils/model_utils.py:441-445).  ``forward(x, position_ids)`` -> (cos, sin) ``[B, L, head_dim]`` in
+    ``x.dtype`` with the two halves equal (the transformers layout); ``forward(x, seq_len=n)`` -> the
+    first ``n`` rows ``[n, head_dim]``.  The decode kernels read the half-width tables of
+    ``engine.rope_tables`` instead; this class serves code that asks the module for its embedding."""
+
+    def __init__(self, dim: int, max_position_embeddings: int = 2048, base: float = 10000.0, device=None):
+        super().__init__()
+        self.dim, self.max_position_embeddings, self.base = int(dim), int(max_position_embeddings), float(base)
+        inv = 1.0 / (self.base ** (torch.arange(0, self.dim, 2, dtype=torch.float32, device=device) / self.dim))
+        self.register_buffer("inv_freq", inv, persistent=False)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, position_ids: Optional[torch.Tensor] = None, seq_len: Optional[int] = None):
+        if position_ids is None:
+            n = int(seq_len) if seq_len is not None else int(x.shape[-2])
+            position_ids = torch.arange(n, device=x.device)
+        pos = position_ids.to(device=x.device, dtype=torch.float32)
+        freqs = pos[..., None] * self.inv_freq.to(x.device)
+        emb = torch.cat([freqs, freqs], dim=-1)
+        return emb.cos().to(x.dtype), emb.sin().to(x.dtype)
+
+
+def enable_flashsvd_llama_layer_tail_cuda_graph() -> bool:
+    """The reference patches transformers' decoder layer so that the part of a layer after attention
+    replays as a CUDA graph (called at import by its compression scripts and by its loaders,
+    utils/model_utils.py:768-786).  Here a whole decode step is one kernel launch (or one graph
+    launch for wide batches) built by ``DecodeEngine``, so there is nothing to patch: the function
+    exists for callers of that name and returns False (nothing was changed)."""
+    return False
 
 
 def _rope_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

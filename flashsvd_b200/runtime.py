@@ -293,6 +293,20 @@ class FlashSVDV15DenseKVCache(_CacheBase):
         return out
 
 
+class FlashSVDLegacySparseKVCache:
+    """Name of the reference's rank-space cache (runtime/cache/attn_legacy_sparse_kv.py:23-257: it
+    keeps x . k_v^T and x . v_v^T per position and rebuilds keys and values inside its own decode
+    kernels).  That is another decode mode than the dense-cache path this package serves; the name
+    is importable, constructing it says so."""
+
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("the rank-space KV cache belongs to the reference's legacy decode mode; flashsvd_b200 "
+                                  "serves mode='flashsvd' with FlashSVDV15DenseKVCache")
+
+
+LowRankKVCache = FlashSVDLegacySparseKVCache   # the reference's alias (runtime/cache/attn_legacy_sparse_kv.py:260)
+
+
 # --------------------------------------------------------------------------------- kernel wrappers
 _layout_cache: dict = {}
 _workspaces: dict = {}
@@ -358,6 +372,31 @@ def flashsvd_mlp_dual_split_triton_pcat_s(PCat, GateU, UpU, DownV, DownU, b2=Non
     if b2 is not None:
         y = y + b2.to(y.dtype)
     return y.reshape(B, L, Hd)
+
+
+def flashsvd_mlp_dual_split_triton_v1(PUp, PGate, GateU, UpU, DownV, DownU, b2=None, *, BR=None, BD=None, BR2=None,
+                                      num_warps=None, num_stages=None, store_partials_fp32: bool = False,
+                                      workspace_s2d=None):
+    """The split-input form of the decode MLP (kernels/mlp/decode/dual_split_triton.py:535-624 and its
+    v2 / v2_sm80 / v3 variants, which differ in tiling and scratch only): PUp and PGate [B, L, R]
+    instead of one PCat.  Same arithmetic as ``flashsvd_mlp_dual_split_triton_pcat_s``; the tile
+    arguments, ``store_partials_fp32`` and ``workspace_s2d`` are accepted and ignored."""
+    assert PUp.is_cuda and PGate.is_cuda and GateU.is_cuda and UpU.is_cuda and DownV.is_cuda and DownU.is_cuda
+    if PUp.ndim != 3 or PGate.ndim != 3:
+        raise ValueError(f"PUp/PGate must be [B, L, R], got {tuple(PUp.shape)} and {tuple(PGate.shape)}")
+    if PUp.shape != PGate.shape:
+        raise ValueError(f"PUp and PGate shapes must match, got {tuple(PUp.shape)} and {tuple(PGate.shape)}")
+    return flashsvd_mlp_dual_split_triton_pcat_s(torch.cat([PUp, PGate], dim=-1), GateU, UpU, DownV, DownU, b2)
+
+
+flashsvd_mlp_dual_split_triton_v2 = flashsvd_mlp_dual_split_triton_v1
+flashsvd_mlp_dual_split_triton_v2_sm80 = flashsvd_mlp_dual_split_triton_v1
+flashsvd_mlp_dual_split_triton_v3 = flashsvd_mlp_dual_split_triton_v1
+# the names the reference exports beside them (kernels/mlp/decode/dual_split_triton.py:969-983)
+flashsvd_ffn_dual_split_token = flashsvd_mlp_dual_split_triton_v1
+flashsvd_ffn_dual_split_token_v2 = flashsvd_mlp_dual_split_triton_v2
+flashsvd_ffn_dual_split_token_v2_sm80 = flashsvd_mlp_dual_split_triton_v2_sm80
+flashsvd_ffn_dual_split_token_v3 = flashsvd_mlp_dual_split_triton_v3
 
 
 def pack_qkv_shared_bases(Vq, Vk, Vv):
@@ -497,6 +536,65 @@ def call_flash_attn_with_kvcache(flash_attn_with_kvcache, q_bmhd, k_cache_bmhd, 
     ws = _workspace(q.device, q.dtype, B, H=H, Hk=Hk, Dh=Dh, S_max=S_max)
     out = ops.flash_decode(q.contiguous(), k_cache_bmhd, v_cache_bmhd, sl.contiguous(), ws, seqlen_add=add)
     return out.view(B, 1, H, Dh)
+
+
+# ---- the other names of runtime/attn/__init__.py:19-33
+def maybe_kwargs(fn, kwargs: dict) -> dict:
+    """The entries of ``kwargs`` that ``fn`` takes (all of them when its signature cannot be read;
+    runtime/attn/decode_registry.py:30-35)."""
+    import inspect
+
+    try:
+        params = inspect.signature(fn).parameters
+    except Exception:
+        return kwargs
+    return {k: v for k, v in kwargs.items() if k in params}
+
+
+def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None, rotary_sin=None, cache_seqlens=None,
+                            causal: bool = True, rotary_interleaved: bool = False, softmax_scale=None, dropout_p: float = 0.0,
+                            window_size=(-1, -1), **unsupported):
+    """The part of flash-attn's ``flash_attn_with_kvcache`` signature that the reference's decode uses
+    (runtime/attn/decode_registry.py:177-211), served by this library."""
+    if rotary_interleaved or dropout_p or tuple(window_size) != (-1, -1) or softmax_scale is not None or unsupported:
+        raise ValueError("only the decode call of the reference is served: non-interleaved rotary, no dropout, no window, "
+                         "default scale")
+    return call_flash_attn_with_kvcache(None, q, k_cache, v_cache, k_bmhd=k, v_bmhd=v, cache_seqlens=cache_seqlens,
+                                        rotary_cos=rotary_cos, rotary_sin=rotary_sin, causal=causal)
+
+
+def get_flash_attn_with_kvcache():
+    """The reference resolves flash-attn's function here (None when the wheel is missing,
+    runtime/attn/decode_registry.py:154-175); this package returns its own implementation."""
+    return flash_attn_with_kvcache
+
+
+def get_flashsvd_v15_attn_densekv_decode_mod():
+    """The module that holds ``reconstruct_qkv_token*`` and ``pack_qkv_shared_bases``
+    (runtime/attn/decode_registry.py:212-236): here, this module."""
+    import sys
+
+    return sys.modules[__name__]
+
+
+get_dense_token_decode_mod = get_flashsvd_v15_attn_densekv_decode_mod
+
+
+def _no_legacy_kernels(*_args, **_kwargs):
+    raise ImportError("Failed to load any decode attention module: the rank-space (legacy sparse-KV) decode kernels are "
+                      "not part of flashsvd_b200, which serves the dense-cache path (mode='flashsvd')")
+
+
+# the rank-space cache path of the reference (runtime/attn/decode_registry.py:51-150, 238-330) is a different decode
+# mode: its registry functions exist and fail the way the reference fails when those kernel files are absent
+get_flashsvd_attn_legacy_sparsekv_decode_mods = _no_legacy_kernels
+get_flashsvd_decode_attn_mods = _no_legacy_kernels
+get_default_flashsvd_attn_legacy_sparsekv_decode_mod = _no_legacy_kernels
+get_default_flashsvd_decode_attn_mod = _no_legacy_kernels
+resolve_legacy_sparsekv_decode_variant = _no_legacy_kernels
+resolve_decode_variant = _no_legacy_kernels
+select_legacy_sparsekv_decode_variant = _no_legacy_kernels
+select_decode_variant = _no_legacy_kernels
 
 
 def manual_llama_decode_step(model, input_ids: torch.Tensor, *, past_key_values, cache_position: torch.Tensor,

@@ -99,3 +99,65 @@ def test_kernel_wrappers_validate_before_launch():
 def test_generate_text_needs_a_model():
     with pytest.raises(TypeError):
         R.generate_text(object(), None, prompt="x")
+
+
+def test_every_name_of_the_reference_runtime_packages_is_importable():
+    # runtime/attn/__init__.py:19-33, runtime/cache/__init__.py:6-10, kernels/mlp/decode/dual_split_triton.py:974-983
+    names = ("call_flash_attn_with_kvcache", "get_default_flashsvd_decode_attn_mod",
+             "get_default_flashsvd_attn_legacy_sparsekv_decode_mod", "get_dense_token_decode_mod",
+             "get_flash_attn_with_kvcache", "get_flashsvd_decode_attn_mods", "get_flashsvd_attn_legacy_sparsekv_decode_mods",
+             "get_flashsvd_v15_attn_densekv_decode_mod", "maybe_kwargs", "resolve_decode_variant",
+             "resolve_legacy_sparsekv_decode_variant", "select_decode_variant", "select_legacy_sparsekv_decode_variant",
+             "FlashSVDLegacySparseKVCache", "FlashSVDV15DenseKVCache", "LowRankKVCache",
+             "flashsvd_mlp_dual_split_triton_v1", "flashsvd_mlp_dual_split_triton_v2", "flashsvd_mlp_dual_split_triton_v2_sm80",
+             "flashsvd_mlp_dual_split_triton_v3", "flashsvd_ffn_dual_split_token", "flashsvd_ffn_dual_split_token_v2",
+             "flashsvd_ffn_dual_split_token_v2_sm80", "flashsvd_ffn_dual_split_token_v3")
+    for n in names:
+        assert callable(getattr(R, n)), n
+    mod = R.get_flashsvd_v15_attn_densekv_decode_mod()
+    assert mod is R.get_dense_token_decode_mod()
+    for n in ("reconstruct_qkv_token", "reconstruct_qkv_token_shared", "reconstruct_qkv_token_shared_hetero",
+              "reconstruct_qkv_token_shared_prepacked", "pack_qkv_shared_bases"):
+        assert callable(getattr(mod, n))
+    assert R.get_flash_attn_with_kvcache() is R.flash_attn_with_kvcache
+    # the rank-space path is another decode mode: its registry fails as the reference's does without its kernel files
+    with pytest.raises(ImportError, match="Failed to load any decode attention module"):
+        R.get_flashsvd_decode_attn_mods()
+    with pytest.raises(NotImplementedError):
+        R.LowRankKVCache(None, max_batch_size=1, max_cache_len=8)
+
+
+def test_maybe_kwargs_and_wrapper_argument_checks():
+    def f(a, b=1, *, c=2):
+        return a
+
+    assert R.maybe_kwargs(f, {"b": 3, "c": 4, "d": 5}) == {"b": 3, "c": 4}
+    assert R.maybe_kwargs(len, {"x": 1}) in ({}, {"x": 1})      # builtins may hide their signature
+    t = torch.zeros
+    with pytest.raises(AssertionError):                          # CPU tensors are refused first, as in the reference
+        R.flashsvd_mlp_dual_split_triton_v1(t(1, 1, 8), t(1, 1, 8), t(8, 32), t(8, 32), t(32, 8), t(8, 16))
+    with pytest.raises(ValueError, match="only the decode call of the reference"):
+        R.flash_attn_with_kvcache(t(1, 1, 2, 64), t(1, 8, 2, 64), t(1, 8, 2, 64), cache_seqlens=t(1), dropout_p=0.1)
+    with pytest.raises(ValueError, match="expects CUDA tensors"):
+        R.flash_attn_with_kvcache(t(1, 1, 2, 64), t(1, 8, 2, 64), t(1, 8, 2, 64), cache_seqlens=t(1))
+
+
+def test_module_level_names_of_the_reference_models_module():
+    # models/llama.py is absent from the reference tree; these names come from its call sites
+    # (utils/model_utils.py:441-445, 768-786; benchmark/mlp/bench_real_checkpoint_mlp.py:78-86)
+    from flashsvd_b200 import modules as M
+    from oracle import lowrank_llama as O
+
+    rope = M.LlamaRotaryEmbedding(64, max_position_embeddings=128, base=10000.0)
+    x = torch.zeros(2, 5, 64)
+    cos, sin = rope(x, torch.arange(5).expand(2, 5))
+    assert cos.shape == (2, 5, 64) and torch.equal(cos[..., :32], cos[..., 32:])
+    tab_c, tab_s = O.rope_tables(8, 64, 10000.0, torch.float32)         # the oracle's half-width tables
+    assert torch.allclose(cos[0, :, :32], tab_c[:5], atol=1e-6) and torch.allclose(sin[1, :, :32], tab_s[:5], atol=1e-6)
+    c8, _ = rope(x, seq_len=8)
+    assert c8.shape == (8, 64)
+    assert M.enable_flashsvd_llama_layer_tail_cuda_graph() is False
+    mlp = M.SVD_LlamaMLP(64, 96, "silu", ratio=0.5)
+    for name in ("_flashsvd_graph_cache", "_flashsvd_layer_graph_cache"):
+        assert getattr(mlp, name) == {}
+        getattr(mlp, name).clear()
