@@ -57,3 +57,19 @@ def test_tp_layer_entry_rejects_null_arguments_before_any_launch():
     assert lib.fsvd_tp_decode_layer(C.byref(dims), C.byref(layer), None, None, None, None, None, None, None, None, None,
                                     None, 0, None) == -1
     assert lib.fsvd_exchange_set_trace(None, None, 0) == -1
+
+
+def test_trace_summary_arithmetic():
+    import torch
+
+    ex = object.__new__(TP.PeerExchange)
+    ex._trace = None
+    assert ex.trace_summary() == {"exchanges": 0}
+    t = torch.zeros(8, 3, dtype=torch.int64)
+    base = 1_000_000
+    for i, (wait_ns, red_ns) in enumerate(((2000, 5000), (1000, 4000), (3000, 6000), (50000, 5000))):
+        t[i] = torch.tensor([base, base + wait_ns, base + wait_ns + red_ns])
+    ex._trace = t                                     # four records written, four still empty
+    s = ex.trace_summary()
+    assert s["exchanges"] == 4 and s["wait_us_max"] == 50.0
+    assert s["wait_us_median"] == pytest.approx(2.5) and s["reduce_us_median"] == pytest.approx(5.0)
