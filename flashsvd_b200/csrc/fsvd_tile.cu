@@ -18,8 +18,15 @@
 //   * epilogues: store / residual / SwiGLU (two accumulators) / RoPE + q buffer / RoPE + key cache /
 //     value cache, with the rounding points of the PyTorch low-rank path (every nn.Linear output
 //     rounded to bf16), the same as the interpreter's.
-// A decoder layer is 13 launches on the caller's stream (2 RMSNorm, 9 GEMMs over its 13 factors,
-// attention, and the split merge inside the kernels); a model step is captured once into a CUDA graph.
+// A decoder layer is 12 launches on the caller's stream (2 RMSNorm, 9 GEMM launches over its 13
+// factors with the q / k / v lifts grouped, attention with the split merge inside the kernel); a
+// model step is captured once into a CUDA graph.  Attention: batch_attn_kernel (1 or 2 query heads per
+// kv head, shuffle-reduced dot products at the HBM rate), gqa_decode_attn_kernel (4 or 8: the heads as
+// rows of a tensor-core tile), prompt_attn_kernel (causal attention of a prompt pass).
+// Tensor-parallel layer (fsvd_tile_tp_decode_layer): the o lift and the down lift end in the push
+// epilogue (TE_PUSH: partial sums stored into every rank's exchange region over peer memory, one flag
+// per CTA), exchange_reduce_rows_kernel sums them in rank order with the residual and applies the
+// RMSNorm that follows; protocol in fsvd_exchange.h.
 //
 // Reference functions replaced: kernels/mlp/decode/dual_split_triton_pcat_s.py:39-120 (token-tiled
 // SwiGLU MLP), kernels/attn/decode/densekv_reconstruct_triton.py:464-760 (q/k/v lift),
