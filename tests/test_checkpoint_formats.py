@@ -191,3 +191,78 @@ def test_pickle_shims_exist_only_during_a_load():
         assert float(act.SiLUActivation()(torch.tensor(0.0))) == 0.0
     assert hasattr(act, "SiLUActivation") == had
     assert "modules.module" not in sys.modules
+
+
+# ---- pinned against the reference's own helpers (tests/golden/make_checkpoint_golden.py ran them)
+def _golden():
+    from pathlib import Path
+
+    return json.loads((Path(__file__).parent / "golden" / "checkpoint_format_cases.json").read_text())
+
+
+def test_key_sets_and_destinations_match_the_reference_functions():
+    g = _golden()
+    assert sorted(CK.expected_basis_sharing_keys(2)) == g["expected_keys_2_layers"]
+    assert len(g["destination"]) >= 40
+    for key, want in g["destination"].items():
+        assert CK.basis_sharing_destination(key) == want, key
+    for raw, want in g["is_basis_sharing"].items():
+        assert CK.is_basis_sharing_config(json.loads(raw)) == want, raw
+    for raw, want in g["dtype"].items():
+        assert str(CK._DTYPES.get(raw.strip().lower())) == want, raw
+
+
+def test_shard_discovery_matches_the_reference_function(tmp_path):
+    g = _golden()["shards"]
+
+    def names():
+        try:
+            return [p.name for p in CK.iter_weight_shards(tmp_path)]
+        except Exception as e:
+            return f"{type(e).__name__}: {str(e).replace(str(tmp_path), '<dir>')}"
+
+    assert names() == g["empty"]
+    for n in ("pytorch_model-00003-of-00003.bin", "pytorch_model-00001-of-00003.bin", "pytorch_model-00002-of-00003.bin"):
+        (tmp_path / n).write_bytes(b"")
+    assert names() == g["numbered"]
+    (tmp_path / "pytorch_model.bin").write_bytes(b"")
+    assert names() == g["single_wins_over_numbered"]
+    index = tmp_path / "pytorch_model.bin.index.json"
+    index.write_text(json.dumps({"weight_map": {"b": "pytorch_model-00002-of-00003.bin", "a": "pytorch_model-00003-of-00003.bin",
+                                                "c": "pytorch_model-00002-of-00003.bin"}}))
+    assert names() == g["index_order_of_first_mention"]
+    index.write_text(json.dumps({"weight_map": {"a": "missing.bin"}}))
+    assert names() == g["index_missing_file"]
+    index.write_text(json.dumps({"weight_map": {}}))
+    assert names() == g["index_empty"]
+
+
+def test_group_tying_and_trust_heuristics_match_the_reference_functions(monkeypatch):
+    from transformers import LlamaConfig
+
+    g = _golden()
+    cfg = LlamaConfig(**dict(CFG, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+                             num_key_value_heads=1, vocab_size=20))
+    model = DS.build_svd_llama(cfg)
+    L = model.model.layers
+    for holder, lin in (("self_attn", "q_v_proj"), ("mlp", "down_v_proj")):
+        getattr(getattr(L[1], holder), lin).weight.data.copy_(getattr(getattr(L[0], holder), lin).weight.data)
+    CK.tie_basis_groups(model, {"q_groups": [[0, 1]], "down_groups": [[0, 1]], "k_groups": [[0], [1]], "o_groups": "x"})
+    got = {"q_v_proj": L[0].self_attn.q_v_proj.weight is L[1].self_attn.q_v_proj.weight,
+           "down_v_proj": L[0].mlp.down_v_proj.weight is L[1].mlp.down_v_proj.weight,
+           "k_v_proj": L[0].self_attn.k_v_proj.weight is L[1].self_attn.k_v_proj.weight,
+           "o_v_proj": L[0].self_attn.o_v_proj.weight is L[1].self_attn.o_v_proj.weight}
+    assert got == g["tied"]
+    with pytest.raises(ValueError) as e:
+        CK.tie_basis_groups(DS.build_svd_llama(cfg), {"up_groups": [[0, 1]]})
+    assert str(e.value).split("max diff")[0] == g["tie_errors"]["not_shared"].split("max diff")[0]
+    bad = DS.build_svd_llama(cfg)
+    bad.model.layers[1].mlp.gate_v_proj = nn.Linear(32, 4, bias=False)
+    with pytest.raises(ValueError) as e:
+        CK.tie_basis_groups(bad, {"gate_groups": [[0, 1]]})
+    assert str(e.value) == g["tie_errors"]["shape"]
+    # file names the reference treats as its own outputs (it also asks that the file lies inside its
+    # checkout; this package looks at the name only)
+    monkeypatch.delenv("FLASH_SVD_TRUST_PICKLE", raising=False)
+    for name, want in g["trusted_name"].items():
+        assert CK.is_trusted_pickle("/somewhere/" + name) == want, name
