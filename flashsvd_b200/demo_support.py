@@ -153,7 +153,8 @@ def decode_kvcache_eval(model, *, prompt_len: int = 2048, new_tokens: int = 128,
     """Decode benchmark with the reference's protocol (utils/evaluator.py:272-540): a prompt of
     ``prompt_len`` random tokens fills the cache, ``warmup`` untimed steps, then ``new_tokens`` timed
     single-token steps between CUDA events.  ``model`` is a ``DecodeEngine`` or a model with low-rank
-    modules.  Returns decode_ms_per_token and decode_tokens_per_s (plus the sizes)."""
+    modules.  Returns the reference's result dictionary (sizes, prefill / decode seconds and tokens/s,
+    decode_ms_per_token, the three cache flags)."""
     from .engine import DecodeEngine, engine_for_model
 
     del flags
@@ -165,22 +166,29 @@ def decode_kvcache_eval(model, *, prompt_len: int = 2048, new_tokens: int = 128,
     vocab = eng.vocab
     prompt = torch.randint(0, vocab, (eng.B, int(prompt_len)), device=eng.device, dtype=torch.int32)
     eng.reset()
-    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
     e0.record()
     eng.prefill(prompt)
     e1.record()
     if warmup > 0:
         eng.step(int(warmup))
     torch.cuda.synchronize()
-    e1.record()
-    eng.step(int(new_tokens))
     e2.record()
+    eng.step(int(new_tokens))
+    e3.record()
     torch.cuda.synchronize()
-    ms = e1.elapsed_time(e2)
+    t_prefill, t_decode = e0.elapsed_time(e1) * 1e-3, e2.elapsed_time(e3) * 1e-3
     if eng.status() != 0:
         raise RuntimeError("a device-side wait ran out during the benchmark")
+    inf = float("inf")
+    decode_tok_s = eng.B * int(new_tokens) / t_decode if t_decode > 0 else inf
+    # the keys of the reference's result (utils/evaluator.py:529-541); decode_tokens_per_s = decode_tok_s
     return {"prompt_len": int(prompt_len), "new_tokens": int(new_tokens), "batch_size": int(eng.B),
-            "decode_ms_per_token": ms / int(new_tokens), "decode_tokens_per_s": eng.B * int(new_tokens) / (ms * 1e-3)}
+            "prefill_time_s": float(t_prefill), "decode_time_s": float(t_decode),
+            "prefill_tok_s": eng.B * int(prompt_len) / t_prefill if t_prefill > 0 else inf,
+            "decode_tok_s": float(decode_tok_s), "decode_ms_per_token": t_decode * 1000.0 / max(1, int(new_tokens)),
+            "lowrank_cache": False, "flashsvd_dense_cache": True, "baseline_dense_kvcache": False,
+            "decode_tokens_per_s": float(decode_tok_s)}
 
 
 __all__ = ["__version__", "cast_model_for_inference", "configure_runtime", "decode_kvcache_eval", "generate_text",
