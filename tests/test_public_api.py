@@ -108,3 +108,41 @@ def test_cache_is_a_transformers_cache_with_direct_write_step():
                                                cache_position=torch.tensor([1, 2])) is None
     with pytest.raises(IndexError):
         cache.prepare_fa2_direct_write_step(0, batch_size=2, num_heads=4, head_dim=64, q_len=1, cache_position=8)
+
+
+def test_decode_kvcache_eval_returns_the_reference_result_keys(monkeypatch):
+    """The benchmark helper's control flow and result dictionary (utils/evaluator.py:529-541) on a
+    stand-in engine and stand-in CUDA events: no GPU, nothing is computed."""
+    import torch
+
+    from flashsvd_b200 import demo_support
+    from flashsvd_b200.engine import DecodeEngine
+
+    clock = {"t": 0.0}
+
+    class Event:
+        def __init__(self, enable_timing=False):
+            self.t = None
+
+        def record(self):
+            self.t = clock["t"]
+
+        def elapsed_time(self, other):
+            return (other.t - self.t) * 1e3
+
+    monkeypatch.setattr(torch.cuda, "Event", Event)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    eng = object.__new__(DecodeEngine)
+    eng.B, eng.vocab, eng.device = 2, 50, torch.device("cpu")
+    calls = []
+    eng.reset = lambda: calls.append("reset")
+    eng.prefill = lambda prompt: (calls.append(("prefill", tuple(prompt.shape))), clock.__setitem__("t", clock["t"] + 0.5))
+    eng.step = lambda n: (calls.append(("step", n)), clock.__setitem__("t", clock["t"] + 0.01 * n))
+    eng.status = lambda: 0
+    out = demo_support.decode_kvcache_eval(eng, prompt_len=10, new_tokens=20, warmup=3)
+    assert calls == ["reset", ("prefill", (2, 10)), ("step", 3), ("step", 20)]
+    assert set(out) >= {"prompt_len", "new_tokens", "batch_size", "prefill_time_s", "decode_time_s", "prefill_tok_s",
+                        "decode_tok_s", "decode_ms_per_token", "lowrank_cache", "flashsvd_dense_cache", "baseline_dense_kvcache"}
+    assert out["prefill_time_s"] == pytest.approx(0.5) and out["decode_time_s"] == pytest.approx(0.2)
+    assert out["decode_ms_per_token"] == pytest.approx(10.0) and out["decode_tok_s"] == pytest.approx(200.0)
+    assert out["prefill_tok_s"] == pytest.approx(40.0) and out["flashsvd_dense_cache"] is True
