@@ -623,10 +623,29 @@ def manual_llama_decode_step(model, input_ids: torch.Tensor, *, past_key_values,
 
 
 # --------------------------------------------------------------------------------- generation
+def _sample_next_token(logits: torch.Tensor, *, do_sample: bool, temperature: float, top_p: float) -> torch.Tensor:
+    """Next token ids [B, 1] from logits [B, vocab] as the reference draws them
+    (scripts/demo_support/api.py:192-209): argmax unless sampling with a positive temperature; else
+    softmax(logits / temperature), and for top_p < 1 the nucleus = the most probable tokens up to and
+    including the first one that carries the cumulative probability past top_p, renormalised."""
+    if not do_sample or temperature <= 0.0:
+        return logits.argmax(dim=-1, keepdim=True)
+    probs = torch.softmax(logits / float(max(temperature, 1e-5)), dim=-1)
+    if float(top_p) >= 1.0:
+        return torch.multinomial(probs, num_samples=1)
+    sp, si = torch.sort(probs, dim=-1, descending=True)
+    before = torch.cumsum(sp, dim=-1) > float(top_p)        # True where the mass up to and including the token exceeds top_p
+    drop = torch.zeros_like(before)
+    drop[..., 1:] = before[..., :-1]                         # a token goes when the mass BEFORE it already exceeded top_p
+    sp = sp.masked_fill(drop, 0.0)
+    sp = sp / sp.sum(dim=-1, keepdim=True).clamp_min(1e-12)
+    return torch.gather(si, dim=-1, index=torch.multinomial(sp, num_samples=1))
+
+
 @torch.inference_mode()
 def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: int = 64, device=None,
                   do_sample: bool = False, temperature: float = 0.8, top_p: float = 0.95) -> dict:
-    """Single-prompt greedy generation on a ``DecodeEngine``; returns the reference's result dict
+    """Single-prompt generation (greedy, or sampled with temperature / top_p) on a ``DecodeEngine``; returns the reference's result dict
     (prompt_token_count, generated_token_count, output_ids, completion_ids, text, completion_text).
     Generation stops after an end-of-sequence token, like the reference loop."""
     from .engine import DecodeEngine, engine_for_model, has_lowrank_modules
@@ -637,13 +656,9 @@ def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: in
                 raise TypeError("generate_text takes a DecodeEngine, a model with low-rank modules or a transformers model")
             return _generate_text_generic(model, tokenizer, prompt=prompt, max_new_tokens=max_new_tokens, device=device,
                                           do_sample=do_sample, temperature=temperature, top_p=top_p)
-        if do_sample:
-            raise NotImplementedError("the decode kernel samples greedily (do_sample=False)")
         enc0 = tokenizer(prompt, return_tensors="pt", add_special_tokens=False)
         need = int(enc0["input_ids"].shape[1]) + int(max_new_tokens)
         model = engine_for_model(model, batch_size=1, max_cache_len=need + 4)
-    if do_sample:
-        raise NotImplementedError("the decode kernel samples greedily (do_sample=False)")
     enc = tokenizer(prompt, return_tensors="pt", add_special_tokens=False)
     input_ids = enc["input_ids"]
     if int(input_ids.shape[0]) != 1:
@@ -654,12 +669,25 @@ def generate_text(model: Any, tokenizer: Any, *, prompt: str, max_new_tokens: in
         raise IndexError(f"prompt of {prompt_len} tokens + {max_new_tokens} new tokens exceeds the cache length {model.S_max}")
     model.reset()
     model.prefill(input_ids)
-    if max_new_tokens > 1:
-        model.step(max_new_tokens - 1)
-    new = model.last_tokens(max_new_tokens)[:, 0].cpu().tolist() if max_new_tokens else []
+    eos = getattr(tokenizer, "eos_token_id", None)
+    if do_sample and float(temperature) > 0.0 and max_new_tokens:
+        # sampled: the kernel leaves the logits of every step on the device; the token drawn from them
+        # on the host side of the API is written back as the next step's input (the kernel's own greedy
+        # choice is overwritten), one launch per token
+        new = []
+        for i in range(max_new_tokens):
+            nxt = _sample_next_token(model.logits[:1].float(), do_sample=True, temperature=temperature, top_p=top_p)
+            new.append(int(nxt[0, 0]))
+            if (eos is not None and new[-1] == int(eos)) or i + 1 == max_new_tokens:
+                break
+            model.tokens.copy_(nxt.view(-1).to(torch.int32))
+            model.step(1)
+    else:
+        if max_new_tokens > 1:
+            model.step(max_new_tokens - 1)
+        new = model.last_tokens(max_new_tokens)[:, 0].cpu().tolist() if max_new_tokens else []
     if model.status() != 0:
         raise RuntimeError("a device-side wait ran out during generation")
-    eos = getattr(tokenizer, "eos_token_id", None)
     if eos is not None and int(eos) in new:
         new = new[: new.index(int(eos)) + 1]
     output_ids = input_ids[0].tolist() + new
@@ -688,14 +716,7 @@ def _generate_text_generic(model, tokenizer, *, prompt, max_new_tokens, device, 
     past, logits = out.past_key_values, out.logits[:, -1, :]
     new = []
     for _ in range(int(max_new_tokens)):
-        if do_sample:
-            probs = torch.softmax(logits.float() / max(float(temperature), 1e-5), -1)
-            sp, si = torch.sort(probs, descending=True)
-            keep = torch.cumsum(sp, -1) - sp < float(top_p)
-            sp = sp * keep
-            nxt = si.gather(-1, torch.multinomial(sp / sp.sum(-1, keepdim=True), 1))
-        else:
-            nxt = logits.argmax(-1, keepdim=True)
+        nxt = _sample_next_token(logits.float(), do_sample=do_sample, temperature=float(temperature), top_p=float(top_p))
         new.append(int(nxt[0, 0]))
         if eos is not None and new[-1] == int(eos):
             break

@@ -161,3 +161,58 @@ def test_module_level_names_of_the_reference_models_module():
     for name in ("_flashsvd_graph_cache", "_flashsvd_layer_graph_cache"):
         assert getattr(mlp, name) == {}
         getattr(mlp, name).clear()
+
+
+def test_sampler_draws_the_reference_samplers_tokens():
+    """Same seeded logits, same seeded generator: the tokens of the reference's _sample_next_token
+    (scripts/demo_support/api.py:192-209), recorded by tests/golden/make_sampling_golden.py."""
+    cases = json.loads((GOLD / "sampling_cases.json").read_text())
+    assert len(cases) >= 7
+    for c in cases:
+        logits = torch.randn(3, c["vocab"], generator=torch.Generator().manual_seed(100 + c["seed"])) * 3.0
+        torch.manual_seed(c["seed"])
+        draws = [R._sample_next_token(logits, do_sample=c["do_sample"], temperature=c["temperature"], top_p=c["top_p"]).view(-1).tolist()
+                 for _ in range(6)]
+        assert draws == c["draws"], c
+
+
+def test_generate_text_samples_through_the_engine_api(monkeypatch):
+    """Sampled generation on a stand-in engine: logits read after every step, the drawn token written
+    back as the next input, one step per token, stop at the end-of-sequence token."""
+    from flashsvd_b200.engine import DecodeEngine
+
+    eng = object.__new__(DecodeEngine)
+    eng.B, eng.vocab, eng.S_max = 1, 6, 64
+    state = {"logits": torch.full((1, 6), -50.0), "tokens": torch.zeros(1, dtype=torch.int32), "steps": 0, "fed": []}
+    order = [4, 2, 5, 1]          # the only token with mass at each step
+
+    def refresh():
+        state["logits"].fill_(-50.0)
+        state["logits"][0, order[min(state["steps"], len(order) - 1)]] = 50.0
+
+    def step(n):
+        assert n == 1
+        state["fed"].append(int(state["tokens"][0]))
+        state["steps"] += 1
+        refresh()
+
+    eng.reset = lambda: None
+    eng.prefill = lambda ids: refresh()
+    eng.step = step
+    eng.status = lambda: 0
+    monkeypatch.setattr(DecodeEngine, "logits", property(lambda self: state["logits"]))
+    monkeypatch.setattr(DecodeEngine, "tokens", property(lambda self: state["tokens"]))
+
+    class Tok:
+        eos_token_id = 5
+
+        def __call__(self, prompt, **kw):
+            return {"input_ids": torch.tensor([[1, 2, 3]])}
+
+        def decode(self, ids, **kw):
+            return " ".join(str(i) for i in ids)
+
+    out = R.generate_text(eng, Tok(), prompt="x", max_new_tokens=8, do_sample=True, temperature=0.7, top_p=0.9)
+    assert out["completion_ids"] == [4, 2, 5]            # stops at the end-of-sequence token
+    assert state["fed"] == [4, 2]                        # each drawn token became the next step's input
+    assert out["output_ids"] == [1, 2, 3, 4, 2, 5] and out["generated_token_count"] == 3
