@@ -157,7 +157,10 @@ def decode_kvcache_eval(model, *, prompt_len: int = 2048, new_tokens: int = 128,
     decode_ms_per_token, the three cache flags)."""
     from .engine import DecodeEngine, engine_for_model
 
-    del flags
+    if flags.get("lowrank_cache", False):
+        raise NotImplementedError("lowrank_cache=True selects the reference's rank-space cache mode; flashsvd_b200 serves the "
+                                  "dense-cache decode (flashsvd_dense_cache)")
+    echo = {k: bool(flags.get(k, False)) for k in ("lowrank_cache", "flashsvd_dense_cache", "baseline_dense_kvcache")}
     if max_cache_len is None:
         max_cache_len = int(prompt_len) + int(warmup) + int(new_tokens) + 1
     eng = model if isinstance(model, DecodeEngine) else engine_for_model(
@@ -187,7 +190,7 @@ def decode_kvcache_eval(model, *, prompt_len: int = 2048, new_tokens: int = 128,
             "prefill_time_s": float(t_prefill), "decode_time_s": float(t_decode),
             "prefill_tok_s": eng.B * int(prompt_len) / t_prefill if t_prefill > 0 else inf,
             "decode_tok_s": float(decode_tok_s), "decode_ms_per_token": t_decode * 1000.0 / max(1, int(new_tokens)),
-            "lowrank_cache": False, "flashsvd_dense_cache": True, "baseline_dense_kvcache": False,
+            **echo,   # the flags as passed, like the reference; the cache is the dense [B, S, Hk, Dh] one whatever they say
             "decode_tokens_per_s": float(decode_tok_s)}
 
 

@@ -139,10 +139,14 @@ def test_decode_kvcache_eval_returns_the_reference_result_keys(monkeypatch):
     eng.prefill = lambda prompt: (calls.append(("prefill", tuple(prompt.shape))), clock.__setitem__("t", clock["t"] + 0.5))
     eng.step = lambda n: (calls.append(("step", n)), clock.__setitem__("t", clock["t"] + 0.01 * n))
     eng.status = lambda: 0
-    out = demo_support.decode_kvcache_eval(eng, prompt_len=10, new_tokens=20, warmup=3)
+    with pytest.raises(NotImplementedError):
+        demo_support.decode_kvcache_eval(eng, prompt_len=10, new_tokens=20, lowrank_cache=True)
+    out = demo_support.decode_kvcache_eval(eng, prompt_len=10, new_tokens=20, warmup=3, flashsvd_dense_cache=True,
+                                           profile_decode=False)
     assert calls == ["reset", ("prefill", (2, 10)), ("step", 3), ("step", 20)]
     assert set(out) >= {"prompt_len", "new_tokens", "batch_size", "prefill_time_s", "decode_time_s", "prefill_tok_s",
                         "decode_tok_s", "decode_ms_per_token", "lowrank_cache", "flashsvd_dense_cache", "baseline_dense_kvcache"}
     assert out["prefill_time_s"] == pytest.approx(0.5) and out["decode_time_s"] == pytest.approx(0.2)
     assert out["decode_ms_per_token"] == pytest.approx(10.0) and out["decode_tok_s"] == pytest.approx(200.0)
     assert out["prefill_tok_s"] == pytest.approx(40.0) and out["flashsvd_dense_cache"] is True
+    assert out["lowrank_cache"] is False and out["baseline_dense_kvcache"] is False
