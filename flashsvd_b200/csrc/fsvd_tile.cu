@@ -1668,6 +1668,17 @@ struct LayerPlan {
   AttnArgs at;
 };
 
+// The largest segment count, from the largest of the three planned counts (at most the smallest
+// number of k-blocks) down to 2, that cuts all three K ranges into exactly that many non-empty
+// segments; 0 when there is none.
+static int common_segments(int nkb_q, int nkb_k, int nkb_v, int segs_q, int segs_k, int segs_v) {
+  auto segs_for = [](int nkb, int want) { const int kbs = (nkb + want - 1) / want; return (nkb + kbs - 1) / kbs; };
+  const int nkb_min = std::min(nkb_q, std::min(nkb_k, nkb_v));
+  for (int S = std::min(std::max(segs_q, std::max(segs_k, segs_v)), nkb_min); S >= 2; --S)
+    if (segs_for(nkb_q, S) == S && segs_for(nkb_k, S) == S && segs_for(nkb_v, S) == S) return S;
+  return 0;
+}
+
 static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, const void* cos_tab, const void* sin_tab,
                       const int* seqlens, const void* x_in, void* x_out, char* ws, const TileWs& L, long long wait_limit,
                       const void* xn_in = nullptr) {
@@ -1699,21 +1710,20 @@ static int plan_layer(LayerPlan& lp, const fsvd_dims& D, const fsvd_layer& Lw, c
   if (lp.g[1].a.segs != lp.g[2].a.segs || lp.g[1].a.segs != lp.g[3].a.segs) {
     // the three lifts go out as one launch when they cut K into the same number of segments: look for
     // a count (>= 2) that all three can take
-    const int nkb_min = std::min(lp.g[1].a.nkb, std::min(lp.g[2].a.nkb, lp.g[3].a.nkb));
-    auto segs_for = [](int nkb, int want) { const int kbs = (nkb + want - 1) / want; return (nkb + kbs - 1) / kbs; };
-    for (int S = std::min(std::max(lp.g[1].a.segs, std::max(lp.g[2].a.segs, lp.g[3].a.segs)), nkb_min); S >= 2; --S) {
-      if (segs_for(lp.g[1].a.nkb, S) != S || segs_for(lp.g[2].a.nkb, S) != S || segs_for(lp.g[3].a.nkb, S) != S) continue;
+    const int S = common_segments(lp.g[1].a.nkb, lp.g[2].a.nkb, lp.g[3].a.nkb, lp.g[1].a.segs, lp.g[2].a.segs, lp.g[3].a.segs);
+    if (S >= 2) {
       LayerPlan t = lp;
-      if (plan_gemm(t.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc, S)) break;
-      if (plan_gemm(t.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sc, S)) break;
-      if (plan_gemm(t.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc, S)) break;
-      if (t.g[1].a.segs != S || t.g[2].a.segs != S || t.g[3].a.segs != S) break;
-      t.g[1].a.out = qb;
-      rope(t.g[1].a, nullptr);
-      rope(t.g[2].a, Lw.k_cache);
-      rope(t.g[3].a, Lw.v_cache);
-      for (int i = 1; i < 4; ++i) lp.g[i] = t.g[i];
-      break;
+      const bool planned = !plan_gemm(t.g[1], Lw.q_u, nullptr, HD, D.Rq, D.Rq, pb, nullptr, Rqkv, B, TE_ROPE_Q, sc, S) &&
+                           !plan_gemm(t.g[2], Lw.k_u, nullptr, KD, D.Rk, D.Rk, pb + D.Rq, nullptr, Rqkv, B, TE_ROPE_K, sc, S) &&
+                           !plan_gemm(t.g[3], Lw.v_u, nullptr, KD, D.Rv, D.Rv, pb + D.Rq + D.Rk, nullptr, Rqkv, B, TE_VCACHE, sc, S);
+      // (the shared-memory plan may still have changed a count: then the separate plans stay)
+      if (planned && t.g[1].a.segs == S && t.g[2].a.segs == S && t.g[3].a.segs == S) {
+        t.g[1].a.out = qb;
+        rope(t.g[1].a, nullptr);
+        rope(t.g[2].a, Lw.k_cache);
+        rope(t.g[3].a, Lw.v_cache);
+        for (int i = 1; i < 4; ++i) lp.g[i] = t.g[i];
+      }
     }
   }
   // attention
@@ -2172,5 +2182,15 @@ int fsvd_tile_model_reset(fsvd_tile_model* m, void* stream) {
 // %globaltimer marks (entry, set-up done, dependency met, accumulators done, cluster barrier 1,
 // partial sums sent, cluster barrier 2, epilogue done, exit) at [cta][16]; later launches overwrite
 // earlier ones.  Not part of the public header.
+// Host arithmetic of the planner, callable without a device (unit tests): the K split of a GEMM of
+// `tiles` row tiles and `nkb` k-blocks on `sms` SMs, and the segment count the three q / k / v lifts
+// can share (0 = none: they go out as separate launches).
+extern "C" void fsvd_tile_debug_split_k(int tiles, int nkb, int sms, int* segs, int* kbs) {
+  split_k(tiles, nkb, sms, *segs, *kbs);
+}
+extern "C" int fsvd_tile_debug_common_segments(int nkb_q, int nkb_k, int nkb_v, int segs_q, int segs_k, int segs_v) {
+  return common_segments(nkb_q, nkb_k, nkb_v, segs_q, segs_k, segs_v);
+}
+
 extern "C" void fsvd_tile_debug_trace(void* dev_ptr) { g_tile_trace = reinterpret_cast<unsigned long long*>(dev_ptr); }
 extern "C" void fsvd_tile_debug_trace_epilogue(int epi) { g_tile_trace_epi = epi; }   // -1: every GEMM
